@@ -1,0 +1,11 @@
+"""B200-native generation control: sampling (penalties, temperature, top-k / top-p / min-p, greedy argmax, seeded
+draws) and DSpark speculative verification, as hand-written sm_100a CUDA behind a C ABI (include/lithos_b200.h).
+
+The Python names mirror the reference's sampler interface (monolith/nn/sampler.py, monolith/nn/sampling_ref.py).
+"""
+from .sampler import (GreedySampler, SampleOutput, SamplingParams, StochasticSampler, argmax, sample, sample_row, thresholds,
+                      warped_probabilities)
+from .verify import verify
+
+__all__ = ["GreedySampler", "StochasticSampler", "SamplingParams", "SampleOutput", "sample", "argmax", "sample_row", "thresholds",
+           "warped_probabilities", "verify"]

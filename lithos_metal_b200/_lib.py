@@ -1,0 +1,95 @@
+"""ctypes binding of the CUDA library (C ABI in include/lithos_b200.h). There is no CPU fallback: if the shared
+object is missing and cannot be built, importing the binding raises."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+LM_OK = 0
+DTYPE_BF16, DTYPE_F32 = 0, 1
+DRAW_GUMBEL, DRAW_INVERSE_CDF = 0, 1
+FLAG_TOPP_IN_TOPK = 1
+VERIFY_GREEDY, VERIFY_STOCHASTIC = 0, 1
+STATUS_GENERIC_PATH, STATUS_NAN, STATUS_NEAR_TIE, STATUS_TOPP_EDGE = 1, 2, 4, 8
+MAX_DRAFT = 15
+MAX_VOCAB = 1048576
+
+
+class SampleArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("dtype", C.c_int32), ("logits", C.c_void_p), ("rows", C.c_int64), ("vocab", C.c_int64),
+        ("row_stride", C.c_int64),
+        ("temperature", C.c_void_p), ("temperature_s", C.c_float), ("top_k", C.c_void_p), ("top_k_s", C.c_int32),
+        ("top_p", C.c_void_p), ("top_p_s", C.c_float), ("min_p", C.c_void_p), ("min_p_s", C.c_float),
+        ("flags", C.c_uint32), ("draw", C.c_int32),
+        ("history", C.c_void_p), ("hist_len", C.c_int64), ("hist_stride", C.c_int64), ("repetition_penalty", C.c_float),
+        ("presence_penalty", C.c_float),
+        ("uniforms", C.c_void_p), ("seed", C.c_uint64), ("step", C.c_uint32), ("row_offset", C.c_int64),
+        ("out_tokens", C.c_void_p), ("out_tau", C.c_void_p), ("out_stats", C.c_void_p), ("out_probs", C.c_void_p), ("probs_stride", C.c_int64),
+        ("out_status", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
+class VerifyArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("mode", C.c_int32), ("dtype", C.c_int32), ("n_draft", C.c_int32), ("target_logits", C.c_void_p),
+        ("vocab", C.c_int64), ("row_stride", C.c_int64), ("draft_ids", C.c_void_p), ("draft_probs", C.c_void_p), ("probs_stride", C.c_int64),
+        ("temperature", C.c_float), ("tau", C.c_void_p), ("u_accept", C.c_void_p), ("u_final", C.c_void_p),
+        ("out_accept", C.c_void_p), ("out_final", C.c_void_p), ("out_tokens", C.c_void_p), ("out_p_draft", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
+EXPORTS = ["lm_sample", "lm_argmax", "lm_verify", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
+           "lm_error_string", "lm_last_cuda_error", "lm_device_sm_count"]
+
+_lib = None
+
+
+def library_path() -> str:
+    return _build.OUT
+
+
+def lib():
+    """The loaded library (built on first use if the in-tree shared object is missing or older than its sources)."""
+    global _lib
+    if _lib is None:
+        path = _build.build() if os.environ.get("LITHOS_B200_NO_BUILD") != "1" else _build.OUT
+        if not os.path.exists(path):
+            raise RuntimeError(f"lithos_metal_b200: CUDA library {path} is missing; run `python -m lithos_metal_b200.build`")
+        L = C.CDLL(path)
+        L.lm_sample.restype = C.c_int
+        L.lm_sample.argtypes = [C.POINTER(SampleArgs)]
+        L.lm_verify.restype = C.c_int
+        L.lm_verify.argtypes = [C.POINTER(VerifyArgs)]
+        L.lm_argmax.restype = C.c_int
+        L.lm_argmax.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.lm_workspace_bytes.restype = C.c_size_t
+        L.lm_workspace_bytes.argtypes = [C.c_int64, C.c_int64]
+        L.lm_verify_workspace_bytes.restype = C.c_size_t
+        L.lm_verify_workspace_bytes.argtypes = [C.c_int32, C.c_int64]
+        L.lm_uniform01.restype = C.c_float
+        L.lm_uniform01.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32]
+        L.lm_abi_version.restype = C.c_int
+        L.lm_error_string.restype = C.c_char_p
+        L.lm_error_string.argtypes = [C.c_int]
+        L.lm_last_cuda_error.restype = C.c_char_p
+        L.lm_device_sm_count.restype = C.c_int
+        if L.lm_abi_version() != 1:
+            raise RuntimeError("lithos_metal_b200: ABI version mismatch between the binding and the shared object")
+        _lib = L
+    return _lib
+
+
+class LithosError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc != LM_OK:
+        L = lib()
+        detail = L.lm_last_cuda_error().decode() if rc == -3 else ""
+        raise LithosError(f"{what}: {L.lm_error_string(rc).decode()} ({rc}){': ' + detail if detail else ''}")

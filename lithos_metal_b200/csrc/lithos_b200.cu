@@ -1,0 +1,230 @@
+// C ABI of the B200 generation-control library (declared in include/lithos_b200.h): argument checks, launch
+// geometry, kernel launches. No allocation, no synchronisation, no CPU arithmetic on the data path.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "sample_generic.cuh"
+#include "verify.cuh"
+
+namespace lm {
+
+// ---- greedy argmax: rows x splits blocks, packed (value, lowest index) maxima meet in the workspace --------------
+constexpr int kArgmaxBlock = 512;
+
+struct ArgmaxWs { unsigned long long best; unsigned arrivals; unsigned pad; };   // one per row, zero when idle
+
+__global__ void __launch_bounds__(kArgmaxBlock) argmax_kernel(const void* logits, int dtype, int rows, int vocab, int64_t row_stride, int splits,
+                                                             int32_t* out_tokens, ArgmaxWs* ws) {
+  __shared__ uint64_t scratch[32];
+  const int row = blockIdx.y, split = blockIdx.x, tid = threadIdx.x;
+  RowView rv;
+  rv.dtype = dtype; rv.vocab = vocab; rv.pen = nullptr; rv.rho = 1.0f; rv.pi = 0.0f;
+  rv.row = static_cast<const char*>(logits) + static_cast<size_t>(row) * static_cast<size_t>(row_stride) * (dtype == LM_DTYPE_BF16 ? 2 : 4);
+  rv.aligned = (reinterpret_cast<uintptr_t>(rv.row) & 15u) == 0;
+  const int n_chunks = (vocab + kChunk - 1) / kChunk;
+  uint64_t best = 0ull;
+  for (int c = split * kArgmaxBlock + tid; c < n_chunks; c += splits * kArgmaxBlock) {
+    float z[kChunk];
+    const int n = load_chunk(rv, c, z);
+#pragma unroll
+    for (int e = 0; e < kChunk; e++) if (e < n) {
+      const uint64_t p = pack_best(z[e], static_cast<uint32_t>(c * kChunk + e));
+      best = p > best ? p : best;
+    }
+  }
+  best = block_max_u64(best, scratch);
+  if (tid != 0) return;
+  if (splits == 1) { out_tokens[row] = best ? static_cast<int>(best_index(best)) : -1; return; }
+  if (best) atomicMax(&ws[row].best, static_cast<unsigned long long>(best));
+  __threadfence();
+  if (atomicAdd(&ws[row].arrivals, 1u) == static_cast<unsigned>(splits) - 1u) {   // the last block of the row
+    __threadfence();
+    const unsigned long long b = atomicExch(&ws[row].best, 0ull);
+    ws[row].arrivals = 0u;
+    out_tokens[row] = b ? static_cast<int>(best_index(b)) : -1;
+  }
+}
+
+// ---- the generic sampler: one block per row, grid-stride over rows ------------------------------------------------
+__global__ void __launch_bounds__(kBlock, 1) sample_generic_kernel(SampleDev P) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  GenericSmem& s = *reinterpret_cast<GenericSmem*>(smem_raw);
+  uint32_t* pen_bits = reinterpret_cast<uint32_t*>(smem_raw + sizeof(GenericSmem));
+  for (int row = blockIdx.x; row < P.rows; row += gridDim.x) {
+    if (P.row_select != nullptr && P.row_select[row] == 0u) continue;
+    sample_row_generic(P, row, s, pen_bits);
+    __syncthreads();
+  }
+}
+
+thread_local char g_cuda_error[256] = "";
+
+static int cuda_fail(cudaError_t e) {
+  std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+  return LM_E_CUDA;
+}
+
+static int sm_count(int* out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  static thread_local int cached_dev = -1, cached = 0;
+  if (cached_dev != dev) {
+    e = cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    cached_dev = dev;
+  }
+  *out = cached;
+  return LM_OK;
+}
+
+static size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+}  // namespace lm
+
+using namespace lm;
+
+extern "C" {
+
+int lm_abi_version(void) { return LM_ABI_VERSION; }
+
+const char* lm_error_string(int code) {
+  switch (code) {
+    case LM_OK: return "ok";
+    case LM_E_INVALID: return "invalid argument";
+    case LM_E_WORKSPACE: return "workspace missing, misaligned or too small";
+    case LM_E_CUDA: return "CUDA runtime error";
+    case LM_E_UNSUPPORTED: return "size outside the supported range";
+    default: return "unknown error";
+  }
+}
+
+const char* lm_last_cuda_error(void) { return g_cuda_error; }
+
+int lm_device_sm_count(void) {
+  int n = 0;
+  const int rc = sm_count(&n);
+  return rc == LM_OK ? n : rc;
+}
+
+float lm_uniform01(uint64_t seed, uint32_t step, uint32_t t, uint32_t index) { return uniform01(seed, step, t, index); }
+
+size_t lm_workspace_bytes(int64_t rows, int64_t vocab) {
+  (void)vocab;
+  if (rows < 0) rows = 0;
+  return align256(static_cast<size_t>(rows) * sizeof(ArgmaxWs)) + 256;
+}
+
+size_t lm_verify_workspace_bytes(int32_t n_draft, int64_t vocab) {
+  (void)n_draft; (void)vocab;
+  const size_t max_grid = 1024;                                          // far above any SM count
+  return align256(sizeof(VerifyWs) + sizeof(unsigned long long) * (static_cast<size_t>(kVerifyMaxRows) + 1) * max_grid);
+}
+
+int lm_argmax(const void* logits, int32_t dtype, int64_t rows, int64_t vocab, int64_t row_stride, int32_t* out_tokens, void* workspace,
+              size_t workspace_bytes, void* stream) {
+  if (rows < 0 || vocab < 0 || (dtype != LM_DTYPE_BF16 && dtype != LM_DTYPE_F32)) return LM_E_INVALID;
+  if (rows == 0) return LM_OK;
+  if (!logits || !out_tokens || row_stride < vocab) return LM_E_INVALID;
+  if (vocab > LM_MAX_VOCAB || rows > 65535 * 32) return LM_E_UNSUPPORTED;
+  int sms = 0;
+  int rc = sm_count(&sms);
+  if (rc != LM_OK) return rc;
+  const int n_chunks = static_cast<int>((vocab + kChunk - 1) / kChunk);
+  // enough blocks to cover the machine twice; a block needs at least one sweep of work
+  int splits = static_cast<int>((2 * sms + rows - 1) / rows);
+  const int max_splits = (n_chunks + kArgmaxBlock - 1) / kArgmaxBlock;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < lm_workspace_bytes(rows, vocab)))
+    return LM_E_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int64_t r0 = 0; r0 < rows; r0 += 65535) {                          // gridDim.y limit
+    const int nr = static_cast<int>(rows - r0 < 65535 ? rows - r0 : 65535);
+    const size_t esz = dtype == LM_DTYPE_BF16 ? 2 : 4;
+    argmax_kernel<<<dim3(splits, nr), kArgmaxBlock, 0, st>>>(static_cast<const char*>(logits) + static_cast<size_t>(r0) * row_stride * esz, dtype, nr,
+                                                            static_cast<int>(vocab), row_stride, splits, out_tokens + r0,
+                                                            static_cast<ArgmaxWs*>(workspace) + r0);
+  }
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+int lm_sample(const lm_sample_args* a) {
+  if (!a || a->struct_size != sizeof(lm_sample_args)) return LM_E_INVALID;
+  if (a->rows < 0 || a->vocab < 0 || (a->dtype != LM_DTYPE_BF16 && a->dtype != LM_DTYPE_F32)) return LM_E_INVALID;
+  if (a->draw != LM_DRAW_GUMBEL && a->draw != LM_DRAW_INVERSE_CDF) return LM_E_INVALID;
+  if (a->rows == 0) return LM_OK;
+  if (!a->logits || !a->out_tokens || a->row_stride < a->vocab) return LM_E_INVALID;
+  if (a->vocab > LM_MAX_VOCAB || a->rows > 0x7FFFFFFF || a->hist_len > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
+  if (a->temperature == nullptr && !(a->temperature_s >= 0.0f)) return LM_E_INVALID;
+  if (a->history != nullptr && (a->hist_len < 0 || a->hist_stride < a->hist_len)) return LM_E_INVALID;
+  if (a->history != nullptr && !(a->repetition_penalty > 0.0f)) return LM_E_INVALID;
+  if (a->out_probs != nullptr && a->probs_stride < a->vocab) return LM_E_INVALID;
+  // an all-greedy call needs no uniforms; a stochastic inverse-CDF call does
+  if (a->draw == LM_DRAW_INVERSE_CDF && a->uniforms == nullptr && (a->temperature != nullptr || a->temperature_s > 0.0f)) return LM_E_INVALID;
+
+  SampleDev P;
+  P.logits = a->logits; P.dtype = a->dtype; P.rows = static_cast<int>(a->rows); P.vocab = static_cast<int>(a->vocab); P.row_stride = a->row_stride;
+  P.temperature = a->temperature; P.temperature_s = a->temperature_s; P.top_k = a->top_k; P.top_k_s = a->top_k_s;
+  P.top_p = a->top_p; P.top_p_s = a->top_p_s; P.min_p = a->min_p; P.min_p_s = a->min_p_s;
+  P.flags = a->flags; P.draw = a->draw;
+  const bool pen = a->history != nullptr && a->hist_len > 0 && !(a->repetition_penalty == 1.0f && a->presence_penalty == 0.0f);
+  P.history = pen ? a->history : nullptr; P.hist_len = static_cast<int>(a->hist_len); P.hist_stride = a->hist_stride;
+  P.rho = a->repetition_penalty; P.pi = a->presence_penalty;
+  P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
+  P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_stats = a->out_stats; P.out_probs = a->out_probs; P.probs_stride = a->probs_stride;
+  P.out_status = a->out_status; P.row_select = nullptr;
+
+  int sms = 0;
+  int rc = sm_count(&sms);
+  if (rc != LM_OK) return rc;
+  const size_t smem = sizeof(GenericSmem) + (pen ? static_cast<size_t>((a->vocab + 31) / 32) * 4 : 0) + 16;
+  static thread_local size_t smem_set = 0;
+  if (smem > smem_set) {
+    const cudaError_t e = cudaFuncSetAttribute(sample_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return cuda_fail(e);
+    smem_set = smem;
+  }
+  const int grid = static_cast<int>(a->rows < 8LL * sms ? a->rows : 8LL * sms);
+  sample_generic_kernel<<<grid, kBlock, smem, static_cast<cudaStream_t>(a->stream)>>>(P);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+int lm_verify(const lm_verify_args* a) {
+  if (!a || a->struct_size != sizeof(lm_verify_args)) return LM_E_INVALID;
+  if (a->mode != LM_VERIFY_GREEDY && a->mode != LM_VERIFY_STOCHASTIC) return LM_E_INVALID;
+  if (a->dtype != LM_DTYPE_BF16 && a->dtype != LM_DTYPE_F32) return LM_E_INVALID;
+  if (a->n_draft < 1 || a->n_draft > LM_MAX_DRAFT) return LM_E_INVALID;
+  if (!a->target_logits || !a->draft_ids || !a->out_accept || !a->out_final || a->vocab < 1 || a->row_stride < a->vocab) return LM_E_INVALID;
+  if (a->vocab > LM_MAX_VOCAB) return LM_E_UNSUPPORTED;
+  if (a->mode == LM_VERIFY_STOCHASTIC &&
+      (!a->draft_probs || a->probs_stride < a->vocab || !a->u_accept || !a->u_final || !(a->temperature > 0.0f)))
+    return LM_E_INVALID;
+  if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) || a->workspace_bytes < lm_verify_workspace_bytes(a->n_draft, a->vocab))
+    return LM_E_WORKSPACE;
+  int sms = 0;
+  int rc = sm_count(&sms);
+  if (rc != LM_OK) return rc;
+  VerifyDev P;
+  P.mode = a->mode; P.dtype = a->dtype; P.n_draft = a->n_draft; P.vocab = static_cast<int>(a->vocab); P.row_stride = a->row_stride;
+  P.target = a->target_logits; P.drafts = a->draft_ids; P.q = a->draft_probs; P.q_stride = a->probs_stride; P.temperature = a->temperature;
+  P.tau = a->tau; P.u_accept = a->u_accept; P.u_final = a->u_final;
+  P.out_accept = a->out_accept; P.out_final = a->out_final; P.out_tokens = a->out_tokens; P.out_p_draft = a->out_p_draft;
+  P.ws = static_cast<VerifyWs*>(a->workspace);
+  // one block per SM, all resident at once (the phases meet at a grid barrier): a cooperative launch guarantees it
+  int grid = sms < 1024 ? sms : 1024;
+  const int max_useful = static_cast<int>((a->vocab + 7) / 8);
+  if (grid > max_useful) grid = max_useful;
+  void* params[] = {&P};
+  const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(verify_kernel), dim3(grid), dim3(kVerifyBlock), params, 0,
+                                                    static_cast<cudaStream_t>(a->stream));
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+}  // extern "C"

@@ -1,0 +1,236 @@
+// DSpark verification of one speculative step in ONE launch: n_draft drafted tokens against n_draft + 1 rows of
+// target logits. Greedy: row-wise argmax and prefix match (kernels/common/spec_ops.metal:162-165). Stochastic:
+// accept draft r with probability min(1, p/q), replace the first rejected one by a draw from max(p - q, 0)
+// (kernels/common/sample.metal:273-347), on the integer fixed-point weights so the outcome is independent of how the
+// vocabulary is split between blocks.
+//
+// The step is latency-bound (a few MB of input, a chain of three data dependencies), so the kernel is one
+// cooperative launch of one block per SM; every block owns the same vocabulary slice of every row in every phase
+// (re-reads hit L1/L2), partial results meet in a small workspace, and the phases are separated by a bounded
+// grid barrier on a counter in that workspace.
+#pragma once
+#include "common.cuh"
+
+namespace lm {
+
+constexpr int kVerifyBlock = 512;
+constexpr int kVerifyMaxRows = LM_MAX_DRAFT + 1;
+constexpr unsigned kBarrierSpinLimit = 1u << 22;       // ~ tens of ms: far beyond any legitimate wait
+
+struct VerifyWs {                                       // lives in the caller's workspace, zero-filled once
+  unsigned barrier;                                     // arrivals; returns to 0 when the launch ends
+  unsigned exits;
+  unsigned error;                                       // sticky: 1 = a barrier wait ran out
+  unsigned pad;
+  unsigned long long row_best[kVerifyMaxRows];          // packed (max logit, lowest index) per row
+  unsigned long long row_mass[kVerifyMaxRows];          // fixed-point mass of the kept set per row
+  unsigned long long draft_w[kVerifyMaxRows];           // fixed-point weight of draft r in row r (0 if not kept)
+  // followed by: unsigned long long part_w[kVerifyMaxRows][grid], part_r[grid]
+};
+
+struct VerifyDev {
+  int mode; int dtype; int n_draft; int vocab; int64_t row_stride;
+  const void* target; const int32_t* drafts; const float* q; int64_t q_stride; float temperature;
+  const float* tau; const float* u_accept; const float* u_final;
+  int32_t* out_accept; int32_t* out_final; int32_t* out_tokens; float* out_p_draft;
+  VerifyWs* ws;
+};
+
+// Every block arrives, block 0..grid-1 wait until `target` arrivals are visible. Bounded: on time-out the error
+// word is set and the block carries on (its results are then meaningless, the host sees the error).
+__device__ __forceinline__ void grid_barrier(VerifyWs* ws, unsigned target) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(&ws->barrier, 1u);
+    unsigned spins = 0;
+    while (*reinterpret_cast<volatile unsigned*>(&ws->barrier) < target) {
+      if (++spins > kBarrierSpinLimit) { atomicExch(&ws->error, 1u); break; }
+      __nanosleep(20);
+    }
+    __threadfence();
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ uint64_t ws_load(const unsigned long long* p) { return __ldcg(p); }
+
+__device__ __forceinline__ float verify_load(const VerifyDev& P, int row, int i) {
+  const char* base = static_cast<const char*>(P.target);
+  const float z = (P.dtype == LM_DTYPE_BF16)
+                      ? __uint_as_float(static_cast<uint32_t>(__ldg(reinterpret_cast<const uint16_t*>(base) + static_cast<int64_t>(row) * P.row_stride + i)) << 16)
+                      : __ldg(reinterpret_cast<const float*>(base) + static_cast<int64_t>(row) * P.row_stride + i);
+  return canon_zero(z);
+}
+
+__global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P) {
+  __shared__ uint64_t scratch[32];
+  __shared__ int s_j, s_token;
+  __shared__ uint64_t s_base, s_total;
+  const int tid = threadIdx.x, G = gridDim.x, b = blockIdx.x;
+  const int R = P.n_draft + 1, V = P.vocab;
+  VerifyWs* ws = P.ws;
+  unsigned long long* part_w = reinterpret_cast<unsigned long long*>(ws + 1);   // [R][G]
+  unsigned long long* part_r = part_w + static_cast<size_t>(kVerifyMaxRows) * G; // [G]
+  // this block's vocabulary slice, a multiple of 8 elements so that slices start 16-byte aligned within a row
+  const int per = ((V + G - 1) / G + 7) & ~7;
+  const int lo = min(V, b * per), hi = min(V, lo + per);
+  const int len = hi - lo;
+
+  // ---- phase 0: row maxima (with the lowest index, which is also the greedy pick) ------------------------------
+  for (int r = 0; r < R; r++) {
+    uint64_t best = 0ull;
+    for (int i = tid; i < len; i += kVerifyBlock) {
+      const uint64_t p = pack_best(verify_load(P, r, lo + i), static_cast<uint32_t>(lo + i));
+      best = p > best ? p : best;
+    }
+    best = block_max_u64(best, scratch);
+    if (tid == 0 && best) atomicMax(&ws->row_best[r], static_cast<unsigned long long>(best));
+  }
+  grid_barrier(ws, 1u * G);
+
+  if (P.mode == LM_VERIFY_GREEDY) {
+    if (b == 0 && tid == 0) {
+      int acc = 0;
+      while (acc < P.n_draft && static_cast<int>(best_index(ws_load(&ws->row_best[acc]))) == P.drafts[acc]) acc++;
+      const int fin = static_cast<int>(best_index(ws_load(&ws->row_best[acc])));
+      const bool bad = ws->error != 0;
+      P.out_accept[0] = bad ? -1 : acc; P.out_final[0] = bad ? -1 : fin;
+      if (P.out_tokens) for (int r = 0; r < R; r++) P.out_tokens[r] = r < acc ? P.drafts[r] : (r == acc ? fin : -1);
+    }
+    // the last block to leave puts the workspace back to its clean state
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      if (atomicAdd(&ws->exits, 1u) == static_cast<unsigned>(G) - 1u) {
+        for (int r = 0; r < R; r++) ws->row_best[r] = 0ull;
+        ws->exits = 0u; __threadfence(); ws->barrier = 0u;
+      }
+    }
+    return;
+  }
+
+  // ---- phase 1: fixed-point mass of every row's kept set; the drafts' own weights -------------------------------
+  const float c2 = exp2_scale(P.temperature);
+  for (int r = 0; r < R; r++) {
+    const float vmax = best_value(ws_load(&ws->row_best[r]));
+    const float tau = P.tau ? P.tau[r] : -INFINITY;
+    uint64_t w = 0ull;
+    for (int i = tid; i < len; i += kVerifyBlock) {
+      const float z = verify_load(P, r, lo + i);
+      if (z >= tau) w += weight_q40(z, vmax, c2);
+    }
+    w = block_sum_u64(w, scratch);
+    if (tid == 0) {
+      part_w[static_cast<size_t>(r) * G + b] = w;
+      if (w) atomicAdd(&ws->row_mass[r], static_cast<unsigned long long>(w));
+      if (r < P.n_draft) {
+        const int d = P.drafts[r];
+        if (d >= lo && d < hi) {
+          const float z = verify_load(P, r, d);
+          ws->draft_w[r] = (z >= tau) ? weight_q40(z, vmax, c2) : 0ull;
+        }
+      }
+    }
+  }
+  grid_barrier(ws, 2u * G);
+
+  // ---- phase 2: accept tests (every block, identically), then this slice's share of the residual mass -----------
+  if (tid == 0) {
+    int j = P.n_draft;
+    for (int r = P.n_draft - 1; r >= 0; r--) {
+      const int d = P.drafts[r];
+      const uint64_t k = ws_load(&ws->row_mass[r]);
+      const float pd = (d >= 0 && d < V && k > 0ull) ? prob_q40(ws_load(&ws->draft_w[r]), k) : 0.0f;
+      const float qd = (d >= 0 && d < V) ? __ldg(P.q + static_cast<int64_t>(r) * P.q_stride + d) : 0.0f;
+      if (__fmul_rn(P.u_accept[r], qd) >= pd) j = r;
+      if (b == 0 && P.out_p_draft) P.out_p_draft[r] = pd;
+    }
+    s_j = j;
+  }
+  __syncthreads();
+  const int j = s_j;
+  const float vmax_j = best_value(ws_load(&ws->row_best[j]));
+  const float tau_j = P.tau ? P.tau[j] : -INFINITY;
+  const uint64_t mass_j = ws_load(&ws->row_mass[j]);
+  const float* qj = (j < P.n_draft) ? P.q + static_cast<int64_t>(j) * P.q_stride : nullptr;
+  {
+    uint64_t w = 0ull;
+    if (mass_j > 0ull) for (int i = tid; i < len; i += kVerifyBlock) {
+      const float z = verify_load(P, j, lo + i);
+      if (z >= tau_j) {
+        const float p = prob_q40(weight_q40(z, vmax_j, c2), mass_j);
+        const float res = qj ? __fsub_rn(p, __ldg(qj + lo + i)) : p;
+        if (res > 0.0f) w += residual_q40(res);
+      }
+    }
+    w = block_sum_u64(w, scratch);
+    if (tid == 0) part_r[b] = w;
+  }
+  grid_barrier(ws, 3u * G);
+
+  // ---- phase 3: locate the draw; the block whose slice holds it writes the outputs -------------------------------
+  {
+    // totals and this block's exclusive prefix over the per-block partials, for the residual and for the row's own mass
+    uint64_t tot_r = 0ull, pre_r = 0ull, pre_w = 0ull;
+    for (int g = tid; g < G; g += kVerifyBlock) {
+      const uint64_t vr = ws_load(&part_r[g]), vw = ws_load(&part_w[static_cast<size_t>(j) * G + g]);
+      tot_r += vr;
+      if (g < b) { pre_r += vr; pre_w += vw; }
+    }
+    tot_r = block_sum_u64(tot_r, scratch);
+    pre_r = block_sum_u64(pre_r, scratch);
+    pre_w = block_sum_u64(pre_w, scratch);
+    const bool use_res = tot_r > 0ull;                                   // an empty residual: draw from the row's own kept softmax
+    const uint64_t total = use_res ? tot_r : mass_j;
+    const uint64_t mine = use_res ? ws_load(&part_r[b]) : ws_load(&part_w[static_cast<size_t>(j) * G + b]);
+    const uint64_t pre = use_res ? pre_r : pre_w;
+    if (tid == 0) { s_token = -2; s_total = total; }
+    __syncthreads();
+    if (total > 0ull) {
+      const uint64_t target = cdf_target(P.u_final[0], total);
+      if (mine > 0ull && pre <= target && target < pre + mine) {           // the crossing lies in this block's slice
+        uint64_t base = pre;
+        for (int i0 = 0; i0 < len; i0 += kVerifyBlock) {                  // uniform trip count: block-wide scans inside
+          const int i = i0 + tid;
+          uint64_t w = 0ull;
+          if (i < len) {
+            const float z = verify_load(P, j, lo + i);
+            if (z >= tau_j) {
+              const uint64_t wq = weight_q40(z, vmax_j, c2);
+              if (use_res) {
+                const float p = prob_q40(wq, mass_j);
+                const float res = qj ? __fsub_rn(p, __ldg(qj + lo + i)) : p;
+                if (res > 0.0f) w = residual_q40(res);
+              } else w = wq;
+            }
+          }
+          uint64_t sweep = 0ull;
+          const uint64_t excl = block_exclusive_scan_u64(w, scratch, &sweep);
+          if (w && base + excl <= target && target < base + excl + w) s_token = lo + i;
+          base += sweep;
+          __syncthreads();
+          if (s_token != -2) break;
+        }
+        if (tid == 0) {
+          const bool bad = ws->error != 0;
+          P.out_accept[0] = bad ? -1 : j; P.out_final[0] = bad ? -1 : s_token;
+          if (P.out_tokens) for (int r = 0; r < R; r++) P.out_tokens[r] = r < j ? P.drafts[r] : (r == j ? s_token : -1);
+        }
+      }
+    } else if (b == 0 && tid == 0) {                                     // a row with no weight at all (empty or all -inf)
+      P.out_accept[0] = ws->error ? -1 : j; P.out_final[0] = -1;
+      if (P.out_tokens) for (int r = 0; r < R; r++) P.out_tokens[r] = r < j ? P.drafts[r] : -1;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(&ws->exits, 1u) == static_cast<unsigned>(G) - 1u) {
+      for (int r = 0; r < R; r++) { ws->row_best[r] = 0ull; ws->row_mass[r] = 0ull; ws->draft_w[r] = 0ull; }
+      ws->exits = 0u; __threadfence(); ws->barrier = 0u;
+    }
+  }
+}
+
+}  // namespace lm

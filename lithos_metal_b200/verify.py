@@ -1,0 +1,77 @@
+"""DSpark speculative verification on the GPU: one launch checks ``n`` drafted tokens against ``n + 1`` rows of
+target logits. Stands in for the accept chain of a speculative round in the reference (greedy: the prefix match of
+``accept_scan``, kernels/common/spec_ops.metal:162-165; sampled drafts: ``spec_q_accept`` and the residual draw,
+kernels/common/sample.metal:279-347)."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .sampler import _check_logits, _dtype_code, _row_stride, _workspace
+
+
+def verify(target_logits: torch.Tensor, draft_ids: torch.Tensor, draft_probs: Optional[torch.Tensor] = None, uniforms: Optional[torch.Tensor] = None,
+           u_resample: Optional[torch.Tensor] = None, mode: str = "greedy", *, temperature: float = 1.0, tau: Optional[torch.Tensor] = None,
+           return_p_draft: bool = False) -> Tuple[torch.Tensor, ...]:
+    """``(accept_len [1], final_token [1], tokens [n + 1])`` as int32 CUDA tensors (plus ``p_draft [n]`` on request).
+
+    ``target_logits`` [n + 1, V] bfloat16/float32; ``draft_ids`` [n] int32; stochastic mode also takes the drafter's
+    probabilities ``draft_probs`` [n, V] float32, the accept uniforms ``uniforms`` [n] and the resample uniform
+    ``u_resample`` [1], all in [0, 1); ``tau`` [n + 1] optionally restricts every row to its kept set (``sample(...,
+    return_tau=True)``). Asynchronous on the current stream.
+    """
+    if mode not in ("greedy", "stochastic"):
+        raise ValueError("mode must be 'greedy' or 'stochastic'")
+    target_logits = _check_logits(target_logits)
+    dev = target_logits.device
+    n = int(draft_ids.numel())
+    if target_logits.shape[0] != n + 1:
+        raise ValueError("target_logits must have one row per draft plus the bonus row")
+    if not 1 <= n <= _lib.MAX_DRAFT:
+        raise ValueError(f"1..{_lib.MAX_DRAFT} drafts")
+    a = _lib.VerifyArgs()
+    a.struct_size = C.sizeof(_lib.VerifyArgs)
+    a.mode = _lib.VERIFY_GREEDY if mode == "greedy" else _lib.VERIFY_STOCHASTIC
+    a.dtype, a.n_draft = _dtype_code(target_logits), n
+    a.target_logits, a.vocab, a.row_stride = target_logits.data_ptr(), target_logits.shape[1], _row_stride(target_logits)
+    draft_ids = draft_ids.to(device=dev, dtype=torch.int32).contiguous()
+    a.draft_ids = draft_ids.data_ptr()
+    keep = [draft_ids]
+    if mode == "stochastic":
+        if draft_probs is None or uniforms is None or u_resample is None:
+            raise ValueError("stochastic verification needs draft_probs, uniforms and u_resample")
+        if not temperature > 0:
+            raise ValueError("temperature must be positive")
+        if draft_probs.shape != (n, target_logits.shape[1]) or draft_probs.dtype != torch.float32 or not draft_probs.is_cuda:
+            raise ValueError("draft_probs must be float32 CUDA [n, V]")
+        if draft_probs.stride(1) != 1:
+            draft_probs = draft_probs.contiguous()
+        uniforms = uniforms.to(device=dev, dtype=torch.float32).contiguous()
+        u_resample = u_resample.to(device=dev, dtype=torch.float32).reshape(1).contiguous()
+        if uniforms.numel() != n:
+            raise ValueError("uniforms must hold one value per draft")
+        a.draft_probs, a.probs_stride = draft_probs.data_ptr(), _row_stride(draft_probs)
+        a.u_accept, a.u_final, a.temperature = uniforms.data_ptr(), u_resample.data_ptr(), float(temperature)
+        keep += [draft_probs, uniforms, u_resample]
+        if tau is not None:
+            tau = tau.to(device=dev, dtype=torch.float32).contiguous()
+            if tau.numel() != n + 1:
+                raise ValueError("tau must hold one value per row")
+            a.tau = tau.data_ptr()
+    out = torch.empty(n + 3, dtype=torch.int32, device=dev)
+    a.out_accept, a.out_final, a.out_tokens = out.data_ptr(), out.data_ptr() + 4, out.data_ptr() + 8
+    p_draft = None
+    if return_p_draft and mode == "stochastic":
+        p_draft = torch.empty(n, dtype=torch.float32, device=dev)
+        a.out_p_draft = p_draft.data_ptr()
+    L = _lib.lib()
+    ws = _workspace(dev, L.lm_verify_workspace_bytes(n, target_logits.shape[1]), "verify")
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.stream = torch.cuda.current_stream(dev).cuda_stream
+    with torch.cuda.device(dev):
+        _lib.check(L.lm_verify(C.byref(a)), "lm_verify")
+    res = (out[0:1], out[1:2], out[2:])
+    return res + (p_draft,) if p_draft is not None else res

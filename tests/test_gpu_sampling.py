@@ -1,0 +1,209 @@
+"""The CUDA sampler against the reference's golden outputs and against the CPU oracle (bit-exact token ids,
+thresholds and kept sets; probabilities within 1e-5 relative). All calls go through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import lithos_metal_b200 as lm
+from tests import inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def bf16_tensor(codes: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(codes.view(np.int16)).cuda().view(torch.bfloat16)
+
+
+@pytest.mark.parametrize("vocab", [248320, 1000, 300])
+def test_argmax_edge_cases(golden, vocab):
+    lb = inputs.argmax_test_logits(vocab)
+    out = torch.full((4,), -1, dtype=torch.int32, device="cuda")
+    lm.argmax(bf16_tensor(lb)[:3], out=out[:3])
+    got = out.cpu().tolist()
+    assert got[:3] == golden["argmax"][str(vocab)][:3] and got[0] == vocab - 1 and got[1] == 5
+    assert got[3] == -1                                                   # rows beyond the active ones stay untouched
+    assert lm.GreedySampler().forward(bf16_tensor(lb)).cpu().tolist() == golden["argmax"][str(vocab)]
+    # the same rows as FP32, and through the sampler entry point with temperature 0
+    lf = torch.from_numpy(oracle.bf16_to_f32(lb)).cuda()
+    assert lm.argmax(lf).cpu().tolist() == golden["argmax"][str(vocab)]
+    assert lm.sample(bf16_tensor(lb), temperature=0.0).tokens.cpu().tolist() == golden["argmax"][str(vocab)]
+
+
+@pytest.mark.parametrize("rows,vocab", [(1, 151936), (8, 151936), (300, 4096), (2, 7), (5, 8193)])
+def test_argmax_shapes_and_strides(rows, vocab):
+    rng = np.random.default_rng(rows * 1000 + vocab)
+    lb = oracle.f32_to_bf16((rng.standard_normal((rows, vocab + 3)) * 3).astype(np.float32))
+    t = bf16_tensor(lb)[:, 1:vocab + 1]                                   # a strided, misaligned view
+    exp = oracle.bf16_to_f32(lb)[:, 1:vocab + 1].argmax(-1)
+    assert lm.argmax(t).cpu().tolist() == exp.tolist()
+
+
+@pytest.mark.parametrize("vocab", [1000, 248320])
+@pytest.mark.parametrize("name", list(inputs.OPTION_SETS))
+def test_draws_equal_the_reference(golden, vocab, name):
+    """tests/kernels/test_sampling.py:51-67 of the reference, with the reference's outputs as goldens."""
+    opts = inputs.OPTION_SETS[name]
+    g = golden["draws"][f"{vocab}/{name}"]
+    lb = inputs.sampling_test_logits(vocab, opts)
+    x = bf16_tensor(lb)
+    s = lm.StochasticSampler(seed=12345, **opts)
+    for step in (0, 1, 7):
+        r = lm.sample(x, s.params(), step=step, return_tau=True, return_status=True)
+        assert r.tau.cpu().tolist() == [np.float32(t) for t in g["tau"]]
+        tok, status = r.tokens.cpu().tolist(), r.status.cpu().tolist()
+        for i in range(3):
+            assert tok[i] == g["tokens"][str(step)][i] or (status[i] & 4), (step, i)   # equal, or flagged as a float32-log near-tie
+        assert s.forward(x, step=step).cpu().tolist() == tok
+    assert sum(1 for st in status if st & 4) == 0
+
+
+def test_kept_sets_equal_the_hf_warpers(golden):
+    rng = np.random.default_rng(3)
+    lb = oracle.f32_to_bf16((rng.standard_normal((2, 4096)) * 3.0).astype(np.float32))
+    lf = oracle.bf16_to_f32(lb)
+    for name, g in golden["hf_warpers"].items():
+        o = dict(g["opts"])
+        r = lm.sample(bf16_tensor(lb), return_tau=True, return_probs=True, **o)
+        tau = r.tau.cpu().numpy()
+        probs = r.probs.cpu().numpy()
+        for i in range(2):
+            assert np.nonzero(lf[i] >= tau[i])[0].tolist() == g["kept"][i], name
+            assert np.nonzero(probs[i])[0].tolist() == g["kept"][i], name
+
+
+@pytest.mark.parametrize("name", ["plain", "topk", "topp", "minp", "all"])
+def test_kept_probabilities_equal_the_reference(golden, name):
+    opts = inputs.OPTION_SETS[name]
+    lb = inputs.sampling_test_logits(1000, opts)
+    g = golden["warped_probabilities"][name]
+    p = lm.warped_probabilities(bf16_tensor(lb)[0], **opts)
+    assert np.nonzero(p)[0].tolist() == g["idx"]
+    np.testing.assert_allclose(p[g["idx"]], g["p"], rtol=1e-5)           # the tolerance the task states for probabilities
+
+
+def test_known_answer_vector(golden):
+    g = golden["known_answer_5"]
+    lg = np.array(g["logits"], dtype=np.float32)
+    assert lm.thresholds(lg, top_k=3, top_p=0.85) == g["topp"]
+    assert lm.thresholds(lg, top_k=3, top_p=0.85, topp_in_topk=True) == g["topp_in_topk"]
+
+
+def test_config1_single_fp32_row(golden):
+    g = golden["config1"]
+    z, u = inputs.config1()
+    x = torch.from_numpy(z).cuda()
+    assert lm.GreedySampler().forward(x).cpu().tolist() == [g["greedy"]]
+    opts = dict(temperature=0.7, top_k=20, top_p=0.95)
+    r = lm.sample(x, seed=1, return_tau=True, return_probs=True, return_stats=True, **opts)
+    assert float(r.tau[0]) == g["tau"] and int(r.tokens[0]) == g["gumbel_token_seed1_step0"]
+    p = r.probs[0].cpu().numpy()
+    assert np.nonzero(p)[0].tolist() == g["kept_idx"]
+    np.testing.assert_allclose(p[g["kept_idx"]], g["kept_p"], rtol=1e-5)
+    assert r.stats.cpu().tolist() == [[12.0, 8.0]]
+    r = lm.sample(x, draw="inverse_cdf", uniforms=torch.tensor([u]), **opts)
+    assert int(r.tokens[0]) == oracle.sample_invcdf(z[0], u, **opts) == g["spikes"][int(np.floor(8 * float(u)))]
+
+
+def run_both(cfg, draw, rows, seed=77, step=3, row_offset=0, **extra):
+    """The same batch through the CUDA library and through the CPU oracle."""
+    x = bf16_tensor(cfg["logits"][:rows]) if cfg["logits"].dtype == np.uint16 else torch.from_numpy(cfg["logits"][:rows]).cuda()
+    knobs = {k: torch.from_numpy(cfg[k][:rows]).cuda() for k in ("temperature", "top_k", "top_p") if k in cfg}
+    hist = cfg.get("history")
+    r = lm.sample(x, lm.SamplingParams(seed=seed, draw=draw, repetition_penalty=cfg.get("repetition_penalty", 1.0),
+                                       presence_penalty=cfg.get("presence_penalty", 0.0), **knobs, **extra),
+                  history=None if hist is None else torch.from_numpy(hist[:rows]).cuda(),
+                  uniforms=torch.from_numpy(cfg["uniforms"][:rows]).cuda(), step=step, row_offset=row_offset,
+                  return_tau=True, return_stats=True, return_status=True)
+    tok, tau, stats = oracle.sample_batch(cfg["logits"][:rows], temperature=cfg["temperature"][:rows], top_k=cfg["top_k"][:rows],
+                                          top_p=cfg["top_p"][:rows], history=None if hist is None else hist[:rows],
+                                          repetition_penalty=cfg.get("repetition_penalty", 1.0), presence_penalty=cfg.get("presence_penalty", 0.0),
+                                          draw=draw, uniforms=cfg["uniforms"][:rows], seed=seed, step=step, row_offset=row_offset, n_threads=8,
+                                          **{k: v for k, v in extra.items() if k in ("min_p", "topp_in_topk")})
+    return r, tok, tau, stats
+
+
+@pytest.mark.parametrize("draw", ["inverse_cdf", "gumbel"])
+def test_penalised_batch_equals_the_oracle(draw):
+    """Benchmark configuration 3 (per-row knobs, 2048-id histories, both penalties) on its first rows."""
+    rows = 24
+    cfg = inputs.config3(rows=rows)
+    r, tok, tau, stats = run_both(cfg, draw, rows, row_offset=1000)
+    np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
+    status = r.status.cpu().numpy()
+    got = r.tokens.cpu().numpy()
+    if draw == "gumbel":
+        assert np.all((got == tok) | ((status & 4) != 0))
+    else:
+        np.testing.assert_array_equal(got, tok)
+    np.testing.assert_allclose(r.stats.cpu().numpy(), stats, rtol=1e-5)
+
+
+@pytest.mark.parametrize("vocab,rows", [(300, 5), (1000, 7), (8191, 3), (32768, 4)])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_small_and_ragged_vocabularies(vocab, rows, dtype):
+    rng = np.random.default_rng(vocab)
+    z = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    cfg = dict(logits=oracle.f32_to_bf16(z) if dtype == "bf16" else z, temperature=rng.uniform(0.3, 1.5, rows).astype(np.float32),
+               top_k=rng.choice(np.array([0, 1, 5, 50, vocab + 10], dtype=np.int32), rows), top_p=rng.uniform(0.5, 1.0, rows).astype(np.float32),
+               history=rng.integers(-2, vocab + 2, (rows, 64)).astype(np.int32), uniforms=rng.random(rows).astype(np.float32),
+               repetition_penalty=1.3, presence_penalty=0.25)
+    for draw in ("inverse_cdf", "gumbel"):
+        r, tok, tau, stats = run_both(cfg, draw, rows, min_p=0.01)
+        np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
+        status = r.status.cpu().numpy()
+        assert np.all((r.tokens.cpu().numpy() == tok) | ((status & 4) != 0))
+        np.testing.assert_allclose(r.stats.cpu().numpy(), stats, rtol=1e-5)
+
+
+def test_ties_duplicates_and_degenerate_rows():
+    V = 4096
+    z = np.zeros((4, V), dtype=np.float32)                                 # row 0: every logit equal
+    z[1, :] = -np.inf; z[1, 17] = 0.5; z[1, 99] = 0.5                      # row 1: a masked row with two survivors
+    z[2, :] = np.repeat(np.arange(V // 8, dtype=np.float32), 8) * 0.01    # row 2: ties of eight everywhere
+    z[3, :] = np.linspace(-5, 5, V, dtype=np.float32)
+    cfg = dict(logits=oracle.f32_to_bf16(z), temperature=np.array([1.0, 0.5, 0.8, 1.2], np.float32), top_k=np.array([10, 0, 12, 3], np.int32),
+               top_p=np.array([0.9, 0.95, 0.5, 0.0], np.float32), uniforms=np.array([0.999999, 0.5, 0.0, 0.3], np.float32))
+    r, tok, tau, stats = run_both(cfg, "inverse_cdf", 4)
+    np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
+    np.testing.assert_array_equal(r.tokens.cpu().numpy(), tok)
+    np.testing.assert_allclose(r.stats.cpu().numpy(), stats, rtol=1e-5)
+    assert tau[0] == 0.0 and tok[0] == V - 1 and tau[2] == z[2, -16]       # ties kept: all of row 0; 16 elements for top_k 12
+
+
+def test_mixed_greedy_rows_and_repeatability():
+    cfg = inputs.config3(rows=8, vocab=32000, hist_len=128)
+    cfg["temperature"][::2] = 0.0                                          # every other row greedy
+    x = bf16_tensor(cfg["logits"])
+    knobs = {k: torch.from_numpy(cfg[k]).cuda() for k in ("temperature", "top_k", "top_p")}
+    hist = torch.from_numpy(cfg["history"]).cuda()
+    u = torch.from_numpy(cfg["uniforms"]).cuda()
+    p = lm.SamplingParams(draw="inverse_cdf", repetition_penalty=1.1, presence_penalty=0.5, **knobs)
+    a = lm.sample(x, p, history=hist, uniforms=u, return_tau=True)
+    b = lm.sample(x, p, history=hist, uniforms=u, return_tau=True)
+    assert torch.equal(a.tokens, b.tokens) and torch.equal(a.tau, b.tau)   # run twice: identical bits
+    for i in range(0, 8, 2):
+        z = oracle.apply_penalties(oracle.bf16_to_f32(cfg["logits"][i]), cfg["history"][i], 1.1, 0.5)
+        assert int(a.tokens[i]) == oracle.argmax(z)
+    # results do not depend on how the batch is split (row-sharded batches): rows 4..7 alone, with their global offset
+    s = lm.SamplingParams(seed=9, draw="gumbel", **{k: v[4:] for k, v in knobs.items()})
+    full = lm.sample(x, lm.SamplingParams(seed=9, draw="gumbel", **knobs), step=2)
+    part = lm.sample(x[4:], s, step=2, row_offset=4)
+    assert torch.equal(full.tokens[4:], part.tokens)
+
+
+def test_invalid_arguments_raise_before_launch():
+    x = torch.zeros(2, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        lm.StochasticSampler(temperature=0.0)
+    with pytest.raises(ValueError):
+        lm.sample(x, temperature=-1.0)
+    with pytest.raises(ValueError):
+        lm.sample(x, temperature=1.0, draw="inverse_cdf")                  # no uniforms
+    with pytest.raises(TypeError):
+        lm.sample(x.to(torch.float16), temperature=1.0)
+    with pytest.raises(RuntimeError):
+        lm.sample(x.cpu(), temperature=1.0)
+    bad_t = torch.tensor([float("nan"), 1.0], device="cuda")               # a per-row knob cannot be checked on the host: the row reports -1
+    r = lm.sample(x, temperature=bad_t, return_status=True)
+    assert int(r.tokens[0]) == -1 and int(r.status[0]) & 16 and int(r.tokens[1]) >= 0
