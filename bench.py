@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the generation-control hot path on B200.
+
+A "step" is one pass of the fused sampler over one batch of synthetic logits: the row-sharded large-batch
+configuration (4096 rows x 151936 BF16 logits from N(0, 2^2); per-row temperature U[0.3, 1.5], top_k from
+{0, 20, 50, 1000}, top_p U[0.8, 1.0]; repetition penalty 1.1 and presence penalty 0.5 over a 2048-id history per row;
+injected uniforms), rows split evenly over the ranks, no collective. Prints ONE JSON line on rank 0.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+``value`` is rows/s with the inputs resident in HBM (CUDA events, max over ranks); ``e2e`` is the same metric through
+the public API with HOST (pinned) inputs, copies inside the timed region; ``roofline`` relates the sampler kernel's
+algorithmic bytes per launch to the measured HBM copy peak; ``cpu_baseline`` is the CPU oracle (a C restatement
+of the reference's numpy sampler) timed on this host's cores on a bounded sample of the same workload.
+``--impl reference`` times that CPU path alone, as the reference arm.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+VOCAB = 151936
+TOTAL_ROWS = 4096
+HIST_LEN = 2048
+RHO, PI = 1.1, 0.5
+SEED = 1234
+ROW_BYTES = VOCAB * 2 + HIST_LEN * 4 + 4 * 4 + 4          # logits + history + (T, k, p, u) + token: algorithmic bytes per row
+METRIC, UNIT = "sampled_rows_per_s", "rows/s"
+WORKLOAD = ("row-sharded penalised sampling: 4096 rows x 151936 bf16 logits N(0,2^2), per-row T~U[0.3,1.5], top_k in {0,20,50,1000}, "
+            "top_p~U[0.8,1.0], repetition 1.1 + presence 0.5 over 2048-id histories, inverse-CDF draw from injected uniforms")
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+def ncu_traffic():
+    """DRAM bytes per row of the sampler kernel from the committed ncu capture summary, if there is one."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)
+    return None
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown," \
+        "clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index), "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+
+
+def make_inputs(torch, rows: int, row_offset: int, device):
+    """Seeded synthetic inputs of the workload's shapes and distributions, generated on the device."""
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED + row_offset)
+    logits = torch.empty(rows, VOCAB, dtype=torch.bfloat16, device=device)
+    for r0 in range(0, rows, 256):                                         # bounded temporaries
+        n = min(256, rows - r0)
+        logits[r0:r0 + n] = (torch.randn(n, VOCAB, generator=g, device=device) * 2.0).to(torch.bfloat16)
+    temperature = torch.rand(rows, generator=g, device=device) * 1.2 + 0.3
+    top_k = torch.tensor([0, 20, 50, 1000], dtype=torch.int32, device=device)[torch.randint(0, 4, (rows,), generator=g, device=device)]
+    top_p = torch.rand(rows, generator=g, device=device) * 0.2 + 0.8
+    history = torch.randint(0, VOCAB, (rows, HIST_LEN), generator=g, device=device, dtype=torch.int32)
+    uniforms = torch.rand(rows, generator=g, device=device)
+    return dict(logits=logits, temperature=temperature, top_k=top_k.contiguous(), top_p=top_p, history=history, uniforms=uniforms)
+
+
+def cpu_rows_per_s(inp_host, n_rows: int, n_threads: int, repeats: int = 1):
+    """The C oracle over the first n_rows of a host copy of the workload, all host threads; rows/s (best of repeats)."""
+    import numpy as np
+    import oracle
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        tok, _, _ = oracle.sample_batch(inp_host["logits"][:n_rows], temperature=inp_host["temperature"][:n_rows], top_k=inp_host["top_k"][:n_rows],
+                                        top_p=inp_host["top_p"][:n_rows], history=inp_host["history"][:n_rows], repetition_penalty=RHO,
+                                        presence_penalty=PI, draw="inverse_cdf", uniforms=inp_host["uniforms"][:n_rows], n_threads=n_threads)
+        dt = time.perf_counter() - t0
+        best = dt if best is None or dt < best else best
+    return n_rows / best, tok
+
+
+def host_copy(torch, inp, n_rows: int):
+    import numpy as np
+    return dict(logits=inp["logits"][:n_rows].view(torch.int16).cpu().numpy().view(np.uint16), temperature=inp["temperature"][:n_rows].cpu().numpy(),
+                top_k=inp["top_k"][:n_rows].cpu().numpy(), top_p=inp["top_p"][:n_rows].cpu().numpy(), history=inp["history"][:n_rows].cpu().numpy(),
+                uniforms=inp["uniforms"][:n_rows].cpu().numpy())
+
+
+def reference_arm(args, rank: int, world: int) -> None:
+    """The reference's CPU path (its numpy sampler restated in C, every host thread), timed on a bounded sample."""
+    if rank != 0:
+        return
+    import numpy as np
+    import oracle
+    cores = len(os.sched_getaffinity(0))
+    n_rows = max(64, min(512, 2 * cores))
+    rng = np.random.default_rng(SEED)
+    inp = dict(logits=oracle.f32_to_bf16(rng.standard_normal((n_rows, VOCAB), dtype=np.float32) * np.float32(2.0)),
+               temperature=rng.uniform(0.3, 1.5, n_rows).astype(np.float32), top_k=rng.choice(np.array([0, 20, 50, 1000], np.int32), n_rows),
+               top_p=rng.uniform(0.8, 1.0, n_rows).astype(np.float32), history=rng.integers(0, VOCAB, (n_rows, HIST_LEN)).astype(np.int32),
+               uniforms=rng.random(n_rows).astype(np.float32))
+    for _ in range(args.warmup):
+        cpu_rows_per_s(inp, n_rows, cores)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_rows_per_s(inp, n_rows, cores)
+    dt = time.perf_counter() - t0
+    value = n_rows * args.steps / dt
+    sample = f"{n_rows} rows of the workload per step, C restatement of monolith/nn/sampling_ref.py (oracle/lm_oracle.c), {cores} threads"
+    print(json.dumps({"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64",
+                      "data": "synthetic", "config": {"workload": WORKLOAD, "vocab": VOCAB, "rows_per_step": n_rows},
+                      "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+                      "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=TOTAL_ROWS, help="total rows over all ranks (default: the workload's 4096)")
+    ap.add_argument("--skip-extras", action="store_true", help="skip the e2e, CPU-baseline, small-batch and verify legs")
+    args = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        reference_arm(args, rank, world)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+    import lithos_metal_b200 as lm
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the sampler has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    total_rows = args.rows
+    rows = total_rows // world
+    row_offset = rank * rows
+    inp = make_inputs(torch, rows, row_offset, dev)
+    # inputs larger than L2 (126 MB) between timed iterations: rotate over as many copies as it takes to pass 512 MB
+    n_buf = max(1, -(-512 * 2**20 // (rows * VOCAB * 2)))
+    logit_bufs = [inp["logits"]] + [inp["logits"].clone() for _ in range(n_buf - 1)]
+    params = lm.SamplingParams(temperature=inp["temperature"], top_k=inp["top_k"], top_p=inp["top_p"], repetition_penalty=RHO, presence_penalty=PI,
+                               draw="inverse_cdf")
+    tokens = torch.empty(rows, dtype=torch.int32, device=dev)
+
+    def step(i: int):
+        lm.sample(logit_bufs[i % n_buf], params, history=inp["history"], uniforms=inp["uniforms"], row_offset=row_offset, out=tokens)
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    for i in range(args.warmup):
+        step(i)
+    sync_all()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        sync_all()
+        ev0.record()
+        for i in range(args.steps):
+            step(i)
+        ev1.record()
+        sync_all()
+        elapsed_ms = ev0.elapsed_time(ev1)
+        if elapsed_ms < 300:                                               # give nvidia-smi time for a few samples under the same load
+            t_end = time.perf_counter() + 0.5
+            i = 0
+            while time.perf_counter() < t_end:
+                step(i); i += 1
+                if i % 8 == 0:
+                    torch.cuda.synchronize(dev)
+            torch.cuda.synchronize(dev)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = total_rows / (ms_per_step * 1e-3)
+    peak, peak_src = peaks()
+    achieved = rows * ROW_BYTES / (ms_per_step * 1e-3) / 1e9              # per GPU: one launch covers this rank's rows
+    traffic = ncu_traffic()
+    out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+           "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 logits; f64/u64 selection arithmetic", "data": "synthetic",
+           "config": {"workload": WORKLOAD, "vocab": VOCAB, "total_rows": total_rows, "rows_per_gpu": rows, "parallelism": f"rows/{world}, no collective",
+                      "l2": f"inputs larger than L2: {n_buf} logits buffer(s) of {rows * VOCAB * 2 / 2**20:.0f} MiB rotated"},
+           "logits_gbs_per_gpu": rows * VOCAB * 2 / (ms_per_step * 1e-3) / 1e9,
+           "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+                        "frac_of_nominal_8TBs": achieved / 8000.0, "algorithmic_bytes_per_row": ROW_BYTES,
+                        "traffic": (traffic["dram_bytes_per_row"] * rows if traffic else None)},
+           "gpu_launches": args.steps, "clocks": clocks.summary()}
+
+    if not args.skip_extras:
+        # ---- e2e: host (pinned) inputs -> public API -> tokens on the host, copies inside the timed region
+        e2e_steps = max(3, min(args.steps, 5))
+        host = {k: torch.empty(v.shape, dtype=v.dtype, pin_memory=True).copy_(v) for k, v in inp.items()}
+        host_tok = torch.empty(rows, dtype=torch.int32, pin_memory=True)
+        h2d = sum(v.numel() * v.element_size() for v in host.values())
+
+        def e2e_step():
+            d = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+            p = lm.SamplingParams(temperature=d["temperature"], top_k=d["top_k"], top_p=d["top_p"], repetition_penalty=RHO, presence_penalty=PI,
+                                  draw="inverse_cdf")
+            r = lm.sample(d["logits"], p, history=d["history"], uniforms=d["uniforms"], row_offset=row_offset)
+            host_tok.copy_(r.tokens, non_blocking=True)
+
+        e2e_step()
+        sync_all()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        sync_all()
+        e2e_s = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t.item())
+        out["e2e"] = {"value": total_rows * e2e_steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": rows * 4,
+                      "steps": e2e_steps, "note": "pinned host logits/history/knobs copied in every step; PCIe-bound"}
+        del host
+
+        if rank == 0 and world == 1:
+            # ---- the small-batch configuration (256 rows) and the DSpark verify step, reported beside the headline
+            small = {k: v[:256] for k, v in inp.items()}
+            sp = lm.SamplingParams(temperature=small["temperature"], top_k=small["top_k"], top_p=small["top_p"], repetition_penalty=RHO,
+                                   presence_penalty=PI, draw="inverse_cdf")
+            flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=dev)
+            times = []
+            for i in range(args.warmup + 10):
+                flush.zero_()                                              # flush L2 between iterations (80 MB of logits would fit)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                lm.sample(small["logits"], sp, history=small["history"], uniforms=small["uniforms"], out=tokens[:256])
+                b.record()
+                torch.cuda.synchronize(dev)
+                if i >= args.warmup:
+                    times.append(a.elapsed_time(b))
+            t256 = min(times)
+            out["batch256"] = {"us_per_launch": 1e3 * t256, "rows_per_s": 256 / (t256 * 1e-3), "algorithmic_gbs": 256 * ROW_BYTES / (t256 * 1e-3) / 1e9,
+                               "frac_of_peak": 256 * ROW_BYTES / (t256 * 1e-3) / 1e9 / peak, "l2": "flushed between launches", "timing": "min of 10"}
+            out["verify"] = bench_verify(torch, lm, dev)
+            # ---- CPU baseline on this host's cores: a bounded sample of the same workload
+            cores = len(os.sched_getaffinity(0))
+            n_cpu = max(64, min(512, 2 * cores))
+            hc = host_copy(torch, inp, n_cpu)
+            cpu_rows_per_s(hc, min(n_cpu, cores), cores)
+            cpu_v, cpu_tok = cpu_rows_per_s(hc, n_cpu, cores)
+            step(0)
+            torch.cuda.synchronize(dev)
+            same = bool((tokens[:n_cpu].cpu().numpy() == cpu_tok).all())
+            out["cpu_baseline"] = {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port",
+                                   "sample": f"first {n_cpu} rows of the workload, C restatement of monolith/nn/sampling_ref.py (oracle/lm_oracle.c), {cores} threads",
+                                   "tokens_equal_gpu": same}
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def bench_verify(torch, lm, dev):
+    """One DSpark step (7 drafts + bonus row, V = 151936, BF16 target, FP32 draft probabilities): GPU microseconds per
+    step, measured over a CUDA graph of 20 back-to-back steps so that host launch overhead is not in the number."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(SEED)
+    target = (torch.randn(8, VOCAB, generator=g, device=dev) * 2.0).to(torch.bfloat16)
+    drafts = torch.randint(0, VOCAB, (7,), generator=g, device=dev, dtype=torch.int32)
+    drafts[:3] = target[:3].float().argmax(-1).to(torch.int32)
+    q = torch.softmax(target[:7].float() + torch.randn(7, VOCAB, generator=g, device=dev) * 0.5, dim=-1)
+    ua, uf = torch.rand(7, generator=g, device=dev), torch.rand(1, generator=g, device=dev)
+    res = {}
+    for mode in ("stochastic", "greedy"):
+        call = (lambda: lm.verify(target, drafts, q, ua, uf, "stochastic")) if mode == "stochastic" else (lambda: lm.verify(target, drafts, mode="greedy"))
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize(dev)
+        side = torch.cuda.Stream(dev)
+        graph = torch.cuda.CUDAGraph()
+        n = 20
+        try:
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(n):
+                        call()
+            torch.cuda.synchronize(dev)
+            graph.replay()
+            torch.cuda.synchronize(dev)
+            best = None
+            for _ in range(10):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); graph.replay(); b.record()
+                torch.cuda.synchronize(dev)
+                t = a.elapsed_time(b) * 1e3 / n
+                best = t if best is None or t < best else best
+            res[mode + "_us_per_step"] = best
+            res["timing"] = "CUDA graph of 20 steps, min of 10 replays"
+        except Exception as e:                                             # graph capture unavailable: time single launches
+            torch.cuda.synchronize(dev)
+            ts = []
+            for _ in range(20):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); call(); b.record()
+                torch.cuda.synchronize(dev)
+                ts.append(a.elapsed_time(b) * 1e3)
+            res[mode + "_us_per_step"] = min(ts)
+            res["timing"] = f"single launches, min of 20 (graph capture failed: {type(e).__name__})"
+    res["bytes_algorithmic_min"] = 8 * VOCAB * 2 + VOCAB * 4
+    res["bytes_one_pass"] = 8 * VOCAB * 2 + 7 * VOCAB * 4
+    return res
+
+
+if __name__ == "__main__":
+    main()

@@ -168,7 +168,8 @@ def test_ties_duplicates_and_degenerate_rows():
     np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
     np.testing.assert_array_equal(r.tokens.cpu().numpy(), tok)
     np.testing.assert_allclose(r.stats.cpu().numpy(), stats, rtol=1e-5)
-    assert tau[0] == 0.0 and tok[0] == V - 1 and tau[2] == z[2, -16]       # ties kept: all of row 0; 16 elements for top_k 12
+    zb = oracle.bf16_to_f32(cfg["logits"])
+    assert tau[0] == 0.0 and tok[0] == V - 1 and tau[2] == zb[2, -16]      # ties kept: all of row 0; 16 elements for top_k 12
 
 
 def test_mixed_greedy_rows_and_repeatability():
