@@ -8,6 +8,7 @@
 
 #include "common.cuh"
 #include "sample_generic.cuh"
+#include "sample_fast.cuh"
 #include "verify.cuh"
 
 namespace lm {
@@ -57,6 +58,16 @@ __global__ void __launch_bounds__(kBlock, 1) sample_generic_kernel(SampleDev P) 
   for (int row = blockIdx.x; row < P.rows; row += gridDim.x) {
     if (P.row_select != nullptr && P.row_select[row] == 0u) continue;
     sample_row_generic(P, row, s, pen_bits);
+    __syncthreads();
+  }
+}
+
+// ---- the streaming BF16 sampler: one block per SM, each walks rows blockIdx.x, blockIdx.x + gridDim.x, ... ---------------
+__global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, uint32_t* punt) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  FastSmem& s = *reinterpret_cast<FastSmem*>(smem_raw);
+  for (int row = blockIdx.x; row < P.rows; row += gridDim.x) {
+    sample_row_fast(P, row, s, punt);
     __syncthreads();
   }
 }
@@ -116,7 +127,7 @@ float lm_uniform01(uint64_t seed, uint32_t step, uint32_t t, uint32_t index) { r
 size_t lm_workspace_bytes(int64_t rows, int64_t vocab) {
   (void)vocab;
   if (rows < 0) rows = 0;
-  return align256(static_cast<size_t>(rows) * sizeof(ArgmaxWs)) + 256;
+  return align256(static_cast<size_t>(rows) * sizeof(ArgmaxWs)) + align256(static_cast<size_t>(rows) * sizeof(uint32_t)) + 256;
 }
 
 size_t lm_verify_workspace_bytes(int32_t n_draft, int64_t vocab) {
@@ -183,6 +194,27 @@ int lm_sample(const lm_sample_args* a) {
   int sms = 0;
   int rc = sm_count(&sms);
   if (rc != LM_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+  // BF16 rows that only need tokens (and tau) stream through the one-pass kernel; it marks the rows it cannot take
+  // and the generic kernel behind it handles exactly those.
+  const bool fast = a->dtype == LM_DTYPE_BF16 && a->out_stats == nullptr && a->out_probs == nullptr && a->vocab <= kFastMaxVocab &&
+                    (a->vocab % kChunk) == 0 && (!pen || a->hist_len <= 65536);
+  if (fast) {
+    if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) || a->workspace_bytes < lm_workspace_bytes(a->rows, a->vocab))
+      return LM_E_WORKSPACE;
+    uint32_t* punt = reinterpret_cast<uint32_t*>(static_cast<char*>(a->workspace) + align256(static_cast<size_t>(a->rows) * sizeof(ArgmaxWs)));
+    static thread_local bool fast_attr = false;
+    if (!fast_attr) {
+      const cudaError_t e = cudaFuncSetAttribute(sample_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FastSmem)));
+      if (e != cudaSuccess) return cuda_fail(e);
+      fast_attr = true;
+    }
+    const int grid = static_cast<int>(a->rows < sms ? a->rows : sms);
+    sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, punt);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e);
+    P.row_select = punt;
+  }
   const size_t smem = sizeof(GenericSmem) + (pen ? static_cast<size_t>((a->vocab + 31) / 32) * 4 : 0) + 16;
   static thread_local size_t smem_set = 0;
   if (smem > smem_set) {
@@ -190,8 +222,9 @@ int lm_sample(const lm_sample_args* a) {
     if (e != cudaSuccess) return cuda_fail(e);
     smem_set = smem;
   }
-  const int grid = static_cast<int>(a->rows < 8LL * sms ? a->rows : 8LL * sms);
-  sample_generic_kernel<<<grid, kBlock, smem, static_cast<cudaStream_t>(a->stream)>>>(P);
+  const long long cap = fast ? sms : 8LL * sms;
+  const int grid = static_cast<int>(a->rows < cap ? a->rows : cap);
+  sample_generic_kernel<<<grid, kBlock, smem, st>>>(P);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }

@@ -9,6 +9,7 @@
 // reference's sample.metal:87-162 does this walk on BF16 buckets in FP32).
 #pragma once
 #include "common.cuh"
+#include "draw.cuh"
 
 namespace lm {
 
@@ -32,15 +33,13 @@ struct GenericSmem {
   double mass0[kBins];                // level-0 bin masses, kept for the top-p descent
   double cum_m[8];
   uint64_t scratch[32];
-  uint64_t iter_total[LM_MAX_VOCAB / (kBlock * kChunk) + 1];
+  DrawSmem draw;
   uint32_t cnt[kBins];
   uint32_t cnt0[kBins];
   uint32_t cum_c[8];
   int sel_pos, last_pos;
   double sel_base_m, sel_incl_m;
   uint32_t sel_base_c;
-  int found_iter; uint64_t found_base;
-  int token;
 };
 
 __device__ __forceinline__ double softmass(float z, float vmax, double inv_t) {
@@ -267,95 +266,28 @@ __device__ void sample_row_generic(const SampleDev& P, int row, GenericSmem& s, 
   }
   const float tau = have_tau ? __double2float_rn(tau64) : -INFINITY;
 
-  // ---- kept-set statistics and, for the inverse-CDF draw, the fixed-point mass per sweep of the block ----------
+  // ---- kept-set statistics (only when asked for) ----------------------------------------------------------------
   const bool need_mass = (P.out_stats != nullptr) || (P.out_probs != nullptr);
-  const bool invcdf = P.draw == LM_DRAW_INVERSE_CDF;
-  const float c2 = exp2_scale(T);
-  const int n_iter = (n_chunks + kBlock - 1) / kBlock;
   double kept_mass = 0.0;
-  if (need_mass || invcdf) {
-    for (int i = tid; i < n_iter; i += kBlock) s.iter_total[i] = 0ull;
-    __syncthreads();
+  if (need_mass) {
     double m = 0.0;
-    for (int it = 0; it < n_iter; it++) {
-      const int c = it * kBlock + tid;
-      float z[kChunk];
-      const int n = load_chunk(rv, c, z);
-      uint64_t w = 0ull;
-#pragma unroll
-      for (int e = 0; e < kChunk; e++) if (e < n && z[e] >= tau) {
-        if (need_mass) m += softmass(z[e], vmax, inv_t);
-        if (invcdf) w += weight_q40(z[e], vmax, c2);
-      }
-      if (invcdf) {
-        w = warp_sum_u64(w);
-        if ((tid & 31) == 0 && w) atomicAdd(reinterpret_cast<unsigned long long*>(&s.iter_total[it]), static_cast<unsigned long long>(w));
-      }
-    }
-    if (need_mass) kept_mass = block_sum_f64(m, s.scratch);
-    __syncthreads();
-  }
-
-  // ---- the draw --------------------------------------------------------------------------------------------------
-  if (tid == 0) s.token = -1;
-  __syncthreads();
-  if (invcdf) {
-    if (tid == 0) {
-      uint64_t total = 0ull;
-      for (int it = 0; it < n_iter; it++) total += s.iter_total[it];
-      s.found_iter = -1; s.found_base = 0ull;
-      if (total > 0ull) {
-        const float u = P.uniforms ? P.uniforms[row] : 0.0f;
-        const uint64_t target = cdf_target(u, total);
-        uint64_t run = 0ull;
-        for (int it = 0; it < n_iter; it++) {
-          if (run + s.iter_total[it] > target) { s.found_iter = it; s.found_base = target - run; break; }
-          run += s.iter_total[it];
-        }
-      }
-    }
-    __syncthreads();
-    const int it = s.found_iter;
-    if (it >= 0) {
-      const uint64_t local_target = s.found_base;                        // find the first cumulative weight > local_target in this sweep
-      const int c = it * kBlock + tid;
-      float z[kChunk];
-      const int n = load_chunk(rv, c, z);
-      uint64_t w[kChunk];
-      uint64_t mine = 0ull;
-#pragma unroll
-      for (int e = 0; e < kChunk; e++) { w[e] = (e < n && z[e] >= tau) ? weight_q40(z[e], vmax, c2) : 0ull; mine += w[e]; }
-      const uint64_t excl = block_exclusive_scan_u64(mine, s.scratch, nullptr);
-      if (excl <= local_target && local_target < excl + mine) {
-        uint64_t run = excl;
-#pragma unroll
-        for (int e = 0; e < kChunk; e++) { run += w[e]; if (w[e] && run > local_target) { s.token = c * kChunk + e; break; } }
-      }
-    }
-    __syncthreads();
-  } else {
-    const float inv_t32 = __double2float_rn(1.0 / T64);
-    const uint32_t t_id = static_cast<uint32_t>(P.row_offset + row);
-    uint64_t b1 = 0ull; float second = -INFINITY;
     for (int c = tid; c < n_chunks; c += kBlock) {
       float z[kChunk];
       const int n = load_chunk(rv, c, z);
 #pragma unroll
-      for (int e = 0; e < kChunk; e++) if (e < n && z[e] >= tau) {
-        const uint32_t i = static_cast<uint32_t>(c * kChunk + e);
-        const float key = __fadd_rn(__fmul_rn(z[e], inv_t32), gumbel(P.seed, P.step, t_id, i));
-        const uint64_t p = pack_best(key, i);
-        if (p > b1) { if (b1) second = fmaxf(second, best_value(b1)); b1 = p; } else second = fmaxf(second, key);
-      }
+      for (int e = 0; e < kChunk; e++) if (e < n && z[e] >= tau) m += softmass(z[e], vmax, inv_t);
     }
-    const uint64_t win = block_max_u64(b1, s.scratch);
-    if (win) {
-      const float wkey = best_value(win);
-      float rival = (b1 == win) ? second : (b1 ? best_value(b1) : -INFINITY);   // this thread's best candidate other than the winner
-      if (__syncthreads_or(rival >= wkey - 4e-6f)) status |= LM_STATUS_NEAR_TIE;
-      if (tid == 0) s.token = static_cast<int>(best_index(win));
-    }
-    __syncthreads();
+    kept_mass = block_sum_f64(m, s.scratch);
+  }
+
+  // ---- the draw --------------------------------------------------------------------------------------------------
+  int token;
+  if (P.draw == LM_DRAW_INVERSE_CDF) {
+    token = draw_inverse_cdf(rv, tau, vmax, T, P.uniforms ? P.uniforms[row] : 0.0f, s.draw);
+  } else {
+    bool tie = false;
+    token = draw_gumbel(rv, tau, T, P.seed, P.step, static_cast<uint32_t>(P.row_offset + row), s.draw, &tie);
+    if (tie) status |= LM_STATUS_NEAR_TIE;
   }
 
   // ---- outputs ----------------------------------------------------------------------------------------------------
@@ -368,7 +300,7 @@ __device__ void sample_row_generic(const SampleDev& P, int row, GenericSmem& s, 
     }
   }
   if (tid == 0) {
-    P.out_tokens[row] = s.token;
+    P.out_tokens[row] = token;
     if (P.out_tau) P.out_tau[row] = tau;
     if (P.out_stats) { P.out_stats[2 * row] = vmax; P.out_stats[2 * row + 1] = static_cast<float>(kept_mass); }
     if (P.out_status) P.out_status[row] = status;

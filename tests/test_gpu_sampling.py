@@ -208,3 +208,48 @@ def test_invalid_arguments_raise_before_launch():
     bad_t = torch.tensor([float("nan"), 1.0], device="cuda")               # a per-row knob cannot be checked on the host: the row reports -1
     r = lm.sample(x, temperature=bad_t, return_status=True)
     assert int(r.tokens[0]) == -1 and int(r.status[0]) & 16 and int(r.tokens[1]) >= 0
+
+
+def test_streaming_and_generic_paths_agree():
+    """BF16 rows that only ask for tokens take the one-pass streaming kernel; asking for statistics routes the same rows
+    through the generic kernel. Same tokens, same thresholds; rows the streaming kernel cannot take fall back by themselves."""
+    rows = 40
+    cfg = inputs.config3(rows=rows, seed=31)
+    cfg["logits"][5, :70000] = 0xFF80                                      # a masked row: 70000 x -inf overflows a 16-bit counter -> falls back
+    cfg["logits"][6, :] = oracle.f32_to_bf16(np.float32([1.5]))[0]         # every logit equal
+    cfg["history"][7, :] = 11                                              # one distinct history id
+    cfg["top_k"][8] = 1
+    cfg["top_p"][9] = 1.0                                                  # top-p off
+    x = bf16_tensor(cfg["logits"])
+    knobs = {k: torch.from_numpy(cfg[k]).cuda() for k in ("temperature", "top_k", "top_p")}
+    hist, u = torch.from_numpy(cfg["history"]).cuda(), torch.from_numpy(cfg["uniforms"]).cuda()
+    for draw in ("inverse_cdf", "gumbel"):
+        for extra in (dict(), dict(min_p=0.02), dict(topp_in_topk=True)):
+            p = lm.SamplingParams(seed=5, draw=draw, repetition_penalty=1.1, presence_penalty=0.5, **knobs, **extra)
+            fast = lm.sample(x, p, history=hist, uniforms=u, step=1, return_tau=True, return_status=True)
+            slow = lm.sample(x, p, history=hist, uniforms=u, step=1, return_tau=True, return_status=True, return_stats=True)
+            fs, ss = fast.status.cpu().numpy(), slow.status.cpu().numpy()
+            assert np.all(ss & 1) and (fs[5] & 1) and (fs[6] & 1) and not np.any(np.delete(fs, [5, 6]) & 1), fs
+            assert torch.equal(fast.tau, slow.tau), (draw, extra)
+            assert torch.equal(fast.tokens, slow.tokens), (draw, extra)
+    tok, tau, _ = oracle.sample_batch(cfg["logits"], temperature=cfg["temperature"], top_k=cfg["top_k"], top_p=cfg["top_p"], history=cfg["history"],
+                                      repetition_penalty=1.1, presence_penalty=0.5, draw="inverse_cdf", uniforms=cfg["uniforms"], n_threads=8)
+    r = lm.sample(x, lm.SamplingParams(draw="inverse_cdf", repetition_penalty=1.1, presence_penalty=0.5, **knobs), history=hist, uniforms=u, return_tau=True)
+    np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
+    np.testing.assert_array_equal(r.tokens.cpu().numpy(), tok)
+
+
+def test_streaming_path_with_dense_side_values():
+    """Penalised logits that crowd one BF16 bin (equal history targets, thresholds landing on penalised values)."""
+    V, rows = 8192, 6
+    rng = np.random.default_rng(8)
+    z = (rng.standard_normal((rows, V)) * 2).astype(np.float32)
+    z[:, :40] = 6.0                                                        # forty equal top logits, all penalised below: 40 side values in one bin
+    hist = np.tile(np.arange(40, dtype=np.int32), (rows, 1))
+    hist[3:, 20:] = 5000                                                   # rows 3..: only twenty of them penalised
+    cfg = dict(logits=oracle.f32_to_bf16(z), temperature=np.full(rows, 0.9, np.float32), top_k=np.array([5, 30, 45, 5, 30, 0], np.int32),
+               top_p=np.array([0.0, 0.5, 0.99, 0.3, 0.0, 0.7], np.float32), history=hist, uniforms=rng.random(rows).astype(np.float32),
+               repetition_penalty=1.07, presence_penalty=0.013)
+    r, tok, tau, _ = run_both(cfg, "inverse_cdf", rows)
+    np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
+    np.testing.assert_array_equal(r.tokens.cpu().numpy(), tok)
