@@ -101,6 +101,14 @@ using namespace lm;
 
 extern "C" {
 
+#ifdef LM_PROFILE_PHASES
+__attribute__((visibility("default"))) int lm_debug_phases(unsigned long long* out, int reset) {
+  if (cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 16) != cudaSuccess) return -3;
+  if (reset) { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z)); }
+  return 0;
+}
+#endif
+
 int lm_abi_version(void) { return LM_ABI_VERSION; }
 
 const char* lm_error_string(int code) {

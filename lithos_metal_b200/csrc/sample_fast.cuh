@@ -5,14 +5,13 @@
 // walk over counts, the top-p boundary a walk over count x exp(value) in FP64, exactly as the reference's numpy
 // definition forms them per distinct value (monolith/nn/sampling_ref.py:26-35; the reference's Metal kernels build
 // the same histogram in device memory with 256 KB per row, kernels/common/sample.metal:34-162). Logits changed by
-// the penalties are arbitrary FP32 values: they are counted in the bin of the largest BF16 value below them
-// and kept aside in a short list, so the walk stays exact by refining inside the one bin where it lands.
+// the penalties are arbitrary FP32 values: they leave the histogram and are kept aside as a short (index, value)
+// list that joins the walk at group level and exactly inside the one group where a threshold lands.
 // The draw then takes a second pass that finds the row in L2 (the next row is prefetched into L2 meanwhile).
 //
 // Rows this kernel cannot take (a counter overflow: more than 65535 equal logits; more than kSideCap penalised
-// logits; more than kBinSideCap of them in the bin a threshold lands in; vocabularies that are not a multiple of
-// 8 or exceed kFastMaxVocab; misaligned rows) are marked in `punt` and handled by the generic kernel launched
-// behind this one.
+// logits, or more than kLaneSideCap of them next to a threshold; vocabularies that are not a multiple of 8 or exceed
+// kFastMaxVocab; misaligned rows) are marked in `punt` and handled by the generic kernel launched behind this one.
 #pragma once
 #include "common.cuh"
 #include "draw.cuh"
@@ -20,27 +19,50 @@
 
 namespace lm {
 
+#ifdef LM_PROFILE_PHASES
+__device__ unsigned long long g_phase_cycles[16];
+#define LM_PHASE(i) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == 0) { const long long _t = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(_t - _t0)); _t0 = _t; } } while (0)
+#else
+#define LM_PHASE(i) do {} while (0)
+#endif
+
 constexpr int kFastMaxVocab = 262144;
 constexpr int kCodes = 65536;
-constexpr int kGroups = kCodes / 32;        // 2048 groups of 32 consecutive positions (descending value order)
+constexpr int kGroupBins = 256;             // positions per group: one 512-byte block of counters = one uint4 per lane
+constexpr int kGroups = kCodes / kGroupBins;
 constexpr int kSideCap = 4096;              // penalised logits per row the kernel keeps aside
-constexpr int kBinSideCap = 32;             // of those, how many may share the BF16 bin a threshold lands in
+constexpr int kLaneSideCap = 48;            // of those, how many may fall into one lane's 8 bins of the group being refined
 
 struct FastSmem {
   uint32_t hist[kCodes / 2];                // 128 KB: 16-bit counters, code c in half (c & 1) of word c >> 1
-  double gmass[kGroups];                    // 16 KB
-  uint32_t gcnt[kGroups];                   // 8 KB
-  float side_val[kSideCap];                 // 16 KB
-  float bin_side[32][kBinSideCap];          // 4 KB: side values of the 32 bins of the group being refined
+  float side_val[kSideCap];                 // 16 KB: penalised values ...
+  int side_idx[kSideCap];                   // 16 KB: ... and their vocabulary indices
+  union {                                   // the threshold walk and the draw never run at the same time
+    struct {
+      double lane_side_mass[32][kLaneSideCap];  // 12 KB: softmass of the side values of the group being refined, by owning lane
+      double lane_bin_mass[32][8];              // 2 KB: softmass of each lane's eight bins
+      float lane_side[32][kLaneSideCap];        // 6 KB: the side values themselves
+    };
+    struct {
+      uint64_t sweep_part[kFastMaxVocab / (kBlock * kChunk)][32];   // 8 KB: per-warp fixed-point mass of every sweep of the draw
+      uint32_t side_limb[kFastMaxVocab / (kBlock * kChunk)][3];     // 16-bit limbs of the side values' fixed-point mass per sweep
+    };
+  };
+  double gmass[kGroups];
+  uint32_t gcnt[kGroups];
+  uint32_t goff[kGroups + 1];               // side list sorted by group: group g holds entries [goff[g], goff[g + 1])
+  uint32_t gfill[kGroups];
+  uint32_t lane_side_n[32];
   DrawSmem draw;
   double warp_m[32];
   uint32_t warp_c[32];
-  uint32_t side_n, bin_side_n[32];
+  uint32_t side_n;
   uint32_t side_max_key;
+  uint32_t top_group, top_pos;
   int sel_group;
   uint32_t sel_base_c;
   double sel_base_m;
-  float res_tau; double res_cum_m; uint32_t res_cum_c; int res_fail;
+  float res_tau; double res_cum_m, res_above_m; uint32_t res_cum_c; int res_fail;
   uint32_t pen[kFastMaxVocab / 32];         // 32 KB bitmap of the row's distinct history ids
 };
 
@@ -56,7 +78,6 @@ __device__ __forceinline__ uint32_t floor_code(float v) {
   return code;
 }
 __device__ __forceinline__ uint32_t hist_get(const uint32_t* hist, uint32_t code) { return (hist[code >> 1] >> ((code & 1u) * 16u)) & 0xFFFFu; }
-__device__ __forceinline__ void hist_add(uint32_t* hist, uint32_t code) { atomicAdd(&hist[code >> 1], (code & 1u) ? 0x10000u : 1u); }
 
 // two logits of one 32-bit word into the histogram: address = code / 2 words, increment = 1 << (16 * (code & 1))
 __device__ __forceinline__ void hist_add_word(uint32_t* hist, uint32_t w) {
@@ -69,71 +90,99 @@ __device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
-// Exact walk inside one group of 32 positions (warp 0; the other warps wait at the barriers around the call).
-// Finds the first distinct value, descending, at which the running count reaches k_target (BY_MASS false) or the
-// running mass reaches m_target (BY_MASS true), starting from (base_c, base_m) = totals strictly above the group.
-// Results in s.res_*; s.res_fail = 1 if too many side values share one bin.
+// The eight counters a lane owns in group g: positions 256 g + 8 lane + j, j = 0..7, in descending value order.
+// Group g is one aligned block of 256 codes (block 127 - g for the positive half, block g for the negative half);
+// in the positive half codes run against positions, so the lane takes the mirrored uint4 and reverses it.
+__device__ __forceinline__ void lane_counts(const uint32_t* hist, int g, int lane, uint32_t cnt[8]) {
+  const bool pos_half = g < kGroups / 2;
+  const int block = pos_half ? (kGroups / 2 - 1 - g) : g;
+  const int q = pos_half ? (31 - lane) : lane;
+  const uint4 v = reinterpret_cast<const uint4*>(hist)[block * 32 + q];
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const int jj = pos_half ? 7 - j : j;                                  // code offset inside the uint4
+    cnt[j] = (w[jj >> 1] >> ((jj & 1) * 16)) & 0xFFFFu;
+  }
+}
+__device__ __forceinline__ uint32_t sum8(const uint4 v) {
+  const uint32_t a = (v.x & 0xFFFFu) + (v.x >> 16), b = (v.y & 0xFFFFu) + (v.y >> 16), c = (v.z & 0xFFFFu) + (v.z >> 16), d = (v.w & 0xFFFFu) + (v.w >> 16);
+  return a + b + c + d;
+}
+
+// Exact walk inside one group of 256 positions. Finds the first distinct value, descending, at which the running
+// count reaches k_target (BY_MASS false) or the running mass reaches m_target (BY_MASS true), starting from
+// (base_c, base_m) = totals strictly above the group. Lane L of warp 0 owns positions 8L..8L+7 of the group and
+// the side values whose bin lies there; the masses are computed by all warps first (warp w for owner lane w) so
+// that no thread runs a long chain of FP64 exponentials. Results in s.res_*; s.res_fail = 1 if too many side
+// values crowd one lane's bins.
 template <bool BY_MASS, bool NEED_MASS>
 __device__ void refine_group(FastSmem& s, int group, uint32_t base_c, double base_m, uint32_t k_target, double m_target, float vmax, double inv_t) {
-  const int tid = threadIdx.x, lane = tid & 31;
-  // every thread: the side values whose floor position falls in this group go to the list of their bin
-  if (tid < 32) s.bin_side_n[tid] = 0u;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < 32) s.lane_side_n[tid] = 0u;
   if (tid == 0) s.res_fail = 0;
   __syncthreads();
-  const uint32_t n_side = min(s.side_n, static_cast<uint32_t>(kSideCap));
-  for (uint32_t i = tid; i < n_side; i += kBlock) {
+  const uint32_t s0 = s.goff[group], s1 = s.goff[group + 1];               // this group's side values (the list is sorted by group)
+  for (uint32_t i = s0 + tid; i < s1; i += kBlock) {
     const float v = s.side_val[i];
-    const uint32_t pos = code_to_pos(floor_code(v));
-    if (static_cast<int>(pos >> 5) == group) {
-      const uint32_t slot = atomicAdd(&s.bin_side_n[pos & 31u], 1u);
-      if (slot < kBinSideCap) s.bin_side[pos & 31u][slot] = v; else s.res_fail = 1;
-    }
+    const uint32_t owner = (code_to_pos(floor_code(v)) % kGroupBins) >> 3;
+    const uint32_t slot = atomicAdd(&s.lane_side_n[owner], 1u);
+    if (slot < kLaneSideCap) s.lane_side[owner][slot] = v; else s.res_fail = 1;
   }
   __syncthreads();
   if (s.res_fail) return;
-  if (tid < 32) {
-    const uint32_t pos = static_cast<uint32_t>(group) * 32u + lane;
-    const uint32_t code = pos_to_code(pos);
-    const float bval = code_val(code);
-    const uint32_t cnt = hist_get(s.hist, code);
-    const uint32_t mine = s.bin_side_n[lane];                            // side values living in this lane's bin
-    const float* sv = s.bin_side[lane];
-    const uint32_t pure = cnt - mine;
-    double m = 0.0;
-    if (NEED_MASS && cnt) {
-      if (pure) m = static_cast<double>(pure) * softmass(bval, vmax, inv_t);
-      for (uint32_t i = 0; i < mine; i++) m += softmass(sv[i], vmax, inv_t);
+  if (NEED_MASS) {                                                         // warp w: the masses of owner lane w's bins and side values
+    const uint32_t pos0 = static_cast<uint32_t>(group) * kGroupBins + warp * 8u;
+    if (lane < 8) {
+      const uint32_t code = pos_to_code(pos0 + lane);
+      const uint32_t c = hist_get(s.hist, code);
+      s.lane_bin_mass[warp][lane] = c ? static_cast<double>(c) * softmass(code_val(code), vmax, inv_t) : 0.0;
+    } else {
+      for (uint32_t i = lane - 8; i < s.lane_side_n[warp]; i += 24) s.lane_side_mass[warp][i] = softmass(s.lane_side[warp][i], vmax, inv_t);
     }
-    uint32_t ci = cnt; double mi = m;
+    __syncthreads();
+  }
+  if (tid < 32) {
+    uint32_t cnt[8];
+    lane_counts(s.hist, group, lane, cnt);
+    const uint32_t m_side = s.lane_side_n[lane];
+    const float* sv = s.lane_side[lane];
+    const double* sm = s.lane_side_mass[lane];
+    const uint32_t pos0 = static_cast<uint32_t>(group) * kGroupBins + lane * 8u;
+    uint32_t c_lane = m_side; double m_lane = 0.0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) { c_lane += cnt[j]; if (NEED_MASS) m_lane += s.lane_bin_mass[lane][j]; }
+    if (NEED_MASS) for (uint32_t i = 0; i < m_side; i++) m_lane += sm[i];
+    uint32_t ci = c_lane; double mi = m_lane;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const uint32_t tc = __shfl_up_sync(kFull, ci, o);
       const double tm = __shfl_up_sync(kFull, mi, o);
       if (lane >= o) { ci += tc; mi += tm; }
     }
-    const bool hit = BY_MASS ? (cnt > 0 && base_m + mi >= m_target) : (base_c + ci >= k_target);
+    const bool hit = BY_MASS ? (c_lane > 0 && base_m + mi >= m_target) : (base_c + ci >= k_target);
     const uint32_t hits = __ballot_sync(kFull, hit);
-    const uint32_t occ = __ballot_sync(kFull, cnt > 0);
-    const int sel = hits ? (__ffs(hits) - 1) : (31 - __clz(occ));        // mass never reached (rounding): the lowest occupied bin
+    const uint32_t occ = __ballot_sync(kFull, c_lane > 0);
+    const int sel = hits ? (__ffs(hits) - 1) : (31 - __clz(occ));        // mass never reached (rounding): the lowest occupied lane
     if (lane == sel) {
-      // inside the bin: side values above the BF16 value, descending, equal values as one step, then the BF16 value itself
-      uint32_t run_c = base_c + ci - cnt; double run_m = base_m + mi - m;
-      float tau = bval; bool done = false;
-      float prev = INFINITY;
-      for (uint32_t step = 0; step < mine && !done; step++) {
-        float best = -INFINITY;                                          // the next distinct side value below `prev` and above bval
-        for (uint32_t i = 0; i < mine; i++) { const float v = sv[i]; if (v < prev && v > bval && v > best) best = v; }
-        if (best == -INFINITY) break;
-        uint32_t n_eq = 0;
-        for (uint32_t i = 0; i < mine; i++) if (sv[i] == best) n_eq++;
-        run_c += n_eq; if (NEED_MASS) run_m += static_cast<double>(n_eq) * softmass(best, vmax, inv_t);
-        if (BY_MASS ? (run_m >= m_target) : (run_c >= k_target)) { tau = best; done = true; }
-        prev = best;
+      // this lane's distinct values, descending: BF16 bin values (pure counts) merged with its side values
+      uint32_t run_c = base_c + ci - c_lane; double run_m = base_m + mi - m_lane;
+      float tau = 0.0f, prev = INFINITY; bool done = false;
+      double above_m = run_m;
+      for (int step = 0; step < 8 + kLaneSideCap && !done; step++) {
+        above_m = run_m;
+        float best = -INFINITY; bool any = false;                        // the next distinct value below `prev`
+#pragma unroll
+        for (int j = 0; j < 8; j++) { const float b = code_val(pos_to_code(pos0 + j)); if (cnt[j] && b < prev && (!any || b > best)) { best = b; any = true; } }
+        for (uint32_t i = 0; i < m_side; i++) { const float v = sv[i]; if (v < prev && (!any || v > best)) { best = v; any = true; } }
+        if (!any) break;
+#pragma unroll
+        for (int j = 0; j < 8; j++) if (cnt[j] && code_val(pos_to_code(pos0 + j)) == best) { run_c += cnt[j]; if (NEED_MASS) run_m += s.lane_bin_mass[lane][j]; }
+        for (uint32_t i = 0; i < m_side; i++) if (sv[i] == best) { run_c += 1u; if (NEED_MASS) run_m += sm[i]; }
+        tau = best; prev = best;
+        if (BY_MASS ? (run_m >= m_target) : (run_c >= k_target)) done = true;
       }
-      if (!done) {                                                        // the BF16 value's own tie group (pure elements + side values equal to it)
-        run_c = base_c + ci; run_m = base_m + mi; tau = bval;
-      }
-      s.res_tau = tau; s.res_cum_c = run_c; s.res_cum_m = run_m;
+      s.res_tau = tau; s.res_cum_c = run_c; s.res_cum_m = run_m; s.res_above_m = above_m;   // not done: rounding left the target unreached; the last value stands
     }
   }
   __syncthreads();
@@ -144,44 +193,38 @@ __device__ void refine_group(FastSmem& s, int group, uint32_t base_c, double bas
 template <bool BY_MASS>
 __device__ void find_group(FastSmem& s, uint32_t k_target, double m_target) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // thread t owns groups 2t and 2t + 1
-  const uint32_t c0 = s.gcnt[2 * tid], c1 = s.gcnt[2 * tid + 1];
-  const double m0 = BY_MASS ? s.gmass[2 * tid] : 0.0, m1 = BY_MASS ? s.gmass[2 * tid + 1] : 0.0;
-  uint32_t ci = c0 + c1; double mi = m0 + m1;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t tc = __shfl_up_sync(kFull, ci, o);
-    const double tm = BY_MASS ? __shfl_up_sync(kFull, mi, o) : 0.0;
-    if (lane >= o) { ci += tc; mi += tm; }
-  }
+  uint32_t c = 0, ci = 0; double m = 0.0, mi = 0.0;
   if (tid == 0) s.sel_group = kGroups;
-  if (lane == 31) { s.warp_c[warp] = ci; s.warp_m[warp] = mi; }
-  __syncthreads();
-  uint32_t wc = 0; double wm = 0.0;
-  for (int w = 0; w < warp; w++) { wc += s.warp_c[w]; if (BY_MASS) wm += s.warp_m[w]; }
-  const uint32_t excl_c = wc + ci - (c0 + c1); const double excl_m = wm + mi - (m0 + m1);
-  // first of this thread's two groups that reaches the target
-  int g = kGroups;
-  if (BY_MASS) {
-    if (c0 > 0 && excl_m + m0 >= m_target) g = 2 * tid; else if (c1 > 0 && excl_m + m0 + m1 >= m_target) g = 2 * tid + 1;
-  } else {
-    if (excl_c + c0 >= k_target) g = 2 * tid; else if (excl_c + c0 + c1 >= k_target) g = 2 * tid + 1;
+  if (tid < kGroups) {
+    c = s.gcnt[tid]; ci = c;
+    if (BY_MASS) { m = s.gmass[tid]; mi = m; }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t tc = __shfl_up_sync(kFull, ci, o);
+      const double tm = BY_MASS ? __shfl_up_sync(kFull, mi, o) : 0.0;
+      if (lane >= o) { ci += tc; mi += tm; }
+    }
+    if (lane == 31) { s.warp_c[warp] = ci; s.warp_m[warp] = mi; }
   }
-  if (g < kGroups) atomicMin(&s.sel_group, g);
+  __syncthreads();
+  if (tid < kGroups) {
+    uint32_t wc = 0; double wm = 0.0;
+    for (int w = 0; w < warp; w++) { wc += s.warp_c[w]; if (BY_MASS) wm += s.warp_m[w]; }
+    ci += wc; mi += wm;
+    const bool hit = BY_MASS ? (c > 0 && mi >= m_target) : (ci >= k_target);
+    if (hit) atomicMin(&s.sel_group, tid);
+  }
   __syncthreads();
   int sel = s.sel_group;
   if (sel == kGroups) {                                                   // mass never reached (rounding): the last occupied group
     __syncthreads();
     if (tid == 0) s.sel_group = -1;
     __syncthreads();
-    if (c1 > 0) atomicMax(&s.sel_group, 2 * tid + 1); else if (c0 > 0) atomicMax(&s.sel_group, 2 * tid);
+    if (tid < kGroups && c > 0) atomicMax(&s.sel_group, tid);
     __syncthreads();
     sel = s.sel_group;
   }
-  if ((sel >> 1) == tid) {
-    s.sel_base_c = excl_c + ((sel & 1) ? c0 : 0u);
-    s.sel_base_m = excl_m + ((sel & 1) ? m0 : 0.0);
-  }
+  if (tid == sel) { s.sel_base_c = ci - c; s.sel_base_m = mi - m; }
   __syncthreads();
 }
 
@@ -197,36 +240,68 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
   const bool takeable = (V % kChunk) == 0 && V <= kFastMaxVocab && (reinterpret_cast<uintptr_t>(rowp) & 15u) == 0 && (T >= 0.0f) && V > 0;
   if (!takeable) { if (tid == 0) punt[row] = 1u; return; }
 
+#ifdef LM_PROFILE_PHASES
+  long long _t0 = clock64();
+#endif
   RowView rv;
   rv.dtype = LM_DTYPE_BF16; rv.vocab = V; rv.rho = P.rho; rv.pi = P.pi; rv.row = rowp; rv.aligned = true; rv.pen = nullptr;
   const int n_chunks = V / kChunk;
 
-  // ---- clear the histogram; the history's distinct ids as a bitmap ---------------------------------------------
+  // ---- clear the histogram; the history's distinct ids as a bitmap and as a list -------------------------------------
   {
     uint4* h4 = reinterpret_cast<uint4*>(s.hist);
     for (int i = tid; i < kCodes / 8; i += kBlock) h4[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (tid == 0) { s.side_n = 0u; s.side_max_key = 0u; }
+    if (tid == 0) { s.side_n = 0u; s.side_max_key = 0u; s.top_group = kGroups; s.top_pos = 0xFFFFFFFFu; }
+    if (tid < kGroups) { s.gfill[tid] = 0u; s.goff[tid] = 0u; }
+    if (tid == 0) s.goff[kGroups] = 0u;
     if (pen_on) {
       const int words = (V + 31) / 32;
       for (int i = tid; i < words; i += kBlock) s.pen[i] = 0u;
       __syncthreads();
       const int32_t* h = P.history + static_cast<int64_t>(row) * P.hist_stride;
-      for (int i = tid; i < P.hist_len; i += kBlock) {
-        const int id = __ldg(h + i);
-        if (id >= 0 && id < V) atomicOr(&s.pen[id >> 5], 1u << (id & 31));
+      const int n_hist = (P.hist_len + kBlock - 1) / kBlock * kBlock;       // uniform trip count: warp votes inside
+      for (int i = tid; i < n_hist; i += kBlock) {
+        const int id = (i < P.hist_len) ? __ldg(h + i) : -1;
+        bool fresh = false;
+        if (id >= 0 && id < V) {
+          const uint32_t bit = 1u << (id & 31);
+          fresh = (atomicOr(&s.pen[id >> 5], bit) & bit) == 0u;           // the thread that sets the bit owns the id
+        }
+        const uint32_t votes = __ballot_sync(kFull, fresh);
+        uint32_t base = 0;
+        if (lane == 0 && votes) base = atomicAdd(&s.side_n, __popc(votes));
+        base = __shfl_sync(kFull, base, 0);
+        if (fresh) {
+          const uint32_t slot = base + __popc(votes & ((1u << lane) - 1u));
+          if (slot < kSideCap) s.side_idx[slot] = id;
+        }
       }
       rv.pen = s.pen;
     }
     __syncthreads();
   }
+  LM_PHASE(0);
+  if (s.side_n > kSideCap) { if (tid == 0) punt[row] = 1u; return; }      // more distinct penalised ids than the list holds
+  const uint32_t n_side = s.side_n;
+  const SideList side{s.side_idx, s.side_val, n_side};
 
   if (T == 0.0f) {                                                        // greedy: a streaming argmax, no histogram
     uint64_t best = 0ull;
     for (int c = tid; c < n_chunks; c += kBlock) {
-      float z[kChunk];
-      load_chunk(rv, c, z);
+      const uint4 q = __ldg(reinterpret_cast<const uint4*>(rowp) + c);
+      const uint32_t bits = pen_on ? ((s.pen[c >> 2] >> ((c & 3) * 8)) & 0xFFu) : 0u;
+      const float z[kChunk] = {bf16_lo(q.x), bf16_hi(q.x), bf16_lo(q.y), bf16_hi(q.y), bf16_lo(q.z), bf16_hi(q.z), bf16_lo(q.w), bf16_hi(q.w)};
 #pragma unroll
-      for (int e = 0; e < kChunk; e++) { const uint64_t p = pack_best(z[e], static_cast<uint32_t>(c * kChunk + e)); best = p > best ? p : best; }
+      for (int e = 0; e < kChunk; e++) {
+        const uint64_t p = pack_best(canon_zero(z[e]), static_cast<uint32_t>(c * kChunk + e));
+        if (!((bits >> e) & 1u)) best = p > best ? p : best;              // penalised positions come from the list below
+      }
+    }
+    for (uint32_t i = tid; i < n_side; i += kBlock) {
+      const int id = s.side_idx[i];
+      const float v = canon_zero(penalise(code_val(__ldg(rowp + id)), P.rho, P.pi));
+      const uint64_t p = pack_best(v, static_cast<uint32_t>(id));
+      best = p > best ? p : best;
     }
     best = block_max_u64(best, s.draw.scratch);
     if (tid == 0) {
@@ -238,41 +313,79 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
     return;
   }
 
-  // ---- pass 1: the histogram, straight from HBM; penalised logits also go to the side list -------------------------
+  // ---- pass 1: the histogram of the raw row, straight from HBM ----------------------------------------------------------
   {
     const uint4* p4 = reinterpret_cast<const uint4*>(rowp);
     constexpr int kUnroll = 4;
     for (int c0 = tid; c0 < n_chunks; c0 += kBlock * kUnroll) {
       uint4 q[kUnroll];
 #pragma unroll
-      for (int j = 0; j < kUnroll; j++) { const int c = c0 + j * kBlock; if (c < n_chunks) q[j] = __ldg(p4 + c); }
+      for (int j = 0; j < kUnroll; j++) { const int c = c0 + j * kBlock; q[j] = (c < n_chunks) ? __ldg(p4 + c) : make_uint4(0u, 0u, 0u, 0u); }
 #pragma unroll
       for (int j = 0; j < kUnroll; j++) {
-        const int c = c0 + j * kBlock;
-        if (c >= n_chunks) break;
-        const uint32_t bits = pen_on ? ((s.pen[c >> 2] >> ((c & 3) * 8)) & 0xFFu) : 0u;
-        if (bits == 0u) {
+        if (c0 + j * kBlock < n_chunks) {
           hist_add_word(s.hist, q[j].x); hist_add_word(s.hist, q[j].y); hist_add_word(s.hist, q[j].z); hist_add_word(s.hist, q[j].w);
-        } else {
-          const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
-#pragma unroll
-          for (int e = 0; e < kChunk; e++) {
-            const uint32_t code = (e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xFFFFu);
-            if ((bits >> e) & 1u) {
-              const float v = penalise(code_val(code), P.rho, P.pi);
-              hist_add(s.hist, floor_code(v));
-              const uint32_t slot = atomicAdd(&s.side_n, 1u);
-              if (slot < kSideCap) s.side_val[slot] = v;
-              atomicMax(&s.side_max_key, fkey(v));
-            } else {
-              hist_add(s.hist, code);
-            }
-          }
         }
+      }
+    }
+  }
+  // ---- the penalised logits leave the histogram (their raw value was counted above) and go to the side list, sorted by
+  // group. Each thread keeps its (index, code) in registers: the gathers are issued before the barrier that ends
+  // pass 1, and the list is rewritten in place once every thread has read its entries.
+  uint32_t sd_code[kSideCap / kBlock]; int sd_idx[kSideCap / kBlock];
+#pragma unroll
+  for (int j = 0; j < kSideCap / kBlock; j++) {
+    const uint32_t i = tid + j * kBlock;
+    sd_idx[j] = (i < n_side) ? s.side_idx[i] : 0;
+    sd_code[j] = (i < n_side) ? __ldg(rowp + sd_idx[j]) : 0u;
+  }
+  __syncthreads();
+  LM_PHASE(1);
+  if (n_side) {
+    float sd_val[kSideCap / kBlock]; uint32_t sd_grp[kSideCap / kBlock];
+    uint32_t mx = 0u;
+#pragma unroll
+    for (int j = 0; j < kSideCap / kBlock; j++) {
+      if (tid + j * kBlock < n_side) {
+        const float v = penalise(code_val(sd_code[j]), P.rho, P.pi);
+        sd_val[j] = v; sd_grp[j] = code_to_pos(floor_code(v)) / kGroupBins;
+        atomicSub(&s.hist[sd_code[j] >> 1], (sd_code[j] & 1u) ? 0x10000u : 1u);
+        atomicAdd(&s.gfill[sd_grp[j]], 1u);
+        mx = max(mx, fkey(v));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(kFull, mx, o));
+    if (lane == 0 && mx) atomicMax(&s.side_max_key, mx);
+    __syncthreads();
+    if (tid < kGroups) {                                                  // exclusive prefix of the per-group side counts -> goff
+      const uint32_t c = s.gfill[tid];
+      uint32_t ci = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, ci, o); if (lane >= o) ci += t; }
+      if (lane == 31) s.warp_c[warp] = ci;
+      __syncwarp();
+      s.gcnt[tid] = ci - c;                                               // parked here until the warp totals are known
+    }
+    __syncthreads();
+    if (tid < kGroups) {
+      uint32_t wc = 0;
+      for (int w = 0; w < warp; w++) wc += s.warp_c[w];
+      s.goff[tid] = s.gcnt[tid] + wc;
+      s.gfill[tid] = 0u;
+      if (tid == kGroups - 1) s.goff[kGroups] = n_side;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kSideCap / kBlock; j++) {
+      if (tid + j * kBlock < n_side) {
+        const uint32_t slot = s.goff[sd_grp[j]] + atomicAdd(&s.gfill[sd_grp[j]], 1u);
+        s.side_val[slot] = sd_val[j]; s.side_idx[slot] = sd_idx[j];
       }
     }
     __syncthreads();
   }
+  LM_PHASE(2);
   // the next row of this block: start pulling it into L2 while this one is selected and drawn
   {
     const int next = row + gridDim.x;
@@ -283,31 +396,27 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
       const uint32_t off = piece * lane;
       if (off < bytes) prefetch_l2(np + off, min(piece, bytes - off));
     }
+    if (next < P.rows && tid == 32 && pen_on) {
+      const char* hp = reinterpret_cast<const char*>(P.history + static_cast<int64_t>(next) * P.hist_stride);
+      const uint32_t hb = (static_cast<uint32_t>(P.hist_len) * 4u) & ~15u;
+      if ((reinterpret_cast<uintptr_t>(hp) & 15u) == 0 && hb) prefetch_l2(hp, hb);
+    }
   }
 
-  // ---- group counts, the overflow check, the maximum ---------------------------------------------------------------
-  uint32_t total_c = 0; uint32_t top_pos = 0xFFFFFFFFu;
+  // ---- group counts (pure BF16 logits), the overflow check, the maximum ------------------------------------------------
   for (int g = warp; g < kGroups; g += 32) {
-    const uint32_t pos = static_cast<uint32_t>(g) * 32u + lane;
-    const uint32_t cnt = hist_get(s.hist, pos_to_code(pos));
-    const uint32_t occ = __ballot_sync(kFull, cnt > 0);
-    uint32_t c = cnt;
+    const bool pos_half = g < kGroups / 2;
+    const int block = pos_half ? (kGroups / 2 - 1 - g) : g;
+    uint32_t c = sum8(reinterpret_cast<const uint4*>(s.hist)[block * 32 + lane]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(kFull, c, o);
-    if (lane == 0) s.gcnt[g] = c;
-    total_c += c;
-    if (occ && top_pos == 0xFFFFFFFFu) top_pos = static_cast<uint32_t>(g) * 32u + (__ffs(occ) - 1);
-  }
-  // total over the warps; the lowest occupied position
-  if (lane == 0) { s.warp_c[warp] = total_c; s.draw.scratch[warp] = top_pos; }
-  __syncthreads();
-  {
-    uint32_t t = 0, tp = 0xFFFFFFFFu;
-    for (int w = 0; w < 32; w++) { t += s.warp_c[w]; tp = min(tp, static_cast<uint32_t>(s.draw.scratch[w])); }
-    total_c = t; top_pos = tp;
+    if (lane == 0) { s.gcnt[g] = c; if (c) atomicMin(&s.top_group, static_cast<uint32_t>(g)); }
   }
   __syncthreads();
-  if (total_c != static_cast<uint32_t>(V) || s.side_n > kSideCap) {       // a 16-bit counter wrapped, or too many penalised logits
+  uint32_t total_c = 0;
+  if (tid < kGroups) total_c = s.gcnt[tid];
+  total_c = static_cast<uint32_t>(block_sum_u64(total_c, s.draw.scratch));
+  if (total_c + n_side != static_cast<uint32_t>(V)) {                     // a 16-bit counter wrapped: more than 65535 equal logits
     if (tid == 0) punt[row] = 1u;
     return;
   }
@@ -317,9 +426,21 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
     if (tid < 127) nan_c = hist_get(s.hist, 0x7F81u + tid) + hist_get(s.hist, 0xFF81u + tid);
     if (__syncthreads_or(nan_c != 0u)) status |= LM_STATUS_NAN;
   }
-  const float top_val = code_val(pos_to_code(top_pos));
+  if (tid < 32 && s.top_group < kGroups) {                                // the highest occupied bin of the highest occupied group
+    uint32_t cnt[8];
+    lane_counts(s.hist, static_cast<int>(s.top_group), lane, cnt);
+    uint32_t p = 0xFFFFFFFFu;
+#pragma unroll
+    for (int j = 7; j >= 0; j--) if (cnt[j]) p = s.top_group * kGroupBins + lane * 8u + j;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) p = min(p, __shfl_xor_sync(kFull, p, o));
+    if (lane == 0) s.top_pos = p;
+  }
+  __syncthreads();
+  const float top_val = (s.top_pos != 0xFFFFFFFFu) ? code_val(pos_to_code(s.top_pos)) : -INFINITY;
   const float side_max = s.side_max_key ? fkey_inv(s.side_max_key) : -INFINITY;
-  const float vmax = (s.side_n > 0 && side_max > top_val) ? side_max : top_val;
+  const float vmax = (n_side > 0 && side_max > top_val) ? side_max : top_val;
+  LM_PHASE(3);
 
   // ---- thresholds ----------------------------------------------------------------------------------------------------
   const double T64 = static_cast<double>(T), inv_t = 1.0 / T64;
@@ -329,57 +450,65 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
   double tau64 = -INFINITY; bool have_tau = false;
   double topk_mass = 0.0;
   if (has_p) {
-    // group masses: every bin as if all its logits sat at the bin's BF16 value, then the side values' excess
+    // group masses: count x exp64 per occupied bin (eight bins per lane) plus the exact softmass of the group's side values
     for (int g = warp; g < kGroups; g += 32) {
-      if (s.gcnt[g] == 0u) { if (lane == 0) s.gmass[g] = 0.0; continue; }
-      const uint32_t code = pos_to_code(static_cast<uint32_t>(g) * 32u + lane);
-      const uint32_t cnt = hist_get(s.hist, code);
-      double m = cnt ? static_cast<double>(cnt) * softmass(code_val(code), vmax, inv_t) : 0.0;
+      const uint32_t s0 = s.goff[g], s1 = s.goff[g + 1];
+      if (s.gcnt[g] == 0u && s0 == s1) { if (lane == 0) s.gmass[g] = 0.0; continue; }
+      double m = 0.0;
+      if (s.gcnt[g]) {
+        uint32_t cnt[8];
+        lane_counts(s.hist, g, lane, cnt);
+        const uint32_t pos0 = static_cast<uint32_t>(g) * kGroupBins + lane * 8u;
+#pragma unroll
+        for (int j = 0; j < 8; j++) if (cnt[j]) m += static_cast<double>(cnt[j]) * softmass(code_val(pos_to_code(pos0 + j)), vmax, inv_t);
+      }
+      for (uint32_t i = s0 + lane; i < s1; i += 32) m += softmass(s.side_val[i], vmax, inv_t);
       m = warp_sum_f64(m);
       if (lane == 0) s.gmass[g] = m;
     }
     __syncthreads();
-    const uint32_t n_side = s.side_n;
-    for (uint32_t i = tid; i < n_side; i += kBlock) {
-      const float v = s.side_val[i];
-      const uint32_t code = floor_code(v);
-      const double d = softmass(v, vmax, inv_t) - softmass(code_val(code), vmax, inv_t);
-      if (d != 0.0) atomicAdd(&s.gmass[code_to_pos(code) >> 5], d);
-    }
-    __syncthreads();
   }
+  if (tid < kGroups) s.gcnt[tid] += s.goff[tid + 1] - s.goff[tid];         // the side values join the group counts
+  __syncthreads();
+  LM_PHASE(4);
+  // The running mass strictly above tau_k (the top-k walk carries masses whenever top-p is on): if it stays below the
+  // top-p target, the top-p boundary lies at or below tau_k and tau = tau_k without a second walk.
+  double above_k_mass = 0.0;
   if (has_k) {
     find_group<false>(s, static_cast<uint32_t>(top_k), 0.0);
     double base_m = 0.0;
-    if (in_topk) {                                                        // the mass strictly above the group: needed for the top-k set's mass
+    if (has_p) {                                                          // the mass strictly above the group
       double m = 0.0;
-      for (int g = tid; g < s.sel_group; g += kBlock) m += s.gmass[g];
+      if (tid < s.sel_group) m = s.gmass[tid];
       base_m = block_sum_f64(m, s.draw.scratch);
     }
-    if (in_topk) refine_group<false, true>(s, s.sel_group, s.sel_base_c, base_m, static_cast<uint32_t>(top_k), 0.0, vmax, inv_t);
+    if (has_p) refine_group<false, true>(s, s.sel_group, s.sel_base_c, base_m, static_cast<uint32_t>(top_k), 0.0, vmax, inv_t);
     else refine_group<false, false>(s, s.sel_group, s.sel_base_c, 0.0, static_cast<uint32_t>(top_k), 0.0, vmax, inv_t);
     if (s.res_fail) { if (tid == 0) punt[row] = 1u; return; }
     tau64 = s.res_tau; have_tau = true;
-    topk_mass = s.res_cum_m;
+    topk_mass = s.res_cum_m; above_k_mass = s.res_above_m;
     __syncthreads();
   }
+  LM_PHASE(5);
   if (has_p) {
     double total;
     if (in_topk) total = topk_mass;
     else {
       double m = 0.0;
-      for (int g = tid; g < kGroups; g += kBlock) m += s.gmass[g];
+      if (tid < kGroups) m = s.gmass[tid];
       total = block_sum_f64(m, s.draw.scratch);
     }
     const double target = static_cast<double>(top_p) * total;
-    find_group<true>(s, 0u, target);
-    refine_group<true, true>(s, s.sel_group, s.sel_base_c, s.sel_base_m, 0u, target, vmax, inv_t);
-    if (s.res_fail) { if (tid == 0) punt[row] = 1u; return; }
-    const double eps = 1e-12 * total;
-    if (fabs(s.res_cum_m - target) <= eps) status |= LM_STATUS_TOPP_EDGE;
-    if (!have_tau || static_cast<double>(s.res_tau) > tau64) tau64 = s.res_tau;
-    have_tau = true;
-    __syncthreads();
+    if (!has_k || above_k_mass >= target) {
+      find_group<true>(s, 0u, target);
+      refine_group<true, true>(s, s.sel_group, s.sel_base_c, s.sel_base_m, 0u, target, vmax, inv_t);
+      if (s.res_fail) { if (tid == 0) punt[row] = 1u; return; }
+      const double eps = 1e-12 * total;
+      if (fabs(s.res_cum_m - target) <= eps) status |= LM_STATUS_TOPP_EDGE;
+      if (!have_tau || static_cast<double>(s.res_tau) > tau64) tau64 = s.res_tau;
+      have_tau = true;
+      __syncthreads();
+    } else if (fabs(above_k_mass - target) <= 1e-12 * total) status |= LM_STATUS_TOPP_EDGE;
   }
   if (has_m) {
     const double tau_m = static_cast<double>(vmax) + T64 * log(static_cast<double>(min_p));
@@ -387,16 +516,18 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
     have_tau = true;
   }
   const float tau = have_tau ? __double2float_rn(tau64) : -INFINITY;
+  LM_PHASE(6);
 
   // ---- pass 2: the draw over the kept set (the row is in L2) ---------------------------------------------------------
   int token;
   if (P.draw == LM_DRAW_INVERSE_CDF) {
-    token = draw_inverse_cdf(rv, tau, vmax, T, P.uniforms ? P.uniforms[row] : 0.0f, s.draw);
+    token = draw_inverse_cdf<true>(rv, tau, vmax, T, P.uniforms ? P.uniforms[row] : 0.0f, s.draw, side, &s.sweep_part[0][0], &s.side_limb[0][0]);
   } else {
     bool tie = false;
-    token = draw_gumbel(rv, tau, T, P.seed, P.step, static_cast<uint32_t>(P.row_offset + row), s.draw, &tie);
+    token = draw_gumbel<true>(rv, tau, T, P.seed, P.step, static_cast<uint32_t>(P.row_offset + row), s.draw, &tie, side);
     if (tie) status |= LM_STATUS_NEAR_TIE;
   }
+  LM_PHASE(7);
   if (tid == 0) {
     P.out_tokens[row] = token;
     if (P.out_tau) P.out_tau[row] = tau;
