@@ -128,6 +128,28 @@ LM_API int lm_argmax(const void* logits, int32_t dtype, int64_t rows, int64_t vo
               void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * lm_argmax with its scratch inside the library: for callers that cannot allocate device memory.
+ *
+ * Has no counterpart in lithos-metal (whose programs size every buffer at compile time). Some hosts of this library
+ * are handed tensors and a stream and nothing else: a runtime plug-in called from a frozen decode loop, a step
+ * that runs while the engine's allocator is locked or while a memory budget is already spent, code that must not
+ * call cudaMalloc because cudaMalloc synchronises the device. They cannot create the workspace lm_argmax needs when it
+ * splits rows over several thread blocks, so this entry point keeps that workspace in a fixed device array that is
+ * part of the library image: LM_ARGMAX_STATIC_MAX_ROWS entries of 16 bytes (64 KiB), resident on every GPU that
+ * loads the library for as long as the process lives.
+ *
+ *   - same arguments and result as lm_argmax, minus the workspace; rows > LM_ARGMAX_STATIC_MAX_ROWS returns LM_E_UNSUPPORTED;
+ *   - it allocates nothing: no cudaMalloc / cudaFree and no allocating library call, on any call;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current) and remembers it; make that first call before starting a stream capture;
+ *   - every call uses the same array and clears the part it needs on the given stream before the kernel runs, so
+ *     calls on one stream may follow each other freely, but two calls that can overlap on the GPU (different
+ *     streams without an ordering between them, or different host threads) race on it: order them yourself.
+ */
+#define LM_ARGMAX_STATIC_MAX_ROWS 4096
+LM_API int lm_argmax_static(const void* logits, int32_t dtype, int64_t rows, int64_t vocab, int64_t row_stride, int32_t* out_tokens, void* stream);
+
+/*
  * One DSpark verification step: n_draft drafted tokens checked against n_draft + 1 rows of target logits.
  *
  * Stands in for accept_scan's prefix match (kernels/common/spec_ops.metal:162-165) when mode == LM_VERIFY_GREEDY and for

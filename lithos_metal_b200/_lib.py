@@ -15,6 +15,7 @@ VERIFY_GREEDY, VERIFY_STOCHASTIC = 0, 1
 STATUS_GENERIC_PATH, STATUS_NAN, STATUS_NEAR_TIE, STATUS_TOPP_EDGE = 1, 2, 4, 8
 MAX_DRAFT = 15
 MAX_VOCAB = 1048576
+ARGMAX_STATIC_MAX_ROWS = 4096
 
 
 class SampleArgs(C.Structure):
@@ -43,7 +44,7 @@ class VerifyArgs(C.Structure):
     ]
 
 
-EXPORTS = ["lm_sample", "lm_argmax", "lm_verify", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
+EXPORTS = ["lm_sample", "lm_argmax", "lm_argmax_static", "lm_verify", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
            "lm_error_string", "lm_last_cuda_error", "lm_device_sm_count"]
 
 _lib = None
@@ -67,6 +68,8 @@ def lib():
         L.lm_verify.argtypes = [C.POINTER(VerifyArgs)]
         L.lm_argmax.restype = C.c_int
         L.lm_argmax.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.lm_argmax_static.restype = C.c_int
+        L.lm_argmax_static.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
         L.lm_workspace_bytes.restype = C.c_size_t
         L.lm_workspace_bytes.argtypes = [C.c_int64, C.c_int64]
         L.lm_verify_workspace_bytes.restype = C.c_size_t

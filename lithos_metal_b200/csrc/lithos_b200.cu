@@ -5,6 +5,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 #include "sample_generic.cuh"
@@ -71,6 +72,10 @@ __global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, uin
     __syncthreads();
   }
 }
+
+// Scratch of lm_argmax_static: a fixed array in the library image (zero at load). In host code this name is only a
+// handle for cudaGetSymbolAddress; the kernels get the device address that call returns.
+static __device__ __align__(256) ArgmaxWs g_argmax_static_ws[LM_ARGMAX_STATIC_MAX_ROWS];
 
 thread_local char g_cuda_error[256] = "";
 
@@ -171,6 +176,40 @@ int lm_argmax(const void* logits, int32_t dtype, int64_t rows, int64_t vocab, in
   }
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+// The allocation-free variant of lm_argmax: the same kernel, its workspace in g_argmax_static_ws.
+int lm_argmax_static(const void* logits, int32_t dtype, int64_t rows, int64_t vocab, int64_t row_stride, int32_t* out_tokens, void* stream) {
+  if (rows < 0 || vocab < 0 || (dtype != LM_DTYPE_BF16 && dtype != LM_DTYPE_F32)) return LM_E_INVALID;
+  if (rows == 0) return LM_OK;
+  if (!logits || !out_tokens || row_stride < vocab) return LM_E_INVALID;
+  if (rows > LM_ARGMAX_STATIC_MAX_ROWS || vocab > LM_MAX_VOCAB) return LM_E_UNSUPPORTED;   // beyond the fixed scratch
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  // set-up, once per device, with that device current: the device address of the scratch array
+  constexpr int kMaxDevices = 64;
+  static void* ws_addr[kMaxDevices] = {nullptr};
+  static std::mutex ws_mutex;
+  if (dev < 0 || dev >= kMaxDevices) return LM_E_UNSUPPORTED;
+  void* ws = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(ws_mutex);
+    if (ws_addr[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_argmax_static_ws);
+      if (e != cudaSuccess) return cuda_fail(e);
+      ws_addr[dev] = p;
+    }
+    ws = ws_addr[dev];
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the array keeps whatever the last call left: the entries this call uses must start at zero
+  e = cudaMemsetAsync(ws, 0, static_cast<size_t>(rows) * sizeof(ArgmaxWs), st);
+  if (e != cudaSuccess) return cuda_fail(e);
+  // lm_argmax touches one ArgmaxWs entry per row and nothing else of a workspace; the size given here only has to
+  // pass its general workspace check
+  return lm_argmax(logits, dtype, rows, vocab, row_stride, out_tokens, ws, lm_workspace_bytes(rows, vocab), st);
 }
 
 int lm_sample(const lm_sample_args* a) {
