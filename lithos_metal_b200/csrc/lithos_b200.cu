@@ -107,6 +107,9 @@ using namespace lm;
 extern "C" {
 
 #ifdef LM_PROFILE_PHASES
+__attribute__((visibility("default"))) int lm_debug_verify_times(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_verify_times, sizeof(unsigned long long) * 8) == cudaSuccess ? 0 : -3;
+}
 __attribute__((visibility("default"))) int lm_debug_phases(unsigned long long* out, int reset) {
   if (cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 16) != cudaSuccess) return -3;
   if (reset) { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z)); }
@@ -301,9 +304,27 @@ int lm_verify(const lm_verify_args* a) {
   int grid = sms < 1024 ? sms : 1024;
   const int max_useful = static_cast<int>((a->vocab + 7) / 8);
   if (grid > max_useful) grid = max_useful;
-  void* params[] = {&P};
-  const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(verify_kernel), dim3(grid), dim3(kVerifyBlock), params, 0,
+  // the block's slices of all rows in shared memory when they fit (they do for every vocabulary up to ~700k at 148 SMs)
+  const int per = (static_cast<int>((a->vocab + grid - 1) / grid) + 7) & ~7;
+  const size_t rows_cached = static_cast<size_t>(a->n_draft + 1) + (a->mode == LM_VERIFY_STOCHASTIC ? a->n_draft : 0);
+  size_t smem = rows_cached * static_cast<size_t>(per) * sizeof(float);
+  int cached = smem <= 200 * 1024 ? 1 : 0;
+  if (!cached) smem = 0;
+  static thread_local size_t verify_smem_set = 0;
+  if (smem > 48 * 1024 && smem > verify_smem_set) {
+    const cudaError_t ea = cudaFuncSetAttribute(verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (ea != cudaSuccess) return cuda_fail(ea);
+    verify_smem_set = smem;
+  }
+  void* params[] = {&P, &cached};
+#ifdef LM_VERIFY_PLAIN_LAUNCH
+  verify_kernel<<<grid, kVerifyBlock, smem, static_cast<cudaStream_t>(a->stream)>>>(P, cached);
+  const cudaError_t e = cudaGetLastError();
+  (void)params;
+#else
+  const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(verify_kernel), dim3(grid), dim3(kVerifyBlock), params, smem,
                                                     static_cast<cudaStream_t>(a->stream));
+#endif
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }
 

@@ -5,15 +5,20 @@
 // vocabulary is split between blocks.
 //
 // The step is latency-bound (a few MB of input, a chain of three data dependencies), so the kernel is one
-// cooperative launch of one block per SM; every block owns the same vocabulary slice of every row in every phase
-// (re-reads hit L1/L2), partial results meet in a small workspace, and the phases are separated by a bounded
-// grid barrier on a counter in that workspace.
+// cooperative launch of one block per SM; every block owns the same vocabulary slice of every row in every phase.
+// Phase 0 is the only one that touches HBM: it pulls the block's slice of all target rows and all draft-probability
+// rows into shared memory (one pass over both inputs, every load in flight at once); the later phases work from
+// there. Partial results meet in a small workspace, and the phases are separated by a bounded grid barrier on a
+// counter in that workspace.
 #pragma once
 #include "common.cuh"
 
 namespace lm {
 
-constexpr int kVerifyBlock = 512;
+#ifndef LM_VERIFY_BLOCK
+#define LM_VERIFY_BLOCK 1024
+#endif
+constexpr int kVerifyBlock = LM_VERIFY_BLOCK;
 constexpr int kVerifyMaxRows = LM_MAX_DRAFT + 1;
 constexpr unsigned kBarrierSpinLimit = 1u << 22;       // ~ tens of ms: far beyond any legitimate wait
 
@@ -36,19 +41,18 @@ struct VerifyDev {
   VerifyWs* ws;
 };
 
-// Every block arrives, block 0..grid-1 wait until `target` arrivals are visible. Bounded: on time-out the error
-// word is set and the block carries on (its results are then meaningless, the host sees the error).
+// Every block arrives, then waits until `target` arrivals are visible. Bounded: on time-out the error word is set and
+// the block carries on (its results are then meaningless, the host sees the error).
 __device__ __forceinline__ void grid_barrier(VerifyWs* ws, unsigned target) {
-  __syncthreads();
+  __syncthreads();                                                        // the block's writes happen-before thread 0's release below
   if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(&ws->barrier, 1u);
-    unsigned spins = 0;
-    while (*reinterpret_cast<volatile unsigned*>(&ws->barrier) < target) {
+    unsigned seen = 0, spins = 0;
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&ws->barrier) : "memory");
+    do {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(&ws->barrier) : "memory");
+      if (seen >= target) break;
       if (++spins > kBarrierSpinLimit) { atomicExch(&ws->error, 1u); break; }
-      __nanosleep(20);
-    }
-    __threadfence();
+    } while (true);
   }
   __syncthreads();
 }
@@ -63,33 +67,90 @@ __device__ __forceinline__ float verify_load(const VerifyDev& P, int row, int i)
   return canon_zero(z);
 }
 
-__global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P) {
+// The block's view of its slice: shared-memory copies when they fit, global memory otherwise.
+struct VerifySlice {
+  const VerifyDev* P; const float* zs; const float* qs; int per, lo;
+  __device__ __forceinline__ float z(int r, int i) const { return zs ? zs[r * per + i] : verify_load(*P, r, lo + i); }
+  __device__ __forceinline__ float q(int r, int i) const { return qs ? qs[r * per + i] : __ldg(P->q + static_cast<int64_t>(r) * P->q_stride + lo + i); }
+};
+
+#ifdef LM_PROFILE_PHASES
+__device__ unsigned long long g_verify_times[8];
+#define LM_VSTAMP(i) do { if (threadIdx.x == 0 && blockIdx.x == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_verify_times[i] = _t; } } while (0)
+#else
+#define LM_VSTAMP(i) do {} while (0)
+#endif
+
+__global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, int cached) {
+  extern __shared__ __align__(16) float v_smem[];
   __shared__ uint64_t scratch[32];
   __shared__ int s_j, s_token;
-  __shared__ uint64_t s_base, s_total;
-  const int tid = threadIdx.x, G = gridDim.x, b = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, G = gridDim.x, b = blockIdx.x;
+  constexpr int kWarps = kVerifyBlock / 32;
   const int R = P.n_draft + 1, V = P.vocab;
+  const bool stochastic = P.mode == LM_VERIFY_STOCHASTIC;
   VerifyWs* ws = P.ws;
-  unsigned long long* part_w = reinterpret_cast<unsigned long long*>(ws + 1);   // [R][G]
+  unsigned long long* part_w = reinterpret_cast<unsigned long long*>(ws + 1);   // [kVerifyMaxRows][G]
   unsigned long long* part_r = part_w + static_cast<size_t>(kVerifyMaxRows) * G; // [G]
-  // this block's vocabulary slice, a multiple of 8 elements so that slices start 16-byte aligned within a row
+  // this block's vocabulary slice, a multiple of 8 elements
   const int per = ((V + G - 1) / G + 7) & ~7;
   const int lo = min(V, b * per), hi = min(V, lo + per);
   const int len = hi - lo;
+  LM_VSTAMP(0);
+  float* zs = cached ? v_smem : nullptr;
+  float* qs = (cached && stochastic) ? v_smem + R * per : nullptr;
+  VerifySlice S{&P, zs, qs, per, lo};
 
-  // ---- phase 0: row maxima (with the lowest index, which is also the greedy pick) ------------------------------
-  for (int r = 0; r < R; r++) {
-    uint64_t best = 0ull;
+  // ---- phase 0: the only HBM pass. Slices of every target row and every draft-probability row into shared memory,
+  // then row maxima with their lowest index (which is also the greedy pick).
+  // the scalars the accept test needs later are fetched now, so their latency hides behind the slice loads
+  int my_draft = -1; float my_q = 0.0f, my_u = 0.0f;
+  if (stochastic && tid < P.n_draft) {
+    my_draft = P.drafts[tid];
+    my_u = P.u_accept[tid];
+    if (my_draft >= 0 && my_draft < V) my_q = __ldg(P.q + static_cast<int64_t>(tid) * P.q_stride + my_draft);
+  }
+  const float c2 = stochastic ? exp2_scale(P.temperature) : 0.0f;
+  if (cached) {
+    // row by row, up to eight rows' loads in flight per thread; rows R.. are the draft-probability rows
+    const int n_rows = R + (stochastic ? P.n_draft : 0);
     for (int i = tid; i < len; i += kVerifyBlock) {
-      const uint64_t p = pack_best(verify_load(P, r, lo + i), static_cast<uint32_t>(lo + i));
+      for (int r0 = 0; r0 < n_rows; r0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          const int r = r0 + k;
+          if (r < R) v[k] = verify_load(P, r, lo + i);
+          else if (r < n_rows) v[k] = __ldg(P.q + static_cast<int64_t>(r - R) * P.q_stride + lo + i);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          const int r = r0 + k;
+          if (r < R) zs[r * per + i] = v[k];
+          else if (r < n_rows) qs[(r - R) * per + i] = v[k];
+        }
+      }
+    }
+    __syncthreads();
+  }
+  LM_VSTAMP(1);
+  // every row is shared by `split` warps; their partial results meet in the workspace through atomics
+  const int split = max(1, kWarps / R);
+  for (int item = warp; item < R * split; item += kWarps) {
+    const int r = item / split, part = item - r * split;
+    uint64_t best = 0ull;
+    for (int i = part * 32 + lane; i < len; i += 32 * split) {
+      const uint64_t p = pack_best(S.z(r, i), static_cast<uint32_t>(lo + i));
       best = p > best ? p : best;
     }
-    best = block_max_u64(best, scratch);
-    if (tid == 0 && best) atomicMax(&ws->row_best[r], static_cast<unsigned long long>(best));
+    best = warp_max_u64(best);
+    if (lane == 0 && best) atomicMax(&ws->row_best[r], static_cast<unsigned long long>(best));
   }
+  LM_VSTAMP(2);
   grid_barrier(ws, 1u * G);
+  LM_VSTAMP(3);
 
-  if (P.mode == LM_VERIFY_GREEDY) {
+  if (!stochastic) {
     if (b == 0 && tid == 0) {
       int acc = 0;
       while (acc < P.n_draft && static_cast<int>(best_index(ws_load(&ws->row_best[acc]))) == P.drafts[acc]) acc++;
@@ -110,64 +171,70 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P) {
     return;
   }
 
-  // ---- phase 1: fixed-point mass of every row's kept set; the drafts' own weights -------------------------------
-  const float c2 = exp2_scale(P.temperature);
-  for (int r = 0; r < R; r++) {
+  // ---- phase 1: fixed-point mass of every row's kept set; the drafts' own weights -----------------------------------
+  if (tid < R) part_w[static_cast<size_t>(tid) * G + b] = 0ull;
+  __syncthreads();
+  for (int item = warp; item < R * split; item += kWarps) {
+    const int r = item / split, part = item - r * split;
     const float vmax = best_value(ws_load(&ws->row_best[r]));
     const float tau = P.tau ? P.tau[r] : -INFINITY;
     uint64_t w = 0ull;
-    for (int i = tid; i < len; i += kVerifyBlock) {
-      const float z = verify_load(P, r, lo + i);
+    for (int i = part * 32 + lane; i < len; i += 32 * split) {
+      const float z = S.z(r, i);
       if (z >= tau) w += weight_q40(z, vmax, c2);
     }
-    w = block_sum_u64(w, scratch);
-    if (tid == 0) {
-      part_w[static_cast<size_t>(r) * G + b] = w;
-      if (w) atomicAdd(&ws->row_mass[r], static_cast<unsigned long long>(w));
-      if (r < P.n_draft) {
+    w = warp_sum_u64(w);
+    if (lane == 0) {
+      if (w) { atomicAdd(&part_w[static_cast<size_t>(r) * G + b], static_cast<unsigned long long>(w)); atomicAdd(&ws->row_mass[r], static_cast<unsigned long long>(w)); }
+      if (part == 0 && r < P.n_draft) {
         const int d = P.drafts[r];
         if (d >= lo && d < hi) {
-          const float z = verify_load(P, r, d);
+          const float z = S.z(r, d - lo);
           ws->draft_w[r] = (z >= tau) ? weight_q40(z, vmax, c2) : 0ull;
         }
       }
     }
   }
+  LM_VSTAMP(4);
   grid_barrier(ws, 2u * G);
+  LM_VSTAMP(5);
 
   // ---- phase 2: accept tests (every block, identically), then this slice's share of the residual mass -----------
-  if (tid == 0) {
-    int j = P.n_draft;
-    for (int r = P.n_draft - 1; r >= 0; r--) {
-      const int d = P.drafts[r];
+  if (tid < 32) {
+    bool reject = false;
+    if (tid < P.n_draft) {
+      const int r = tid, d = my_draft;
       const uint64_t k = ws_load(&ws->row_mass[r]);
       const float pd = (d >= 0 && d < V && k > 0ull) ? prob_q40(ws_load(&ws->draft_w[r]), k) : 0.0f;
-      const float qd = (d >= 0 && d < V) ? __ldg(P.q + static_cast<int64_t>(r) * P.q_stride + d) : 0.0f;
-      if (__fmul_rn(P.u_accept[r], qd) >= pd) j = r;
+      reject = __fmul_rn(my_u, my_q) >= pd;
       if (b == 0 && P.out_p_draft) P.out_p_draft[r] = pd;
     }
-    s_j = j;
+    const uint32_t rejects = __ballot_sync(kFull, reject);
+    if (tid == 0) s_j = rejects ? (__ffs(rejects) - 1) : P.n_draft;
   }
   __syncthreads();
   const int j = s_j;
   const float vmax_j = best_value(ws_load(&ws->row_best[j]));
   const float tau_j = P.tau ? P.tau[j] : -INFINITY;
   const uint64_t mass_j = ws_load(&ws->row_mass[j]);
-  const float* qj = (j < P.n_draft) ? P.q + static_cast<int64_t>(j) * P.q_stride : nullptr;
+  const bool has_q = j < P.n_draft;
+  // residual weight of element i of this slice (0 when not kept or not positive)
+  auto residual = [&](int i) -> uint64_t {
+    const float z = S.z(j, i);
+    if (!(z >= tau_j)) return 0ull;
+    const float p = prob_q40(weight_q40(z, vmax_j, c2), mass_j);
+    const float res = has_q ? __fsub_rn(p, S.q(j, i)) : p;
+    return res > 0.0f ? residual_q40(res) : 0ull;
+  };
   {
     uint64_t w = 0ull;
-    if (mass_j > 0ull) for (int i = tid; i < len; i += kVerifyBlock) {
-      const float z = verify_load(P, j, lo + i);
-      if (z >= tau_j) {
-        const float p = prob_q40(weight_q40(z, vmax_j, c2), mass_j);
-        const float res = qj ? __fsub_rn(p, __ldg(qj + lo + i)) : p;
-        if (res > 0.0f) w += residual_q40(res);
-      }
-    }
+    if (mass_j > 0ull) for (int i = tid; i < len; i += kVerifyBlock) w += residual(i);
     w = block_sum_u64(w, scratch);
     if (tid == 0) part_r[b] = w;
   }
+  LM_VSTAMP(6);
   grid_barrier(ws, 3u * G);
+  LM_VSTAMP(7);
 
   // ---- phase 3: locate the draw; the block whose slice holds it writes the outputs -------------------------------
   {
@@ -185,7 +252,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P) {
     const uint64_t total = use_res ? tot_r : mass_j;
     const uint64_t mine = use_res ? ws_load(&part_r[b]) : ws_load(&part_w[static_cast<size_t>(j) * G + b]);
     const uint64_t pre = use_res ? pre_r : pre_w;
-    if (tid == 0) { s_token = -2; s_total = total; }
+    if (tid == 0) s_token = -2;
     __syncthreads();
     if (total > 0ull) {
       const uint64_t target = cdf_target(P.u_final[0], total);
@@ -195,15 +262,8 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P) {
           const int i = i0 + tid;
           uint64_t w = 0ull;
           if (i < len) {
-            const float z = verify_load(P, j, lo + i);
-            if (z >= tau_j) {
-              const uint64_t wq = weight_q40(z, vmax_j, c2);
-              if (use_res) {
-                const float p = prob_q40(wq, mass_j);
-                const float res = qj ? __fsub_rn(p, __ldg(qj + lo + i)) : p;
-                if (res > 0.0f) w = residual_q40(res);
-              } else w = wq;
-            }
+            if (use_res) w = residual(i);
+            else { const float z = S.z(j, i); if (z >= tau_j) w = weight_q40(z, vmax_j, c2); }
           }
           uint64_t sweep = 0ull;
           const uint64_t excl = block_exclusive_scan_u64(w, scratch, &sweep);
