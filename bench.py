@@ -305,10 +305,48 @@ def main() -> None:
             out["cpu_baseline"] = {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port",
                                    "sample": f"first {n_cpu} rows of the workload, C restatement of monolith/nn/sampling_ref.py (oracle/lm_oracle.c), {cores} threads",
                                    "tokens_equal_gpu": same}
+    if world > 1 and not args.skip_extras:
+        out["vocab_parallel"] = bench_vocab_parallel(torch, dist, lm, dev, rank, world, args.warmup)
     if rank == 0:
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_vocab_parallel(torch, dist, lm, dev, rank, world, warmup):
+    """The vocab-parallel configuration (64 rows x 262144 BF16 logits N(0, 2^2), top_k 50, top_p 0.9, temperature 0.8), the
+    vocabulary split over the ranks: per-step time of local kernel + NCCL all-gather + merge kernel (CUDA events, max over
+    ranks), and whether every rank's tokens equal rank 0's single-GPU result on the whole rows."""
+    from lithos_metal_b200 import parallel
+    rows, vocab = 64, 262144
+    g = torch.Generator(device=dev)
+    g.manual_seed(SEED)                                                    # every rank generates the same full rows, keeps its shard
+    full = (torch.randn(rows, vocab, generator=g, device=dev) * 2.0).to(torch.bfloat16)
+    u = torch.rand(rows, generator=g, device=dev)
+    p = lm.SamplingParams(temperature=0.8, top_k=50, top_p=0.9, draw="inverse_cdf")
+    sampler = parallel.VocabParallelSampler(p, vocab)
+    lo, width = parallel.shard_vocab(vocab, rank, world)
+    shard = full[:, lo:lo + width].contiguous()
+    for _ in range(max(3, warmup)):
+        r = sampler.sample(shard, uniforms=u)
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    n = 20
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(n):
+        r = sampler.sample(shard, uniforms=u)
+    b.record()
+    torch.cuda.synchronize(dev)
+    t = torch.tensor([a.elapsed_time(b) / n], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    one = lm.sample(full, p, uniforms=u).tokens
+    same = torch.tensor([int(torch.equal(one, r.tokens))], device=dev)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    ms = float(t.item())
+    return {"workload": "64 rows x 262144 bf16, vocab split over the ranks, top_k 50, top_p 0.9, T 0.8", "us_per_step": 1e3 * ms,
+            "rows_per_s": rows / (ms * 1e-3), "allgather_bytes_per_rank": int(rows * sampler.backend.record_bytes(sampler.cap)),
+            "tokens_equal_single_gpu_on_every_rank": bool(same.item())}
 
 
 def bench_verify(torch, lm, dev):

@@ -197,6 +197,95 @@ typedef struct lm_verify_args {
 
 LM_API int lm_verify(const lm_verify_args* args);
 
+/*
+ * Vocab-parallel sampling: every row's vocabulary is split into `shards` contiguous pieces, one per GPU.
+ *
+ * No counterpart in lithos-metal (which is single-device). The result is defined as what lm_sample returns for the
+ * whole row, bit for bit. Protocol, per step:
+ *   1. every GPU calls lm_vocab_local on its shard: per row it writes one record (lm_vocab_record_bytes(cap) bytes) with
+ *      the shard's maximum, its FP64 softmass and every logit at or above the shard's own top_k-th largest value
+ *      (ties kept) with global indices;
+ *   2. the caller all-gathers the records (the only exchange: rows * record bytes per GPU; NCCL in the Python layer)
+ *      into [shards][rows] records, shard order = vocabulary order;
+ *   3. every GPU calls lm_vocab_merge on the gathered records and gets the same tokens.
+ * Requirements: top_k >= 1 on every row (the kept set must lie inside the top-k candidates), cap =
+ * lm_vocab_candidate_cap(largest top_k), shards * cap <= LM_VOCAB_MAX_CANDIDATES, no penalties. A row whose ties overflow
+ * a record reports LM_STATUS_OVERFLOW and token -1.
+ */
+#define LM_VOCAB_MAX_CANDIDATES 1024
+#define LM_STATUS_OVERFLOW 32u
+
+typedef struct lm_vocab_args {
+  uint32_t struct_size;
+  int32_t dtype;
+  const void* logits;          /* local step: [rows, row_stride], this GPU's shard */
+  int64_t rows;
+  int64_t vocab_local;         /* local step: width of the shard */
+  int64_t row_stride;
+  int64_t shard_start;         /* local step: global index of the shard's first logit */
+  int32_t shards;              /* merge step */
+  int32_t cap;                 /* candidates per row per shard */
+  const float* temperature;  float temperature_s;
+  const int32_t* top_k;      int32_t top_k_s;
+  const float* top_p;        float top_p_s;      /* merge step */
+  const float* min_p;        float min_p_s;      /* merge step */
+  uint32_t flags;              /* LM_FLAG_*, merge step */
+  int32_t draw;                /* LM_DRAW_*, merge step */
+  const float* uniforms;       /* [rows], merge step */
+  uint64_t seed; uint32_t step; int64_t row_offset;
+  void* records;               /* local step: out [rows] records; merge step: in [shards][rows] records */
+  int32_t* out_tokens;         /* merge step: [rows] */
+  float* out_tau;              /* merge step, optional */
+  uint32_t* out_status;        /* merge step, optional */
+  void* stream;
+} lm_vocab_args;
+
+LM_API int lm_vocab_local(const lm_vocab_args* args);
+LM_API int lm_vocab_merge(const lm_vocab_args* args);
+LM_API size_t lm_vocab_record_bytes(int32_t cap);
+LM_API int32_t lm_vocab_candidate_cap(int32_t top_k);
+
+/*
+ * The scalar step-closing kernels, on the reference's StepState buffer (monolith/core/step_state.py:38-62: 4-byte fields in the
+ * reference's order, for the given t_max / gamma_max; size = lm_step_state_bytes). One thread each, stream-ordered: the
+ * host never reads a token to keep the decode loop going.
+ *
+ * lm_accept_scan stands in for accept_scan (kernels/common/spec_ops.metal:148-195; AcceptParams, monolith/kernels.py:831-835):
+ *   greedy prefix match of token[] against pending_tokens, commit of the accepted drafts + bonus token to the token ring
+ *   as (sequence << 32) | token, stop at the first stop token / stop_at / context capacity, log entry
+ *   (committed << 16) | (L << 8) | accepted, state advance. Errors are device-side status: error 1 = ring overflow,
+ *   2 = context capacity reached, with done = 1.
+ * lm_verify_select stands in for verify_select (spec_ops.metal:108-146; SelectParams, kernels.py:814-825): stages drafts and
+ *   confidences, picks the verify length L (mode 0 confident prefix, 1 cost-aware argmax_l (1 + sum a_i)/cost[l], 2 fixed),
+ *   clamps it to t_max - 1 and the context capacity, writes pending_tokens = [anchor, d_0 .. d_{L-1}], t_this_step = 1 + L.
+ * lm_advance stands in for advance (kernels/common/advance.metal:15-37; AdvanceParams, kernels.py:748-752): publishes the
+ *   last row's token, checks ring / stop / context, advances the state.
+ * Stop tokens: `eos` (a single id, -1 for none) and/or a device list of `n_eos` ids (the reference compiles a list into the
+ * kernel, kernels.py:729-741).
+ */
+typedef struct lm_step_args {
+  uint32_t struct_size;
+  int32_t t_max, gamma_max;    /* the StepState layout */
+  void* step_state;            /* device, lm_step_state_bytes(t_max, gamma_max) bytes */
+  const int32_t* tokens;       /* accept_scan / advance: the sampler's token[] */
+  uint64_t* ring;              /* accept_scan / advance: token ring, ring_cap slots */
+  uint32_t ring_cap;
+  int32_t eos; const int32_t* eos_list; int32_t n_eos;
+  uint32_t* log; uint32_t log_cap;     /* accept_scan: optional accept log */
+  uint32_t ctx_cap;            /* 0 = unbounded */
+  int32_t lm;                  /* an LM drafter (changes n_inject / drafter_ctx_len bookkeeping) */
+  /* verify_select only */
+  const int32_t* drafts; const float* conf; uint32_t gamma; float threshold; uint32_t mode; float cost[16];
+  float* conf_log; uint32_t conf_log_cap;
+  uint32_t t_limit;            /* rows the step program holds (SelectParams.t_max); 0 = the layout's t_max */
+  void* stream;
+} lm_step_args;
+
+LM_API int lm_accept_scan(const lm_step_args* args);
+LM_API int lm_verify_select(const lm_step_args* args);
+LM_API int lm_advance(const lm_step_args* args);
+LM_API size_t lm_step_state_bytes(int32_t t_max, int32_t gamma_max);
+
 /* Scratch sizes (host calls, no CUDA work). Stand in for sample_workspace (monolith/kernels.py:777-779). */
 LM_API size_t lm_workspace_bytes(int64_t rows, int64_t vocab);
 LM_API size_t lm_verify_workspace_bytes(int32_t n_draft, int64_t vocab);

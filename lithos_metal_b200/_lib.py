@@ -12,7 +12,8 @@ DTYPE_BF16, DTYPE_F32 = 0, 1
 DRAW_GUMBEL, DRAW_INVERSE_CDF = 0, 1
 FLAG_TOPP_IN_TOPK = 1
 VERIFY_GREEDY, VERIFY_STOCHASTIC = 0, 1
-STATUS_GENERIC_PATH, STATUS_NAN, STATUS_NEAR_TIE, STATUS_TOPP_EDGE = 1, 2, 4, 8
+STATUS_GENERIC_PATH, STATUS_NAN, STATUS_NEAR_TIE, STATUS_TOPP_EDGE, STATUS_OVERFLOW = 1, 2, 4, 8, 32
+VOCAB_MAX_CANDIDATES = 1024
 MAX_DRAFT = 15
 MAX_VOCAB = 1048576
 ARGMAX_STATIC_MAX_ROWS = 4096
@@ -44,7 +45,28 @@ class VerifyArgs(C.Structure):
     ]
 
 
-EXPORTS = ["lm_sample", "lm_argmax", "lm_argmax_static", "lm_verify", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
+class StepArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("t_max", C.c_int32), ("gamma_max", C.c_int32), ("step_state", C.c_void_p), ("tokens", C.c_void_p),
+        ("ring", C.c_void_p), ("ring_cap", C.c_uint32), ("eos", C.c_int32), ("eos_list", C.c_void_p), ("n_eos", C.c_int32),
+        ("log", C.c_void_p), ("log_cap", C.c_uint32), ("ctx_cap", C.c_uint32), ("lm", C.c_int32),
+        ("drafts", C.c_void_p), ("conf", C.c_void_p), ("gamma", C.c_uint32), ("threshold", C.c_float), ("mode", C.c_uint32), ("cost", C.c_float * 16),
+        ("conf_log", C.c_void_p), ("conf_log_cap", C.c_uint32), ("t_limit", C.c_uint32), ("stream", C.c_void_p),
+    ]
+
+
+class VocabArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("dtype", C.c_int32), ("logits", C.c_void_p), ("rows", C.c_int64), ("vocab_local", C.c_int64),
+        ("row_stride", C.c_int64), ("shard_start", C.c_int64), ("shards", C.c_int32), ("cap", C.c_int32),
+        ("temperature", C.c_void_p), ("temperature_s", C.c_float), ("top_k", C.c_void_p), ("top_k_s", C.c_int32),
+        ("top_p", C.c_void_p), ("top_p_s", C.c_float), ("min_p", C.c_void_p), ("min_p_s", C.c_float),
+        ("flags", C.c_uint32), ("draw", C.c_int32), ("uniforms", C.c_void_p), ("seed", C.c_uint64), ("step", C.c_uint32), ("row_offset", C.c_int64),
+        ("records", C.c_void_p), ("out_tokens", C.c_void_p), ("out_tau", C.c_void_p), ("out_status", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
+EXPORTS = ["lm_accept_scan", "lm_verify_select", "lm_advance", "lm_step_state_bytes", "lm_sample", "lm_argmax", "lm_argmax_static", "lm_vocab_local", "lm_vocab_merge", "lm_vocab_record_bytes", "lm_vocab_candidate_cap", "lm_verify", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
            "lm_error_string", "lm_last_cuda_error", "lm_device_sm_count"]
 
 _lib = None
@@ -70,6 +92,16 @@ def lib():
         L.lm_argmax.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
         L.lm_argmax_static.restype = C.c_int
         L.lm_argmax_static.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
+        L.lm_vocab_local.restype = L.lm_vocab_merge.restype = C.c_int
+        L.lm_vocab_local.argtypes = L.lm_vocab_merge.argtypes = [C.POINTER(VocabArgs)]
+        L.lm_vocab_record_bytes.restype = C.c_size_t
+        L.lm_vocab_record_bytes.argtypes = [C.c_int32]
+        L.lm_vocab_candidate_cap.restype = C.c_int32
+        L.lm_vocab_candidate_cap.argtypes = [C.c_int32]
+        for fn in (L.lm_accept_scan, L.lm_verify_select, L.lm_advance):
+            fn.restype, fn.argtypes = C.c_int, [C.POINTER(StepArgs)]
+        L.lm_step_state_bytes.restype = C.c_size_t
+        L.lm_step_state_bytes.argtypes = [C.c_int32, C.c_int32]
         L.lm_workspace_bytes.restype = C.c_size_t
         L.lm_workspace_bytes.argtypes = [C.c_int64, C.c_int64]
         L.lm_verify_workspace_bytes.restype = C.c_size_t

@@ -11,6 +11,8 @@
 #include "sample_generic.cuh"
 #include "sample_fast.cuh"
 #include "verify.cuh"
+#include "vocab_parallel.cuh"
+#include "spec_ops.cuh"
 
 namespace lm {
 
@@ -275,6 +277,121 @@ int lm_sample(const lm_sample_args* a) {
   const long long cap = fast ? sms : 8LL * sms;
   const int grid = static_cast<int>(a->rows < cap ? a->rows : cap);
   sample_generic_kernel<<<grid, kBlock, smem, st>>>(P);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+size_t lm_vocab_record_bytes(int32_t cap) { return cap > 0 ? static_cast<size_t>(kVpHeader) + 8u * static_cast<size_t>(cap) : 0; }
+
+int32_t lm_vocab_candidate_cap(int32_t top_k) { return top_k > 0 ? (top_k + 64 + 7) / 8 * 8 : 0; }
+
+int lm_vocab_local(const lm_vocab_args* a) {
+  if (!a || a->struct_size != sizeof(lm_vocab_args)) return LM_E_INVALID;
+  if (a->rows < 0 || a->vocab_local < 1 || (a->dtype != LM_DTYPE_BF16 && a->dtype != LM_DTYPE_F32)) return LM_E_INVALID;
+  if (a->rows == 0) return LM_OK;
+  if (!a->logits || !a->records || a->row_stride < a->vocab_local || a->cap < 1 || a->shard_start < 0) return LM_E_INVALID;
+  if (a->temperature == nullptr && !(a->temperature_s > 0.0f)) return LM_E_INVALID;
+  if (a->top_k == nullptr && a->top_k_s < 1) return LM_E_INVALID;
+  if (a->vocab_local > LM_MAX_VOCAB || a->rows > 0x7FFFFFFF || a->shard_start + a->vocab_local > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
+  VpLocalDev P;
+  P.logits = a->logits; P.dtype = a->dtype; P.rows = static_cast<int>(a->rows); P.vocab_local = static_cast<int>(a->vocab_local);
+  P.row_stride = a->row_stride; P.shard_start = static_cast<int>(a->shard_start);
+  P.temperature = a->temperature; P.temperature_s = a->temperature_s; P.top_k = a->top_k; P.top_k_s = a->top_k_s;
+  P.cap = a->cap; P.records = static_cast<unsigned char*>(a->records); P.record_bytes = static_cast<int64_t>(lm_vocab_record_bytes(a->cap));
+  int sms = 0;
+  const int rc = sm_count(&sms);
+  if (rc != LM_OK) return rc;
+  const size_t smem = sizeof(GenericSmem) + 16;
+  static thread_local bool attr = false;
+  if (!attr) {
+    const cudaError_t e = cudaFuncSetAttribute(vocab_local_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return cuda_fail(e);
+    attr = true;
+  }
+  const int grid = static_cast<int>(a->rows < 2LL * sms ? a->rows : 2LL * sms);
+  vocab_local_kernel<<<grid, kBlock, smem, static_cast<cudaStream_t>(a->stream)>>>(P);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+int lm_vocab_merge(const lm_vocab_args* a) {
+  if (!a || a->struct_size != sizeof(lm_vocab_args)) return LM_E_INVALID;
+  if (a->rows < 0 || a->shards < 1 || a->cap < 1) return LM_E_INVALID;
+  if (a->draw != LM_DRAW_GUMBEL && a->draw != LM_DRAW_INVERSE_CDF) return LM_E_INVALID;
+  if (a->rows == 0) return LM_OK;
+  if (!a->records || !a->out_tokens) return LM_E_INVALID;
+  if (a->temperature == nullptr && !(a->temperature_s > 0.0f)) return LM_E_INVALID;
+  if (a->top_k == nullptr && a->top_k_s < 1) return LM_E_INVALID;
+  if (a->draw == LM_DRAW_INVERSE_CDF && a->uniforms == nullptr) return LM_E_INVALID;
+  if (static_cast<int64_t>(a->shards) * a->cap > LM_VOCAB_MAX_CANDIDATES || a->rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
+  VpMergeDev P;
+  P.records = static_cast<const unsigned char*>(a->records); P.shards = a->shards; P.rows = static_cast<int>(a->rows); P.cap = a->cap;
+  P.record_bytes = static_cast<int64_t>(lm_vocab_record_bytes(a->cap));
+  P.temperature = a->temperature; P.temperature_s = a->temperature_s; P.top_k = a->top_k; P.top_k_s = a->top_k_s;
+  P.top_p = a->top_p; P.top_p_s = a->top_p_s; P.min_p = a->min_p; P.min_p_s = a->min_p_s;
+  P.flags = a->flags; P.draw = a->draw; P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
+  P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_status = a->out_status;
+  int sms = 0;
+  const int rc = sm_count(&sms);
+  if (rc != LM_OK) return rc;
+  const int grid = static_cast<int>(a->rows < 4LL * sms ? a->rows : 4LL * sms);
+  vocab_merge_kernel<<<grid, kVpMaxCandidates, 0, static_cast<cudaStream_t>(a->stream)>>>(P);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+size_t lm_step_state_bytes(int32_t t_max, int32_t gamma_max) {
+  if (t_max < 1 || gamma_max < 0 || t_max < gamma_max + 1) return 0;
+  const size_t g = gamma_max > 1 ? gamma_max : 1;
+  const size_t words = 4 + static_cast<size_t>(t_max) + 4 + 2 * g + 12;
+  return (words * 4 + 15) / 16 * 16;
+}
+
+static int step_args_ok(const lm_step_args* a) {
+  if (!a || a->struct_size != sizeof(lm_step_args)) return LM_E_INVALID;
+  if (lm_step_state_bytes(a->t_max, a->gamma_max) == 0 || !a->step_state) return LM_E_INVALID;
+  if (a->n_eos < 0 || (a->n_eos > 0 && !a->eos_list)) return LM_E_INVALID;
+  return LM_OK;
+}
+
+int lm_accept_scan(const lm_step_args* a) {
+  int rc = step_args_ok(a);
+  if (rc != LM_OK) return rc;
+  if (!a->tokens || !a->ring || a->ring_cap == 0 || (a->log_cap && !a->log)) return LM_E_INVALID;
+  AcceptDev p{a->tokens, static_cast<uint32_t*>(a->step_state), a->t_max, a->gamma_max > 1 ? a->gamma_max : 1,
+              reinterpret_cast<unsigned long long*>(a->ring), a->ring_cap, EosSet{a->eos, a->eos_list, a->n_eos}, a->log, a->log_cap, a->ctx_cap, a->lm};
+  accept_scan_kernel<<<1, 32, 0, static_cast<cudaStream_t>(a->stream)>>>(p);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+int lm_verify_select(const lm_step_args* a) {
+  int rc = step_args_ok(a);
+  if (rc != LM_OK) return rc;
+  if (!a->drafts || !a->conf || a->gamma > 16u || static_cast<int>(a->gamma) > (a->gamma_max > 1 ? a->gamma_max : 1) || a->mode > 2u) return LM_E_INVALID;
+  if (a->conf_log_cap && !a->conf_log) return LM_E_INVALID;
+  if (a->mode == 1u) {                                                     // the cost rule: positive costs relative to cost[0] = 1 (kernels.py:820-822)
+    if (std::fabs(a->cost[0] - 1.0f) > 1e-6f) return LM_E_INVALID;
+    for (int i = 0; i < 16; i++) if (!(a->cost[i] > 0.0f)) return LM_E_INVALID;
+  }
+  SelectDev p;
+  if (a->t_limit > static_cast<uint32_t>(a->t_max)) return LM_E_INVALID;
+  p.drafts = a->drafts; p.conf = a->conf; p.state = static_cast<uint32_t*>(a->step_state); p.t_max = a->t_max; p.t_limit = a->t_limit ? a->t_limit : static_cast<uint32_t>(a->t_max); p.g = a->gamma_max > 1 ? a->gamma_max : 1;
+  p.gamma = a->gamma; p.threshold = a->threshold; p.mode = a->mode;
+  for (int i = 0; i < 16; i++) p.cost[i] = a->cost[i];
+  p.conf_log = a->conf_log; p.log_cap = a->conf_log_cap; p.ctx_cap = a->ctx_cap; p.lm = a->lm;
+  verify_select_kernel<<<1, 32, 0, static_cast<cudaStream_t>(a->stream)>>>(p);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+int lm_advance(const lm_step_args* a) {
+  int rc = step_args_ok(a);
+  if (rc != LM_OK) return rc;
+  if (!a->tokens || !a->ring || a->ring_cap == 0) return LM_E_INVALID;
+  AdvanceDev p{a->tokens, static_cast<uint32_t*>(a->step_state), a->t_max, a->gamma_max > 1 ? a->gamma_max : 1,
+               reinterpret_cast<unsigned long long*>(a->ring), a->ring_cap, EosSet{a->eos, a->eos_list, a->n_eos}, a->ctx_cap};
+  advance_kernel<<<1, 32, 0, static_cast<cudaStream_t>(a->stream)>>>(p);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }

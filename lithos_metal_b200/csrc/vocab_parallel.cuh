@@ -1,0 +1,266 @@
+// Vocab-parallel sampling: the vocabulary of every row is split into contiguous shards, one per GPU. No counterpart
+// in the reference (which is single-device); the result is defined as the single-GPU sampler's result on the whole
+// row, bit for bit.
+//
+//   vocab_local_kernel  (each GPU, its shard): per row the shard's maximum, its FP64 softmass relative to that
+//                       maximum, and every logit at or above the shard's own k-th largest value (ties kept), with
+//                       global indices -> one fixed-size record per row;
+//   [one all-gather of the records, done by the host layer over NCCL]
+//   vocab_merge_kernel  (every GPU, identically): sorts the gathered candidates, rebuilds the global maximum and
+//                       mass, finds tau_k / tau_p / tau_m exactly as the single-GPU walk does, and draws.
+//
+// Every logit at or above the global k-th largest value is a candidate of its shard (a shard holds fewer than k logits
+// above that value, so its own k-th largest lies at or below it), which is why the merge sees the complete top-k set.
+#pragma once
+#include "common.cuh"
+#include "sample_generic.cuh"
+
+namespace lm {
+
+constexpr int kVpHeader = 32;          // float vmax, float pad, double mass, int32 n, uint32 status, 8 bytes pad
+constexpr int kVpMaxCandidates = 1024; // all shards together, per row
+constexpr uint32_t kStatusOverflow = 32u;
+
+struct VpLocalDev {
+  const void* logits; int dtype; int rows; int vocab_local; int64_t row_stride; int shard_start;
+  const float* temperature; float temperature_s; const int32_t* top_k; int32_t top_k_s;
+  int cap; unsigned char* records; int64_t record_bytes;
+};
+
+__global__ void __launch_bounds__(kBlock, 1) vocab_local_kernel(VpLocalDev P) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  GenericSmem& s = *reinterpret_cast<GenericSmem*>(smem_raw);
+  __shared__ uint32_t s_n;
+  const int tid = threadIdx.x;
+  for (int row = blockIdx.x; row < P.rows; row += gridDim.x) {
+    const int V = P.vocab_local;
+    const float T = P.temperature ? P.temperature[row] : P.temperature_s;
+    int top_k = P.top_k ? P.top_k[row] : P.top_k_s;
+    unsigned char* rec = P.records + static_cast<int64_t>(row) * P.record_bytes;
+    float* out_val = reinterpret_cast<float*>(rec + kVpHeader);
+    int32_t* out_idx = reinterpret_cast<int32_t*>(rec + kVpHeader + 4 * static_cast<size_t>(P.cap));
+    RowView rv;
+    rv.dtype = P.dtype; rv.vocab = V; rv.rho = 1.0f; rv.pi = 0.0f; rv.pen = nullptr;
+    rv.row = static_cast<const char*>(P.logits) + static_cast<size_t>(row) * static_cast<size_t>(P.row_stride) * (P.dtype == LM_DTYPE_BF16 ? 2 : 4);
+    rv.aligned = (reinterpret_cast<uintptr_t>(rv.row) & 15u) == 0;
+    const int n_chunks = (V + kChunk - 1) / kChunk;
+    if (tid == 0) s_n = 0u;
+    // the shard's maximum
+    uint64_t best = 0ull;
+    for (int c = tid; c < n_chunks; c += kBlock) {
+      float z[kChunk];
+      const int n = load_chunk(rv, c, z);
+#pragma unroll
+      for (int e = 0; e < kChunk; e++) if (e < n) { const uint64_t p = pack_best(z[e], static_cast<uint32_t>(c * kChunk + e)); best = p > best ? p : best; }
+    }
+    best = block_max_u64(best, s.scratch);
+    const float vmax = best_value(best);
+    // its FP64 softmass relative to that maximum
+    const double inv_t = 1.0 / static_cast<double>(T);
+    double m = 0.0;
+    for (int c = tid; c < n_chunks; c += kBlock) {
+      float z[kChunk];
+      const int n = load_chunk(rv, c, z);
+#pragma unroll
+      for (int e = 0; e < kChunk; e++) if (e < n) m += softmass(z[e], vmax, inv_t);
+    }
+    const double mass = block_sum_f64(m, s.scratch);
+    // its k-th largest value: 4 x 8-bit radix select on the monotone key, ties kept
+    if (top_k > V) top_k = V;
+    if (top_k < 1) top_k = 1;
+    if (tid == 0) { s.sel_base_c = 0; s.sel_base_m = 0.0; }
+    __syncthreads();
+    uint32_t prefix = 0u;
+    for (int level = 0; level < 4; level++) {
+      hist_pass<false>(rv, level, prefix, vmax, inv_t, s);
+      prefix |= static_cast<uint32_t>(select_bin<false>(s.cnt, nullptr, static_cast<uint32_t>(top_k), 0.0, s)) << (24 - 8 * level);
+    }
+    const float tau_local = fkey_inv(prefix);
+    // every logit at or above it, with its global index
+    for (int c = tid; c < n_chunks; c += kBlock) {
+      float z[kChunk];
+      const int n = load_chunk(rv, c, z);
+#pragma unroll
+      for (int e = 0; e < kChunk; e++) if (e < n && z[e] >= tau_local) {
+        const uint32_t slot = atomicAdd(&s_n, 1u);
+        if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = z[e]; out_idx[slot] = P.shard_start + c * kChunk + e; }
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const uint32_t n = s_n;
+      *reinterpret_cast<float*>(rec) = vmax;
+      *reinterpret_cast<float*>(rec + 4) = 0.0f;
+      *reinterpret_cast<double*>(rec + 8) = mass;
+      *reinterpret_cast<int32_t*>(rec + 16) = static_cast<int32_t>(n < static_cast<uint32_t>(P.cap) ? n : static_cast<uint32_t>(P.cap));
+      *reinterpret_cast<uint32_t*>(rec + 20) = (n > static_cast<uint32_t>(P.cap) ? kStatusOverflow : 0u) | ((vmax != vmax) ? LM_STATUS_NAN : 0u);
+    }
+    __syncthreads();
+  }
+}
+
+struct VpMergeDev {
+  const unsigned char* records;      // [shards][rows] records, as the all-gather leaves them
+  int shards; int rows; int cap; int64_t record_bytes;
+  const float* temperature; float temperature_s; const int32_t* top_k; int32_t top_k_s;
+  const float* top_p; float top_p_s; const float* min_p; float min_p_s;
+  uint32_t flags; int draw; const float* uniforms; uint64_t seed; uint32_t step; int64_t row_offset;
+  int32_t* out_tokens; float* out_tau; uint32_t* out_status;
+};
+
+struct VpMergeSmem {
+  unsigned long long key[kVpMaxCandidates];   // (monotone value key << 32) | ~global index: descending = value desc, index asc
+  double cum[kVpMaxCandidates];
+  unsigned long long w[kVpMaxCandidates];
+  uint64_t scratch[32];
+  double warp_m[32];
+  int n_total; int hit; int token; uint32_t status;
+};
+
+__global__ void __launch_bounds__(kVpMaxCandidates, 1) vocab_merge_kernel(VpMergeDev P) {
+  __shared__ VpMergeSmem s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int row = blockIdx.x; row < P.rows; row += gridDim.x) {
+    const float T = P.temperature ? P.temperature[row] : P.temperature_s;
+    int top_k = P.top_k ? P.top_k[row] : P.top_k_s;
+    const float top_p = P.top_p ? P.top_p[row] : P.top_p_s;
+    const float min_p = P.min_p ? P.min_p[row] : P.min_p_s;
+    const double T64 = static_cast<double>(T), inv_t = 1.0 / T64;
+    // ---- gather: candidate t of the concatenated shards
+    if (tid == 0) { s.hit = kVpMaxCandidates; s.token = -1; s.status = 0u; }
+    __syncthreads();
+    unsigned long long key = 0ull;
+    {
+      int base = 0, total = 0;
+      uint32_t st = 0u;
+      for (int g = 0; g < P.shards; g++) {
+        const unsigned char* rec = P.records + (static_cast<int64_t>(g) * P.rows + row) * P.record_bytes;
+        const int n = *reinterpret_cast<const int32_t*>(rec + 16);
+        st |= *reinterpret_cast<const uint32_t*>(rec + 20);
+        if (tid >= base && tid < base + n) {
+          const float v = reinterpret_cast<const float*>(rec + kVpHeader)[tid - base];
+          const int32_t i = reinterpret_cast<const int32_t*>(rec + kVpHeader + 4 * static_cast<size_t>(P.cap))[tid - base];
+          key = (static_cast<unsigned long long>(fkey(v)) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(i));
+        }
+        base += n; total += n;
+      }
+      if (tid == 0) { s.n_total = total < kVpMaxCandidates ? total : kVpMaxCandidates; s.status = st | (total > kVpMaxCandidates ? kStatusOverflow : 0u); }
+    }
+    s.key[tid] = key;
+    __syncthreads();
+    // ---- bitonic sort, descending
+    for (int k = 2; k <= kVpMaxCandidates; k <<= 1) {
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        const int partner = tid ^ j;
+        if (partner > tid) {
+          const unsigned long long a = s.key[tid], b = s.key[partner];
+          const bool desc = (tid & k) == 0;
+          if (desc ? (a < b) : (a > b)) { s.key[tid] = b; s.key[partner] = a; }
+        }
+        __syncthreads();
+      }
+    }
+    const int N = s.n_total;
+    const uint32_t status0 = s.status;
+    if ((status0 & kStatusOverflow) || N == 0) {
+      if (tid == 0) { P.out_tokens[row] = -1; if (P.out_tau) P.out_tau[row] = -INFINITY; if (P.out_status) P.out_status[row] = status0; }
+      __syncthreads();
+      continue;
+    }
+    key = s.key[tid];
+    const bool valid = tid < N;
+    const float val = valid ? fkey_inv(static_cast<uint32_t>(key >> 32)) : -INFINITY;
+    const int idx = valid ? static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(key)) : -1;
+    // ---- global maximum and mass (shards in order)
+    float vmax = -INFINITY;
+    for (int g = 0; g < P.shards; g++) vmax = fmaxf(vmax, *reinterpret_cast<const float*>(P.records + (static_cast<int64_t>(g) * P.rows + row) * P.record_bytes));
+    double z_total = 0.0;
+    for (int g = 0; g < P.shards; g++) {
+      const unsigned char* rec = P.records + (static_cast<int64_t>(g) * P.rows + row) * P.record_bytes;
+      z_total += *reinterpret_cast<const double*>(rec + 8) * exp((static_cast<double>(*reinterpret_cast<const float*>(rec)) - static_cast<double>(vmax)) * inv_t);
+    }
+    // ---- thresholds
+    const bool has_k = top_k > 0, has_p = top_p > 0.0f && top_p < 1.0f, has_m = min_p > 0.0f;
+    double tau64 = -INFINITY; bool have_tau = false;
+    float tau_k = -INFINITY;
+    if (has_k) {
+      const int kk = (top_k < N ? top_k : N) - 1;
+      tau_k = fkey_inv(static_cast<uint32_t>(s.key[kk] >> 32));
+      tau64 = tau_k; have_tau = true;
+    }
+    if (has_p) {
+      // inclusive FP64 prefix of the softmass in sorted order
+      double m = valid ? softmass(val, vmax, inv_t) : 0.0, mi = m;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const double t = __shfl_up_sync(kFull, mi, o); if (lane >= o) mi += t; }
+      if (lane == 31) s.warp_m[warp] = mi;
+      __syncthreads();
+      double wm = 0.0;
+      for (int w = 0; w < warp; w++) wm += s.warp_m[w];
+      mi += wm;
+      s.cum[tid] = mi;
+      __syncthreads();
+      double total = z_total;
+      if ((P.flags & LM_FLAG_TOPP_IN_TOPK) && has_k) {                     // mass of the top-k set: prefix at the last candidate >= tau_k
+        int last = 0;
+        for (int t = 0; t < N; t++) if (fkey_inv(static_cast<uint32_t>(s.key[t] >> 32)) >= tau_k) last = t; else break;
+        total = s.cum[last];
+      }
+      const double target = static_cast<double>(top_p) * total;
+      const bool run_end = valid && (tid == N - 1 || (s.key[tid + 1] >> 32) != (key >> 32));
+      if (run_end && mi >= target) atomicMin(&s.hit, tid);
+      __syncthreads();
+      if (s.hit < kVpMaxCandidates) {
+        const float tau_p = fkey_inv(static_cast<uint32_t>(s.key[s.hit] >> 32));
+        if (!have_tau || static_cast<double>(tau_p) > tau64) tau64 = tau_p;
+        have_tau = true;
+      }
+    }
+    if (has_m) {
+      const double tau_m = static_cast<double>(vmax) + T64 * log(static_cast<double>(min_p));
+      if (!have_tau || tau_m > tau64) tau64 = tau_m;
+      have_tau = true;
+    }
+    const float tau = have_tau ? __double2float_rn(tau64) : -INFINITY;
+    const bool kept = valid && val >= tau;
+    uint32_t status = status0;
+    // ---- the draw
+    if (P.draw == LM_DRAW_INVERSE_CDF) {
+      const float c2 = exp2_scale(T);
+      const uint64_t w = kept ? weight_q40(val, vmax, c2) : 0ull;
+      s.w[tid] = w;
+      __syncthreads();
+      const uint64_t total = block_sum_u64(w, s.scratch);
+      if (total > 0ull && w) {
+        const uint64_t target = cdf_target(P.uniforms ? P.uniforms[row] : 0.0f, total);
+        uint64_t before = 0ull;                                            // weight of the kept candidates with a smaller index
+        for (int t = 0; t < N; t++) {
+          const uint64_t wt = s.w[t];
+          if (wt && static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(s.key[t])) < idx) before += wt;
+        }
+        if (before <= target && target < before + w) s.token = idx;
+      }
+    } else {
+      const float inv_t32 = __double2float_rn(1.0 / T64);
+      uint64_t mine = 0ull; float kf = -INFINITY;
+      if (kept) {
+        kf = __fadd_rn(__fmul_rn(val, inv_t32), gumbel(P.seed, P.step, static_cast<uint32_t>(P.row_offset + row), static_cast<uint32_t>(idx)));
+        mine = pack_best(kf, static_cast<uint32_t>(idx));
+      }
+      const uint64_t win = block_max_u64(mine, s.scratch);
+      if (win) {
+        if (__syncthreads_or(kept && mine != win && kf >= best_value(win) - 4e-6f)) status |= LM_STATUS_NEAR_TIE;
+        if (tid == 0) s.token = static_cast<int>(best_index(win));
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      P.out_tokens[row] = s.token;
+      if (P.out_tau) P.out_tau[row] = tau;
+      if (P.out_status) P.out_status[row] = status;
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace lm

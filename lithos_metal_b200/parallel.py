@@ -1,0 +1,143 @@
+"""Multi-GPU layer of the generation-control path. One process per GPU (``torch.distributed``).
+
+The reference is single-device, so both modes are new; each is defined by "same result as one GPU":
+
+* row-sharded batches (``shard_rows``, ``sample_row_sharded``): rows are independent, every rank samples a contiguous block
+  of rows with ``row_offset`` = its first global row, so Gumbel streams and tokens do not depend on the split. No
+  collective on the data path.
+* vocab-parallel sampling (``VocabParallelSampler``): every rank holds a contiguous shard of each row's vocabulary; per
+  step it computes one small record per row (shard maximum, FP64 softmass, top-k candidates), all-gathers the records
+  (the only exchange: a few hundred bytes per row and rank, NCCL over NVLink), and merges them identically on every
+  rank. The kept set must lie inside the top-k candidates, so ``top_k >= 1`` is required.
+
+The compute steps go through a backend object so that the exchange logic can be exercised on CPU ranks (gloo) with a
+stand-in backend; the default backend is the CUDA library and nothing else ships.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .sampler import SampleOutput, SamplingParams, _check_logits, _dtype_code, _knob, _row_stride, sample
+
+
+def shard_rows(total_rows: int, rank: int, world: int) -> Tuple[int, int]:
+    """(first row, row count) of ``rank``'s contiguous block; the remainder goes to the first ranks."""
+    if not 0 <= rank < world:
+        raise ValueError("rank outside the group")
+    base, extra = divmod(total_rows, world)
+    return rank * base + min(rank, extra), base + (1 if rank < extra else 0)
+
+
+def shard_vocab(vocab: int, rank: int, world: int) -> Tuple[int, int]:
+    """(first index, width) of ``rank``'s contiguous vocabulary shard."""
+    return shard_rows(vocab, rank, world)
+
+
+def sample_row_sharded(local_logits: torch.Tensor, params: SamplingParams, *, first_row: int, history: Optional[torch.Tensor] = None,
+                       uniforms: Optional[torch.Tensor] = None, step: int = 0, **kw) -> SampleOutput:
+    """This rank's rows of a row-sharded batch: ``lm_sample`` with the global index of its first row. Per-row knobs,
+    history and uniforms are this rank's slices."""
+    return sample(local_logits, params, history=history, uniforms=uniforms, step=step, row_offset=first_row, **kw)
+
+
+class CudaVocabBackend:
+    """The two kernels of the vocab-parallel mode through the C ABI."""
+
+    def candidate_cap(self, top_k: int) -> int:
+        return int(_lib.lib().lm_vocab_candidate_cap(int(top_k)))
+
+    def record_bytes(self, cap: int) -> int:
+        return int(_lib.lib().lm_vocab_record_bytes(cap))
+
+    def _fill(self, a, p: SamplingParams, rows: int, dev, keep):
+        ptr, s, t = _knob(p.temperature, rows, torch.float32, dev, "temperature"); a.temperature, a.temperature_s = ptr, float(s); keep.append(t)
+        ptr, s, t = _knob(p.top_k, rows, torch.int32, dev, "top_k"); a.top_k, a.top_k_s = ptr, int(s); keep.append(t)
+        ptr, s, t = _knob(p.top_p, rows, torch.float32, dev, "top_p"); a.top_p, a.top_p_s = ptr, float(s); keep.append(t)
+        ptr, s, t = _knob(p.min_p, rows, torch.float32, dev, "min_p"); a.min_p, a.min_p_s = ptr, float(s); keep.append(t)
+
+    def local(self, logits: torch.Tensor, shard_start: int, p: SamplingParams, cap: int) -> torch.Tensor:
+        logits = _check_logits(logits)
+        rows, width = logits.shape
+        rec = torch.empty(rows, self.record_bytes(cap), dtype=torch.uint8, device=logits.device)
+        a = _lib.VocabArgs()
+        a.struct_size = C.sizeof(_lib.VocabArgs)
+        a.dtype, a.logits, a.rows, a.vocab_local, a.row_stride, a.shard_start = _dtype_code(logits), logits.data_ptr(), rows, width, _row_stride(logits), shard_start
+        a.cap, a.records = cap, rec.data_ptr()
+        keep = []
+        self._fill(a, p, rows, logits.device, keep)
+        a.stream = torch.cuda.current_stream(logits.device).cuda_stream
+        with torch.cuda.device(logits.device):
+            _lib.check(_lib.lib().lm_vocab_local(C.byref(a)), "lm_vocab_local")
+        return rec
+
+    def merge(self, gathered: torch.Tensor, p: SamplingParams, cap: int, uniforms: Optional[torch.Tensor], step: int, row_offset: int):
+        shards, rows, _ = gathered.shape
+        dev = gathered.device
+        a = _lib.VocabArgs()
+        a.struct_size = C.sizeof(_lib.VocabArgs)
+        a.rows, a.shards, a.cap, a.records = rows, shards, cap, gathered.data_ptr()
+        keep = []
+        self._fill(a, p, rows, dev, keep)
+        a.flags = _lib.FLAG_TOPP_IN_TOPK if p.topp_in_topk else 0
+        a.draw = _lib.DRAW_GUMBEL if p.draw == "gumbel" else _lib.DRAW_INVERSE_CDF
+        if uniforms is not None:
+            uniforms = uniforms.to(device=dev, dtype=torch.float32).contiguous()
+            a.uniforms = uniforms.data_ptr()
+        a.seed, a.step, a.row_offset = int(p.seed) & (2**64 - 1), int(step) & 0xFFFFFFFF, int(row_offset)
+        tokens = torch.empty(rows, dtype=torch.int32, device=dev)
+        tau = torch.empty(rows, dtype=torch.float32, device=dev)
+        status = torch.empty(rows, dtype=torch.int32, device=dev)
+        a.out_tokens, a.out_tau, a.out_status = tokens.data_ptr(), tau.data_ptr(), status.data_ptr()
+        a.stream = torch.cuda.current_stream(dev).cuda_stream
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().lm_vocab_merge(C.byref(a)), "lm_vocab_merge")
+        return tokens, tau, status
+
+
+class VocabParallelSampler:
+    """Sampling with the vocabulary split over the ranks of ``group`` (shard order = rank order).
+
+    ``sample(local_logits [rows, width of this rank's shard])`` returns the same tokens on every rank, equal to what a
+    single GPU draws from the concatenated rows. ``params.top_k`` must be >= 1 everywhere; penalties are not supported
+    in this mode.
+    """
+
+    def __init__(self, params: SamplingParams, vocab: int, group=None, backend=None, rank: Optional[int] = None, world: Optional[int] = None):
+        self.params, self.vocab, self.group = params, int(vocab), group
+        self.rank = dist.get_rank(group) if rank is None else rank
+        self.world = dist.get_world_size(group) if world is None else world
+        self.backend = backend if backend is not None else CudaVocabBackend()
+        if params.repetition_penalty != 1.0 or params.presence_penalty != 0.0:
+            raise ValueError("vocab-parallel sampling does not take penalties")
+        if not isinstance(params.temperature, torch.Tensor) and not params.temperature > 0:
+            raise ValueError("vocab-parallel sampling needs temperature > 0 (greedy: use argmax per shard and a max-reduce)")
+        k = params.top_k
+        k_max = int(k.max()) if isinstance(k, torch.Tensor) else int(k)
+        k_min = int(k.min()) if isinstance(k, torch.Tensor) else int(k)
+        if k_min < 1:
+            raise ValueError("vocab-parallel sampling needs top_k >= 1 on every row")
+        self.cap = self.backend.candidate_cap(k_max)
+        if self.cap * self.world > _lib.VOCAB_MAX_CANDIDATES:
+            raise ValueError(f"top_k {k_max} over {self.world} shards needs {self.cap * self.world} candidates per row; the limit is "
+                             f"{_lib.VOCAB_MAX_CANDIDATES}")
+        self.shard_start, self.shard_width = shard_vocab(self.vocab, self.rank, self.world)
+
+    def sample(self, local_logits: torch.Tensor, uniforms: Optional[torch.Tensor] = None, step: int = 0, row_offset: int = 0) -> SampleOutput:
+        if local_logits.shape[1] != self.shard_width:
+            raise ValueError(f"this rank's shard is {self.shard_width} wide, got {local_logits.shape[1]}")
+        if self.params.draw == "inverse_cdf" and uniforms is None:
+            raise ValueError("draw='inverse_cdf' needs uniforms [rows]")
+        rec = self.backend.local(local_logits, self.shard_start, self.params, self.cap)
+        flat = torch.empty(self.world * rec.shape[0], rec.shape[1], dtype=rec.dtype, device=rec.device)   # shard-major: [shard][row]
+        if self.world > 1:
+            dist.all_gather_into_tensor(flat, rec, group=self.group)           # the one exchange of the step
+        else:
+            flat.copy_(rec)
+        gathered = flat.view(self.world, rec.shape[0], rec.shape[1])
+        tokens, tau, status = self.backend.merge(gathered, self.params, self.cap, uniforms, step, row_offset)
+        return SampleOutput(tokens, tau=tau, status=status)

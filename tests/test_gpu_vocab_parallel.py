@@ -1,0 +1,95 @@
+"""Vocab-parallel sampling on the GPU: the local and merge kernels with the shards of 2, 4 and 8 ranks emulated on one
+device (every shard's records computed one after the other, concatenated as the all-gather would leave them). The
+result must equal the single-GPU sampler's on the whole rows, bit for bit, and the CPU model's."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import vocab_parallel as vp
+import lithos_metal_b200 as lm
+from lithos_metal_b200 import parallel
+from tests.test_gpu_sampling import bf16_tensor
+
+pytestmark = pytest.mark.gpu
+
+
+def run_sharded(x, shards, p, uniforms, step=0, row_offset=0):
+    backend = parallel.CudaVocabBackend()
+    vocab = x.shape[1]
+    k = int(p.top_k.max()) if isinstance(p.top_k, torch.Tensor) else int(p.top_k)
+    cap = backend.candidate_cap(k)
+    recs = []
+    for s in range(shards):
+        lo, width = parallel.shard_vocab(vocab, s, shards)
+        recs.append(backend.local(x[:, lo:lo + width], lo, p, cap))
+    gathered = torch.stack(recs)
+    return backend.merge(gathered, p, cap, uniforms, step, row_offset), gathered, cap
+
+
+@pytest.mark.parametrize("shards", [2, 4, 8])
+@pytest.mark.parametrize("draw", ["inverse_cdf", "gumbel"])
+def test_config5_equals_the_single_gpu_result(shards, draw):
+    """Benchmark configuration 5: 64 rows x 262144 BF16 logits N(0, 2^2), top_k 50, top_p 0.9, temperature 0.8."""
+    rng = np.random.default_rng(55)
+    rows, vocab = 64, 262144
+    codes = oracle.f32_to_bf16(rng.standard_normal((rows, vocab), dtype=np.float32) * np.float32(2.0))
+    x = bf16_tensor(codes)
+    u = torch.from_numpy(rng.random(rows).astype(np.float32)).cuda()
+    p = lm.SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=21, draw=draw)
+    (tok, tau, status), _, _ = run_sharded(x, shards, p, u, step=4, row_offset=100)
+    one = lm.sample(x, p, uniforms=u, step=4, row_offset=100, return_tau=True, return_status=True)
+    assert int(status.max()) & ~4 == 0
+    assert torch.equal(tau, one.tau)
+    assert torch.equal(tok, one.tokens)
+    if shards == 8:                                                        # and the CPU definition, on a few rows
+        t_o, tau_o, _ = oracle.sample_batch(codes[:6], temperature=0.8, top_k=50, top_p=0.9, draw=draw, uniforms=u[:6].cpu().numpy(), seed=21, step=4,
+                                            row_offset=100, n_threads=6)
+        np.testing.assert_array_equal(tau[:6].cpu().numpy(), tau_o)
+        np.testing.assert_array_equal(tok[:6].cpu().numpy(), t_o)
+
+
+def test_records_ties_and_knob_variants():
+    rng = np.random.default_rng(3)
+    rows, vocab, shards = 9, 8192, 4
+    z = (rng.standard_normal((rows, vocab)) * 2).astype(np.float32)
+    z[0, 100:140] = 7.5                                                    # 40 tied maxima inside one shard: all of them candidates
+    z[1, ::1024] = 8.0                                                     # tied maxima spread over every shard
+    z[2, :200] = 9.0                                                       # more ties than a record holds: reported
+    x = torch.from_numpy(z).cuda()                                         # FP32 shards
+    u = torch.from_numpy(rng.random(rows).astype(np.float32)).cuda()
+    for kw in (dict(top_k=20, top_p=0.0), dict(top_k=50, top_p=0.95, min_p=0.01), dict(top_k=30, top_p=0.7, topp_in_topk=True), dict(top_k=1)):
+        p = lm.SamplingParams(temperature=0.9, draw="inverse_cdf", **kw)
+        (tok, tau, status), gathered, cap = run_sharded(x, shards, p, u)
+        status = status.cpu().numpy()
+        assert status[2] & 32 and int(tok[2]) == -1 and not np.any(np.delete(status, 2) & 32)
+        one = lm.sample(x, p, uniforms=u, return_tau=True)
+        keep = np.arange(rows) != 2
+        np.testing.assert_array_equal(tau.cpu().numpy()[keep], one.tau.cpu().numpy()[keep])
+        np.testing.assert_array_equal(tok.cpu().numpy()[keep], one.tokens.cpu().numpy()[keep])
+        # the records against the CPU model: same maximum, same candidate set, same mass
+        g = gathered.cpu().numpy()
+        for s in range(shards):
+            lo, width = parallel.shard_vocab(vocab, s, shards)
+            for r in (0, 1, 5):
+                a = vp.unpack_record(g[s, r].tobytes(), cap)
+                b = vp.unpack_record(vp.local_record(z[r, lo:lo + width], lo, temperature=0.9, top_k=kw["top_k"], cap=cap), cap)
+                assert a[0] == b[0] and a[2] == b[2] and sorted(a[5].tolist()) == sorted(b[5].tolist())
+                assert abs(a[1] - b[1]) <= 1e-12 * b[1]
+                tok_m, tau_m, _ = vp.merge_records([g[t, r].tobytes() for t in range(shards)], cap, temperature=0.9, top_k=kw["top_k"],
+                                                   top_p=kw.get("top_p", 0.0), min_p=kw.get("min_p", 0.0), topp_in_topk=kw.get("topp_in_topk", False),
+                                                   u=float(u[r]))
+                assert tok_m == int(tok[r]) and np.float32(tau_m) == np.float32(float(tau[r]))
+
+
+def test_invalid_vocab_parallel_requests():
+    with pytest.raises(ValueError):
+        parallel.VocabParallelSampler(lm.SamplingParams(temperature=0.8, top_k=0, top_p=0.9), 1024, rank=0, world=2)
+    with pytest.raises(ValueError):
+        parallel.VocabParallelSampler(lm.SamplingParams(temperature=0.8, top_k=500), 1024, rank=0, world=8)      # 8 x 568 candidates
+    with pytest.raises(ValueError):
+        parallel.VocabParallelSampler(lm.SamplingParams(temperature=0.8, top_k=5, repetition_penalty=1.2), 1024, rank=0, world=2)
+    s = parallel.VocabParallelSampler(lm.SamplingParams(temperature=0.8, top_k=5, draw="inverse_cdf"), 1024, rank=0, world=1)
+    x = torch.randn(3, 1024, device="cuda")
+    u = torch.rand(3)
+    assert torch.equal(s.sample(x, uniforms=u).tokens, lm.sample(x, s.params, uniforms=u).tokens)      # one shard: the plain sampler
