@@ -51,12 +51,14 @@ extern "C" {
 
 /* lm_sample_args.flags */
 #define LM_FLAG_TOPP_IN_TOPK 1u /* top-p over the top-k set's renormalised mass (the Hugging Face warpers' order) */
+#define LM_FLAG_GRID_LIMIT(n) (((uint32_t)(n) & 0xFFu) << 8) /* at most n thread blocks (0 = one per SM): leaves SMs to other streams */
 
 /* per-row status bits written to lm_sample_args.out_status (optional) */
 #define LM_STATUS_GENERIC_PATH 1u /* the row was handled by the generic multi-pass path */
 #define LM_STATUS_NAN 2u          /* the row holds a NaN: results for the row are unspecified */
 #define LM_STATUS_NEAR_TIE 4u     /* Gumbel draw: best and second-best key closer than 4e-6 (float32 log is library-specific) */
 #define LM_STATUS_TOPP_EDGE 8u    /* top-p: cumulative mass within 1e-12 (relative) of the target at the boundary */
+#define LM_STATUS_CANDIDATE_PATH 64u /* the row was finished by the one-pass candidate path (informational) */
 
 #define LM_MAX_VOCAB 1048576
 

@@ -13,6 +13,7 @@ DRAW_GUMBEL, DRAW_INVERSE_CDF = 0, 1
 FLAG_TOPP_IN_TOPK = 1
 VERIFY_GREEDY, VERIFY_STOCHASTIC = 0, 1
 STATUS_GENERIC_PATH, STATUS_NAN, STATUS_NEAR_TIE, STATUS_TOPP_EDGE, STATUS_OVERFLOW = 1, 2, 4, 8, 32
+STATUS_CANDIDATE_PATH = 64
 VOCAB_MAX_CANDIDATES = 1024
 MAX_DRAFT = 15
 MAX_VOCAB = 1048576

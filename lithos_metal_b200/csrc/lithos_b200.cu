@@ -69,6 +69,8 @@ __global__ void __launch_bounds__(kBlock, 1) sample_generic_kernel(SampleDev P) 
 __global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, uint32_t* punt) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   FastSmem& s = *reinterpret_cast<FastSmem*>(smem_raw);
+  if (threadIdx.x == 0) { s.cut.code = 0u; s.cut.valid = 0u; }
+  __syncthreads();
   for (int row = blockIdx.x; row < P.rows; row += gridDim.x) {
     sample_row_fast(P, row, s, punt);
     __syncthreads();
@@ -261,7 +263,9 @@ int lm_sample(const lm_sample_args* a) {
       if (e != cudaSuccess) return cuda_fail(e);
       fast_attr = true;
     }
-    const int grid = static_cast<int>(a->rows < sms ? a->rows : sms);
+    int grid = static_cast<int>(a->rows < sms ? a->rows : sms);
+    const int limit = static_cast<int>((a->flags >> 8) & 0xFFu);
+    if (limit > 0 && grid > limit) grid = limit;
     sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, punt);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e);

@@ -16,11 +16,11 @@
 #include "common.cuh"
 #include "draw.cuh"
 #include "sample_generic.cuh"
+#include "sample_cand.cuh"
 
 namespace lm {
 
 #ifdef LM_PROFILE_PHASES
-__device__ unsigned long long g_phase_cycles[16];
 #define LM_PHASE(i) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == 0) { const long long _t = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(_t - _t0)); _t0 = _t; } } while (0)
 #else
 #define LM_PHASE(i) do {} while (0)
@@ -56,6 +56,7 @@ struct FastSmem {
   DrawSmem draw;
   double warp_m[32];
   uint32_t warp_c[32];
+  CutoffState cut;                          // the candidate path's cutoff, carried from row to row of this block
   uint32_t side_n;
   uint32_t side_max_key;
   uint32_t top_group, top_pos;
@@ -247,10 +248,8 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
   rv.dtype = LM_DTYPE_BF16; rv.vocab = V; rv.rho = P.rho; rv.pi = P.pi; rv.row = rowp; rv.aligned = true; rv.pen = nullptr;
   const int n_chunks = V / kChunk;
 
-  // ---- clear the histogram; the history's distinct ids as a bitmap and as a list -------------------------------------
+  // ---- the history's distinct ids as a bitmap and as a list -------------------------------------
   {
-    uint4* h4 = reinterpret_cast<uint4*>(s.hist);
-    for (int i = tid; i < kCodes / 8; i += kBlock) h4[i] = make_uint4(0u, 0u, 0u, 0u);
     if (tid == 0) { s.side_n = 0u; s.side_max_key = 0u; s.top_group = kGroups; s.top_pos = 0xFFFFFFFFu; }
     if (tid < kGroups) { s.gfill[tid] = 0u; s.goff[tid] = 0u; }
     if (tid == 0) s.goff[kGroups] = 0u;
@@ -313,6 +312,20 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
     return;
   }
 
+  // ---- rows with a small top_k: the candidate path (one pass, no histogram); it hands the row back when it cannot decide ----
+  if (top_k >= 1 && top_k <= kCandMaxK && top_k <= V && s.cut.valid) {
+    if (sample_row_candidates(P, row, rowp, V, T, top_k, top_p, min_p, *reinterpret_cast<CandSmem*>(s.hist), s.cut, s.side_idx, s.side_val, n_side,
+                              pen_on ? s.pen : nullptr, s.draw.scratch)) {
+      if (tid == 0) punt[row] = 0u;
+      return;
+    }
+  }
+  LM_PHASE(8);
+  {
+    uint4* h4 = reinterpret_cast<uint4*>(s.hist);
+    for (int i = tid; i < kCodes / 8; i += kBlock) h4[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+  }
   // ---- pass 1: the histogram of the raw row, straight from HBM ----------------------------------------------------------
   {
     const uint4* p4 = reinterpret_cast<const uint4*>(rowp);
@@ -516,6 +529,16 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
     have_tau = true;
   }
   const float tau = have_tau ? __double2float_rn(tau64) : -INFINITY;
+  // ---- the candidate path's cutoff, when it has none: the value of rank ~1500 of this row, from the histogram -------------
+  if (!s.cut.valid && V >= 8 * kCandHigh) {
+    find_group<false>(s, 1500u, 0.0);
+    refine_group<false, false>(s, s.sel_group, s.sel_base_c, 0.0, 1500u, 0.0, vmax, inv_t);
+    if (tid == 0 && !s.res_fail) {
+      const uint32_t code = floor_code(s.res_tau);
+      if (s.res_tau > 0.0f && code > 0x0081u && code < 0x7F00u) { s.cut.code = code; s.cut.valid = 1u; }
+    }
+    __syncthreads();
+  }
   LM_PHASE(6);
 
   // ---- pass 2: the draw over the kept set (the row is in L2) ---------------------------------------------------------
