@@ -242,7 +242,7 @@ def main() -> None:
            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                         "frac_of_nominal_8TBs": achieved / 8000.0, "algorithmic_bytes_per_row": ROW_BYTES,
                         "traffic": (traffic["dram_bytes_per_row"] * rows if traffic else None)},
-           "gpu_launches": args.steps, "clocks": clocks.summary()}
+           "gpu_launches": 2 * args.steps, "clocks": clocks.summary()}
 
     if not args.skip_extras:
         # ---- e2e: host (pinned) inputs -> public API -> tokens on the host, copies inside the timed region

@@ -11,7 +11,11 @@
 
 namespace lm {
 
-constexpr int kBlock = 1024;           // threads per block of the row kernels
+#ifndef LM_BLOCK
+#define LM_BLOCK 1024
+#endif
+constexpr int kBlock = LM_BLOCK;       // threads per block of the row kernels
+constexpr int kWarps = kBlock / 32;
 constexpr int kChunk = 8;              // consecutive logits one thread takes per step (one 128-bit load of BF16)
 constexpr uint32_t kFull = 0xFFFFFFFFu;
 

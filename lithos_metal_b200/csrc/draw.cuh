@@ -149,7 +149,7 @@ __device__ int draw_inverse_cdf(const RowView& rv, float tau, float vmax, float 
     __syncthreads();
     if (tid < n_sweeps) {
       uint64_t t = 0ull;
-      for (int w = 0; w < 32; w++) t += sweep_part[tid * 32 + w];
+      for (int w = 0; w < kWarps; w++) t += sweep_part[tid * 32 + w];
       t += static_cast<uint64_t>(side_limb[3 * tid]) + (static_cast<uint64_t>(side_limb[3 * tid + 1]) << 16) + (static_cast<uint64_t>(side_limb[3 * tid + 2]) << 32);
       d.sweep_total[tid] = t;
     }

@@ -16,6 +16,8 @@
 
 namespace lm {
 
+static_assert(kBlock == 512 || kBlock == 1024, "the row kernels are written for 512 or 1024 threads per block");
+
 // ---- greedy argmax: rows x splits blocks, packed (value, lowest index) maxima meet in the workspace --------------
 constexpr int kArgmaxBlock = 512;
 

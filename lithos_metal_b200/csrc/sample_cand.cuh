@@ -26,6 +26,7 @@ __device__ unsigned long long g_phase_cycles[16];    // clock64 totals per phase
 constexpr int kCandCap = 2048;            // candidates per row (logits at or above the cutoff)
 constexpr int kCandBins = 512;            // BF16 codes above the cutoff that the coarse count covers
 constexpr int kCandMaxK = 1024;           // largest top_k this path takes
+constexpr int kHitSlots = 12288 / kBlock;  // chunks with a candidate one thread may meet in a row (expected 1.4 at 1024 threads)
 constexpr int kCandHigh = 1800, kCandLow = 1200;   // the cutoff moves one BF16 step when the candidate count leaves this band
 
 struct CandSmem {                          // lives in the histogram's shared memory: the two paths never run at the same time
@@ -34,6 +35,7 @@ struct CandSmem {                          // lives in the histogram's shared me
   double cum[kCandCap];                    // inclusive FP64 softmass prefix over sel
   unsigned long long w[kCandCap];          // fixed-point weights / index-sort keys of the kept prefix
   uint32_t bins[kCandBins];                // candidates per BF16 code, relative to the cutoff code
+  uint32_t hits[kHitSlots * kBlock];       // per thread: (chunk << 8 | 8-bit mask) of its chunks that hold a candidate; slot-major
   double warp_d[32];
   float warp_f[32];
   uint32_t n, n_sel, wide, cross_bin;
@@ -43,17 +45,17 @@ struct CandSmem {                          // lives in the histogram's shared me
 
 __device__ __forceinline__ float ex2_approx(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 
-// bitonic sort of a[0 .. n_pow2) in shared memory, descending; every thread of the block calls
+// bitonic sort of a[0 .. n_pow2) in shared memory, descending; every thread of the block calls. One compare-exchange
+// per thread and step: thread t takes the t-th pair (i, i ^ j) with i's bit j clear.
 __device__ __forceinline__ void bitonic_desc(unsigned long long* a, int n_pow2) {
   for (int k = 2; k <= n_pow2; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int i = threadIdx.x; i < n_pow2; i += kBlock) {
-        const int partner = i ^ j;
-        if (partner > i) {
-          const unsigned long long x = a[i], y = a[partner];
-          const bool desc = (i & k) == 0;
-          if (desc ? (x < y) : (x > y)) { a[i] = y; a[partner] = x; }
-        }
+      for (int t = threadIdx.x; t < (n_pow2 >> 1); t += kBlock) {
+        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+        const int partner = i | j;
+        const unsigned long long x = a[i], y = a[partner];
+        const bool desc = (i & k) == 0;
+        if (desc ? (x < y) : (x > y)) { a[i] = y; a[partner] = x; }
       }
       __syncthreads();
     }
@@ -78,7 +80,7 @@ __device__ __forceinline__ void scan_f64(double* v, int n, double* warp_d) {
     for (int w = 0; w < warp; w++) wsum += warp_d[w];
     if (i < n) v[i] = carry + wsum + x;
     double tot = 0.0;
-    for (int w = 0; w < 32; w++) tot += warp_d[w];
+    for (int w = 0; w < kWarps; w++) tot += warp_d[w];
     carry += tot;
   }
   __syncthreads();
@@ -133,6 +135,7 @@ __device__ bool sample_row_candidates(const SampleDev& P, int row, const uint16_
 
   // ---- the one pass: candidates at or above the cutoff; FP32 softmass with a per-thread running maximum ---------------
   float m = -INFINITY, sacc = 0.0f;
+  int n_hits = 0;
   {
     const uint4* p4 = reinterpret_cast<const uint4*>(rowp);
     const uint32_t cut2 = cut_code | (cut_code << 16);
@@ -149,14 +152,11 @@ __device__ bool sample_row_candidates(const SampleDev& P, int row, const uint16_
         const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
         const uint32_t m0 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[0]), t2), m1 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[1]), t2);
         const uint32_t m2 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[2]), t2), m3 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[3]), t2);
-        if (m0 | m1 | m2 | m3) {                                           // rare: about one logit in a hundred
-          const uint32_t bits = pen ? ((pen[cc >> 2] >> ((cc & 3) * 8)) & 0xFFu) : 0u;
-          const uint32_t mk[4] = {m0, m1, m2, m3};
-#pragma unroll
-          for (int e = 0; e < kChunk; e++) {
-            const bool on = (e & 1) ? (mk[e >> 1] >> 16) != 0u : (mk[e >> 1] & 0xFFFFu) != 0u;
-            if (on && !((bits >> e) & 1u)) cand_append(c, (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]), static_cast<uint32_t>(cc * kChunk + e), cut_code);
-          }
+        if (m0 | m1 | m2 | m3) {                                           // rare per thread (7 % of its chunks): just note the chunk
+          const uint32_t mask = (m0 & 1u) | ((m0 >> 15) & 2u) | ((m1 & 1u) << 2) | ((m1 >> 13) & 8u) | ((m2 & 1u) << 4) | ((m2 >> 11) & 32u) |
+                                ((m3 & 1u) << 6) | ((m3 >> 9) & 128u);
+          if (n_hits < kHitSlots) c.hits[n_hits * kBlock + tid] = (static_cast<uint32_t>(cc) << 8) | mask;
+          n_hits++;
         }
         if (need_z) {
           const __nv_bfloat162 a = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&w[0]), *reinterpret_cast<const __nv_bfloat162*>(&w[1]));
@@ -174,10 +174,59 @@ __device__ bool sample_row_candidates(const SampleDev& P, int row, const uint16_
     }
   }
   LM_CPHASE(9);
-  // the penalised logits: gathers issued before the barrier that ends the pass
-  uint32_t sd_code[kCandCap / kBlock * 2]; int sd_idx[kCandCap / kBlock * 2];   // 4 per thread: the side list holds up to 4096
+  // ---- the noted chunks, expanded with every lane active: their logits come back from L2, the candidates are written
+  // in thread order (a block-wide prefix of the per-thread counts), so the list is the same on every run
+  {
+    uint32_t my[kHitSlots];
+    const int nh = n_hits < kHitSlots ? n_hits : kHitSlots;
+    uint32_t ne = 0;
 #pragma unroll
-  for (int j = 0; j < 4; j++) {
+    for (int h = 0; h < kHitSlots; h++) {
+      my[h] = 0u;
+      if (h < nh) {
+        const uint32_t ent = c.hits[h * kBlock + tid];
+        const int cc = static_cast<int>(ent >> 8);
+        uint32_t mask = ent & 0xFFu;
+        if (pen) mask &= ~((pen[cc >> 2] >> ((cc & 3) * 8)) & 0xFFu);       // penalised positions come from the side list
+        my[h] = (ent & ~0xFFu) | mask;
+        ne += __popc(mask);
+      }
+    }
+    if (n_hits > kHitSlots) c.wide = 1u;
+    uint64_t tot = 0ull;
+    uint32_t slot = static_cast<uint32_t>(block_exclusive_scan_u64(ne, scratch, &tot));
+    if (tid == 0) c.n = static_cast<uint32_t>(tot);
+    for (int h0 = 0; h0 < kHitSlots; h0 += 4) {                            // four reloads in flight; most threads need one round or none
+      if (__syncthreads_or(h0 < nh) == 0) break;
+      uint4 qq[4];
+#pragma unroll
+      for (int h = 0; h < 4; h++) if (h0 + h < nh) qq[h] = __ldg(reinterpret_cast<const uint4*>(rowp) + (my[h0 + h] >> 8));
+#pragma unroll
+      for (int h = 0; h < 4; h++) {
+        if (h0 + h < nh) {
+          const uint32_t w[4] = {qq[h].x, qq[h].y, qq[h].z, qq[h].w};
+          const uint32_t ent = my[h0 + h];
+          const int cc = static_cast<int>(ent >> 8);
+#pragma unroll
+          for (int e = 0; e < kChunk; e++) {
+            if ((ent >> e) & 1u) {
+              const float value = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
+              if (slot < kCandCap) c.key[slot] = (static_cast<unsigned long long>(fkey(value)) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(cc * kChunk + e));
+              slot++;
+              const uint32_t rel = (__float_as_uint(value) >> 16) - cut_code;
+              if (rel >= kCandBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // the penalised logits: gathers issued before the barrier that ends the pass
+  constexpr int kSideSlots = 4096 / kBlock;                                // the side list holds up to 4096 entries
+  uint32_t sd_code[kSideSlots]; int sd_idx[kSideSlots];
+#pragma unroll
+  for (int j = 0; j < kSideSlots; j++) {
     const uint32_t i = tid + j * kBlock;
     sd_idx[j] = (i < n_side) ? side_idx[i] : 0;
     sd_code[j] = (i < n_side) ? __ldg(rowp + sd_idx[j]) : 0u;
@@ -188,12 +237,12 @@ __device__ bool sample_row_candidates(const SampleDev& P, int row, const uint16_
   for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(kFull, M, o));
   if (lane == 0) c.warp_f[warp] = M;
   __syncthreads();
-  M = c.warp_f[lane];
+  M = lane < kWarps ? c.warp_f[lane] : -INFINITY;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(kFull, M, o));
   double zsum = (need_z && m > -INFINITY) ? static_cast<double>(sacc * ex2_approx((m - M) * c2a)) : 0.0;
 #pragma unroll
-  for (int j = 0; j < 4; j++) {
+  for (int j = 0; j < kSideSlots; j++) {
     if (tid + j * kBlock < n_side) {
       const float raw = __uint_as_float(sd_code[j] << 16);
       const float v = penalise(raw, P.rho, P.pi);

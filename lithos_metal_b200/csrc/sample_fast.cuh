@@ -132,14 +132,16 @@ __device__ void refine_group(FastSmem& s, int group, uint32_t base_c, double bas
   }
   __syncthreads();
   if (s.res_fail) return;
-  if (NEED_MASS) {                                                         // warp w: the masses of owner lane w's bins and side values
-    const uint32_t pos0 = static_cast<uint32_t>(group) * kGroupBins + warp * 8u;
-    if (lane < 8) {
-      const uint32_t code = pos_to_code(pos0 + lane);
-      const uint32_t c = hist_get(s.hist, code);
-      s.lane_bin_mass[warp][lane] = c ? static_cast<double>(c) * softmass(code_val(code), vmax, inv_t) : 0.0;
-    } else {
-      for (uint32_t i = lane - 8; i < s.lane_side_n[warp]; i += 24) s.lane_side_mass[warp][i] = softmass(s.lane_side[warp][i], vmax, inv_t);
+  if (NEED_MASS) {                                                         // a warp per owner lane: the masses of its bins and side values
+    for (int o = warp; o < 32; o += kWarps) {
+      const uint32_t pos0 = static_cast<uint32_t>(group) * kGroupBins + o * 8u;
+      if (lane < 8) {
+        const uint32_t code = pos_to_code(pos0 + lane);
+        const uint32_t c = hist_get(s.hist, code);
+        s.lane_bin_mass[o][lane] = c ? static_cast<double>(c) * softmass(code_val(code), vmax, inv_t) : 0.0;
+      } else {
+        for (uint32_t i = lane - 8; i < s.lane_side_n[o]; i += 24) s.lane_side_mass[o][i] = softmass(s.lane_side[o][i], vmax, inv_t);
+      }
     }
     __syncthreads();
   }
@@ -247,6 +249,24 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
   RowView rv;
   rv.dtype = LM_DTYPE_BF16; rv.vocab = V; rv.rho = P.rho; rv.pi = P.pi; rv.row = rowp; rv.aligned = true; rv.pen = nullptr;
   const int n_chunks = V / kChunk;
+
+  // the next row of this block (and its history): start pulling it into L2 now, a whole row ahead of its use, so that its
+  // pass runs against L2 latency instead of loaded-HBM latency
+  {
+    const int next = row + gridDim.x;
+    const char* np = reinterpret_cast<const char*>(rowp) + static_cast<size_t>(gridDim.x) * static_cast<size_t>(P.row_stride) * 2;
+    if (next < P.rows && tid < 32 && (reinterpret_cast<uintptr_t>(np) & 15u) == 0) {
+      const uint32_t bytes = static_cast<uint32_t>(V) * 2u;
+      const uint32_t piece = ((bytes / 32u) + 15u) & ~15u;
+      const uint32_t off = piece * lane;
+      if (off < bytes) prefetch_l2(np + off, min(piece, bytes - off));
+    }
+    if (next < P.rows && tid == 32 % kBlock && pen_on) {
+      const char* hp = reinterpret_cast<const char*>(P.history + static_cast<int64_t>(next) * P.hist_stride);
+      const uint32_t hb = (static_cast<uint32_t>(P.hist_len) * 4u) & ~15u;
+      if ((reinterpret_cast<uintptr_t>(hp) & 15u) == 0 && hb) prefetch_l2(hp, hb);
+    }
+  }
 
   // ---- the history's distinct ids as a bitmap and as a list -------------------------------------
   {
@@ -399,25 +419,8 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
     __syncthreads();
   }
   LM_PHASE(2);
-  // the next row of this block: start pulling it into L2 while this one is selected and drawn
-  {
-    const int next = row + gridDim.x;
-    const char* np = reinterpret_cast<const char*>(rowp) + static_cast<size_t>(gridDim.x) * static_cast<size_t>(P.row_stride) * 2;
-    if (next < P.rows && tid < 32 && (reinterpret_cast<uintptr_t>(np) & 15u) == 0) {
-      const uint32_t bytes = static_cast<uint32_t>(V) * 2u;
-      const uint32_t piece = ((bytes / 32u) + 15u) & ~15u;
-      const uint32_t off = piece * lane;
-      if (off < bytes) prefetch_l2(np + off, min(piece, bytes - off));
-    }
-    if (next < P.rows && tid == 32 && pen_on) {
-      const char* hp = reinterpret_cast<const char*>(P.history + static_cast<int64_t>(next) * P.hist_stride);
-      const uint32_t hb = (static_cast<uint32_t>(P.hist_len) * 4u) & ~15u;
-      if ((reinterpret_cast<uintptr_t>(hp) & 15u) == 0 && hb) prefetch_l2(hp, hb);
-    }
-  }
-
   // ---- group counts (pure BF16 logits), the overflow check, the maximum ------------------------------------------------
-  for (int g = warp; g < kGroups; g += 32) {
+  for (int g = warp; g < kGroups; g += kWarps) {
     const bool pos_half = g < kGroups / 2;
     const int block = pos_half ? (kGroups / 2 - 1 - g) : g;
     uint32_t c = sum8(reinterpret_cast<const uint4*>(s.hist)[block * 32 + lane]);
@@ -464,7 +467,7 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
   double topk_mass = 0.0;
   if (has_p) {
     // group masses: count x exp64 per occupied bin (eight bins per lane) plus the exact softmass of the group's side values
-    for (int g = warp; g < kGroups; g += 32) {
+    for (int g = warp; g < kGroups; g += kWarps) {
       const uint32_t s0 = s.goff[g], s1 = s.goff[g + 1];
       if (s.gcnt[g] == 0u && s0 == s1) { if (lane == 0) s.gmass[g] = 0.0; continue; }
       double m = 0.0;
