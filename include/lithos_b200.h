@@ -51,6 +51,7 @@ extern "C" {
 
 /* lm_sample_args.flags */
 #define LM_FLAG_TOPP_IN_TOPK 1u /* top-p over the top-k set's renormalised mass (the Hugging Face warpers' order) */
+#define LM_FLAG_EXACT_ONLY 2u /* skip the one-pass candidate kernel for rows with a top_k: every row takes the histogram path (same results) */
 #define LM_FLAG_GRID_LIMIT(n) (((uint32_t)(n) & 0xFFu) << 8) /* at most n thread blocks (0 = one per SM): leaves SMs to other streams */
 
 /* per-row status bits written to lm_sample_args.out_status (optional) */

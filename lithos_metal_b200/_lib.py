@@ -11,6 +11,7 @@ LM_OK = 0
 DTYPE_BF16, DTYPE_F32 = 0, 1
 DRAW_GUMBEL, DRAW_INVERSE_CDF = 0, 1
 FLAG_TOPP_IN_TOPK = 1
+FLAG_EXACT_ONLY = 2
 VERIFY_GREEDY, VERIFY_STOCHASTIC = 0, 1
 STATUS_GENERIC_PATH, STATUS_NAN, STATUS_NEAR_TIE, STATUS_TOPP_EDGE, STATUS_OVERFLOW = 1, 2, 4, 8, 32
 STATUS_CANDIDATE_PATH = 64

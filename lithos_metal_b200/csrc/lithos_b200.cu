@@ -10,6 +10,7 @@
 #include "common.cuh"
 #include "sample_generic.cuh"
 #include "sample_fast.cuh"
+#include "sample_topk.cuh"
 #include "verify.cuh"
 #include "vocab_parallel.cuh"
 #include "spec_ops.cuh"
@@ -67,14 +68,17 @@ __global__ void __launch_bounds__(kBlock, 1) sample_generic_kernel(SampleDev P) 
   }
 }
 
-// ---- the streaming BF16 sampler: one block per SM, each walks rows blockIdx.x, blockIdx.x + gridDim.x, ... ---------------
-__global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, uint32_t* punt) {
+// ---- the streaming BF16 sampler: one block per SM. With a row list (written by the top-k kernel: the rows it left), block b
+// takes entries b, b + gridDim.x, ... of it; without one, rows b, b + gridDim.x, ... ------------------------------------------
+__global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, uint32_t* punt, const int* list, const int* n_list) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   FastSmem& s = *reinterpret_cast<FastSmem*>(smem_raw);
-  if (threadIdx.x == 0) { s.cut.code = 0u; s.cut.valid = 0u; }
-  __syncthreads();
-  for (int row = blockIdx.x; row < P.rows; row += gridDim.x) {
-    sample_row_fast(P, row, s, punt);
+  const int n = list ? *n_list : P.rows;
+  for (int i = blockIdx.x; i < n; i += gridDim.x) {
+    const int row = list ? list[i] : i;
+    const int in = i + static_cast<int>(gridDim.x);
+    const int next = in < n ? (list ? list[in] : in) : -1;
+    sample_row_fast(P, row, next, s, punt);
     __syncthreads();
   }
 }
@@ -149,7 +153,8 @@ float lm_uniform01(uint64_t seed, uint32_t step, uint32_t t, uint32_t index) { r
 size_t lm_workspace_bytes(int64_t rows, int64_t vocab) {
   (void)vocab;
   if (rows < 0) rows = 0;
-  return align256(static_cast<size_t>(rows) * sizeof(ArgmaxWs)) + align256(static_cast<size_t>(rows) * sizeof(uint32_t)) + 256;
+  // argmax partials | rows left to the generic kernel | rows left to the histogram kernel | two counters
+  return align256(static_cast<size_t>(rows) * sizeof(ArgmaxWs)) + 2 * align256(static_cast<size_t>(rows) * sizeof(uint32_t)) + 256;
 }
 
 size_t lm_verify_workspace_bytes(int32_t n_draft, int64_t vocab) {
@@ -258,17 +263,33 @@ int lm_sample(const lm_sample_args* a) {
   if (fast) {
     if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) || a->workspace_bytes < lm_workspace_bytes(a->rows, a->vocab))
       return LM_E_WORKSPACE;
-    uint32_t* punt = reinterpret_cast<uint32_t*>(static_cast<char*>(a->workspace) + align256(static_cast<size_t>(a->rows) * sizeof(ArgmaxWs)));
+    char* ws = static_cast<char*>(a->workspace) + align256(static_cast<size_t>(a->rows) * sizeof(ArgmaxWs));
+    uint32_t* punt = reinterpret_cast<uint32_t*>(ws);
+    int* list = reinterpret_cast<int*>(ws + align256(static_cast<size_t>(a->rows) * sizeof(uint32_t)));
+    int* counters = reinterpret_cast<int*>(ws + 2 * align256(static_cast<size_t>(a->rows) * sizeof(uint32_t)));
     static thread_local bool fast_attr = false;
     if (!fast_attr) {
-      const cudaError_t e = cudaFuncSetAttribute(sample_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FastSmem)));
+      cudaError_t e = cudaFuncSetAttribute(sample_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FastSmem)));
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(sample_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(TopkSmem)));
       if (e != cudaSuccess) return cuda_fail(e);
       fast_attr = true;
     }
-    int grid = static_cast<int>(a->rows < sms ? a->rows : sms);
     const int limit = static_cast<int>((a->flags >> 8) & 0xFFu);
+    // rows with a top_k go through the candidate kernel first (three small blocks per SM); it lists the rows it leaves
+    const bool topk = !(a->flags & LM_FLAG_EXACT_ONLY) && a->vocab >= kTopkMinVocab && (a->top_k != nullptr || (a->top_k_s >= 1 && a->top_k_s <= kTopkMaxK)) &&
+                      (a->temperature != nullptr || a->temperature_s > 0.0f) && (!pen || a->hist_len <= kTopkHist);
+    if (topk) {
+      cudaError_t e = cudaMemsetAsync(counters, 0, 2 * sizeof(int), st);
+      if (e != cudaSuccess) return cuda_fail(e);
+      int grid1 = static_cast<int>(a->rows < 3LL * sms ? a->rows : 3LL * sms);
+      if (limit > 0 && grid1 > limit) grid1 = limit;
+      sample_topk_kernel<<<grid1, kTB, sizeof(TopkSmem), st>>>(P, punt, list, counters);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return cuda_fail(e);
+    }
+    int grid = static_cast<int>(a->rows < sms ? a->rows : sms);
     if (limit > 0 && grid > limit) grid = limit;
-    sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, punt);
+    sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, punt, topk ? list : nullptr, topk ? counters + 1 : nullptr);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e);
     P.row_select = punt;

@@ -16,11 +16,11 @@
 #include "common.cuh"
 #include "draw.cuh"
 #include "sample_generic.cuh"
-#include "sample_cand.cuh"
 
 namespace lm {
 
 #ifdef LM_PROFILE_PHASES
+__device__ unsigned long long g_phase_cycles[16];    // clock64 totals per phase of block 0 (profiling builds only)
 #define LM_PHASE(i) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == 0) { const long long _t = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(_t - _t0)); _t0 = _t; } } while (0)
 #else
 #define LM_PHASE(i) do {} while (0)
@@ -56,7 +56,6 @@ struct FastSmem {
   DrawSmem draw;
   double warp_m[32];
   uint32_t warp_c[32];
-  CutoffState cut;                          // the candidate path's cutoff, carried from row to row of this block
   uint32_t side_n;
   uint32_t side_max_key;
   uint32_t top_group, top_pos;
@@ -231,7 +230,8 @@ __device__ void find_group(FastSmem& s, uint32_t k_target, double m_target) {
   __syncthreads();
 }
 
-__device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32_t* punt) {
+// `next` is the row this block takes after this one (-1: none): it is pulled into L2 while this one is worked on.
+__device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem& s, uint32_t* punt) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int V = P.vocab;
   const float T = P.temperature ? P.temperature[row] : P.temperature_s;
@@ -253,15 +253,14 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
   // the next row of this block (and its history): start pulling it into L2 now, a whole row ahead of its use, so that its
   // pass runs against L2 latency instead of loaded-HBM latency
   {
-    const int next = row + gridDim.x;
-    const char* np = reinterpret_cast<const char*>(rowp) + static_cast<size_t>(gridDim.x) * static_cast<size_t>(P.row_stride) * 2;
-    if (next < P.rows && tid < 32 && (reinterpret_cast<uintptr_t>(np) & 15u) == 0) {
+    const char* np = reinterpret_cast<const char*>(P.logits) + static_cast<size_t>(next < 0 ? 0 : next) * static_cast<size_t>(P.row_stride) * 2;
+    if (next >= 0 && tid < 32 && (reinterpret_cast<uintptr_t>(np) & 15u) == 0) {
       const uint32_t bytes = static_cast<uint32_t>(V) * 2u;
       const uint32_t piece = ((bytes / 32u) + 15u) & ~15u;
       const uint32_t off = piece * lane;
       if (off < bytes) prefetch_l2(np + off, min(piece, bytes - off));
     }
-    if (next < P.rows && tid == 32 % kBlock && pen_on) {
+    if (next >= 0 && tid == 32 % kBlock && pen_on) {
       const char* hp = reinterpret_cast<const char*>(P.history + static_cast<int64_t>(next) * P.hist_stride);
       const uint32_t hb = (static_cast<uint32_t>(P.hist_len) * 4u) & ~15u;
       if ((reinterpret_cast<uintptr_t>(hp) & 15u) == 0 && hb) prefetch_l2(hp, hb);
@@ -332,14 +331,6 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
     return;
   }
 
-  // ---- rows with a small top_k: the candidate path (one pass, no histogram); it hands the row back when it cannot decide ----
-  if (top_k >= 1 && top_k <= kCandMaxK && top_k <= V && s.cut.valid) {
-    if (sample_row_candidates(P, row, rowp, V, T, top_k, top_p, min_p, *reinterpret_cast<CandSmem*>(s.hist), s.cut, s.side_idx, s.side_val, n_side,
-                              pen_on ? s.pen : nullptr, s.draw.scratch)) {
-      if (tid == 0) punt[row] = 0u;
-      return;
-    }
-  }
   LM_PHASE(8);
   {
     uint4* h4 = reinterpret_cast<uint4*>(s.hist);
@@ -532,16 +523,6 @@ __device__ void sample_row_fast(const SampleDev& P, int row, FastSmem& s, uint32
     have_tau = true;
   }
   const float tau = have_tau ? __double2float_rn(tau64) : -INFINITY;
-  // ---- the candidate path's cutoff, when it has none: the value of rank ~1500 of this row, from the histogram -------------
-  if (!s.cut.valid && V >= 8 * kCandHigh) {
-    find_group<false>(s, 1500u, 0.0);
-    refine_group<false, false>(s, s.sel_group, s.sel_base_c, 0.0, 1500u, 0.0, vmax, inv_t);
-    if (tid == 0 && !s.res_fail) {
-      const uint32_t code = floor_code(s.res_tau);
-      if (s.res_tau > 0.0f && code > 0x0081u && code < 0x7F00u) { s.cut.code = code; s.cut.valid = 1u; }
-    }
-    __syncthreads();
-  }
   LM_PHASE(6);
 
   // ---- pass 2: the draw over the kept set (the row is in L2) ---------------------------------------------------------

@@ -1,0 +1,482 @@
+// The top-k candidate kernel: rows with 1 <= top_k <= kTopkMaxK in ONE pass over the row, no histogram, small blocks.
+//
+// With top-k on, the kept set lies inside the row's top-k logits. So the pass only has to (a) collect the few logits at or
+// above a cutoff (estimated per row from 8192 of its logits: about 1 % of the row ends up above it), and
+// (b) accumulate the softmass of the whole row in FP32 (the top-p target needs it). Everything exact then happens on the
+// candidates alone: the k-th largest value, FP64 masses, the top-p boundary, integer weights, the draw. The FP32 mass is
+// only used to decide on which side of top_p * Z a cumulative mass lies; if that is closer than the FP32 error bound, or
+// the candidates do not cover the top-k set, or anything else does not fit, the row is flagged and the histogram
+// kernel launched behind this one redoes it exactly.
+// Blocks are small (256 threads, ~72 KB of shared memory) so that three rows are in flight per SM: the per-row phases after
+// the pass are chains of short dependent steps, and only rows in other blocks can hide them.
+// No counterpart in the reference (its sampler always builds the full histogram, kernels/common/sample.metal:34-162).
+#pragma once
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "sample_generic.cuh"
+
+namespace lm {
+
+constexpr int kTB = 256;                   // threads per block
+constexpr int kTW = kTB / 32;
+constexpr int kTopkCap = 2048;             // candidates per row (a power of two: the sorts pad to one)
+constexpr int kTopkBins = 512;             // BF16 codes above the cutoff that the coarse count covers
+constexpr int kTopkMaxK = 1024;            // largest top_k this kernel takes
+constexpr int kTopkHist = 2048;            // longest history it takes (distinct ids live in a 4096-slot hash set)
+constexpr int kHashSlots = 4096;
+constexpr uint32_t kHashEmpty = 0xFFFFFFFFu;
+constexpr int kSampleChunks = 4;           // chunks per thread in the cutoff sample: 4 * 256 * 8 = 8192 logits
+constexpr int kTopkMinVocab = 32768;
+
+struct TopkSmem {
+  unsigned long long key[kTopkCap];        // candidates as (monotone value key << 32) | ~index, arrival order; later the index-sort keys
+  unsigned long long sel[kTopkCap];        // those at or above the coarse top-k crossing, sorted: value descending, index ascending
+  union { double cum[kTopkCap]; unsigned long long w[kTopkCap]; };   // FP64 softmass prefix, then fixed-point weight prefix
+  uint32_t hs[kHashSlots];                 // the row's distinct history ids (open addressing)
+  uint32_t hitlist[2048];                  // (chunk << 8 | 8-bit mask) of the chunks that hold a logit >= cutoff
+  uint32_t bins[kTopkBins];                // candidates per BF16 code, relative to the cutoff code
+  uint64_t scratch[32];
+  double warp_d[kTW];
+  uint32_t warp_u[kTW];
+  float warp_f[kTW];
+  uint32_t n_hit, n, n_sel, wide, cross_bin;
+  int hit, token, row;
+};
+
+static_assert(3 * (sizeof(TopkSmem) + 1024) <= 233472, "three blocks of the top-k kernel must fit one SM's shared memory");
+
+#ifdef LM_PROFILE_PHASES
+#define LM_TPHASE(i) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == 0) { const long long _t = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(_t - _t0)); _t0 = _t; } } while (0)
+#else
+#define LM_TPHASE(i) do {} while (0)
+#endif
+
+__device__ __forceinline__ float ex2_approx(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ int next_pow2(int n) { int p = 32; while (p < n) p <<= 1; return p; }
+__device__ __forceinline__ uint32_t hash_id(uint32_t id) { return (id * 2654435761u) >> 20; }   // 12 bits
+
+// bitonic sort of a[0 .. n_pow2) in shared memory, descending; every thread of the block calls. One compare-exchange
+// per thread and step: thread t takes the t-th pair (i, i | j) with i's bit j clear.
+__device__ __forceinline__ void bitonic_desc(unsigned long long* a, int n_pow2) {
+  for (int k = 2; k <= n_pow2; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int t = threadIdx.x; t < (n_pow2 >> 1); t += blockDim.x) {
+        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+        const int partner = i | j;
+        const unsigned long long x = a[i], y = a[partner];
+        const bool desc = (i & k) == 0;
+        if (desc ? (x < y) : (x > y)) { a[i] = y; a[partner] = x; }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// Inclusive FP64 prefix sum over v[0 .. n) in place, index order; every thread calls. warp_d: one entry per warp.
+__device__ __forceinline__ void scan_f64(double* v, int n, double* warp_d) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+  double carry = 0.0;
+  for (int base = 0; base < n; base += blockDim.x) {
+    const int i = base + tid;
+    double x = (i < n) ? v[i] : 0.0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const double t = __shfl_up_sync(kFull, x, o); if (lane >= o) x += t; }
+    __syncthreads();
+    if (lane == 31) warp_d[warp] = x;
+    __syncthreads();
+    double wsum = 0.0, tot = 0.0;
+    for (int w = 0; w < nw; w++) { if (w < warp) wsum += warp_d[w]; tot += warp_d[w]; }
+    if (i < n) v[i] = carry + wsum + x;
+    carry += tot;
+  }
+  __syncthreads();
+}
+
+// Inclusive u64 prefix sum over v[0 .. n) in place, index order; every thread calls. Returns the total.
+__device__ __forceinline__ uint64_t scan_u64(unsigned long long* v, int n, uint64_t* scratch) {
+  uint64_t carry = 0ull;
+  for (int base = 0; base < n; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const uint64_t x = (i < n) ? v[i] : 0ull;
+    uint64_t tot = 0ull;
+    const uint64_t excl = block_exclusive_scan_u64(x, scratch, &tot);
+    if (i < n) v[i] = carry + excl + x;
+    carry += tot;
+    __syncthreads();
+  }
+  return carry;
+}
+
+// Warp-aggregated append: every lane of the warp calls with its count; returns the lane's first slot.
+__device__ __forceinline__ uint32_t warp_reserve(uint32_t* counter, uint32_t mine) {
+  const int lane = threadIdx.x & 31;
+  uint32_t incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
+  const uint32_t total = __shfl_sync(kFull, incl, 31);
+  uint32_t base = 0u;
+  if (lane == 0 && total) base = atomicAdd(counter, total);
+  base = __shfl_sync(kFull, base, 0);
+  return base + incl - mine;
+}
+
+__device__ __forceinline__ bool hash_contains(const uint32_t* hs, uint32_t id) {
+  uint32_t h = hash_id(id);
+  for (int probe = 0; probe < kHashSlots; probe++) {
+    const uint32_t v = hs[h];
+    if (v == id) return true;
+    if (v == kHashEmpty) return false;
+    h = (h + 1u) & (kHashSlots - 1u);
+  }
+  return false;
+}
+
+// One row. Every thread of the block calls with the same arguments; returns true when the row is finished, false when the
+// histogram kernel has to take it (nothing has been written then).
+__device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int V = P.vocab;
+  const float T = P.temperature ? P.temperature[row] : P.temperature_s;
+  const int top_k = P.top_k ? P.top_k[row] : P.top_k_s;
+  const float top_p = P.top_p ? P.top_p[row] : P.top_p_s;
+  const float min_p = P.min_p ? P.min_p[row] : P.min_p_s;
+  const uint16_t* rowp = reinterpret_cast<const uint16_t*>(P.logits) + static_cast<size_t>(row) * static_cast<size_t>(P.row_stride);
+  const bool pen_on = P.history != nullptr;
+  if (!(T > 0.0f) || top_k < 1 || top_k > kTopkMaxK || (V % kChunk) != 0 || V < kTopkMinVocab || V > (1 << 18) ||
+      (reinterpret_cast<uintptr_t>(rowp) & 15u) != 0 || (pen_on && P.hist_len > kTopkHist))
+    return false;
+  const int n_chunks = V / kChunk;
+  const uint4* p4 = reinterpret_cast<const uint4*>(rowp);
+  const bool has_p = top_p > 0.0f && top_p < 1.0f, has_m = min_p > 0.0f;
+  const bool in_topk = (P.flags & LM_FLAG_TOPP_IN_TOPK) && has_p;
+  const bool need_z = has_p && !in_topk;
+  const double T64 = static_cast<double>(T), inv_t = 1.0 / T64;
+  const float c2a = static_cast<float>(1.4426950408889634 * inv_t);          // the FP32 softmass only: approximate on purpose
+
+#ifdef LM_PROFILE_PHASES
+  long long _t0 = clock64();
+#endif
+  // ---- the cutoff sample goes out first; the hash set of the history's distinct ids is built under its latency ---------
+  // (four runs of 256 chunks at 0, 1/4, 1/2 and 3/4 of the row: token ids are not exchangeable in a real vocabulary)
+  uint4 qs[kSampleChunks];
+#pragma unroll
+  for (int j = 0; j < kSampleChunks; j++) qs[j] = __ldg(p4 + tid + j * (n_chunks / kSampleChunks));
+  for (int i = tid; i < kTopkBins; i += kTB) c.bins[i] = 0u;
+  for (int i = tid; i < kHashSlots; i += kTB) c.hs[i] = kHashEmpty;
+  if (tid == 0) { c.n_hit = 0u; c.n = 0u; c.n_sel = 0u; c.wide = 0u; c.hit = kTopkCap; c.token = -1; c.cross_bin = 0u; }
+  __syncthreads();
+  if (pen_on) {
+    const int32_t* h = P.history + static_cast<int64_t>(row) * P.hist_stride;
+    for (int i = tid; i < P.hist_len; i += kTB) {
+      const int id = __ldg(h + i);
+      if (id < 0 || id >= V) continue;
+      uint32_t slot = hash_id(static_cast<uint32_t>(id));
+      for (int probe = 0; probe < kHashSlots; probe++) {
+        const uint32_t old = atomicCAS(&c.hs[slot], kHashEmpty, static_cast<uint32_t>(id));
+        if (old == kHashEmpty || old == static_cast<uint32_t>(id)) break;
+        slot = (slot + 1u) & (kHashSlots - 1u);
+      }
+    }
+  }
+  // ---- the cutoff: the largest positive BF16 code with at least `want` of the 8192 sampled logits at or above it ---------
+  // (about 1.3 k + 150 candidates expected in the whole row, at most ~1500)
+  uint32_t cut_code;
+  {
+    const int n_target = min(1500, top_k + top_k / 3 + 150);
+    const uint32_t want = max(8u, static_cast<uint32_t>((static_cast<long long>(n_target) * kSampleChunks * kTB * kChunk + V - 1) / V));
+    uint32_t lo = 0x0000u, hi = 0x7F7Fu;                                    // invariant: count(sample >= lo) >= want, or lo is still 0 (handed back below)
+    for (int it = 0; it < 16; it++) {
+      const uint32_t mid = (lo + hi + 1u) >> 1;
+      const uint32_t m2 = mid | (mid << 16);
+      const __nv_bfloat162 t2 = *reinterpret_cast<const __nv_bfloat162*>(&m2);
+      uint32_t cnt = 0;
+#pragma unroll
+      for (int j = 0; j < kSampleChunks; j++) {
+        cnt += __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].x), t2)) + __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].y), t2)) +
+               __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].z), t2)) + __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].w), t2));
+      }
+      cnt >>= 4;                                                            // 16 mask bits per logit
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(kFull, cnt, o);
+      __syncthreads();
+      if (lane == 0) c.warp_u[warp] = cnt;
+      __syncthreads();
+      uint32_t total = 0;
+      for (int w = 0; w < kTW; w++) total += c.warp_u[w];
+      if (total >= want) lo = mid; else hi = mid - 1u;
+      if (lo >= hi) break;
+    }
+    cut_code = lo;
+    if (cut_code < 0x0080u) return false;                                   // fewer positive logits than candidates wanted: not this kernel's row
+  }
+  const float cut_val = __uint_as_float(cut_code << 16);
+  LM_TPHASE(8);
+
+  // ---- the one pass: note the chunks that hold a logit >= cutoff; FP32 softmass with a per-thread running maximum ---------
+  float m = -INFINITY, sacc0 = 0.0f, sacc1 = 0.0f;
+  uint32_t nan_seen = 0u;
+  {
+    const uint32_t cut2 = cut_code | (cut_code << 16);
+    const __nv_bfloat162 t2 = *reinterpret_cast<const __nv_bfloat162*>(&cut2);
+    constexpr int kUnroll = 4;
+    for (int base = 0; base < n_chunks; base += kTB * kUnroll) {            // uniform trip count: warp votes inside
+      const int c0 = base + tid;
+      uint4 q[kUnroll];
+#pragma unroll
+      for (int j = 0; j < kUnroll; j++) { const int cc = c0 + j * kTB; q[j] = (cc < n_chunks) ? __ldg(p4 + cc) : make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u); }
+#pragma unroll
+      for (int j = 0; j < kUnroll; j++) {
+        const int cc = c0 + j * kTB;
+        const bool live = cc < n_chunks;                                    // warp-uniform control flow below: votes inside
+        const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+        const uint32_t m0 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[0]), t2), m1 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[1]), t2);
+        const uint32_t m2 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[2]), t2), m3 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[3]), t2);
+        const bool hit = live && (m0 | m1 | m2 | m3) != 0u;
+        const uint32_t votes = __ballot_sync(kFull, hit);
+        if (votes) {                                                        // one reservation per warp for all its hit chunks
+          uint32_t base = 0u;
+          if (lane == 0) base = atomicAdd(&c.n_hit, __popc(votes));
+          base = __shfl_sync(kFull, base, 0);
+          if (hit) {
+            const uint32_t mask = (m0 & 1u) | ((m0 >> 15) & 2u) | ((m1 & 1u) << 2) | ((m1 >> 13) & 8u) | ((m2 & 1u) << 4) | ((m2 >> 11) & 32u) |
+                                  ((m3 & 1u) << 6) | ((m3 >> 9) & 128u);
+            const uint32_t slot = base + __popc(votes & ((1u << lane) - 1u));
+            if (slot < 2048u) c.hitlist[slot] = (static_cast<uint32_t>(cc) << 8) | mask;
+          }
+        }
+        const __nv_bfloat162 a = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[0]), *reinterpret_cast<const __nv_bfloat162*>(&w[1]));
+        const __nv_bfloat162 b = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[2]), *reinterpret_cast<const __nv_bfloat162*>(&w[3]));
+        const __nv_bfloat162 ab = __hmax2_nan(a, b);
+        nan_seen |= ~__heq2_mask(ab, ab);                                   // a NaN anywhere in the chunk survives the maxima
+        if (need_z && live) {
+          const float mx = fmaxf(__low2float(ab), __high2float(ab));
+          if (mx > m) { const float r = (m > -INFINITY) ? ex2_approx((m - mx) * c2a) : 0.0f; sacc0 *= r; sacc1 *= r; m = mx; }
+          if (m > -INFINITY) {
+            const float nb = -m * c2a;
+#pragma unroll
+            for (int k = 0; k < 4; k++) { sacc0 += ex2_approx(fmaf(bf16_lo(w[k]), c2a, nb)); sacc1 += ex2_approx(fmaf(bf16_hi(w[k]), c2a, nb)); }
+          }
+        }
+      }
+    }
+  }
+  LM_TPHASE(9);
+  // block maximum of the running maxima
+  float M = m;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(kFull, M, o));
+  if (lane == 0) c.warp_f[warp] = M;
+  __syncthreads();
+  M = c.warp_f[0];
+  for (int w = 1; w < kTW; w++) M = fmaxf(M, c.warp_f[w]);
+  double zsum = (need_z && m > -INFINITY) ? static_cast<double>((sacc0 + sacc1) * ex2_approx((m - M) * c2a)) : 0.0;
+  const uint32_t n_hit = c.n_hit;
+  if (__syncthreads_or(nan_seen != 0u) || n_hit > 2048u) return false;      // rows with a NaN go to the exact path, which reports them
+
+  // ---- the noted chunks, expanded: their logits come back from L2; penalised positions are skipped (the hash set knows them)
+  for (uint32_t e0 = 0; e0 < n_hit; e0 += kTB) {                            // uniform trip count
+    const uint32_t e = e0 + tid;
+    uint32_t ent = 0u, mask = 0u; uint4 q = make_uint4(0u, 0u, 0u, 0u);
+    if (e < n_hit) {
+      ent = c.hitlist[e];
+      q = __ldg(p4 + (ent >> 8));
+      mask = ent & 0xFFu;
+      if (pen_on) {
+#pragma unroll
+        for (int b = 0; b < kChunk; b++) if (((mask >> b) & 1u) && hash_contains(c.hs, (ent >> 8) * kChunk + b)) mask &= ~(1u << b);
+      }
+    }
+    uint32_t slot = warp_reserve(&c.n, __popc(mask));
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int b = 0; b < kChunk; b++) {
+      if ((mask >> b) & 1u) {
+        const float value = (b & 1) ? bf16_hi(w[b >> 1]) : bf16_lo(w[b >> 1]);
+        if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(value)) << 32) | (0xFFFFFFFFu - ((ent >> 8) * kChunk + b));
+        slot++;
+        const uint32_t rel = (__float_as_uint(value) >> 16) - cut_code;
+        if (rel >= kTopkBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
+      }
+    }
+  }
+  // ---- the penalised logits: every occupied slot of the hash set is one distinct id ----------------------------------------
+  if (pen_on) {
+    for (int s0 = 0; s0 < kHashSlots; s0 += kTB) {                          // uniform trip count
+      const uint32_t id = c.hs[s0 + tid];
+      float v = -INFINITY;
+      if (id != kHashEmpty) {
+        const float raw = __uint_as_float(static_cast<uint32_t>(__ldg(rowp + id)) << 16);
+        v = penalise(raw, P.rho, P.pi);
+        if (need_z) zsum += static_cast<double>(ex2_approx((v - M) * c2a)) - static_cast<double>(ex2_approx((raw - M) * c2a));
+      }
+      const bool cand = v >= cut_val;
+      const uint32_t slot = warp_reserve(&c.n, cand ? 1u : 0u);
+      if (cand) {
+        if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(v)) << 32) | (0xFFFFFFFFu - id);
+        const uint32_t rel = (__float_as_uint(v) >> 16) - cut_code;
+        if (rel >= kTopkBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
+      }
+    }
+  }
+  const double z_tilde = need_z ? block_sum_f64(zsum, c.scratch) : 0.0;     // relative to M
+  __syncthreads();
+  const int n = static_cast<int>(c.n);
+  if (n > kTopkCap || n < top_k || c.wide) return false;
+
+  LM_TPHASE(10);
+  // ---- the coarse top-k crossing: the highest code bin b with at least top_k candidates in bins >= b ---------------------
+  {
+    uint32_t run = 0u;                                                       // 512 bins, 2 per thread, walked from the top
+    const uint32_t c_hi = c.bins[kTopkBins - 1 - 2 * tid], c_lo = c.bins[kTopkBins - 2 - 2 * tid];
+    uint32_t incl = c_hi + c_lo;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
+    if (lane == 31) c.warp_u[warp] = incl;
+    __syncthreads();
+    for (int w = 0; w < warp; w++) run += c.warp_u[w];
+    incl += run;
+    const uint32_t excl = incl - c_hi - c_lo;
+    if (excl + c_hi >= static_cast<uint32_t>(top_k)) atomicMin(&c.hit, 2 * tid); else if (incl >= static_cast<uint32_t>(top_k)) atomicMin(&c.hit, 2 * tid + 1);
+    __syncthreads();
+    if (tid == 0) { c.cross_bin = static_cast<uint32_t>(kTopkBins - 1 - c.hit); c.hit = kTopkCap; }
+    __syncthreads();
+  }
+  const uint32_t cross = c.cross_bin;
+  for (int i0 = 0; i0 < n; i0 += kTB) {                                     // uniform trip count
+    const int i = i0 + tid;
+    unsigned long long k = 0ull; bool take = false;
+    if (i < n) {
+      k = c.key[i];
+      take = (__float_as_uint(fkey_inv(static_cast<uint32_t>(k >> 32))) >> 16) - cut_code >= cross;
+    }
+    const uint32_t slot = warp_reserve(&c.n_sel, take ? 1u : 0u);
+    if (take) c.sel[slot] = k;
+  }
+  __syncthreads();
+  const int n_sel = static_cast<int>(c.n_sel);
+  const int p2 = next_pow2(n_sel);
+  for (int i = n_sel + tid; i < p2; i += kTB) c.sel[i] = 0ull;
+  __syncthreads();
+  LM_TPHASE(11);
+  bitonic_desc(c.sel, p2);
+  LM_TPHASE(12);
+
+  // ---- exact thresholds on the sorted candidates ------------------------------------------------------------------------
+  const float vmax = fkey_inv(static_cast<uint32_t>(c.sel[0] >> 32));
+  const float tau_k = fkey_inv(static_cast<uint32_t>(c.sel[top_k - 1] >> 32));
+  double tau64 = tau_k;
+  uint32_t status = LM_STATUS_CANDIDATE_PATH;
+  if (has_p) {
+    for (int i = tid; i < n_sel; i += kTB) c.cum[i] = softmass(fkey_inv(static_cast<uint32_t>(c.sel[i] >> 32)), vmax, inv_t);
+    __syncthreads();
+    scan_f64(c.cum, n_sel, c.warp_d);
+    uint64_t cnt_k = 0ull;
+    for (int i = tid; i < n_sel; i += kTB) cnt_k += fkey_inv(static_cast<uint32_t>(c.sel[i] >> 32)) >= tau_k ? 1ull : 0ull;
+    const int n_topk = static_cast<int>(block_sum_u64(cnt_k, c.scratch));
+    double total, err = 0.0;
+    if (in_topk) total = c.cum[n_topk - 1];
+    else {                                                                 // the FP32 mass of the whole row, moved to the exact maximum
+      total = z_tilde * exp2((static_cast<double>(M) - static_cast<double>(vmax)) * 1.4426950408889634 * inv_t);
+      err = 2e-6 * total;
+    }
+    const double target = static_cast<double>(top_p) * total;
+    bool amb = false;
+    for (int i = tid; i < n_sel; i += kTB) {
+      const bool run_end = (i == n_sel - 1) || ((c.sel[i + 1] >> 32) != (c.sel[i] >> 32));
+      if (!run_end) continue;
+      const double cm = c.cum[i];
+      if (cm >= target) atomicMin(&c.hit, i);
+      if (i < n_topk - 1 && fabs(cm - target) <= err && fkey_inv(static_cast<uint32_t>(c.sel[i] >> 32)) > tau_k) amb = true;
+    }
+    if (__syncthreads_or(amb)) return false;                               // too close to call in FP32: the exact path decides
+    if (c.hit < kTopkCap) {
+      const float tau_p = fkey_inv(static_cast<uint32_t>(c.sel[c.hit] >> 32));
+      if (static_cast<double>(tau_p) > tau64) tau64 = tau_p;
+      if (fabs(c.cum[c.hit] - target) <= 1e-12 * total) status |= LM_STATUS_TOPP_EDGE;
+    }
+  }
+  if (has_m) {
+    const double tau_m = static_cast<double>(vmax) + T64 * log(static_cast<double>(min_p));
+    if (tau_m > tau64) tau64 = tau_m;
+  }
+  const float tau = __double2float_rn(tau64);
+  uint64_t cnt_kept = 0ull;
+  for (int i = tid; i < n_sel; i += kTB) cnt_kept += fkey_inv(static_cast<uint32_t>(c.sel[i] >> 32)) >= tau ? 1ull : 0ull;
+  const int n_kept = static_cast<int>(block_sum_u64(cnt_kept, c.scratch));   // the kept set is the first n_kept sorted candidates
+
+  LM_TPHASE(13);
+  // ---- the draw ----------------------------------------------------------------------------------------------------------
+  int token = -1;
+  if (P.draw == LM_DRAW_INVERSE_CDF) {
+    const float c2 = exp2_scale(T);
+    const int q2 = next_pow2(n_kept);
+    // order the kept candidates by index: keys (~index << 32 | position), descending = index ascending
+    for (int i = tid; i < q2; i += kTB)
+      c.key[i] = (i < n_kept) ? ((c.sel[i] & 0xFFFFFFFFull) << 32) | static_cast<unsigned long long>(i) : 0ull;
+    __syncthreads();
+    bitonic_desc(c.key, q2);
+    for (int i = tid; i < n_kept; i += kTB) {
+      const unsigned long long k = c.sel[static_cast<uint32_t>(c.key[i])];
+      c.w[i] = weight_q40(fkey_inv(static_cast<uint32_t>(k >> 32)), vmax, c2);
+    }
+    __syncthreads();
+    const uint64_t total = scan_u64(c.w, n_kept, c.scratch);
+    if (total > 0ull) {
+      const uint64_t target = cdf_target(P.uniforms ? P.uniforms[row] : 0.0f, total);
+      for (int i = tid; i < n_kept; i += kTB) {
+        const uint64_t incl = c.w[i], before = i ? c.w[i - 1] : 0ull;
+        if (before <= target && target < incl) c.token = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(c.key[i] >> 32));
+      }
+    }
+    __syncthreads();
+    token = c.token;
+  } else {
+    const float inv_t32 = __double2float_rn(1.0 / T64);
+    const uint32_t t_id = static_cast<uint32_t>(P.row_offset + row);
+    uint64_t b1 = 0ull; float second = -INFINITY;
+    for (int i = tid; i < n_kept; i += kTB) {
+      const unsigned long long k = c.sel[i];
+      const uint32_t idx = 0xFFFFFFFFu - static_cast<uint32_t>(k);
+      const float key = __fadd_rn(__fmul_rn(fkey_inv(static_cast<uint32_t>(k >> 32)), inv_t32), gumbel(P.seed, P.step, t_id, idx));
+      const uint64_t pk = pack_best(key, idx);
+      if (pk > b1) { if (b1) second = fmaxf(second, best_value(b1)); b1 = pk; } else second = fmaxf(second, key);
+    }
+    const uint64_t win = block_max_u64(b1, c.scratch);
+    if (win) {
+      const float rival = (b1 == win) ? second : (b1 ? best_value(b1) : -INFINITY);
+      if (__syncthreads_or(rival >= best_value(win) - 4e-6f)) status |= LM_STATUS_NEAR_TIE;
+      token = static_cast<int>(best_index(win));
+    }
+  }
+  LM_TPHASE(14);
+  if (tid == 0) {
+    P.out_tokens[row] = token;
+    if (P.out_tau) P.out_tau[row] = tau;
+    if (P.out_status) P.out_status[row] = status;
+  }
+  __syncthreads();
+  return true;
+}
+
+// Rows are handed out through a counter in the workspace (counters[0], zeroed by the host before the launch): a block takes
+// the next row and either finishes it (punt[row] = 0: no later kernel touches it) or appends it to `list` (length in
+// counters[1]) for the histogram kernel. The order of the list varies from run to run; what is computed per row does not.
+__global__ void __launch_bounds__(kTB, 3) sample_topk_kernel(SampleDev P, uint32_t* punt, int* list, int* counters) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  TopkSmem& c = *reinterpret_cast<TopkSmem*>(smem_raw);
+  for (;;) {
+    __syncthreads();
+    if (threadIdx.x == 0) c.row = atomicAdd(&counters[0], 1);
+    __syncthreads();
+    const int row = c.row;
+    if (row >= P.rows) break;
+    const bool done = topk_row(P, row, c);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (done) punt[row] = 0u; else list[atomicAdd(&counters[1], 1)] = row;
+    }
+  }
+}
+
+}  // namespace lm

@@ -33,6 +33,7 @@ class SamplingParams:
     repetition_penalty: float = 1.0
     presence_penalty: float = 0.0
     draw: str = "gumbel"               # "gumbel" (the reference's counter-based Gumbel-max) or "inverse_cdf" (injected uniforms)
+    exact_only: bool = False           # skip the candidate kernel for rows with a top_k (same results; for cross-checks)
     grid_limit: int = 0                # at most this many thread blocks (0 = one per SM); leaves SMs free for other streams
 
 
@@ -122,7 +123,7 @@ def sample(logits: torch.Tensor, params: Optional[SamplingParams] = None, *, his
     ptr, s, t = _knob(p.top_k, rows, torch.int32, dev, "top_k"); a.top_k, a.top_k_s = ptr, int(s); keep.append(t)
     ptr, s, t = _knob(p.top_p, rows, torch.float32, dev, "top_p"); a.top_p, a.top_p_s = ptr, float(s); keep.append(t)
     ptr, s, t = _knob(p.min_p, rows, torch.float32, dev, "min_p"); a.min_p, a.min_p_s = ptr, float(s); keep.append(t)
-    a.flags = (_lib.FLAG_TOPP_IN_TOPK if p.topp_in_topk else 0) | ((int(p.grid_limit) & 0xFF) << 8)
+    a.flags = (_lib.FLAG_TOPP_IN_TOPK if p.topp_in_topk else 0) | (_lib.FLAG_EXACT_ONLY if p.exact_only else 0) | ((int(p.grid_limit) & 0xFF) << 8)
     a.draw = _lib.DRAW_GUMBEL if p.draw == "gumbel" else _lib.DRAW_INVERSE_CDF
     if history is not None:
         if history.dim() != 2 or history.shape[0] != rows:

@@ -257,28 +257,35 @@ def test_streaming_path_with_dense_side_values():
 
 @pytest.mark.parametrize("draw", ["inverse_cdf", "gumbel"])
 def test_candidate_path_equals_the_oracle(draw):
-    """Rows with a small top_k take the one-pass candidate path once their block has a cutoff from an earlier row: force
-    several rows per block (grid_limit) and check those rows against the CPU oracle like any other."""
+    """Rows with 1 <= top_k <= 1024 take the one-pass candidate kernel (several rows per block here: grid_limit); check them
+    against the CPU oracle like any other, and against the histogram path alone (exact_only)."""
     rows = 36
     cfg = inputs.config3(rows=rows, seed=91)
     cfg["top_k"][:] = np.array([20, 50, 1000, 1, 7, 333], np.int32)[np.arange(rows) % 6]
     cfg["temperature"][3] = 0.05                                            # nearly greedy: the top-p boundary falls inside the top-k set
     cfg["temperature"][10] = 0.11
+    z30 = oracle.bf16_to_f32(cfg["logits"][30]) - np.float32(20.0)          # no positive logit: the kernel hands the row back
+    cfg["logits"][30] = oracle.f32_to_bf16(z30)
     x = bf16_tensor(cfg["logits"])
     knobs = {k: torch.from_numpy(cfg[k]).cuda() for k in ("temperature", "top_k", "top_p")}
     hist, u = torch.from_numpy(cfg["history"]).cuda(), torch.from_numpy(cfg["uniforms"]).cuda()
+    with_nan = x.clone()
+    with_nan[4, 77777] = float("nan")                                       # a NaN row is reported by the exact path, not decided here
+    st = lm.sample(with_nan, lm.SamplingParams(seed=5, draw=draw, **knobs), uniforms=u, return_status=True).status.cpu().numpy()
+    assert (st[4] & 2) and not (st[4] & 64) and not np.any(np.delete(st, 4) & 2)
     for extra in (dict(), dict(min_p=0.05), dict(topp_in_topk=True)):
         p = lm.SamplingParams(seed=5, draw=draw, repetition_penalty=1.1, presence_penalty=0.5, grid_limit=3, **knobs, **extra)
         r = lm.sample(x, p, history=hist, uniforms=u, step=2, return_tau=True, return_status=True)
         status = r.status.cpu().numpy()
-        assert np.count_nonzero(status & 64) >= rows - 8, status           # all but each block's first row (and the odd hand-back)
+        assert np.count_nonzero(status & 64) >= rows - 5 and not (status[30] & 64), status   # all but row 30 and the odd hand-back
         tok, tau, _ = oracle.sample_batch(cfg["logits"], temperature=cfg["temperature"], top_k=cfg["top_k"], top_p=cfg["top_p"], history=cfg["history"],
                                           repetition_penalty=1.1, presence_penalty=0.5, draw=draw, uniforms=cfg["uniforms"], seed=5, step=2, n_threads=8,
                                           **{k: v for k, v in extra.items()})
         np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
         got = r.tokens.cpu().numpy()
         assert np.all((got == tok) | ((status & 4) != 0)), (extra, np.nonzero(got != tok))
-        # and the same rows through the histogram path alone (one row per block): identical
-        q = lm.SamplingParams(seed=5, draw=draw, repetition_penalty=1.1, presence_penalty=0.5, **knobs, **extra)
-        h = lm.sample(x, q, history=hist, uniforms=u, step=2, return_tau=True)
+        # and the same rows through the histogram path alone: identical
+        q = lm.SamplingParams(seed=5, draw=draw, repetition_penalty=1.1, presence_penalty=0.5, exact_only=True, **knobs, **extra)
+        h = lm.sample(x, q, history=hist, uniforms=u, step=2, return_tau=True, return_status=True)
+        assert not np.any(h.status.cpu().numpy() & 64)
         assert torch.equal(h.tau, r.tau) and torch.equal(h.tokens, r.tokens)
