@@ -68,17 +68,23 @@ __global__ void __launch_bounds__(kBlock, 1) sample_generic_kernel(SampleDev P) 
   }
 }
 
-// ---- the streaming BF16 sampler: one block per SM. With a row list (written by the top-k kernel: the rows it left), block b
-// takes entries b, b + gridDim.x, ... of it; without one, rows b, b + gridDim.x, ... ------------------------------------------
-__global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, uint32_t* punt, const int* list, const int* n_list) {
+// ---- the streaming BF16 sampler: one block per SM. Rows cost very different amounts (the draw scales with the kept set), so
+// blocks take them from a counter (`next_item`, zeroed by the host) instead of a fixed stride; a block always holds the item
+// after its current one too, so that it can pull that row into L2 while it works. With a row list (written by the
+// top-k kernel: the rows it left) the items are entries of the list, without one they are the rows themselves.
+__global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, uint32_t* punt, const int* list, const int* n_list, int* next_item) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   FastSmem& s = *reinterpret_cast<FastSmem*>(smem_raw);
+  __shared__ int item[2];
   const int n = list ? *n_list : P.rows;
-  for (int i = blockIdx.x; i < n; i += gridDim.x) {
-    const int row = list ? list[i] : i;
-    const int in = i + static_cast<int>(gridDim.x);
-    const int next = in < n ? (list ? list[in] : in) : -1;
-    sample_row_fast(P, row, next, s, punt);
+  if (threadIdx.x == 0) { item[0] = atomicAdd(next_item, 1); item[1] = item[0] < n ? atomicAdd(next_item, 1) : n; }
+  __syncthreads();
+  for (;;) {
+    const int i = item[0], in = item[1];
+    if (i >= n) break;
+    __syncthreads();
+    if (threadIdx.x == 0) { item[0] = in; item[1] = in < n ? atomicAdd(next_item, 1) : n; }
+    sample_row_fast(P, list ? list[i] : i, in < n ? (list ? list[in] : in) : -1, s, punt);
     __syncthreads();
   }
 }
@@ -153,7 +159,7 @@ float lm_uniform01(uint64_t seed, uint32_t step, uint32_t t, uint32_t index) { r
 size_t lm_workspace_bytes(int64_t rows, int64_t vocab) {
   (void)vocab;
   if (rows < 0) rows = 0;
-  // argmax partials | rows left to the generic kernel | rows left to the histogram kernel | two counters
+  // argmax partials | rows left to the generic kernel | rows left to the histogram kernel | three counters
   return align256(static_cast<size_t>(rows) * sizeof(ArgmaxWs)) + 2 * align256(static_cast<size_t>(rows) * sizeof(uint32_t)) + 256;
 }
 
@@ -278,18 +284,20 @@ int lm_sample(const lm_sample_args* a) {
     // rows with a top_k go through the candidate kernel first (three small blocks per SM); it lists the rows it leaves
     const bool topk = !(a->flags & LM_FLAG_EXACT_ONLY) && a->vocab >= kTopkMinVocab && (a->top_k != nullptr || (a->top_k_s >= 1 && a->top_k_s <= kTopkMaxK)) &&
                       (a->temperature != nullptr || a->temperature_s > 0.0f) && (!pen || a->hist_len <= kTopkHist);
-    if (topk) {
-      cudaError_t e = cudaMemsetAsync(counters, 0, 2 * sizeof(int), st);
+    {
+      const cudaError_t e = cudaMemsetAsync(counters, 0, 3 * sizeof(int), st);   // next row of the top-k kernel, length of its list, next item of the histogram kernel
       if (e != cudaSuccess) return cuda_fail(e);
+    }
+    if (topk) {
       int grid1 = static_cast<int>(a->rows < 3LL * sms ? a->rows : 3LL * sms);
       if (limit > 0 && grid1 > limit) grid1 = limit;
       sample_topk_kernel<<<grid1, kTB, sizeof(TopkSmem), st>>>(P, punt, list, counters);
-      e = cudaGetLastError();
+      const cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return cuda_fail(e);
     }
     int grid = static_cast<int>(a->rows < sms ? a->rows : sms);
     if (limit > 0 && grid > limit) grid = limit;
-    sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, punt, topk ? list : nullptr, topk ? counters + 1 : nullptr);
+    sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, punt, topk ? list : nullptr, topk ? counters + 1 : nullptr, counters + 2);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e);
     P.row_select = punt;

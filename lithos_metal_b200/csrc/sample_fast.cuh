@@ -10,7 +10,7 @@
 // The draw then takes a second pass that finds the row in L2 (the next row is prefetched into L2 meanwhile).
 //
 // Rows this kernel cannot take (a counter overflow: more than 65535 equal logits; more than kSideCap penalised
-// logits, or more than kLaneSideCap of them next to a threshold; vocabularies that are not a multiple of 8 or exceed
+// logits, or more than kSidePool of them in the 256 codes around a threshold; vocabularies that are not a multiple of 8 or exceed
 // kFastMaxVocab; misaligned rows) are marked in `punt` and handled by the generic kernel launched behind this one.
 #pragma once
 #include "common.cuh"
@@ -31,7 +31,7 @@ constexpr int kCodes = 65536;
 constexpr int kGroupBins = 256;             // positions per group: one 512-byte block of counters = one uint4 per lane
 constexpr int kGroups = kCodes / kGroupBins;
 constexpr int kSideCap = 4096;              // penalised logits per row the kernel keeps aside
-constexpr int kLaneSideCap = 48;            // of those, how many may fall into one lane's 8 bins of the group being refined
+constexpr int kSidePool = 1536;              // of those, how many may fall into the group being refined
 
 struct FastSmem {
   uint32_t hist[kCodes / 2];                // 128 KB: 16-bit counters, code c in half (c & 1) of word c >> 1
@@ -39,9 +39,9 @@ struct FastSmem {
   int side_idx[kSideCap];                   // 16 KB: ... and their vocabulary indices
   union {                                   // the threshold walk and the draw never run at the same time
     struct {
-      double lane_side_mass[32][kLaneSideCap];  // 12 KB: softmass of the side values of the group being refined, by owning lane
+      double pool_mass[kSidePool];              // 12 KB: softmass of the side values of the group being refined, sorted by owning lane
       double lane_bin_mass[32][8];              // 2 KB: softmass of each lane's eight bins
-      float lane_side[32][kLaneSideCap];        // 6 KB: the side values themselves
+      float pool_val[kSidePool];                // 6 KB: the side values themselves; lane L owns [lane_off[L], lane_off[L + 1])
     };
     struct {
       uint64_t sweep_part[kFastMaxVocab / (kBlock * kChunk)][32];   // 8 KB: per-warp fixed-point mass of every sweep of the draw
@@ -53,6 +53,9 @@ struct FastSmem {
   uint32_t goff[kGroups + 1];               // side list sorted by group: group g holds entries [goff[g], goff[g + 1])
   uint32_t gfill[kGroups];
   uint32_t lane_side_n[32];
+  uint32_t lane_off[33];
+  uint32_t lane_fill[32];
+  uint32_t sel_cnt[8];
   DrawSmem draw;
   double warp_m[32];
   uint32_t warp_c[32];
@@ -114,23 +117,34 @@ __device__ __forceinline__ uint32_t sum8(const uint4 v) {
 // count reaches k_target (BY_MASS false) or the running mass reaches m_target (BY_MASS true), starting from
 // (base_c, base_m) = totals strictly above the group. Lane L of warp 0 owns positions 8L..8L+7 of the group and
 // the side values whose bin lies there; the masses are computed by all warps first (warp w for owner lane w) so
-// that no thread runs a long chain of FP64 exponentials. Results in s.res_*; s.res_fail = 1 if too many side
-// values crowd one lane's bins.
+// that no thread runs a long chain of FP64 exponentials. Results in s.res_*; s.res_fail = 1 if the group holds more
+// side values than the pool.
 template <bool BY_MASS, bool NEED_MASS>
 __device__ void refine_group(FastSmem& s, int group, uint32_t base_c, double base_m, uint32_t k_target, double m_target, float vmax, double inv_t) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid < 32) s.lane_side_n[tid] = 0u;
+  if (tid < 32) { s.lane_side_n[tid] = 0u; s.lane_fill[tid] = 0u; }
   if (tid == 0) s.res_fail = 0;
   __syncthreads();
   const uint32_t s0 = s.goff[group], s1 = s.goff[group + 1];               // this group's side values (the list is sorted by group)
+  if (s1 - s0 > static_cast<uint32_t>(kSidePool)) { if (tid == 0) s.res_fail = 1; __syncthreads(); return; }
+  for (uint32_t i = s0 + tid; i < s1; i += kBlock)                         // counting sort by owning lane: count, offsets, fill
+    atomicAdd(&s.lane_side_n[(code_to_pos(floor_code(s.side_val[i])) % kGroupBins) >> 3], 1u);
+  __syncthreads();
+  if (tid < 32) {
+    const uint32_t n = s.lane_side_n[tid];
+    uint32_t incl = n;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
+    s.lane_off[tid] = incl - n;
+    if (tid == 31) s.lane_off[32] = incl;
+  }
+  __syncthreads();
   for (uint32_t i = s0 + tid; i < s1; i += kBlock) {
     const float v = s.side_val[i];
     const uint32_t owner = (code_to_pos(floor_code(v)) % kGroupBins) >> 3;
-    const uint32_t slot = atomicAdd(&s.lane_side_n[owner], 1u);
-    if (slot < kLaneSideCap) s.lane_side[owner][slot] = v; else s.res_fail = 1;
+    s.pool_val[s.lane_off[owner] + atomicAdd(&s.lane_fill[owner], 1u)] = v;
   }
   __syncthreads();
-  if (s.res_fail) return;
   if (NEED_MASS) {                                                         // a warp per owner lane: the masses of its bins and side values
     for (int o = warp; o < 32; o += kWarps) {
       const uint32_t pos0 = static_cast<uint32_t>(group) * kGroupBins + o * 8u;
@@ -139,7 +153,7 @@ __device__ void refine_group(FastSmem& s, int group, uint32_t base_c, double bas
         const uint32_t c = hist_get(s.hist, code);
         s.lane_bin_mass[o][lane] = c ? static_cast<double>(c) * softmass(code_val(code), vmax, inv_t) : 0.0;
       } else {
-        for (uint32_t i = lane - 8; i < s.lane_side_n[o]; i += 24) s.lane_side_mass[o][i] = softmass(s.lane_side[o][i], vmax, inv_t);
+        for (uint32_t i = s.lane_off[o] + lane - 8; i < s.lane_off[o + 1]; i += 24) s.pool_mass[i] = softmass(s.pool_val[i], vmax, inv_t);
       }
     }
     __syncthreads();
@@ -148,9 +162,7 @@ __device__ void refine_group(FastSmem& s, int group, uint32_t base_c, double bas
     uint32_t cnt[8];
     lane_counts(s.hist, group, lane, cnt);
     const uint32_t m_side = s.lane_side_n[lane];
-    const float* sv = s.lane_side[lane];
-    const double* sm = s.lane_side_mass[lane];
-    const uint32_t pos0 = static_cast<uint32_t>(group) * kGroupBins + lane * 8u;
+    const double* sm = s.pool_mass + s.lane_off[lane];
     uint32_t c_lane = m_side; double m_lane = 0.0;
 #pragma unroll
     for (int j = 0; j < 8; j++) { c_lane += cnt[j]; if (NEED_MASS) m_lane += s.lane_bin_mass[lane][j]; }
@@ -166,25 +178,47 @@ __device__ void refine_group(FastSmem& s, int group, uint32_t base_c, double bas
     const uint32_t hits = __ballot_sync(kFull, hit);
     const uint32_t occ = __ballot_sync(kFull, c_lane > 0);
     const int sel = hits ? (__ffs(hits) - 1) : (31 - __clz(occ));        // mass never reached (rounding): the lowest occupied lane
+    // The selected lane's distinct values, descending: its eight BF16 bins (pure counts) and its side values. The warp ranks
+    // them together: lane l takes items l, l + 32, ... and sums, over all items, those at or above its own value; the
+    // answer is the largest value whose inclusive total reaches the target (or, if rounding left it unreached, the smallest).
     if (lane == sel) {
-      // this lane's distinct values, descending: BF16 bin values (pure counts) merged with its side values
-      uint32_t run_c = base_c + ci - c_lane; double run_m = base_m + mi - m_lane;
-      float tau = 0.0f, prev = INFINITY; bool done = false;
-      double above_m = run_m;
-      for (int step = 0; step < 8 + kLaneSideCap && !done; step++) {
-        above_m = run_m;
-        float best = -INFINITY; bool any = false;                        // the next distinct value below `prev`
 #pragma unroll
-        for (int j = 0; j < 8; j++) { const float b = code_val(pos_to_code(pos0 + j)); if (cnt[j] && b < prev && (!any || b > best)) { best = b; any = true; } }
-        for (uint32_t i = 0; i < m_side; i++) { const float v = sv[i]; if (v < prev && (!any || v > best)) { best = v; any = true; } }
-        if (!any) break;
-#pragma unroll
-        for (int j = 0; j < 8; j++) if (cnt[j] && code_val(pos_to_code(pos0 + j)) == best) { run_c += cnt[j]; if (NEED_MASS) run_m += s.lane_bin_mass[lane][j]; }
-        for (uint32_t i = 0; i < m_side; i++) if (sv[i] == best) { run_c += 1u; if (NEED_MASS) run_m += sm[i]; }
-        tau = best; prev = best;
-        if (BY_MASS ? (run_m >= m_target) : (run_c >= k_target)) done = true;
+      for (int j = 0; j < 8; j++) s.sel_cnt[j] = cnt[j];
+    }
+    __syncwarp();
+    const uint32_t n_side_sel = __shfl_sync(kFull, m_side, sel);
+    const uint32_t top_c = __shfl_sync(kFull, base_c + ci - c_lane, sel);
+    const double top_m = __shfl_sync(kFull, base_m + mi - m_lane, sel);
+    const float* ssv = s.pool_val + s.lane_off[sel];
+    const double* ssm = s.pool_mass + s.lane_off[sel];
+    const uint32_t spos0 = static_cast<uint32_t>(group) * kGroupBins + static_cast<uint32_t>(sel) * 8u;
+    const uint32_t n_items = 8u + n_side_sel;
+    uint32_t best_key = 0u, low_key = 0xFFFFFFFFu;                          // best: largest qualifying value; low: smallest value present
+    uint32_t best_c = 0u, low_c = 0u; double best_m = 0.0, best_above = 0.0, low_m = 0.0, low_above = 0.0;
+    for (uint32_t i = lane; i < n_items; i += 32) {
+      const float v = i < 8u ? code_val(pos_to_code(spos0 + i)) : ssv[i - 8u];
+      if (i < 8u && s.sel_cnt[i] == 0u) continue;
+      uint32_t inc_c = top_c; double inc_m = top_m, abv_m = top_m;
+      for (uint32_t t = 0; t < n_items; t++) {
+        const float vt = t < 8u ? code_val(pos_to_code(spos0 + t)) : ssv[t - 8u];
+        const uint32_t ct = t < 8u ? s.sel_cnt[t] : 1u;
+        if (ct == 0u || vt < v) continue;
+        const double mt = NEED_MASS ? (t < 8u ? s.lane_bin_mass[sel][t] : ssm[t - 8u]) : 0.0;
+        inc_c += ct; inc_m += mt;
+        if (vt > v) abv_m += mt;
       }
-      s.res_tau = tau; s.res_cum_c = run_c; s.res_cum_m = run_m; s.res_above_m = above_m;   // not done: rounding left the target unreached; the last value stands
+      const uint32_t key = fkey(v);
+      if ((BY_MASS ? (inc_m >= m_target) : (inc_c >= k_target)) && key > best_key) { best_key = key; best_c = inc_c; best_m = inc_m; best_above = abv_m; }
+      if (key < low_key) { low_key = key; low_c = inc_c; low_m = inc_m; low_above = abv_m; }
+    }
+    uint32_t win = best_key, lowest = low_key;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { win = max(win, __shfl_xor_sync(kFull, win, o)); lowest = min(lowest, __shfl_xor_sync(kFull, lowest, o)); }
+    const bool mine = win ? (best_key == win) : (low_key == lowest);
+    const uint32_t owners = __ballot_sync(kFull, mine);
+    if (lane == __ffs(owners) - 1) {                                        // equal values carry equal totals: any owner will do
+      s.res_tau = fkey_inv(win ? win : lowest);
+      s.res_cum_c = win ? best_c : low_c; s.res_cum_m = win ? best_m : low_m; s.res_above_m = win ? best_above : low_above;
     }
   }
   __syncthreads();

@@ -28,6 +28,7 @@ constexpr int kHashSlots = 4096;
 constexpr uint32_t kHashEmpty = 0xFFFFFFFFu;
 constexpr int kSampleChunks = 4;           // chunks per thread in the cutoff sample: 4 * 256 * 8 = 8192 logits
 constexpr int kTopkMinVocab = 32768;
+constexpr int kIdxBuckets = 1024;          // the draw buckets candidates by index >> 8: vocabularies up to 2^18
 
 struct TopkSmem {
   unsigned long long key[kTopkCap];        // candidates as (monotone value key << 32) | ~index, arrival order; later the index-sort keys
@@ -40,7 +41,8 @@ struct TopkSmem {
   double warp_d[kTW];
   uint32_t warp_u[kTW];
   float warp_f[kTW];
-  uint32_t n_hit, n, n_sel, wide, cross_bin;
+  unsigned long long base;
+  uint32_t n_hit, n, n_sel, n_on, wide, cross_bin;
   int hit, token, row;
 };
 
@@ -162,14 +164,20 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
   uint4 qs[kSampleChunks];
 #pragma unroll
   for (int j = 0; j < kSampleChunks; j++) qs[j] = __ldg(p4 + tid + j * (n_chunks / kSampleChunks));
+  int hid[kTopkHist / kTB];                                                 // this thread's share of the history, in flight with the sample
+#pragma unroll
+  for (int j = 0; j < kTopkHist / kTB; j++) {
+    const int i = tid + j * kTB;
+    hid[j] = (pen_on && i < P.hist_len) ? __ldg(P.history + static_cast<int64_t>(row) * P.hist_stride + i) : -1;
+  }
   for (int i = tid; i < kTopkBins; i += kTB) c.bins[i] = 0u;
   for (int i = tid; i < kHashSlots; i += kTB) c.hs[i] = kHashEmpty;
-  if (tid == 0) { c.n_hit = 0u; c.n = 0u; c.n_sel = 0u; c.wide = 0u; c.hit = kTopkCap; c.token = -1; c.cross_bin = 0u; }
+  if (tid == 0) { c.n_hit = 0u; c.n = 0u; c.n_sel = 0u; c.n_on = 0u; c.wide = 0u; c.hit = kTopkCap; c.token = -1; c.cross_bin = 0u; }
   __syncthreads();
   if (pen_on) {
-    const int32_t* h = P.history + static_cast<int64_t>(row) * P.hist_stride;
-    for (int i = tid; i < P.hist_len; i += kTB) {
-      const int id = __ldg(h + i);
+#pragma unroll
+    for (int j = 0; j < kTopkHist / kTB; j++) {
+      const int id = hid[j];
       if (id < 0 || id >= V) continue;
       uint32_t slot = hash_id(static_cast<uint32_t>(id));
       for (int probe = 0; probe < kHashSlots; probe++) {
@@ -275,47 +283,65 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
   if (__syncthreads_or(nan_seen != 0u) || n_hit > 2048u) return false;      // rows with a NaN go to the exact path, which reports them
 
   // ---- the noted chunks, expanded: their logits come back from L2; penalised positions are skipped (the hash set knows them)
-  for (uint32_t e0 = 0; e0 < n_hit; e0 += kTB) {                            // uniform trip count
-    const uint32_t e = e0 + tid;
-    uint32_t ent = 0u, mask = 0u; uint4 q = make_uint4(0u, 0u, 0u, 0u);
-    if (e < n_hit) {
-      ent = c.hitlist[e];
-      q = __ldg(p4 + (ent >> 8));
-      mask = ent & 0xFFu;
+  constexpr int kExpand = 4;                                                // chunk reloads in flight per thread
+  for (uint32_t e0 = 0; e0 < n_hit; e0 += kTB * kExpand) {                  // uniform trip count
+    uint32_t ents[kExpand]; uint4 qq[kExpand];
+#pragma unroll
+    for (int j = 0; j < kExpand; j++) {
+      const uint32_t e = e0 + j * kTB + tid;
+      ents[j] = (e < n_hit) ? c.hitlist[e] : 0u;
+      qq[j] = (e < n_hit) ? __ldg(p4 + (ents[j] >> 8)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int j = 0; j < kExpand; j++) {
+      if (e0 + j * kTB >= n_hit) break;                                     // block-uniform
+      const uint32_t ent = ents[j];
+      uint32_t mask = ent & 0xFFu;
       if (pen_on) {
 #pragma unroll
         for (int b = 0; b < kChunk; b++) if (((mask >> b) & 1u) && hash_contains(c.hs, (ent >> 8) * kChunk + b)) mask &= ~(1u << b);
       }
-    }
-    uint32_t slot = warp_reserve(&c.n, __popc(mask));
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      uint32_t slot = warp_reserve(&c.n, __popc(mask));
+      const uint32_t w[4] = {qq[j].x, qq[j].y, qq[j].z, qq[j].w};
 #pragma unroll
-    for (int b = 0; b < kChunk; b++) {
-      if ((mask >> b) & 1u) {
-        const float value = (b & 1) ? bf16_hi(w[b >> 1]) : bf16_lo(w[b >> 1]);
-        if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(value)) << 32) | (0xFFFFFFFFu - ((ent >> 8) * kChunk + b));
-        slot++;
-        const uint32_t rel = (__float_as_uint(value) >> 16) - cut_code;
-        if (rel >= kTopkBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
+      for (int b = 0; b < kChunk; b++) {
+        if ((mask >> b) & 1u) {
+          const float value = (b & 1) ? bf16_hi(w[b >> 1]) : bf16_lo(w[b >> 1]);
+          if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(value)) << 32) | (0xFFFFFFFFu - ((ent >> 8) * kChunk + b));
+          slot++;
+          const uint32_t rel = (__float_as_uint(value) >> 16) - cut_code;
+          if (rel >= kTopkBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
+        }
       }
     }
   }
+  LM_TPHASE(15);
   // ---- the penalised logits: every occupied slot of the hash set is one distinct id ----------------------------------------
   if (pen_on) {
-    for (int s0 = 0; s0 < kHashSlots; s0 += kTB) {                          // uniform trip count
-      const uint32_t id = c.hs[s0 + tid];
-      float v = -INFINITY;
-      if (id != kHashEmpty) {
-        const float raw = __uint_as_float(static_cast<uint32_t>(__ldg(rowp + id)) << 16);
-        v = penalise(raw, P.rho, P.pi);
-        if (need_z) zsum += static_cast<double>(ex2_approx((v - M) * c2a)) - static_cast<double>(ex2_approx((raw - M) * c2a));
+    constexpr int kGather = 8;                                               // gathers in flight per thread
+    for (int s0 = 0; s0 < kHashSlots; s0 += kTB * kGather) {                 // uniform trip count
+      uint32_t ids[kGather]; uint16_t raws[kGather];
+#pragma unroll
+      for (int j = 0; j < kGather; j++) {
+        ids[j] = c.hs[s0 + j * kTB + tid];
+        raws[j] = (ids[j] != kHashEmpty) ? __ldg(rowp + ids[j]) : static_cast<uint16_t>(0xFF80u);
       }
-      const bool cand = v >= cut_val;
-      const uint32_t slot = warp_reserve(&c.n, cand ? 1u : 0u);
-      if (cand) {
-        if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(v)) << 32) | (0xFFFFFFFFu - id);
-        const uint32_t rel = (__float_as_uint(v) >> 16) - cut_code;
-        if (rel >= kTopkBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
+#pragma unroll
+      for (int j = 0; j < kGather; j++) {
+        const uint32_t id = ids[j];
+        float v = -INFINITY;
+        if (id != kHashEmpty) {
+          const float raw = __uint_as_float(static_cast<uint32_t>(raws[j]) << 16);
+          v = penalise(raw, P.rho, P.pi);
+          if (need_z) zsum += static_cast<double>(ex2_approx((v - M) * c2a)) - static_cast<double>(ex2_approx((raw - M) * c2a));
+        }
+        const bool cand = v >= cut_val;
+        const uint32_t slot = warp_reserve(&c.n, cand ? 1u : 0u);
+        if (cand) {
+          if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(v)) << 32) | (0xFFFFFFFFu - id);
+          const uint32_t rel = (__float_as_uint(v) >> 16) - cut_code;
+          if (rel >= kTopkBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
+        }
       }
     }
   }
@@ -343,23 +369,34 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
     __syncthreads();
   }
   const uint32_t cross = c.cross_bin;
+  // the candidates above the crossing code (fewer than top_k) and those on it are sorted apart: every one of the
+  // first group lies above every one of the second, and two small sorts beat one padded to the next power of two
+  unsigned long long* on_cross = c.w;
   for (int i0 = 0; i0 < n; i0 += kTB) {                                     // uniform trip count
     const int i = i0 + tid;
-    unsigned long long k = 0ull; bool take = false;
+    unsigned long long k = 0ull; bool above = false, on = false;
     if (i < n) {
       k = c.key[i];
-      take = (__float_as_uint(fkey_inv(static_cast<uint32_t>(k >> 32))) >> 16) - cut_code >= cross;
+      const uint32_t rel = (__float_as_uint(fkey_inv(static_cast<uint32_t>(k >> 32))) >> 16) - cut_code;
+      above = rel > cross; on = rel == cross;
     }
-    const uint32_t slot = warp_reserve(&c.n_sel, take ? 1u : 0u);
-    if (take) c.sel[slot] = k;
+    const uint32_t sa = warp_reserve(&c.n_sel, above ? 1u : 0u);
+    const uint32_t sb = warp_reserve(&c.n_on, on ? 1u : 0u);
+    if (above) c.sel[sa] = k;
+    if (on) on_cross[sb] = k;
   }
   __syncthreads();
-  const int n_sel = static_cast<int>(c.n_sel);
-  const int p2 = next_pow2(n_sel);
-  for (int i = n_sel + tid; i < p2; i += kTB) c.sel[i] = 0ull;
+  const int n_above = static_cast<int>(c.n_sel), n_on = static_cast<int>(c.n_on);
+  const int n_sel = n_above + n_on;
+  const int pa = next_pow2(n_above), pb = next_pow2(n_on);
+  for (int i = n_above + tid; i < pa; i += kTB) c.sel[i] = 0ull;
+  for (int i = n_on + tid; i < pb; i += kTB) on_cross[i] = 0ull;
   __syncthreads();
   LM_TPHASE(11);
-  bitonic_desc(c.sel, p2);
+  bitonic_desc(c.sel, pa);
+  bitonic_desc(on_cross, pb);
+  for (int i = tid; i < n_on; i += kTB) c.sel[n_above + i] = on_cross[i];
+  __syncthreads();
   LM_TPHASE(12);
 
   // ---- exact thresholds on the sorted candidates ------------------------------------------------------------------------
@@ -409,24 +446,55 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
   // ---- the draw ----------------------------------------------------------------------------------------------------------
   int token = -1;
   if (P.draw == LM_DRAW_INVERSE_CDF) {
+    // token = first kept index, ascending, whose cumulative fixed-point weight exceeds the target. The kept candidates are
+    // in value order: their weights are summed per bucket of 256 indices (two 20-bit limbs in 32-bit counters), the
+    // bucket that holds the target is found by a scan, and only its few candidates are ranked by index.
     const float c2 = exp2_scale(T);
-    const int q2 = next_pow2(n_kept);
-    // order the kept candidates by index: keys (~index << 32 | position), descending = index ascending
-    for (int i = tid; i < q2; i += kTB)
-      c.key[i] = (i < n_kept) ? ((c.sel[i] & 0xFFFFFFFFull) << 32) | static_cast<unsigned long long>(i) : 0ull;
+    uint32_t* blo = reinterpret_cast<uint32_t*>(c.key);                     // the arrival-order list is no longer needed
+    uint32_t* bhi = blo + kIdxBuckets;
+    for (int i = tid; i < 2 * kIdxBuckets; i += kTB) blo[i] = 0u;
+    if (tid == 0) c.n_hit = 0u;
     __syncthreads();
-    bitonic_desc(c.key, q2);
+    uint64_t mine = 0ull;
     for (int i = tid; i < n_kept; i += kTB) {
-      const unsigned long long k = c.sel[static_cast<uint32_t>(c.key[i])];
-      c.w[i] = weight_q40(fkey_inv(static_cast<uint32_t>(k >> 32)), vmax, c2);
+      const unsigned long long k = c.sel[i];
+      const uint32_t idx = 0xFFFFFFFFu - static_cast<uint32_t>(k);
+      const uint64_t w = weight_q40(fkey_inv(static_cast<uint32_t>(k >> 32)), vmax, c2);
+      c.w[i] = w; mine += w;
+      atomicAdd(&blo[idx >> 8], static_cast<uint32_t>(w & 0xFFFFFull));
+      atomicAdd(&bhi[idx >> 8], static_cast<uint32_t>(w >> 20));
     }
-    __syncthreads();
-    const uint64_t total = scan_u64(c.w, n_kept, c.scratch);
+    const uint64_t total = block_sum_u64(mine, c.scratch);
     if (total > 0ull) {
       const uint64_t target = cdf_target(P.uniforms ? P.uniforms[row] : 0.0f, total);
-      for (int i = tid; i < n_kept; i += kTB) {
-        const uint64_t incl = c.w[i], before = i ? c.w[i - 1] : 0ull;
-        if (before <= target && target < incl) c.token = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(c.key[i] >> 32));
+      constexpr int kPer = kIdxBuckets / kTB;
+      uint64_t bt[kPer], sum = 0ull;
+#pragma unroll
+      for (int j = 0; j < kPer; j++) { const int b = tid * kPer + j; bt[j] = static_cast<uint64_t>(blo[b]) + (static_cast<uint64_t>(bhi[b]) << 20); sum += bt[j]; }
+      uint64_t run = block_exclusive_scan_u64(sum, c.scratch, nullptr);
+#pragma unroll
+      for (int j = 0; j < kPer; j++) {
+        if (run <= target && target < run + bt[j]) { c.cross_bin = static_cast<uint32_t>(tid * kPer + j); c.base = run; }
+        run += bt[j];
+      }
+      __syncthreads();
+      const uint32_t bucket = c.cross_bin;
+      for (int i0 = 0; i0 < n_kept; i0 += kTB) {                            // uniform trip count
+        const int i = i0 + tid;
+        const bool take = i < n_kept && ((0xFFFFFFFFu - static_cast<uint32_t>(c.sel[i])) >> 8) == bucket;
+        const uint32_t slot = warp_reserve(&c.n_hit, take ? 1u : 0u);
+        if (take) c.hitlist[slot] = static_cast<uint32_t>(i);
+      }
+      __syncthreads();
+      const uint32_t m = c.n_hit;                                           // at most 256: one per index of the bucket
+      for (uint32_t j = tid; j < m; j += kTB) {
+        const uint32_t ij = c.hitlist[j], idx_j = 0xFFFFFFFFu - static_cast<uint32_t>(c.sel[ij]);
+        uint64_t before = c.base;
+        for (uint32_t t = 0; t < m; t++) {
+          const uint32_t it = c.hitlist[t];
+          if (0xFFFFFFFFu - static_cast<uint32_t>(c.sel[it]) < idx_j) before += c.w[it];
+        }
+        if (before <= target && target < before + c.w[ij]) c.token = static_cast<int>(idx_j);
       }
     }
     __syncthreads();

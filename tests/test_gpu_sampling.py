@@ -289,3 +289,30 @@ def test_candidate_path_equals_the_oracle(draw):
         h = lm.sample(x, q, history=hist, uniforms=u, step=2, return_tau=True, return_status=True)
         assert not np.any(h.status.cpu().numpy() & 64)
         assert torch.equal(h.tau, r.tau) and torch.equal(h.tokens, r.tokens)
+
+
+def test_streaming_draw_over_wide_kept_sets():
+    """Rows without a top_k draw through the streaming kernel: kept sets that stay in the
+    positive codes, reach into the negative ones (no filter at all, a loose min_p, a row shifted below zero) or
+    lie many binades apart must all give the oracle's token."""
+    rows, V = 12, 151936
+    rng = np.random.default_rng(23)
+    z = (rng.standard_normal((rows, V)) * 2).astype(np.float32)
+    z[3] -= 30.0                                                            # every logit negative
+    z[4] *= 1e-3                                                            # tiny magnitudes: many binades below the maximum
+    z[5, ::7] *= 1e-30                                                      # values far outside both windows
+    z[6] = np.abs(z[6])                                                     # no negative code at all
+    cfg = dict(logits=oracle.f32_to_bf16(z), temperature=np.float32([1.0, 1.5, 0.7, 1.2, 1.0, 0.9, 1.0, 0.3, 1.0, 1.4, 0.6, 1.1]),
+               top_k=np.zeros(rows, np.int32), top_p=np.float32([0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.9, 0.999, 0.97, 0.5, 1.0]),
+               history=rng.integers(0, V, (rows, 64)).astype(np.int32), uniforms=rng.random(rows).astype(np.float32),
+               repetition_penalty=1.2, presence_penalty=0.3)
+    x = bf16_tensor(cfg["logits"])
+    knobs = {k: torch.from_numpy(cfg[k]).cuda() for k in ("temperature", "top_k", "top_p")}
+    for extra in (dict(), dict(min_p=1e-6), dict(min_p=0.01)):
+        r = lm.sample(x, lm.SamplingParams(draw="inverse_cdf", repetition_penalty=1.2, presence_penalty=0.3, **knobs, **extra),
+                      history=torch.from_numpy(cfg["history"]).cuda(), uniforms=torch.from_numpy(cfg["uniforms"]).cuda(), return_tau=True, return_status=True)
+        tok, tau, _ = oracle.sample_batch(cfg["logits"], temperature=cfg["temperature"], top_k=cfg["top_k"], top_p=cfg["top_p"], history=cfg["history"],
+                                          repetition_penalty=1.2, presence_penalty=0.3, draw="inverse_cdf", uniforms=cfg["uniforms"], n_threads=8, **extra)
+        assert not np.any(r.status.cpu().numpy() & 1), r.status                 # all through the streaming kernel
+        np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
+        np.testing.assert_array_equal(r.tokens.cpu().numpy(), tok)
