@@ -289,7 +289,7 @@ int lm_sample(const lm_sample_args* a) {
       if (e != cudaSuccess) return cuda_fail(e);
     }
     if (topk) {
-      int grid1 = static_cast<int>(a->rows < 3LL * sms ? a->rows : 3LL * sms);
+      int grid1 = static_cast<int>(a->rows < static_cast<long long>(kTopkPerSM) * sms ? a->rows : static_cast<long long>(kTopkPerSM) * sms);
       if (limit > 0 && grid1 > limit) grid1 = limit;
       sample_topk_kernel<<<grid1, kTB, sizeof(TopkSmem), st>>>(P, punt, list, counters);
       const cudaError_t e = cudaGetLastError();

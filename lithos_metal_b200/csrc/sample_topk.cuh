@@ -18,35 +18,41 @@
 
 namespace lm {
 
-constexpr int kTB = 256;                   // threads per block
+constexpr int kTB = 512;                   // threads per block
+constexpr int kTopkPerSM = 2;              // blocks per SM (64 registers per thread, ~92 KB of shared memory each)
 constexpr int kTW = kTB / 32;
 constexpr int kTopkCap = 2048;             // candidates per row (a power of two: the sorts pad to one)
 constexpr int kTopkBins = 512;             // BF16 codes above the cutoff that the coarse count covers
 constexpr int kTopkMaxK = 1024;            // largest top_k this kernel takes
-constexpr int kTopkHist = 2048;            // longest history it takes (distinct ids live in a 4096-slot hash set)
-constexpr int kHashSlots = 4096;
-constexpr uint32_t kHashEmpty = 0xFFFFFFFFu;
-constexpr int kSampleChunks = 4;           // chunks per thread in the cutoff sample: 4 * 256 * 8 = 8192 logits
+constexpr int kTopkHist = 2048;            // longest history it takes
+constexpr int kTopkMaxVocab = 1 << 18;
+constexpr int kBinSortMax = 256;           // a code bin with more candidates than this must already be in order (all equal)
+constexpr int kSampleChunks = 1024 / kTB;   // chunks per thread in the cutoff sample: 1024 chunks = 8192 logits
 constexpr int kTopkMinVocab = 32768;
 constexpr int kIdxBuckets = 1024;          // the draw buckets candidates by index >> 8: vocabularies up to 2^18
 
 struct TopkSmem {
   unsigned long long key[kTopkCap];        // candidates as (monotone value key << 32) | ~index, arrival order; later the index-sort keys
   unsigned long long sel[kTopkCap];        // those at or above the coarse top-k crossing, sorted: value descending, index ascending
-  union { double cum[kTopkCap]; unsigned long long w[kTopkCap]; };   // FP64 softmass prefix, then fixed-point weight prefix
-  uint32_t hs[kHashSlots];                 // the row's distinct history ids (open addressing)
+  union {
+    double cum[kTopkCap];                  // FP64 softmass prefix over sel ...
+    unsigned long long w[kTopkCap];        // ... then the fixed-point weights of the kept prefix
+    struct { uint32_t side_id[kTopkHist]; uint16_t side_raw[kTopkHist]; };   // before either: the distinct history ids and their raw logits
+  };
+  uint32_t pen[kTopkMaxVocab / 32];        // bitmap of the row's distinct history ids
   uint32_t hitlist[2048];                  // (chunk << 8 | 8-bit mask) of the chunks that hold a logit >= cutoff
   uint32_t bins[kTopkBins];                // candidates per BF16 code, relative to the cutoff code
+  uint32_t off[kTopkBins];                 // candidates in the bins above each bin
   uint64_t scratch[32];
   double warp_d[kTW];
-  uint32_t warp_u[kTW];
+  uint32_t warp_u[2][kTW];
   float warp_f[kTW];
   unsigned long long base;
-  uint32_t n_hit, n, n_sel, n_on, wide, cross_bin;
+  uint32_t n_hit, n, n_side, wide, cross_bin;
   int hit, token, row;
 };
 
-static_assert(3 * (sizeof(TopkSmem) + 1024) <= 233472, "three blocks of the top-k kernel must fit one SM's shared memory");
+static_assert(kTopkPerSM * (sizeof(TopkSmem) + 1024) <= 233472, "the blocks of the top-k kernel must fit one SM's shared memory");
 
 #ifdef LM_PROFILE_PHASES
 #define LM_TPHASE(i) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == 0) { const long long _t = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(_t - _t0)); _t0 = _t; } } while (0)
@@ -56,8 +62,6 @@ static_assert(3 * (sizeof(TopkSmem) + 1024) <= 233472, "three blocks of the top-
 
 __device__ __forceinline__ float ex2_approx(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ int next_pow2(int n) { int p = 32; while (p < n) p <<= 1; return p; }
-__device__ __forceinline__ uint32_t hash_id(uint32_t id) { return (id * 2654435761u) >> 20; }   // 12 bits
-
 // bitonic sort of a[0 .. n_pow2) in shared memory, descending; every thread of the block calls. One compare-exchange
 // per thread and step: thread t takes the t-th pair (i, i | j) with i's bit j clear.
 __device__ __forceinline__ void bitonic_desc(unsigned long long* a, int n_pow2) {
@@ -123,17 +127,6 @@ __device__ __forceinline__ uint32_t warp_reserve(uint32_t* counter, uint32_t min
   return base + incl - mine;
 }
 
-__device__ __forceinline__ bool hash_contains(const uint32_t* hs, uint32_t id) {
-  uint32_t h = hash_id(id);
-  for (int probe = 0; probe < kHashSlots; probe++) {
-    const uint32_t v = hs[h];
-    if (v == id) return true;
-    if (v == kHashEmpty) return false;
-    h = (h + 1u) & (kHashSlots - 1u);
-  }
-  return false;
-}
-
 // One row. Every thread of the block calls with the same arguments; returns true when the row is finished, false when the
 // histogram kernel has to take it (nothing has been written then).
 __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
@@ -159,33 +152,39 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
 #ifdef LM_PROFILE_PHASES
   long long _t0 = clock64();
 #endif
-  // ---- the cutoff sample goes out first; the hash set of the history's distinct ids is built under its latency ---------
-  // (four runs of 256 chunks at 0, 1/4, 1/2 and 3/4 of the row: token ids are not exchangeable in a real vocabulary)
+  // ---- the cutoff sample goes out first; the bitmap and the list of the history's distinct ids are built under its latency ---
+  // (runs of chunks spread over the row: token ids are not exchangeable in a real vocabulary)
   uint4 qs[kSampleChunks];
 #pragma unroll
   for (int j = 0; j < kSampleChunks; j++) qs[j] = __ldg(p4 + tid + j * (n_chunks / kSampleChunks));
-  int hid[kTopkHist / kTB];                                                 // this thread's share of the history, in flight with the sample
+  constexpr int kHistPer = kTopkHist / kTB;
+  int hid[kHistPer];                                                        // this thread's share of the history, in flight with the sample
 #pragma unroll
-  for (int j = 0; j < kTopkHist / kTB; j++) {
+  for (int j = 0; j < kHistPer; j++) {
     const int i = tid + j * kTB;
     hid[j] = (pen_on && i < P.hist_len) ? __ldg(P.history + static_cast<int64_t>(row) * P.hist_stride + i) : -1;
   }
   for (int i = tid; i < kTopkBins; i += kTB) c.bins[i] = 0u;
-  for (int i = tid; i < kHashSlots; i += kTB) c.hs[i] = kHashEmpty;
-  if (tid == 0) { c.n_hit = 0u; c.n = 0u; c.n_sel = 0u; c.n_on = 0u; c.wide = 0u; c.hit = kTopkCap; c.token = -1; c.cross_bin = 0u; }
-  __syncthreads();
   if (pen_on) {
+    uint4* p = reinterpret_cast<uint4*>(c.pen);
+    for (int i = tid; i < (V + 127) / 128; i += kTB) p[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (tid == 0) { c.n_hit = 0u; c.n = 0u; c.n_side = 0u; c.wide = 0u; c.hit = kTopkCap; c.token = -1; c.cross_bin = 0u; }
+  __syncthreads();
+  // the thread that sets an id's bit owns the id: it lists it and fetches its raw logit (stored once the cutoff is known,
+  // long after the load has come back)
+  uint32_t side_slot[kHistPer]; uint16_t side_raw[kHistPer];
 #pragma unroll
-    for (int j = 0; j < kTopkHist / kTB; j++) {
-      const int id = hid[j];
-      if (id < 0 || id >= V) continue;
-      uint32_t slot = hash_id(static_cast<uint32_t>(id));
-      for (int probe = 0; probe < kHashSlots; probe++) {
-        const uint32_t old = atomicCAS(&c.hs[slot], kHashEmpty, static_cast<uint32_t>(id));
-        if (old == kHashEmpty || old == static_cast<uint32_t>(id)) break;
-        slot = (slot + 1u) & (kHashSlots - 1u);
-      }
+  for (int j = 0; j < kHistPer; j++) {
+    const int id = hid[j];
+    bool fresh = false;
+    if (id >= 0 && id < V) {
+      const uint32_t bit = 1u << (id & 31);
+      fresh = (atomicOr(&c.pen[id >> 5], bit) & bit) == 0u;
     }
+    side_slot[j] = warp_reserve(&c.n_side, fresh ? 1u : 0u);
+    side_raw[j] = fresh ? __ldg(rowp + id) : static_cast<uint16_t>(0u);
+    if (fresh) c.side_id[side_slot[j]] = static_cast<uint32_t>(id); else side_slot[j] = 0xFFFFFFFFu;
   }
   // ---- the cutoff: the largest positive BF16 code with at least `want` of the 8192 sampled logits at or above it ---------
   // (about 1.3 k + 150 candidates expected in the whole row, at most ~1500)
@@ -207,11 +206,10 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
       cnt >>= 4;                                                            // 16 mask bits per logit
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(kFull, cnt, o);
-      __syncthreads();
-      if (lane == 0) c.warp_u[warp] = cnt;
+      if (lane == 0) c.warp_u[it & 1][warp] = cnt;                        // two buffers: a warp is never more than one step ahead
       __syncthreads();
       uint32_t total = 0;
-      for (int w = 0; w < kTW; w++) total += c.warp_u[w];
+      for (int w = 0; w < kTW; w++) total += c.warp_u[it & 1][w];
       if (total >= want) lo = mid; else hi = mid - 1u;
       if (lo >= hi) break;
     }
@@ -219,6 +217,8 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
     if (cut_code < 0x0080u) return false;                                   // fewer positive logits than candidates wanted: not this kernel's row
   }
   const float cut_val = __uint_as_float(cut_code << 16);
+#pragma unroll
+  for (int j = 0; j < kHistPer; j++) if (side_slot[j] != 0xFFFFFFFFu) c.side_raw[side_slot[j]] = side_raw[j];
   LM_TPHASE(8);
 
   // ---- the one pass: note the chunks that hold a logit >= cutoff; FP32 softmass with a per-thread running maximum ---------
@@ -283,7 +283,7 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
   if (__syncthreads_or(nan_seen != 0u) || n_hit > 2048u) return false;      // rows with a NaN go to the exact path, which reports them
 
   // ---- the noted chunks, expanded: their logits come back from L2; penalised positions are skipped (the hash set knows them)
-  constexpr int kExpand = 4;                                                // chunk reloads in flight per thread
+  constexpr int kExpand = 1024 / kTB;                                       // chunk reloads in flight per thread
   for (uint32_t e0 = 0; e0 < n_hit; e0 += kTB * kExpand) {                  // uniform trip count
     uint32_t ents[kExpand]; uint4 qq[kExpand];
 #pragma unroll
@@ -297,51 +297,39 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
       if (e0 + j * kTB >= n_hit) break;                                     // block-uniform
       const uint32_t ent = ents[j];
       uint32_t mask = ent & 0xFFu;
-      if (pen_on) {
-#pragma unroll
-        for (int b = 0; b < kChunk; b++) if (((mask >> b) & 1u) && hash_contains(c.hs, (ent >> 8) * kChunk + b)) mask &= ~(1u << b);
-      }
-      uint32_t slot = warp_reserve(&c.n, __popc(mask));
-      const uint32_t w[4] = {qq[j].x, qq[j].y, qq[j].z, qq[j].w};
-#pragma unroll
-      for (int b = 0; b < kChunk; b++) {
-        if ((mask >> b) & 1u) {
-          const float value = (b & 1) ? bf16_hi(w[b >> 1]) : bf16_lo(w[b >> 1]);
-          if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(value)) << 32) | (0xFFFFFFFFu - ((ent >> 8) * kChunk + b));
-          slot++;
-          const uint32_t rel = (__float_as_uint(value) >> 16) - cut_code;
-          if (rel >= kTopkBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
-        }
+      const uint32_t cc = ent >> 8;
+      const uint32_t keep = pen_on ? mask & ~((c.pen[cc >> 2] >> ((cc & 3u) * 8u)) & 0xFFu) : mask;   // penalised positions come from the list
+      uint32_t slot = warp_reserve(&c.n, __popc(keep));
+      for (uint32_t m = keep; m; m &= m - 1u) {                             // usually one bit
+        const uint32_t b = __ffs(m) - 1u;
+        const uint32_t word = b < 4u ? (b < 2u ? qq[j].x : qq[j].y) : (b < 6u ? qq[j].z : qq[j].w);
+        const float value = (b & 1u) ? bf16_hi(word) : bf16_lo(word);
+        if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(value)) << 32) | (0xFFFFFFFFu - (cc * kChunk + b));
+        slot++;
+        const uint32_t rel = (__float_as_uint(value) >> 16) - cut_code;
+        if (rel >= kTopkBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
       }
     }
   }
   LM_TPHASE(15);
-  // ---- the penalised logits: every occupied slot of the hash set is one distinct id ----------------------------------------
+  // ---- the penalised logits, from the list ---------------------------------------------------------------------------------
   if (pen_on) {
-    constexpr int kGather = 8;                                               // gathers in flight per thread
-    for (int s0 = 0; s0 < kHashSlots; s0 += kTB * kGather) {                 // uniform trip count
-      uint32_t ids[kGather]; uint16_t raws[kGather];
-#pragma unroll
-      for (int j = 0; j < kGather; j++) {
-        ids[j] = c.hs[s0 + j * kTB + tid];
-        raws[j] = (ids[j] != kHashEmpty) ? __ldg(rowp + ids[j]) : static_cast<uint16_t>(0xFF80u);
+    const uint32_t n_side = c.n_side;
+    for (uint32_t i0 = 0; i0 < n_side; i0 += kTB) {                         // uniform trip count
+      const uint32_t i = i0 + tid;
+      float v = -INFINITY; uint32_t id = 0u;
+      if (i < n_side) {
+        id = c.side_id[i];
+        const float raw = __uint_as_float(static_cast<uint32_t>(c.side_raw[i]) << 16);
+        v = penalise(raw, P.rho, P.pi);
+        if (need_z) zsum += static_cast<double>(ex2_approx((v - M) * c2a)) - static_cast<double>(ex2_approx((raw - M) * c2a));
       }
-#pragma unroll
-      for (int j = 0; j < kGather; j++) {
-        const uint32_t id = ids[j];
-        float v = -INFINITY;
-        if (id != kHashEmpty) {
-          const float raw = __uint_as_float(static_cast<uint32_t>(raws[j]) << 16);
-          v = penalise(raw, P.rho, P.pi);
-          if (need_z) zsum += static_cast<double>(ex2_approx((v - M) * c2a)) - static_cast<double>(ex2_approx((raw - M) * c2a));
-        }
-        const bool cand = v >= cut_val;
-        const uint32_t slot = warp_reserve(&c.n, cand ? 1u : 0u);
-        if (cand) {
-          if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(v)) << 32) | (0xFFFFFFFFu - id);
-          const uint32_t rel = (__float_as_uint(v) >> 16) - cut_code;
-          if (rel >= kTopkBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
-        }
+      const bool cand = v >= cut_val;
+      const uint32_t slot = warp_reserve(&c.n, cand ? 1u : 0u);
+      if (cand) {
+        if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(v)) << 32) | (0xFFFFFFFFu - id);
+        const uint32_t rel = (__float_as_uint(v) >> 16) - cut_code;
+        if (rel >= kTopkBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
       }
     }
   }
@@ -351,52 +339,54 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
   if (n > kTopkCap || n < top_k || c.wide) return false;
 
   LM_TPHASE(10);
-  // ---- the coarse top-k crossing: the highest code bin b with at least top_k candidates in bins >= b ---------------------
+  // ---- the candidates at or above the top-k crossing, in descending value order: a counting sort by code bin ---------------
+  // (the bins are the BF16 codes relative to the cutoff; the crossing is the highest bin b with at least top_k
+  // candidates in the bins >= b; inside a bin only penalised values can differ, and one thread puts its bin in order)
   {
-    uint32_t run = 0u;                                                       // 512 bins, 2 per thread, walked from the top
-    const uint32_t c_hi = c.bins[kTopkBins - 1 - 2 * tid], c_lo = c.bins[kTopkBins - 2 - 2 * tid];
-    uint32_t incl = c_hi + c_lo;
+    constexpr int kPer = kTopkBins / kTB;                                    // bins per thread, walked from the top
+    uint32_t run = 0u, cb[kPer], mine = 0u;
+#pragma unroll
+    for (int j = 0; j < kPer; j++) { cb[j] = c.bins[kTopkBins - 1 - (kPer * tid + j)]; mine += cb[j]; }
+    uint32_t incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
-    if (lane == 31) c.warp_u[warp] = incl;
+    if (lane == 31) c.warp_u[0][warp] = incl;
     __syncthreads();
-    for (int w = 0; w < warp; w++) run += c.warp_u[w];
-    incl += run;
-    const uint32_t excl = incl - c_hi - c_lo;
-    if (excl + c_hi >= static_cast<uint32_t>(top_k)) atomicMin(&c.hit, 2 * tid); else if (incl >= static_cast<uint32_t>(top_k)) atomicMin(&c.hit, 2 * tid + 1);
-    __syncthreads();
-    if (tid == 0) { c.cross_bin = static_cast<uint32_t>(kTopkBins - 1 - c.hit); c.hit = kTopkCap; }
+    for (int w = 0; w < warp; w++) run += c.warp_u[0][w];
+    uint32_t acc = run + incl - mine;
+#pragma unroll
+    for (int j = 0; j < kPer; j++) {
+      c.off[kTopkBins - 1 - (kPer * tid + j)] = acc;
+      if (acc < static_cast<uint32_t>(top_k) && acc + cb[j] >= static_cast<uint32_t>(top_k)) c.cross_bin = static_cast<uint32_t>(kTopkBins - 1 - (kPer * tid + j));
+      acc += cb[j];
+    }
     __syncthreads();
   }
   const uint32_t cross = c.cross_bin;
-  // the candidates above the crossing code (fewer than top_k) and those on it are sorted apart: every one of the
-  // first group lies above every one of the second, and two small sorts beat one padded to the next power of two
-  unsigned long long* on_cross = c.w;
-  for (int i0 = 0; i0 < n; i0 += kTB) {                                     // uniform trip count
-    const int i = i0 + tid;
-    unsigned long long k = 0ull; bool above = false, on = false;
-    if (i < n) {
-      k = c.key[i];
-      const uint32_t rel = (__float_as_uint(fkey_inv(static_cast<uint32_t>(k >> 32))) >> 16) - cut_code;
-      above = rel > cross; on = rel == cross;
-    }
-    const uint32_t sa = warp_reserve(&c.n_sel, above ? 1u : 0u);
-    const uint32_t sb = warp_reserve(&c.n_on, on ? 1u : 0u);
-    if (above) c.sel[sa] = k;
-    if (on) on_cross[sb] = k;
+  const int n_sel = static_cast<int>(c.off[cross] + c.bins[cross]);
+  __syncthreads();                                                          // the counts are consumed below
+  for (int i = tid; i < n; i += kTB) {
+    const unsigned long long k = c.key[i];
+    const uint32_t rel = (__float_as_uint(fkey_inv(static_cast<uint32_t>(k >> 32))) >> 16) - cut_code;
+    if (rel >= cross) c.sel[c.off[rel] + atomicSub(&c.bins[rel], 1u) - 1u] = k;
   }
   __syncthreads();
-  const int n_above = static_cast<int>(c.n_sel), n_on = static_cast<int>(c.n_on);
-  const int n_sel = n_above + n_on;
-  const int pa = next_pow2(n_above), pb = next_pow2(n_on);
-  for (int i = n_above + tid; i < pa; i += kTB) c.sel[i] = 0ull;
-  for (int i = n_on + tid; i < pb; i += kTB) on_cross[i] = 0ull;
-  __syncthreads();
   LM_TPHASE(11);
-  bitonic_desc(c.sel, pa);
-  bitonic_desc(on_cross, pb);
-  for (int i = tid; i < n_on; i += kTB) c.sel[n_above + i] = on_cross[i];
+  for (uint32_t b = cross + tid; b < kTopkBins; b += kTB) {
+    const uint32_t lo = c.off[b], hi = (b == cross) ? static_cast<uint32_t>(n_sel) : c.off[b - 1];
+    bool sorted = true;
+    for (uint32_t i = lo + 1u; i < hi; i++) sorted = sorted && (c.sel[i - 1u] >> 32) >= (c.sel[i] >> 32);
+    if (sorted) continue;
+    if (hi - lo > static_cast<uint32_t>(kBinSortMax)) { c.wide = 1u; continue; }
+    for (uint32_t i = lo + 1u; i < hi; i++) {                               // insertion sort on the value part: equal values stay put
+      const unsigned long long k = c.sel[i];
+      uint32_t j = i;
+      while (j > lo && (c.sel[j - 1u] >> 32) < (k >> 32)) { c.sel[j] = c.sel[j - 1u]; j--; }
+      c.sel[j] = k;
+    }
+  }
   __syncthreads();
+  if (c.wide) return false;                                                 // a large bin of unequal (penalised) values: the exact path takes the row
   LM_TPHASE(12);
 
   // ---- exact thresholds on the sorted candidates ------------------------------------------------------------------------
@@ -530,7 +520,7 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
 // Rows are handed out through a counter in the workspace (counters[0], zeroed by the host before the launch): a block takes
 // the next row and either finishes it (punt[row] = 0: no later kernel touches it) or appends it to `list` (length in
 // counters[1]) for the histogram kernel. The order of the list varies from run to run; what is computed per row does not.
-__global__ void __launch_bounds__(kTB, 3) sample_topk_kernel(SampleDev P, uint32_t* punt, int* list, int* counters) {
+__global__ void __launch_bounds__(kTB, kTopkPerSM) sample_topk_kernel(SampleDev P, uint32_t* punt, int* list, int* counters) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   TopkSmem& c = *reinterpret_cast<TopkSmem*>(smem_raw);
   for (;;) {
