@@ -56,14 +56,14 @@ __global__ void __launch_bounds__(kArgmaxBlock) argmax_kernel(const void* logits
   }
 }
 
-// ---- the generic sampler: one block per row, grid-stride over rows ------------------------------------------------
-__global__ void __launch_bounds__(kBlock, 1) sample_generic_kernel(SampleDev P) {
+// ---- the generic sampler: one block per row, grid-stride over rows, or over the rows an earlier kernel listed ---------------
+__global__ void __launch_bounds__(kBlock, 1) sample_generic_kernel(SampleDev P, const int* list, const int* n_list) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   GenericSmem& s = *reinterpret_cast<GenericSmem*>(smem_raw);
   uint32_t* pen_bits = reinterpret_cast<uint32_t*>(smem_raw + sizeof(GenericSmem));
-  for (int row = blockIdx.x; row < P.rows; row += gridDim.x) {
-    if (P.row_select != nullptr && P.row_select[row] == 0u) continue;
-    sample_row_generic(P, row, s, pen_bits);
+  const int n = list ? *n_list : P.rows;
+  for (int i = blockIdx.x; i < n; i += gridDim.x) {
+    sample_row_generic(P, list ? list[i] : i, s, pen_bits);
     __syncthreads();
   }
 }
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(kBlock, 1) sample_generic_kernel(SampleDev P) 
 // blocks take them from a counter (`next_item`, zeroed by the host) instead of a fixed stride; a block always holds the item
 // after its current one too, so that it can pull that row into L2 while it works. With a row list (written by the
 // top-k kernel: the rows it left) the items are entries of the list, without one they are the rows themselves.
-__global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, uint32_t* punt, const int* list, const int* n_list, int* next_item) {
+__global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, const int* list, const int* n_list, int* next_item, int* redo, int* n_redo) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   FastSmem& s = *reinterpret_cast<FastSmem*>(smem_raw);
   __shared__ int item[2];
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, uin
     if (i >= n) break;
     __syncthreads();
     if (threadIdx.x == 0) { item[0] = in; item[1] = in < n ? atomicAdd(next_item, 1) : n; }
-    sample_row_fast(P, list ? list[i] : i, in < n ? (list ? list[in] : in) : -1, s, punt);
+    sample_row_fast(P, list ? list[i] : i, in < n ? (list ? list[in] : in) : -1, s, redo, n_redo);
     __syncthreads();
   }
 }
@@ -159,7 +159,7 @@ float lm_uniform01(uint64_t seed, uint32_t step, uint32_t t, uint32_t index) { r
 size_t lm_workspace_bytes(int64_t rows, int64_t vocab) {
   (void)vocab;
   if (rows < 0) rows = 0;
-  // argmax partials | rows left to the generic kernel | rows left to the histogram kernel | three counters
+  // argmax partials | rows left to the generic kernel | rows left to the histogram kernel | four counters
   return align256(static_cast<size_t>(rows) * sizeof(ArgmaxWs)) + 2 * align256(static_cast<size_t>(rows) * sizeof(uint32_t)) + 256;
 }
 
@@ -256,12 +256,13 @@ int lm_sample(const lm_sample_args* a) {
   P.rho = a->repetition_penalty; P.pi = a->presence_penalty;
   P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
   P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_stats = a->out_stats; P.out_probs = a->out_probs; P.probs_stride = a->probs_stride;
-  P.out_status = a->out_status; P.row_select = nullptr;
+  P.out_status = a->out_status;
 
   int sms = 0;
   int rc = sm_count(&sms);
   if (rc != LM_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+  const int* redo_list = nullptr; const int* redo_n = nullptr;
   // BF16 rows that only need tokens (and tau) stream through the one-pass kernel; it marks the rows it cannot take
   // and the generic kernel behind it handles exactly those.
   const bool fast = a->dtype == LM_DTYPE_BF16 && a->out_stats == nullptr && a->out_probs == nullptr && a->vocab <= kFastMaxVocab &&
@@ -270,7 +271,7 @@ int lm_sample(const lm_sample_args* a) {
     if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) || a->workspace_bytes < lm_workspace_bytes(a->rows, a->vocab))
       return LM_E_WORKSPACE;
     char* ws = static_cast<char*>(a->workspace) + align256(static_cast<size_t>(a->rows) * sizeof(ArgmaxWs));
-    uint32_t* punt = reinterpret_cast<uint32_t*>(ws);
+    int* redo = reinterpret_cast<int*>(ws);
     int* list = reinterpret_cast<int*>(ws + align256(static_cast<size_t>(a->rows) * sizeof(uint32_t)));
     int* counters = reinterpret_cast<int*>(ws + 2 * align256(static_cast<size_t>(a->rows) * sizeof(uint32_t)));
     static thread_local bool fast_attr = false;
@@ -285,22 +286,22 @@ int lm_sample(const lm_sample_args* a) {
     const bool topk = !(a->flags & LM_FLAG_EXACT_ONLY) && a->vocab >= kTopkMinVocab && (a->top_k != nullptr || (a->top_k_s >= 1 && a->top_k_s <= kTopkMaxK)) &&
                       (a->temperature != nullptr || a->temperature_s > 0.0f) && (!pen || a->hist_len <= kTopkHist);
     {
-      const cudaError_t e = cudaMemsetAsync(counters, 0, 3 * sizeof(int), st);   // next row of the top-k kernel, length of its list, next item of the histogram kernel
+      const cudaError_t e = cudaMemsetAsync(counters, 0, 4 * sizeof(int), st);   // next row of the top-k kernel, length of its list, next item of the histogram kernel, length of its list
       if (e != cudaSuccess) return cuda_fail(e);
     }
     if (topk) {
       int grid1 = static_cast<int>(a->rows < static_cast<long long>(kTopkPerSM) * sms ? a->rows : static_cast<long long>(kTopkPerSM) * sms);
       if (limit > 0 && grid1 > limit) grid1 = limit;
-      sample_topk_kernel<<<grid1, kTB, sizeof(TopkSmem), st>>>(P, punt, list, counters);
+      sample_topk_kernel<<<grid1, kTB, sizeof(TopkSmem), st>>>(P, list, counters);
       const cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return cuda_fail(e);
     }
     int grid = static_cast<int>(a->rows < sms ? a->rows : sms);
     if (limit > 0 && grid > limit) grid = limit;
-    sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, punt, topk ? list : nullptr, topk ? counters + 1 : nullptr, counters + 2);
+    sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, topk ? list : nullptr, topk ? counters + 1 : nullptr, counters + 2, redo, counters + 3);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e);
-    P.row_select = punt;
+    redo_list = redo; redo_n = counters + 3;
   }
   const size_t smem = sizeof(GenericSmem) + (pen ? static_cast<size_t>((a->vocab + 31) / 32) * 4 : 0) + 16;
   static thread_local size_t smem_set = 0;
@@ -311,7 +312,7 @@ int lm_sample(const lm_sample_args* a) {
   }
   const long long cap = fast ? sms : 8LL * sms;
   const int grid = static_cast<int>(a->rows < cap ? a->rows : cap);
-  sample_generic_kernel<<<grid, kBlock, smem, st>>>(P);
+  sample_generic_kernel<<<grid, kBlock, smem, st>>>(P, redo_list, redo_n);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }

@@ -11,7 +11,7 @@
 //
 // Rows this kernel cannot take (a counter overflow: more than 65535 equal logits; more than kSideCap penalised
 // logits, or more than kSidePool of them in the 256 codes around a threshold; vocabularies that are not a multiple of 8 or exceed
-// kFastMaxVocab; misaligned rows) are marked in `punt` and handled by the generic kernel launched behind this one.
+// kFastMaxVocab; misaligned rows) are listed in `redo` and handled by the generic kernel launched behind this one.
 #pragma once
 #include "common.cuh"
 #include "draw.cuh"
@@ -264,8 +264,123 @@ __device__ void find_group(FastSmem& s, uint32_t k_target, double m_target) {
   __syncthreads();
 }
 
+// The inverse-CDF draw of the streaming kernel. The total weight S of the kept set comes from the histogram (count x weight
+// per code) and the side list, so the target is known before the row is read again. The sweeps over the row then run from
+// whichever end is closer to the target (a suffix sum is as exact as a prefix sum in integers) and stop at the sweep that
+// holds it: a quarter of the row on average instead of all of it. Every thread calls; every thread gets the token.
+__device__ int draw_inverse_cdf_bidir(const RowView& rv, FastSmem& s, const SideList& side, float tau, float vmax, float temperature, float u) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n_chunks = rv.vocab / kChunk;
+  const int n_sweeps = (n_chunks + kBlock - 1) / kBlock;
+  const float c2 = exp2_scale(temperature);
+  const uint32_t tc = ceil_bf16_code(tau);
+  const uint32_t tau2 = tc | (tc << 16);
+  DrawSmem& d = s.draw;
+  uint32_t* side_limb = &s.side_limb[0][0];
+  uint64_t* sweep_part = &s.sweep_part[0][0];
+  for (int i = tid; i < n_sweeps * 3; i += kBlock) side_limb[i] = 0u;
+  if (tid == 0) { d.token = -1; d.found_sweep = -1; d.found_base = 0ull; }
+  __syncthreads();
+  // ---- S: every kept BF16 code once, times its count; the kept side values join their sweep's limbs on the way ----------
+  uint64_t mine = 0ull;
+  {
+    const uint32_t pos_last = tc == 0x0000u ? 0x8000u : code_to_pos(tc);   // the last kept position (-0 is kept with +0)
+    const uint32_t pos_first = max(0x7Fu, s.top_group * static_cast<uint32_t>(kGroupBins));   // +inf, or the first occupied group
+    for (uint32_t pos = pos_first + tid; pos <= pos_last && pos <= 0xFF80u; pos += kBlock) {
+      const uint32_t code = pos_to_code(pos);
+      const uint32_t cnt = hist_get(s.hist, code);
+      if (cnt) mine += static_cast<uint64_t>(cnt) * weight_q40(code_val(code), vmax, c2);
+    }
+    for (uint32_t i = tid; i < side.n; i += kBlock) {
+      const float v = side.val[i];
+      if (v >= tau) {
+        const uint64_t w = weight_q40(v, vmax, c2);
+        if (w) {
+          mine += w;
+          uint32_t* l = side_limb + 3 * ((side.idx[i] / kChunk) / kBlock);
+          atomicAdd(l, static_cast<uint32_t>(w & 0xFFFFull)); atomicAdd(l + 1, static_cast<uint32_t>((w >> 16) & 0xFFFFull));
+          atomicAdd(l + 2, static_cast<uint32_t>(w >> 32));
+        }
+      }
+    }
+  }
+  const uint64_t total = block_sum_u64(mine, d.scratch);
+  if (total == 0ull) return -1;
+  const uint64_t target = cdf_target(u, total);
+  const bool forward = target < total - target;
+  const uint64_t tt = forward ? target : total - target - 1ull;             // the first sweep, in scan order, whose running sum exceeds tt
+  // ---- the sweeps, four at a time, from the nearer end ----------------------------------------------------------------------
+  const uint4* p4 = reinterpret_cast<const uint4*>(rv.row);
+  const uint4 neg = make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);
+  uint64_t run = 0ull;
+  int found = -1; uint64_t before = 0ull, found_total = 0ull;
+  for (int b0 = 0; b0 < n_sweeps && found < 0; b0 += kDrawBatch) {
+    uint4 q[kDrawBatch];
+#pragma unroll
+    for (int j = 0; j < kDrawBatch; j++) {
+      const int it = forward ? b0 + j : n_sweeps - 1 - (b0 + j);
+      const int cc = it * kBlock + tid;
+      q[j] = (b0 + j < n_sweeps && cc < n_chunks) ? __ldg(p4 + cc) : neg;
+    }
+#pragma unroll
+    for (int j = 0; j < kDrawBatch; j++) {
+      if (b0 + j >= n_sweeps) break;
+      const int it = forward ? b0 + j : n_sweeps - 1 - (b0 + j);
+      const int cc = it * kBlock + tid;
+      float z[kChunk];
+      const uint32_t mask = (cc < n_chunks) ? kept_from_q(rv, cc, q[j], tau2, z) : 0u;
+      uint64_t w = 0ull;
+      if (mask) {
+#pragma unroll
+        for (int e = 0; e < kChunk; e++) if ((mask >> e) & 1u) w += weight_q40(z[e], vmax, c2);
+      }
+      if (__any_sync(kFull, w != 0ull)) w = warp_sum_u64(w);
+      if (lane == 0) sweep_part[it * 32 + warp] = w;
+    }
+    __syncthreads();
+    if (warp < kDrawBatch && b0 + warp < n_sweeps) {                        // warp j sums sweep j of the batch
+      const int it = forward ? b0 + warp : n_sweeps - 1 - (b0 + warp);
+      uint64_t t = lane < kWarps ? sweep_part[it * 32 + lane] : 0ull;
+      t = warp_sum_u64(t);
+      t += static_cast<uint64_t>(side_limb[3 * it]) + (static_cast<uint64_t>(side_limb[3 * it + 1]) << 16) + (static_cast<uint64_t>(side_limb[3 * it + 2]) << 32);
+      if (lane == 0) d.sweep_total[it] = t;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kDrawBatch; j++) {
+      if (b0 + j >= n_sweeps || found >= 0) break;
+      const int it = forward ? b0 + j : n_sweeps - 1 - (b0 + j);
+      const uint64_t t = d.sweep_total[it];
+      if (run + t > tt) { found = it; before = run; found_total = t; }
+      run += t;
+    }
+  }
+  if (found < 0) return -1;                                                 // cannot happen: the sweeps sum to `total`
+  // ---- inside the sweep: the first cumulative weight, in index order, that exceeds the target ----------------------------
+  const uint64_t prefix = forward ? before : total - before - found_total;  // the weight of everything before the sweep
+  const uint64_t local_target = target - prefix;
+  {
+    const int c = found * kBlock + tid;
+    float z[kChunk];
+    const uint32_t mask = kept_chunk(rv, c, tau, tau2, z);
+    uint64_t w[kChunk];
+    uint64_t sum = 0ull;
+#pragma unroll
+    for (int e = 0; e < kChunk; e++) { w[e] = ((mask >> e) & 1u) ? weight_q40(z[e], vmax, c2) : 0ull; sum += w[e]; }
+    const uint64_t excl = block_exclusive_scan_u64(sum, d.scratch, nullptr);
+    if (excl <= local_target && local_target < excl + sum) {
+      uint64_t r = excl;
+#pragma unroll
+      for (int e = 0; e < kChunk; e++) { r += w[e]; if (w[e] && r > local_target) { d.token = c * kChunk + e; break; } }
+    }
+  }
+  __syncthreads();
+  return d.token;
+}
+
 // `next` is the row this block takes after this one (-1: none): it is pulled into L2 while this one is worked on.
-__device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem& s, uint32_t* punt) {
+// A row the kernel cannot take is appended to `redo` (length in *n_redo) for the generic kernel.
+__device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem& s, int* redo, int* n_redo) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int V = P.vocab;
   const float T = P.temperature ? P.temperature[row] : P.temperature_s;
@@ -275,7 +390,7 @@ __device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem&
   const uint16_t* rowp = reinterpret_cast<const uint16_t*>(P.logits) + static_cast<size_t>(row) * static_cast<size_t>(P.row_stride);
   const bool pen_on = P.history != nullptr;
   const bool takeable = (V % kChunk) == 0 && V <= kFastMaxVocab && (reinterpret_cast<uintptr_t>(rowp) & 15u) == 0 && (T >= 0.0f) && V > 0;
-  if (!takeable) { if (tid == 0) punt[row] = 1u; return; }
+  if (!takeable) { if (tid == 0) redo[atomicAdd(n_redo, 1)] = row; return; }
 
 #ifdef LM_PROFILE_PHASES
   long long _t0 = clock64();
@@ -333,7 +448,7 @@ __device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem&
     __syncthreads();
   }
   LM_PHASE(0);
-  if (s.side_n > kSideCap) { if (tid == 0) punt[row] = 1u; return; }      // more distinct penalised ids than the list holds
+  if (s.side_n > kSideCap) { if (tid == 0) redo[atomicAdd(n_redo, 1)] = row; return; }      // more distinct penalised ids than the list holds
   const uint32_t n_side = s.side_n;
   const SideList side{s.side_idx, s.side_val, n_side};
 
@@ -360,7 +475,6 @@ __device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem&
       P.out_tokens[row] = static_cast<int>(best_index(best));
       if (P.out_tau) P.out_tau[row] = -INFINITY;
       if (P.out_status) P.out_status[row] = (best_value(best) != best_value(best)) ? LM_STATUS_NAN : 0u;
-      punt[row] = 0u;
     }
     return;
   }
@@ -458,7 +572,7 @@ __device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem&
   if (tid < kGroups) total_c = s.gcnt[tid];
   total_c = static_cast<uint32_t>(block_sum_u64(total_c, s.draw.scratch));
   if (total_c + n_side != static_cast<uint32_t>(V)) {                     // a 16-bit counter wrapped: more than 65535 equal logits
-    if (tid == 0) punt[row] = 1u;
+    if (tid == 0) redo[atomicAdd(n_redo, 1)] = row;
     return;
   }
   uint32_t status = 0u;
@@ -525,7 +639,7 @@ __device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem&
     }
     if (has_p) refine_group<false, true>(s, s.sel_group, s.sel_base_c, base_m, static_cast<uint32_t>(top_k), 0.0, vmax, inv_t);
     else refine_group<false, false>(s, s.sel_group, s.sel_base_c, 0.0, static_cast<uint32_t>(top_k), 0.0, vmax, inv_t);
-    if (s.res_fail) { if (tid == 0) punt[row] = 1u; return; }
+    if (s.res_fail) { if (tid == 0) redo[atomicAdd(n_redo, 1)] = row; return; }
     tau64 = s.res_tau; have_tau = true;
     topk_mass = s.res_cum_m; above_k_mass = s.res_above_m;
     __syncthreads();
@@ -543,7 +657,7 @@ __device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem&
     if (!has_k || above_k_mass >= target) {
       find_group<true>(s, 0u, target);
       refine_group<true, true>(s, s.sel_group, s.sel_base_c, s.sel_base_m, 0u, target, vmax, inv_t);
-      if (s.res_fail) { if (tid == 0) punt[row] = 1u; return; }
+      if (s.res_fail) { if (tid == 0) redo[atomicAdd(n_redo, 1)] = row; return; }
       const double eps = 1e-12 * total;
       if (fabs(s.res_cum_m - target) <= eps) status |= LM_STATUS_TOPP_EDGE;
       if (!have_tau || static_cast<double>(s.res_tau) > tau64) tau64 = s.res_tau;
@@ -562,7 +676,7 @@ __device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem&
   // ---- pass 2: the draw over the kept set (the row is in L2) ---------------------------------------------------------
   int token;
   if (P.draw == LM_DRAW_INVERSE_CDF) {
-    token = draw_inverse_cdf<true>(rv, tau, vmax, T, P.uniforms ? P.uniforms[row] : 0.0f, s.draw, side, &s.sweep_part[0][0], &s.side_limb[0][0]);
+    token = draw_inverse_cdf_bidir(rv, s, side, tau, vmax, T, P.uniforms ? P.uniforms[row] : 0.0f);
   } else {
     bool tie = false;
     token = draw_gumbel<true>(rv, tau, T, P.seed, P.step, static_cast<uint32_t>(P.row_offset + row), s.draw, &tie, side);
@@ -573,7 +687,6 @@ __device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem&
     P.out_tokens[row] = token;
     if (P.out_tau) P.out_tau[row] = tau;
     if (P.out_status) P.out_status[row] = status;
-    punt[row] = 0u;
   }
 }
 

@@ -21,7 +21,6 @@ struct SampleDev {              // lm_sample_args without the host-only fields
   const int32_t* history; int hist_len; int64_t hist_stride; float rho, pi;
   const float* uniforms; uint64_t seed; uint32_t step; int64_t row_offset;
   int32_t* out_tokens; float* out_tau; float* out_stats; float* out_probs; int64_t probs_stride; uint32_t* out_status;
-  const uint32_t* row_select;   // optional [rows] mask from an earlier kernel: process only rows with a non-zero entry
 };
 
 constexpr uint32_t kStatusBadParam = 16u;

@@ -26,18 +26,26 @@ constexpr int kTopkBins = 512;             // BF16 codes above the cutoff that t
 constexpr int kTopkMaxK = 1024;            // largest top_k this kernel takes
 constexpr int kTopkHist = 2048;            // longest history it takes
 constexpr int kTopkMaxVocab = 1 << 18;
+constexpr int kMaxProbes = 24;             // probes of the cutoff search per row (2 for the bracket + 15 for a full bisection)
 constexpr int kBinSortMax = 256;           // a code bin with more candidates than this must already be in order (all equal)
 constexpr int kSampleChunks = 1024 / kTB;   // chunks per thread in the cutoff sample: 1024 chunks = 8192 logits
 constexpr int kTopkMinVocab = 32768;
 constexpr int kIdxBuckets = 1024;          // the draw buckets candidates by index >> 8: vocabularies up to 2^18
 
+constexpr int kStages = 4;                 // 16-byte asynchronous copies in flight per thread during the pass
+
 struct TopkSmem {
-  unsigned long long key[kTopkCap];        // candidates as (monotone value key << 32) | ~index, arrival order; later the index-sort keys
-  unsigned long long sel[kTopkCap];        // those at or above the coarse top-k crossing, sorted: value descending, index ascending
+  union {
+    struct {
+      unsigned long long key[kTopkCap];    // candidates as (monotone value key << 32) | ~index, arrival order; later the draw's index buckets
+      unsigned long long sel[kTopkCap];    // those at or above the top-k crossing, in descending value order
+    };
+    uint4 ring[kStages][kTB];              // during the pass: each thread's own landing slots for its chunks of the row
+  };
   union {
     double cum[kTopkCap];                  // FP64 softmass prefix over sel ...
     unsigned long long w[kTopkCap];        // ... then the fixed-point weights of the kept prefix
-    struct { uint32_t side_id[kTopkHist]; uint16_t side_raw[kTopkHist]; };   // before either: the distinct history ids and their raw logits
+    uint32_t side_id[kTopkHist];           // before either: the distinct history ids
   };
   uint32_t pen[kTopkMaxVocab / 32];        // bitmap of the row's distinct history ids
   uint32_t hitlist[2048];                  // (chunk << 8 | 8-bit mask) of the chunks that hold a logit >= cutoff
@@ -45,7 +53,9 @@ struct TopkSmem {
   uint32_t off[kTopkBins];                 // candidates in the bins above each bin
   uint64_t scratch[32];
   double warp_d[kTW];
-  uint32_t warp_u[2][kTW];
+  uint32_t warp_u[kTW];
+  uint32_t probe_cnt[kMaxProbes];          // block totals of the cutoff search, one slot per probe
+  uint32_t prev_cut[8];                    // the block's last cutoff per size class of the candidate target (0: none yet)
   float warp_f[kTW];
   unsigned long long base;
   uint32_t n_hit, n, n_side, wide, cross_bin;
@@ -59,6 +69,18 @@ static_assert(kTopkPerSM * (sizeof(TopkSmem) + 1024) <= 233472, "the blocks of t
 #else
 #define LM_TPHASE(i) do {} while (0)
 #endif
+#if defined(LM_PROFILE_PHASES) && defined(LM_PROFILE_SUB)
+#define LM_TSUB(i) LM_TPHASE(i)
+#else
+#define LM_TSUB(i) do {} while (0)
+#endif
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void prefetch_l2_line(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 __device__ __forceinline__ float ex2_approx(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ int next_pow2(int n) { int p = 32; while (p < n) p <<= 1; return p; }
@@ -129,7 +151,8 @@ __device__ __forceinline__ uint32_t warp_reserve(uint32_t* counter, uint32_t min
 
 // One row. Every thread of the block calls with the same arguments; returns true when the row is finished, false when the
 // histogram kernel has to take it (nothing has been written then).
-__device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
+// `next` is the row this block takes afterwards (-1: none): its sample and history are pulled into L2 meanwhile.
+__device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int V = P.vocab;
   const float T = P.temperature ? P.temperature[row] : P.temperature_s;
@@ -152,6 +175,21 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
 #ifdef LM_PROFILE_PHASES
   long long _t0 = clock64();
 #endif
+  // the first chunks of the pass do not depend on the cutoff: they start now and land in this thread's slots
+  const int n_it = (n_chunks + kTB - 1) / kTB;
+#pragma unroll
+  for (int it = 0; it < kStages - 1; it++) {
+    if (it * kTB + tid < n_chunks) cp_async16(&c.ring[it][tid], p4 + it * kTB + tid);
+    cp_async_commit();
+  }
+  if (next >= 0) {
+    const uint4* np4 = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(P.logits) + static_cast<size_t>(next) * static_cast<size_t>(P.row_stride));
+    if ((tid & 7) == 0) {                                                   // one prefetch per 128-byte line of the sample runs
+#pragma unroll
+      for (int j = 0; j < kSampleChunks; j++) prefetch_l2_line(np4 + tid + j * (n_chunks / kSampleChunks));
+    }
+    if (pen_on && tid * 32 < P.hist_len) prefetch_l2_line(P.history + static_cast<int64_t>(next) * P.hist_stride + tid * 32);
+  }
   // ---- the cutoff sample goes out first; the bitmap and the list of the history's distinct ids are built under its latency ---
   // (runs of chunks spread over the row: token ids are not exchangeable in a real vocabulary)
   uint4 qs[kSampleChunks];
@@ -165,15 +203,15 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
     hid[j] = (pen_on && i < P.hist_len) ? __ldg(P.history + static_cast<int64_t>(row) * P.hist_stride + i) : -1;
   }
   for (int i = tid; i < kTopkBins; i += kTB) c.bins[i] = 0u;
+  if (tid < kMaxProbes) c.probe_cnt[tid] = 0u;
   if (pen_on) {
     uint4* p = reinterpret_cast<uint4*>(c.pen);
     for (int i = tid; i < (V + 127) / 128; i += kTB) p[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   if (tid == 0) { c.n_hit = 0u; c.n = 0u; c.n_side = 0u; c.wide = 0u; c.hit = kTopkCap; c.token = -1; c.cross_bin = 0u; }
   __syncthreads();
-  // the thread that sets an id's bit owns the id: it lists it and fetches its raw logit (stored once the cutoff is known,
-  // long after the load has come back)
-  uint32_t side_slot[kHistPer]; uint16_t side_raw[kHistPer];
+  LM_TSUB(0);
+  // the thread that sets an id's bit owns the id and lists it
 #pragma unroll
   for (int j = 0; j < kHistPer; j++) {
     const int id = hid[j];
@@ -182,20 +220,22 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
       const uint32_t bit = 1u << (id & 31);
       fresh = (atomicOr(&c.pen[id >> 5], bit) & bit) == 0u;
     }
-    side_slot[j] = warp_reserve(&c.n_side, fresh ? 1u : 0u);
-    side_raw[j] = fresh ? __ldg(rowp + id) : static_cast<uint16_t>(0u);
-    if (fresh) c.side_id[side_slot[j]] = static_cast<uint32_t>(id); else side_slot[j] = 0xFFFFFFFFu;
+    const uint32_t slot = warp_reserve(&c.n_side, fresh ? 1u : 0u);
+    if (fresh) c.side_id[slot] = static_cast<uint32_t>(id);
   }
+  LM_TSUB(1);
   // ---- the cutoff: the largest positive BF16 code with at least `want` of the 8192 sampled logits at or above it ---------
   // (about 1.3 k + 150 candidates expected in the whole row, at most ~1500)
+  // A bisection over the codes, one barrier per probe; it starts from a bracket around the cutoff of the block's last
+  // row of the same size class, which usually holds (rows of one batch come from one model), and costs ~7 probes then.
   uint32_t cut_code;
   {
     const int n_target = min(1500, top_k + top_k / 3 + 150);
     const uint32_t want = max(8u, static_cast<uint32_t>((static_cast<long long>(n_target) * kSampleChunks * kTB * kChunk + V - 1) / V));
-    uint32_t lo = 0x0000u, hi = 0x7F7Fu;                                    // invariant: count(sample >= lo) >= want, or lo is still 0 (handed back below)
-    for (int it = 0; it < 16; it++) {
-      const uint32_t mid = (lo + hi + 1u) >> 1;
-      const uint32_t m2 = mid | (mid << 16);
+    const int cls = min(31 - __clz(want), 7);
+    int probe = 0;
+    auto count_ge = [&](uint32_t code) -> uint32_t {                        // sampled logits at or above `code`; every thread calls
+      const uint32_t m2 = code | (code << 16);
       const __nv_bfloat162 t2 = *reinterpret_cast<const __nv_bfloat162*>(&m2);
       uint32_t cnt = 0;
 #pragma unroll
@@ -203,22 +243,32 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
         cnt += __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].x), t2)) + __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].y), t2)) +
                __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].z), t2)) + __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].w), t2));
       }
-      cnt >>= 4;                                                            // 16 mask bits per logit
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(kFull, cnt, o);
-      if (lane == 0) c.warp_u[it & 1][warp] = cnt;                        // two buffers: a warp is never more than one step ahead
+      cnt = __reduce_add_sync(kFull, cnt >> 4);                             // 16 mask bits per logit
+      if (lane == 0 && cnt) atomicAdd(&c.probe_cnt[probe], cnt);
       __syncthreads();
-      uint32_t total = 0;
-      for (int w = 0; w < kTW; w++) total += c.warp_u[it & 1][w];
-      if (total >= want) lo = mid; else hi = mid - 1u;
-      if (lo >= hi) break;
+      return c.probe_cnt[probe++];
+    };
+    uint32_t lo = 0x0000u, hi = 0x7F7Fu;                                    // invariant: count(sample >= lo) >= want, or lo is still 0 (handed back below)
+    const uint32_t prev = c.prev_cut[cls];
+    if (prev >= 0x0080u) {
+      const uint32_t blo = max(prev, 0x0090u) - 16u, bhi = min(prev + 15u, 0x7F7Fu);
+      const uint32_t ca = count_ge(blo), cb = bhi < 0x7F7Fu ? count_ge(bhi + 1u) : 0u;
+      if (ca < want) hi = blo - 1u;
+      else if (cb >= want) lo = bhi + 1u;
+      else { lo = blo; hi = bhi; }
     }
+    LM_TSUB(2);
+    while (lo < hi && probe < kMaxProbes) {
+      const uint32_t mid = (lo + hi + 1u) >> 1;
+      if (count_ge(mid) >= want) lo = mid; else hi = mid - 1u;
+    }
+    LM_TSUB(3);
     cut_code = lo;
-    if (cut_code < 0x0080u) return false;                                   // fewer positive logits than candidates wanted: not this kernel's row
+    if (cut_code < 0x0080u || lo < hi) { cp_async_wait<0>(); return false; }   // fewer positive logits than candidates wanted: not this kernel's row
+                                                                            // (the copies in flight must land before the slots are used again)
+    if (tid == 0) c.prev_cut[cls] = cut_code;
   }
   const float cut_val = __uint_as_float(cut_code << 16);
-#pragma unroll
-  for (int j = 0; j < kHistPer; j++) if (side_slot[j] != 0xFFFFFFFFu) c.side_raw[side_slot[j]] = side_raw[j];
   LM_TPHASE(8);
 
   // ---- the one pass: note the chunks that hold a logit >= cutoff; FP32 softmass with a per-thread running maximum ---------
@@ -227,47 +277,49 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
   {
     const uint32_t cut2 = cut_code | (cut_code << 16);
     const __nv_bfloat162 t2 = *reinterpret_cast<const __nv_bfloat162*>(&cut2);
-    constexpr int kUnroll = 4;
-    for (int base = 0; base < n_chunks; base += kTB * kUnroll) {            // uniform trip count: warp votes inside
-      const int c0 = base + tid;
-      uint4 q[kUnroll];
-#pragma unroll
-      for (int j = 0; j < kUnroll; j++) { const int cc = c0 + j * kTB; q[j] = (cc < n_chunks) ? __ldg(p4 + cc) : make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u); }
-#pragma unroll
-      for (int j = 0; j < kUnroll; j++) {
-        const int cc = c0 + j * kTB;
-        const bool live = cc < n_chunks;                                    // warp-uniform control flow below: votes inside
-        const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
-        const uint32_t m0 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[0]), t2), m1 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[1]), t2);
-        const uint32_t m2 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[2]), t2), m3 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[3]), t2);
-        const bool hit = live && (m0 | m1 | m2 | m3) != 0u;
-        const uint32_t votes = __ballot_sync(kFull, hit);
-        if (votes) {                                                        // one reservation per warp for all its hit chunks
-          uint32_t base = 0u;
-          if (lane == 0) base = atomicAdd(&c.n_hit, __popc(votes));
-          base = __shfl_sync(kFull, base, 0);
-          if (hit) {
-            const uint32_t mask = (m0 & 1u) | ((m0 >> 15) & 2u) | ((m1 & 1u) << 2) | ((m1 >> 13) & 8u) | ((m2 & 1u) << 4) | ((m2 >> 11) & 32u) |
-                                  ((m3 & 1u) << 6) | ((m3 >> 9) & 128u);
-            const uint32_t slot = base + __popc(votes & ((1u << lane) - 1u));
-            if (slot < 2048u) c.hitlist[slot] = (static_cast<uint32_t>(cc) << 8) | mask;
-          }
+    const uint4 pad = make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);   // -inf
+#pragma unroll 4
+    for (int it = 0; it < n_it; it++) {                                     // uniform trip count: warp votes inside
+      {
+        const int ahead = it + kStages - 1, ca = ahead * kTB + tid;         // refill the slot read one step ago
+        if (ca < n_chunks) cp_async16(&c.ring[ahead % kStages][tid], p4 + ca);
+        cp_async_commit();
+      }
+      cp_async_wait<kStages - 1>();                                         // this step's chunk has landed
+      const int cc = it * kTB + tid;
+      const bool live = cc < n_chunks;                                      // warp-uniform control flow below: votes inside
+      const uint4 q = live ? c.ring[it % kStages][tid] : pad;
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      const uint32_t m0 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[0]), t2), m1 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[1]), t2);
+      const uint32_t m2 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[2]), t2), m3 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[3]), t2);
+      const bool hit = live && (m0 | m1 | m2 | m3) != 0u;
+      const uint32_t votes = __ballot_sync(kFull, hit);
+      if (votes) {                                                          // one reservation per warp for all its hit chunks
+        uint32_t base = 0u;
+        if (lane == 0) base = atomicAdd(&c.n_hit, __popc(votes));
+        base = __shfl_sync(kFull, base, 0);
+        if (hit) {
+          const uint32_t mask = (m0 & 1u) | ((m0 >> 15) & 2u) | ((m1 & 1u) << 2) | ((m1 >> 13) & 8u) | ((m2 & 1u) << 4) | ((m2 >> 11) & 32u) |
+                                ((m3 & 1u) << 6) | ((m3 >> 9) & 128u);
+          const uint32_t slot = base + __popc(votes & ((1u << lane) - 1u));
+          if (slot < 2048u) c.hitlist[slot] = (static_cast<uint32_t>(cc) << 8) | mask;
         }
-        const __nv_bfloat162 a = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[0]), *reinterpret_cast<const __nv_bfloat162*>(&w[1]));
-        const __nv_bfloat162 b = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[2]), *reinterpret_cast<const __nv_bfloat162*>(&w[3]));
-        const __nv_bfloat162 ab = __hmax2_nan(a, b);
-        nan_seen |= ~__heq2_mask(ab, ab);                                   // a NaN anywhere in the chunk survives the maxima
-        if (need_z && live) {
-          const float mx = fmaxf(__low2float(ab), __high2float(ab));
-          if (mx > m) { const float r = (m > -INFINITY) ? ex2_approx((m - mx) * c2a) : 0.0f; sacc0 *= r; sacc1 *= r; m = mx; }
-          if (m > -INFINITY) {
-            const float nb = -m * c2a;
+      }
+      const __nv_bfloat162 a = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[0]), *reinterpret_cast<const __nv_bfloat162*>(&w[1]));
+      const __nv_bfloat162 b = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[2]), *reinterpret_cast<const __nv_bfloat162*>(&w[3]));
+      const __nv_bfloat162 ab = __hmax2_nan(a, b);
+      nan_seen |= ~__heq2_mask(ab, ab);                                     // a NaN anywhere in the chunk survives the maxima
+      if (need_z && live) {
+        const float mx = fmaxf(__low2float(ab), __high2float(ab));
+        if (mx > m) { const float r = (m > -INFINITY) ? ex2_approx((m - mx) * c2a) : 0.0f; sacc0 *= r; sacc1 *= r; m = mx; }
+        if (m > -INFINITY) {
+          const float nb = -m * c2a;
 #pragma unroll
-            for (int k = 0; k < 4; k++) { sacc0 += ex2_approx(fmaf(bf16_lo(w[k]), c2a, nb)); sacc1 += ex2_approx(fmaf(bf16_hi(w[k]), c2a, nb)); }
-          }
+          for (int k = 0; k < 4; k++) { sacc0 += ex2_approx(fmaf(bf16_lo(w[k]), c2a, nb)); sacc1 += ex2_approx(fmaf(bf16_hi(w[k]), c2a, nb)); }
         }
       }
     }
+    cp_async_wait<0>();
   }
   LM_TPHASE(9);
   // block maximum of the running maxima
@@ -314,20 +366,30 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
   LM_TPHASE(15);
   // ---- the penalised logits, from the list ---------------------------------------------------------------------------------
   if (pen_on) {
+    // their raw logits are fetched now, after the pass: the row has just gone through L2
     const uint32_t n_side = c.n_side;
-    for (uint32_t i0 = 0; i0 < n_side; i0 += kTB) {                         // uniform trip count
-      const uint32_t i = i0 + tid;
-      float v = -INFINITY; uint32_t id = 0u;
+    constexpr int kGather = kTopkHist / kTB;
+    uint32_t ids[kGather]; uint16_t raws[kGather];
+#pragma unroll
+    for (int j = 0; j < kGather; j++) {
+      const uint32_t i = j * kTB + tid;
+      ids[j] = i < n_side ? c.side_id[i] : 0u;
+      raws[j] = __ldg(rowp + ids[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < kGather; j++) {
+      const uint32_t i = j * kTB + tid;
+      if (j * kTB >= n_side) break;                                         // block-uniform
+      float v = -INFINITY;
       if (i < n_side) {
-        id = c.side_id[i];
-        const float raw = __uint_as_float(static_cast<uint32_t>(c.side_raw[i]) << 16);
+        const float raw = __uint_as_float(static_cast<uint32_t>(raws[j]) << 16);
         v = penalise(raw, P.rho, P.pi);
         if (need_z) zsum += static_cast<double>(ex2_approx((v - M) * c2a)) - static_cast<double>(ex2_approx((raw - M) * c2a));
       }
       const bool cand = v >= cut_val;
       const uint32_t slot = warp_reserve(&c.n, cand ? 1u : 0u);
       if (cand) {
-        if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(v)) << 32) | (0xFFFFFFFFu - id);
+        if (slot < kTopkCap) c.key[slot] = (static_cast<unsigned long long>(fkey(v)) << 32) | (0xFFFFFFFFu - ids[j]);
         const uint32_t rel = (__float_as_uint(v) >> 16) - cut_code;
         if (rel >= kTopkBins) c.wide = 1u; else atomicAdd(&c.bins[rel], 1u);
       }
@@ -350,9 +412,9 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
     uint32_t incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
-    if (lane == 31) c.warp_u[0][warp] = incl;
+    if (lane == 31) c.warp_u[warp] = incl;
     __syncthreads();
-    for (int w = 0; w < warp; w++) run += c.warp_u[0][w];
+    for (int w = 0; w < warp; w++) run += c.warp_u[w];
     uint32_t acc = run + incl - mine;
 #pragma unroll
     for (int j = 0; j < kPer; j++) {
@@ -518,21 +580,24 @@ __device__ bool topk_row(const SampleDev& P, int row, TopkSmem& c) {
 }
 
 // Rows are handed out through a counter in the workspace (counters[0], zeroed by the host before the launch): a block takes
-// the next row and either finishes it (punt[row] = 0: no later kernel touches it) or appends it to `list` (length in
+// the next row and either finishes it (no later kernel touches it) or appends it to `list` (length in
 // counters[1]) for the histogram kernel. The order of the list varies from run to run; what is computed per row does not.
-__global__ void __launch_bounds__(kTB, kTopkPerSM) sample_topk_kernel(SampleDev P, uint32_t* punt, int* list, int* counters) {
+__global__ void __launch_bounds__(kTB, kTopkPerSM) sample_topk_kernel(SampleDev P, int* list, int* counters) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   TopkSmem& c = *reinterpret_cast<TopkSmem*>(smem_raw);
+  __shared__ int item[2];                                                   // the row in hand and the one after it
+  if (threadIdx.x < 8) c.prev_cut[threadIdx.x] = 0u;
+  if (threadIdx.x == 0) { item[0] = atomicAdd(&counters[0], 1); item[1] = item[0] < P.rows ? atomicAdd(&counters[0], 1) : P.rows; }
+  __syncthreads();
   for (;;) {
-    __syncthreads();
-    if (threadIdx.x == 0) c.row = atomicAdd(&counters[0], 1);
-    __syncthreads();
-    const int row = c.row;
+    const int row = item[0], next = item[1];
     if (row >= P.rows) break;
-    const bool done = topk_row(P, row, c);
+    __syncthreads();
+    if (threadIdx.x == 0) { item[0] = next; item[1] = next < P.rows ? atomicAdd(&counters[0], 1) : P.rows; }
+    const bool done = topk_row(P, row, next < P.rows ? next : -1, c);
     __syncthreads();
     if (threadIdx.x == 0) {
-      if (done) punt[row] = 0u; else list[atomicAdd(&counters[1], 1)] = row;
+      if (!done) list[atomicAdd(&counters[1], 1)] = row;
     }
   }
 }
