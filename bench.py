@@ -48,10 +48,10 @@ def peaks():
 
 
 def ncu_traffic():
-    """DRAM bytes per row of the sampler kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of 512 of
-    the workload's rows; traffic grows in proportion to the rows, so a launch's traffic is this times its rows). The
-    capture is summarised in profiles/sample_fast_kernel_512rows_ncu_full.md."""
-    return {"dram_bytes_per_row": (181828096 + 10442240) / 512}
+    """DRAM bytes per row of one sampling call (dram__bytes_read.sum + dram__bytes_write.sum, summed over the top-k kernel and
+    the histogram kernel, of one ncu capture of 888 of the workload's rows; traffic grows in proportion to the rows, so a
+    call's traffic is this times its rows). The capture is summarised in profiles/sample_kernels_888rows_ncu_full.md."""
+    return {"dram_bytes_per_row": (224220416 + 3980032 + 72878848 + 2363392) / 888}
 
 
 class ClockSampler:
@@ -242,7 +242,9 @@ def main() -> None:
            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                         "frac_of_nominal_8TBs": achieved / 8000.0, "algorithmic_bytes_per_row": ROW_BYTES,
                         "traffic": (traffic["dram_bytes_per_row"] * rows if traffic else None)},
-           "gpu_launches": 2 * args.steps, "clocks": clocks.summary()}
+           "gpu_launches": 3 * args.steps, "clocks": clocks.summary()}
+    out["roofline"]["launch"] = ("one sampling call = sample_topk_kernel (rows with a top_k) + sample_fast_kernel (the other rows) + "
+                                 "sample_generic_kernel (rows handed on: none here); duration = CUDA events around the call")
 
     if not args.skip_extras:
         # ---- e2e: host (pinned) inputs -> public API -> tokens on the host, copies inside the timed region

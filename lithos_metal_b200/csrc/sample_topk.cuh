@@ -69,6 +69,10 @@ static_assert(kTopkPerSM * (sizeof(TopkSmem) + 1024) <= 233472, "the blocks of t
 #else
 #define LM_TPHASE(i) do {} while (0)
 #endif
+#ifdef LM_STOP_AFTER
+#undef LM_TPHASE
+#define LM_TPHASE(i) do { if ((i) == LM_STOP_AFTER) { cp_async_wait<0>(); __syncthreads(); return true; } } while (0)
+#endif
 #if defined(LM_PROFILE_PHASES) && defined(LM_PROFILE_SUB)
 #define LM_TSUB(i) LM_TPHASE(i)
 #else
