@@ -455,6 +455,9 @@ int lm_verify(const lm_verify_args* a) {
   P.ws = static_cast<VerifyWs*>(a->workspace);
   // one block per SM, all resident at once (the phases meet at a grid barrier): a cooperative launch guarantees it
   int grid = sms < 1024 ? sms : 1024;
+#ifdef LM_VERIFY_GRID_DIV
+  grid = grid / LM_VERIFY_GRID_DIV > 0 ? grid / LM_VERIFY_GRID_DIV : 1;
+#endif
   const int max_useful = static_cast<int>((a->vocab + 7) / 8);
   if (grid > max_useful) grid = max_useful;
   // the block's slices of all rows in shared memory when they fit (they do for every vocabulary up to ~700k at 148 SMs)

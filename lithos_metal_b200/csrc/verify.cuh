@@ -85,6 +85,8 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   extern __shared__ __align__(16) float v_smem[];
   __shared__ uint64_t scratch[32];
   __shared__ int s_j, s_token;
+  __shared__ int s_drafts[kVerifyMaxRows];
+  __shared__ unsigned long long s_best[kVerifyMaxRows], s_mass[kVerifyMaxRows];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, G = gridDim.x, b = blockIdx.x;
   constexpr int kWarps = kVerifyBlock / 32;
   const int R = P.n_draft + 1, V = P.vocab;
@@ -105,30 +107,68 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   // then row maxima with their lowest index (which is also the greedy pick).
   // the scalars the accept test needs later are fetched now, so their latency hides behind the slice loads
   int my_draft = -1; float my_q = 0.0f, my_u = 0.0f;
+  if (tid < P.n_draft) { my_draft = P.drafts[tid]; s_drafts[tid] = my_draft; }
   if (stochastic && tid < P.n_draft) {
-    my_draft = P.drafts[tid];
     my_u = P.u_accept[tid];
     if (my_draft >= 0 && my_draft < V) my_q = __ldg(P.q + static_cast<int64_t>(tid) * P.q_stride + my_draft);
   }
   const float c2 = stochastic ? exp2_scale(P.temperature) : 0.0f;
   if (cached) {
-    // row by row, up to eight rows' loads in flight per thread; rows R.. are the draft-probability rows
-    const int n_rows = R + (stochastic ? P.n_draft : 0);
-    for (int i = tid; i < len; i += kVerifyBlock) {
-      for (int r0 = 0; r0 < n_rows; r0 += 8) {
-        float v[8];
+    // 8 elements per load item (one 16-byte load of BF16 logits, two of FP32 logits or draft probabilities), every item of
+    // a thread issued before the first is used: the whole slice arrives in one memory round trip
+    const int n_q = stochastic ? P.n_draft : 0;
+    const int chunks = (len + 7) / 8;
+    const bool z_vec = (P.dtype == LM_DTYPE_BF16 ? (P.row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(P.target) & 15u) == 0)
+                                                 : (P.row_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(P.target) & 15u) == 0));
+    const bool q_vec = n_q == 0 || (P.q_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(P.q) & 15u) == 0);
+    const int n_items = (R + n_q) * chunks;
+    constexpr int kItems = 3;                                             // items in flight per thread
+    for (int i0 = 0; i0 < n_items; i0 += kItems * kVerifyBlock) {
+      float4 va[kItems], vb[kItems];
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
-          const int r = r0 + k;
-          if (r < R) v[k] = verify_load(P, r, lo + i);
-          else if (r < n_rows) v[k] = __ldg(P.q + static_cast<int64_t>(r - R) * P.q_stride + lo + i);
+      for (int k = 0; k < kItems; k++) {
+        const int item = i0 + k * kVerifyBlock + tid;
+        va[k] = make_float4(0.f, 0.f, 0.f, 0.f); vb[k] = va[k];
+        if (item >= n_items) continue;
+        const int r = item / chunks, c8 = (item - r * chunks) * 8;
+        const bool full = c8 + 8 <= len;
+        if (r < R) {
+          if (P.dtype == LM_DTYPE_BF16) {
+            const uint16_t* src = reinterpret_cast<const uint16_t*>(P.target) + static_cast<int64_t>(r) * P.row_stride + lo + c8;
+            if (full && z_vec) va[k] = __ldg(reinterpret_cast<const float4*>(src));      // eight BF16 codes, widened below
+          } else {
+            const float* src = reinterpret_cast<const float*>(P.target) + static_cast<int64_t>(r) * P.row_stride + lo + c8;
+            if (full && z_vec) { va[k] = __ldg(reinterpret_cast<const float4*>(src)); vb[k] = __ldg(reinterpret_cast<const float4*>(src) + 1); }
+          }
+        } else {
+          const float* src = P.q + static_cast<int64_t>(r - R) * P.q_stride + lo + c8;
+          if (full && q_vec) { va[k] = __ldg(reinterpret_cast<const float4*>(src)); vb[k] = __ldg(reinterpret_cast<const float4*>(src) + 1); }
         }
+      }
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
-          const int r = r0 + k;
-          if (r < R) zs[r * per + i] = v[k];
-          else if (r < n_rows) qs[(r - R) * per + i] = v[k];
+      for (int k = 0; k < kItems; k++) {
+        const int item = i0 + k * kVerifyBlock + tid;
+        if (item >= n_items) continue;
+        const int r = item / chunks, c8 = (item - r * chunks) * 8;
+        const bool full = c8 + 8 <= len;
+        float* dst = (r < R ? zs + r * per : qs + (r - R) * per) + c8;
+        const bool vec = full && (r < R ? z_vec : q_vec);
+        if (!vec) {                                                       // a ragged last chunk or an unaligned tensor: element by element
+          for (int e = 0; e < 8 && c8 + e < len; e++)
+            dst[e] = r < R ? verify_load(P, r, lo + c8 + e) : __ldg(P.q + static_cast<int64_t>(r - R) * P.q_stride + lo + c8 + e);
+          continue;
         }
+        float4 x = va[k], y = vb[k];
+        if (r < R && P.dtype == LM_DTYPE_BF16) {
+          const uint32_t w0 = __float_as_uint(va[k].x), w1 = __float_as_uint(va[k].y), w2 = __float_as_uint(va[k].z), w3 = __float_as_uint(va[k].w);
+          x = make_float4(bf16_lo(w0), bf16_hi(w0), bf16_lo(w1), bf16_hi(w1));
+          y = make_float4(bf16_lo(w2), bf16_hi(w2), bf16_lo(w3), bf16_hi(w3));
+        }
+        if (r < R) {
+          x = make_float4(canon_zero(x.x), canon_zero(x.y), canon_zero(x.z), canon_zero(x.w));
+          y = make_float4(canon_zero(y.x), canon_zero(y.y), canon_zero(y.z), canon_zero(y.w));
+        }
+        reinterpret_cast<float4*>(dst)[0] = x; reinterpret_cast<float4*>(dst)[1] = y;
       }
     }
     __syncthreads();
@@ -151,13 +191,14 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   LM_VSTAMP(3);
 
   if (!stochastic) {
-    if (b == 0 && tid == 0) {
-      int acc = 0;
-      while (acc < P.n_draft && static_cast<int>(best_index(ws_load(&ws->row_best[acc]))) == P.drafts[acc]) acc++;
-      const int fin = static_cast<int>(best_index(ws_load(&ws->row_best[acc])));
+    if (b == 0 && tid < 32) {                                              // one round trip for every row's pick, then a vote
+      const int pick = tid < R ? static_cast<int>(best_index(ws_load(&ws->row_best[tid]))) : -1;
+      const uint32_t miss = __ballot_sync(kFull, tid < P.n_draft && pick != s_drafts[tid]);
+      const int acc = miss ? (__ffs(miss) - 1) : P.n_draft;
+      const int fin = __shfl_sync(kFull, pick, acc);
       const bool bad = ws->error != 0;
-      P.out_accept[0] = bad ? -1 : acc; P.out_final[0] = bad ? -1 : fin;
-      if (P.out_tokens) for (int r = 0; r < R; r++) P.out_tokens[r] = r < acc ? P.drafts[r] : (r == acc ? fin : -1);
+      if (tid == 0) { P.out_accept[0] = bad ? -1 : acc; P.out_final[0] = bad ? -1 : fin; }
+      if (P.out_tokens && tid < R) P.out_tokens[tid] = tid < acc ? s_drafts[tid] : (tid == acc ? fin : -1);
     }
     // the last block to leave puts the workspace back to its clean state
     __syncthreads();
@@ -187,7 +228,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     if (lane == 0) {
       if (w) { atomicAdd(&part_w[static_cast<size_t>(r) * G + b], static_cast<unsigned long long>(w)); atomicAdd(&ws->row_mass[r], static_cast<unsigned long long>(w)); }
       if (part == 0 && r < P.n_draft) {
-        const int d = P.drafts[r];
+        const int d = s_drafts[r];
         if (d >= lo && d < hi) {
           const float z = S.z(r, d - lo);
           ws->draft_w[r] = (z >= tau) ? weight_q40(z, vmax, c2) : 0ull;
@@ -200,12 +241,15 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   LM_VSTAMP(5);
 
   // ---- phase 2: accept tests (every block, identically), then this slice's share of the residual mass -----------
-  if (tid < 32) {
+  if (tid < 32) {                                                           // every row's maximum and mass in one round trip
+    uint64_t best = 0ull, mass = 0ull, dw = 0ull;
+    if (tid < R) { best = ws_load(&ws->row_best[tid]); mass = ws_load(&ws->row_mass[tid]); }
+    if (tid < P.n_draft) dw = ws_load(&ws->draft_w[tid]);
+    if (tid < R) { s_best[tid] = best; s_mass[tid] = mass; }
     bool reject = false;
     if (tid < P.n_draft) {
       const int r = tid, d = my_draft;
-      const uint64_t k = ws_load(&ws->row_mass[r]);
-      const float pd = (d >= 0 && d < V && k > 0ull) ? prob_q40(ws_load(&ws->draft_w[r]), k) : 0.0f;
+      const float pd = (d >= 0 && d < V && mass > 0ull) ? prob_q40(dw, mass) : 0.0f;
       reject = __fmul_rn(my_u, my_q) >= pd;
       if (b == 0 && P.out_p_draft) P.out_p_draft[r] = pd;
     }
@@ -214,9 +258,9 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   }
   __syncthreads();
   const int j = s_j;
-  const float vmax_j = best_value(ws_load(&ws->row_best[j]));
+  const float vmax_j = best_value(s_best[j]);
   const float tau_j = P.tau ? P.tau[j] : -INFINITY;
-  const uint64_t mass_j = ws_load(&ws->row_mass[j]);
+  const uint64_t mass_j = s_mass[j];
   const bool has_q = j < P.n_draft;
   // residual weight of element i of this slice (0 when not kept or not positive)
   auto residual = [&](int i) -> uint64_t {
@@ -245,9 +289,15 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
       tot_r += vr;
       if (g < b) { pre_r += vr; pre_w += vw; }
     }
-    tot_r = block_sum_u64(tot_r, scratch);
-    pre_r = block_sum_u64(pre_r, scratch);
-    pre_w = block_sum_u64(pre_w, scratch);
+    {                                                                     // three sums, one pair of barriers
+      __shared__ uint64_t sums[3][32];
+      tot_r = warp_sum_u64(tot_r); pre_r = warp_sum_u64(pre_r); pre_w = warp_sum_u64(pre_w);
+      if (lane == 0) { sums[0][warp] = tot_r; sums[1][warp] = pre_r; sums[2][warp] = pre_w; }
+      __syncthreads();
+      tot_r = warp_sum_u64(lane < kWarps ? sums[0][lane] : 0ull);
+      pre_r = warp_sum_u64(lane < kWarps ? sums[1][lane] : 0ull);
+      pre_w = warp_sum_u64(lane < kWarps ? sums[2][lane] : 0ull);
+    }
     const bool use_res = tot_r > 0ull;                                   // an empty residual: draw from the row's own kept softmax
     const uint64_t total = use_res ? tot_r : mass_j;
     const uint64_t mine = use_res ? ws_load(&part_r[b]) : ws_load(&part_w[static_cast<size_t>(j) * G + b]);
