@@ -361,9 +361,15 @@ def bench_verify(torch, lm, dev):
     drafts[:3] = target[:3].float().argmax(-1).to(torch.int32)
     q = torch.softmax(target[:7].float() + torch.randn(7, VOCAB, generator=g, device=dev) * 0.5, dim=-1)
     ua, uf = torch.rand(7, generator=g, device=dev), torch.rand(1, generator=g, device=dev)
+    # the drafter's side of the same round: seven BF16 logits rows, sampled one position per call as a Markov drafter does
+    drafter = (target[:7].float() + torch.randn(7, VOCAB, generator=g, device=dev) * 0.5).to(torch.bfloat16)
+    stats = lm.draft_q(drafter, temperature=1.0, seed=SEED, step=0)
+    calls = {"stochastic": lambda: lm.verify(target, drafts, q, ua, uf, "stochastic"),
+             "stochastic_q_logits": lambda: lm.verify(target, stats.tokens, None, ua, uf, "stochastic", draft_logits=drafter, draft_stats=stats),
+             "greedy": lambda: lm.verify(target, drafts, mode="greedy"),
+             "draft_q_one_position": lambda: lm.draft_q(drafter[3:4], temperature=1.0, seed=SEED, step=0, first_position=3)}
     res = {}
-    for mode in ("stochastic", "greedy"):
-        call = (lambda: lm.verify(target, drafts, q, ua, uf, "stochastic")) if mode == "stochastic" else (lambda: lm.verify(target, drafts, mode="greedy"))
+    for mode, call in calls.items():
         for _ in range(3):
             call()
         torch.cuda.synchronize(dev)
@@ -399,6 +405,7 @@ def bench_verify(torch, lm, dev):
             res["timing"] = f"single launches, min of 20 (graph capture failed: {type(e).__name__})"
     res["bytes_algorithmic_min"] = 8 * VOCAB * 2 + VOCAB * 4
     res["bytes_one_pass"] = 8 * VOCAB * 2 + 7 * VOCAB * 4
+    res["bytes_one_pass_q_logits"] = 8 * VOCAB * 2 + 7 * VOCAB * 2
     return res
 
 

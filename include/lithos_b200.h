@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define LM_ABI_VERSION 1
+#define LM_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define LM_API __attribute__((visibility("default")))
@@ -157,12 +157,15 @@ LM_API int lm_argmax_static(const void* logits, int32_t dtype, int64_t rows, int
  *
  * Stands in for accept_scan's prefix match (kernels/common/spec_ops.metal:162-165) when mode == LM_VERIFY_GREEDY and for
  * spec_q_accept + spec_residual_partial/final (kernels/common/sample.metal:279-347, probabilities per spec_p, :273-276)
- * when mode == LM_VERIFY_STOCHASTIC, with the drafter's distribution given as probabilities and the uniforms supplied
- * by the caller.
+ * when mode == LM_VERIFY_STOCHASTIC, with the uniforms supplied by the caller and the drafter's distribution given either
+ * as probabilities (draft_probs) or, as the reference keeps it, as the drafter's BF16 logits rows with the row statistics
+ * lm_draft_q returned for them (draft_logits + draft_vmax + draft_mass; half the bytes).
  *
  * Row r < n_draft holds the target's distribution for the position draft r fills; row n_draft is the bonus row.
  *   greedy:     pick[r] = argmax row r; accept = longest prefix with pick[r] == draft[r]; final = pick[accept].
  *   stochastic: p_r = kept softmax of row r at `temperature` with threshold tau[r] (NULL = keep everything);
+ *               q[r, v] = draft_probs[r, v], or float32(W / draft_mass[r]) with W the fixed-point weight of
+ *               draft_logits[r, v] relative to draft_vmax[r] at `temperature` (the drafter's unfiltered softmax);
  *               reject r  <=>  float32(u_accept[r] * q[r, draft[r]]) >= p_r(draft[r]);  accept = first rejected r
  *               (n_draft if none); final = inverse-CDF draw with u_final over max(p - q, 0) of row `accept`
  *               (over p itself on the bonus row, or when the residual is empty).
@@ -194,11 +197,57 @@ typedef struct lm_verify_args {
   void* workspace;             /* lm_verify_workspace_bytes() bytes, 256-byte aligned, zero-filled once */
   size_t workspace_bytes;
   void* stream;
+  const void* draft_logits;    /* [n_draft, draft_logits_stride] BF16, used when draft_probs is NULL (stochastic) */
+  int64_t draft_logits_stride;
+  const float* draft_vmax;     /* [n_draft] row maxima from lm_draft_q */
+  const uint64_t* draft_mass;  /* [n_draft] fixed-point row masses from lm_draft_q */
 } lm_verify_args;
 
 #define LM_MAX_DRAFT 15
 
 LM_API int lm_verify(const lm_verify_args* args);
+
+/*
+ * Draft-side sampling: the draw of draft k from the drafter's logits row, and the row statistics the verify step needs to
+ * evaluate q_k(v) later.
+ *
+ * Stands in for draft_q_partial + draft_q_final (kernels/common/sample.metal:212-269). Row r of the call is draft
+ * position first_position + r:
+ *   token[r] = argmax_i ( z_i * float32(1/T) + gumbel(seed, step, 2000 + first_position + r, i) ), ties -> lowest index
+ *              (the reference's stream numbering, sample.metal:239): what lm_sample draws for an unfiltered row with
+ *              row_offset + row = 2000 + position;
+ *   vmax[r]  = max_i z_i;  mass[r] = sum_i floor(2^40 * exp2_fixed((z_i - vmax) * log2(e)/T)), the integer weights every
+ *              kernel of this library uses, so q_k(v) = float32(W_v / mass) is the same number on any GPU count or CPU;
+ *   lse[r]   = float32(vmax/T + ln(mass * 2^-40)): the reference's q_lse (log sum exp(z/T); it accumulates in FP32 in
+ *              an order that depends on its grid, so the two agree to ~1e-6 relative, not bit for bit);
+ *   out_q_logits (optional) receives a copy of the rows, as the reference keeps them in its state.
+ * BF16 or FP32 rows; 1..LM_MAX_DRAFT + 1 rows per call; temperature > 0. Workspace: lm_verify_workspace_bytes() bytes,
+ * 256-byte aligned, zero-filled once (it may be the verify step's workspace: the calls are stream-ordered).
+ */
+typedef struct lm_draft_q_args {
+  uint32_t struct_size;
+  int32_t dtype;
+  int32_t rows;
+  int32_t first_position;
+  const void* logits;          /* [rows, row_stride] */
+  int64_t vocab;
+  int64_t row_stride;
+  float temperature;
+  uint64_t seed;
+  uint32_t step;
+  int32_t* out_tokens;         /* [rows] */
+  float* out_lse;              /* [rows] or NULL */
+  float* out_vmax;             /* [rows] or NULL */
+  uint64_t* out_mass;          /* [rows] or NULL */
+  uint32_t* out_status;        /* [rows] LM_STATUS_NEAR_TIE / LM_STATUS_NAN bits, or NULL */
+  void* out_q_logits;          /* [rows, q_logits_stride] same dtype as logits, or NULL */
+  int64_t q_logits_stride;
+  void* workspace;
+  size_t workspace_bytes;
+  void* stream;
+} lm_draft_q_args;
+
+LM_API int lm_draft_q(const lm_draft_q_args* args);
 
 /*
  * Vocab-parallel sampling: every row's vocabulary is split into `shards` contiguous pieces, one per GPU.

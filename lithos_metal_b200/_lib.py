@@ -44,6 +44,16 @@ class VerifyArgs(C.Structure):
         ("temperature", C.c_float), ("tau", C.c_void_p), ("u_accept", C.c_void_p), ("u_final", C.c_void_p),
         ("out_accept", C.c_void_p), ("out_final", C.c_void_p), ("out_tokens", C.c_void_p), ("out_p_draft", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+        ("draft_logits", C.c_void_p), ("draft_logits_stride", C.c_int64), ("draft_vmax", C.c_void_p), ("draft_mass", C.c_void_p),
+    ]
+
+
+class DraftQArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("dtype", C.c_int32), ("rows", C.c_int32), ("first_position", C.c_int32), ("logits", C.c_void_p),
+        ("vocab", C.c_int64), ("row_stride", C.c_int64), ("temperature", C.c_float), ("seed", C.c_uint64), ("step", C.c_uint32),
+        ("out_tokens", C.c_void_p), ("out_lse", C.c_void_p), ("out_vmax", C.c_void_p), ("out_mass", C.c_void_p), ("out_status", C.c_void_p),
+        ("out_q_logits", C.c_void_p), ("q_logits_stride", C.c_int64), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
     ]
 
 
@@ -68,7 +78,7 @@ class VocabArgs(C.Structure):
     ]
 
 
-EXPORTS = ["lm_accept_scan", "lm_verify_select", "lm_advance", "lm_step_state_bytes", "lm_sample", "lm_argmax", "lm_argmax_static", "lm_vocab_local", "lm_vocab_merge", "lm_vocab_record_bytes", "lm_vocab_candidate_cap", "lm_verify", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
+EXPORTS = ["lm_accept_scan", "lm_verify_select", "lm_advance", "lm_step_state_bytes", "lm_sample", "lm_argmax", "lm_argmax_static", "lm_vocab_local", "lm_vocab_merge", "lm_vocab_record_bytes", "lm_vocab_candidate_cap", "lm_verify", "lm_draft_q", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
            "lm_error_string", "lm_last_cuda_error", "lm_device_sm_count"]
 
 _lib = None
@@ -90,6 +100,8 @@ def lib():
         L.lm_sample.argtypes = [C.POINTER(SampleArgs)]
         L.lm_verify.restype = C.c_int
         L.lm_verify.argtypes = [C.POINTER(VerifyArgs)]
+        L.lm_draft_q.restype = C.c_int
+        L.lm_draft_q.argtypes = [C.POINTER(DraftQArgs)]
         L.lm_argmax.restype = C.c_int
         L.lm_argmax.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
         L.lm_argmax_static.restype = C.c_int
@@ -115,7 +127,7 @@ def lib():
         L.lm_error_string.argtypes = [C.c_int]
         L.lm_last_cuda_error.restype = C.c_char_p
         L.lm_device_sm_count.restype = C.c_int
-        if L.lm_abi_version() != 1:
+        if L.lm_abi_version() != 2:
             raise RuntimeError("lithos_metal_b200: ABI version mismatch between the binding and the shared object")
         _lib = L
     return _lib

@@ -12,6 +12,7 @@
 #include "sample_fast.cuh"
 #include "sample_topk.cuh"
 #include "verify.cuh"
+#include "draft_q.cuh"
 #include "vocab_parallel.cuh"
 #include "spec_ops.cuh"
 
@@ -439,9 +440,11 @@ int lm_verify(const lm_verify_args* a) {
   if (a->n_draft < 1 || a->n_draft > LM_MAX_DRAFT) return LM_E_INVALID;
   if (!a->target_logits || !a->draft_ids || !a->out_accept || !a->out_final || a->vocab < 1 || a->row_stride < a->vocab) return LM_E_INVALID;
   if (a->vocab > LM_MAX_VOCAB) return LM_E_UNSUPPORTED;
-  if (a->mode == LM_VERIFY_STOCHASTIC &&
-      (!a->draft_probs || a->probs_stride < a->vocab || !a->u_accept || !a->u_final || !(a->temperature > 0.0f)))
-    return LM_E_INVALID;
+  if (a->mode == LM_VERIFY_STOCHASTIC) {
+    if (!a->u_accept || !a->u_final || !(a->temperature > 0.0f)) return LM_E_INVALID;
+    if (a->draft_probs) { if (a->probs_stride < a->vocab) return LM_E_INVALID; }
+    else if (!a->draft_logits || a->draft_logits_stride < a->vocab || !a->draft_vmax || !a->draft_mass) return LM_E_INVALID;
+  }
   if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) || a->workspace_bytes < lm_verify_workspace_bytes(a->n_draft, a->vocab))
     return LM_E_WORKSPACE;
   int sms = 0;
@@ -450,6 +453,8 @@ int lm_verify(const lm_verify_args* a) {
   VerifyDev P;
   P.mode = a->mode; P.dtype = a->dtype; P.n_draft = a->n_draft; P.vocab = static_cast<int>(a->vocab); P.row_stride = a->row_stride;
   P.target = a->target_logits; P.drafts = a->draft_ids; P.q = a->draft_probs; P.q_stride = a->probs_stride; P.temperature = a->temperature;
+  P.q_logits = static_cast<const uint16_t*>(a->draft_logits); P.q_logits_stride = a->draft_logits_stride;
+  P.q_vmax = a->draft_vmax; P.q_mass = reinterpret_cast<const unsigned long long*>(a->draft_mass);
   P.tau = a->tau; P.u_accept = a->u_accept; P.u_final = a->u_final;
   P.out_accept = a->out_accept; P.out_final = a->out_final; P.out_tokens = a->out_tokens; P.out_p_draft = a->out_p_draft;
   P.ws = static_cast<VerifyWs*>(a->workspace);
@@ -481,6 +486,49 @@ int lm_verify(const lm_verify_args* a) {
   const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(verify_kernel), dim3(grid), dim3(kVerifyBlock), params, smem,
                                                     static_cast<cudaStream_t>(a->stream));
 #endif
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+int lm_draft_q(const lm_draft_q_args* a) {
+  if (!a || a->struct_size != sizeof(lm_draft_q_args)) return LM_E_INVALID;
+  if (a->rows < 1 || a->rows > LM_MAX_DRAFT + 1 || a->first_position < 0 || (a->dtype != LM_DTYPE_BF16 && a->dtype != LM_DTYPE_F32)) return LM_E_INVALID;
+  if (!a->logits || !a->out_tokens || a->vocab < 1 || a->row_stride < a->vocab || !(a->temperature > 0.0f)) return LM_E_INVALID;
+  if (a->out_q_logits && a->q_logits_stride < a->vocab) return LM_E_INVALID;
+  if (a->vocab > LM_MAX_VOCAB) return LM_E_UNSUPPORTED;
+  if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) || a->workspace_bytes < lm_verify_workspace_bytes(a->rows, a->vocab))
+    return LM_E_WORKSPACE;
+  int sms = 0;
+  const int rc = sm_count(&sms);
+  if (rc != LM_OK) return rc;
+  DraftQDev P;
+  P.dtype = a->dtype; P.rows = a->rows; P.first_position = a->first_position; P.vocab = static_cast<int>(a->vocab); P.row_stride = a->row_stride;
+  P.logits = a->logits; P.temperature = a->temperature; P.seed = a->seed; P.step = a->step;
+  P.out_tokens = a->out_tokens; P.out_lse = a->out_lse; P.out_vmax = a->out_vmax; P.out_mass = reinterpret_cast<unsigned long long*>(a->out_mass);
+  P.out_status = a->out_status; P.out_q_logits = a->out_q_logits; P.q_logits_stride = a->q_logits_stride;
+  P.ws = static_cast<VerifyWs*>(a->workspace);
+  // one block per SM, all resident at once (one grid barrier), each holding its slice of every row in shared memory;
+  // more blocks than that never, fewer when the slices would not fit
+  int grid = sms < 1024 ? sms : 1024;
+#ifndef LM_DRAFTQ_PER_THREAD
+#define LM_DRAFTQ_PER_THREAD 4
+#endif
+  {
+    // a single row is ~150 logits per SM: fewer blocks with a few logits per thread meet sooner at the barrier
+    const long long want = (static_cast<long long>(a->rows) * a->vocab + kVerifyBlock * LM_DRAFTQ_PER_THREAD - 1) / (kVerifyBlock * LM_DRAFTQ_PER_THREAD);
+    if (want < grid) grid = static_cast<int>(want < 1 ? 1 : want);
+  }
+  const int per = (static_cast<int>((a->vocab + grid - 1) / grid) + 7) & ~7;
+  const size_t smem = static_cast<size_t>(a->rows) * static_cast<size_t>(per) * sizeof(float);
+  if (smem > 200 * 1024) return LM_E_UNSUPPORTED;                          // rows x vocabulary beyond what the SMs can hold between the phases
+  static thread_local size_t draft_smem_set = 0;
+  if (smem > 48 * 1024 && smem > draft_smem_set) {
+    const cudaError_t ea = cudaFuncSetAttribute(draft_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (ea != cudaSuccess) return cuda_fail(ea);
+    draft_smem_set = smem;
+  }
+  void* params[] = {&P};
+  const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(draft_q_kernel), dim3(grid), dim3(kVerifyBlock), params, smem,
+                                                    static_cast<cudaStream_t>(a->stream));
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }
 

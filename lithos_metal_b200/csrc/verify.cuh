@@ -30,12 +30,14 @@ struct VerifyWs {                                       // lives in the caller's
   unsigned long long row_best[kVerifyMaxRows];          // packed (max logit, lowest index) per row
   unsigned long long row_mass[kVerifyMaxRows];          // fixed-point mass of the kept set per row
   unsigned long long draft_w[kVerifyMaxRows];           // fixed-point weight of draft r in row r (0 if not kept)
+  unsigned long long rival[kVerifyMaxRows];             // draft-side sampling: the best Gumbel key that lost (monotone code)
   // followed by: unsigned long long part_w[kVerifyMaxRows][grid], part_r[grid]
 };
 
 struct VerifyDev {
   int mode; int dtype; int n_draft; int vocab; int64_t row_stride;
   const void* target; const int32_t* drafts; const float* q; int64_t q_stride; float temperature;
+  const uint16_t* q_logits; int64_t q_logits_stride; const float* q_vmax; const unsigned long long* q_mass;   // q from the drafter's BF16 logits when q is null
   const float* tau; const float* u_accept; const float* u_final;
   int32_t* out_accept; int32_t* out_final; int32_t* out_tokens; float* out_p_draft;
   VerifyWs* ws;
@@ -67,11 +69,20 @@ __device__ __forceinline__ float verify_load(const VerifyDev& P, int row, int i)
   return canon_zero(z);
 }
 
+// q_r(v): the drafter's probability of token v at draft position r, as given or from the drafter's logits and row statistics.
+__device__ __forceinline__ float q_from_code(uint32_t code, float vmax, unsigned long long mass, float c2) {
+  return mass ? prob_q40(weight_q40(canon_zero(__uint_as_float(code << 16)), vmax, c2), mass) : 0.0f;
+}
+__device__ __forceinline__ float verify_q(const VerifyDev& P, int r, int i, float c2) {
+  if (P.q) return __ldg(P.q + static_cast<int64_t>(r) * P.q_stride + i);
+  return q_from_code(__ldg(P.q_logits + static_cast<int64_t>(r) * P.q_logits_stride + i), __ldg(P.q_vmax + r), __ldg(P.q_mass + r), c2);
+}
+
 // The block's view of its slice: shared-memory copies when they fit, global memory otherwise.
 struct VerifySlice {
-  const VerifyDev* P; const float* zs; const float* qs; int per, lo;
+  const VerifyDev* P; const float* zs; const float* qs; int per, lo; float c2;
   __device__ __forceinline__ float z(int r, int i) const { return zs ? zs[r * per + i] : verify_load(*P, r, lo + i); }
-  __device__ __forceinline__ float q(int r, int i) const { return qs ? qs[r * per + i] : __ldg(P->q + static_cast<int64_t>(r) * P->q_stride + lo + i); }
+  __device__ __forceinline__ float q(int r, int i) const { return qs ? qs[r * per + i] : verify_q(*P, r, lo + i, c2); }
 };
 
 #ifdef LM_PROFILE_PHASES
@@ -101,7 +112,8 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   LM_VSTAMP(0);
   float* zs = cached ? v_smem : nullptr;
   float* qs = (cached && stochastic) ? v_smem + R * per : nullptr;
-  VerifySlice S{&P, zs, qs, per, lo};
+  const float c2 = stochastic ? exp2_scale(P.temperature) : 0.0f;
+  VerifySlice S{&P, zs, qs, per, lo, c2};
 
   // ---- phase 0: the only HBM pass. Slices of every target row and every draft-probability row into shared memory,
   // then row maxima with their lowest index (which is also the greedy pick).
@@ -110,9 +122,8 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   if (tid < P.n_draft) { my_draft = P.drafts[tid]; s_drafts[tid] = my_draft; }
   if (stochastic && tid < P.n_draft) {
     my_u = P.u_accept[tid];
-    if (my_draft >= 0 && my_draft < V) my_q = __ldg(P.q + static_cast<int64_t>(tid) * P.q_stride + my_draft);
+    if (my_draft >= 0 && my_draft < V) my_q = verify_q(P, tid, my_draft, c2);
   }
-  const float c2 = stochastic ? exp2_scale(P.temperature) : 0.0f;
   if (cached) {
     // 8 elements per load item (one 16-byte load of BF16 logits, two of FP32 logits or draft probabilities), every item of
     // a thread issued before the first is used: the whole slice arrives in one memory round trip
@@ -120,7 +131,8 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     const int chunks = (len + 7) / 8;
     const bool z_vec = (P.dtype == LM_DTYPE_BF16 ? (P.row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(P.target) & 15u) == 0)
                                                  : (P.row_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(P.target) & 15u) == 0));
-    const bool q_vec = n_q == 0 || (P.q_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(P.q) & 15u) == 0);
+    const bool q_vec = n_q == 0 || (P.q ? (P.q_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(P.q) & 15u) == 0)
+                                        : (P.q_logits_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(P.q_logits) & 15u) == 0));
     const int n_items = (R + n_q) * chunks;
     constexpr int kItems = 3;                                             // items in flight per thread
     for (int i0 = 0; i0 < n_items; i0 += kItems * kVerifyBlock) {
@@ -140,9 +152,12 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
             const float* src = reinterpret_cast<const float*>(P.target) + static_cast<int64_t>(r) * P.row_stride + lo + c8;
             if (full && z_vec) { va[k] = __ldg(reinterpret_cast<const float4*>(src)); vb[k] = __ldg(reinterpret_cast<const float4*>(src) + 1); }
           }
-        } else {
+        } else if (P.q) {
           const float* src = P.q + static_cast<int64_t>(r - R) * P.q_stride + lo + c8;
           if (full && q_vec) { va[k] = __ldg(reinterpret_cast<const float4*>(src)); vb[k] = __ldg(reinterpret_cast<const float4*>(src) + 1); }
+        } else {
+          const uint16_t* src = P.q_logits + static_cast<int64_t>(r - R) * P.q_logits_stride + lo + c8;
+          if (full && q_vec) va[k] = __ldg(reinterpret_cast<const float4*>(src));          // eight BF16 codes of the drafter's row
         }
       }
 #pragma unroll
@@ -155,10 +170,16 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
         const bool vec = full && (r < R ? z_vec : q_vec);
         if (!vec) {                                                       // a ragged last chunk or an unaligned tensor: element by element
           for (int e = 0; e < 8 && c8 + e < len; e++)
-            dst[e] = r < R ? verify_load(P, r, lo + c8 + e) : __ldg(P.q + static_cast<int64_t>(r - R) * P.q_stride + lo + c8 + e);
+            dst[e] = r < R ? verify_load(P, r, lo + c8 + e) : verify_q(P, r - R, lo + c8 + e, c2);
           continue;
         }
         float4 x = va[k], y = vb[k];
+        if (r >= R && !P.q) {                                             // the drafter's logits: probabilities from the row statistics
+          const float qv = __ldg(P.q_vmax + (r - R)); const unsigned long long qm = __ldg(P.q_mass + (r - R));
+          const uint32_t w0 = __float_as_uint(va[k].x), w1 = __float_as_uint(va[k].y), w2 = __float_as_uint(va[k].z), w3 = __float_as_uint(va[k].w);
+          x = make_float4(q_from_code(w0 & 0xFFFFu, qv, qm, c2), q_from_code(w0 >> 16, qv, qm, c2), q_from_code(w1 & 0xFFFFu, qv, qm, c2), q_from_code(w1 >> 16, qv, qm, c2));
+          y = make_float4(q_from_code(w2 & 0xFFFFu, qv, qm, c2), q_from_code(w2 >> 16, qv, qm, c2), q_from_code(w3 & 0xFFFFu, qv, qm, c2), q_from_code(w3 >> 16, qv, qm, c2));
+        }
         if (r < R && P.dtype == LM_DTYPE_BF16) {
           const uint32_t w0 = __float_as_uint(va[k].x), w1 = __float_as_uint(va[k].y), w2 = __float_as_uint(va[k].z), w3 = __float_as_uint(va[k].w);
           x = make_float4(bf16_lo(w0), bf16_hi(w0), bf16_lo(w1), bf16_hi(w1));

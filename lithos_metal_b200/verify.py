@@ -1,11 +1,13 @@
 """DSpark speculative verification on the GPU: one launch checks ``n`` drafted tokens against ``n + 1`` rows of
 target logits. Stands in for the accept chain of a speculative round in the reference (greedy: the prefix match of
 ``accept_scan``, kernels/common/spec_ops.metal:162-165; sampled drafts: ``spec_q_accept`` and the residual draw,
-kernels/common/sample.metal:279-347)."""
+kernels/common/sample.metal:279-347). ``draft_q`` is the drafter's side of such a round: the draw of draft k from the
+drafter's logits plus the row statistics that let ``verify`` evaluate q_k later (``draft_q_partial`` / ``draft_q_final``,
+kernels/common/sample.metal:212-269)."""
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Tuple
+from typing import NamedTuple, Optional, Tuple
 
 import torch
 
@@ -13,15 +15,61 @@ from . import _lib
 from .sampler import _check_logits, _dtype_code, _row_stride, _workspace
 
 
+class DraftQ(NamedTuple):
+    """What the drafter keeps of its sampled drafts: tokens int32 [n], ``lse`` float32 [n] (log sum exp(z / T), the
+    reference's q_lse), and the exact row statistics ``vmax`` float32 [n] / ``mass`` int64 [n] that ``verify`` evaluates
+    q from; ``status`` int32 [n] (LM_STATUS_NEAR_TIE / LM_STATUS_NAN bits); ``q_logits`` the copy of the rows, if asked for."""
+    tokens: torch.Tensor
+    lse: torch.Tensor
+    vmax: torch.Tensor
+    mass: torch.Tensor
+    status: torch.Tensor
+    q_logits: Optional[torch.Tensor]
+
+
+def draft_q(logits: torch.Tensor, *, temperature: float, seed: int = 0, step: int = 0, first_position: int = 0, copy_logits: bool = False) -> DraftQ:
+    """The drafter's draw for draft positions ``first_position .. first_position + rows - 1``, one logits row each
+    (``logits`` [rows, V] bfloat16/float32, rows <= 16): ``argmax_i(z_i * float32(1/T) + gumbel(seed, step, 2000 + position, i))``,
+    the unfiltered softmax at ``temperature`` as the reference's drafter samples it. Asynchronous on the current stream."""
+    if not temperature > 0:
+        raise ValueError("temperature must be positive")
+    logits = _check_logits(logits)
+    dev, rows, vocab = logits.device, int(logits.shape[0]), int(logits.shape[1])
+    if not 1 <= rows <= _lib.MAX_DRAFT + 1:
+        raise ValueError(f"1..{_lib.MAX_DRAFT + 1} rows")
+    a = _lib.DraftQArgs()
+    a.struct_size = C.sizeof(_lib.DraftQArgs)
+    a.dtype, a.rows, a.first_position = _dtype_code(logits), rows, int(first_position)
+    a.logits, a.vocab, a.row_stride = logits.data_ptr(), vocab, _row_stride(logits)
+    a.temperature, a.seed, a.step = float(temperature), int(seed) & (2**64 - 1), int(step)
+    tokens = torch.empty(rows, dtype=torch.int32, device=dev)
+    lse, vmax = torch.empty(rows, dtype=torch.float32, device=dev), torch.empty(rows, dtype=torch.float32, device=dev)
+    mass, status = torch.empty(rows, dtype=torch.int64, device=dev), torch.empty(rows, dtype=torch.int32, device=dev)
+    a.out_tokens, a.out_lse, a.out_vmax, a.out_mass, a.out_status = tokens.data_ptr(), lse.data_ptr(), vmax.data_ptr(), mass.data_ptr(), status.data_ptr()
+    q_logits = None
+    if copy_logits:
+        q_logits = torch.empty(rows, vocab, dtype=logits.dtype, device=dev)
+        a.out_q_logits, a.q_logits_stride = q_logits.data_ptr(), vocab
+    L = _lib.lib()
+    ws = _workspace(dev, L.lm_verify_workspace_bytes(rows, vocab), "verify")
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.stream = torch.cuda.current_stream(dev).cuda_stream
+    with torch.cuda.device(dev):
+        _lib.check(L.lm_draft_q(C.byref(a)), "lm_draft_q")
+    return DraftQ(tokens, lse, vmax, mass, status, q_logits)
+
+
 def verify(target_logits: torch.Tensor, draft_ids: torch.Tensor, draft_probs: Optional[torch.Tensor] = None, uniforms: Optional[torch.Tensor] = None,
            u_resample: Optional[torch.Tensor] = None, mode: str = "greedy", *, temperature: float = 1.0, tau: Optional[torch.Tensor] = None,
-           return_p_draft: bool = False) -> Tuple[torch.Tensor, ...]:
+           return_p_draft: bool = False, draft_logits: Optional[torch.Tensor] = None, draft_stats: Optional[DraftQ] = None) -> Tuple[torch.Tensor, ...]:
     """``(accept_len [1], final_token [1], tokens [n + 1])`` as int32 CUDA tensors (plus ``p_draft [n]`` on request).
 
     ``target_logits`` [n + 1, V] bfloat16/float32; ``draft_ids`` [n] int32; stochastic mode also takes the drafter's
     probabilities ``draft_probs`` [n, V] float32, the accept uniforms ``uniforms`` [n] and the resample uniform
     ``u_resample`` [1], all in [0, 1); ``tau`` [n + 1] optionally restricts every row to its kept set (``sample(...,
-    return_tau=True)``). Asynchronous on the current stream.
+    return_tau=True)``). Instead of ``draft_probs`` the drafter's distribution may be given the way the reference keeps it:
+    ``draft_logits`` [n, V] bfloat16 (the rows ``draft_q`` sampled from) with ``draft_stats`` = what ``draft_q`` returned
+    for them at the same temperature. Asynchronous on the current stream.
     """
     if mode not in ("greedy", "stochastic"):
         raise ValueError("mode must be 'greedy' or 'stochastic'")
@@ -41,21 +89,34 @@ def verify(target_logits: torch.Tensor, draft_ids: torch.Tensor, draft_probs: Op
     a.draft_ids = draft_ids.data_ptr()
     keep = [draft_ids]
     if mode == "stochastic":
-        if draft_probs is None or uniforms is None or u_resample is None:
-            raise ValueError("stochastic verification needs draft_probs, uniforms and u_resample")
+        if (draft_probs is None and (draft_logits is None or draft_stats is None)) or uniforms is None or u_resample is None:
+            raise ValueError("stochastic verification needs draft_probs (or draft_logits + draft_stats), uniforms and u_resample")
         if not temperature > 0:
             raise ValueError("temperature must be positive")
-        if draft_probs.shape != (n, target_logits.shape[1]) or draft_probs.dtype != torch.float32 or not draft_probs.is_cuda:
+        if draft_probs is None:
+            if draft_logits.shape != (n, target_logits.shape[1]) or draft_logits.dtype != torch.bfloat16 or not draft_logits.is_cuda:
+                raise ValueError("draft_logits must be bfloat16 CUDA [n, V]")
+            if draft_logits.stride(1) != 1:
+                draft_logits = draft_logits.contiguous()
+            q_vmax, q_mass = draft_stats.vmax[:n].contiguous(), draft_stats.mass[:n].contiguous()
+            if q_vmax.numel() != n or q_mass.numel() != n:
+                raise ValueError("draft_stats must hold one entry per draft")
+            a.draft_logits, a.draft_logits_stride = draft_logits.data_ptr(), _row_stride(draft_logits)
+            a.draft_vmax, a.draft_mass = q_vmax.data_ptr(), q_mass.data_ptr()
+            keep += [draft_logits, q_vmax, q_mass]
+        elif draft_probs.shape != (n, target_logits.shape[1]) or draft_probs.dtype != torch.float32 or not draft_probs.is_cuda:
             raise ValueError("draft_probs must be float32 CUDA [n, V]")
-        if draft_probs.stride(1) != 1:
+        elif draft_probs.stride(1) != 1:
             draft_probs = draft_probs.contiguous()
         uniforms = uniforms.to(device=dev, dtype=torch.float32).contiguous()
         u_resample = u_resample.to(device=dev, dtype=torch.float32).reshape(1).contiguous()
         if uniforms.numel() != n:
             raise ValueError("uniforms must hold one value per draft")
-        a.draft_probs, a.probs_stride = draft_probs.data_ptr(), _row_stride(draft_probs)
+        if draft_probs is not None:
+            a.draft_probs, a.probs_stride = draft_probs.data_ptr(), _row_stride(draft_probs)
+            keep.append(draft_probs)
         a.u_accept, a.u_final, a.temperature = uniforms.data_ptr(), u_resample.data_ptr(), float(temperature)
-        keep += [draft_probs, uniforms, u_resample]
+        keep += [uniforms, u_resample]
         if tau is not None:
             tau = tau.to(device=dev, dtype=torch.float32).contiguous()
             if tau.numel() != n + 1:

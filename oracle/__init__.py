@@ -50,6 +50,10 @@ def lib():
         _lib.lmo_sample_invcdf.argtypes = [f32p, C.c_int64, C.c_float, C.c_float, C.c_float, u64p]
         _lib.lmo_accept_greedy.restype = C.c_int32
         _lib.lmo_accept_greedy.argtypes = [i32p, i32p, C.c_int32, i32p]
+        _lib.lmo_draft_q.restype = C.c_int32
+        _lib.lmo_draft_q.argtypes = [f32p, C.c_int64, C.c_float, C.c_uint64, C.c_uint32, C.c_uint32, f32p, C.POINTER(C.c_uint64), f32p, f32p]
+        _lib.lmo_draft_probs.restype = None
+        _lib.lmo_draft_probs.argtypes = [f32p, C.c_int64, C.c_float, C.c_float, C.c_uint64, f32p]
         _lib.lmo_verify_stochastic.restype = C.c_int32
         _lib.lmo_verify_stochastic.argtypes = [f32p, C.c_int64, C.c_int32, f32p, C.c_float, i32p, f32p, f32p, C.c_float, i32p, f32p]
         _lib.lmo_sample_batch.restype = None
@@ -173,6 +177,23 @@ def verify_greedy(target_logits: np.ndarray, draft_ids: Sequence[int]) -> Tuple[
     fin = C.c_int32()
     acc = lib().lmo_accept_greedy(_p(toks, C.c_int32), _p(d, C.c_int32), d.size, C.byref(fin))
     return int(acc), int(fin.value), toks
+
+
+def draft_q(logits_row: np.ndarray, *, temperature: float, seed: int, step: int, position: int):
+    """(token, vmax, integer mass, lse, gap between the two best Gumbel keys) of the drafter's draw at draft ``position``."""
+    z = np.ascontiguousarray(widen(logits_row)).reshape(-1)
+    vmax, lse, gap, mass = C.c_float(), C.c_float(), C.c_float(), C.c_uint64()
+    tok = lib().lmo_draft_q(_p(z, C.c_float), z.shape[0], np.float32(temperature), seed, step, position, C.byref(vmax), C.byref(mass), C.byref(lse),
+                            C.byref(gap))
+    return int(tok), float(vmax.value), int(mass.value), float(lse.value), float(gap.value)
+
+
+def draft_probs(logits_row: np.ndarray, *, temperature: float, vmax: float, mass: int) -> np.ndarray:
+    """q(v) of one drafter row from its logits and statistics, float32 [V]."""
+    z = np.ascontiguousarray(widen(logits_row)).reshape(-1)
+    out = np.zeros(z.shape[0], dtype=np.float32)
+    lib().lmo_draft_probs(_p(z, C.c_float), z.shape[0], np.float32(temperature), np.float32(vmax), mass, _p(out, C.c_float))
+    return out
 
 
 def verify_stochastic(target_logits: np.ndarray, draft_ids, draft_probs: np.ndarray, u_accept, u_final: float, *, temperature: float = 1.0,

@@ -233,6 +233,30 @@ LMO_API int32_t lmo_sample_invcdf(const float* z, int64_t vocab, float tau, floa
   return -1;
 }
 
+/* ---- draft-side sampling (kernels/common/sample.metal:212-269) -------------------------------------------------------
+ * The drafter's draw of draft k from its logits row z (widened) at temperature T, unfiltered, on noise stream 2000 + k
+ * (sample.metal:239): the masked Gumbel-max draw with tau = -inf. Alongside, the row statistics the verify step evaluates
+ * q_k(v) from: vmax, the integer mass sum_i W(z_i) of the fixed-point weights, and lse = fl32(vmax/T + ln(mass * 2^-40))
+ * (the reference's q_lse is an FP32 running sum in grid order: equal to ~1e-6 relative, not bit for bit). */
+LMO_API int32_t lmo_draft_q(const float* z, int64_t vocab, float temperature, uint64_t seed, uint32_t step, uint32_t position,
+                            float* out_vmax, uint64_t* out_mass, float* out_lse, float* out_gap) {
+  float vmax = -INFINITY;
+  for (int64_t i = 0; i < vocab; i++) if (z[i] > vmax) vmax = z[i];
+  const float c = lmo_exp2_scale(temperature);
+  uint64_t mass = 0;
+  for (int64_t i = 0; i < vocab; i++) mass += lmo_weight_q40(z[i], vmax, c);
+  if (out_vmax) *out_vmax = vmax;
+  if (out_mass) *out_mass = mass;
+  if (out_lse) *out_lse = mass ? (float)((double)vmax / (double)temperature + log((double)mass * 9.094947017729282e-13)) : -INFINITY;
+  return lmo_sample_gumbel(z, vocab, -INFINITY, (double)temperature, seed, step, 2000u + position, out_gap);
+}
+
+/* q_k(v) from the drafter's logits row and its statistics: fl32(W(z_v) / mass), 0 for an empty row. */
+LMO_API void lmo_draft_probs(const float* z, int64_t vocab, float temperature, float vmax, uint64_t mass, float* out_q) {
+  const float c = lmo_exp2_scale(temperature);
+  for (int64_t i = 0; i < vocab; i++) out_q[i] = mass ? (float)((double)lmo_weight_q40(z[i], vmax, c) / (double)mass) : 0.0f;
+}
+
 /* ---- DSpark verification ------------------------------------------------------------------------------------- */
 
 /* Greedy (spec_ops.metal:162-165 with base = 0): acc = longest prefix with token[r] == draft[r]; final = token[acc]. */

@@ -3,6 +3,7 @@
 Run once, in a container where the reference checkout is available, with its path as the only argument:
 
     python tests/golden/make_golden.py /path/to/lithos-metal
+    python tests/golden/make_golden.py /path/to/lithos-metal --only draft_q      (adds that section to the existing file)
 
 It imports ``monolith.nn.sampling_ref`` / ``monolith.nn.sampler`` / ``monolith.kernels`` / ``monolith.core`` read-only
 (numpy and torch are their only dependencies), extracts the ``model_accept`` function from
@@ -31,9 +32,37 @@ OPTION_SETS = {   # tests/kernels/test_sampling.py:52-55
 }
 
 
-def main(ref_root: str) -> None:
+def draft_q_section(ref, f32_to_bf16, bf16_to_f32) -> dict:
+    """The drafter's draws (kernels/common/sample.metal:212-269): draft position k of a round draws from its own logits row,
+    unfiltered, on noise stream 2000 + k; the reference's CPU statement of that draw is ``sampling_ref.sample`` with
+    ``t = 2000 + k``. q_lse is stored as the float64 log-sum-exp of z / T (the Metal kernel accumulates it in FP32)."""
+    out = {}
+    for vocab in (1000, 151936):
+        for temperature in (0.3, 1.0):
+            rng = np.random.default_rng(7000 + vocab)
+            lb = f32_to_bf16((rng.standard_normal((7, vocab)) * 2.0).astype(np.float32))
+            lf = bf16_to_f32(lb)
+            toks = [int(ref.sample(lf[k], seed=12345, step=3, t=2000 + k, temperature=temperature)) for k in range(7)]
+            lse = [float(np.log(np.sum(np.exp(lf[k].astype(np.float64) / temperature)))) for k in range(7)]
+            out[f"{vocab}/{temperature}"] = {"tokens": toks, "lse": lse, "logits_crc": int(lb.astype(np.uint64).sum())}
+            print("draft_q", vocab, temperature, toks, flush=True)
+    return out
+
+
+def main(ref_root: str, only: str = "") -> None:
     sys.dont_write_bytecode = True
     sys.path.insert(0, ref_root)
+    if only == "draft_q":                                                  # add this section to the existing file without redoing the rest
+        from monolith.formats.fp import bf16_to_f32, f32_to_bf16
+        from monolith.nn import sampling_ref as ref
+        path = os.path.join(HERE, "reference_outputs.json")
+        with open(path) as f:
+            out = json.load(f)
+        out["draft_q"] = draft_q_section(ref, f32_to_bf16, bf16_to_f32)
+        with open(path, "w") as f:
+            json.dump(out, f, indent=1, sort_keys=True)
+        print("updated", path)
+        return
     import torch
     from monolith import kernels
     from monolith.core import StepStateLayout
@@ -165,10 +194,12 @@ def main(ref_root: str) -> None:
     out["select_params_hex"] = kernels.select_params(7, 0.5, 8, mode=1, cost=[1.0, 1.28, 1.5], log_cap=4, ctx_cap=64).hex()
     out["accept_params_hex"] = kernels.accept_params(16, 2, 64, ctx_cap=44).hex()
 
+    out["draft_q"] = draft_q_section(ref, f32_to_bf16, bf16_to_f32)
+
     with open(os.path.join(HERE, "reference_outputs.json"), "w") as f:
         json.dump(out, f, indent=1, sort_keys=True)
     print("wrote", os.path.join(HERE, "reference_outputs.json"))
 
 
 if __name__ == "__main__":
-    main(sys.argv[1])
+    main(sys.argv[1], sys.argv[3] if len(sys.argv) > 3 and sys.argv[2] == "--only" else "")

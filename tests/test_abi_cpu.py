@@ -23,19 +23,21 @@ def test_library_exports_every_declared_symbol():
     assert set(names) == set(_lib.EXPORTS) and len(names) >= 10
     for n in names:
         assert getattr(L, n) is not None
-    assert L.lm_abi_version() == 1
+    assert L.lm_abi_version() == 2
     assert L.lm_error_string(0) == b"ok" and L.lm_error_string(-2).startswith(b"workspace")
 
 
 def test_ctypes_structs_match_the_c_layout():
-    src = '#include <stdio.h>\n#include "lithos_b200.h"\nint main(){printf("%zu %zu %zu %zu\\n", sizeof(lm_sample_args), sizeof(lm_verify_args),' \
-          ' offsetof(lm_sample_args, out_tokens), offsetof(lm_verify_args, workspace));return 0;}\n'
+    src = '#include <stdio.h>\n#include "lithos_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu\\n", sizeof(lm_sample_args), sizeof(lm_verify_args),' \
+          ' offsetof(lm_sample_args, out_tokens), offsetof(lm_verify_args, workspace), sizeof(lm_draft_q_args), offsetof(lm_draft_q_args, out_mass),' \
+          ' offsetof(lm_verify_args, draft_mass));return 0;}\n'
     with tempfile.TemporaryDirectory() as d:
         open(os.path.join(d, "t.c"), "w").write(src)
         subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), "-o", os.path.join(d, "t"), os.path.join(d, "t.c")], check=True)
         out = subprocess.run([os.path.join(d, "t")], capture_output=True, text=True, check=True).stdout.split()
     assert [int(x) for x in out] == [C.sizeof(_lib.SampleArgs), C.sizeof(_lib.VerifyArgs), _lib.SampleArgs.out_tokens.offset,
-                                     _lib.VerifyArgs.workspace.offset]
+                                     _lib.VerifyArgs.workspace.offset, C.sizeof(_lib.DraftQArgs), _lib.DraftQArgs.out_mass.offset,
+                                     _lib.VerifyArgs.draft_mass.offset]
 
 
 def test_argument_validation_needs_no_device():
@@ -53,6 +55,11 @@ def test_argument_validation_needs_no_device():
     v.struct_size = C.sizeof(_lib.VerifyArgs)
     v.n_draft = 0
     assert L.lm_verify(C.byref(v)) == -1
+    d = _lib.DraftQArgs()
+    assert L.lm_draft_q(C.byref(d)) == -1                      # struct_size not set
+    d.struct_size = C.sizeof(_lib.DraftQArgs)
+    d.rows, d.vocab, d.temperature = 17, 100, 1.0
+    assert L.lm_draft_q(C.byref(d)) == -1                      # more rows than a round has
     assert L.lm_argmax(None, 0, 0, 10, 10, None, None, 0, None) == 0
     assert L.lm_argmax(None, 0, 2, 10, 10, None, None, 0, None) == -1
     assert L.lm_workspace_bytes(256, 151936) >= 256 * 16 and L.lm_verify_workspace_bytes(7, 151936) > 0

@@ -137,3 +137,27 @@ def test_verify_models_on_a_small_step():
     assert acc == 7 and fin == oracle.sample_invcdf(z[7], uf)
     acc, fin, _ = oracle.verify_stochastic(target, drafts, q, np.full(7, 0.999, np.float32), uf)
     assert 0 <= acc < 7 and 0 <= fin < 2000
+
+
+@pytest.mark.parametrize("vocab", [1000, 151936])
+@pytest.mark.parametrize("temperature", [0.3, 1.0])
+def test_draft_q_equals_the_reference(golden, vocab, temperature):
+    """The drafter's draw: the reference's sampling_ref.sample on stream 2000 + k; lse against the float64 log-sum-exp;
+    the probabilities rebuilt from (vmax, integer mass) sum to one and reproduce exp(z/T - lse)."""
+    g = golden["draft_q"][f"{vocab}/{temperature}"]
+    rng = np.random.default_rng(7000 + vocab)
+    lb = oracle.f32_to_bf16((rng.standard_normal((7, vocab)) * 2.0).astype(np.float32))
+    assert int(lb.astype(np.uint64).sum()) == g["logits_crc"]
+    for k in range(7):
+        tok, vmax, mass, lse, gap = oracle.draft_q(lb[k], temperature=temperature, seed=12345, step=3, position=k)
+        assert tok == g["tokens"][k] or gap < 4e-6
+        assert abs(lse - g["lse"][k]) <= 2e-6 * abs(g["lse"][k])
+        assert vmax == float(oracle.bf16_to_f32(lb[k]).max())
+    q = oracle.draft_probs(lb[0], temperature=temperature, vmax=vmax_of(lb[0]), mass=oracle.draft_q(lb[0], temperature=temperature, seed=1, step=0, position=0)[2])
+    z = oracle.bf16_to_f32(lb[0]).astype(np.float64)
+    np.testing.assert_allclose(q, np.exp(z / temperature - g["lse"][0]), rtol=2e-5, atol=1e-12)
+    assert abs(float(q.astype(np.float64).sum()) - 1.0) < 1e-5
+
+
+def vmax_of(codes):
+    return float(oracle.bf16_to_f32(codes).max())
