@@ -338,6 +338,31 @@ LM_API int lm_verify_select(const lm_step_args* args);
 LM_API int lm_advance(const lm_step_args* args);
 LM_API size_t lm_step_state_bytes(int32_t t_max, int32_t gamma_max);
 
+/*
+ * The DSpark confidence head that feeds lm_verify_select: conf[k] = sigmoid(bf16(bf16(w . [hidden_k ; emb_k]) + b) / sts[k]) for
+ * k < gamma. Stands in for the `confidence` kernel (kernels/common/spec_ops.metal:85-106; parameters as conf_params,
+ * monolith/kernels.py:802-808): FP32 FMA accumulation in the same lane order, both BF16 roundings, then the sigmoid (on this
+ * library's fixed exp2 instead of the Metal exp: within 2e-7 of it; the reference's own test bar is 2e-3). Positions >= gamma
+ * are not written. step_state (optional): nothing is written once the state is done.
+ */
+typedef struct lm_confidence_args {
+  uint32_t struct_size;
+  int32_t gamma;               /* positions to score, 0..16 */
+  int32_t hidden;              /* width of a hidden row */
+  int32_t rank;                /* width of an embedding row (0: no Markov part) */
+  const void* hidden_rows;     /* [gamma, hidden] BF16 */
+  const void* emb_rows;        /* [gamma, rank] BF16, or NULL when rank == 0 */
+  const float* w;              /* [hidden + rank] */
+  const float* b;              /* [1] */
+  const float* sts;            /* [gamma] positive calibration temperatures, or NULL for 1 */
+  float* out_conf;             /* [>= gamma] */
+  void* step_state;            /* StepState bytes or NULL */
+  int32_t t_max, gamma_max;    /* the layout of step_state */
+  void* stream;
+} lm_confidence_args;
+
+LM_API int lm_confidence(const lm_confidence_args* args);
+
 /* Scratch sizes (host calls, no CUDA work). Stand in for sample_workspace (monolith/kernels.py:777-779). */
 LM_API size_t lm_workspace_bytes(int64_t rows, int64_t vocab);
 LM_API size_t lm_verify_workspace_bytes(int32_t n_draft, int64_t vocab);

@@ -6,8 +6,8 @@ The Python names mirror the reference's sampler interface (monolith/nn/sampler.p
 from .sampler import (GreedySampler, SampleOutput, SamplingParams, StochasticSampler, argmax, sample, sample_row, thresholds,
                       warped_probabilities)
 from .verify import DraftQ, draft_q, verify
-from .step_state import StepStateLayout, accept_scan, advance, verify_select
+from .step_state import StepStateLayout, accept_scan, advance, confidence, verify_select
 from . import parallel
 
 __all__ = ["GreedySampler", "StochasticSampler", "SamplingParams", "SampleOutput", "sample", "argmax", "sample_row", "thresholds",
-           "warped_probabilities", "verify", "draft_q", "DraftQ", "StepStateLayout", "accept_scan", "verify_select", "advance", "parallel"]
+           "warped_probabilities", "verify", "draft_q", "DraftQ", "StepStateLayout", "accept_scan", "verify_select", "advance", "confidence", "parallel"]

@@ -57,6 +57,14 @@ class DraftQArgs(C.Structure):
     ]
 
 
+class ConfidenceArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("gamma", C.c_int32), ("hidden", C.c_int32), ("rank", C.c_int32), ("hidden_rows", C.c_void_p),
+        ("emb_rows", C.c_void_p), ("w", C.c_void_p), ("b", C.c_void_p), ("sts", C.c_void_p), ("out_conf", C.c_void_p), ("step_state", C.c_void_p),
+        ("t_max", C.c_int32), ("gamma_max", C.c_int32), ("stream", C.c_void_p),
+    ]
+
+
 class StepArgs(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint32), ("t_max", C.c_int32), ("gamma_max", C.c_int32), ("step_state", C.c_void_p), ("tokens", C.c_void_p),
@@ -78,7 +86,7 @@ class VocabArgs(C.Structure):
     ]
 
 
-EXPORTS = ["lm_accept_scan", "lm_verify_select", "lm_advance", "lm_step_state_bytes", "lm_sample", "lm_argmax", "lm_argmax_static", "lm_vocab_local", "lm_vocab_merge", "lm_vocab_record_bytes", "lm_vocab_candidate_cap", "lm_verify", "lm_draft_q", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
+EXPORTS = ["lm_accept_scan", "lm_verify_select", "lm_advance", "lm_step_state_bytes", "lm_sample", "lm_argmax", "lm_argmax_static", "lm_vocab_local", "lm_vocab_merge", "lm_vocab_record_bytes", "lm_vocab_candidate_cap", "lm_verify", "lm_draft_q", "lm_confidence", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
            "lm_error_string", "lm_last_cuda_error", "lm_device_sm_count"]
 
 _lib = None
@@ -100,6 +108,8 @@ def lib():
         L.lm_sample.argtypes = [C.POINTER(SampleArgs)]
         L.lm_verify.restype = C.c_int
         L.lm_verify.argtypes = [C.POINTER(VerifyArgs)]
+        L.lm_confidence.restype = C.c_int
+        L.lm_confidence.argtypes = [C.POINTER(ConfidenceArgs)]
         L.lm_draft_q.restype = C.c_int
         L.lm_draft_q.argtypes = [C.POINTER(DraftQArgs)]
         L.lm_argmax.restype = C.c_int

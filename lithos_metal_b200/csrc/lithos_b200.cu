@@ -532,4 +532,19 @@ int lm_draft_q(const lm_draft_q_args* a) {
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }
 
+int lm_confidence(const lm_confidence_args* a) {
+  if (!a || a->struct_size != sizeof(lm_confidence_args)) return LM_E_INVALID;
+  if (a->gamma < 0 || a->gamma > 16 || a->hidden < 0 || a->rank < 0 || a->hidden + a->rank < 1) return LM_E_INVALID;
+  if (a->gamma == 0) return LM_OK;
+  if (!a->w || !a->b || !a->out_conf || (a->hidden > 0 && !a->hidden_rows) || (a->rank > 0 && !a->emb_rows)) return LM_E_INVALID;
+  if (a->step_state && (a->t_max < 1 || a->gamma_max < 0 || a->t_max < a->gamma_max + 1)) return LM_E_INVALID;
+  ConfDev P;
+  P.hidden = static_cast<const uint16_t*>(a->hidden_rows); P.emb = static_cast<const uint16_t*>(a->emb_rows); P.w = a->w; P.b = a->b; P.sts = a->sts;
+  P.conf = a->out_conf; P.state = static_cast<uint32_t*>(a->step_state); P.t_max = a->t_max; P.g = a->gamma_max > 1 ? a->gamma_max : 1;
+  P.gamma = a->gamma; P.n_hidden = a->hidden; P.rank = a->rank;
+  confidence_kernel<<<(a->gamma + 3) / 4, 128, 0, static_cast<cudaStream_t>(a->stream)>>>(P);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
 }  // extern "C"

@@ -2,6 +2,7 @@
 //   accept_scan   (kernels/common/spec_ops.metal:148-195)  greedy prefix match, commit to the token ring, advance the state
 //   verify_select (kernels/common/spec_ops.metal:108-146)  stage the next round's drafts and pick the verify length
 //   advance       (kernels/common/advance.metal:15-37)     close a plain decode step
+//   confidence    (kernels/common/spec_ops.metal:85-106)   the DSpark confidence head that feeds verify_select
 // One thread each: they are a few dozen dependent scalar operations; what matters is that they run on the device,
 // in stream order, so the host never has to read a token to keep the loop going. The state is the reference's
 // binary contract (monolith/core/step_state.py:38-62): 4-byte fields, same order, for any t_max / gamma_max.
@@ -170,6 +171,36 @@ __global__ void advance_kernel(AdvanceDev p) {
   st.t_this_step() = 1u;
   if (is_eos(p.eos, tok)) st.done() = 1u;
   if (p.ctx_cap && st.position() >= p.ctx_cap) { st.error() = 2u; st.done() = 1u; }
+}
+
+// The confidence head: conf[k] = sigmoid(bf16(bf16(w . [hidden_k ; emb_k]) + b) / sts[k]) for the gamma draft positions.
+// One warp per position, the reference's arithmetic step by step: lane l accumulates elements l, l + 32, ... of the hidden
+// row and then of the embedding row with one FMA each (FP32), the lanes meet in a butterfly sum, the dot product and the
+// biased sum are each rounded to BF16 (round to nearest even on the bit pattern). The sigmoid is evaluated on the library's
+// fixed exp2 (common.cuh) so that a CPU gives the same bits; the reference calls the Metal exp (test bar there: 2e-3).
+struct ConfDev { const uint16_t* hidden; const uint16_t* emb; const float* w; const float* b; const float* sts; float* conf; uint32_t* state; int t_max, g; int gamma, n_hidden, rank; };
+
+__device__ __forceinline__ float round_bf16(float x) {
+  uint32_t u = __float_as_uint(x);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return __uint_as_float(u & 0xFFFF0000u);
+}
+
+__global__ void confidence_kernel(ConfDev p) {
+  const int k = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (k >= p.gamma) return;
+  if (p.state) { StepStateView st{p.state, p.t_max, p.g}; if (st.done()) return; }
+  float acc = 0.0f;
+  for (int i = lane; i < p.n_hidden; i += 32) acc = __fmaf_rn(__uint_as_float(static_cast<uint32_t>(__ldg(p.hidden + static_cast<int64_t>(k) * p.n_hidden + i)) << 16), __ldg(p.w + i), acc);
+  for (int i = lane; i < p.rank; i += 32) acc = __fmaf_rn(__uint_as_float(static_cast<uint32_t>(__ldg(p.emb + static_cast<int64_t>(k) * p.rank + i)) << 16), __ldg(p.w + p.n_hidden + i), acc);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(kFull, acc, o));
+  if (lane == 0) {
+    const float z = round_bf16(__fadd_rn(round_bf16(acc), p.b[0]));
+    const float x = __fdiv_rn(z, p.sts ? p.sts[k] : 1.0f);
+    const float e = spec_exp2(__fmul_rn(-fabsf(x), 1.44269502f));          // exp(-|x|), in (0, 1]
+    p.conf[k] = x >= 0.0f ? __fdiv_rn(1.0f, __fadd_rn(1.0f, e)) : __fdiv_rn(e, __fadd_rn(1.0f, e));
+  }
 }
 
 }  // namespace lm

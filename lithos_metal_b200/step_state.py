@@ -3,7 +3,8 @@
 ``StepStateLayout`` mirrors ``monolith/core/step_state.py:28-119`` (same field order, offsets, padding, ``pack`` / ``unpack``), so a
 state buffer written by either side reads the same. ``accept_scan``, ``verify_select`` and ``advance`` launch the CUDA
 counterparts of the reference's ``accept_scan`` / ``verify_select`` (kernels/common/spec_ops.metal:108-195) and ``advance``
-(kernels/common/advance.metal:15-37) on such a buffer; parameters follow ``accept_params`` / ``select_params`` / ``advance_params``
+(kernels/common/advance.metal:15-37) on such a buffer; ``confidence`` is the DSpark confidence head that produces the
+``conf`` vector ``verify_select`` reads (kernels/common/spec_ops.metal:85-106, ``conf_params`` monolith/kernels.py:802-808); parameters follow ``accept_params`` / ``select_params`` / ``advance_params``
 (monolith/kernels.py:748-752, 814-835).
 """
 from __future__ import annotations
@@ -144,3 +145,48 @@ def advance(layout: StepStateLayout, state: torch.Tensor, tokens: torch.Tensor, 
     a.tokens, a.ring, a.ring_cap, a.ctx_cap = tokens.data_ptr(), ring.data_ptr(), ring.numel(), ctx_cap
     with torch.cuda.device(state.device):
         _lib.check(_lib.lib().lm_advance(C.byref(a)), "lm_advance")
+
+
+def confidence(hidden: torch.Tensor, emb: Optional[torch.Tensor], w: torch.Tensor, b: torch.Tensor, *, gamma: Optional[int] = None,
+               sts: Optional[Sequence[float]] = None, out: Optional[torch.Tensor] = None, layout: Optional[StepStateLayout] = None,
+               state: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``conf[k] = sigmoid(bf16(bf16(w . [hidden_k ; emb_k]) + b) / sts[k])`` for ``k < gamma`` (default: every row of ``hidden``).
+
+    ``hidden`` [rows, H] bfloat16, ``emb`` [rows, rank] bfloat16 or None, ``w`` [H + rank] float32, ``b`` [1] float32, ``sts`` up
+    to 16 positive calibration temperatures (missing ones are 1). Returns float32 [rows]; positions >= gamma keep what ``out``
+    held (zeros for a fresh tensor). With ``layout`` / ``state`` nothing is written once the state is done."""
+    if hidden.dtype != torch.bfloat16 or not hidden.is_cuda or hidden.dim() != 2 or not hidden.is_contiguous():
+        raise ValueError("hidden must be a contiguous bfloat16 CUDA tensor [rows, H]")
+    rows, n_hidden = int(hidden.shape[0]), int(hidden.shape[1])
+    gamma = rows if gamma is None else int(gamma)
+    if not 0 <= gamma <= min(rows, 16):
+        raise ValueError("gamma must lie in 0..min(rows, 16)")
+    rank = 0
+    if emb is not None:
+        if emb.dtype != torch.bfloat16 or not emb.is_cuda or emb.dim() != 2 or emb.shape[0] < gamma or not emb.is_contiguous():
+            raise ValueError("emb must be a contiguous bfloat16 CUDA tensor [rows, rank]")
+        rank = int(emb.shape[1])
+    t = [float(x) for x in (sts or [])]
+    if len(t) > 16 or any(x <= 0 for x in t):
+        raise ValueError("conf_params: up to 16 positive STS temperatures")
+    dev = hidden.device
+    w = w.to(device=dev, dtype=torch.float32).contiguous()
+    b = b.to(device=dev, dtype=torch.float32).reshape(1).contiguous()
+    if w.numel() != n_hidden + rank:
+        raise ValueError("w must hold hidden + rank weights")
+    conf = torch.zeros(rows, dtype=torch.float32, device=dev) if out is None else out
+    a = _lib.ConfidenceArgs()
+    a.struct_size = C.sizeof(_lib.ConfidenceArgs)
+    a.gamma, a.hidden, a.rank = gamma, n_hidden, rank
+    a.hidden_rows, a.emb_rows, a.w, a.b, a.out_conf = hidden.data_ptr(), (emb.data_ptr() if rank else None), w.data_ptr(), b.data_ptr(), conf.data_ptr()
+    keep = [w, b]
+    if t:
+        ts = torch.tensor(t + [1.0] * (16 - len(t)), dtype=torch.float32, device=dev)
+        keep.append(ts)
+        a.sts = ts.data_ptr()
+    if state is not None:
+        a.step_state, a.t_max, a.gamma_max = state.data_ptr(), layout.t_max, layout.gamma_max
+    a.stream = torch.cuda.current_stream(dev).cuda_stream
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().lm_confidence(C.byref(a)), "lm_confidence")
+    return conf

@@ -50,6 +50,8 @@ def lib():
         _lib.lmo_sample_invcdf.argtypes = [f32p, C.c_int64, C.c_float, C.c_float, C.c_float, u64p]
         _lib.lmo_accept_greedy.restype = C.c_int32
         _lib.lmo_accept_greedy.argtypes = [i32p, i32p, C.c_int32, i32p]
+        _lib.lmo_confidence.restype = None
+        _lib.lmo_confidence.argtypes = [C.POINTER(C.c_uint16), C.POINTER(C.c_uint16), f32p, C.c_float, f32p, C.c_int32, C.c_int32, C.c_int32, f32p]
         _lib.lmo_draft_q.restype = C.c_int32
         _lib.lmo_draft_q.argtypes = [f32p, C.c_int64, C.c_float, C.c_uint64, C.c_uint32, C.c_uint32, f32p, C.POINTER(C.c_uint64), f32p, f32p]
         _lib.lmo_draft_probs.restype = None
@@ -177,6 +179,19 @@ def verify_greedy(target_logits: np.ndarray, draft_ids: Sequence[int]) -> Tuple[
     fin = C.c_int32()
     acc = lib().lmo_accept_greedy(_p(toks, C.c_int32), _p(d, C.c_int32), d.size, C.byref(fin))
     return int(acc), int(fin.value), toks
+
+
+def confidence(hidden: np.ndarray, emb, w: np.ndarray, b: float, sts=None) -> np.ndarray:
+    """conf [gamma] float32 of the DSpark confidence head; ``hidden`` [gamma, H] / ``emb`` [gamma, rank] as BF16 codes (uint16)."""
+    h = np.ascontiguousarray(hidden, dtype=np.uint16)
+    gamma, n_hidden = h.shape
+    e = np.ascontiguousarray(emb, dtype=np.uint16) if emb is not None else np.zeros((gamma, 0), dtype=np.uint16)
+    ww = _f32(w)
+    out = np.zeros(gamma, dtype=np.float32)
+    t = None if sts is None else _f32(sts)
+    lib().lmo_confidence(_p(h, C.c_uint16), _p(e, C.c_uint16) if e.size else None, _p(ww, C.c_float), np.float32(b),
+                         None if t is None else _p(t, C.c_float), gamma, n_hidden, e.shape[1], _p(out, C.c_float))
+    return out
 
 
 def draft_q(logits_row: np.ndarray, *, temperature: float, seed: int, step: int, position: int):

@@ -257,6 +257,44 @@ LMO_API void lmo_draft_probs(const float* z, int64_t vocab, float temperature, f
   for (int64_t i = 0; i < vocab; i++) out_q[i] = mass ? (float)((double)lmo_weight_q40(z[i], vmax, c) / (double)mass) : 0.0f;
 }
 
+/* ---- the confidence head (kernels/common/spec_ops.metal:85-106) ---------------------------------------------------------
+ * conf[k] = sigmoid(bf16(bf16(w . [hidden_k ; emb_k]) + b) / sts[k]). The dot product is the reference kernel's: 32 lanes,
+ * lane l takes elements l, l + 32, ... of the hidden row and then of the embedding row, one binary32 FMA each; the lanes are
+ * summed pairwise at distances 16, 8, 4, 2, 1. The two BF16 roundings are round-to-nearest-even on the bit pattern. The
+ * sigmoid uses lmo_spec_exp2 (the reference calls the Metal exp). */
+static inline float round_bf16(float x) {
+  uint32_t u; memcpy(&u, &x, 4);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  u &= 0xFFFF0000u;
+  float r; memcpy(&r, &u, 4);
+  return r;
+}
+
+LMO_API void lmo_confidence(const uint16_t* hidden, const uint16_t* emb, const float* w, float b, const float* sts, int32_t gamma, int32_t n_hidden,
+                            int32_t rank, float* out) {
+  for (int32_t k = 0; k < gamma; k++) {
+    float lane[32];
+    for (int l = 0; l < 32; l++) {
+      float acc = 0.0f;
+      for (int32_t i = l; i < n_hidden; i += 32) acc = fmaf(bits_f((uint32_t)hidden[(int64_t)k * n_hidden + i] << 16), w[i], acc);
+      for (int32_t i = l; i < rank; i += 32) acc = fmaf(bits_f((uint32_t)emb[(int64_t)k * rank + i] << 16), w[n_hidden + i], acc);
+      lane[l] = acc;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      float next[32];
+      for (int l = 0; l < 32; l++) { volatile float t = lane[l] + lane[l ^ o]; next[l] = t; }
+      memcpy(lane, next, sizeof(lane));
+    }
+    volatile float zb = round_bf16(lane[0]) + b;
+    const float z = round_bf16(zb);
+    volatile float x = z / (sts ? sts[k] : 1.0f);
+    volatile float arg = -fabsf(x) * 1.44269502f;
+    const float e = lmo_spec_exp2(arg);
+    volatile float den = 1.0f + e;
+    out[k] = x >= 0.0f ? 1.0f / den : e / den;
+  }
+}
+
 /* ---- DSpark verification ------------------------------------------------------------------------------------- */
 
 /* Greedy (spec_ops.metal:162-165 with base = 0): acc = longest prefix with token[r] == draft[r]; final = token[acc]. */

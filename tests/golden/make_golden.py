@@ -3,7 +3,7 @@
 Run once, in a container where the reference checkout is available, with its path as the only argument:
 
     python tests/golden/make_golden.py /path/to/lithos-metal
-    python tests/golden/make_golden.py /path/to/lithos-metal --only draft_q      (adds that section to the existing file)
+    python tests/golden/make_golden.py /path/to/lithos-metal --only draft_q      (adds that section, or `confidence`, to the existing file)
 
 It imports ``monolith.nn.sampling_ref`` / ``monolith.nn.sampler`` / ``monolith.kernels`` / ``monolith.core`` read-only
 (numpy and torch are their only dependencies), extracts the ``model_accept`` function from
@@ -49,16 +49,40 @@ def draft_q_section(ref, f32_to_bf16, bf16_to_f32) -> dict:
     return out
 
 
+def confidence_section(f32_to_bf16, bf16_to_f32) -> dict:
+    """The expected values of the reference's confidence-head test (tests/kernels/test_draft_ops.py:228-263), formed by its own
+    float64 statement with the reference's BF16 conversions: inputs from default_rng(4), gamma 7, hidden 256, rank 64; the three
+    cases of the test (Markov part on, off, per-position STS temperatures). The test's bar for the kernel is 2e-3."""
+    rbf = lambda x: bf16_to_f32(f32_to_bf16(np.asarray(x, dtype=np.float32)))
+    rng = np.random.default_rng(4)
+    gamma, hid, rank = 7, 256, 64
+    hidden = f32_to_bf16(rng.standard_normal((gamma, hid)).astype(np.float32))
+    emb = f32_to_bf16(rng.standard_normal((gamma, rank)).astype(np.float32))
+    w = rbf(rng.standard_normal(hid + rank) * 0.05)
+    b = rbf(rng.standard_normal(1) * 0.5)
+    feats = np.concatenate([bf16_to_f32(hidden), bf16_to_f32(emb)], axis=1).astype(np.float64)
+    z = rbf(rbf(feats @ w.astype(np.float64)) + b[0])
+    with_emb = 1.0 / (1.0 + np.exp(-z.astype(np.float64)))
+    z2 = rbf(rbf(bf16_to_f32(hidden).astype(np.float64) @ w[:hid].astype(np.float64)) + b[0])
+    sts = [0.5, 1.0, 2.0, 1.5, 0.8, 1.2, 3.0]
+    return {"with_emb": with_emb.tolist(), "hidden_only": (1.0 / (1.0 + np.exp(-z2.astype(np.float64)))).tolist(),
+            "sts": sts, "hidden_only_sts": (1.0 / (1.0 + np.exp(-z2.astype(np.float64) / np.array(sts)))).tolist(),
+            "inputs_crc": int(hidden.astype(np.uint64).sum() + emb.astype(np.uint64).sum())}
+
+
 def main(ref_root: str, only: str = "") -> None:
     sys.dont_write_bytecode = True
     sys.path.insert(0, ref_root)
-    if only == "draft_q":                                                  # add this section to the existing file without redoing the rest
+    if only in ("draft_q", "confidence"):                                  # add this section to the existing file without redoing the rest
         from monolith.formats.fp import bf16_to_f32, f32_to_bf16
         from monolith.nn import sampling_ref as ref
         path = os.path.join(HERE, "reference_outputs.json")
         with open(path) as f:
             out = json.load(f)
-        out["draft_q"] = draft_q_section(ref, f32_to_bf16, bf16_to_f32)
+        if only == "draft_q":
+            out["draft_q"] = draft_q_section(ref, f32_to_bf16, bf16_to_f32)
+        else:
+            out["confidence"] = confidence_section(f32_to_bf16, bf16_to_f32)
         with open(path, "w") as f:
             json.dump(out, f, indent=1, sort_keys=True)
         print("updated", path)
@@ -195,6 +219,7 @@ def main(ref_root: str, only: str = "") -> None:
     out["accept_params_hex"] = kernels.accept_params(16, 2, 64, ctx_cap=44).hex()
 
     out["draft_q"] = draft_q_section(ref, f32_to_bf16, bf16_to_f32)
+    out["confidence"] = confidence_section(f32_to_bf16, bf16_to_f32)
 
     with open(os.path.join(HERE, "reference_outputs.json"), "w") as f:
         json.dump(out, f, indent=1, sort_keys=True)

@@ -28,16 +28,16 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_ctypes_structs_match_the_c_layout():
-    src = '#include <stdio.h>\n#include "lithos_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu\\n", sizeof(lm_sample_args), sizeof(lm_verify_args),' \
+    src = '#include <stdio.h>\n#include "lithos_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu ", sizeof(lm_sample_args), sizeof(lm_verify_args),' \
           ' offsetof(lm_sample_args, out_tokens), offsetof(lm_verify_args, workspace), sizeof(lm_draft_q_args), offsetof(lm_draft_q_args, out_mass),' \
-          ' offsetof(lm_verify_args, draft_mass));return 0;}\n'
+          ' offsetof(lm_verify_args, draft_mass));printf("%zu %zu\\n", sizeof(lm_confidence_args), offsetof(lm_confidence_args, stream));return 0;}\n'
     with tempfile.TemporaryDirectory() as d:
         open(os.path.join(d, "t.c"), "w").write(src)
         subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), "-o", os.path.join(d, "t"), os.path.join(d, "t.c")], check=True)
         out = subprocess.run([os.path.join(d, "t")], capture_output=True, text=True, check=True).stdout.split()
     assert [int(x) for x in out] == [C.sizeof(_lib.SampleArgs), C.sizeof(_lib.VerifyArgs), _lib.SampleArgs.out_tokens.offset,
                                      _lib.VerifyArgs.workspace.offset, C.sizeof(_lib.DraftQArgs), _lib.DraftQArgs.out_mass.offset,
-                                     _lib.VerifyArgs.draft_mass.offset]
+                                     _lib.VerifyArgs.draft_mass.offset, C.sizeof(_lib.ConfidenceArgs), _lib.ConfidenceArgs.stream.offset]
 
 
 def test_argument_validation_needs_no_device():
@@ -60,6 +60,12 @@ def test_argument_validation_needs_no_device():
     d.struct_size = C.sizeof(_lib.DraftQArgs)
     d.rows, d.vocab, d.temperature = 17, 100, 1.0
     assert L.lm_draft_q(C.byref(d)) == -1                      # more rows than a round has
+    c = _lib.ConfidenceArgs()
+    c.struct_size = C.sizeof(_lib.ConfidenceArgs)
+    c.gamma, c.hidden = 17, 8
+    assert L.lm_confidence(C.byref(c)) == -1                   # more positions than a round has
+    c.gamma = 0
+    assert L.lm_confidence(C.byref(c)) == 0                    # nothing to do
     assert L.lm_argmax(None, 0, 0, 10, 10, None, None, 0, None) == 0
     assert L.lm_argmax(None, 0, 2, 10, 10, None, None, 0, None) == -1
     assert L.lm_workspace_bytes(256, 151936) >= 256 * 16 and L.lm_verify_workspace_bytes(7, 151936) > 0

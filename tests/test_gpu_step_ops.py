@@ -5,6 +5,8 @@ import numpy as np
 import pytest
 import torch
 
+import lithos_metal_b200 as lm
+import oracle
 from lithos_metal_b200 import step_state as ss
 from oracle import spec_models
 
@@ -114,3 +116,35 @@ def test_advance_equals_the_model():
         exp, writes = spec_models.advance(st, [60, 61], 16, eos, kw.get("ctx_cap", 0))
         assert LAYOUT.from_device(dev) == exp, (st, kw)
         assert {i: int(v) for i, v in enumerate(ring.cpu().numpy().view(np.uint64)) if v} == dict(writes)
+
+
+def test_confidence_head(golden):
+    """lm_confidence: bit-exact with the CPU oracle (same FMA order, same BF16 roundings, same fixed exp2) and within the
+    reference test's bar of its float64 statement; positions >= gamma untouched; feeds verify_select; silent once done."""
+    from tests.test_oracle_golden import confidence_inputs
+    g = golden["confidence"]
+    hidden, emb, w, b = confidence_inputs()
+    as_bf16 = lambda codes: torch.from_numpy(codes.view(np.int16).copy()).cuda().view(torch.bfloat16)
+    th, te, tw, tb = as_bf16(hidden), as_bf16(emb), torch.from_numpy(w).cuda(), torch.from_numpy(b).cuda()
+    got = lm.confidence(th, te, tw, tb, gamma=6).cpu().numpy()
+    np.testing.assert_array_equal(got[:6], oracle.confidence(hidden, emb, w, float(b[0]))[:6])
+    assert got[6] == 0.0 and np.abs(got[:6] - np.array(g["with_emb"])[:6]).max() <= 2e-3
+    got = lm.confidence(th, None, tw[:256], tb).cpu().numpy()
+    np.testing.assert_array_equal(got, oracle.confidence(hidden, None, w[:256], float(b[0])))
+    assert np.abs(got - np.array(g["hidden_only"])).max() <= 2e-3
+    got = lm.confidence(th, None, tw[:256], tb, sts=g["sts"]).cpu().numpy()
+    np.testing.assert_array_equal(got, oracle.confidence(hidden, None, w[:256], float(b[0]), sts=g["sts"]))
+    assert np.abs(got - np.array(g["hidden_only_sts"])).max() <= 2e-3
+    # odd widths (not multiples of 32) and the state's done flag
+    rng = np.random.default_rng(9)
+    h2 = oracle.f32_to_bf16(rng.standard_normal((3, 77)).astype(np.float32)); e2 = oracle.f32_to_bf16(rng.standard_normal((3, 5)).astype(np.float32))
+    w2 = (rng.standard_normal(82) * 0.1).astype(np.float32); b2 = np.float32([0.25])
+    got = lm.confidence(as_bf16(h2), as_bf16(e2), torch.from_numpy(w2).cuda(), torch.from_numpy(b2).cuda()).cpu().numpy()
+    np.testing.assert_array_equal(got, oracle.confidence(h2, e2, w2, 0.25))
+    layout = lm.StepStateLayout(8, 7)
+    done = layout.to_device({"done": 1})
+    out = torch.full((3,), -1.0, device="cuda")
+    lm.confidence(as_bf16(h2), as_bf16(e2), torch.from_numpy(w2).cuda(), torch.from_numpy(b2).cuda(), out=out, layout=layout, state=done)
+    assert out.cpu().tolist() == [-1.0, -1.0, -1.0]
+    with pytest.raises(ValueError):
+        lm.confidence(th, None, tw[:256], tb, sts=[0.0])

@@ -161,3 +161,27 @@ def test_draft_q_equals_the_reference(golden, vocab, temperature):
 
 def vmax_of(codes):
     return float(oracle.bf16_to_f32(codes).max())
+
+
+def confidence_inputs():
+    """tests/kernels/test_draft_ops.py:229-235: default_rng(4), gamma 7, hidden 256, rank 64, BF16-rounded weights and bias."""
+    rbf = lambda x: oracle.bf16_to_f32(oracle.f32_to_bf16(np.asarray(x, dtype=np.float32)))
+    rng = np.random.default_rng(4)
+    hidden = oracle.f32_to_bf16(rng.standard_normal((7, 256)).astype(np.float32))
+    emb = oracle.f32_to_bf16(rng.standard_normal((7, 64)).astype(np.float32))
+    w = rbf(rng.standard_normal(320) * 0.05)
+    b = rbf(rng.standard_normal(1) * 0.5)
+    return hidden, emb, w, b
+
+
+def test_confidence_head_equals_the_reference_test_values(golden):
+    g = golden["confidence"]
+    hidden, emb, w, b = confidence_inputs()
+    assert int(hidden.astype(np.uint64).sum() + emb.astype(np.uint64).sum()) == g["inputs_crc"]
+    # the reference's bar for its kernel is 2e-3; FP32 accumulation in the kernel's order stays within 1e-6 of the float64 statement
+    # unless a BF16 rounding of the dot product flips (one BF16 ulp of the logit moves the sigmoid by < 2e-3)
+    for got, want in ((oracle.confidence(hidden, emb, w, float(b[0])), g["with_emb"]),
+                      (oracle.confidence(hidden, None, w[:256], float(b[0])), g["hidden_only"]),
+                      (oracle.confidence(hidden, None, w[:256], float(b[0]), sts=g["sts"]), g["hidden_only_sts"])):
+        assert np.abs(got - np.array(want)).max() <= 2e-3
+        assert np.count_nonzero(np.abs(got - np.array(want)) > 1e-6) <= 1
