@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) draft_q_kernel(DraftQDev P) {
   // every row is shared by `split` warps: row maximum and best Gumbel key (with this thread's runner-up, for the tie flag)
   const int split = max(1, kWarps / R);
   const float inv_t32 = __double2float_rn(1.0 / static_cast<double>(P.temperature));
-  uint64_t my_best = 0ull; float my_second = -INFINITY; bool my_nan = false;  // of the (single) item this warp owns per pass
+  uint64_t my_best = 0ull; float my_second = -INFINITY;                       // of the (single) item this warp owns
   for (int item = warp; item < R * split; item += kWarps) {
     const int r = item / split, part = item - r * split;
     const uint32_t t_id = 2000u + static_cast<uint32_t>(P.first_position + r);
@@ -70,9 +70,8 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) draft_q_kernel(DraftQDev P) {
     if (lane == 0 && wv) atomicMax(&ws->row_best[r], static_cast<unsigned long long>(wv));
     if (lane == 0 && wk) atomicMax(&ws->draft_w[r], static_cast<unsigned long long>(wk));
     if (__any_sync(kFull, nan) && lane == 0) atomicOr(&ws->pad, 1u << r);
-    if (item < kWarps) { my_best = kbest; my_second = ksecond; my_nan = nan; }   // R * split <= kWarps unless R > kWarps (not allowed)
+    if (item < kWarps) { my_best = kbest; my_second = ksecond; }            // R * split <= kWarps: one item per warp
   }
-  (void)my_nan;
   grid_barrier(ws, 1u * G);
 
   // ---- phase 1: the fixed-point mass relative to the row maximum; the best key that lost ----------------------------------

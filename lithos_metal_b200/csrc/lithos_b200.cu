@@ -62,9 +62,10 @@ __global__ void __launch_bounds__(kBlock, 1) sample_generic_kernel(SampleDev P, 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   GenericSmem& s = *reinterpret_cast<GenericSmem*>(smem_raw);
   uint32_t* pen_bits = reinterpret_cast<uint32_t*>(smem_raw + sizeof(GenericSmem));
-  const int n = list ? *n_list : P.rows;
+  const int n = list ? min(*n_list, P.rows) : P.rows;
   for (int i = blockIdx.x; i < n; i += gridDim.x) {
-    sample_row_generic(P, list ? list[i] : i, s, pen_bits);
+    const int row = list ? list[i] : i;
+    if (row >= 0 && row < P.rows) sample_row_generic(P, row, s, pen_bits);
     __syncthreads();
   }
 }
@@ -77,7 +78,10 @@ __global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, con
   extern __shared__ __align__(16) unsigned char smem_raw[];
   FastSmem& s = *reinterpret_cast<FastSmem*>(smem_raw);
   __shared__ int item[2];
-  const int n = list ? *n_list : P.rows;
+  // A kernel launched behind this one with programmatic stream serialization (the top-k kernel, which works on other rows and
+  // reads nothing this kernel writes) may take every SM a block of this grid has left, instead of waiting for the whole grid.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int n = list ? min(*n_list, P.rows) : P.rows;
   if (threadIdx.x == 0) { item[0] = atomicAdd(next_item, 1); item[1] = item[0] < n ? atomicAdd(next_item, 1) : n; }
   __syncthreads();
   for (;;) {
@@ -85,7 +89,10 @@ __global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, con
     if (i >= n) break;
     __syncthreads();
     if (threadIdx.x == 0) { item[0] = in; item[1] = in < n ? atomicAdd(next_item, 1) : n; }
-    sample_row_fast(P, list ? list[i] : i, in < n ? (list ? list[in] : in) : -1, s, redo, n_redo);
+    const int row = list ? list[i] : i;
+    int next = in < n ? (list ? list[in] : in) : -1;
+    if (next >= P.rows) next = -1;
+    if (row >= 0 && row < P.rows) sample_row_fast(P, row, next, s, redo, n_redo);   // (a list entry is a row index by construction)
     __syncthreads();
   }
 }
@@ -100,6 +107,8 @@ static int cuda_fail(cudaError_t e) {
   std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
   return LM_E_CUDA;
 }
+
+constexpr int kOverlapRowsPerSM = 8;   // up to this many rows per SM the two sampler kernels run side by side (lm_sample)
 
 static int sm_count(int* out) {
   int dev = 0;
@@ -160,8 +169,8 @@ float lm_uniform01(uint64_t seed, uint32_t step, uint32_t t, uint32_t index) { r
 size_t lm_workspace_bytes(int64_t rows, int64_t vocab) {
   (void)vocab;
   if (rows < 0) rows = 0;
-  // argmax partials | rows left to the generic kernel | rows left to the histogram kernel | four counters
-  return align256(static_cast<size_t>(rows) * sizeof(ArgmaxWs)) + 2 * align256(static_cast<size_t>(rows) * sizeof(uint32_t)) + 256;
+  // argmax partials | rows for the generic kernel | rows that are not the top-k kernel's | rows the top-k kernel left | counters
+  return align256(static_cast<size_t>(rows) * sizeof(ArgmaxWs)) + 3 * align256(static_cast<size_t>(rows) * sizeof(uint32_t)) + 256;
 }
 
 size_t lm_verify_workspace_bytes(int32_t n_draft, int64_t vocab) {
@@ -271,10 +280,14 @@ int lm_sample(const lm_sample_args* a) {
   if (fast) {
     if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) || a->workspace_bytes < lm_workspace_bytes(a->rows, a->vocab))
       return LM_E_WORKSPACE;
+    const size_t rows_bytes = align256(static_cast<size_t>(a->rows) * sizeof(uint32_t));
     char* ws = static_cast<char*>(a->workspace) + align256(static_cast<size_t>(a->rows) * sizeof(ArgmaxWs));
-    int* redo = reinterpret_cast<int*>(ws);
-    int* list = reinterpret_cast<int*>(ws + align256(static_cast<size_t>(a->rows) * sizeof(uint32_t)));
-    int* counters = reinterpret_cast<int*>(ws + 2 * align256(static_cast<size_t>(a->rows) * sizeof(uint32_t)));
+    int* redo = reinterpret_cast<int*>(ws);                                // rows for the generic kernel
+    int* list_other = reinterpret_cast<int*>(ws + rows_bytes);             // rows that are not the top-k kernel's
+    int* list_left = reinterpret_cast<int*>(ws + 2 * rows_bytes);          // rows the top-k kernel left
+    int* counters = reinterpret_cast<int*>(ws + 3 * rows_bytes);
+    // counters: 0 next row of the top-k kernel, 1 length of list_left, 2 next item of the histogram kernel, 3 length of redo,
+    //           4 length of list_other, 5 next item of the histogram kernel's second launch
     static thread_local bool fast_attr = false;
     if (!fast_attr) {
       cudaError_t e = cudaFuncSetAttribute(sample_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FastSmem)));
@@ -283,23 +296,43 @@ int lm_sample(const lm_sample_args* a) {
       fast_attr = true;
     }
     const int limit = static_cast<int>((a->flags >> 8) & 0xFFu);
-    // rows with a top_k go through the candidate kernel first (three small blocks per SM); it lists the rows it leaves
     const bool topk = !(a->flags & LM_FLAG_EXACT_ONLY) && a->vocab >= kTopkMinVocab && (a->top_k != nullptr || (a->top_k_s >= 1 && a->top_k_s <= kTopkMaxK)) &&
                       (a->temperature != nullptr || a->temperature_s > 0.0f) && (!pen || a->hist_len <= kTopkHist);
     {
-      const cudaError_t e = cudaMemsetAsync(counters, 0, 4 * sizeof(int), st);   // next row of the top-k kernel, length of its list, next item of the histogram kernel, length of its list
-      if (e != cudaSuccess) return cuda_fail(e);
-    }
-    if (topk) {
-      int grid1 = static_cast<int>(a->rows < static_cast<long long>(kTopkPerSM) * sms ? a->rows : static_cast<long long>(kTopkPerSM) * sms);
-      if (limit > 0 && grid1 > limit) grid1 = limit;
-      sample_topk_kernel<<<grid1, kTB, sizeof(TopkSmem), st>>>(P, list, counters);
-      const cudaError_t e = cudaGetLastError();
+      const cudaError_t e = cudaMemsetAsync(counters, 0, 8 * sizeof(int), st);
       if (e != cudaSuccess) return cuda_fail(e);
     }
     int grid = static_cast<int>(a->rows < sms ? a->rows : sms);
     if (limit > 0 && grid > limit) grid = limit;
-    sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, topk ? list : nullptr, topk ? counters + 1 : nullptr, counters + 2, redo, counters + 3);
+    int grid1 = static_cast<int>(a->rows < static_cast<long long>(kTopkPerSM) * sms ? a->rows : static_cast<long long>(kTopkPerSM) * sms);
+    if (limit > 0 && grid1 > limit) grid1 = limit;
+    if (!topk) {
+      sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, nullptr, nullptr, counters + 2, redo, counters + 3);
+    } else if (a->rows > static_cast<int64_t>(kOverlapRowsPerSM) * sms) {
+      // Many rows per SM: the top-k kernel first (it lists the rows it does not take or cannot finish), then the histogram
+      // kernel on that list. The few rows the top-k kernel hands on are absorbed among the histogram kernel's other rows.
+      sample_topk_kernel<<<grid1, kTB, sizeof(TopkSmem), st>>>(P, list_left, counters, 1);
+      sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, list_left, counters + 1, counters + 2, redo, counters + 3);
+    } else {
+      // Few rows per SM: the length of a launch is the length of its longest rows, so the two kernels, which work on different
+      // rows, share the GPU. The histogram kernel (long rows, one block per SM) goes first on the rows a one-thread-per-row
+      // kernel lists for it; the top-k kernel is launched behind it with programmatic stream serialization and takes the SMs
+      // as the histogram kernel's blocks leave them (at once, for the SMs it has no rows for); a second launch of the histogram
+      // kernel takes what the top-k kernel handed on (usually nothing: it leaves at once).
+      sample_classify_kernel<<<static_cast<int>((a->rows + 255) / 256), 256, 0, st>>>(P, list_other, counters + 4);
+      sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, list_other, counters + 4, counters + 2, redo, counters + 3);
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return cuda_fail(e);
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(grid1); cfg.blockDim = dim3(kTB); cfg.dynamicSmemBytes = sizeof(TopkSmem); cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr; cfg.numAttrs = 1;
+      e = cudaLaunchKernelEx(&cfg, sample_topk_kernel, P, list_left, counters, 0);
+      if (e != cudaSuccess) return cuda_fail(e);
+      sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, list_left, counters + 1, counters + 5, redo, counters + 3);
+    }
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e);
     redo_list = redo; redo_n = counters + 3;

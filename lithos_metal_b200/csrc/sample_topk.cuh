@@ -153,6 +153,22 @@ __device__ __forceinline__ uint32_t warp_reserve(uint32_t* counter, uint32_t min
   return base + incl - mine;
 }
 
+// Whether a row is this kernel's at all, from its knobs and address alone (no look at the logits).
+__device__ __forceinline__ bool topk_row_eligible(const SampleDev& P, int row) {
+  const int V = P.vocab;
+  const float T = P.temperature ? P.temperature[row] : P.temperature_s;
+  const int top_k = P.top_k ? P.top_k[row] : P.top_k_s;
+  const uint16_t* rowp = reinterpret_cast<const uint16_t*>(P.logits) + static_cast<size_t>(row) * static_cast<size_t>(P.row_stride);
+  return T > 0.0f && top_k >= 1 && top_k <= kTopkMaxK && (V % kChunk) == 0 && V >= kTopkMinVocab && V <= kTopkMaxVocab &&
+         (reinterpret_cast<uintptr_t>(rowp) & 15u) == 0 && !(P.history != nullptr && P.hist_len > kTopkHist);
+}
+
+// The rows that are not the top-k kernel's, listed for the histogram kernel (one thread per row).
+__global__ void sample_classify_kernel(SampleDev P, int* list, int* n_list) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row < P.rows && !topk_row_eligible(P, row)) list[atomicAdd(n_list, 1)] = row;
+}
+
 // One row. Every thread of the block calls with the same arguments; returns true when the row is finished, false when the
 // histogram kernel has to take it (nothing has been written then).
 // `next` is the row this block takes afterwards (-1: none): its sample and history are pulled into L2 meanwhile.
@@ -165,9 +181,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   const float min_p = P.min_p ? P.min_p[row] : P.min_p_s;
   const uint16_t* rowp = reinterpret_cast<const uint16_t*>(P.logits) + static_cast<size_t>(row) * static_cast<size_t>(P.row_stride);
   const bool pen_on = P.history != nullptr;
-  if (!(T > 0.0f) || top_k < 1 || top_k > kTopkMaxK || (V % kChunk) != 0 || V < kTopkMinVocab || V > (1 << 18) ||
-      (reinterpret_cast<uintptr_t>(rowp) & 15u) != 0 || (pen_on && P.hist_len > kTopkHist))
-    return false;
   const int n_chunks = V / kChunk;
   const uint4* p4 = reinterpret_cast<const uint4*>(rowp);
   const bool has_p = top_p > 0.0f && top_p < 1.0f, has_m = min_p > 0.0f;
@@ -584,9 +597,9 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
 }
 
 // Rows are handed out through a counter in the workspace (counters[0], zeroed by the host before the launch): a block takes
-// the next row and either finishes it (no later kernel touches it) or appends it to `list` (length in
+// the next row, passes over it if it is not this kernel's (listing it if `list_others`), and else either finishes it or appends it to `list` (length in
 // counters[1]) for the histogram kernel. The order of the list varies from run to run; what is computed per row does not.
-__global__ void __launch_bounds__(kTB, kTopkPerSM) sample_topk_kernel(SampleDev P, int* list, int* counters) {
+__global__ void __launch_bounds__(kTB, kTopkPerSM) sample_topk_kernel(SampleDev P, int* list, int* counters, int list_others) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   TopkSmem& c = *reinterpret_cast<TopkSmem*>(smem_raw);
   __shared__ int item[2];                                                   // the row in hand and the one after it
@@ -598,12 +611,20 @@ __global__ void __launch_bounds__(kTB, kTopkPerSM) sample_topk_kernel(SampleDev 
     if (row >= P.rows) break;
     __syncthreads();
     if (threadIdx.x == 0) { item[0] = next; item[1] = next < P.rows ? atomicAdd(&counters[0], 1) : P.rows; }
+    if (!topk_row_eligible(P, row)) {                                       // not this kernel's row: listed here, or already by sample_classify_kernel
+      if (list_others && threadIdx.x == 0) list[atomicAdd(&counters[1], 1)] = row;
+      __syncthreads();                                                      // thread 0 has moved item[] on: nobody reads it again before that
+      continue;
+    }
     const bool done = topk_row(P, row, next < P.rows ? next : -1, c);
     __syncthreads();
     if (threadIdx.x == 0) {
       if (!done) list[atomicAdd(&counters[1], 1)] = row;
     }
   }
+  // This grid may have been started before the grid launched ahead of it had finished (programmatic stream serialization). The
+  // stream takes the end of this grid for the end of both, so no block leaves before the earlier grid is complete.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 }  // namespace lm

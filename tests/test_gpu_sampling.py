@@ -316,3 +316,24 @@ def test_streaming_draw_over_wide_kept_sets():
         assert not np.any(r.status.cpu().numpy() & 1), r.status                 # all through the streaming kernel
         np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
         np.testing.assert_array_equal(r.tokens.cpu().numpy(), tok)
+
+
+def test_large_batch_launch_order():
+    """More than eight rows per SM: the top-k kernel runs first and the histogram kernel takes its list (smaller batches run the
+    two side by side). Same tokens and thresholds as the oracle either way."""
+    rows, V = 1400, 32768
+    cfg = inputs.config3(rows=rows, vocab=V, hist_len=256, seed=61)
+    x = bf16_tensor(cfg["logits"])
+    knobs = {k: torch.from_numpy(cfg[k]).cuda() for k in ("temperature", "top_k", "top_p")}
+    hist, u = torch.from_numpy(cfg["history"]).cuda(), torch.from_numpy(cfg["uniforms"]).cuda()
+    p = lm.SamplingParams(draw="inverse_cdf", repetition_penalty=1.1, presence_penalty=0.5, **knobs)
+    r = lm.sample(x, p, history=hist, uniforms=u, return_tau=True, return_status=True)
+    tok, tau, _ = oracle.sample_batch(cfg["logits"], temperature=cfg["temperature"], top_k=cfg["top_k"], top_p=cfg["top_p"], history=cfg["history"],
+                                      repetition_penalty=1.1, presence_penalty=0.5, draw="inverse_cdf", uniforms=cfg["uniforms"], n_threads=8)
+    status = r.status.cpu().numpy()
+    assert np.count_nonzero(status & 64) >= 0.7 * np.count_nonzero(cfg["top_k"] > 0)        # the rows with a top_k went through the top-k kernel
+    np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
+    np.testing.assert_array_equal(r.tokens.cpu().numpy(), tok)
+    small = lm.sample(x[:700], lm.SamplingParams(draw="inverse_cdf", repetition_penalty=1.1, presence_penalty=0.5, **{k: v[:700] for k, v in knobs.items()}),
+                      history=hist[:700], uniforms=u[:700], return_tau=True)
+    assert torch.equal(small.tokens, r.tokens[:700]) and torch.equal(small.tau, r.tau[:700])
