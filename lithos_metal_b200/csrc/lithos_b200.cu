@@ -108,7 +108,10 @@ static int cuda_fail(cudaError_t e) {
   return LM_E_CUDA;
 }
 
-constexpr int kOverlapRowsPerSM = 8;   // up to this many rows per SM the two sampler kernels run side by side (lm_sample)
+#ifndef LM_OVERLAP_ROWS_PER_SM
+#define LM_OVERLAP_ROWS_PER_SM 16
+#endif
+constexpr int kOverlapRowsPerSM = LM_OVERLAP_ROWS_PER_SM;   // up to this many rows per SM the two sampler kernels run side by side (lm_sample)
 
 static int sm_count(int* out) {
   int dev = 0;

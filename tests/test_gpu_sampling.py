@@ -319,9 +319,9 @@ def test_streaming_draw_over_wide_kept_sets():
 
 
 def test_large_batch_launch_order():
-    """More than eight rows per SM: the top-k kernel runs first and the histogram kernel takes its list (smaller batches run the
+    """More than sixteen rows per SM: the top-k kernel runs first and the histogram kernel takes its list (smaller batches run the
     two side by side). Same tokens and thresholds as the oracle either way."""
-    rows, V = 1400, 32768
+    rows, V = 2600, 32768
     cfg = inputs.config3(rows=rows, vocab=V, hist_len=256, seed=61)
     x = bf16_tensor(cfg["logits"])
     knobs = {k: torch.from_numpy(cfg[k]).cuda() for k in ("temperature", "top_k", "top_p")}
