@@ -171,9 +171,17 @@ LM_API int lm_argmax_static(const void* logits, int32_t dtype, int64_t rows, int
  *               (over p itself on the bonus row, or when the residual is empty).
  * Outputs: out_accept[0] = accept length; out_final[0] = final token; out_tokens (optional, [n_draft + 1]) =
  * drafts[0..accept) followed by the final token, -1 beyond.
+ *
+ * commit (optional): the fields lm_accept_scan takes (step_state, t_max, gamma_max, ring, ring_cap, eos, eos_list, n_eos, log,
+ * log_cap, ctx_cap, lm; `tokens` and `stream` are ignored). The thread that writes out_tokens then runs the accept scan on them
+ * (kernels/common/spec_ops.metal:148-195): commit to the token ring, advance the StepState; one launch closes the round. The
+ * state must describe this round (verify_len == n_draft, t_this_step == n_draft + 1; a prefill chunk takes the scan's prefill
+ * branch); otherwise the state gets error 4 and done = 1. A grid-barrier timeout of the launch gives error 3 and done = 1.
  */
 #define LM_VERIFY_GREEDY 0
 #define LM_VERIFY_STOCHASTIC 1
+
+struct lm_step_args;
 
 typedef struct lm_verify_args {
   uint32_t struct_size;
@@ -201,6 +209,7 @@ typedef struct lm_verify_args {
   int64_t draft_logits_stride;
   const float* draft_vmax;     /* [n_draft] row maxima from lm_draft_q */
   const uint64_t* draft_mass;  /* [n_draft] fixed-point row masses from lm_draft_q */
+  const struct lm_step_args* commit;  /* NULL, or: close the round in the same launch (see below); needs out_tokens */
 } lm_verify_args;
 
 #define LM_MAX_DRAFT 15

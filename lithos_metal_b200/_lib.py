@@ -45,6 +45,7 @@ class VerifyArgs(C.Structure):
         ("out_accept", C.c_void_p), ("out_final", C.c_void_p), ("out_tokens", C.c_void_p), ("out_p_draft", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
         ("draft_logits", C.c_void_p), ("draft_logits_stride", C.c_int64), ("draft_vmax", C.c_void_p), ("draft_mass", C.c_void_p),
+        ("commit", C.c_void_p),
     ]
 
 

@@ -494,6 +494,17 @@ int lm_verify(const lm_verify_args* a) {
   P.tau = a->tau; P.u_accept = a->u_accept; P.u_final = a->u_final;
   P.out_accept = a->out_accept; P.out_final = a->out_final; P.out_tokens = a->out_tokens; P.out_p_draft = a->out_p_draft;
   P.ws = static_cast<VerifyWs*>(a->workspace);
+  P.commit = 0;
+  if (a->commit) {
+    const lm_step_args* c = a->commit;
+    rc = step_args_ok(c);
+    if (rc != LM_OK) return rc;
+    if (!a->out_tokens || !c->ring || c->ring_cap == 0 || (c->log_cap && !c->log)) return LM_E_INVALID;
+    P.commit = 1;
+    P.accept = AcceptDev{a->out_tokens, static_cast<uint32_t*>(c->step_state), c->t_max, c->gamma_max > 1 ? c->gamma_max : 1,
+                         reinterpret_cast<unsigned long long*>(c->ring), c->ring_cap, EosSet{c->eos, c->eos_list, c->n_eos}, c->log, c->log_cap,
+                         c->ctx_cap, c->lm};
+  }
   // one block per SM, all resident at once (the phases meet at a grid barrier): a cooperative launch guarantees it
   int grid = sms < 1024 ? sms : 1024;
 #ifdef LM_VERIFY_GRID_DIV

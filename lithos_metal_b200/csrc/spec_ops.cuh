@@ -52,8 +52,8 @@ struct AcceptDev {
   uint32_t* log; uint32_t log_cap; uint32_t ctx_cap; int lm;
 };
 
-__global__ void accept_scan_kernel(AcceptDev p) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+// The accept scan proper; one thread. Also the last act of the verify kernel when a round is committed there.
+__device__ void accept_scan_body(const AcceptDev& p) {
   StepStateView st{p.state, p.t_max, p.g};
   if (st.done()) return;
   const uint32_t t = st.t_this_step();
@@ -98,6 +98,11 @@ __global__ void accept_scan_kernel(AcceptDev p) {
   if (p.lm) st.n_inject() = (st.position() > st.drafter_ctx_len()) ? st.position() - st.drafter_ctx_len() : 0u;
   if (stop) st.done() = 1u;
   if (p.ctx_cap && st.position() >= p.ctx_cap) { st.error() = 2u; st.done() = 1u; }
+}
+
+__global__ void accept_scan_kernel(AcceptDev p) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  accept_scan_body(p);
 }
 
 struct SelectDev {

@@ -12,6 +12,7 @@
 // counter in that workspace.
 #pragma once
 #include "common.cuh"
+#include "spec_ops.cuh"
 
 namespace lm {
 
@@ -41,7 +42,24 @@ struct VerifyDev {
   const float* tau; const float* u_accept; const float* u_final;
   int32_t* out_accept; int32_t* out_final; int32_t* out_tokens; float* out_p_draft;
   VerifyWs* ws;
+  int commit; AcceptDev accept;                          // commit != 0: close the round on the StepState as accept_scan would
 };
+
+// The round's bookkeeping, by the thread that has just written out_tokens: the accept scan on those tokens
+// (kernels/common/spec_ops.metal:148-195). The verify rows must be the step's rows (a decode round: t_this_step = verify_len + 1
+// = n_draft + 1); a prefill chunk takes the scan's prefill branch, which reads no token; anything else is a caller error and
+// ends the generation with error code 4.
+__device__ __forceinline__ void verify_commit(const VerifyDev& P) {
+  if (!P.commit) return;
+  StepStateView st{P.accept.state, P.accept.t_max, P.accept.g};
+  if (!st.done() && P.ws->error != 0u) { st.error() = 3u; st.done() = 1u; return; }   // a grid barrier of this launch ran out: nothing to commit
+  if (!st.done() && st.prefill_left() == 0u && (st.verify_len() != static_cast<uint32_t>(P.n_draft) || st.t_this_step() != static_cast<uint32_t>(P.n_draft) + 1u)) {
+    st.error() = 4u; st.done() = 1u;
+    return;
+  }
+  __threadfence();
+  accept_scan_body(P.accept);
+}
 
 // Every block arrives, then waits until `target` arrivals are visible. Bounded: on time-out the error word is set and
 // the block carries on (its results are then meaningless, the host sees the error).
@@ -220,6 +238,8 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
       const bool bad = ws->error != 0;
       if (tid == 0) { P.out_accept[0] = bad ? -1 : acc; P.out_final[0] = bad ? -1 : fin; }
       if (P.out_tokens && tid < R) P.out_tokens[tid] = tid < acc ? s_drafts[tid] : (tid == acc ? fin : -1);
+      __syncwarp();
+      if (tid == 0) verify_commit(P);
     }
     // the last block to leave puts the workspace back to its clean state
     __syncthreads();
@@ -347,11 +367,13 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
           const bool bad = ws->error != 0;
           P.out_accept[0] = bad ? -1 : j; P.out_final[0] = bad ? -1 : s_token;
           if (P.out_tokens) for (int r = 0; r < R; r++) P.out_tokens[r] = r < j ? P.drafts[r] : (r == j ? s_token : -1);
+          verify_commit(P);
         }
       }
     } else if (b == 0 && tid == 0) {                                     // a row with no weight at all (empty or all -inf)
       P.out_accept[0] = ws->error ? -1 : j; P.out_final[0] = -1;
       if (P.out_tokens) for (int r = 0; r < R; r++) P.out_tokens[r] = r < j ? P.drafts[r] : -1;
+      verify_commit(P);
     }
   }
   __syncthreads();

@@ -61,7 +61,8 @@ def draft_q(logits: torch.Tensor, *, temperature: float, seed: int = 0, step: in
 
 def verify(target_logits: torch.Tensor, draft_ids: torch.Tensor, draft_probs: Optional[torch.Tensor] = None, uniforms: Optional[torch.Tensor] = None,
            u_resample: Optional[torch.Tensor] = None, mode: str = "greedy", *, temperature: float = 1.0, tau: Optional[torch.Tensor] = None,
-           return_p_draft: bool = False, draft_logits: Optional[torch.Tensor] = None, draft_stats: Optional[DraftQ] = None) -> Tuple[torch.Tensor, ...]:
+           return_p_draft: bool = False, draft_logits: Optional[torch.Tensor] = None, draft_stats: Optional[DraftQ] = None,
+           commit: Optional[dict] = None) -> Tuple[torch.Tensor, ...]:
     """``(accept_len [1], final_token [1], tokens [n + 1])`` as int32 CUDA tensors (plus ``p_draft [n]`` on request).
 
     ``target_logits`` [n + 1, V] bfloat16/float32; ``draft_ids`` [n] int32; stochastic mode also takes the drafter's
@@ -69,7 +70,10 @@ def verify(target_logits: torch.Tensor, draft_ids: torch.Tensor, draft_probs: Op
     ``u_resample`` [1], all in [0, 1); ``tau`` [n + 1] optionally restricts every row to its kept set (``sample(...,
     return_tau=True)``). Instead of ``draft_probs`` the drafter's distribution may be given the way the reference keeps it:
     ``draft_logits`` [n, V] bfloat16 (the rows ``draft_q`` sampled from) with ``draft_stats`` = what ``draft_q`` returned
-    for them at the same temperature. Asynchronous on the current stream.
+    for them at the same temperature. ``commit`` closes the round in the same launch: a dict with ``layout`` (StepStateLayout),
+    ``state`` and ``ring`` tensors and optionally ``eos``, ``log``, ``ctx_cap``, ``lm`` — the arguments of ``accept_scan``, which
+    then runs on the verified tokens inside the verify kernel (the state must describe this round: ``verify_len == n``,
+    ``t_this_step == n + 1``). Asynchronous on the current stream.
     """
     if mode not in ("greedy", "stochastic"):
         raise ValueError("mode must be 'greedy' or 'stochastic'")
@@ -128,6 +132,18 @@ def verify(target_logits: torch.Tensor, draft_ids: torch.Tensor, draft_probs: Op
     if return_p_draft and mode == "stochastic":
         p_draft = torch.empty(n, dtype=torch.float32, device=dev)
         a.out_p_draft = p_draft.data_ptr()
+    if commit is not None:
+        from . import step_state as _ss
+        c = _ss._args(commit["layout"], commit["state"], commit.get("eos", -1), keep)
+        ring, log = commit["ring"], commit.get("log")
+        if ring.dtype != torch.int64 or not ring.is_cuda:
+            raise ValueError("ring must be an int64 CUDA tensor")
+        c.ring, c.ring_cap = ring.data_ptr(), ring.numel()
+        if log is not None:
+            c.log, c.log_cap = log.data_ptr(), log.numel()
+        c.ctx_cap, c.lm = int(commit.get("ctx_cap", 0)), int(bool(commit.get("lm", False)))
+        keep.append(c)
+        a.commit = C.addressof(c)
     L = _lib.lib()
     ws = _workspace(dev, L.lm_verify_workspace_bytes(n, target_logits.shape[1]), "verify")
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()

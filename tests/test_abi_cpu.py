@@ -30,14 +30,14 @@ def test_library_exports_every_declared_symbol():
 def test_ctypes_structs_match_the_c_layout():
     src = '#include <stdio.h>\n#include "lithos_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu ", sizeof(lm_sample_args), sizeof(lm_verify_args),' \
           ' offsetof(lm_sample_args, out_tokens), offsetof(lm_verify_args, workspace), sizeof(lm_draft_q_args), offsetof(lm_draft_q_args, out_mass),' \
-          ' offsetof(lm_verify_args, draft_mass));printf("%zu %zu\\n", sizeof(lm_confidence_args), offsetof(lm_confidence_args, stream));return 0;}\n'
+          ' offsetof(lm_verify_args, draft_mass));printf("%zu ", offsetof(lm_verify_args, commit));printf("%zu %zu\\n", sizeof(lm_confidence_args), offsetof(lm_confidence_args, stream));return 0;}\n'
     with tempfile.TemporaryDirectory() as d:
         open(os.path.join(d, "t.c"), "w").write(src)
         subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), "-o", os.path.join(d, "t"), os.path.join(d, "t.c")], check=True)
         out = subprocess.run([os.path.join(d, "t")], capture_output=True, text=True, check=True).stdout.split()
     assert [int(x) for x in out] == [C.sizeof(_lib.SampleArgs), C.sizeof(_lib.VerifyArgs), _lib.SampleArgs.out_tokens.offset,
                                      _lib.VerifyArgs.workspace.offset, C.sizeof(_lib.DraftQArgs), _lib.DraftQArgs.out_mass.offset,
-                                     _lib.VerifyArgs.draft_mass.offset, C.sizeof(_lib.ConfidenceArgs), _lib.ConfidenceArgs.stream.offset]
+                                     _lib.VerifyArgs.draft_mass.offset, _lib.VerifyArgs.commit.offset, C.sizeof(_lib.ConfidenceArgs), _lib.ConfidenceArgs.stream.offset]
 
 
 def test_argument_validation_needs_no_device():

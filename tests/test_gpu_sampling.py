@@ -337,3 +337,25 @@ def test_large_batch_launch_order():
     small = lm.sample(x[:700], lm.SamplingParams(draw="inverse_cdf", repetition_penalty=1.1, presence_penalty=0.5, **{k: v[:700] for k, v in knobs.items()}),
                       history=hist[:700], uniforms=u[:700], return_tau=True)
     assert torch.equal(small.tokens, r.tokens[:700]) and torch.equal(small.tau, r.tau[:700])
+
+
+@pytest.mark.parametrize("rows,vocab,calls", [(600, 32768, 300), (2600, 32768, 60)])
+def test_back_to_back_calls_are_repeatable(rows, vocab, calls):
+    """Many calls in a row on one stream without a host synchronisation in between (each reuses the workspace's counters and
+    row lists, in both launch orders): every call returns what the first one did."""
+    cfg = inputs.config3(rows=rows, vocab=vocab, hist_len=128, seed=5)
+    x = bf16_tensor(cfg["logits"])
+    knobs = {k: torch.from_numpy(cfg[k]).cuda() for k in ("temperature", "top_k", "top_p")}
+    hist, u = torch.from_numpy(cfg["history"]).cuda(), torch.from_numpy(cfg["uniforms"]).cuda()
+    p = lm.SamplingParams(draw="inverse_cdf", repetition_penalty=1.1, presence_penalty=0.5, **knobs)
+    first = lm.sample(x, p, history=hist, uniforms=u, return_tau=True)
+    outs = [torch.empty(rows, dtype=torch.int32, device="cuda") for _ in range(calls)]
+    for o in outs:
+        lm.sample(x, p, history=hist, uniforms=u, out=o)
+    torch.cuda.synchronize()
+    stacked = torch.stack(outs)
+    assert bool((stacked == first.tokens.unsqueeze(0)).all())
+    tok, _, _ = oracle.sample_batch(cfg["logits"][:64], temperature=cfg["temperature"][:64], top_k=cfg["top_k"][:64], top_p=cfg["top_p"][:64],
+                                    history=cfg["history"][:64], repetition_penalty=1.1, presence_penalty=0.5, draw="inverse_cdf",
+                                    uniforms=cfg["uniforms"][:64], n_threads=8)
+    np.testing.assert_array_equal(first.tokens[:64].cpu().numpy(), tok)

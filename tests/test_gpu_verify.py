@@ -96,3 +96,56 @@ def test_repeated_calls_leave_the_workspace_clean():
     for _ in range(5):
         assert gpu_verify(target, drafts, q, ua, uf, "stochastic")[:3] == first[:3]
         gpu_verify(target, drafts, None, None, None, "greedy")
+
+
+@pytest.mark.parametrize("mode", ["greedy", "stochastic"])
+def test_verify_commits_the_round_like_accept_scan(mode):
+    """verify(..., commit=...) = verify followed by accept_scan on the same StepState: state bytes, token ring and accept log
+    equal; a stop token among the accepted drafts truncates the commit; a state that does not describe the round is refused
+    (error 4), a finished one is left alone."""
+    import lithos_metal_b200 as lm
+    V, n = 8192, 7
+    rng = np.random.default_rng(77)
+    target = oracle.f32_to_bf16((rng.standard_normal((n + 1, V)) * 2.0).astype(np.float32))
+    tx = torch.from_numpy(target.view(np.int16).copy()).cuda().view(torch.bfloat16)
+    greedy_pick = oracle.bf16_to_f32(target).argmax(axis=1).astype(np.int32)
+    layout = lm.StepStateLayout(8, 7)
+    for trial in range(4):
+        drafts = greedy_pick[:n].copy()
+        if trial:
+            drafts[rng.integers(1, n)] = 5                                  # a mismatch somewhere: accepted prefix + correction
+        q = torch.softmax(tx[:n].float() + 0.3 * torch.randn(n, V, device="cuda", generator=torch.Generator("cuda").manual_seed(trial)), -1)
+        ua, uf = torch.from_numpy(rng.random(n).astype(np.float32)), torch.tensor([float(rng.random())])
+        eos = int(drafts[1]) if trial == 2 else -1                          # a stop token inside the accepted prefix
+        base = {"step": 11, "position": 40, "t_this_step": n + 1, "verify_len": n, "anchor": 3, "pending_tokens": [3] + drafts.tolist(),
+                "ring_head": 6, "ring_tail": 2, "gamma": n}
+        args = (tx, torch.from_numpy(drafts)) + ((q, ua, uf, "stochastic") if mode == "stochastic" else (None, None, None, "greedy"))
+        # separate launches
+        st_a, ring_a, log_a = layout.to_device(base), torch.zeros(16, dtype=torch.int64, device="cuda"), torch.zeros(4, dtype=torch.int32, device="cuda")
+        out_a = lm.verify(*args)
+        lm.accept_scan(layout, st_a, out_a[2], ring_a, eos=eos, log=log_a, ctx_cap=64)
+        # one launch
+        st_b, ring_b, log_b = layout.to_device(base), torch.zeros(16, dtype=torch.int64, device="cuda"), torch.zeros(4, dtype=torch.int32, device="cuda")
+        out_b = lm.verify(*args, commit=dict(layout=layout, state=st_b, ring=ring_b, eos=eos, log=log_b, ctx_cap=64))
+        assert all(torch.equal(x, y) for x, y in zip(out_a, out_b))
+        assert torch.equal(st_a, st_b) and torch.equal(ring_a, ring_b) and torch.equal(log_a, log_b)
+        got = layout.from_device(st_b)
+        assert got["accepted"] == int(out_b[0]) and got["step"] == 12 and got["ring_head"] > 6
+        if trial == 2:
+            assert got["done"] == 1 and got["ring_head"] == 6 + 2           # drafts 0 and 1 (the stop token), nothing after it
+    # a state that is not this round's
+    st = layout.to_device({"t_this_step": 4, "verify_len": 3, "pending_tokens": [1, 2, 3, 4]})
+    ring = torch.zeros(16, dtype=torch.int64, device="cuda")
+    lm.verify(*args, commit=dict(layout=layout, state=st, ring=ring))
+    got = layout.from_device(st)
+    assert got["error"] == 4 and got["done"] == 1 and int(ring.abs().sum()) == 0
+    st = layout.to_device({"done": 1, "t_this_step": n + 1, "verify_len": n})
+    before = st.clone()
+    lm.verify(*args, commit=dict(layout=layout, state=st, ring=ring))
+    assert torch.equal(st, before)
+    # a prefill chunk: the scan's prefill branch, no token read
+    pre = {"prefill_left": 5, "t_this_step": 4, "position": 8, "step": 2}
+    st_a, st_b = layout.to_device(pre), layout.to_device(pre)
+    lm.accept_scan(layout, st_a, out_a[2], ring)
+    lm.verify(*args, commit=dict(layout=layout, state=st_b, ring=ring))
+    assert torch.equal(st_a, st_b)
