@@ -10,6 +10,7 @@ from . import build as _build
 LM_OK = 0
 DTYPE_BF16, DTYPE_F32 = 0, 1
 DRAW_GUMBEL, DRAW_INVERSE_CDF = 0, 1
+ABI_VERSION = 2                      # LM_ABI_VERSION of include/lithos_b200.h this binding was written against
 FLAG_TOPP_IN_TOPK = 1
 FLAG_EXACT_ONLY = 2
 VERIFY_GREEDY, VERIFY_STOCHASTIC = 0, 1
@@ -138,7 +139,7 @@ def lib():
         L.lm_error_string.argtypes = [C.c_int]
         L.lm_last_cuda_error.restype = C.c_char_p
         L.lm_device_sm_count.restype = C.c_int
-        if L.lm_abi_version() != 2:
+        if L.lm_abi_version() != ABI_VERSION:
             raise RuntimeError("lithos_metal_b200: ABI version mismatch between the binding and the shared object")
         _lib = L
     return _lib

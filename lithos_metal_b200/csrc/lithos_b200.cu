@@ -127,6 +127,27 @@ static int sm_count(int* out) {
   return LM_OK;
 }
 
+// Kernels that need more than 48 KB of dynamic shared memory must be told so once per device (the attribute belongs to the
+// device's copy of the function); remembered per device and kernel, raised when a call needs more.
+enum KernelSlot { kSlotFast, kSlotTopk, kSlotGeneric, kSlotVocabLocal, kSlotVerify, kSlotDraftQ, kSlotCount };
+
+static int ensure_dynamic_smem(KernelSlot slot, const void* func, size_t bytes) {
+  if (bytes <= 48 * 1024) return LM_OK;
+  constexpr int kMaxDevices = 64;
+  static std::mutex mutex;
+  static size_t granted[kMaxDevices][kSlotCount] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  std::lock_guard<std::mutex> lock(mutex);
+  const bool tracked = dev >= 0 && dev < kMaxDevices;
+  if (tracked && bytes <= granted[dev][slot]) return LM_OK;
+  e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (tracked) granted[dev][slot] = bytes;
+  return LM_OK;
+}
+
 static size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
 }  // namespace lm
@@ -291,13 +312,9 @@ int lm_sample(const lm_sample_args* a) {
     int* counters = reinterpret_cast<int*>(ws + 3 * rows_bytes);
     // counters: 0 next row of the top-k kernel, 1 length of list_left, 2 next item of the histogram kernel, 3 length of redo,
     //           4 length of list_other, 5 next item of the histogram kernel's second launch
-    static thread_local bool fast_attr = false;
-    if (!fast_attr) {
-      cudaError_t e = cudaFuncSetAttribute(sample_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FastSmem)));
-      if (e == cudaSuccess) e = cudaFuncSetAttribute(sample_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(TopkSmem)));
-      if (e != cudaSuccess) return cuda_fail(e);
-      fast_attr = true;
-    }
+    rc = ensure_dynamic_smem(kSlotFast, reinterpret_cast<const void*>(sample_fast_kernel), sizeof(FastSmem));
+    if (rc == LM_OK) rc = ensure_dynamic_smem(kSlotTopk, reinterpret_cast<const void*>(sample_topk_kernel), sizeof(TopkSmem));
+    if (rc != LM_OK) return rc;
     const int limit = static_cast<int>((a->flags >> 8) & 0xFFu);
     const bool topk = !(a->flags & LM_FLAG_EXACT_ONLY) && a->vocab >= kTopkMinVocab && (a->top_k != nullptr || (a->top_k_s >= 1 && a->top_k_s <= kTopkMaxK)) &&
                       (a->temperature != nullptr || a->temperature_s > 0.0f) && (!pen || a->hist_len <= kTopkHist);
@@ -341,12 +358,8 @@ int lm_sample(const lm_sample_args* a) {
     redo_list = redo; redo_n = counters + 3;
   }
   const size_t smem = sizeof(GenericSmem) + (pen ? static_cast<size_t>((a->vocab + 31) / 32) * 4 : 0) + 16;
-  static thread_local size_t smem_set = 0;
-  if (smem > smem_set) {
-    const cudaError_t e = cudaFuncSetAttribute(sample_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return cuda_fail(e);
-    smem_set = smem;
-  }
+  rc = ensure_dynamic_smem(kSlotGeneric, reinterpret_cast<const void*>(sample_generic_kernel), smem);
+  if (rc != LM_OK) return rc;
   const long long cap = fast ? sms : 8LL * sms;
   const int grid = static_cast<int>(a->rows < cap ? a->rows : cap);
   sample_generic_kernel<<<grid, kBlock, smem, st>>>(P, redo_list, redo_n);
@@ -375,12 +388,8 @@ int lm_vocab_local(const lm_vocab_args* a) {
   const int rc = sm_count(&sms);
   if (rc != LM_OK) return rc;
   const size_t smem = sizeof(GenericSmem) + 16;
-  static thread_local bool attr = false;
-  if (!attr) {
-    const cudaError_t e = cudaFuncSetAttribute(vocab_local_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return cuda_fail(e);
-    attr = true;
-  }
+  const int rs = ensure_dynamic_smem(kSlotVocabLocal, reinterpret_cast<const void*>(vocab_local_kernel), smem);
+  if (rs != LM_OK) return rs;
   const int grid = static_cast<int>(a->rows < 2LL * sms ? a->rows : 2LL * sms);
   vocab_local_kernel<<<grid, kBlock, smem, static_cast<cudaStream_t>(a->stream)>>>(P);
   const cudaError_t e = cudaGetLastError();
@@ -518,12 +527,8 @@ int lm_verify(const lm_verify_args* a) {
   size_t smem = rows_cached * static_cast<size_t>(per) * sizeof(float);
   int cached = smem <= 200 * 1024 ? 1 : 0;
   if (!cached) smem = 0;
-  static thread_local size_t verify_smem_set = 0;
-  if (smem > 48 * 1024 && smem > verify_smem_set) {
-    const cudaError_t ea = cudaFuncSetAttribute(verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (ea != cudaSuccess) return cuda_fail(ea);
-    verify_smem_set = smem;
-  }
+  rc = ensure_dynamic_smem(kSlotVerify, reinterpret_cast<const void*>(verify_kernel), smem);
+  if (rc != LM_OK) return rc;
   void* params[] = {&P, &cached};
 #ifdef LM_VERIFY_PLAIN_LAUNCH
   verify_kernel<<<grid, kVerifyBlock, smem, static_cast<cudaStream_t>(a->stream)>>>(P, cached);
@@ -567,12 +572,8 @@ int lm_draft_q(const lm_draft_q_args* a) {
   const int per = (static_cast<int>((a->vocab + grid - 1) / grid) + 7) & ~7;
   const size_t smem = static_cast<size_t>(a->rows) * static_cast<size_t>(per) * sizeof(float);
   if (smem > 200 * 1024) return LM_E_UNSUPPORTED;                          // rows x vocabulary beyond what the SMs can hold between the phases
-  static thread_local size_t draft_smem_set = 0;
-  if (smem > 48 * 1024 && smem > draft_smem_set) {
-    const cudaError_t ea = cudaFuncSetAttribute(draft_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (ea != cudaSuccess) return cuda_fail(ea);
-    draft_smem_set = smem;
-  }
+  const int rs = ensure_dynamic_smem(kSlotDraftQ, reinterpret_cast<const void*>(draft_q_kernel), smem);
+  if (rs != LM_OK) return rs;
   void* params[] = {&P};
   const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(draft_q_kernel), dim3(grid), dim3(kVerifyBlock), params, smem,
                                                     static_cast<cudaStream_t>(a->stream));
