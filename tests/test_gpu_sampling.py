@@ -359,3 +359,29 @@ def test_back_to_back_calls_are_repeatable(rows, vocab, calls):
                                     history=cfg["history"][:64], repetition_penalty=1.1, presence_penalty=0.5, draw="inverse_cdf",
                                     uniforms=cfg["uniforms"][:64], n_threads=8)
     np.testing.assert_array_equal(first.tokens[:64].cpu().numpy(), tok)
+
+
+@pytest.mark.parametrize("rows", [96, 2600])
+def test_sampling_call_in_a_cuda_graph(rows):
+    """A sampling call captured into a CUDA graph (both launch orders; the small one uses programmatic stream serialization)
+    replays to the same tokens as the eager call, several times over."""
+    V = 32768
+    cfg = inputs.config3(rows=rows, vocab=V, hist_len=64, seed=17)
+    x = bf16_tensor(cfg["logits"])
+    knobs = {k: torch.from_numpy(cfg[k]).cuda() for k in ("temperature", "top_k", "top_p")}
+    hist, u = torch.from_numpy(cfg["history"]).cuda(), torch.from_numpy(cfg["uniforms"]).cuda()
+    p = lm.SamplingParams(draw="inverse_cdf", repetition_penalty=1.1, presence_penalty=0.5, **knobs)
+    eager = lm.sample(x, p, history=hist, uniforms=u).tokens.clone()
+    out = torch.full((rows,), -7, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            lm.sample(x, p, history=hist, uniforms=u, out=out)
+    torch.cuda.synchronize()
+    for _ in range(5):
+        out.fill_(-7)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
