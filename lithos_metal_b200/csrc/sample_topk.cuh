@@ -58,7 +58,7 @@ struct TopkSmem {
   uint32_t prev_cut[8];                    // the block's last cutoff per size class of the candidate target (0: none yet)
   float warp_f[kTW];
   unsigned long long base;
-  uint32_t n_hit, n, n_side, wide, cross_bin;
+  uint32_t n_hit, n, n_side, wide, cross_bin, ref_key;
   int hit, token, row;
 };
 
@@ -225,7 +225,7 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
     uint4* p = reinterpret_cast<uint4*>(c.pen);
     for (int i = tid; i < (V + 127) / 128; i += kTB) p[i] = make_uint4(0u, 0u, 0u, 0u);
   }
-  if (tid == 0) { c.n_hit = 0u; c.n = 0u; c.n_side = 0u; c.wide = 0u; c.hit = kTopkCap; c.token = -1; c.cross_bin = 0u; }
+  if (tid == 0) { c.n_hit = 0u; c.n = 0u; c.n_side = 0u; c.wide = 0u; c.ref_key = 0u; c.hit = kTopkCap; c.token = -1; c.cross_bin = 0u; }
   __syncthreads();
   LM_TSUB(0);
   // the thread that sets an id's bit owns the id and lists it
@@ -265,6 +265,19 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
       __syncthreads();
       return c.probe_cnt[probe++];
     };
+    // the largest sampled logit: the reference point of the FP32 softmass (any value near the row maximum will do); it
+    // travels with the first probe's barrier
+    if (need_z) {
+      __nv_bfloat162 mx = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&qs[0].x), *reinterpret_cast<const __nv_bfloat162*>(&qs[0].y));
+      mx = __hmax2(mx, __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&qs[0].z), *reinterpret_cast<const __nv_bfloat162*>(&qs[0].w)));
+#pragma unroll
+      for (int j = 1; j < kSampleChunks; j++) {
+        mx = __hmax2(mx, __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].x), *reinterpret_cast<const __nv_bfloat162*>(&qs[j].y)));
+        mx = __hmax2(mx, __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].z), *reinterpret_cast<const __nv_bfloat162*>(&qs[j].w)));
+      }
+      const uint32_t key = __reduce_max_sync(kFull, fkey(fmaxf(__low2float(mx), __high2float(mx))));
+      if (lane == 0) atomicMax(&c.ref_key, key);
+    }
     uint32_t lo = 0x0000u, hi = 0x7F7Fu;                                    // invariant: count(sample >= lo) >= want, or lo is still 0 (handed back below)
     const uint32_t prev = c.prev_cut[cls];
     if (prev >= 0x0080u) {
@@ -288,8 +301,10 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   const float cut_val = __uint_as_float(cut_code << 16);
   LM_TPHASE(8);
 
-  // ---- the one pass: note the chunks that hold a logit >= cutoff; FP32 softmass with a per-thread running maximum ---------
-  float m = -INFINITY, sacc0 = 0.0f, sacc1 = 0.0f;
+  // ---- the one pass: note the chunks that hold a logit >= cutoff; FP32 softmass relative to the sampled maximum ----------
+  const float M = need_z ? fkey_inv(c.ref_key) : 0.0f;
+  const float nb = -M * c2a;
+  float sacc0 = 0.0f, sacc1 = 0.0f;
   uint32_t nan_seen = 0u;
   {
     const uint32_t cut2 = cut_code | (cut_code << 16);
@@ -322,34 +337,30 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
           if (slot < 2048u) c.hitlist[slot] = (static_cast<uint32_t>(cc) << 8) | mask;
         }
       }
-      const __nv_bfloat162 a = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[0]), *reinterpret_cast<const __nv_bfloat162*>(&w[1]));
-      const __nv_bfloat162 b = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[2]), *reinterpret_cast<const __nv_bfloat162*>(&w[3]));
-      const __nv_bfloat162 ab = __hmax2_nan(a, b);
-      nan_seen |= ~__heq2_mask(ab, ab);                                     // a NaN anywhere in the chunk survives the maxima
-      if (need_z && live) {
-        const float mx = fmaxf(__low2float(ab), __high2float(ab));
-        if (mx > m) { const float r = (m > -INFINITY) ? ex2_approx((m - mx) * c2a) : 0.0f; sacc0 *= r; sacc1 *= r; m = mx; }
-        if (m > -INFINITY) {
-          const float nb = -m * c2a;
+      if (need_z) {                                                         // (the padding is -inf: weight 0; a NaN or +inf logit poisons the sum)
 #pragma unroll
-          for (int k = 0; k < 4; k++) { sacc0 += ex2_approx(fmaf(bf16_lo(w[k]), c2a, nb)); sacc1 += ex2_approx(fmaf(bf16_hi(w[k]), c2a, nb)); }
-        }
+        for (int k = 0; k < 4; k++) { sacc0 += ex2_approx(fmaf(bf16_lo(w[k]), c2a, nb)); sacc1 += ex2_approx(fmaf(bf16_hi(w[k]), c2a, nb)); }
+      } else {                                                              // no mass wanted: the NaN check on its own
+        const __nv_bfloat162 a = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[0]), *reinterpret_cast<const __nv_bfloat162*>(&w[1]));
+        const __nv_bfloat162 b = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[2]), *reinterpret_cast<const __nv_bfloat162*>(&w[3]));
+        const __nv_bfloat162 ab = __hmax2_nan(a, b);
+        nan_seen |= ~__heq2_mask(ab, ab);                                   // a NaN anywhere in the chunk survives the maxima
       }
     }
     cp_async_wait<0>();
   }
   LM_TPHASE(9);
-  // block maximum of the running maxima
-  float M = m;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(kFull, M, o));
-  if (lane == 0) c.warp_f[warp] = M;
-  __syncthreads();
-  M = c.warp_f[0];
-  for (int w = 1; w < kTW; w++) M = fmaxf(M, c.warp_f[w]);
-  double zsum = (need_z && m > -INFINITY) ? static_cast<double>((sacc0 + sacc1) * ex2_approx((m - M) * c2a)) : 0.0;
-  const uint32_t n_hit = c.n_hit;
-  if (__syncthreads_or(nan_seen != 0u) || n_hit > 2048u) return false;      // rows with a NaN go to the exact path, which reports them
+  // a NaN or +inf logit (or a logit far above the sampled maximum) has made this thread's sum NaN or infinite: the exact path
+  // takes such rows and reports them
+  double zsum = 0.0;
+  if (need_z) {
+    const float sacc = sacc0 + sacc1;
+    if (!(sacc < INFINITY)) nan_seen = 1u;
+    zsum = static_cast<double>(sacc);
+  }
+  if (__syncthreads_or(nan_seen != 0u)) return false;                       // rows with a NaN go to the exact path, which reports them
+  const uint32_t n_hit = c.n_hit;                                           // (complete: every warp is past the pass)
+  if (n_hit > 2048u) return false;
 
   // ---- the noted chunks, expanded: their logits come back from L2; penalised positions are skipped (the hash set knows them)
   constexpr int kExpand = 1024 / kTB;                                       // chunk reloads in flight per thread
