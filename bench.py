@@ -49,9 +49,9 @@ def peaks():
 
 def ncu_traffic():
     """DRAM bytes per row of one sampling call (dram__bytes_read.sum + dram__bytes_write.sum, summed over the top-k kernel and
-    the histogram kernel, of one ncu capture of 888 of the workload's rows; traffic grows in proportion to the rows, so a
-    call's traffic is this times its rows). The capture is summarised in profiles/sample_kernels_888rows_ncu_full.md."""
-    return {"dram_bytes_per_row": (224220416 + 3980032 + 72878848 + 2363392) / 888}
+    the histogram kernel, of one ncu capture of the 4096-row workload itself; a call's traffic is this times its rows). The
+    capture is summarised in profiles/sample_kernels_4096rows_ncu_full.md."""
+    return {"dram_bytes_per_row": (1043868000 + 3853568 + 508108000 + 41251584) / 4096}
 
 
 class ClockSampler:
