@@ -7,7 +7,7 @@
 // the same histogram in device memory with 256 KB per row, kernels/common/sample.metal:34-162). Logits changed by
 // the penalties are arbitrary FP32 values: they leave the histogram and are kept aside as a short (index, value)
 // list that joins the walk at group level and exactly inside the one group where a threshold lands.
-// The draw then takes a second pass that finds the row in L2 (the next row is prefetched into L2 meanwhile).
+// The draw then takes a second look at the part of the row it needs, usually still in L2.
 //
 // Rows this kernel cannot take (a counter overflow: more than 65535 equal logits; more than kSideCap penalised
 // logits, or more than kSidePool of them in the 256 codes around a threshold; vocabularies that are not a multiple of 8 or exceed
@@ -399,21 +399,13 @@ __device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem&
   rv.dtype = LM_DTYPE_BF16; rv.vocab = V; rv.rho = P.rho; rv.pi = P.pi; rv.row = rowp; rv.aligned = true; rv.pen = nullptr;
   const int n_chunks = V / kChunk;
 
-  // the next row of this block (and its history): start pulling it into L2 now, a whole row ahead of its use, so that its
-  // pass runs against L2 latency instead of loaded-HBM latency
-  {
-    const char* np = reinterpret_cast<const char*>(P.logits) + static_cast<size_t>(next < 0 ? 0 : next) * static_cast<size_t>(P.row_stride) * 2;
-    if (next >= 0 && tid < 32 && (reinterpret_cast<uintptr_t>(np) & 15u) == 0) {
-      const uint32_t bytes = static_cast<uint32_t>(V) * 2u;
-      const uint32_t piece = ((bytes / 32u) + 15u) & ~15u;
-      const uint32_t off = piece * lane;
-      if (off < bytes) prefetch_l2(np + off, min(piece, bytes - off));
-    }
-    if (next >= 0 && tid == 32 % kBlock && pen_on) {
-      const char* hp = reinterpret_cast<const char*>(P.history + static_cast<int64_t>(next) * P.hist_stride);
-      const uint32_t hb = (static_cast<uint32_t>(P.hist_len) * 4u) & ~15u;
-      if ((reinterpret_cast<uintptr_t>(hp) & 15u) == 0 && hb) prefetch_l2(hp, hb);
-    }
+  // the history of this block's next row: start pulling it into L2 now. (Doing the same for the next row's logits was measured
+  // and dropped: the histogram pass is bound by its shared-memory atomics, not by load latency, and the prefetched rows push
+  // the current rows out of L2 before the draw looks at them again.)
+  if (next >= 0 && tid == 0 && pen_on) {
+    const char* hp = reinterpret_cast<const char*>(P.history + static_cast<int64_t>(next) * P.hist_stride);
+    const uint32_t hb = (static_cast<uint32_t>(P.hist_len) * 4u) & ~15u;
+    if ((reinterpret_cast<uintptr_t>(hp) & 15u) == 0 && hb) prefetch_l2(hp, hb);
   }
 
   // ---- the history's distinct ids as a bitmap and as a list -------------------------------------
