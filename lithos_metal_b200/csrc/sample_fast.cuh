@@ -662,6 +662,9 @@ __device__ void sample_row_fast(const SampleDev& P, int row, int next, FastSmem&
     if (!have_tau || tau_m > tau64) tau64 = tau_m;
     have_tau = true;
   }
+  // A +inf logit makes every mass NaN: the reference's top-p search then finds nothing and falls back to the largest value, and
+  // its min-p threshold is +inf itself (sampling_ref.py:33-37 with numpy's argmax of an all-false mask): only the +inf logits stay.
+  if (vmax == INFINITY && (has_p || has_m)) { tau64 = INFINITY; have_tau = true; }
   const float tau = have_tau ? __double2float_rn(tau64) : -INFINITY;
   LM_PHASE(6);
 

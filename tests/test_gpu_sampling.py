@@ -385,3 +385,42 @@ def test_sampling_call_in_a_cuda_graph(rows):
         graph.replay()
         torch.cuda.synchronize()
         assert torch.equal(out, eager)
+
+
+@pytest.mark.parametrize("draw", ["inverse_cdf", "gumbel"])
+def test_top_k_kernel_edge_rows(draw):
+    """Rows built to stress the one-pass top-k kernel at a vocabulary it accepts (32768): ties through the k-th rank, more
+    ties than it can hold, every logit equal, a -inf mask over most of the row, a +inf logit, a tiny temperature, one
+    repeated history id, penalised values crowding the top. Whatever kernel ends up finishing a row, tokens and thresholds
+    are the oracle's."""
+    V, rows = 32768, 12
+    rng = np.random.default_rng(123)
+    z = (rng.standard_normal((rows, V)) * 2).astype(np.float32)
+    z[0, 100:140] = 7.5                                                     # forty equal logits across the 20th rank
+    z[1, :3000] = 8.0                                                       # 3000 equal top logits: more than the kernel's candidate list
+    z[2, :] = 1.25                                                          # every logit equal
+    z[3, 5000:] = -np.inf                                                   # masked vocabulary
+    z[4, 77] = np.inf
+    z[6, 9] = 30.0                                                          # far above anything sampled for the cutoff
+    z[8, :64] = 6.0                                                         # the top of the row is all penalised (history below)
+    z[10] *= 0.01                                                           # tiny logits: few positive codes above the cutoff
+    codes = oracle.f32_to_bf16(z)
+    hist = rng.integers(0, V, (rows, 512)).astype(np.int32)
+    hist[7, :] = 31                                                         # one repeated id
+    hist[8, :64] = np.arange(64)
+    cfg = dict(logits=codes, temperature=np.float32([0.7, 1.0, 0.9, 1.1, 1.0, 0.02, 0.8, 1.0, 0.9, 1.3, 1.0, 0.6]),
+               top_k=np.int32([20, 1000, 5, 50, 20, 50, 20, 7, 50, 1024, 20, 1]), top_p=np.float32([0.9, 0.95, 0.5, 0.9, 0.9, 0.99, 0.8, 0.0, 0.97, 0.9, 0.9, 0.3]),
+               history=hist, uniforms=rng.random(rows).astype(np.float32))
+    x = bf16_tensor(codes)
+    knobs = {k: torch.from_numpy(cfg[k]).cuda() for k in ("temperature", "top_k", "top_p")}
+    for extra in (dict(), dict(min_p=0.01), dict(topp_in_topk=True)):
+        r = lm.sample(x, lm.SamplingParams(seed=9, draw=draw, repetition_penalty=1.3, presence_penalty=0.4, **knobs, **extra),
+                      history=torch.from_numpy(hist).cuda(), uniforms=torch.from_numpy(cfg["uniforms"]).cuda(), step=4, return_tau=True, return_status=True)
+        tok, tau, _ = oracle.sample_batch(codes, temperature=cfg["temperature"], top_k=cfg["top_k"], top_p=cfg["top_p"], history=hist,
+                                          repetition_penalty=1.3, presence_penalty=0.4, draw=draw, uniforms=cfg["uniforms"], seed=9, step=4, n_threads=8, **extra)
+        status = r.status.cpu().numpy()
+        keep = np.arange(rows) != 4                                         # the +inf row: weights are NaN by definition, only the threshold is compared
+        np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
+        got = r.tokens.cpu().numpy()
+        assert np.all((got == tok)[keep] | ((status & 4) != 0)[keep]), (extra, got, tok, status)
+        assert np.count_nonzero(status & 64) >= 5                           # the ordinary rows did go through the top-k kernel
