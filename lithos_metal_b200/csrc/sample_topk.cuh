@@ -26,7 +26,7 @@ constexpr int kTopkBins = 512;             // BF16 codes above the cutoff that t
 constexpr int kTopkMaxK = 1024;            // largest top_k this kernel takes
 constexpr int kTopkHist = 2048;            // longest history it takes
 constexpr int kTopkMaxVocab = 1 << 18;
-constexpr int kMaxProbes = 24;             // probes of the cutoff search per row (2 for the bracket + 15 for a full bisection)
+constexpr int kMaxProbes = 30;             // counters of the cutoff search per row: three per round, one round for the bracket + eight for the whole code range
 constexpr int kBinSortMax = 256;           // a code bin with more candidates than this must already be in order (all equal)
 constexpr int kSampleChunks = 1024 / kTB;   // chunks per thread in the cutoff sample: 1024 chunks = 8192 logits
 constexpr int kTopkMinVocab = 32768;
@@ -251,19 +251,26 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
     const uint32_t want = max(8u, static_cast<uint32_t>((static_cast<long long>(n_target) * kSampleChunks * kTB * kChunk + V - 1) / V));
     const int cls = min(31 - __clz(want), 7);
     int probe = 0;
-    auto count_ge = [&](uint32_t code) -> uint32_t {                        // sampled logits at or above `code`; every thread calls
-      const uint32_t m2 = code | (code << 16);
-      const __nv_bfloat162 t2 = *reinterpret_cast<const __nv_bfloat162*>(&m2);
-      uint32_t cnt = 0;
+    // sampled logits at or above each of three codes, with one barrier; every thread calls
+    auto count3 = [&](uint32_t a, uint32_t b, uint32_t d, uint32_t out[3]) {
+      const uint32_t codes[3] = {a, b, d};
+      uint32_t cnt[3] = {0u, 0u, 0u};
 #pragma unroll
-      for (int j = 0; j < kSampleChunks; j++) {
-        cnt += __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].x), t2)) + __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].y), t2)) +
-               __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].z), t2)) + __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].w), t2));
+      for (int t = 0; t < 3; t++) {
+        const uint32_t m2 = codes[t] | (codes[t] << 16);
+        const __nv_bfloat162 t2 = *reinterpret_cast<const __nv_bfloat162*>(&m2);
+#pragma unroll
+        for (int j = 0; j < kSampleChunks; j++) {
+          cnt[t] += __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].x), t2)) + __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].y), t2)) +
+                    __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].z), t2)) + __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].w), t2));
+        }
+        cnt[t] = __reduce_add_sync(kFull, cnt[t] >> 4);                     // 16 mask bits per logit
+        if (lane == 0 && cnt[t]) atomicAdd(&c.probe_cnt[probe + t], cnt[t]);
       }
-      cnt = __reduce_add_sync(kFull, cnt >> 4);                             // 16 mask bits per logit
-      if (lane == 0 && cnt) atomicAdd(&c.probe_cnt[probe], cnt);
       __syncthreads();
-      return c.probe_cnt[probe++];
+#pragma unroll
+      for (int t = 0; t < 3; t++) out[t] = c.probe_cnt[probe + t];
+      probe += 3;
     };
     // the largest sampled logit: the reference point of the FP32 softmass (any value near the row maximum will do); it
     // travels with the first probe's barrier
@@ -280,17 +287,24 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
     }
     uint32_t lo = 0x0000u, hi = 0x7F7Fu;                                    // invariant: count(sample >= lo) >= want, or lo is still 0 (handed back below)
     const uint32_t prev = c.prev_cut[cls];
-    if (prev >= 0x0080u) {
-      const uint32_t blo = max(prev, 0x0090u) - 16u, bhi = min(prev + 15u, 0x7F7Fu);
-      const uint32_t ca = count_ge(blo), cb = bhi < 0x7F7Fu ? count_ge(bhi + 1u) : 0u;
-      if (ca < want) hi = blo - 1u;
-      else if (cb >= want) lo = bhi + 1u;
-      else { lo = blo; hi = bhi; }
+    uint32_t n3[3];
+    if (prev >= 0x0080u) {                                                  // both ends of the bracket and its middle in one round
+      const uint32_t blo = max(prev, 0x0090u) - 16u, bhi = min(prev + 15u, 0x7F7Eu), mid = (blo + bhi + 1u) >> 1;
+      count3(blo, mid, bhi + 1u, n3);
+      if (n3[0] < want) hi = blo - 1u;
+      else if (n3[2] >= want) lo = bhi + 1u;
+      else if (n3[1] >= want) { lo = mid; hi = bhi; }
+      else { lo = blo; hi = mid - 1u; }
     }
     LM_TSUB(2);
-    while (lo < hi && probe < kMaxProbes) {
-      const uint32_t mid = (lo + hi + 1u) >> 1;
-      if (count_ge(mid) >= want) lo = mid; else hi = mid - 1u;
+    while (lo < hi && probe + 3 <= kMaxProbes) {                            // three cuts per round: the range shrinks fourfold
+      const uint32_t span = hi - lo;
+      const uint32_t q1 = lo + (span + 3u) / 4u, q2 = lo + (2u * span + 3u) / 4u, q3 = lo + (3u * span + 3u) / 4u;   // lo < q1 <= q2 <= q3 <= hi
+      count3(q1, q2, q3, n3);
+      if (n3[2] >= want) lo = q3;
+      else if (n3[1] >= want) { lo = q2; hi = q3 - 1u; }
+      else if (n3[0] >= want) { lo = q1; hi = q2 - 1u; }
+      else hi = q1 - 1u;
     }
     LM_TSUB(3);
     cut_code = lo;
