@@ -166,6 +166,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=TOTAL_ROWS, help="total rows over all ranks (default: the workload's 4096)")
     ap.add_argument("--skip-extras", action="store_true", help="skip the e2e, CPU-baseline, small-batch and verify legs")
+    ap.add_argument("--verify-only", action="store_true", help="run only the DSpark verify / draft legs (plain launches first, then the timed graphs)")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -183,6 +184,10 @@ def main() -> None:
         raise SystemExit("bench.py needs a CUDA device: the sampler has no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    if args.verify_only:
+        if rank == 0:
+            print(json.dumps({"verify": bench_verify(torch, lm, dev)}))
+        return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     total_rows = args.rows
