@@ -54,6 +54,15 @@ def ncu_traffic():
     return {"dram_bytes_per_row": (1043868000 + 3853568 + 508108000 + 41251584) / 4096}
 
 
+def launches_per_call(lm, rows: int) -> int:
+    """Kernels one lm_sample call launches on this workload (per rank): top-k kernel, histogram kernel, generic kernel; with at
+    most 16 rows per SM the two sampler kernels run side by side and a row-listing kernel plus a second (usually empty) launch
+    of the histogram kernel join them (the rule is lm_sample's, lithos_metal_b200/csrc/lithos_b200.cu)."""
+    from lithos_metal_b200 import _lib
+    sms = _lib.lib().lm_device_sm_count()
+    return 3 if rows > 16 * max(sms, 1) else 5
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown," \
@@ -247,9 +256,10 @@ def main() -> None:
            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                         "frac_of_nominal_8TBs": achieved / 8000.0, "algorithmic_bytes_per_row": ROW_BYTES,
                         "traffic": (traffic["dram_bytes_per_row"] * rows if traffic else None)},
-           "gpu_launches": 3 * args.steps, "clocks": clocks.summary()}
+           "gpu_launches": launches_per_call(lm, rows) * args.steps, "clocks": clocks.summary()}
     out["roofline"]["launch"] = ("one sampling call = sample_topk_kernel (rows with a top_k) + sample_fast_kernel (the other rows) + "
-                                 "sample_generic_kernel (rows handed on: none here); duration = CUDA events around the call")
+                                 "sample_generic_kernel (rows handed on: none here)" + (" + the row-listing kernel and a second sample_fast_kernel launch "
+                                 "(side-by-side order below 16 rows per SM)" if launches_per_call(lm, rows) == 5 else "") + "; duration = CUDA events around the call")
 
     if not args.skip_extras:
         # ---- e2e: host (pinned) inputs -> public API -> tokens on the host, copies inside the timed region
