@@ -16,6 +16,10 @@
  *   lmo_verify_stochastic kernels/common/sample.metal:273-347 (p/q accept, first reject, residual draw) -- the
  *                         reference has no CPU code and no exact-output test for this part: PARITY UNPINNED; this
  *                         restatement is the frozen definition.
+ *   lmo_draft_q           kernels/common/sample.metal:212-269 (the drafter's draw on noise stream 2000 + k; the token is
+ *                         pinned by sampling_ref.sample with t = 2000 + k; lse to 2e-6; q from the integer mass: unpinned)
+ *   lmo_confidence        kernels/common/spec_ops.metal:85-106 (confidence head; pinned to the reference test's expected
+ *                         values, tests/kernels/test_draft_ops.py:228-263, within its own bar of 2e-3)
  * What has no counterpart in the reference (PARITY UNPINNED; this file is the frozen definition):
  *   lmo_apply_penalties   repetition / presence penalties over the distinct ids of a token history
  *   lmo_spec_exp2, lmo_weight_q40, lmo_sample_invcdf   inverse-CDF draw from a caller-supplied uniform, defined
