@@ -133,6 +133,24 @@ __device__ __forceinline__ uint64_t weight_q40(float z, float vmax, float c) {
   const float x = __fmul_rn(__fsub_rn(z, vmax), c);
   return __float2ull_rz(__fmul_rn(spec_exp2(x), 1099511627776.0f));
 }
+// Two weights at once on the packed binary32 instructions of sm_100 (fma.rn.f32x2 and friends): element for element the
+// operations of weight_q40, so the same bits. (z - vmax is formed as z + (-vmax); the two exact power-of-two scalings, by 2^n
+// and by 2^40, are one multiplication by 2^(n + 40).)
+__device__ __forceinline__ void weight_q40_x2(float z0, float z1, float vmax, float c, uint64_t& w0, uint64_t& w1) {
+  const float2 x = __fmul2_rn(__fadd2_rn(make_float2(z0, z1), make_float2(-vmax, -vmax)), make_float2(c, c));
+  const float x0 = fminf(x.x, 0.0f), x1 = fminf(x.y, 0.0f);
+  const float n0 = rintf(x0), n1 = rintf(x1);
+  const float2 f = __fadd2_rn(make_float2(x0, x1), make_float2(-n0, -n1));
+  float2 p = make_float2(0x1.5bba20p-10f, 0x1.5bba20p-10f);
+  p = __ffma2_rn(p, f, make_float2(0x1.3cea88p-7f, 0x1.3cea88p-7f));
+  p = __ffma2_rn(p, f, make_float2(0x1.c6b752p-5f, 0x1.c6b752p-5f));
+  p = __ffma2_rn(p, f, make_float2(0x1.ebf9bcp-3f, 0x1.ebf9bcp-3f));
+  p = __ffma2_rn(p, f, make_float2(0x1.62e42ap-1f, 0x1.62e42ap-1f));
+  p = __ffma2_rn(p, f, make_float2(1.0f, 1.0f));
+  const float2 r = __fmul2_rn(p, make_float2(__int_as_float((static_cast<int>(n0) + 167) << 23), __int_as_float((static_cast<int>(n1) + 167) << 23)));
+  w0 = (x.x > -100.0f) ? __float2ull_rz(r.x) : 0ull;                        // also NaN: weight 0
+  w1 = (x.y > -100.0f) ? __float2ull_rz(r.y) : 0ull;
+}
 // floor(floor(u * 2^24) * total / 2^24), u clamped to [0, 1 - 2^-24]
 __device__ __forceinline__ uint64_t cdf_target(float u, uint64_t total) {
   long long u24 = (u > 0.0f) ? __float2ll_rz(__fmul_rn(u, 16777216.0f)) : 0ll;

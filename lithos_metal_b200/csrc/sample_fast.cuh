@@ -332,7 +332,12 @@ __device__ int draw_inverse_cdf_bidir(const RowView& rv, FastSmem& s, const Side
       uint64_t w = 0ull;
       if (mask) {
 #pragma unroll
-        for (int e = 0; e < kChunk; e++) if ((mask >> e) & 1u) w += weight_q40(z[e], vmax, c2);
+        for (int e = 0; e < kChunk; e += 2) if ((mask >> e) & 3u) {             // two logits per packed evaluation
+          uint64_t wa, wb;
+          weight_q40_x2(z[e], z[e + 1], vmax, c2, wa, wb);
+          w += ((mask >> e) & 1u) ? wa : 0ull;
+          w += ((mask >> e) & 2u) ? wb : 0ull;
+        }
       }
       if (__any_sync(kFull, w != 0ull)) w = warp_sum_u64(w);
       if (lane == 0) sweep_part[it * 32 + warp] = w;

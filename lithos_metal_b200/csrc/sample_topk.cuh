@@ -318,7 +318,7 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   // ---- the one pass: note the chunks that hold a logit >= cutoff; FP32 softmass relative to the sampled maximum ----------
   const float M = need_z ? fkey_inv(c.ref_key) : 0.0f;
   const float nb = -M * c2a;
-  float sacc0 = 0.0f, sacc1 = 0.0f;
+  float2 sacc = make_float2(0.0f, 0.0f);
   uint32_t nan_seen = 0u;
   {
     const uint32_t cut2 = cut_code | (cut_code << 16);
@@ -353,7 +353,10 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
       }
       if (need_z) {                                                         // (the padding is -inf: weight 0; a NaN or +inf logit poisons the sum)
 #pragma unroll
-        for (int k = 0; k < 4; k++) { sacc0 += ex2_approx(fmaf(bf16_lo(w[k]), c2a, nb)); sacc1 += ex2_approx(fmaf(bf16_hi(w[k]), c2a, nb)); }
+        for (int k = 0; k < 4; k++) {                                         // two logits per packed multiply-add and per packed add
+          const float2 x = __ffma2_rn(make_float2(bf16_lo(w[k]), bf16_hi(w[k])), make_float2(c2a, c2a), make_float2(nb, nb));
+          sacc = __fadd2_rn(sacc, make_float2(ex2_approx(x.x), ex2_approx(x.y)));
+        }
       } else {                                                              // no mass wanted: the NaN check on its own
         const __nv_bfloat162 a = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[0]), *reinterpret_cast<const __nv_bfloat162*>(&w[1]));
         const __nv_bfloat162 b = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w[2]), *reinterpret_cast<const __nv_bfloat162*>(&w[3]));
@@ -368,9 +371,9 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   // takes such rows and reports them
   double zsum = 0.0;
   if (need_z) {
-    const float sacc = sacc0 + sacc1;
-    if (!(sacc < INFINITY)) nan_seen = 1u;
-    zsum = static_cast<double>(sacc);
+    const float total = sacc.x + sacc.y;
+    if (!(total < INFINITY)) nan_seen = 1u;
+    zsum = static_cast<double>(total);
   }
   if (__syncthreads_or(nan_seen != 0u)) return false;                       // rows with a NaN go to the exact path, which reports them
   const uint32_t n_hit = c.n_hit;                                           // (complete: every warp is past the pass)
