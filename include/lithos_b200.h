@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define LM_ABI_VERSION 2
+#define LM_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define LM_API __attribute__((visibility("default")))
@@ -118,6 +118,12 @@ typedef struct lm_sample_args {
   void* workspace;             /* lm_workspace_bytes(rows, vocab) bytes, 256-byte aligned, zero-filled once */
   size_t workspace_bytes;
   void* stream;                /* cudaStream_t */
+  /* GPU-resident control (optional): a StepState buffer of layout (t_max, gamma_max). When given, the kernels read on the
+   * device what the reference's kernels read there (kernels/common/sample.metal:172-181, argmax.metal:44-46): the noise seed
+   * (rng_hi:rng_lo) and step replace `seed` / `step`, only the first t_this_step rows are sampled (the others are left
+   * untouched), and nothing is written once the state is done. A captured CUDA graph then draws fresh noise on every replay. */
+  const void* step_state;
+  int32_t t_max, gamma_max;
 } lm_sample_args;
 
 LM_API int lm_sample(const lm_sample_args* args);
@@ -170,13 +176,15 @@ LM_API int lm_argmax_static(const void* logits, int32_t dtype, int64_t rows, int
  *               (n_draft if none); final = inverse-CDF draw with u_final over max(p - q, 0) of row `accept`
  *               (over p itself on the bonus row, or when the residual is empty).
  * Outputs: out_accept[0] = accept length; out_final[0] = final token; out_tokens (optional, [n_draft + 1]) =
- * drafts[0..accept) followed by the final token, -1 beyond.
+ * drafts[0..accept) followed by the final token, -1 beyond. A launch whose internal waits ran out (see wait_limit) reports -1
+ * in all three and leaves its workspace clean for the next call.
  *
  * commit (optional): the fields lm_accept_scan takes (step_state, t_max, gamma_max, ring, ring_cap, eos, eos_list, n_eos, log,
  * log_cap, ctx_cap, lm; `tokens` and `stream` are ignored). The thread that writes out_tokens then runs the accept scan on them
  * (kernels/common/spec_ops.metal:148-195): commit to the token ring, advance the StepState; one launch closes the round. The
- * state must describe this round (verify_len == n_draft, t_this_step == n_draft + 1; a prefill chunk takes the scan's prefill
- * branch); otherwise the state gets error 4 and done = 1. A grid-barrier timeout of the launch gives error 3 and done = 1.
+ * state must describe this round (verify_len == n_draft, t_this_step == n_draft + 1, unless step_state hands the round to the
+ * kernel; a prefill chunk takes the scan's prefill branch); otherwise the state gets error 4 and done = 1. A launch whose
+ * internal waits ran out gives error 3 and done = 1.
  */
 #define LM_VERIFY_GREEDY 0
 #define LM_VERIFY_STOCHASTIC 1
@@ -210,7 +218,28 @@ typedef struct lm_verify_args {
   const float* draft_vmax;     /* [n_draft] row maxima from lm_draft_q */
   const uint64_t* draft_mass;  /* [n_draft] fixed-point row masses from lm_draft_q */
   const struct lm_step_args* commit;  /* NULL, or: close the round in the same launch (see below); needs out_tokens */
+  /* randomness on the device: u_accept == NULL takes uniform01(seed, step, 3000 + r, 0) for draft r, the reference's accept
+   * stream (kernels/common/sample.metal:291-296); u_final == NULL takes uniform01(seed, step, 4000, 0) */
+  uint64_t seed;
+  uint32_t step;
+  int32_t residual_draw;       /* LM_RESIDUAL_* (stochastic) */
+  /* GPU-resident control (optional): a StepState buffer of layout (t_max, gamma_max). When given, the round is read from it on
+   * the device (kernels/common/sample.metal:283-296): L = verify_len <= n_draft drafts = pending_tokens[base + 1 ..], rows
+   * base .. base + L of target_logits with base = t_this_step - 1 - L, seed = rng_hi:rng_lo, step; out_tokens is indexed by step
+   * row; nothing is verified or written when the state is done or the step is a prefill chunk (a commit still runs the scan's
+   * prefill branch). A state whose rows do not fit (verify_len > n_draft, t_this_step > n_draft + 1) gets error 4 and done = 1. */
+  const void* step_state;
+  int32_t t_max, gamma_max;
+  uint32_t wait_limit;         /* polls before a wait between thread blocks gives up; 0 = the default (about 0.1 s) */
+  uint32_t selftest;           /* LM_VERIFY_SELFTEST_WITHHOLD: block 0 withholds its row maxima, so every wait of the launch runs
+                                  out and the error path can be exercised (with a small wait_limit) without hanging anything */
 } lm_verify_args;
+
+#define LM_RESIDUAL_INVERSE_CDF 0 /* final token by inverse CDF over max(p - q, 0) (over p on the bonus row) from u_final */
+#define LM_RESIDUAL_GUMBEL 1      /* the reference's form (kernels/common/sample.metal:322-346): argmax of ln(p - q) + gumbel(seed, step,
+                                     4000, i) over the positive residual; with every draft accepted or an empty residual, the row's own
+                                     Gumbel-max draw argmax(z/T + gumbel(seed, step, row, i)) over its kept set */
+#define LM_VERIFY_SELFTEST_WITHHOLD 1u
 
 #define LM_MAX_DRAFT 15
 
@@ -254,6 +283,9 @@ typedef struct lm_draft_q_args {
   void* workspace;
   size_t workspace_bytes;
   void* stream;
+  const void* step_state;      /* optional StepState of layout (t_max, gamma_max): seed = rng_hi:rng_lo and step are read from it on the
+                                  device (kernels/common/sample.metal:236-239); nothing is written once the state is done */
+  int32_t t_max, gamma_max;
 } lm_draft_q_args;
 
 LM_API int lm_draft_q(const lm_draft_q_args* args);

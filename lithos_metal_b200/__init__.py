@@ -7,7 +7,9 @@ from .sampler import (GreedySampler, SampleOutput, SamplingParams, StochasticSam
                       warped_probabilities)
 from .verify import DraftQ, draft_q, verify
 from .step_state import StepStateLayout, accept_scan, advance, confidence, verify_select
+from .records import accept_args_from_record, sample_args_from_record, select_args_from_record
 from . import parallel
 
 __all__ = ["GreedySampler", "StochasticSampler", "SamplingParams", "SampleOutput", "sample", "argmax", "sample_row", "thresholds",
-           "warped_probabilities", "verify", "draft_q", "DraftQ", "StepStateLayout", "accept_scan", "verify_select", "advance", "confidence", "parallel"]
+           "warped_probabilities", "verify", "draft_q", "DraftQ", "StepStateLayout", "accept_scan", "verify_select", "advance", "confidence", "parallel",
+           "sample_args_from_record", "select_args_from_record", "accept_args_from_record"]

@@ -10,10 +10,12 @@ from . import build as _build
 LM_OK = 0
 DTYPE_BF16, DTYPE_F32 = 0, 1
 DRAW_GUMBEL, DRAW_INVERSE_CDF = 0, 1
-ABI_VERSION = 2                      # LM_ABI_VERSION of include/lithos_b200.h this binding was written against
+ABI_VERSION = 3                      # LM_ABI_VERSION of include/lithos_b200.h this binding was written against
 FLAG_TOPP_IN_TOPK = 1
 FLAG_EXACT_ONLY = 2
 VERIFY_GREEDY, VERIFY_STOCHASTIC = 0, 1
+RESIDUAL_INVERSE_CDF, RESIDUAL_GUMBEL = 0, 1
+VERIFY_SELFTEST_WITHHOLD = 1
 STATUS_GENERIC_PATH, STATUS_NAN, STATUS_NEAR_TIE, STATUS_TOPP_EDGE, STATUS_OVERFLOW = 1, 2, 4, 8, 32
 STATUS_CANDIDATE_PATH = 64
 VOCAB_MAX_CANDIDATES = 1024
@@ -35,6 +37,7 @@ class SampleArgs(C.Structure):
         ("out_tokens", C.c_void_p), ("out_tau", C.c_void_p), ("out_stats", C.c_void_p), ("out_probs", C.c_void_p), ("probs_stride", C.c_int64),
         ("out_status", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+        ("step_state", C.c_void_p), ("t_max", C.c_int32), ("gamma_max", C.c_int32),
     ]
 
 
@@ -47,6 +50,8 @@ class VerifyArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
         ("draft_logits", C.c_void_p), ("draft_logits_stride", C.c_int64), ("draft_vmax", C.c_void_p), ("draft_mass", C.c_void_p),
         ("commit", C.c_void_p),
+        ("seed", C.c_uint64), ("step", C.c_uint32), ("residual_draw", C.c_int32),
+        ("step_state", C.c_void_p), ("t_max", C.c_int32), ("gamma_max", C.c_int32), ("wait_limit", C.c_uint32), ("selftest", C.c_uint32),
     ]
 
 
@@ -56,6 +61,7 @@ class DraftQArgs(C.Structure):
         ("vocab", C.c_int64), ("row_stride", C.c_int64), ("temperature", C.c_float), ("seed", C.c_uint64), ("step", C.c_uint32),
         ("out_tokens", C.c_void_p), ("out_lse", C.c_void_p), ("out_vmax", C.c_void_p), ("out_mass", C.c_void_p), ("out_status", C.c_void_p),
         ("out_q_logits", C.c_void_p), ("q_logits_stride", C.c_int64), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+        ("step_state", C.c_void_p), ("t_max", C.c_int32), ("gamma_max", C.c_int32),
     ]
 
 

@@ -9,24 +9,63 @@
 // grid barrier (the weights need the row maximum), and the last block to leave writes the outputs and cleans the workspace.
 #pragma once
 #include "common.cuh"
-#include "verify.cuh"
+#include "spec_ops.cuh"
 
 namespace lm {
+
+constexpr int kDraftQBlock = 1024;
+constexpr int kDraftQMaxRows = LM_MAX_DRAFT + 1;
+constexpr unsigned kBarrierSpinLimit = 1u << 17;       // polls of the counter (about a microsecond each) before the wait gives up
+
+struct DraftQWs {                                       // lives in the caller's workspace, zero-filled once, left all zero by every launch
+  unsigned barrier;                                     // arrivals; returns to 0 when the launch ends
+  unsigned exits;
+  unsigned error;                                       // 1 = the barrier wait of this launch ran out
+  unsigned nan_rows;                                    // bit r: row r holds a NaN
+  unsigned long long row_best[kDraftQMaxRows];          // packed (max logit, lowest index) per row
+  unsigned long long row_mass[kDraftQMaxRows];          // fixed-point mass per row
+  unsigned long long key_best[kDraftQMaxRows];          // packed best Gumbel key per row
+  unsigned long long rival[kDraftQMaxRows];             // the best Gumbel key that lost (monotone code)
+};
+
+// Every block arrives, then waits until `target` arrivals are visible. Bounded: on time-out the error word is set and
+// the block carries on (its results are then meaningless; the outputs report the error).
+__device__ __forceinline__ void grid_barrier(DraftQWs* ws, unsigned target) {
+  __syncthreads();                                                        // the block's writes happen-before thread 0's release below
+  if (threadIdx.x == 0) {
+    unsigned seen = 0, spins = 0;
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&ws->barrier) : "memory");
+    do {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(&ws->barrier) : "memory");
+      if (seen >= target) break;
+      if (++spins > kBarrierSpinLimit) { atomicExch(&ws->error, 1u); break; }
+    } while (true);
+  }
+  __syncthreads();
+}
+__device__ __forceinline__ uint64_t ws_load(const unsigned long long* p) { return __ldcg(p); }
 
 struct DraftQDev {
   int dtype; int rows; int first_position; int vocab; int64_t row_stride;
   const void* logits; float temperature; uint64_t seed; uint32_t step;
   int32_t* out_tokens; float* out_lse; float* out_vmax; unsigned long long* out_mass; uint32_t* out_status;
   void* out_q_logits; int64_t q_logits_stride;
-  VerifyWs* ws;                                          // row_best: packed row maximum; draft_w: packed best Gumbel key; row_mass: the mass
+  DraftQWs* ws;
+  const uint32_t* state; int t_max, g;                   // optional StepState: seed and step come from it; a done state ends the launch
 };
 
-__global__ void __launch_bounds__(kVerifyBlock, 1) draft_q_kernel(DraftQDev P) {
+__global__ void __launch_bounds__(kDraftQBlock, 1) draft_q_kernel(DraftQDev P) {
   extern __shared__ __align__(16) float dq_smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, G = gridDim.x, b = blockIdx.x;
-  constexpr int kWarps = kVerifyBlock / 32;
+  constexpr int kWarps = kDraftQBlock / 32;
   const int R = P.rows, V = P.vocab;
-  VerifyWs* ws = P.ws;
+  DraftQWs* ws = P.ws;
+  uint64_t seed = P.seed; uint32_t step = P.step;
+  if (P.state) {
+    StepStateView st{const_cast<uint32_t*>(P.state), P.t_max, P.g};
+    if (st.done()) return;                                                // every block sees the same state: none touches the workspace
+    seed = st.seed(); step = st.step();
+  }
   unsigned long long* second = ws->rival;                                 // per row: the best key that is not the winner's
   const int per = ((V + G - 1) / G + 7) & ~7;
   const int lo = min(V, b * per), hi = min(V, lo + per);
@@ -34,7 +73,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) draft_q_kernel(DraftQDev P) {
   float* zs = dq_smem;                                                    // [R][per] widened logits of this block's slice
 
   // ---- phase 0: the slice of every row into shared memory (and into the copy, if one is wanted) ------------------------
-  for (int i = tid; i < R * len; i += kVerifyBlock) {
+  for (int i = tid; i < R * len; i += kDraftQBlock) {
     const int r = i / len, e = i - r * len;
     float z;
     if (P.dtype == LM_DTYPE_BF16) {
@@ -62,14 +101,14 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) draft_q_kernel(DraftQDev P) {
       nan = nan || (z != z);
       const uint64_t pv = pack_best(z, idx);
       vbest = pv > vbest ? pv : vbest;
-      const float key = __fadd_rn(__fmul_rn(z, inv_t32), gumbel(P.seed, P.step, t_id, idx));
+      const float key = __fadd_rn(__fmul_rn(z, inv_t32), gumbel(seed, step, t_id, idx));
       const uint64_t pk = pack_best(key, idx);
       if (pk > kbest) { if (kbest) ksecond = fmaxf(ksecond, best_value(kbest)); kbest = pk; } else ksecond = fmaxf(ksecond, key);
     }
     const uint64_t wv = warp_max_u64(vbest), wk = warp_max_u64(kbest);
     if (lane == 0 && wv) atomicMax(&ws->row_best[r], static_cast<unsigned long long>(wv));
-    if (lane == 0 && wk) atomicMax(&ws->draft_w[r], static_cast<unsigned long long>(wk));
-    if (__any_sync(kFull, nan) && lane == 0) atomicOr(&ws->pad, 1u << r);
+    if (lane == 0 && wk) atomicMax(&ws->key_best[r], static_cast<unsigned long long>(wk));
+    if (__any_sync(kFull, nan) && lane == 0) atomicOr(&ws->nan_rows, 1u << r);
     if (item < kWarps) { my_best = kbest; my_second = ksecond; }            // R * split <= kWarps: one item per warp
   }
   grid_barrier(ws, 1u * G);
@@ -79,7 +118,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) draft_q_kernel(DraftQDev P) {
   for (int item = warp; item < R * split; item += kWarps) {
     const int r = item / split, part = item - r * split;
     const float vmax = best_value(ws_load(&ws->row_best[r]));
-    const uint64_t winner = ws_load(&ws->draft_w[r]);
+    const uint64_t winner = ws_load(&ws->key_best[r]);
     uint64_t w = 0ull;
     for (int i = part * 32 + lane; i < len; i += 32 * split) w += weight_q40(zs[r * per + i], vmax, c2);
     w = warp_sum_u64(w);
@@ -102,7 +141,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) draft_q_kernel(DraftQDev P) {
   __threadfence();
   if (tid < R) {
     const int r = tid;
-    const uint64_t vb = ws_load(&ws->row_best[r]), kb = ws_load(&ws->draft_w[r]), mass = ws_load(&ws->row_mass[r]);
+    const uint64_t vb = ws_load(&ws->row_best[r]), kb = ws_load(&ws->key_best[r]), mass = ws_load(&ws->row_mass[r]);
     const uint64_t sec = ws_load(&second[r]);
     const bool bad = ws->error != 0;
     const float vmax = best_value(vb);
@@ -113,13 +152,13 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) draft_q_kernel(DraftQDev P) {
     if (P.out_status) {
       uint32_t st = 0u;
       if (kb && sec && fkey_inv(static_cast<uint32_t>(sec)) >= best_value(kb) - 4e-6f) st |= LM_STATUS_NEAR_TIE;
-      if ((__ldcg(&ws->pad) >> r) & 1u) st |= LM_STATUS_NAN;
+      if ((__ldcg(&ws->nan_rows) >> r) & 1u) st |= LM_STATUS_NAN;
       P.out_status[r] = st;
     }
-    ws->row_best[r] = 0ull; ws->draft_w[r] = 0ull; ws->row_mass[r] = 0ull; second[r] = 0ull;
+    ws->row_best[r] = 0ull; ws->key_best[r] = 0ull; ws->row_mass[r] = 0ull; second[r] = 0ull;
   }
   __syncthreads();
-  if (tid == 0) { ws->pad = 0u; ws->exits = 0u; __threadfence(); ws->barrier = 0u; }
+  if (tid == 0) { ws->nan_rows = 0u; ws->error = 0u; ws->exits = 0u; __threadfence(); ws->barrier = 0u; }
 }
 
 }  // namespace lm

@@ -9,7 +9,7 @@
 
 #include "common.cuh"
 #include "sample_generic.cuh"
-#include "sample_fast.cuh"
+#include "sample_hist.cuh"
 #include "sample_topk.cuh"
 #include "verify.cuh"
 #include "draft_q.cuh"
@@ -62,37 +62,11 @@ __global__ void __launch_bounds__(kBlock, 1) sample_generic_kernel(SampleDev P, 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   GenericSmem& s = *reinterpret_cast<GenericSmem*>(smem_raw);
   uint32_t* pen_bits = reinterpret_cast<uint32_t*>(smem_raw + sizeof(GenericSmem));
+  apply_step_state(P);
   const int n = list ? min(*n_list, P.rows) : P.rows;
   for (int i = blockIdx.x; i < n; i += gridDim.x) {
     const int row = list ? list[i] : i;
     if (row >= 0 && row < P.rows) sample_row_generic(P, row, s, pen_bits);
-    __syncthreads();
-  }
-}
-
-// ---- the streaming BF16 sampler: one block per SM. Rows cost very different amounts (the draw scales with the kept set), so
-// blocks take them from a counter (`next_item`, zeroed by the host) instead of a fixed stride; a block always holds the item
-// after its current one too, so that it can pull that row into L2 while it works. With a row list (written by the
-// top-k kernel: the rows it left) the items are entries of the list, without one they are the rows themselves.
-__global__ void __launch_bounds__(kBlock, 1) sample_fast_kernel(SampleDev P, const int* list, const int* n_list, int* next_item, int* redo, int* n_redo) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  FastSmem& s = *reinterpret_cast<FastSmem*>(smem_raw);
-  __shared__ int item[2];
-  // A kernel launched behind this one with programmatic stream serialization (the top-k kernel, which works on other rows and
-  // reads nothing this kernel writes) may take every SM a block of this grid has left, instead of waiting for the whole grid.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int n = list ? min(*n_list, P.rows) : P.rows;
-  if (threadIdx.x == 0) { item[0] = atomicAdd(next_item, 1); item[1] = item[0] < n ? atomicAdd(next_item, 1) : n; }
-  __syncthreads();
-  for (;;) {
-    const int i = item[0], in = item[1];
-    if (i >= n) break;
-    __syncthreads();
-    if (threadIdx.x == 0) { item[0] = in; item[1] = in < n ? atomicAdd(next_item, 1) : n; }
-    const int row = list ? list[i] : i;
-    int next = in < n ? (list ? list[in] : in) : -1;
-    if (next >= P.rows) next = -1;
-    if (row >= 0 && row < P.rows) sample_row_fast(P, row, next, s, redo, n_redo);   // (a list entry is a row index by construction)
     __syncthreads();
   }
 }
@@ -108,10 +82,7 @@ static int cuda_fail(cudaError_t e) {
   return LM_E_CUDA;
 }
 
-#ifndef LM_OVERLAP_ROWS_PER_SM
-#define LM_OVERLAP_ROWS_PER_SM 16
-#endif
-constexpr int kOverlapRowsPerSM = LM_OVERLAP_ROWS_PER_SM;   // up to this many rows per SM the two sampler kernels run side by side (lm_sample)
+constexpr int kOverlapRowsPerSM = 16;   // up to this many rows per SM the two sampler kernels run side by side (lm_sample)
 
 static int sm_count(int* out) {
   int dev = 0;
@@ -156,16 +127,6 @@ using namespace lm;
 
 extern "C" {
 
-#ifdef LM_PROFILE_PHASES
-__attribute__((visibility("default"))) int lm_debug_verify_times(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_verify_times, sizeof(unsigned long long) * 8) == cudaSuccess ? 0 : -3;
-}
-__attribute__((visibility("default"))) int lm_debug_phases(unsigned long long* out, int reset) {
-  if (cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 16) != cudaSuccess) return -3;
-  if (reset) { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z)); }
-  return 0;
-}
-#endif
 
 int lm_abi_version(void) { return LM_ABI_VERSION; }
 
@@ -199,8 +160,8 @@ size_t lm_workspace_bytes(int64_t rows, int64_t vocab) {
 
 size_t lm_verify_workspace_bytes(int32_t n_draft, int64_t vocab) {
   (void)n_draft; (void)vocab;
-  const size_t max_grid = 1024;                                          // far above any SM count
-  return align256(sizeof(VerifyWs) + sizeof(unsigned long long) * (static_cast<size_t>(kVerifyMaxRows) + 1) * max_grid);
+  const size_t need = sizeof(VerifyWs) > sizeof(DraftQWs) ? sizeof(VerifyWs) : sizeof(DraftQWs);   // lm_verify and lm_draft_q may share it
+  return align256(need);
 }
 
 int lm_argmax(const void* logits, int32_t dtype, int64_t rows, int64_t vocab, int64_t row_stride, int32_t* out_tokens, void* workspace,
@@ -277,6 +238,7 @@ int lm_sample(const lm_sample_args* a) {
   if (a->history != nullptr && (a->hist_len < 0 || a->hist_stride < a->hist_len)) return LM_E_INVALID;
   if (a->history != nullptr && !(a->repetition_penalty > 0.0f)) return LM_E_INVALID;
   if (a->out_probs != nullptr && a->probs_stride < a->vocab) return LM_E_INVALID;
+  if (a->step_state != nullptr && lm_step_state_bytes(a->t_max, a->gamma_max) == 0) return LM_E_INVALID;
   // an all-greedy call needs no uniforms; a stochastic inverse-CDF call does
   if (a->draw == LM_DRAW_INVERSE_CDF && a->uniforms == nullptr && (a->temperature != nullptr || a->temperature_s > 0.0f)) return LM_E_INVALID;
 
@@ -291,6 +253,7 @@ int lm_sample(const lm_sample_args* a) {
   P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
   P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_stats = a->out_stats; P.out_probs = a->out_probs; P.probs_stride = a->probs_stride;
   P.out_status = a->out_status;
+  P.state = static_cast<const uint32_t*>(a->step_state); P.t_max = a->t_max; P.g = a->gamma_max > 1 ? a->gamma_max : 1;
 
   int sms = 0;
   int rc = sm_count(&sms);
@@ -299,7 +262,7 @@ int lm_sample(const lm_sample_args* a) {
   const int* redo_list = nullptr; const int* redo_n = nullptr;
   // BF16 rows that only need tokens (and tau) stream through the one-pass kernel; it marks the rows it cannot take
   // and the generic kernel behind it handles exactly those.
-  const bool fast = a->dtype == LM_DTYPE_BF16 && a->out_stats == nullptr && a->out_probs == nullptr && a->vocab <= kFastMaxVocab &&
+  const bool fast = a->dtype == LM_DTYPE_BF16 && a->out_stats == nullptr && a->out_probs == nullptr && a->vocab <= kHistMaxVocab &&
                     (a->vocab % kChunk) == 0 && (!pen || a->hist_len <= 65536);
   if (fast) {
     if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) || a->workspace_bytes < lm_workspace_bytes(a->rows, a->vocab))
@@ -312,7 +275,8 @@ int lm_sample(const lm_sample_args* a) {
     int* counters = reinterpret_cast<int*>(ws + 3 * rows_bytes);
     // counters: 0 next row of the top-k kernel, 1 length of list_left, 2 next item of the histogram kernel, 3 length of redo,
     //           4 length of list_other, 5 next item of the histogram kernel's second launch
-    rc = ensure_dynamic_smem(kSlotFast, reinterpret_cast<const void*>(sample_fast_kernel), sizeof(FastSmem));
+    const size_t hist_smem = hist_smem_bytes(static_cast<int>(a->vocab));
+    rc = ensure_dynamic_smem(kSlotFast, reinterpret_cast<const void*>(sample_hist_kernel), hist_smem);
     if (rc == LM_OK) rc = ensure_dynamic_smem(kSlotTopk, reinterpret_cast<const void*>(sample_topk_kernel), sizeof(TopkSmem));
     if (rc != LM_OK) return rc;
     const int limit = static_cast<int>((a->flags >> 8) & 0xFFu);
@@ -322,17 +286,18 @@ int lm_sample(const lm_sample_args* a) {
       const cudaError_t e = cudaMemsetAsync(counters, 0, 8 * sizeof(int), st);
       if (e != cudaSuccess) return cuda_fail(e);
     }
-    int grid = static_cast<int>(a->rows < sms ? a->rows : sms);
+    const long long hist_per_sm = 2 * (hist_smem + 1024) <= 233472 ? 2 : 1;   // blocks of the histogram kernel that fit one SM's shared memory
+    int grid = static_cast<int>(a->rows < hist_per_sm * sms ? a->rows : hist_per_sm * sms);
     if (limit > 0 && grid > limit) grid = limit;
     int grid1 = static_cast<int>(a->rows < static_cast<long long>(kTopkPerSM) * sms ? a->rows : static_cast<long long>(kTopkPerSM) * sms);
     if (limit > 0 && grid1 > limit) grid1 = limit;
     if (!topk) {
-      sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, nullptr, nullptr, counters + 2, redo, counters + 3);
+      sample_hist_kernel<<<grid, kHB, hist_smem, st>>>(P, nullptr, nullptr, counters + 2, redo, counters + 3);
     } else if (a->rows > static_cast<int64_t>(kOverlapRowsPerSM) * sms) {
       // Many rows per SM: the top-k kernel first (it lists the rows it does not take or cannot finish), then the histogram
       // kernel on that list. The few rows the top-k kernel hands on are absorbed among the histogram kernel's other rows.
       sample_topk_kernel<<<grid1, kTB, sizeof(TopkSmem), st>>>(P, list_left, counters, 1);
-      sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, list_left, counters + 1, counters + 2, redo, counters + 3);
+      sample_hist_kernel<<<grid, kHB, hist_smem, st>>>(P, list_left, counters + 1, counters + 2, redo, counters + 3);
     } else {
       // Few rows per SM: the length of a launch is the length of its longest rows, so the two kernels, which work on different
       // rows, share the GPU. The histogram kernel (long rows, one block per SM) goes first on the rows a one-thread-per-row
@@ -340,7 +305,7 @@ int lm_sample(const lm_sample_args* a) {
       // as the histogram kernel's blocks leave them (at once, for the SMs it has no rows for); a second launch of the histogram
       // kernel takes what the top-k kernel handed on (usually nothing: it leaves at once).
       sample_classify_kernel<<<static_cast<int>((a->rows + 255) / 256), 256, 0, st>>>(P, list_other, counters + 4);
-      sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, list_other, counters + 4, counters + 2, redo, counters + 3);
+      sample_hist_kernel<<<grid, kHB, hist_smem, st>>>(P, list_other, counters + 4, counters + 2, redo, counters + 3);
       cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return cuda_fail(e);
       cudaLaunchConfig_t cfg = {};
@@ -351,7 +316,7 @@ int lm_sample(const lm_sample_args* a) {
       cfg.attrs = attr; cfg.numAttrs = 1;
       e = cudaLaunchKernelEx(&cfg, sample_topk_kernel, P, list_left, counters, 0);
       if (e != cudaSuccess) return cuda_fail(e);
-      sample_fast_kernel<<<grid, kBlock, sizeof(FastSmem), st>>>(P, list_left, counters + 1, counters + 5, redo, counters + 3);
+      sample_hist_kernel<<<grid, kHB, hist_smem, st>>>(P, list_left, counters + 1, counters + 5, redo, counters + 3);
     }
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e);
@@ -483,10 +448,13 @@ int lm_verify(const lm_verify_args* a) {
   if (a->mode != LM_VERIFY_GREEDY && a->mode != LM_VERIFY_STOCHASTIC) return LM_E_INVALID;
   if (a->dtype != LM_DTYPE_BF16 && a->dtype != LM_DTYPE_F32) return LM_E_INVALID;
   if (a->n_draft < 1 || a->n_draft > LM_MAX_DRAFT) return LM_E_INVALID;
-  if (!a->target_logits || !a->draft_ids || !a->out_accept || !a->out_final || a->vocab < 1 || a->row_stride < a->vocab) return LM_E_INVALID;
+  if (!a->target_logits || !a->out_accept || !a->out_final || a->vocab < 1 || a->row_stride < a->vocab) return LM_E_INVALID;
+  if (!a->draft_ids && !a->step_state) return LM_E_INVALID;                 // the drafts come from the arguments or from the state
   if (a->vocab > LM_MAX_VOCAB) return LM_E_UNSUPPORTED;
+  if (a->step_state && (lm_step_state_bytes(a->t_max, a->gamma_max) == 0 || a->t_max < a->n_draft + 1)) return LM_E_INVALID;
   if (a->mode == LM_VERIFY_STOCHASTIC) {
-    if (!a->u_accept || !a->u_final || !(a->temperature > 0.0f)) return LM_E_INVALID;
+    if (!(a->temperature > 0.0f)) return LM_E_INVALID;
+    if (a->residual_draw != LM_RESIDUAL_INVERSE_CDF && a->residual_draw != LM_RESIDUAL_GUMBEL) return LM_E_INVALID;
     if (a->draft_probs) { if (a->probs_stride < a->vocab) return LM_E_INVALID; }
     else if (!a->draft_logits || a->draft_logits_stride < a->vocab || !a->draft_vmax || !a->draft_mass) return LM_E_INVALID;
   }
@@ -497,28 +465,29 @@ int lm_verify(const lm_verify_args* a) {
   if (rc != LM_OK) return rc;
   VerifyDev P;
   P.mode = a->mode; P.dtype = a->dtype; P.n_draft = a->n_draft; P.vocab = static_cast<int>(a->vocab); P.row_stride = a->row_stride;
+  P.draw = a->residual_draw == LM_RESIDUAL_GUMBEL ? LM_DRAW_GUMBEL : LM_DRAW_INVERSE_CDF;
   P.target = a->target_logits; P.drafts = a->draft_ids; P.q = a->draft_probs; P.q_stride = a->probs_stride; P.temperature = a->temperature;
   P.q_logits = static_cast<const uint16_t*>(a->draft_logits); P.q_logits_stride = a->draft_logits_stride;
   P.q_vmax = a->draft_vmax; P.q_mass = reinterpret_cast<const unsigned long long*>(a->draft_mass);
-  P.tau = a->tau; P.u_accept = a->u_accept; P.u_final = a->u_final;
+  P.tau = a->tau; P.u_accept = a->u_accept; P.u_final = a->u_final; P.seed = a->seed; P.step = a->step;
   P.out_accept = a->out_accept; P.out_final = a->out_final; P.out_tokens = a->out_tokens; P.out_p_draft = a->out_p_draft;
   P.ws = static_cast<VerifyWs*>(a->workspace);
+  P.state = static_cast<uint32_t*>(const_cast<void*>(a->step_state)); P.t_max = a->t_max; P.g = a->gamma_max > 1 ? a->gamma_max : 1;
+  P.wait_limit = a->wait_limit; P.withhold = (a->selftest & LM_VERIFY_SELFTEST_WITHHOLD) ? 1u : 0u;
   P.commit = 0;
   if (a->commit) {
     const lm_step_args* c = a->commit;
     rc = step_args_ok(c);
     if (rc != LM_OK) return rc;
     if (!a->out_tokens || !c->ring || c->ring_cap == 0 || (c->log_cap && !c->log)) return LM_E_INVALID;
+    if (a->step_state && (a->step_state != c->step_state || a->t_max != c->t_max || a->gamma_max != c->gamma_max)) return LM_E_INVALID;
     P.commit = 1;
     P.accept = AcceptDev{a->out_tokens, static_cast<uint32_t*>(c->step_state), c->t_max, c->gamma_max > 1 ? c->gamma_max : 1,
                          reinterpret_cast<unsigned long long*>(c->ring), c->ring_cap, EosSet{c->eos, c->eos_list, c->n_eos}, c->log, c->log_cap,
                          c->ctx_cap, c->lm};
   }
-  // one block per SM, all resident at once (the phases meet at a grid barrier): a cooperative launch guarantees it
-  int grid = sms < 1024 ? sms : 1024;
-#ifdef LM_VERIFY_GRID_DIV
-  grid = grid / LM_VERIFY_GRID_DIV > 0 ? grid / LM_VERIFY_GRID_DIV : 1;
-#endif
+  // one block per SM, all resident at once (the blocks wait for one another's partial results): a cooperative launch guarantees it
+  int grid = sms < 256 ? sms : 256;                                        // consume_rows holds rows x grid words in kConsumeSlots per thread
   const int max_useful = static_cast<int>((a->vocab + 7) / 8);
   if (grid > max_useful) grid = max_useful;
   // the block's slices of all rows in shared memory when they fit (they do for every vocabulary up to ~700k at 148 SMs)
@@ -530,14 +499,8 @@ int lm_verify(const lm_verify_args* a) {
   rc = ensure_dynamic_smem(kSlotVerify, reinterpret_cast<const void*>(verify_kernel), smem);
   if (rc != LM_OK) return rc;
   void* params[] = {&P, &cached};
-#ifdef LM_VERIFY_PLAIN_LAUNCH
-  verify_kernel<<<grid, kVerifyBlock, smem, static_cast<cudaStream_t>(a->stream)>>>(P, cached);
-  const cudaError_t e = cudaGetLastError();
-  (void)params;
-#else
   const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(verify_kernel), dim3(grid), dim3(kVerifyBlock), params, smem,
                                                     static_cast<cudaStream_t>(a->stream));
-#endif
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }
 
@@ -547,6 +510,7 @@ int lm_draft_q(const lm_draft_q_args* a) {
   if (!a->logits || !a->out_tokens || a->vocab < 1 || a->row_stride < a->vocab || !(a->temperature > 0.0f)) return LM_E_INVALID;
   if (a->out_q_logits && a->q_logits_stride < a->vocab) return LM_E_INVALID;
   if (a->vocab > LM_MAX_VOCAB) return LM_E_UNSUPPORTED;
+  if (a->step_state && lm_step_state_bytes(a->t_max, a->gamma_max) == 0) return LM_E_INVALID;
   if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) || a->workspace_bytes < lm_verify_workspace_bytes(a->rows, a->vocab))
     return LM_E_WORKSPACE;
   int sms = 0;
@@ -557,16 +521,15 @@ int lm_draft_q(const lm_draft_q_args* a) {
   P.logits = a->logits; P.temperature = a->temperature; P.seed = a->seed; P.step = a->step;
   P.out_tokens = a->out_tokens; P.out_lse = a->out_lse; P.out_vmax = a->out_vmax; P.out_mass = reinterpret_cast<unsigned long long*>(a->out_mass);
   P.out_status = a->out_status; P.out_q_logits = a->out_q_logits; P.q_logits_stride = a->q_logits_stride;
-  P.ws = static_cast<VerifyWs*>(a->workspace);
+  P.ws = static_cast<DraftQWs*>(a->workspace);
+  P.state = static_cast<const uint32_t*>(a->step_state); P.t_max = a->t_max; P.g = a->gamma_max > 1 ? a->gamma_max : 1;
   // one block per SM, all resident at once (one grid barrier), each holding its slice of every row in shared memory;
   // more blocks than that never, fewer when the slices would not fit
   int grid = sms < 1024 ? sms : 1024;
-#ifndef LM_DRAFTQ_PER_THREAD
-#define LM_DRAFTQ_PER_THREAD 4
-#endif
+  constexpr int kPerThread = 4;
   {
     // a single row is ~150 logits per SM: fewer blocks with a few logits per thread meet sooner at the barrier
-    const long long want = (static_cast<long long>(a->rows) * a->vocab + kVerifyBlock * LM_DRAFTQ_PER_THREAD - 1) / (kVerifyBlock * LM_DRAFTQ_PER_THREAD);
+    const long long want = (static_cast<long long>(a->rows) * a->vocab + kDraftQBlock * kPerThread - 1) / (kDraftQBlock * kPerThread);
     if (want < grid) grid = static_cast<int>(want < 1 ? 1 : want);
   }
   const int per = (static_cast<int>((a->vocab + grid - 1) / grid) + 7) & ~7;
@@ -575,7 +538,7 @@ int lm_draft_q(const lm_draft_q_args* a) {
   const int rs = ensure_dynamic_smem(kSlotDraftQ, reinterpret_cast<const void*>(draft_q_kernel), smem);
   if (rs != LM_OK) return rs;
   void* params[] = {&P};
-  const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(draft_q_kernel), dim3(grid), dim3(kVerifyBlock), params, smem,
+  const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(draft_q_kernel), dim3(grid), dim3(kDraftQBlock), params, smem,
                                                     static_cast<cudaStream_t>(a->stream));
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }

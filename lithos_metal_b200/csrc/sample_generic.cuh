@@ -10,6 +10,7 @@
 #pragma once
 #include "common.cuh"
 #include "draw.cuh"
+#include "spec_ops.cuh"
 
 namespace lm {
 
@@ -21,7 +22,19 @@ struct SampleDev {              // lm_sample_args without the host-only fields
   const int32_t* history; int hist_len; int64_t hist_stride; float rho, pi;
   const float* uniforms; uint64_t seed; uint32_t step; int64_t row_offset;
   int32_t* out_tokens; float* out_tau; float* out_stats; float* out_probs; int64_t probs_stride; uint32_t* out_status;
+  const uint32_t* state; int t_max, g;                  // optional StepState: seed, step and the active rows come from it
 };
+
+// With a StepState, the sampler kernels take from it what the reference's kernels take from theirs (kernels/common/sample.metal:
+// 172-181, argmax.metal:44-46): the noise seed and step, and the number of active rows; a finished generation has none. Every
+// kernel calls this on its copy of the parameters before anything else.
+__device__ __forceinline__ void apply_step_state(SampleDev& P) {
+  if (!P.state) return;
+  StepStateView st{const_cast<uint32_t*>(P.state), P.t_max, P.g};
+  const int active = st.done() ? 0 : static_cast<int>(st.t_this_step());
+  P.rows = active < P.rows ? active : P.rows;
+  P.seed = st.seed(); P.step = st.step();
+}
 
 constexpr uint32_t kStatusBadParam = 16u;
 constexpr int kBins = 256;

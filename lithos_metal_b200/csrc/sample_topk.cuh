@@ -4,11 +4,11 @@
 // above a cutoff (estimated per row from 8192 of its logits: about 1 % of the row ends up above it), and
 // (b) accumulate the softmass of the whole row in FP32 (the top-p target needs it). Everything exact then happens on the
 // candidates alone: the k-th largest value, FP64 masses, the top-p boundary, integer weights, the draw. The FP32 mass is
-// only used to decide on which side of top_p * Z a cumulative mass lies; if that is closer than the FP32 error bound, or
-// the candidates do not cover the top-k set, or anything else does not fit, the row is flagged and the histogram
-// kernel launched behind this one redoes it exactly.
-// Blocks are small (256 threads, ~72 KB of shared memory) so that three rows are in flight per SM: the per-row phases after
-// the pass are chains of short dependent steps, and only rows in other blocks can hide them.
+// only used to decide on which side of top_p * Z a cumulative mass lies; if that is closer than the FP32 error bound (derived
+// where it is applied), or the candidates do not cover the top-k set, or anything else does not fit, the row is handed on and
+// the histogram kernel launched behind this one redoes it exactly.
+// Two blocks of 512 threads share an SM (~93 KB of shared memory each): the per-row phases after the pass are chains of short
+// dependent steps, and only the row in the other block can hide them.
 // No counterpart in the reference (its sampler always builds the full histogram, kernels/common/sample.metal:34-162).
 #pragma once
 #include <cuda_bf16.h>
@@ -165,6 +165,7 @@ __device__ __forceinline__ bool topk_row_eligible(const SampleDev& P, int row) {
 
 // The rows that are not the top-k kernel's, listed for the histogram kernel (one thread per row).
 __global__ void sample_classify_kernel(SampleDev P, int* list, int* n_list) {
+  apply_step_state(P);
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row < P.rows && !topk_row_eligible(P, row)) list[atomicAdd(n_list, 1)] = row;
 }
@@ -369,7 +370,7 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   LM_TPHASE(9);
   // a NaN or +inf logit (or a logit far above the sampled maximum) has made this thread's sum NaN or infinite: the exact path
   // takes such rows and reports them
-  double zsum = 0.0;
+  double zsum = 0.0, zadd = 0.0, zsub = 0.0;                                // the pass's mass; what the penalised logits add; what their raw values had added
   if (need_z) {
     const float total = sacc.x + sacc.y;
     if (!(total < INFINITY)) nan_seen = 1u;
@@ -429,7 +430,7 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
       if (i < n_side) {
         const float raw = __uint_as_float(static_cast<uint32_t>(raws[j]) << 16);
         v = penalise(raw, P.rho, P.pi);
-        if (need_z) zsum += static_cast<double>(ex2_approx((v - M) * c2a)) - static_cast<double>(ex2_approx((raw - M) * c2a));
+        if (need_z) { zadd += static_cast<double>(ex2_approx(__fmaf_rn(v, c2a, nb))); zsub += static_cast<double>(ex2_approx(__fmaf_rn(raw, c2a, nb))); }
       }
       const bool cand = v >= cut_val;
       const uint32_t slot = warp_reserve(&c.n, cand ? 1u : 0u);
@@ -440,7 +441,17 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
       }
     }
   }
-  const double z_tilde = need_z ? block_sum_f64(zsum, c.scratch) : 0.0;     // relative to M
+  double z_raw = 0.0, z_add = 0.0, z_sub = 0.0;                             // block totals, relative to the sampled maximum
+  if (need_z) {
+    zsum = warp_sum_f64(zsum); zadd = warp_sum_f64(zadd); zsub = warp_sum_f64(zsub);
+    double* sd = reinterpret_cast<double*>(c.scratch);
+    __syncthreads();
+    if (lane == 0) { sd[warp] = zsum; sd[kTW + warp] = zadd; c.warp_d[warp] = zsub; }
+    __syncthreads();
+    for (int w = 0; w < kTW; w++) { z_raw += sd[w]; z_add += sd[kTW + w]; z_sub += c.warp_d[w]; }
+  }
+  const double z_tilde = z_raw - z_sub + z_add;
+  if (need_z && !(z_tilde > 0.0)) return false;                             // nothing left after the corrections (cancellation): the exact path
   __syncthreads();
   const int n = static_cast<int>(c.n);
   if (n > kTopkCap || n < top_k || c.wide) return false;
@@ -510,9 +521,28 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
     const int n_topk = static_cast<int>(block_sum_u64(cnt_k, c.scratch));
     double total, err = 0.0;
     if (in_topk) total = c.cum[n_topk - 1];
-    else {                                                                 // the FP32 mass of the whole row, moved to the exact maximum
-      total = z_tilde * exp2((static_cast<double>(M) - static_cast<double>(vmax)) * 1.4426950408889634 * inv_t);
-      err = 2e-6 * total;
+    else {
+      // The FP32 mass of the whole row, moved to the exact maximum. z_tilde approximates sum_i 2^(z_i c2a + nb); nb's own rounding
+      // is a common factor and is taken out exactly here (the true nb is used, not -M c2a).
+      const double c64 = 1.4426950408889634 * inv_t;
+      total = z_tilde * exp2(-static_cast<double>(nb) - static_cast<double>(vmax) * c64);
+      // What separates it from sum_i 2^((z_i - vmax) c), relative, first order, worst case (u = 2^-24, the FP32 unit roundoff):
+      //   - c2a = fl32(c): every term is off by a factor 2^(x_i delta), |delta| <= u, x_i = (z_i - M) c; weighted by the terms that is
+      //     ln2 u E_w|x| <= u (ln V + 2 ln2 D): E_w[-x ln2] = H - ln Z <= ln V (H the entropy of the softmax, Z >= 1 relative to the
+      //     row maximum, V <= 2^18: ln V <= 12.5), and the terms above the sampled maximum have 0 < x <= D = (vmax - M) c;
+      //   - the FMA rounds its result: half an ulp of |x| < 32 is at most 2^-20, a factor 2^(2^-20) = 1 + 6.6e-7 on the term; the terms
+      //     with |x| >= 32 weigh less than V 2^-32 altogether;
+      //   - ex2.approx.ftz.f32: 2 ulp = 4 u;
+      //   - each lane accumulates 4 n_it terms one after the other in FP32, then two accumulators and the lanes meet in FP64:
+      //     (4 n_it + 1) u;
+      // These are relative to the mass the pass summed (z_raw), which holds the penalised positions at their raw values. The penalised
+      // logits then enter as z_raw - z_sub + z_add, every term of z_sub and z_add with the per-term errors above (FMA, ex2, c2a on a
+      // single term: 1.6e-6 covers them for |x| < 32); when penalised tokens carried most of the raw mass the band grows with them.
+      // The band is this bound with a quarter added. A boundary of the cumulative mass inside it is decided by the exact path.
+      const double u = 5.9604644775390625e-8;
+      const double D = fmax(0.0, (static_cast<double>(vmax) - static_cast<double>(M)) * c64);
+      const double rel = u * (12.5 + 1.3862943611198906 * D) + 6.6e-7 + 4.0 * u + (4.0 * n_it + 1.0) * u;
+      err = 1.25 * (rel * z_raw + 1.6e-6 * (z_sub + z_add)) * (total / z_tilde);
     }
     const double target = static_cast<double>(top_p) * total;
     bool amb = false;
@@ -631,6 +661,7 @@ __global__ void __launch_bounds__(kTB, kTopkPerSM) sample_topk_kernel(SampleDev 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   TopkSmem& c = *reinterpret_cast<TopkSmem*>(smem_raw);
   __shared__ int item[2];                                                   // the row in hand and the one after it
+  apply_step_state(P);
   if (threadIdx.x < 8) c.prev_cut[threadIdx.x] = 0u;
   if (threadIdx.x == 0) { item[0] = atomicAdd(&counters[0], 1); item[1] = item[0] < P.rows ? atomicAdd(&counters[0], 1) : P.rows; }
   __syncthreads();

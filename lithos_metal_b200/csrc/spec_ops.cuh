@@ -1,11 +1,13 @@
-// The scalar step-closing kernels of GPU-resident generation control, on the reference's StepState layout:
-//   accept_scan   (kernels/common/spec_ops.metal:148-195)  greedy prefix match, commit to the token ring, advance the state
-//   verify_select (kernels/common/spec_ops.metal:108-146)  stage the next round's drafts and pick the verify length
-//   advance       (kernels/common/advance.metal:15-37)     close a plain decode step
-//   confidence    (kernels/common/spec_ops.metal:85-106)   the DSpark confidence head that feeds verify_select
-// One thread each: they are a few dozen dependent scalar operations; what matters is that they run on the device,
-// in stream order, so the host never has to read a token to keep the loop going. The state is the reference's
-// binary contract (monolith/core/step_state.py:38-62): 4-byte fields, same order, for any t_max / gamma_max.
+// The step-closing kernels of GPU-resident generation control. They keep the decode loop on the device: the host never reads
+// a token to decide what runs next. Each works on the reference's StepState record, a binary contract
+// (monolith/core/step_state.py:38-62: 4-byte fields, fixed order, sized by t_max / gamma_max), and must leave exactly the
+// bytes the reference's kernels leave:
+//   round_close     what accept_scan does  (kernels/common/spec_ops.metal:148-195)  prefix match, ring commit, state advance
+//   round_select    what verify_select does (kernels/common/spec_ops.metal:108-146) stage drafts, pick the verify length
+//   step_advance    what advance does       (kernels/common/advance.metal:15-37)    close a plain decode step
+//   confidence      the DSpark confidence head (kernels/common/spec_ops.metal:85-106) that feeds round_select
+// Each runs as ONE WARP: the per-draft work (token compares, stop-token tests, ring slots, staging) is spread over the lanes
+// and joined with votes; the state record is then updated by lane 0.
 #pragma once
 #include "common.cuh"
 
@@ -38,13 +40,23 @@ struct StepStateView {
   __device__ __forceinline__ uint32_t& n_inject() { return tail(9); }
   __device__ __forceinline__ uint32_t& stop_at() { return tail(10); }
   __device__ __forceinline__ uint32_t& n_chain() { return tail(11); }
+  __device__ __forceinline__ uint64_t seed() { return (static_cast<uint64_t>(rng_hi()) << 32) | rng_lo(); }
 };
+
+constexpr uint32_t kErrRingFull = 1u, kErrContextFull = 2u, kErrBarrier = 3u, kErrRoundMismatch = 4u;
 
 struct EosSet { int32_t eos; const int32_t* list; int n; };                 // eos < 0 and n == 0: no stop token
 __device__ __forceinline__ bool is_eos(const EosSet& e, int32_t tok) {
-  if (e.eos >= 0 && tok == e.eos) return true;
-  for (int i = 0; i < e.n; i++) if (tok == e.list[i]) return true;
-  return false;
+  bool hit = e.eos >= 0 && tok == e.eos;
+  for (int i = 0; i < e.n; i++) hit = hit || tok == e.list[i];
+  return hit;
+}
+
+// Ends a generation with an error code; lane 0 only.
+__device__ __forceinline__ void fail_state(StepStateView& st, uint32_t code) { st.error() = code; st.done() = 1u; }
+// One entry of the token ring: the sequence number of the token (1-based) above the token id.
+__device__ __forceinline__ unsigned long long ring_entry(uint32_t seq, int32_t tok) {
+  return (static_cast<unsigned long long>(seq) << 32) | static_cast<unsigned long long>(static_cast<uint32_t>(tok));
 }
 
 struct AcceptDev {
@@ -52,57 +64,71 @@ struct AcceptDev {
   uint32_t* log; uint32_t log_cap; uint32_t ctx_cap; int lm;
 };
 
-// The accept scan proper; one thread. Also the last act of the verify kernel when a round is committed there.
-__device__ void accept_scan_body(const AcceptDev& p) {
+// Closes a speculative round. All 32 lanes of one warp call it with the same arguments; `p.token` holds the target's pick
+// for every row of the step (written before the call and visible to the warp).
+//   lanes r < L     compare the pick of row base + r with draft r (pending[base + r + 1]); the first mismatch is the accept count
+//   lanes k <= acc  hold the k-th token to commit (accepted draft, or the pick after the last accepted one), test it against the
+//                   stop tokens, and, up to the first stop token, publish it in ring slot head + k
+//   lane 0          writes the log entry and moves the state on
+__device__ void round_close(const AcceptDev& p) {
+  const int lane = threadIdx.x & 31;
   StepStateView st{p.state, p.t_max, p.g};
   if (st.done()) return;
-  const uint32_t t = st.t_this_step();
-  if (st.prefill_left() > 0u) {                                           // a prefill chunk: nothing to verify, inject its positions
-    if (p.log_cap) p.log[st.step() % p.log_cap] = (t << 16) | 0xFFFFu;
-    st.position() += t;
-    st.step() += 1u;
-    st.n_inject() = t;
-    st.checkpoint_index() = t;
-    st.n_chain() = 0u;
-    if (p.ctx_cap && st.position() >= p.ctx_cap) { st.error() = 2u; st.done() = 1u; }
+  const uint32_t rows = st.t_this_step();
+  if (st.prefill_left() > 0u) {
+    // prompt rows only: no draft was checked and nothing is published; the rows become injected context
+    if (lane == 0) {
+      if (p.log_cap) p.log[st.step() % p.log_cap] = (rows << 16) | 0xFFFFu;
+      const uint32_t pos = st.position() + rows;
+      st.position() = pos; st.step() += 1u;
+      st.n_inject() = rows; st.checkpoint_index() = rows; st.n_chain() = 0u;
+      if (p.ctx_cap && pos >= p.ctx_cap) fail_state(st, kErrContextFull);
+    }
     return;
   }
-  const uint32_t L = st.verify_len();
-  const uint32_t base = t - 1u - L;
-  uint32_t acc = 0u;
-  while (acc < L && p.token[base + acc] == st.pending(base + acc + 1u)) acc++;
-  const int32_t bonus = p.token[base + acc];
-  uint32_t head = st.ring_head();
-  if (head + acc + 1u - st.ring_tail() > p.ring_cap) { st.error() = 1u; st.done() = 1u; return; }   // the host fell behind
-  uint32_t committed = 0u;
-  int32_t last = bonus;
-  bool stop = false;
-  for (uint32_t k = 0; k <= acc; k++) {
-    const int32_t tok = (k < acc) ? st.pending(base + k + 1u) : bonus;
-    p.ring[head % p.ring_cap] = (static_cast<unsigned long long>(head + 1u) << 32) | static_cast<unsigned long long>(static_cast<uint32_t>(tok));
-    head++; committed++; last = tok;
-    if (is_eos(p.eos, tok)) { stop = true; break; }                       // nothing after the first stop token is committed
+  const uint32_t L = st.verify_len(), base = rows - 1u - L;
+  // accept count: the number of leading drafts the target agrees with (32 drafts per vote)
+  uint32_t acc = L;
+  for (uint32_t r0 = 0; r0 < L; r0 += 32u) {
+    const uint32_t r = r0 + lane;
+    const bool differs = r < L && p.token[base + r] != st.pending(base + r + 1u);
+    const uint32_t votes = __ballot_sync(kFull, differs);
+    if (votes) { acc = r0 + static_cast<uint32_t>(__ffs(votes)) - 1u; break; }
   }
-  if (p.log_cap) p.log[st.step() % p.log_cap] = (committed << 16) | (L << 8) | acc;
-  st.ring_head() = head;
-  if (st.stop_at() && head >= st.stop_at()) stop = true;
-  st.accepted() = acc;
-  st.anchor() = last;
-  st.position() += base + committed;
-  st.step() += 1u;
-  st.verify_len() = 0u;
-  st.t_this_step() = 1u;
-  st.n_inject() = base + committed;
-  st.checkpoint_index() = base + committed;
-  st.n_chain() = 1u;
-  if (p.lm) st.n_inject() = (st.position() > st.drafter_ctx_len()) ? st.position() - st.drafter_ctx_len() : 0u;
-  if (stop) st.done() = 1u;
-  if (p.ctx_cap && st.position() >= p.ctx_cap) { st.error() = 2u; st.done() = 1u; }
+  const uint32_t head = st.ring_head();
+  if (head + acc + 1u - st.ring_tail() > p.ring_cap) {                      // the consumer has not drained the ring: stop rather than overwrite
+    if (lane == 0) fail_state(st, kErrRingFull);
+    return;
+  }
+  // the tokens of this round in commit order, cut after the first stop token
+  uint32_t n_commit = acc + 1u; bool stop = false; int32_t last = 0;
+  for (uint32_t k0 = 0; k0 <= acc; k0 += 32u) {
+    const uint32_t k = k0 + lane;
+    const bool mine = k <= acc;
+    const int32_t tok = mine ? (k < acc ? st.pending(base + k + 1u) : p.token[base + acc]) : 0;
+    const uint32_t stops = __ballot_sync(kFull, mine && is_eos(p.eos, tok));
+    const uint32_t upto = stops ? k0 + static_cast<uint32_t>(__ffs(stops)) : acc + 1u;   // tokens committed, counted from 0
+    if (k < upto) p.ring[(head + k) % p.ring_cap] = ring_entry(head + k + 1u, tok);
+    const uint32_t last_lane = (upto - 1u) - k0;
+    if (last_lane < 32u) last = __shfl_sync(kFull, tok, static_cast<int>(last_lane));
+    if (stops) { n_commit = upto; stop = true; break; }
+  }
+  if (lane == 0) {
+    if (p.log_cap) p.log[st.step() % p.log_cap] = (n_commit << 16) | (L << 8) | acc;
+    const uint32_t new_head = head + n_commit, fed = base + n_commit, pos = st.position() + fed;
+    st.ring_head() = new_head;
+    st.accepted() = acc; st.anchor() = last;
+    st.position() = pos; st.step() += 1u;
+    st.verify_len() = 0u; st.t_this_step() = 1u;
+    st.checkpoint_index() = fed; st.n_chain() = 1u;
+    st.n_inject() = p.lm ? (pos > st.drafter_ctx_len() ? pos - st.drafter_ctx_len() : 0u) : fed;
+    if (stop || (st.stop_at() && new_head >= st.stop_at())) st.done() = 1u;
+    if (p.ctx_cap && pos >= p.ctx_cap) fail_state(st, kErrContextFull);
+  }
 }
 
 __global__ void accept_scan_kernel(AcceptDev p) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  accept_scan_body(p);
+  if (blockIdx.x == 0 && threadIdx.x < 32) round_close(p);
 }
 
 struct SelectDev {
@@ -110,102 +136,129 @@ struct SelectDev {
   float* conf_log; uint32_t log_cap; uint32_t ctx_cap; int lm; uint32_t t_limit;
 };
 
+// Prepares the next round: lanes k < gamma copy draft k and its confidence into the state (and the confidence log); the verify
+// length L comes from the confidences (mode 0: the confident prefix, by vote; mode 1: the length with the best expected tokens
+// per unit cost, a running product that lane 0 forms in the reference's order; mode 2: a fixed length); lanes k < L then stage
+// draft k as pending token k + 1 behind the anchor. One warp.
 __global__ void verify_select_kernel(SelectDev p) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (blockIdx.x != 0 || threadIdx.x >= 32) return;
+  const uint32_t lane = threadIdx.x;
   StepStateView st{p.state, p.t_max, p.g};
   if (st.done()) return;
-  if (p.lm) st.drafter_ctx_len() = st.position() + ((st.prefill_left() > 0u) ? 0u : p.gamma);
-  else st.drafter_ctx_len() = st.drafter_ctx_len() + st.n_inject();
-  st.n_inject() = 0u;
-  if (st.prefill_left() > 0u) return;                                     // the host feeds the next chunk
-  for (uint32_t k = 0; k < p.gamma; k++) {
-    st.draft(k) = p.drafts[k];
-    st.confidence(k) = p.conf[k];
-    if (p.log_cap) p.conf_log[(st.step() % p.log_cap) * 16u + k] = p.conf[k];
+  const bool prefill = st.prefill_left() > 0u;
+  const uint32_t pos = st.position(), step = st.step();
+  __syncwarp();
+  if (lane == 0) {
+    // how much context the drafter has seen: an LM drafter is fed up to the position (plus its own drafts in a decode round),
+    // a head drafter exactly what the last step injected
+    st.drafter_ctx_len() = p.lm ? pos + (prefill ? 0u : p.gamma) : st.drafter_ctx_len() + st.n_inject();
+    st.n_inject() = 0u;
   }
-  uint32_t L = 0u;
-  uint32_t lmax = min(p.gamma, p.t_limit - 1u);
-  if (p.ctx_cap) {                                                        // the verify rows must fit the target's caches
-    if (st.position() >= p.ctx_cap) { st.error() = 2u; st.done() = 1u; return; }
-    lmax = min(lmax, p.ctx_cap - st.position() - 1u);
+  if (prefill) return;                                                    // the next prompt chunk comes from the host; nothing to stage
+  const float my_conf = lane < p.gamma ? p.conf[lane] : 0.0f;
+  if (lane < p.gamma) {
+    st.draft(lane) = p.drafts[lane];
+    st.confidence(lane) = my_conf;
+    if (p.log_cap) p.conf_log[(step % p.log_cap) * 16u + lane] = my_conf;
   }
+  // the longest length the step program and the context leave room for
+  uint32_t room = min(p.gamma, p.t_limit - 1u);
+  if (p.ctx_cap) {
+    if (pos >= p.ctx_cap) { if (lane == 0) fail_state(st, kErrContextFull); return; }
+    room = min(room, p.ctx_cap - pos - 1u);
+  }
+  uint32_t L;
   if (p.mode == 2u) {
-    L = min(static_cast<uint32_t>(fmaxf(p.threshold, 0.0f)), lmax);
+    L = min(static_cast<uint32_t>(fmaxf(p.threshold, 0.0f)), room);
   } else if (p.mode == 1u) {
-    float a = 1.0f, expect = 1.0f, best = __fdiv_rn(1.0f, p.cost[0]);
-    for (uint32_t l = 1; l <= lmax; l++) {
-      a = __fmul_rn(a, p.conf[l - 1u]);
-      expect = __fadd_rn(expect, a);
-      const float score = __fdiv_rn(expect, p.cost[l]);
-      if (score > best) { best = score; L = l; }
+    // expected tokens of verifying l drafts = 1 + conf_0 + conf_0 conf_1 + ...; its cost = cost[l]; ties keep the shorter length
+    uint32_t best_l = 0u;
+    if (lane == 0) {
+      float reach = 1.0f, tokens = 1.0f, best = __fdiv_rn(1.0f, p.cost[0]);
+      for (uint32_t l = 1; l <= room; l++) {
+        reach = __fmul_rn(reach, p.conf[l - 1u]);
+        tokens = __fadd_rn(tokens, reach);
+        const float rate = __fdiv_rn(tokens, p.cost[l]);
+        if (rate > best) { best = rate; best_l = l; }
+      }
     }
+    L = __shfl_sync(kFull, best_l, 0);
   } else if (p.threshold <= 0.0f) {
-    L = lmax;
+    L = room;
   } else {
-    while (L < lmax && p.conf[L] >= p.threshold) L++;
+    const uint32_t unsure = __ballot_sync(kFull, lane < room && !(my_conf >= p.threshold));
+    L = unsure ? static_cast<uint32_t>(__ffs(unsure)) - 1u : room;
   }
-  st.gamma() = p.gamma;
-  st.verify_len() = L;
-  st.pending(0) = st.anchor();
-  for (uint32_t k = 0; k < L; k++) st.pending(k + 1u) = p.drafts[k];
-  st.t_this_step() = 1u + L;
+  if (lane < L) st.pending(lane + 1u) = p.drafts[lane];
+  if (lane == 0) {
+    st.gamma() = p.gamma; st.verify_len() = L;
+    st.pending(0) = st.anchor();
+    st.t_this_step() = 1u + L;
+  }
 }
 
 struct AdvanceDev { const int32_t* token; uint32_t* state; int t_max, g; unsigned long long* ring; uint32_t ring_cap; EosSet eos; uint32_t ctx_cap; };
 
+// Closes a step that verified nothing: the last row's token is the step's token. The lanes share the stop-token test (one list
+// entry each per vote); lane 0 publishes the token and moves the state on. One warp.
 __global__ void advance_kernel(AdvanceDev p) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (blockIdx.x != 0 || threadIdx.x >= 32) return;
+  const int lane = threadIdx.x;
   StepStateView st{p.state, p.t_max, p.g};
   if (st.done()) return;
-  const uint32_t t = st.t_this_step();
-  if (st.prefill_left() > 0u) {
-    st.position() += t;
-    st.step() += 1u;
-    if (p.ctx_cap && st.position() >= p.ctx_cap) { st.error() = 2u; st.done() = 1u; }
-    return;
+  const uint32_t rows = st.t_this_step();
+  const bool prefill = st.prefill_left() > 0u;
+  const int32_t tok = prefill ? 0 : p.token[rows - 1u];
+  bool stop_tok = false;
+  if (!prefill) {
+    bool hit = lane == 0 && p.eos.eos >= 0 && tok == p.eos.eos;
+    for (int i = lane; i < p.eos.n; i += 32) hit = hit || tok == p.eos.list[i];
+    stop_tok = __any_sync(kFull, hit);
   }
-  const int32_t tok = p.token[t - 1u];
-  const uint32_t head = st.ring_head();
-  if (head - st.ring_tail() >= p.ring_cap) { st.error() = 1u; st.done() = 1u; return; }
-  p.ring[head % p.ring_cap] = (static_cast<unsigned long long>(head + 1u) << 32) | static_cast<unsigned long long>(static_cast<uint32_t>(tok));
-  st.ring_head() = head + 1u;
-  if (st.stop_at() && st.ring_head() >= st.stop_at()) st.done() = 1u;
-  st.pending(0) = tok;
-  st.position() += t;
-  st.step() += 1u;
-  st.t_this_step() = 1u;
-  if (is_eos(p.eos, tok)) st.done() = 1u;
-  if (p.ctx_cap && st.position() >= p.ctx_cap) { st.error() = 2u; st.done() = 1u; }
+  if (lane != 0) return;
+  const uint32_t pos = st.position() + rows;
+  if (!prefill) {
+    const uint32_t head = st.ring_head();
+    if (head - st.ring_tail() >= p.ring_cap) { fail_state(st, kErrRingFull); return; }
+    p.ring[head % p.ring_cap] = ring_entry(head + 1u, tok);
+    st.ring_head() = head + 1u;
+    st.pending(0) = tok;
+    st.t_this_step() = 1u;
+    if (stop_tok || (st.stop_at() && head + 1u >= st.stop_at())) st.done() = 1u;
+  }
+  st.position() = pos; st.step() += 1u;
+  if (p.ctx_cap && pos >= p.ctx_cap) fail_state(st, kErrContextFull);
 }
 
-// The confidence head: conf[k] = sigmoid(bf16(bf16(w . [hidden_k ; emb_k]) + b) / sts[k]) for the gamma draft positions.
-// One warp per position, the reference's arithmetic step by step: lane l accumulates elements l, l + 32, ... of the hidden
-// row and then of the embedding row with one FMA each (FP32), the lanes meet in a butterfly sum, the dot product and the
-// biased sum are each rounded to BF16 (round to nearest even on the bit pattern). The sigmoid is evaluated on the library's
-// fixed exp2 (common.cuh) so that a CPU gives the same bits; the reference calls the Metal exp (test bar there: 2e-3).
+// The confidence head: conf[k] = sigmoid(bf16(bf16(w . [hidden_k ; emb_k]) + b) / sts[k]) for the gamma draft positions, one
+// warp per position. The sum is formed the way the reference's kernel forms it, because the two BF16 roundings make the order
+// visible in the result: lane l takes elements l, l + 32, ... of the hidden row and then of the embedding row with one FP32
+// FMA each, and the lanes meet in a butterfly. The sigmoid runs on the library's fixed exp2 (common.cuh), so a CPU restatement
+// gives the same bits; the reference calls the Metal exp (its test bar: 2e-3).
 struct ConfDev { const uint16_t* hidden; const uint16_t* emb; const float* w; const float* b; const float* sts; float* conf; uint32_t* state; int t_max, g; int gamma, n_hidden, rank; };
 
-__device__ __forceinline__ float round_bf16(float x) {
-  uint32_t u = __float_as_uint(x);
-  u += 0x7FFFu + ((u >> 16) & 1u);
-  return __uint_as_float(u & 0xFFFF0000u);
+__device__ __forceinline__ float round_bf16(float x) {                     // round to nearest even on the bit pattern
+  const uint32_t u = __float_as_uint(x);
+  return __uint_as_float((u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u);
+}
+// acc += row[i] * w[i] over this lane's elements of a BF16 row
+__device__ __forceinline__ float lane_dot_bf16(const uint16_t* row, const float* w, int n, int lane, float acc) {
+  for (int i = lane; i < n; i += 32) acc = __fmaf_rn(__uint_as_float(static_cast<uint32_t>(__ldg(row + i)) << 16), __ldg(w + i), acc);
+  return acc;
 }
 
 __global__ void confidence_kernel(ConfDev p) {
-  const int k = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, k = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (k >= p.gamma) return;
   if (p.state) { StepStateView st{p.state, p.t_max, p.g}; if (st.done()) return; }
-  float acc = 0.0f;
-  for (int i = lane; i < p.n_hidden; i += 32) acc = __fmaf_rn(__uint_as_float(static_cast<uint32_t>(__ldg(p.hidden + static_cast<int64_t>(k) * p.n_hidden + i)) << 16), __ldg(p.w + i), acc);
-  for (int i = lane; i < p.rank; i += 32) acc = __fmaf_rn(__uint_as_float(static_cast<uint32_t>(__ldg(p.emb + static_cast<int64_t>(k) * p.rank + i)) << 16), __ldg(p.w + p.n_hidden + i), acc);
+  float dot = lane_dot_bf16(p.hidden + static_cast<int64_t>(k) * p.n_hidden, p.w, p.n_hidden, lane, 0.0f);
+  dot = lane_dot_bf16(p.emb + static_cast<int64_t>(k) * p.rank, p.w + p.n_hidden, p.rank, lane, dot);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(kFull, acc, o));
-  if (lane == 0) {
-    const float z = round_bf16(__fadd_rn(round_bf16(acc), p.b[0]));
-    const float x = __fdiv_rn(z, p.sts ? p.sts[k] : 1.0f);
-    const float e = spec_exp2(__fmul_rn(-fabsf(x), 1.44269502f));          // exp(-|x|), in (0, 1]
-    p.conf[k] = x >= 0.0f ? __fdiv_rn(1.0f, __fadd_rn(1.0f, e)) : __fdiv_rn(e, __fadd_rn(1.0f, e));
-  }
+  for (int o = 16; o > 0; o >>= 1) dot = __fadd_rn(dot, __shfl_xor_sync(kFull, dot, o));
+  if (lane != 0) return;
+  const float logit = __fdiv_rn(round_bf16(__fadd_rn(round_bf16(dot), p.b[0])), p.sts ? p.sts[k] : 1.0f);
+  const float e = spec_exp2(__fmul_rn(-fabsf(logit), 1.44269502f));        // exp(-|logit|) in (0, 1]: no overflow on either side
+  p.conf[k] = __fdiv_rn(logit >= 0.0f ? 1.0f : e, __fadd_rn(1.0f, e));
 }
 
 }  // namespace lm

@@ -1,83 +1,77 @@
-// DSpark verification of one speculative step in ONE launch: n_draft drafted tokens against n_draft + 1 rows of
-// target logits. Greedy: row-wise argmax and prefix match (kernels/common/spec_ops.metal:162-165). Stochastic:
-// accept draft r with probability min(1, p/q), replace the first rejected one by a draw from max(p - q, 0)
-// (kernels/common/sample.metal:273-347), on the integer fixed-point weights so the outcome is independent of how the
-// vocabulary is split between blocks.
+// DSpark verification of one speculative step in ONE launch: up to n_draft drafted tokens against n_draft + 1 rows of target
+// logits. Greedy: row-wise argmax and prefix match (kernels/common/spec_ops.metal:162-165). Stochastic: accept draft r with
+// probability min(1, p/q), replace the first rejected one by a draw from max(p - q, 0) (kernels/common/sample.metal:273-347),
+// on the integer fixed-point weights so the outcome is independent of how the vocabulary is split between blocks.
 //
-// The step is latency-bound (a few MB of input, a chain of three data dependencies), so the kernel is one
-// cooperative launch of one block per SM; every block owns the same vocabulary slice of every row in every phase.
-// Phase 0 is the only one that touches HBM: it pulls the block's slice of all target rows and all draft-probability
-// rows into shared memory (one pass over both inputs, every load in flight at once); the later phases work from
-// there. Partial results meet in a small workspace, and the phases are separated by a bounded grid barrier on a
-// counter in that workspace.
+// The step is latency-bound (a few MB of input, a chain of three data dependencies: row maxima -> row masses and the accept
+// test -> the residual's total -> the token), so the kernel is one cooperative launch of one block per SM; every block owns the
+// same vocabulary slice of every row in every phase. Phase 0 is the only one that touches HBM: it pulls the block's slice of
+// all target rows and all draft rows into shared memory (every load in flight at once); the later phases work from there.
+//
+// Blocks exchange their partial results through TAGGED WORDS in a small workspace: every partial is one 64-bit word whose top
+// bit says "written". A block publishes with one plain store per word and consumes by polling the words it needs, so a
+// dependency costs one trip to L2 and back -- no counter, no fence, no second read. The workspace starts all zero; the last
+// block to leave zeroes what the launch wrote. Every poll is bounded: when it runs out the launch reports an error through its
+// outputs (and through the StepState when it commits); the GPU is never left waiting.
+//
+// With a StepState given, the kernel takes the round from it on the device, as the reference's kernels do
+// (kernels/common/sample.metal:283-296): verify length, drafts (pending_tokens), seed, step, and it leaves at once when the
+// state is done. The accept uniforms then come from the reference's stream 3000 + r of the counter-based noise.
 #pragma once
 #include "common.cuh"
 #include "spec_ops.cuh"
 
 namespace lm {
 
-#ifndef LM_VERIFY_BLOCK
-#define LM_VERIFY_BLOCK 1024
-#endif
-constexpr int kVerifyBlock = LM_VERIFY_BLOCK;
+constexpr int kVerifyBlock = 1024;
+constexpr int kVerifyWarps = kVerifyBlock / 32;
 constexpr int kVerifyMaxRows = LM_MAX_DRAFT + 1;
-constexpr unsigned kBarrierSpinLimit = 1u << 22;       // ~ tens of ms: far beyond any legitimate wait
+constexpr int kVerifyMaxGrid = 1024;                    // far above any SM count
+constexpr unsigned kVerifyWaitLimit = 1u << 17;         // polls of one word before a wait gives up: about 0.1 s
+constexpr unsigned long long kTagged = 1ull << 63;
 
-struct VerifyWs {                                       // lives in the caller's workspace, zero-filled once
-  unsigned barrier;                                     // arrivals; returns to 0 when the launch ends
-  unsigned exits;
-  unsigned error;                                       // sticky: 1 = a barrier wait ran out
-  unsigned pad;
-  unsigned long long row_best[kVerifyMaxRows];          // packed (max logit, lowest index) per row
-  unsigned long long row_mass[kVerifyMaxRows];          // fixed-point mass of the kept set per row
-  unsigned long long draft_w[kVerifyMaxRows];           // fixed-point weight of draft r in row r (0 if not kept)
-  unsigned long long rival[kVerifyMaxRows];             // draft-side sampling: the best Gumbel key that lost (monotone code)
-  // followed by: unsigned long long part_w[kVerifyMaxRows][grid], part_r[grid]
+struct VerifyWs {                                       // lives in the caller's workspace, zero-filled once, left all zero by every launch
+  unsigned exits;                                       // blocks that have left
+  unsigned error;                                       // a wait of this launch ran out
+  unsigned pad[2];
+  unsigned long long draft_w[kVerifyMaxRows];           // tagged: fixed-point weight of draft r in row r (0 if not kept)
+  unsigned long long best[kVerifyMaxRows][kVerifyMaxGrid];   // tagged: per row and block, the slice's packed (max logit, lowest index)
+  unsigned long long mass[kVerifyMaxRows][kVerifyMaxGrid];   // tagged: per row and block, the slice's fixed-point mass
+  unsigned long long resid[2][kVerifyMaxGrid];          // tagged: per block, the slice's residual mass / its best draw keys
 };
 
 struct VerifyDev {
-  int mode; int dtype; int n_draft; int vocab; int64_t row_stride;
+  int mode; int dtype; int n_draft; int vocab; int64_t row_stride; int draw;
   const void* target; const int32_t* drafts; const float* q; int64_t q_stride; float temperature;
   const uint16_t* q_logits; int64_t q_logits_stride; const float* q_vmax; const unsigned long long* q_mass;   // q from the drafter's BF16 logits when q is null
   const float* tau; const float* u_accept; const float* u_final;
+  uint64_t seed; uint32_t step;
   int32_t* out_accept; int32_t* out_final; int32_t* out_tokens; float* out_p_draft;
   VerifyWs* ws;
+  uint32_t* state; int t_max, g;                          // StepState (optional): the round is read from it
   int commit; AcceptDev accept;                          // commit != 0: close the round on the StepState as accept_scan would
+  unsigned wait_limit; unsigned withhold;                // self-test of the bounded waits: block 0 publishes no row maxima
 };
 
-// The round's bookkeeping, by the thread that has just written out_tokens: the accept scan on those tokens
-// (kernels/common/spec_ops.metal:148-195). The verify rows must be the step's rows (a decode round: t_this_step = verify_len + 1
-// = n_draft + 1); a prefill chunk takes the scan's prefill branch, which reads no token; anything else is a caller error and
-// ends the generation with error code 4.
-__device__ __forceinline__ void verify_commit(const VerifyDev& P) {
-  if (!P.commit) return;
-  StepStateView st{P.accept.state, P.accept.t_max, P.accept.g};
-  if (!st.done() && P.ws->error != 0u) { st.error() = 3u; st.done() = 1u; return; }   // a grid barrier of this launch ran out: nothing to commit
-  if (!st.done() && st.prefill_left() == 0u && (st.verify_len() != static_cast<uint32_t>(P.n_draft) || st.t_this_step() != static_cast<uint32_t>(P.n_draft) + 1u)) {
-    st.error() = 4u; st.done() = 1u;
-    return;
-  }
-  __threadfence();
-  accept_scan_body(P.accept);
-}
+// ---- tagged words ------------------------------------------------------------------------------------------------------------
+// The 52-bit packed (value, lowest index) of the row maxima: indices stay below 2^20 (LM_MAX_VOCAB).
+__device__ __forceinline__ uint64_t pack52(float v, uint32_t idx) { return (static_cast<uint64_t>(fkey(v)) << 20) | (0xFFFFFu - idx); }
+__device__ __forceinline__ float pack52_value(uint64_t p) { return fkey_inv(static_cast<uint32_t>(p >> 20)); }
+__device__ __forceinline__ uint32_t pack52_index(uint64_t p) { return 0xFFFFFu - static_cast<uint32_t>(p & 0xFFFFFu); }
 
-// Every block arrives, then waits until `target` arrivals are visible. Bounded: on time-out the error word is set and
-// the block carries on (its results are then meaningless, the host sees the error).
-__device__ __forceinline__ void grid_barrier(VerifyWs* ws, unsigned target) {
-  __syncthreads();                                                        // the block's writes happen-before thread 0's release below
-  if (threadIdx.x == 0) {
-    unsigned seen = 0, spins = 0;
-    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&ws->barrier) : "memory");
-    do {
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(&ws->barrier) : "memory");
-      if (seen >= target) break;
-      if (++spins > kBarrierSpinLimit) { atomicExch(&ws->error, 1u); break; }
-    } while (true);
-  }
-  __syncthreads();
+__device__ __forceinline__ void publish(unsigned long long* p, uint64_t v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(static_cast<unsigned long long>(v) | kTagged) : "memory");
 }
-
-__device__ __forceinline__ uint64_t ws_load(const unsigned long long* p) { return __ldcg(p); }
+// Polls one word until its tag is set; gives up after `limit` polls (then *failed is set and 0 returned).
+__device__ __forceinline__ uint64_t consume(const unsigned long long* p, unsigned limit, bool* failed) {
+  unsigned long long v;
+  for (unsigned spins = 0;; spins++) {
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    if (v & kTagged) return v & ~kTagged;
+    if (spins >= limit) { *failed = true; return 0ull; }
+    if (spins > 4u) __nanosleep(40);
+  }
+}
 
 __device__ __forceinline__ float verify_load(const VerifyDev& P, int row, int i) {
   const char* base = static_cast<const char*>(P.target);
@@ -96,56 +90,124 @@ __device__ __forceinline__ float verify_q(const VerifyDev& P, int r, int i, floa
   return q_from_code(__ldg(P.q_logits + static_cast<int64_t>(r) * P.q_logits_stride + i), __ldg(P.q_vmax + r), __ldg(P.q_mass + r), c2);
 }
 
-// The block's view of its slice: shared-memory copies when they fit, global memory otherwise.
+// The block's view of its slice: shared-memory copies when they fit, global memory otherwise. Target rows are step rows
+// (row0 + r), draft rows are draft positions r.
 struct VerifySlice {
-  const VerifyDev* P; const float* zs; const float* qs; int per, lo; float c2;
-  __device__ __forceinline__ float z(int r, int i) const { return zs ? zs[r * per + i] : verify_load(*P, r, lo + i); }
+  const VerifyDev* P; const float* zs; const float* qs; int per, lo, row0; float c2;
+  __device__ __forceinline__ float z(int r, int i) const { return zs ? zs[r * per + i] : verify_load(*P, row0 + r, lo + i); }
   __device__ __forceinline__ float q(int r, int i) const { return qs ? qs[r * per + i] : verify_q(*P, r, lo + i, c2); }
 };
 
-#ifdef LM_PROFILE_PHASES
-__device__ unsigned long long g_verify_times[8];
-#define LM_VSTAMP(i) do { if (threadIdx.x == 0 && blockIdx.x == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_verify_times[i] = _t; } } while (0)
-#else
-#define LM_VSTAMP(i) do {} while (0)
-#endif
+// The round's bookkeeping, by the warp whose lane 0 has just written out_tokens: the accept scan on those tokens
+// (kernels/common/spec_ops.metal:148-195). A prefill chunk takes the scan's prefill branch, which reads no token. All 32 lanes call.
+__device__ __forceinline__ void verify_commit(const VerifyDev& P, bool failed) {
+  if (!P.commit) return;
+  __syncwarp();
+  StepStateView st{P.accept.state, P.accept.t_max, P.accept.g};
+  if (st.done()) return;
+  if (failed) { if ((threadIdx.x & 31) == 0) fail_state(st, kErrBarrier); return; }   // a wait of this launch ran out: nothing to commit
+  if (!P.state && st.prefill_left() == 0u && (st.verify_len() != static_cast<uint32_t>(P.n_draft) || st.t_this_step() != static_cast<uint32_t>(P.n_draft) + 1u)) {
+    if ((threadIdx.x & 31) == 0) fail_state(st, kErrRoundMismatch);        // the round came from the arguments and the state describes another
+    return;
+  }
+  __threadfence();
+  round_close(P.accept);
+}
+
+constexpr int kConsumeSlots = 4;                        // words one thread may hold: rows x grid (rounded up to 32) <= 4096
+
+// Consumes words[r][g] for r < R, g < G (row stride kVerifyMaxGrid) and reduces each row over g (SUM false: maximum, true:
+// sum) into out[r] (shared memory). Warps take 32 consecutive blocks of one row at a time. The values a thread consumed stay
+// in vals[] (0 where it had none), vals[k] belonging to word k * kVerifyBlock + tid of the R x Gp index space. Every thread calls.
+template <bool SUM>
+__device__ __forceinline__ void consume_rows(const unsigned long long* words, int R, int G, unsigned long long* out, uint64_t (*red)[32],
+                                             unsigned limit, bool* failed, uint64_t vals[kConsumeSlots]) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int Gp = (G + 31) & ~31, n = R * Gp;
+#pragma unroll
+  for (int k = 0; k < kConsumeSlots; k++) {
+    const int idx = k * kVerifyBlock + tid, r = idx / Gp, g = idx - r * Gp;
+    uint64_t v = 0ull;
+    if (idx < n && g < G) v = consume(words + static_cast<size_t>(r) * kVerifyMaxGrid + g, limit, failed);
+    vals[k] = v;
+    if (k * kVerifyBlock < n) {                                           // block-uniform
+      const uint64_t w = SUM ? warp_sum_u64(v) : warp_max_u64(v);
+      if (lane == 0 && idx < n) red[r][g >> 5] = w;
+    }
+  }
+  __syncthreads();
+  if (tid < R) {
+    uint64_t acc = 0ull;
+    for (int k = 0; k < Gp / 32; k++) { const uint64_t x = red[tid][k]; acc = SUM ? acc + x : (x > acc ? x : acc); }
+    out[tid] = acc;
+  }
+  __syncthreads();
+}
 
 __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, int cached) {
   extern __shared__ __align__(16) float v_smem[];
   __shared__ uint64_t scratch[32];
-  __shared__ int s_j, s_token;
+  __shared__ uint64_t s_red[kVerifyMaxRows][32];
+  __shared__ int s_j, s_token, s_last;
   __shared__ int s_drafts[kVerifyMaxRows];
-  __shared__ unsigned long long s_best[kVerifyMaxRows], s_mass[kVerifyMaxRows];
+  __shared__ unsigned long long s_best[kVerifyMaxRows], s_mass[kVerifyMaxRows], s_own[kVerifyMaxRows];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, G = gridDim.x, b = blockIdx.x;
-  constexpr int kWarps = kVerifyBlock / 32;
-  const int R = P.n_draft + 1, V = P.vocab;
+  const int V = P.vocab;
   const bool stochastic = P.mode == LM_VERIFY_STOCHASTIC;
+  const bool gumbel_draw = stochastic && P.draw == LM_DRAW_GUMBEL;
   VerifyWs* ws = P.ws;
-  unsigned long long* part_w = reinterpret_cast<unsigned long long*>(ws + 1);   // [kVerifyMaxRows][G]
-  unsigned long long* part_r = part_w + static_cast<size_t>(kVerifyMaxRows) * G; // [G]
+  const unsigned limit = P.wait_limit ? P.wait_limit : kVerifyWaitLimit;
+  bool failed = false;
+
+  // ---- the round: from the arguments, or from the StepState ---------------------------------------------------------------
+  int L = P.n_draft, row0 = 0;
+  uint64_t seed = P.seed; uint32_t step = P.step;
+  bool idle = false, mismatch = false;                                    // idle: the state is done, or this step is a prefill chunk
+  bool prefill = false;
+  if (P.state) {
+    StepStateView st{P.state, P.t_max, P.g};
+    if (st.done()) idle = true;
+    else if (st.prefill_left() > 0u) { idle = true; prefill = true; }
+    else {
+      const uint32_t len = st.verify_len(), rows = st.t_this_step();
+      if (len > static_cast<uint32_t>(P.n_draft) || rows < len + 1u || rows > static_cast<uint32_t>(P.n_draft) + 1u) mismatch = true;
+      else { L = static_cast<int>(len); row0 = static_cast<int>(rows - 1u - len); }
+    }
+    seed = st.seed(); step = st.step();
+  }
+  const int R = L + 1;
+  if (idle || mismatch) {
+    // nothing is verified; block 0 still closes a prefill chunk (the scan's prefill branch) or reports the caller's error
+    if (b == 0 && warp == 0) {
+      if (mismatch) {
+        if (lane == 0) { P.out_accept[0] = -1; P.out_final[0] = -1; StepStateView st{P.state, P.t_max, P.g}; fail_state(st, kErrRoundMismatch); }
+      } else if (prefill) verify_commit(P, false);
+    }
+  } else {
   // this block's vocabulary slice, a multiple of 8 elements
   const int per = ((V + G - 1) / G + 7) & ~7;
   const int lo = min(V, b * per), hi = min(V, lo + per);
   const int len = hi - lo;
-  LM_VSTAMP(0);
   float* zs = cached ? v_smem : nullptr;
-  float* qs = (cached && stochastic) ? v_smem + R * per : nullptr;
+  float* qs = (cached && stochastic) ? v_smem + (P.n_draft + 1) * per : nullptr;
   const float c2 = stochastic ? exp2_scale(P.temperature) : 0.0f;
-  VerifySlice S{&P, zs, qs, per, lo, c2};
+  VerifySlice S{&P, zs, qs, per, lo, row0, c2};
 
-  // ---- phase 0: the only HBM pass. Slices of every target row and every draft-probability row into shared memory,
-  // then row maxima with their lowest index (which is also the greedy pick).
-  // the scalars the accept test needs later are fetched now, so their latency hides behind the slice loads
+  // ---- phase 0: the only HBM pass. Slices of every target row and every draft row into shared memory.
+  // The scalars the accept test needs later are fetched now, so their latency hides behind the slice loads.
   int my_draft = -1; float my_q = 0.0f, my_u = 0.0f;
-  if (tid < P.n_draft) { my_draft = P.drafts[tid]; s_drafts[tid] = my_draft; }
-  if (stochastic && tid < P.n_draft) {
-    my_u = P.u_accept[tid];
+  if (tid < L) {
+    my_draft = P.state ? StepStateView{P.state, P.t_max, P.g}.pending(row0 + tid + 1) : P.drafts[tid];
+    s_drafts[tid] = my_draft;
+  }
+  if (stochastic && tid < L) {
+    my_u = P.u_accept ? P.u_accept[tid] : uniform01(seed, step, 3000u + static_cast<uint32_t>(tid), 0u);
     if (my_draft >= 0 && my_draft < V) my_q = verify_q(P, tid, my_draft, c2);
   }
   if (cached) {
     // 8 elements per load item (one 16-byte load of BF16 logits, two of FP32 logits or draft probabilities), every item of
     // a thread issued before the first is used: the whole slice arrives in one memory round trip
-    const int n_q = stochastic ? P.n_draft : 0;
+    const int n_q = stochastic ? L : 0;
     const int chunks = (len + 7) / 8;
     const bool z_vec = (P.dtype == LM_DTYPE_BF16 ? (P.row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(P.target) & 15u) == 0)
                                                  : (P.row_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(P.target) & 15u) == 0));
@@ -164,10 +226,10 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
         const bool full = c8 + 8 <= len;
         if (r < R) {
           if (P.dtype == LM_DTYPE_BF16) {
-            const uint16_t* src = reinterpret_cast<const uint16_t*>(P.target) + static_cast<int64_t>(r) * P.row_stride + lo + c8;
+            const uint16_t* src = reinterpret_cast<const uint16_t*>(P.target) + static_cast<int64_t>(row0 + r) * P.row_stride + lo + c8;
             if (full && z_vec) va[k] = __ldg(reinterpret_cast<const float4*>(src));      // eight BF16 codes, widened below
           } else {
-            const float* src = reinterpret_cast<const float*>(P.target) + static_cast<int64_t>(r) * P.row_stride + lo + c8;
+            const float* src = reinterpret_cast<const float*>(P.target) + static_cast<int64_t>(row0 + r) * P.row_stride + lo + c8;
             if (full && z_vec) { va[k] = __ldg(reinterpret_cast<const float4*>(src)); vb[k] = __ldg(reinterpret_cast<const float4*>(src) + 1); }
           }
         } else if (P.q) {
@@ -188,7 +250,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
         const bool vec = full && (r < R ? z_vec : q_vec);
         if (!vec) {                                                       // a ragged last chunk or an unaligned tensor: element by element
           for (int e = 0; e < 8 && c8 + e < len; e++)
-            dst[e] = r < R ? verify_load(P, r, lo + c8 + e) : verify_q(P, r - R, lo + c8 + e, c2);
+            dst[e] = r < R ? verify_load(P, row0 + r, lo + c8 + e) : verify_q(P, r - R, lo + c8 + e, c2);
           continue;
         }
         float4 x = va[k], y = vb[k];
@@ -212,177 +274,215 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     }
     __syncthreads();
   }
-  LM_VSTAMP(1);
-  // every row is shared by `split` warps; their partial results meet in the workspace through atomics
-  const int split = max(1, kWarps / R);
-  for (int item = warp; item < R * split; item += kWarps) {
+  // ---- row maxima of the slice (lowest index on ties: the greedy pick), published one word per row -----------------------
+  // every row is shared by `split` warps
+  const int split = max(1, kVerifyWarps / R);
+  for (int item = warp; item < R * split; item += kVerifyWarps) {
     const int r = item / split, part = item - r * split;
     uint64_t best = 0ull;
     for (int i = part * 32 + lane; i < len; i += 32 * split) {
-      const uint64_t p = pack_best(S.z(r, i), static_cast<uint32_t>(lo + i));
+      const uint64_t p = pack52(S.z(r, i), static_cast<uint32_t>(lo + i));
       best = p > best ? p : best;
     }
     best = warp_max_u64(best);
-    if (lane == 0 && best) atomicMax(&ws->row_best[r], static_cast<unsigned long long>(best));
+    if (lane == 0) s_red[r][part] = best;
   }
-  LM_VSTAMP(2);
-  grid_barrier(ws, 1u * G);
-  LM_VSTAMP(3);
+  __syncthreads();
+  if (tid < R && !(P.withhold && b == 0)) {
+    uint64_t best = 0ull;
+    for (int k = 0; k < split; k++) best = s_red[tid][k] > best ? s_red[tid][k] : best;
+    publish(&ws->best[tid][b], best);
+  }
+  __syncthreads();                                                        // s_red is reused below
 
+  uint64_t vals[kConsumeSlots];
+  const int Gp = (G + 31) & ~31;
   if (!stochastic) {
-    if (b == 0 && tid < 32) {                                              // one round trip for every row's pick, then a vote
-      const int pick = tid < R ? static_cast<int>(best_index(ws_load(&ws->row_best[tid]))) : -1;
-      const uint32_t miss = __ballot_sync(kFull, tid < P.n_draft && pick != s_drafts[tid]);
-      const int acc = miss ? (__ffs(miss) - 1) : P.n_draft;
-      const int fin = __shfl_sync(kFull, pick, acc);
-      const bool bad = ws->error != 0;
-      if (tid == 0) { P.out_accept[0] = bad ? -1 : acc; P.out_final[0] = bad ? -1 : fin; }
-      if (P.out_tokens && tid < R) P.out_tokens[tid] = tid < acc ? s_drafts[tid] : (tid == acc ? fin : -1);
-      __syncwarp();
-      if (tid == 0) verify_commit(P);
-    }
-    // the last block to leave puts the workspace back to its clean state
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence();
-      if (atomicAdd(&ws->exits, 1u) == static_cast<unsigned>(G) - 1u) {
-        for (int r = 0; r < R; r++) ws->row_best[r] = 0ull;
-        ws->exits = 0u; __threadfence(); ws->barrier = 0u;
+    // ---- greedy: block 0 gathers every row's pick and votes; the others are done --------------------------------------------
+    if (b == 0) {
+      consume_rows<false>(&ws->best[0][0], R, G, s_best, s_red, limit, &failed, vals);
+      const bool bad = __syncthreads_or(failed) != 0;
+      if (bad && tid == 0) atomicExch(&ws->error, 1u);
+      if (tid < 32) {
+        const int pick = tid < R ? static_cast<int>(pack52_index(s_best[tid])) : -1;
+        const uint32_t miss = __ballot_sync(kFull, tid < L && pick != s_drafts[tid]);
+        const int acc = miss ? (__ffs(miss) - 1) : L;
+        const int fin = __shfl_sync(kFull, pick, acc);
+        if (tid == 0) { P.out_accept[0] = bad ? -1 : acc; P.out_final[0] = bad ? -1 : fin; }
+        if (P.out_tokens && tid < R) P.out_tokens[row0 + tid] = bad ? -1 : (tid < acc ? s_drafts[tid] : (tid == acc ? fin : -1));
+        verify_commit(P, bad);
       }
     }
-    return;
-  }
-
-  // ---- phase 1: fixed-point mass of every row's kept set; the drafts' own weights -----------------------------------
-  if (tid < R) part_w[static_cast<size_t>(tid) * G + b] = 0ull;
-  __syncthreads();
-  for (int item = warp; item < R * split; item += kWarps) {
-    const int r = item / split, part = item - r * split;
-    const float vmax = best_value(ws_load(&ws->row_best[r]));
-    const float tau = P.tau ? P.tau[r] : -INFINITY;
-    uint64_t w = 0ull;
-    for (int i = part * 32 + lane; i < len; i += 32 * split) {
-      const float z = S.z(r, i);
-      if (z >= tau) w += weight_q40(z, vmax, c2);
-    }
-    w = warp_sum_u64(w);
-    if (lane == 0) {
-      if (w) { atomicAdd(&part_w[static_cast<size_t>(r) * G + b], static_cast<unsigned long long>(w)); atomicAdd(&ws->row_mass[r], static_cast<unsigned long long>(w)); }
-      if (part == 0 && r < P.n_draft) {
-        const int d = s_drafts[r];
-        if (d >= lo && d < hi) {
-          const float z = S.z(r, d - lo);
-          ws->draft_w[r] = (z >= tau) ? weight_q40(z, vmax, c2) : 0ull;
+  } else {
+    // ---- phase 1: every block learns the row maxima; fixed-point mass of every row's kept set; the drafts' own weights -------
+    consume_rows<false>(&ws->best[0][0], R, G, s_best, s_red, limit, &failed, vals);
+    for (int item = warp; item < R * split; item += kVerifyWarps) {
+      const int r = item / split, part = item - r * split;
+      const float vmax = pack52_value(s_best[r]);
+      const float tau = P.tau ? P.tau[row0 + r] : -INFINITY;
+      uint64_t w = 0ull;
+      for (int i = part * 32 + lane; i < len; i += 32 * split) {
+        const float z = S.z(r, i);
+        if (z >= tau) w += weight_q40(z, vmax, c2);
+      }
+      w = warp_sum_u64(w);
+      if (lane == 0) {
+        s_red[r][part] = w;
+        if (part == 0 && r < L) {
+          const int d = s_drafts[r];
+          if (d >= lo && d < hi) {
+            const float z = S.z(r, d - lo);
+            publish(&ws->draft_w[r], (z >= tau) ? weight_q40(z, vmax, c2) : 0ull);
+          } else if ((d < 0 || d >= V) && b == 0) publish(&ws->draft_w[r], 0ull);   // an id outside the vocabulary: probability 0
         }
       }
     }
-  }
-  LM_VSTAMP(4);
-  grid_barrier(ws, 2u * G);
-  LM_VSTAMP(5);
-
-  // ---- phase 2: accept tests (every block, identically), then this slice's share of the residual mass -----------
-  if (tid < 32) {                                                           // every row's maximum and mass in one round trip
-    uint64_t best = 0ull, mass = 0ull, dw = 0ull;
-    if (tid < R) { best = ws_load(&ws->row_best[tid]); mass = ws_load(&ws->row_mass[tid]); }
-    if (tid < P.n_draft) dw = ws_load(&ws->draft_w[tid]);
-    if (tid < R) { s_best[tid] = best; s_mass[tid] = mass; }
-    bool reject = false;
-    if (tid < P.n_draft) {
-      const int r = tid, d = my_draft;
-      const float pd = (d >= 0 && d < V && mass > 0ull) ? prob_q40(dw, mass) : 0.0f;
-      reject = __fmul_rn(my_u, my_q) >= pd;
-      if (b == 0 && P.out_p_draft) P.out_p_draft[r] = pd;
+    __syncthreads();
+    if (tid < R) {
+      uint64_t w = 0ull;
+      for (int k = 0; k < split; k++) w += s_red[tid][k];
+      s_own[tid] = w;
+      publish(&ws->mass[tid][b], w);
     }
-    const uint32_t rejects = __ballot_sync(kFull, reject);
-    if (tid == 0) s_j = rejects ? (__ffs(rejects) - 1) : P.n_draft;
-  }
-  __syncthreads();
-  const int j = s_j;
-  const float vmax_j = best_value(s_best[j]);
-  const float tau_j = P.tau ? P.tau[j] : -INFINITY;
-  const uint64_t mass_j = s_mass[j];
-  const bool has_q = j < P.n_draft;
-  // residual weight of element i of this slice (0 when not kept or not positive)
-  auto residual = [&](int i) -> uint64_t {
-    const float z = S.z(j, i);
-    if (!(z >= tau_j)) return 0ull;
-    const float p = prob_q40(weight_q40(z, vmax_j, c2), mass_j);
-    const float res = has_q ? __fsub_rn(p, S.q(j, i)) : p;
-    return res > 0.0f ? residual_q40(res) : 0ull;
-  };
-  {
-    uint64_t w = 0ull;
-    if (mass_j > 0ull) for (int i = tid; i < len; i += kVerifyBlock) w += residual(i);
-    w = block_sum_u64(w, scratch);
-    if (tid == 0) part_r[b] = w;
-  }
-  LM_VSTAMP(6);
-  grid_barrier(ws, 3u * G);
-  LM_VSTAMP(7);
-
-  // ---- phase 3: locate the draw; the block whose slice holds it writes the outputs -------------------------------
-  {
-    // totals and this block's exclusive prefix over the per-block partials, for the residual and for the row's own mass
-    uint64_t tot_r = 0ull, pre_r = 0ull, pre_w = 0ull;
-    for (int g = tid; g < G; g += kVerifyBlock) {
-      const uint64_t vr = ws_load(&part_r[g]), vw = ws_load(&part_w[static_cast<size_t>(j) * G + g]);
-      tot_r += vr;
-      if (g < b) { pre_r += vr; pre_w += vw; }
+    __syncthreads();
+    // ---- phase 2: row masses; accept tests (every block, identically); this slice's share of the residual -------------------
+    consume_rows<true>(&ws->mass[0][0], R, G, s_mass, s_red, limit, &failed, vals);
+    if (tid < 32) {
+      bool reject = false;
+      if (tid < L) {
+        const uint64_t dw = consume(&ws->draft_w[tid], limit, &failed), mass = s_mass[tid];
+        const float pd = (my_draft >= 0 && my_draft < V && mass > 0ull) ? prob_q40(dw, mass) : 0.0f;
+        reject = __fmul_rn(my_u, my_q) >= pd;
+        if (b == 0 && P.out_p_draft) P.out_p_draft[tid] = pd;
+      }
+      const uint32_t rejects = __ballot_sync(kFull, reject);
+      if (tid == 0) s_j = rejects ? (__ffs(rejects) - 1) : L;
     }
-    {                                                                     // three sums, one pair of barriers
-      __shared__ uint64_t sums[3][32];
-      tot_r = warp_sum_u64(tot_r); pre_r = warp_sum_u64(pre_r); pre_w = warp_sum_u64(pre_w);
-      if (lane == 0) { sums[0][warp] = tot_r; sums[1][warp] = pre_r; sums[2][warp] = pre_w; }
+    __syncthreads();
+    const int j = s_j;
+    const float vmax_j = pack52_value(s_best[j]);
+    const float tau_j = P.tau ? P.tau[row0 + j] : -INFINITY;
+    const uint64_t mass_j = s_mass[j];
+    const bool has_q = j < L;
+    // this block's exclusive prefix over the blocks' masses of row j (the draw over p itself needs it)
+    uint64_t pre_w = 0ull;
+#pragma unroll
+    for (int k = 0; k < kConsumeSlots; k++) {
+      const int idx = k * kVerifyBlock + tid, r = idx / Gp, g = idx - r * Gp;
+      if (r == j && g < b) pre_w += vals[k];
+    }
+    pre_w = block_sum_u64(pre_w, scratch);
+    // residual weight of element i of this slice (0 when not kept or not positive)
+    auto residual = [&](int i) -> uint64_t {
+      const float z = S.z(j, i);
+      if (!(z >= tau_j)) return 0ull;
+      const float p = prob_q40(weight_q40(z, vmax_j, c2), mass_j);
+      const float res = has_q ? __fsub_rn(p, S.q(j, i)) : p;
+      return res > 0.0f ? residual_q40(res) : 0ull;
+    };
+    const uint32_t t_row = static_cast<uint32_t>(row0 + j);
+    const float inv_t32 = __double2float_rn(1.0 / static_cast<double>(P.temperature));
+    uint64_t total_r = 0ull, pre_r = 0ull, mine_r = 0ull;
+    int token = -2;
+    if (gumbel_draw) {
+      // the reference's draws (kernels/common/sample.metal:322-346): argmax of ln(p - q) + noise of stream 4000 over the positive
+      // residual; with nothing rejected, or an empty residual, the row's own Gumbel-max draw on its stream (the sampler's token)
+      uint64_t best_res = 0ull, best_own = 0ull;
+      if (mass_j > 0ull) for (int i = tid; i < len; i += kVerifyBlock) {
+        const float z = S.z(j, i);
+        if (!(z >= tau_j)) continue;
+        const uint32_t idx = static_cast<uint32_t>(lo + i);
+        const uint64_t own = pack52(__fadd_rn(__fmul_rn(z, inv_t32), gumbel(seed, step, t_row, idx)), idx);
+        best_own = own > best_own ? own : best_own;
+        if (has_q) {
+          const float res = __fsub_rn(prob_q40(weight_q40(z, vmax_j, c2), mass_j), S.q(j, i));
+          if (res > 0.0f) { const uint64_t k = pack52(__fadd_rn(logf(res), gumbel(seed, step, 4000u, idx)), idx); best_res = k > best_res ? k : best_res; }
+        }
+      }
+      best_res = block_max_u64(best_res, scratch);
+      best_own = block_max_u64(best_own, scratch);
+      if (tid == 0) { publish(&ws->resid[0][b], best_res); publish(&ws->resid[1][b], best_own); }
+      if (b == 0) {                                                       // block 0 gathers the blocks' best keys
+        uint64_t kr = 0ull, ko = 0ull;
+        for (int g = tid; g < G; g += kVerifyBlock) {
+          const uint64_t a = consume(&ws->resid[0][g], limit, &failed), c = consume(&ws->resid[1][g], limit, &failed);
+          kr = a > kr ? a : kr; ko = c > ko ? c : ko;
+        }
+        kr = block_max_u64(kr, scratch); ko = block_max_u64(ko, scratch);
+        token = kr ? static_cast<int>(pack52_index(kr)) : (ko ? static_cast<int>(pack52_index(ko)) : -1);
+      }
+    } else if (has_q) {
+      // ---- the residual's total: one more exchange (skipped when every draft was accepted: the bonus row draws from p) --------
+      uint64_t w = 0ull;
+      if (mass_j > 0ull) for (int i = tid; i < len; i += kVerifyBlock) w += residual(i);
+      mine_r = block_sum_u64(w, scratch);
+      if (tid == 0) publish(&ws->resid[0][b], mine_r);
+      uint64_t tr = 0ull, pr = 0ull;
+      for (int g = tid; g < G; g += kVerifyBlock) { const uint64_t v = consume(&ws->resid[0][g], limit, &failed); tr += v; if (g < b) pr += v; }
+      total_r = block_sum_u64(tr, scratch); pre_r = block_sum_u64(pr, scratch);
+    }
+    const bool bad = __syncthreads_or(failed) != 0;
+    if (bad && tid == 0) atomicExch(&ws->error, 1u);
+
+    // ---- phase 3: locate the draw; the block whose slice holds it writes the outputs ---------------------------------------
+    bool writer = false;
+    if (gumbel_draw) {
+      writer = b == 0;
+    } else {
+      const bool use_res = total_r > 0ull;                               // an empty residual: draw from the row's own kept softmax
+      const uint64_t total = use_res ? total_r : mass_j;
+      const uint64_t own = use_res ? mine_r : s_own[j];                   // this block's share of the total
+      const uint64_t pre = use_res ? pre_r : pre_w;
+      if (tid == 0) s_token = -2;
       __syncthreads();
-      tot_r = warp_sum_u64(lane < kWarps ? sums[0][lane] : 0ull);
-      pre_r = warp_sum_u64(lane < kWarps ? sums[1][lane] : 0ull);
-      pre_w = warp_sum_u64(lane < kWarps ? sums[2][lane] : 0ull);
-    }
-    const bool use_res = tot_r > 0ull;                                   // an empty residual: draw from the row's own kept softmax
-    const uint64_t total = use_res ? tot_r : mass_j;
-    const uint64_t mine = use_res ? ws_load(&part_r[b]) : ws_load(&part_w[static_cast<size_t>(j) * G + b]);
-    const uint64_t pre = use_res ? pre_r : pre_w;
-    if (tid == 0) s_token = -2;
-    __syncthreads();
-    if (total > 0ull) {
-      const uint64_t target = cdf_target(P.u_final[0], total);
-      if (mine > 0ull && pre <= target && target < pre + mine) {           // the crossing lies in this block's slice
-        uint64_t base = pre;
-        for (int i0 = 0; i0 < len; i0 += kVerifyBlock) {                  // uniform trip count: block-wide scans inside
-          const int i = i0 + tid;
-          uint64_t w = 0ull;
-          if (i < len) {
-            if (use_res) w = residual(i);
-            else { const float z = S.z(j, i); if (z >= tau_j) w = weight_q40(z, vmax_j, c2); }
+      if (total > 0ull) {
+        const float u = P.u_final ? P.u_final[0] : uniform01(seed, step, 4000u, 0u);
+        const uint64_t target = cdf_target(u, total);
+        if (own > 0ull && pre <= target && target < pre + own) {           // the crossing lies in this block's slice
+          writer = true;
+          uint64_t base = pre;
+          for (int i0 = 0; i0 < len; i0 += kVerifyBlock) {                  // uniform trip count: block-wide scans inside
+            const int i = i0 + tid;
+            uint64_t w = 0ull;
+            if (i < len) {
+              if (use_res) w = residual(i);
+              else { const float z = S.z(j, i); if (z >= tau_j) w = weight_q40(z, vmax_j, c2); }
+            }
+            uint64_t sweep = 0ull;
+            const uint64_t excl = block_exclusive_scan_u64(w, scratch, &sweep);
+            if (w && base + excl <= target && target < base + excl + w) s_token = lo + i;
+            base += sweep;
+            __syncthreads();
+            if (s_token != -2) break;
           }
-          uint64_t sweep = 0ull;
-          const uint64_t excl = block_exclusive_scan_u64(w, scratch, &sweep);
-          if (w && base + excl <= target && target < base + excl + w) s_token = lo + i;
-          base += sweep;
-          __syncthreads();
-          if (s_token != -2) break;
+          token = s_token;
         }
-        if (tid == 0) {
-          const bool bad = ws->error != 0;
-          P.out_accept[0] = bad ? -1 : j; P.out_final[0] = bad ? -1 : s_token;
-          if (P.out_tokens) for (int r = 0; r < R; r++) P.out_tokens[r] = r < j ? P.drafts[r] : (r == j ? s_token : -1);
-          verify_commit(P);
-        }
+      } else if (b == 0) { writer = true; token = -1; }                   // a row with no weight at all (empty or all -inf)
+    }
+    if (bad) writer = b == 0;                                             // a wait ran out: block 0 reports it
+    if (writer && warp == 0) {
+      if (lane == 0) {
+        P.out_accept[0] = bad ? -1 : j; P.out_final[0] = bad ? -1 : token;
+        if (P.out_tokens) for (int r = 0; r < R; r++) P.out_tokens[row0 + r] = bad ? -1 : (r < j ? s_drafts[r] : (r == j ? token : -1));
       }
-    } else if (b == 0 && tid == 0) {                                     // a row with no weight at all (empty or all -inf)
-      P.out_accept[0] = ws->error ? -1 : j; P.out_final[0] = -1;
-      if (P.out_tokens) for (int r = 0; r < R; r++) P.out_tokens[r] = r < j ? P.drafts[r] : -1;
-      verify_commit(P);
+      verify_commit(P, bad);
     }
   }
+  }
+  // ---- the last block to leave puts the workspace back to all zero -------------------------------------------------------------
   __syncthreads();
-  if (tid == 0) {
+  if (tid == 0) { __threadfence(); s_last = atomicAdd(&ws->exits, 1u) == static_cast<unsigned>(G) - 1u; }
+  __syncthreads();
+  if (s_last) {
     __threadfence();
-    if (atomicAdd(&ws->exits, 1u) == static_cast<unsigned>(G) - 1u) {
-      for (int r = 0; r < R; r++) { ws->row_best[r] = 0ull; ws->row_mass[r] = 0ull; ws->draft_w[r] = 0ull; }
-      ws->exits = 0u; __threadfence(); ws->barrier = 0u;
+    for (int i = tid; i < kVerifyMaxRows * G; i += kVerifyBlock) {
+      const int r = i / G, g = i - r * G;
+      ws->best[r][g] = 0ull;
+      if (stochastic) ws->mass[r][g] = 0ull;
     }
+    if (stochastic) for (int g = tid; g < 2 * G; g += kVerifyBlock) ws->resid[g / G][g % G] = 0ull;
+    if (tid < kVerifyMaxRows) ws->draft_w[tid] = 0ull;
+    if (tid == 0) { ws->error = 0u; ws->exits = 0u; }
   }
 }
 

@@ -46,17 +46,32 @@ class SampleOutput:
     status: Optional[torch.Tensor] = None  # int32 [rows] status bits
 
 
-_workspaces: Dict[Tuple[int, str], torch.Tensor] = {}
+_workspaces: Dict[Tuple[int, str, int], torch.Tensor] = {}
 
 
 def _workspace(device: torch.device, nbytes: int, kind: str = "sample") -> torch.Tensor:
-    """A zero-filled scratch buffer per (device, kind), grown on demand. The kernels leave it clean."""
-    key = (device.index if device.index is not None else torch.cuda.current_device(), kind)
+    """A zero-filled scratch buffer per (device, kind, CUDA stream), grown on demand. The kernels keep live counters in their
+    workspace and leave it clean, so calls that can overlap on the GPU must not share one: every stream gets its own, and a
+    stream's calls are ordered. A buffer that is outgrown is handed back to the allocator only after the stream's pending work
+    (``record_stream``)."""
+    stream = torch.cuda.current_stream(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), kind, stream.cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 4096), dtype=torch.uint8, device=device)
+        if ws is not None:
+            ws.record_stream(stream)
+        with torch.cuda.stream(stream):
+            ws = torch.zeros(max(nbytes, 4096), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+def _state_fields(step_state) -> Tuple[int, int, int, torch.Tensor]:
+    """(pointer, t_max, gamma_max, keep-alive) of a ``(StepStateLayout, state tensor)`` pair."""
+    layout, state = step_state
+    if not state.is_cuda or state.dtype != torch.uint8 or state.numel() < layout.size or not state.is_contiguous():
+        raise ValueError("step_state: (StepStateLayout, contiguous uint8 CUDA tensor of layout.size bytes)")
+    return state.data_ptr(), int(layout.t_max), int(layout.gamma_max), state
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -94,13 +109,15 @@ def _knob(x: Knob, rows: int, dtype: torch.dtype, device: torch.device, name: st
 
 def sample(logits: torch.Tensor, params: Optional[SamplingParams] = None, *, history: Optional[torch.Tensor] = None,
            uniforms: Optional[torch.Tensor] = None, step: int = 0, row_offset: int = 0, return_tau: bool = False, return_stats: bool = False,
-           return_probs: bool = False, return_status: bool = False, out: Optional[torch.Tensor] = None, **knobs: Any) -> SampleOutput:
+           return_probs: bool = False, return_status: bool = False, out: Optional[torch.Tensor] = None, step_state=None, **knobs: Any) -> SampleOutput:
     """One sampling step over every row of ``logits`` [rows, vocab] (bfloat16 or float32, CUDA).
 
     ``params`` (or the same fields as keyword arguments) hold scalar knobs or per-row tensors. ``history`` [rows, n]
     int32 token ids enables the penalties; ``uniforms`` [rows] float32 feeds the inverse-CDF draw; ``row_offset`` is
-    the global index of row 0 (the Gumbel stream id of row r is ``row_offset + r``). Asynchronous on the current
-    stream; nothing is copied to the host.
+    the global index of row 0 (the Gumbel stream id of row r is ``row_offset + r``). ``step_state`` = ``(StepStateLayout,
+    state tensor)`` hands the noise seed, the step and the number of active rows to the device-side state, as the reference's
+    kernels read them (rows beyond ``t_this_step`` and a finished state leave ``out`` untouched): a captured CUDA graph then
+    draws fresh noise on every replay. Asynchronous on the current stream; nothing is copied to the host.
     """
     p = params if params is not None else SamplingParams(**knobs)
     if params is not None and knobs:
@@ -142,6 +159,9 @@ def sample(logits: torch.Tensor, params: Optional[SamplingParams] = None, *, his
             raise ValueError("uniforms must hold one value per row")
         a.uniforms = uniforms.data_ptr()
     a.seed, a.step, a.row_offset = int(p.seed) & (2**64 - 1), int(step) & 0xFFFFFFFF, int(row_offset)
+    if step_state is not None:
+        a.step_state, a.t_max, a.gamma_max, st_keep = _state_fields(step_state)
+        keep.append(st_keep)
     tokens = out if out is not None else torch.empty(rows, dtype=torch.int32, device=dev)
     if tokens.dtype != torch.int32 or tokens.numel() != rows or not tokens.is_contiguous():
         raise ValueError("out must be a contiguous int32 tensor with one entry per row")

@@ -12,7 +12,7 @@ from typing import NamedTuple, Optional, Tuple
 import torch
 
 from . import _lib
-from .sampler import _check_logits, _dtype_code, _row_stride, _workspace
+from .sampler import _check_logits, _dtype_code, _row_stride, _state_fields, _workspace
 
 
 class DraftQ(NamedTuple):
@@ -27,10 +27,12 @@ class DraftQ(NamedTuple):
     q_logits: Optional[torch.Tensor]
 
 
-def draft_q(logits: torch.Tensor, *, temperature: float, seed: int = 0, step: int = 0, first_position: int = 0, copy_logits: bool = False) -> DraftQ:
+def draft_q(logits: torch.Tensor, *, temperature: float, seed: int = 0, step: int = 0, first_position: int = 0, copy_logits: bool = False,
+            step_state=None) -> DraftQ:
     """The drafter's draw for draft positions ``first_position .. first_position + rows - 1``, one logits row each
     (``logits`` [rows, V] bfloat16/float32, rows <= 16): ``argmax_i(z_i * float32(1/T) + gumbel(seed, step, 2000 + position, i))``,
-    the unfiltered softmax at ``temperature`` as the reference's drafter samples it. Asynchronous on the current stream."""
+    the unfiltered softmax at ``temperature`` as the reference's drafter samples it. ``step_state`` = ``(StepStateLayout, state)``
+    takes seed and step from the device-side state instead (nothing is written once it is done). Asynchronous on the current stream."""
     if not temperature > 0:
         raise ValueError("temperature must be positive")
     logits = _check_logits(logits)
@@ -54,15 +56,18 @@ def draft_q(logits: torch.Tensor, *, temperature: float, seed: int = 0, step: in
     ws = _workspace(dev, L.lm_verify_workspace_bytes(rows, vocab), "verify")
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     a.stream = torch.cuda.current_stream(dev).cuda_stream
+    if step_state is not None:
+        a.step_state, a.t_max, a.gamma_max, _keep = _state_fields(step_state)
     with torch.cuda.device(dev):
         _lib.check(L.lm_draft_q(C.byref(a)), "lm_draft_q")
     return DraftQ(tokens, lse, vmax, mass, status, q_logits)
 
 
-def verify(target_logits: torch.Tensor, draft_ids: torch.Tensor, draft_probs: Optional[torch.Tensor] = None, uniforms: Optional[torch.Tensor] = None,
+def verify(target_logits: torch.Tensor, draft_ids: Optional[torch.Tensor], draft_probs: Optional[torch.Tensor] = None, uniforms: Optional[torch.Tensor] = None,
            u_resample: Optional[torch.Tensor] = None, mode: str = "greedy", *, temperature: float = 1.0, tau: Optional[torch.Tensor] = None,
            return_p_draft: bool = False, draft_logits: Optional[torch.Tensor] = None, draft_stats: Optional[DraftQ] = None,
-           commit: Optional[dict] = None) -> Tuple[torch.Tensor, ...]:
+           commit: Optional[dict] = None, seed: int = 0, step: int = 0, residual_draw: str = "inverse_cdf", step_state=None,
+           out: Optional[torch.Tensor] = None, wait_limit: int = 0, selftest: int = 0) -> Tuple[torch.Tensor, ...]:
     """``(accept_len [1], final_token [1], tokens [n + 1])`` as int32 CUDA tensors (plus ``p_draft [n]`` on request).
 
     ``target_logits`` [n + 1, V] bfloat16/float32; ``draft_ids`` [n] int32; stochastic mode also takes the drafter's
@@ -73,13 +78,22 @@ def verify(target_logits: torch.Tensor, draft_ids: torch.Tensor, draft_probs: Op
     for them at the same temperature. ``commit`` closes the round in the same launch: a dict with ``layout`` (StepStateLayout),
     ``state`` and ``ring`` tensors and optionally ``eos``, ``log``, ``ctx_cap``, ``lm`` — the arguments of ``accept_scan``, which
     then runs on the verified tokens inside the verify kernel (the state must describe this round: ``verify_len == n``,
-    ``t_this_step == n + 1``). Asynchronous on the current stream.
+    ``t_this_step == n + 1``). Without ``uniforms`` / ``u_resample`` the kernel takes the reference's counter-based noise of
+    ``(seed, step)`` (accept stream 3000 + r, resample stream 4000); ``residual_draw="gumbel"`` selects the reference's
+    Gumbel form of the final draw. ``step_state`` = ``(StepStateLayout, state)`` hands the round itself to the device-side state:
+    verify length, drafts (``draft_ids`` may then be None: ``target_logits`` holds ``layout.t_max`` rows), seed and step are read
+    there, and a finished state leaves the outputs untouched. ``out`` (int32 [rows + 2]) receives accept, final and the tokens.
+    ``wait_limit`` / ``selftest`` exercise the kernel's bounded waits (tests only). Asynchronous on the current stream.
     """
     if mode not in ("greedy", "stochastic"):
         raise ValueError("mode must be 'greedy' or 'stochastic'")
     target_logits = _check_logits(target_logits)
     dev = target_logits.device
-    n = int(draft_ids.numel())
+    if residual_draw not in ("inverse_cdf", "gumbel"):
+        raise ValueError("residual_draw must be 'inverse_cdf' or 'gumbel'")
+    n = int(draft_ids.numel()) if draft_ids is not None else int(target_logits.shape[0]) - 1
+    if draft_ids is None and step_state is None:
+        raise ValueError("draft_ids may only be omitted with a step_state")
     if target_logits.shape[0] != n + 1:
         raise ValueError("target_logits must have one row per draft plus the bonus row")
     if not 1 <= n <= _lib.MAX_DRAFT:
@@ -89,12 +103,20 @@ def verify(target_logits: torch.Tensor, draft_ids: torch.Tensor, draft_probs: Op
     a.mode = _lib.VERIFY_GREEDY if mode == "greedy" else _lib.VERIFY_STOCHASTIC
     a.dtype, a.n_draft = _dtype_code(target_logits), n
     a.target_logits, a.vocab, a.row_stride = target_logits.data_ptr(), target_logits.shape[1], _row_stride(target_logits)
-    draft_ids = draft_ids.to(device=dev, dtype=torch.int32).contiguous()
-    a.draft_ids = draft_ids.data_ptr()
-    keep = [draft_ids]
+    keep = []
+    if draft_ids is not None:
+        draft_ids = draft_ids.to(device=dev, dtype=torch.int32).contiguous()
+        a.draft_ids = draft_ids.data_ptr()
+        keep.append(draft_ids)
+    a.seed, a.step = int(seed) & (2**64 - 1), int(step) & 0xFFFFFFFF
+    a.residual_draw = _lib.RESIDUAL_GUMBEL if residual_draw == "gumbel" else _lib.RESIDUAL_INVERSE_CDF
+    a.wait_limit, a.selftest = int(wait_limit), int(selftest)
+    if step_state is not None:
+        a.step_state, a.t_max, a.gamma_max, st_keep = _state_fields(step_state)
+        keep.append(st_keep)
     if mode == "stochastic":
-        if (draft_probs is None and (draft_logits is None or draft_stats is None)) or uniforms is None or u_resample is None:
-            raise ValueError("stochastic verification needs draft_probs (or draft_logits + draft_stats), uniforms and u_resample")
+        if draft_probs is None and (draft_logits is None or draft_stats is None):
+            raise ValueError("stochastic verification needs draft_probs (or draft_logits + draft_stats)")
         if not temperature > 0:
             raise ValueError("temperature must be positive")
         if draft_probs is None:
@@ -112,21 +134,28 @@ def verify(target_logits: torch.Tensor, draft_ids: torch.Tensor, draft_probs: Op
             raise ValueError("draft_probs must be float32 CUDA [n, V]")
         elif draft_probs.stride(1) != 1:
             draft_probs = draft_probs.contiguous()
-        uniforms = uniforms.to(device=dev, dtype=torch.float32).contiguous()
-        u_resample = u_resample.to(device=dev, dtype=torch.float32).reshape(1).contiguous()
-        if uniforms.numel() != n:
-            raise ValueError("uniforms must hold one value per draft")
+        if uniforms is not None:
+            uniforms = uniforms.to(device=dev, dtype=torch.float32).contiguous()
+            if uniforms.numel() != n:
+                raise ValueError("uniforms must hold one value per draft")
+            a.u_accept = uniforms.data_ptr()
+        if u_resample is not None:
+            u_resample = u_resample.to(device=dev, dtype=torch.float32).reshape(1).contiguous()
+            a.u_final = u_resample.data_ptr()
         if draft_probs is not None:
             a.draft_probs, a.probs_stride = draft_probs.data_ptr(), _row_stride(draft_probs)
             keep.append(draft_probs)
-        a.u_accept, a.u_final, a.temperature = uniforms.data_ptr(), u_resample.data_ptr(), float(temperature)
+        a.temperature = float(temperature)
         keep += [uniforms, u_resample]
         if tau is not None:
             tau = tau.to(device=dev, dtype=torch.float32).contiguous()
             if tau.numel() != n + 1:
                 raise ValueError("tau must hold one value per row")
             a.tau = tau.data_ptr()
-    out = torch.empty(n + 3, dtype=torch.int32, device=dev)
+    if out is None:
+        out = torch.empty(n + 3, dtype=torch.int32, device=dev)
+    elif out.dtype != torch.int32 or out.numel() != n + 3 or not out.is_cuda or not out.is_contiguous():
+        raise ValueError("out must be a contiguous int32 CUDA tensor with n + 3 entries")
     a.out_accept, a.out_final, a.out_tokens = out.data_ptr(), out.data_ptr() + 4, out.data_ptr() + 8
     p_draft = None
     if return_p_draft and mode == "stochastic":

@@ -58,6 +58,8 @@ def lib():
         _lib.lmo_draft_probs.argtypes = [f32p, C.c_int64, C.c_float, C.c_float, C.c_uint64, f32p]
         _lib.lmo_verify_stochastic.restype = C.c_int32
         _lib.lmo_verify_stochastic.argtypes = [f32p, C.c_int64, C.c_int32, f32p, C.c_float, i32p, f32p, f32p, C.c_float, i32p, f32p]
+        _lib.lmo_verify_gumbel.restype = C.c_int32
+        _lib.lmo_verify_gumbel.argtypes = [f32p, C.c_int64, C.c_int32, f32p, C.c_float, i32p, f32p, f32p, C.c_uint64, C.c_uint32, C.c_uint32, i32p, f32p]
         _lib.lmo_sample_batch.restype = None
         _lib.lmo_sample_batch.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, f32p, C.c_float, i32p, C.c_int32, f32p, C.c_float,
                                           f32p, C.c_float, C.c_int32, i32p, C.c_int64, C.c_int64, C.c_float, C.c_float, C.c_int32, f32p,
@@ -209,6 +211,23 @@ def draft_probs(logits_row: np.ndarray, *, temperature: float, vmax: float, mass
     out = np.zeros(z.shape[0], dtype=np.float32)
     lib().lmo_draft_probs(_p(z, C.c_float), z.shape[0], np.float32(temperature), np.float32(vmax), mass, _p(out, C.c_float))
     return out
+
+
+def verify_gumbel(target_logits: np.ndarray, draft_ids, draft_probs: np.ndarray, *, seed: int, step: int, temperature: float = 1.0, tau=None,
+                  u_accept=None, row0: int = 0) -> Tuple[int, int, float]:
+    """(accept length, final token, gap between the two best keys of the deciding draw) for stochastic verification with the
+    reference's own randomness: accept stream 3000 + r (unless u_accept is given), Gumbel-max residual draw on stream 4000."""
+    z = np.ascontiguousarray(widen(target_logits))
+    n = len(draft_ids)
+    assert z.shape[0] == n + 1
+    d = np.ascontiguousarray(draft_ids, dtype=np.int32)
+    q = _f32(draft_probs)
+    ta = np.full(n + 1, -np.inf, dtype=np.float32) if tau is None else _f32(tau)
+    ua = None if u_accept is None else _f32(u_accept)
+    fin, gap = C.c_int32(), C.c_float()
+    acc = lib().lmo_verify_gumbel(_p(z, C.c_float), z.shape[1], n, _p(ta, C.c_float), np.float32(temperature), _p(d, C.c_int32), _p(q, C.c_float),
+                                  _p(ua, C.c_float) if ua is not None else None, int(seed) & (2**64 - 1), int(step), int(row0), C.byref(fin), C.byref(gap))
+    return int(acc), int(fin.value), float(gap.value)
 
 
 def verify_stochastic(target_logits: np.ndarray, draft_ids, draft_probs: np.ndarray, u_accept, u_final: float, *, temperature: float = 1.0,

@@ -16,6 +16,8 @@
  *   lmo_verify_stochastic kernels/common/sample.metal:273-347 (p/q accept, first reject, residual draw) -- the
  *                         reference has no CPU code and no exact-output test for this part: PARITY UNPINNED; this
  *                         restatement is the frozen definition.
+ *   lmo_verify_gumbel     the same step with the reference's own randomness: accept uniforms of stream 3000 + r, Gumbel-max residual
+ *                         draw on stream 4000 (sample.metal:291-296, 322-346); PARITY UNPINNED for the same reason
  *   lmo_draft_q           kernels/common/sample.metal:212-269 (the drafter's draw on noise stream 2000 + k; the token is
  *                         pinned by sampling_ref.sample with t = 2000 + k; lse to 2e-6; q from the integer mass: unpinned)
  *   lmo_confidence        kernels/common/spec_ops.metal:85-106 (confidence head; pinned to the reference test's expected
@@ -367,6 +369,59 @@ LMO_API int32_t lmo_verify_stochastic(const float* z, int64_t vocab, int32_t n_d
   } else {
     token = lmo_sample_invcdf(zj, vocab, tau[j], temperature, u_final, NULL);
   }
+  if (out_final) *out_final = token;
+  free(vmaxs); free(ks);
+  return j;
+}
+
+/* Stochastic verification with the reference's own randomness (sample.metal:279-347): the accept uniform of draft r is
+ * uniform01(seed, step, 3000 + r, 0) unless u_accept is given; the rejected row's token is
+ * argmax_i { logf(res_i) + gumbel(seed, step, 4000, i) : res_i > 0 } with res as in lmo_verify_stochastic; with every draft accepted,
+ * or an empty residual, the row keeps the ordinary sampler's token argmax_i { fl32(z_i * fl32(1/T)) + gumbel(seed, step, row0 + j, i) :
+ * z_i >= tau_j }. Ties -> lowest index. out_gap: best key minus second-best key of the draw that decided (logf is library-specific).
+ * PARITY UNPINNED like lmo_verify_stochastic: the reference only checks this path's distribution. */
+LMO_API int32_t lmo_verify_gumbel(const float* z, int64_t vocab, int32_t n_draft, const float* tau, float temperature, const int32_t* drafts,
+                                  const float* q, const float* u_accept, uint64_t seed, uint32_t step, uint32_t row0, int32_t* out_final, float* out_gap) {
+  const float c = lmo_exp2_scale(temperature);
+  int32_t j = n_draft;
+  float* vmaxs = (float*)malloc(sizeof(float) * (size_t)(n_draft + 1));
+  uint64_t* ks = (uint64_t*)malloc(sizeof(uint64_t) * (size_t)(n_draft + 1));
+  for (int32_t r = 0; r <= n_draft; r++) {
+    const float* zr = z + (int64_t)r * vocab;
+    float vmax = -INFINITY;
+    for (int64_t i = 0; i < vocab; i++) if (zr[i] > vmax) vmax = zr[i];
+    uint64_t k = 0;
+    for (int64_t i = 0; i < vocab; i++) if (zr[i] >= tau[r]) k += lmo_weight_q40(zr[i], vmax, c);
+    vmaxs[r] = vmax; ks[r] = k;
+  }
+  for (int32_t r = 0; r < n_draft; r++) {
+    const float* zr = z + (int64_t)r * vocab;
+    const int32_t d = drafts[r];
+    float pd = 0.0f;
+    if (d >= 0 && d < vocab && zr[d] >= tau[r] && ks[r] > 0) pd = prob_q40(lmo_weight_q40(zr[d], vmaxs[r], c), ks[r]);
+    const float qd = (d >= 0 && d < vocab) ? q[(int64_t)r * vocab + d] : 0.0f;
+    const float u = u_accept ? u_accept[r] : lmo_uniform01(seed, step, 3000u + (uint32_t)r, 0u);
+    volatile float uq = u * qd;
+    if (uq >= pd && r < j) j = r;
+  }
+  const float* zj = z + (int64_t)j * vocab;
+  const float* qj = (j < n_draft) ? q + (int64_t)j * vocab : NULL;
+  float best = -INFINITY, second = -INFINITY; int64_t bi = -1;
+  if (qj && ks[j] > 0) for (int64_t i = 0; i < vocab; i++) {
+    if (!(zj[i] >= tau[j])) continue;
+    const float p = prob_q40(lmo_weight_q40(zj[i], vmaxs[j], c), ks[j]);
+    volatile float res = p - qj[i];
+    if (!(res > 0.0f)) continue;
+    volatile float lr = logf(res);
+    const float key = lr + lmo_gumbel(seed, step, 4000u, (uint32_t)i);
+    if (key > best) { second = best; best = key; bi = i; } else if (key > second) second = key;
+  }
+  int32_t token = (int32_t)bi;
+  if (bi < 0) {
+    float gap = 0.0f;
+    token = ks[j] > 0 ? lmo_sample_gumbel(zj, vocab, tau[j], (double)temperature, seed, step, row0 + (uint32_t)j, &gap) : -1;
+    if (out_gap) *out_gap = gap;
+  } else if (out_gap) *out_gap = best - second;
   if (out_final) *out_final = token;
   free(vmaxs); free(ks);
   return j;

@@ -3,7 +3,7 @@
 Run once, in a container where the reference checkout is available, with its path as the only argument:
 
     python tests/golden/make_golden.py /path/to/lithos-metal
-    python tests/golden/make_golden.py /path/to/lithos-metal --only draft_q      (adds that section, or `confidence`, to the existing file)
+    python tests/golden/make_golden.py /path/to/lithos-metal --only draft_q      (adds that section, or `confidence` / `penalised`, to the existing file)
 
 It imports ``monolith.nn.sampling_ref`` / ``monolith.nn.sampler`` / ``monolith.kernels`` / ``monolith.core`` read-only
 (numpy and torch are their only dependencies), extracts the ``model_accept`` function from
@@ -70,10 +70,37 @@ def confidence_section(f32_to_bf16, bf16_to_f32) -> dict:
             "inputs_crc": int(hidden.astype(np.uint64).sum() + emb.astype(np.uint64).sum())}
 
 
+def penalised_section(ref, f32_to_bf16, bf16_to_f32) -> dict:
+    """Thresholds and Gumbel draws of the reference's own ``sampling_ref`` on PENALISED rows of the batched benchmark
+    configuration: 16 rows of 151936 BF16 logits N(0, 2^2), per-row temperature / top_k / top_p, a 2048-id history per row. The
+    reference has no penalties; they are applied here in binary32 the way this repository defines them (for every distinct
+    history id: z = z / rho if z > 0 else z * rho, then z = z - pi), and the reference then sees arbitrary FP32 rows
+    (``thresholds`` walks ~3800 distinct values per row: about half a second each)."""
+    rows, vocab, hist_len, rho, pi = 16, 151936, 2048, np.float32(1.1), np.float32(0.5)
+    rng = np.random.default_rng(3)                                          # the recipe of tests/inputs.config3(rows=16)
+    lb = f32_to_bf16((rng.standard_normal((rows, vocab), dtype=np.float32) * np.float32(2.0)))
+    temperature = rng.uniform(0.3, 1.5, rows).astype(np.float32)
+    top_k = rng.choice(np.array([0, 20, 50, 1000], dtype=np.int32), rows)
+    top_p = rng.uniform(0.8, 1.0, rows).astype(np.float32)
+    history = rng.integers(0, vocab, (rows, hist_len)).astype(np.int32)
+    taus, toks = [], []
+    for r in range(rows):
+        z = bf16_to_f32(lb[r]).astype(np.float32).copy()
+        ids = np.unique(history[r])
+        v = z[ids]
+        z[ids] = (np.where(v > 0, v / rho, v * rho).astype(np.float32) - pi).astype(np.float32)
+        opts = dict(temperature=float(temperature[r]), top_k=int(top_k[r]), top_p=float(top_p[r]))
+        taus.append(float(ref.thresholds(z, **opts)))
+        toks.append(int(ref.sample(z, seed=12345, step=1, t=r, **opts)))
+        print("penalised", r, opts, taus[-1], toks[-1], flush=True)
+    return {"rows": rows, "tau": taus, "tokens_seed12345_step1": toks, "logits_crc": int(lb.astype(np.uint64).sum()),
+            "history_crc": int(history.astype(np.uint64).sum())}
+
+
 def main(ref_root: str, only: str = "") -> None:
     sys.dont_write_bytecode = True
     sys.path.insert(0, ref_root)
-    if only in ("draft_q", "confidence"):                                  # add this section to the existing file without redoing the rest
+    if only in ("draft_q", "confidence", "penalised"):                                  # add this section to the existing file without redoing the rest
         from monolith.formats.fp import bf16_to_f32, f32_to_bf16
         from monolith.nn import sampling_ref as ref
         path = os.path.join(HERE, "reference_outputs.json")
@@ -81,6 +108,8 @@ def main(ref_root: str, only: str = "") -> None:
             out = json.load(f)
         if only == "draft_q":
             out["draft_q"] = draft_q_section(ref, f32_to_bf16, bf16_to_f32)
+        elif only == "penalised":
+            out["penalised"] = penalised_section(ref, f32_to_bf16, bf16_to_f32)
         else:
             out["confidence"] = confidence_section(f32_to_bf16, bf16_to_f32)
         with open(path, "w") as f:
@@ -220,6 +249,7 @@ def main(ref_root: str, only: str = "") -> None:
 
     out["draft_q"] = draft_q_section(ref, f32_to_bf16, bf16_to_f32)
     out["confidence"] = confidence_section(f32_to_bf16, bf16_to_f32)
+    out["penalised"] = penalised_section(ref, f32_to_bf16, bf16_to_f32)
 
     with open(os.path.join(HERE, "reference_outputs.json"), "w") as f:
         json.dump(out, f, indent=1, sort_keys=True)

@@ -23,7 +23,7 @@ def test_library_exports_every_declared_symbol():
     assert set(names) == set(_lib.EXPORTS) and len(names) >= 10
     for n in names:
         assert getattr(L, n) is not None
-    assert L.lm_abi_version() == _lib.ABI_VERSION == 2
+    assert L.lm_abi_version() == _lib.ABI_VERSION == 3
     assert L.lm_error_string(0) == b"ok" and L.lm_error_string(-2).startswith(b"workspace")
 
 

@@ -185,3 +185,16 @@ def test_confidence_head_equals_the_reference_test_values(golden):
                       (oracle.confidence(hidden, None, w[:256], float(b[0]), sts=g["sts"]), g["hidden_only_sts"])):
         assert np.abs(got - np.array(want)).max() <= 2e-3
         assert np.count_nonzero(np.abs(got - np.array(want)) > 1e-6) <= 1
+
+
+def test_penalised_rows_equal_the_reference(golden):
+    """Thresholds and Gumbel tokens of the reference's own sampling_ref on 16 PENALISED rows of the batched benchmark
+    configuration (the penalties themselves are this repository's definition; what the reference then computes on the penalised
+    FP32 rows is the pin)."""
+    g = golden["penalised"]
+    cfg = inputs.config3(rows=g["rows"], seed=3)
+    assert int(cfg["logits"].astype(np.uint64).sum()) == g["logits_crc"] and int(cfg["history"].astype(np.uint64).sum()) == g["history_crc"]
+    tok, tau, _ = oracle.sample_batch(cfg["logits"], temperature=cfg["temperature"], top_k=cfg["top_k"], top_p=cfg["top_p"], history=cfg["history"],
+                                      repetition_penalty=1.1, presence_penalty=0.5, draw="gumbel", seed=12345, step=1, n_threads=8)
+    np.testing.assert_array_equal(tau, np.array(g["tau"], dtype=np.float32))
+    assert tok.tolist() == g["tokens_seed12345_step1"]
