@@ -48,10 +48,14 @@ def peaks():
 
 
 def ncu_traffic():
-    """DRAM bytes per row of one sampling call (dram__bytes_read.sum + dram__bytes_write.sum, summed over the top-k kernel and
-    the histogram kernel, of one ncu capture of the 4096-row workload itself; a call's traffic is this times its rows). The
-    capture is summarised in profiles/sample_kernels_4096rows_ncu_full.md."""
-    return {"dram_bytes_per_row": (1043868000 + 3853568 + 508108000 + 41251584) / 4096}
+    """DRAM bytes per row of one sampling call: dram__bytes_read.sum + dram__bytes_write.sum of the top-k kernel and of the
+    histogram kernel, from one ncu capture of the 4096-row workload itself (a call's traffic is this times its rows). The
+    figures are typed in from that capture; `captured_at` names the commit whose kernels were captured."""
+    return TRAFFIC
+
+
+# (top-k kernel read + write) + (histogram kernel read + write) over the 4096 rows of one call
+TRAFFIC = {"dram_bytes_per_row": (1043868000 + 3853568 + 508108000 + 41251584) / 4096, "captured_at": "16f2bfc (kernels changed since: indicative only)"}
 
 
 def launches_per_call(lm, rows: int) -> int:
@@ -132,6 +136,58 @@ def cpu_rows_per_s(inp_host, n_rows: int, n_threads: int, repeats: int = 1):
     return n_rows / best, tok
 
 
+def penalised_rows(hc, rows):
+    """FP32 rows `rows` of a host copy with the penalties applied in binary32 (this repository's definition; the reference has none)."""
+    import numpy as np
+    import oracle
+    out = []
+    for r in rows:
+        z = oracle.bf16_to_f32(hc["logits"][r]).astype(np.float32).copy()
+        ids = np.unique(hc["history"][r])
+        v = z[ids]
+        z[ids] = (np.where(v > 0, v / np.float32(RHO), v * np.float32(RHO)).astype(np.float32) - np.float32(PI)).astype(np.float32)
+        out.append(z)
+    return out
+
+
+_AS_SHIPPED = {}
+
+
+def _as_shipped_row(i):
+    ref, zs, hc = _AS_SHIPPED["ref"], _AS_SHIPPED["rows"], _AS_SHIPPED["hc"]
+    return int(ref.sample(zs[i], seed=SEED, step=0, t=i, temperature=float(hc["temperature"][i]), top_k=int(hc["top_k"][i]), top_p=float(hc["top_p"][i])))
+
+
+def as_shipped_baseline(hc, cores: int):
+    """The reference's numpy sampler AS SHIPPED (monolith/nn/sampling_ref.py `sample`: thresholds + Gumbel-max draw), placed
+    under oracle/_ref by oracle/make_ref.py: rows/s of a single process and of a multiprocessing.Pool over the host's cores, on
+    a bounded subset of the workload's rows (a row with top-p costs ~0.3 s). The penalties, which the reference does not have,
+    are applied beforehand and are not timed."""
+    from oracle import make_ref
+    ref = make_ref.load()
+    if ref is None:
+        return {"unavailable": "oracle/_ref/sampling_ref.py is not there (python oracle/make_ref.py <reference checkout> places it)"}
+    import multiprocessing as mp
+    n_single, n_pool = 8, max(8, min(len(hc["temperature"]), 2 * cores))
+    _AS_SHIPPED.update(ref=ref, hc=hc, rows=penalised_rows(hc, range(n_pool)))
+    _as_shipped_row(0)
+    t0 = time.perf_counter()
+    single = [_as_shipped_row(i) for i in range(n_single)]
+    t_single = time.perf_counter() - t0
+    try:
+        with mp.get_context("fork").Pool(cores) as pool:
+            pool.map(_as_shipped_row, range(min(cores, n_pool)))             # workers started and warm
+            t0 = time.perf_counter()
+            pooled = pool.map(_as_shipped_row, range(n_pool), chunksize=1)
+            t_pool = time.perf_counter() - t0
+        pool_v, same = n_pool / t_pool, pooled[:n_single] == single
+    except OSError as e:
+        pool_v, same = None, f"pool unavailable: {e}"
+    return {"single_process_rows_per_s": n_single / t_single, "pool_rows_per_s": pool_v, "unit": UNIT, "cores": cores, "kind": "reference",
+            "sample": f"{n_single} rows single process, {n_pool} rows over a Pool of {cores}; the reference's own Gumbel-max draw (it has no "
+                      "inverse-CDF draw), penalties applied beforehand and not timed", "pool_equals_single": same}
+
+
 def host_copy(torch, inp, n_rows: int):
     import numpy as np
     return dict(logits=inp["logits"][:n_rows].view(torch.int16).cpu().numpy().view(np.uint16), temperature=inp["temperature"][:n_rows].cpu().numpy(),
@@ -164,6 +220,7 @@ def reference_arm(args, rank: int, world: int) -> None:
                       "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64",
                       "data": "synthetic", "config": {"workload": WORKLOAD, "vocab": VOCAB, "rows_per_step": n_rows},
                       "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+                      "cpu_baseline_as_shipped": as_shipped_baseline(inp, cores),
                       "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
@@ -257,8 +314,8 @@ def main() -> None:
                         "frac_of_nominal_8TBs": achieved / 8000.0, "algorithmic_bytes_per_row": ROW_BYTES,
                         "traffic": (traffic["dram_bytes_per_row"] * rows if traffic else None)},
            "gpu_launches": launches_per_call(lm, rows) * args.steps, "clocks": clocks.summary()}
-    out["roofline"]["launch"] = ("one sampling call = sample_topk_kernel (rows with a top_k) + sample_fast_kernel (the other rows) + "
-                                 "sample_generic_kernel (rows handed on: none here)" + (" + the row-listing kernel and a second sample_fast_kernel launch "
+    out["roofline"]["launch"] = ("one sampling call = sample_topk_kernel (rows with a top_k) + sample_hist_kernel (the other rows) + "
+                                 "sample_generic_kernel (rows handed on: none here)" + (" + the row-listing kernel and a second sample_hist_kernel launch "
                                  "(side-by-side order below 16 rows per SM)" if launches_per_call(lm, rows) == 5 else "") + "; duration = CUDA events around the call")
 
     if not args.skip_extras:
@@ -316,18 +373,62 @@ def main() -> None:
             hc = host_copy(torch, inp, n_cpu)
             cpu_rows_per_s(hc, min(n_cpu, cores), cores)
             cpu_v, cpu_tok = cpu_rows_per_s(hc, n_cpu, cores)
+            out["cpu_baseline"] = {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port",
+                                   "sample": f"first {n_cpu} rows of the workload, C restatement of monolith/nn/sampling_ref.py (oracle/lm_oracle.c), {cores} threads"}
+            out["cpu_baseline_as_shipped"] = as_shipped_baseline(hc, cores)
+            # outside every timed region: EVERY row of the workload against the oracle
             step(0)
             torch.cuda.synchronize(dev)
-            same = bool((tokens[:n_cpu].cpu().numpy() == cpu_tok).all())
-            out["cpu_baseline"] = {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port",
-                                   "sample": f"first {n_cpu} rows of the workload, C restatement of monolith/nn/sampling_ref.py (oracle/lm_oracle.c), {cores} threads",
-                                   "tokens_equal_gpu": same}
+            _, all_tok = cpu_rows_per_s(host_copy(torch, inp, rows), rows, cores)
+            gpu_tok = tokens.cpu().numpy()
+            out["cpu_baseline"]["tokens_equal_gpu"] = bool((gpu_tok == all_tok).all())
+            out["cpu_baseline"]["rows_compared"] = int(rows)
+            out["config1"] = bench_config1(torch, lm, dev)
+            out["config5_single_gpu"] = bench_config5_single(torch, lm, dev)
     if world > 1 and not args.skip_extras:
         out["vocab_parallel"] = bench_vocab_parallel(torch, dist, lm, dev, rank, world, args.warmup)
     if rank == 0:
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+
+
+def _min_us(torch, dev, call, flush=None, n=20, warm=3):
+    ts = []
+    for i in range(warm + n):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); call(); b.record()
+        torch.cuda.synchronize(dev)
+        if i >= warm:
+            ts.append(a.elapsed_time(b) * 1e3)
+    return min(ts)
+
+
+def bench_config1(torch, lm, dev):
+    """Configuration 1: one FP32 row of 151936 logits N(0, 2^2) with 8 spikes at +12; greedy, then temperature 0.7 / top_k 20 /
+    top_p 0.95 with an injected uniform. Microseconds per call (L2 flushed before each, min of 20)."""
+    g = torch.Generator(device=dev); g.manual_seed(0)
+    z = torch.randn(1, VOCAB, generator=g, device=dev) * 2.0
+    z[0, torch.randperm(VOCAB, generator=g, device=dev)[:8]] = 12.0
+    u = torch.rand(1, generator=torch.Generator(device=dev).manual_seed(1), device=dev)
+    flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=dev)
+    p = lm.SamplingParams(temperature=0.7, top_k=20, top_p=0.95, draw="inverse_cdf")
+    return {"workload": "1 row x 151936 fp32, 8 spikes at +12", "greedy_us": _min_us(torch, dev, lambda: lm.argmax(z), flush),
+            "stochastic_us": _min_us(torch, dev, lambda: lm.sample(z, p, uniforms=u), flush), "timing": "L2 flushed, min of 20"}
+
+
+def bench_config5_single(torch, lm, dev):
+    """Configuration 5 on ONE GPU through lm_sample (the result the vocab-parallel mode must reproduce): 64 rows x 262144 BF16."""
+    g = torch.Generator(device=dev); g.manual_seed(SEED)
+    full = (torch.randn(64, 262144, generator=g, device=dev) * 2.0).to(torch.bfloat16)
+    u = torch.rand(64, generator=g, device=dev)
+    p = lm.SamplingParams(temperature=0.8, top_k=50, top_p=0.9, draw="inverse_cdf")
+    flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=dev)
+    us = _min_us(torch, dev, lambda: lm.sample(full, p, uniforms=u), flush)
+    return {"workload": "64 rows x 262144 bf16, top_k 50, top_p 0.9, T 0.8, whole rows on one GPU", "us_per_step": us,
+            "frac_of_peak": 64 * 262144 * 2 / (us * 1e-6) / 1e9 / peaks()[0], "timing": "L2 flushed, min of 20"}
 
 
 def bench_vocab_parallel(torch, dist, lm, dev, rank, world, warmup):
@@ -357,12 +458,30 @@ def bench_vocab_parallel(torch, dist, lm, dev, rank, world, warmup):
     torch.cuda.synchronize(dev)
     t = torch.tensor([a.elapsed_time(b) / n], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    # the three parts of a step, each timed on its own (CUDA events, max over ranks): local kernel, NCCL all-gather, merge kernel
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    parts = torch.zeros(3, dtype=torch.float64, device=dev)
+    for _ in range(n):
+        ev[0].record()
+        rec = sampler.backend.local(shard, sampler.shard_start, p, sampler.cap)
+        ev[1].record()
+        flat = torch.empty(world * rec.shape[0], rec.shape[1], dtype=rec.dtype, device=dev)
+        dist.all_gather_into_tensor(flat, rec)
+        ev[2].record()
+        sampler.backend.merge(flat.view(world, rec.shape[0], rec.shape[1]), p, sampler.cap, u, 0, 0)
+        ev[3].record()
+        torch.cuda.synchronize(dev)
+        parts += torch.tensor([ev[i].elapsed_time(ev[i + 1]) for i in range(3)], dtype=torch.float64, device=dev)
+    parts /= n
+    dist.all_reduce(parts, op=dist.ReduceOp.MAX)
     one = lm.sample(full, p, uniforms=u).tokens
     same = torch.tensor([int(torch.equal(one, r.tokens))], device=dev)
     dist.all_reduce(same, op=dist.ReduceOp.MIN)
     ms = float(t.item())
     return {"workload": "64 rows x 262144 bf16, vocab split over the ranks, top_k 50, top_p 0.9, T 0.8", "us_per_step": 1e3 * ms,
-            "rows_per_s": rows / (ms * 1e-3), "allgather_bytes_per_rank": int(rows * sampler.backend.record_bytes(sampler.cap)),
+            "rows_per_s": rows / (ms * 1e-3), "local_kernel_us": 1e3 * float(parts[0]), "allgather_us": 1e3 * float(parts[1]),
+            "merge_kernel_us": 1e3 * float(parts[2]), "parts_timing": "each part between its own CUDA events with a synchronize per step (launch gaps included), max over ranks",
+            "allgather_bytes_per_rank": int(rows * sampler.backend.record_bytes(sampler.cap)),
             "tokens_equal_single_gpu_on_every_rank": bool(same.item())}
 
 

@@ -303,7 +303,10 @@ LM_API int lm_draft_q(const lm_draft_q_args* args);
  *   3. every GPU calls lm_vocab_merge on the gathered records and gets the same tokens.
  * Requirements: top_k >= 1 on every row (the kept set must lie inside the top-k candidates), cap =
  * lm_vocab_candidate_cap(largest top_k), shards * cap <= LM_VOCAB_MAX_CANDIDATES, no penalties. A row whose ties overflow
- * a record reports LM_STATUS_OVERFLOW and token -1.
+ * a record reports LM_STATUS_OVERFLOW and token -1; a row whose per-row temperature is not positive reports status bit 16 and
+ * token -1. One exception to "bit for bit": the FP64 softmass is summed per shard and then over the sorted candidates, another
+ * order than on one GPU, so a top-p boundary within 1e-12 (relative) of the target may fall on the other side; such rows carry
+ * LM_STATUS_TOPP_EDGE here as they do there.
  */
 #define LM_VOCAB_MAX_CANDIDATES 1024
 #define LM_STATUS_OVERFLOW 32u

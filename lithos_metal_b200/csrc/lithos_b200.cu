@@ -182,6 +182,12 @@ int lm_argmax(const void* logits, int32_t dtype, int64_t rows, int64_t vocab, in
   if (splits > 1 && (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < lm_workspace_bytes(rows, vocab)))
     return LM_E_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (splits > 1) {
+    // one entry per row, zero when the kernel starts. A workspace that also served lm_sample with another row count holds that
+    // call's row lists where these entries lie, so they are cleared here rather than trusted.
+    const cudaError_t e = cudaMemsetAsync(workspace, 0, static_cast<size_t>(rows) * sizeof(ArgmaxWs), st);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
   for (int64_t r0 = 0; r0 < rows; r0 += 65535) {                          // gridDim.y limit
     const int nr = static_cast<int>(rows - r0 < 65535 ? rows - r0 : 65535);
     const size_t esz = dtype == LM_DTYPE_BF16 ? 2 : 4;
@@ -219,11 +225,8 @@ int lm_argmax_static(const void* logits, int32_t dtype, int64_t rows, int64_t vo
     ws = ws_addr[dev];
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // the array keeps whatever the last call left: the entries this call uses must start at zero
-  e = cudaMemsetAsync(ws, 0, static_cast<size_t>(rows) * sizeof(ArgmaxWs), st);
-  if (e != cudaSuccess) return cuda_fail(e);
-  // lm_argmax touches one ArgmaxWs entry per row and nothing else of a workspace; the size given here only has to
-  // pass its general workspace check
+  // lm_argmax touches one ArgmaxWs entry per row and nothing else of a workspace (it clears the entries it uses on the stream
+  // before its kernel: the array keeps whatever the last call left); the size given here only has to pass its general check
   return lm_argmax(logits, dtype, rows, vocab, row_stride, out_tokens, ws, lm_workspace_bytes(rows, vocab), st);
 }
 

@@ -378,8 +378,8 @@ __device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint
           w += ((mask >> (2 * e)) & 2u) ? wb : 0ull;
         }
       }
-      // the warp's total in two limbs (w < 2^43): two 32-bit warp reductions instead of ten 64-bit shuffles
-      const uint32_t lo = __reduce_add_sync(kFull, static_cast<uint32_t>(w) & 0x3FFFFFu), hi = __reduce_add_sync(kFull, static_cast<uint32_t>(w >> 22));
+      // the warp's total in two limbs (w < 2^43): two 32-bit butterflies instead of one of 64-bit values
+      const uint32_t lo = warp_sum_u32(static_cast<uint32_t>(w) & 0x3FFFFFu), hi = warp_sum_u32(static_cast<uint32_t>(w >> 22));
       if (lane == 0) s.batch_sum[buf][it * kHW + warp] = k < n_seg ? static_cast<uint64_t>(lo) + (static_cast<uint64_t>(hi) << 22) + s.seg_fix[seg] : 0ull;
     }
     __syncthreads();
@@ -630,7 +630,7 @@ __device__ void sample_row_hist(const SampleDev& P, int row, int next, HistSmem&
   // ---- phase 3: group counts and the top position of the main histogram; the penalised histogram compacted into a list --------
   for (int sg = warp; sg < static_cast<int>(kSlots) / kGrpSlots; sg += kHW) {
     const uint32_t w = s.hist[sg * 32 + lane];
-    const uint32_t tot = __reduce_add_sync(kFull, (w & 0xFFFFu) + (w >> 16));
+    const uint32_t tot = warp_sum_u32((w & 0xFFFFu) + (w >> 16));
     const int g = sg < kSignGroups ? kSignGroups - 1 - sg : sg + 1;
     if (lane == 0) s.g_cnt[g] = tot;
     if (tot) {
@@ -638,7 +638,7 @@ __device__ void sample_row_hist(const SampleDev& P, int row, int next, HistSmem&
       uint32_t p = 0xFFFFFFFFu;
       if (w & 0xFFFFu) p = pos_of_slot(slot);
       if (w >> 16) p = min(p, pos_of_slot(slot + 1u));
-      p = __reduce_min_sync(kFull, p);
+      p = warp_min_u32(p);
       if (lane == 0) atomicMin(&s.top_pos, p);
     }
   }

@@ -64,21 +64,6 @@ struct TopkSmem {
 
 static_assert(kTopkPerSM * (sizeof(TopkSmem) + 1024) <= 233472, "the blocks of the top-k kernel must fit one SM's shared memory");
 
-#ifdef LM_PROFILE_PHASES
-#define LM_TPHASE(i) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == 0) { const long long _t = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(_t - _t0)); _t0 = _t; } } while (0)
-#else
-#define LM_TPHASE(i) do {} while (0)
-#endif
-#ifdef LM_STOP_AFTER
-#undef LM_TPHASE
-#define LM_TPHASE(i) do { if ((i) == LM_STOP_AFTER) { cp_async_wait<0>(); __syncthreads(); return true; } } while (0)
-#endif
-#if defined(LM_PROFILE_PHASES) && defined(LM_PROFILE_SUB)
-#define LM_TSUB(i) LM_TPHASE(i)
-#else
-#define LM_TSUB(i) do {} while (0)
-#endif
-
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src) : "memory");
 }
@@ -190,9 +175,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   const double T64 = static_cast<double>(T), inv_t = 1.0 / T64;
   const float c2a = static_cast<float>(1.4426950408889634 * inv_t);          // the FP32 softmass only: approximate on purpose
 
-#ifdef LM_PROFILE_PHASES
-  long long _t0 = clock64();
-#endif
   // the first chunks of the pass do not depend on the cutoff: they start now and land in this thread's slots
   const int n_it = (n_chunks + kTB - 1) / kTB;
 #pragma unroll
@@ -228,7 +210,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   }
   if (tid == 0) { c.n_hit = 0u; c.n = 0u; c.n_side = 0u; c.wide = 0u; c.ref_key = 0u; c.hit = kTopkCap; c.token = -1; c.cross_bin = 0u; }
   __syncthreads();
-  LM_TSUB(0);
   // the thread that sets an id's bit owns the id and lists it
 #pragma unroll
   for (int j = 0; j < kHistPer; j++) {
@@ -241,7 +222,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
     const uint32_t slot = warp_reserve(&c.n_side, fresh ? 1u : 0u);
     if (fresh) c.side_id[slot] = static_cast<uint32_t>(id);
   }
-  LM_TSUB(1);
   // ---- the cutoff: the largest positive BF16 code with at least `want` of the 8192 sampled logits at or above it ---------
   // (about 1.3 k + 150 candidates expected in the whole row, at most ~1500)
   // A bisection over the codes, one barrier per probe; it starts from a bracket around the cutoff of the block's last
@@ -265,7 +245,7 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
           cnt[t] += __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].x), t2)) + __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].y), t2)) +
                     __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].z), t2)) + __popc(__hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].w), t2));
         }
-        cnt[t] = __reduce_add_sync(kFull, cnt[t] >> 4);                     // 16 mask bits per logit
+        cnt[t] = warp_sum_u32(cnt[t] >> 4);                     // 16 mask bits per logit
         if (lane == 0 && cnt[t]) atomicAdd(&c.probe_cnt[probe + t], cnt[t]);
       }
       __syncthreads();
@@ -283,7 +263,7 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
         mx = __hmax2(mx, __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].x), *reinterpret_cast<const __nv_bfloat162*>(&qs[j].y)));
         mx = __hmax2(mx, __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&qs[j].z), *reinterpret_cast<const __nv_bfloat162*>(&qs[j].w)));
       }
-      const uint32_t key = __reduce_max_sync(kFull, fkey(fmaxf(__low2float(mx), __high2float(mx))));
+      const uint32_t key = warp_max_u32(fkey(fmaxf(__low2float(mx), __high2float(mx))));
       if (lane == 0) atomicMax(&c.ref_key, key);
     }
     uint32_t lo = 0x0000u, hi = 0x7F7Fu;                                    // invariant: count(sample >= lo) >= want, or lo is still 0 (handed back below)
@@ -297,7 +277,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
       else if (n3[1] >= want) { lo = mid; hi = bhi; }
       else { lo = blo; hi = mid - 1u; }
     }
-    LM_TSUB(2);
     while (lo < hi && probe + 3 <= kMaxProbes) {                            // three cuts per round: the range shrinks fourfold
       const uint32_t span = hi - lo;
       const uint32_t q1 = lo + (span + 3u) / 4u, q2 = lo + (2u * span + 3u) / 4u, q3 = lo + (3u * span + 3u) / 4u;   // lo < q1 <= q2 <= q3 <= hi
@@ -307,14 +286,12 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
       else if (n3[0] >= want) { lo = q1; hi = q2 - 1u; }
       else hi = q1 - 1u;
     }
-    LM_TSUB(3);
     cut_code = lo;
     if (cut_code < 0x0080u || lo < hi) { cp_async_wait<0>(); return false; }   // fewer positive logits than candidates wanted: not this kernel's row
                                                                             // (the copies in flight must land before the slots are used again)
     if (tid == 0) c.prev_cut[cls] = cut_code;
   }
   const float cut_val = __uint_as_float(cut_code << 16);
-  LM_TPHASE(8);
 
   // ---- the one pass: note the chunks that hold a logit >= cutoff; FP32 softmass relative to the sampled maximum ----------
   const float M = need_z ? fkey_inv(c.ref_key) : 0.0f;
@@ -367,7 +344,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
     }
     cp_async_wait<0>();
   }
-  LM_TPHASE(9);
   // a NaN or +inf logit (or a logit far above the sampled maximum) has made this thread's sum NaN or infinite: the exact path
   // takes such rows and reports them
   double zsum = 0.0, zadd = 0.0, zsub = 0.0;                                // the pass's mass; what the penalised logits add; what their raw values had added
@@ -409,7 +385,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
       }
     }
   }
-  LM_TPHASE(15);
   // ---- the penalised logits, from the list ---------------------------------------------------------------------------------
   if (pen_on) {
     // their raw logits are fetched now, after the pass: the row has just gone through L2
@@ -456,7 +431,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   const int n = static_cast<int>(c.n);
   if (n > kTopkCap || n < top_k || c.wide) return false;
 
-  LM_TPHASE(10);
   // ---- the candidates at or above the top-k crossing, in descending value order: a counting sort by code bin ---------------
   // (the bins are the BF16 codes relative to the cutoff; the crossing is the highest bin b with at least top_k
   // candidates in the bins >= b; inside a bin only penalised values can differ, and one thread puts its bin in order)
@@ -489,7 +463,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
     if (rel >= cross) c.sel[c.off[rel] + atomicSub(&c.bins[rel], 1u) - 1u] = k;
   }
   __syncthreads();
-  LM_TPHASE(11);
   for (uint32_t b = cross + tid; b < kTopkBins; b += kTB) {
     const uint32_t lo = c.off[b], hi = (b == cross) ? static_cast<uint32_t>(n_sel) : c.off[b - 1];
     bool sorted = true;
@@ -505,7 +478,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   }
   __syncthreads();
   if (c.wide) return false;                                                 // a large bin of unequal (penalised) values: the exact path takes the row
-  LM_TPHASE(12);
 
   // ---- exact thresholds on the sorted candidates ------------------------------------------------------------------------
   const float vmax = fkey_inv(static_cast<uint32_t>(c.sel[0] >> 32));
@@ -569,7 +541,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   for (int i = tid; i < n_sel; i += kTB) cnt_kept += fkey_inv(static_cast<uint32_t>(c.sel[i] >> 32)) >= tau ? 1ull : 0ull;
   const int n_kept = static_cast<int>(block_sum_u64(cnt_kept, c.scratch));   // the kept set is the first n_kept sorted candidates
 
-  LM_TPHASE(13);
   // ---- the draw ----------------------------------------------------------------------------------------------------------
   int token = -1;
   if (P.draw == LM_DRAW_INVERSE_CDF) {
@@ -644,7 +615,6 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
       token = static_cast<int>(best_index(win));
     }
   }
-  LM_TPHASE(14);
   if (tid == 0) {
     P.out_tokens[row] = token;
     if (P.out_tau) P.out_tau[row] = tau;

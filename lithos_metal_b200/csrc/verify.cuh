@@ -62,14 +62,20 @@ __device__ __forceinline__ uint32_t pack52_index(uint64_t p) { return 0xFFFFFu -
 __device__ __forceinline__ void publish(unsigned long long* p, uint64_t v) {
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(static_cast<unsigned long long>(v) | kTagged) : "memory");
 }
-// Polls one word until its tag is set; gives up after `limit` polls (then *failed is set and 0 returned).
-__device__ __forceinline__ uint64_t consume(const unsigned long long* p, unsigned limit, bool* failed) {
+__device__ __forceinline__ unsigned long long peek(const unsigned long long* p) {
   unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// Polls one word until its tag is set; gives up after `limit` polls (then *failed is set and 0 returned). `first`: a value
+// already read from the word.
+__device__ __forceinline__ uint64_t consume(const unsigned long long* p, unsigned limit, bool* failed, unsigned long long first = 0ull) {
+  unsigned long long v = first;
   for (unsigned spins = 0;; spins++) {
-    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     if (v & kTagged) return v & ~kTagged;
     if (spins >= limit) { *failed = true; return 0ull; }
-    if (spins > 4u) __nanosleep(40);
+    if (spins > 64u) __nanosleep(100);                                    // a long wait: leave the memory system to the blocks still working
+    v = peek(p);
   }
 }
 
@@ -124,11 +130,17 @@ __device__ __forceinline__ void consume_rows(const unsigned long long* words, in
                                              unsigned limit, bool* failed, uint64_t vals[kConsumeSlots]) {
   const int tid = threadIdx.x, lane = tid & 31;
   const int Gp = (G + 31) & ~31, n = R * Gp;
+  unsigned long long first[kConsumeSlots];
+#pragma unroll
+  for (int k = 0; k < kConsumeSlots; k++) {                               // every word of this thread in flight at once
+    const int idx = k * kVerifyBlock + tid, r = idx / Gp, g = idx - r * Gp;
+    first[k] = (idx < n && g < G) ? peek(words + static_cast<size_t>(r) * kVerifyMaxGrid + g) : 0ull;
+  }
 #pragma unroll
   for (int k = 0; k < kConsumeSlots; k++) {
     const int idx = k * kVerifyBlock + tid, r = idx / Gp, g = idx - r * Gp;
     uint64_t v = 0ull;
-    if (idx < n && g < G) v = consume(words + static_cast<size_t>(r) * kVerifyMaxGrid + g, limit, failed);
+    if (idx < n && g < G) v = consume(words + static_cast<size_t>(r) * kVerifyMaxGrid + g, limit, failed, first[k]);
     vals[k] = v;
     if (k * kVerifyBlock < n) {                                           // block-uniform
       const uint64_t w = SUM ? warp_sum_u64(v) : warp_max_u64(v);
@@ -188,6 +200,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   const int per = ((V + G - 1) / G + 7) & ~7;
   const int lo = min(V, b * per), hi = min(V, lo + per);
   const int len = hi - lo;
+  const int chunks = (len + 7) / 8;                                        // 8-element load items of one row of the slice
   float* zs = cached ? v_smem : nullptr;
   float* qs = (cached && stochastic) ? v_smem + (P.n_draft + 1) * per : nullptr;
   const float c2 = stochastic ? exp2_scale(P.temperature) : 0.0f;
@@ -208,7 +221,6 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     // 8 elements per load item (one 16-byte load of BF16 logits, two of FP32 logits or draft probabilities), every item of
     // a thread issued before the first is used: the whole slice arrives in one memory round trip
     const int n_q = stochastic ? L : 0;
-    const int chunks = (len + 7) / 8;
     const bool z_vec = (P.dtype == LM_DTYPE_BF16 ? (P.row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(P.target) & 15u) == 0)
                                                  : (P.row_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(P.target) & 15u) == 0));
     const bool q_vec = n_q == 0 || (P.q ? (P.q_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(P.q) & 15u) == 0)
@@ -221,8 +233,8 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
       for (int k = 0; k < kItems; k++) {
         const int item = i0 + k * kVerifyBlock + tid;
         va[k] = make_float4(0.f, 0.f, 0.f, 0.f); vb[k] = va[k];
+        const int r = item / chunks, ci = item - r * chunks, c8 = ci * 8;
         if (item >= n_items) continue;
-        const int r = item / chunks, c8 = (item - r * chunks) * 8;
         const bool full = c8 + 8 <= len;
         if (r < R) {
           if (P.dtype == LM_DTYPE_BF16) {
@@ -244,7 +256,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
       for (int k = 0; k < kItems; k++) {
         const int item = i0 + k * kVerifyBlock + tid;
         if (item >= n_items) continue;
-        const int r = item / chunks, c8 = (item - r * chunks) * 8;
+        const int r = item / chunks, ci = item - r * chunks, c8 = ci * 8;
         const bool full = c8 + 8 <= len;
         float* dst = (r < R ? zs + r * per : qs + (r - R) * per) + c8;
         const bool vec = full && (r < R ? z_vec : q_vec);
@@ -275,23 +287,67 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     __syncthreads();
   }
   // ---- row maxima of the slice (lowest index on ties: the greedy pick), published one word per row -----------------------
-  // every row is shared by `split` warps
-  const int split = max(1, kVerifyWarps / R);
-  for (int item = warp; item < R * split; item += kVerifyWarps) {
-    const int r = item / split, part = item - r * split;
-    uint64_t best = 0ull;
-    for (int i = part * 32 + lane; i < len; i += 32 * split) {
-      const uint64_t p = pack52(S.z(r, i), static_cast<uint32_t>(lo + i));
-      best = p > best ? p : best;
+  // A block of 1024 threads keeps every scheduler of the SM busy, so what counts is the total number of instructions: the rows
+  // are walked four elements per shared-memory load, a warp staying inside one row (rows padded to 32 groups of four), and only
+  // the warps that hold data reduce.
+  const int n4 = (len + 3) / 4, n4p = (n4 + 31) & ~31;                      // groups of four elements per row of the slice
+  const int split = max(1, kVerifyWarps / R);                              // without the shared-memory copy every row is shared by `split` warps
+  const int n_red = cached ? n4p / 32 : split;                             // partial results per row in s_red
+  if (cached) {
+    // stochastic: the value alone (a 32-bit key); greedy: value and lowest index together (the 52-bit pack)
+    for (int i0 = 0; i0 < R * n4p; i0 += kVerifyBlock) {
+      const int r0 = (i0 + (tid & ~31)) / n4p;
+      if (r0 >= R) break;                                                 // warp-uniform
+      const int item = i0 + tid, c4 = item - r0 * n4p;
+      const int left = len - 4 * c4;                                      // 4 except in a ragged last group
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c4 < n4) x = reinterpret_cast<const float4*>(zs + r0 * per)[c4];
+      if (stochastic) {
+        uint32_t key = 0u;
+        if (c4 < n4) {
+          key = fkey(x.x);
+          if (left > 1) key = max(key, fkey(x.y));
+          if (left > 2) key = max(key, fkey(x.z));
+          if (left > 3) key = max(key, fkey(x.w));
+        }
+        key = warp_max_u32(key);
+        if (lane == 0) s_red[r0][c4 >> 5] = static_cast<uint64_t>(key) << 20;
+      } else {
+        uint64_t best = 0ull;
+        if (c4 < n4) {
+          const uint32_t i4 = static_cast<uint32_t>(lo + 4 * c4);
+          best = pack52(x.x, i4);
+          if (left > 1) { const uint64_t p = pack52(x.y, i4 + 1u); best = p > best ? p : best; }
+          if (left > 2) { const uint64_t p = pack52(x.z, i4 + 2u); best = p > best ? p : best; }
+          if (left > 3) { const uint64_t p = pack52(x.w, i4 + 3u); best = p > best ? p : best; }
+        }
+        best = warp_max_u64(best);
+        if (lane == 0) s_red[r0][c4 >> 5] = best;
+      }
     }
-    best = warp_max_u64(best);
-    if (lane == 0) s_red[r][part] = best;
-  }
-  __syncthreads();
-  if (tid < R && !(P.withhold && b == 0)) {
-    uint64_t best = 0ull;
-    for (int k = 0; k < split; k++) best = s_red[tid][k] > best ? s_red[tid][k] : best;
-    publish(&ws->best[tid][b], best);
+    __syncthreads();
+    if (tid < R && !(P.withhold && b == 0)) {
+      uint64_t best = 0ull;
+      for (int k = 0; k < n_red; k++) best = s_red[tid][k] > best ? s_red[tid][k] : best;
+      publish(&ws->best[tid][b], best);
+    }
+  } else {
+    for (int item = warp; item < R * split; item += kVerifyWarps) {
+      const int r = item / split, part = item - r * split;
+      uint64_t best = 0ull;
+      for (int i = part * 32 + lane; i < len; i += 32 * split) {
+        const uint64_t p = pack52(S.z(r, i), static_cast<uint32_t>(lo + i));
+        best = p > best ? p : best;
+      }
+      best = warp_max_u64(best);
+      if (lane == 0) s_red[r][part] = best;
+    }
+    __syncthreads();
+    if (tid < R && !(P.withhold && b == 0)) {
+      uint64_t best = 0ull;
+      for (int k = 0; k < n_red; k++) best = s_red[tid][k] > best ? s_red[tid][k] : best;
+      publish(&ws->best[tid][b], best);
+    }
   }
   __syncthreads();                                                        // s_red is reused below
 
@@ -316,6 +372,37 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   } else {
     // ---- phase 1: every block learns the row maxima; fixed-point mass of every row's kept set; the drafts' own weights -------
     consume_rows<false>(&ws->best[0][0], R, G, s_best, s_red, limit, &failed, vals);
+    if (cached) {
+      // the same walk as for the maxima: four elements per load, two packed weight evaluations, one warp sum per 128 elements
+      for (int i0 = 0; i0 < R * n4p; i0 += kVerifyBlock) {
+        const int r0 = (i0 + (tid & ~31)) / n4p;
+        if (r0 >= R) break;                                               // warp-uniform
+        const int item = i0 + tid, c4 = item - r0 * n4p;
+        uint64_t w = 0ull;
+        if (c4 < n4) {
+          const float vmax = pack52_value(s_best[r0]);
+          const float tau = P.tau ? P.tau[row0 + r0] : -INFINITY;
+          const float4 x = reinterpret_cast<const float4*>(zs + r0 * per)[c4];
+          const int left = len - 4 * c4;
+          uint64_t w0, w1, w2, w3;
+          weight_q40_x2(x.x, x.y, vmax, c2, w0, w1);
+          weight_q40_x2(x.z, x.w, vmax, c2, w2, w3);
+          if (x.x >= tau) w += w0;
+          if (left > 1 && x.y >= tau) w += w1;
+          if (left > 2 && x.z >= tau) w += w2;
+          if (left > 3 && x.w >= tau) w += w3;
+        }
+        const uint32_t wl = warp_sum_u32(static_cast<uint32_t>(w) & 0x3FFFFFu), wh = warp_sum_u32(static_cast<uint32_t>(w >> 22));
+        if (lane == 0) s_red[r0][c4 >> 5] = static_cast<uint64_t>(wl) + (static_cast<uint64_t>(wh) << 22);
+      }
+      if (tid < L) {                                                      // the drafts' own weights: the block whose slice holds the draft
+        const int d = s_drafts[tid];
+        if (d >= lo && d < hi) {
+          const float z = S.z(tid, d - lo), tau = P.tau ? P.tau[row0 + tid] : -INFINITY;
+          publish(&ws->draft_w[tid], (z >= tau) ? weight_q40(z, pack52_value(s_best[tid]), c2) : 0ull);
+        } else if ((d < 0 || d >= V) && b == 0) publish(&ws->draft_w[tid], 0ull);     // an id outside the vocabulary: probability 0
+      }
+    } else {
     for (int item = warp; item < R * split; item += kVerifyWarps) {
       const int r = item / split, part = item - r * split;
       const float vmax = pack52_value(s_best[r]);
@@ -337,20 +424,22 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
         }
       }
     }
+    }
     __syncthreads();
     if (tid < R) {
       uint64_t w = 0ull;
-      for (int k = 0; k < split; k++) w += s_red[tid][k];
+      for (int k = 0; k < n_red; k++) w += s_red[tid][k];
       s_own[tid] = w;
       publish(&ws->mass[tid][b], w);
     }
     __syncthreads();
     // ---- phase 2: row masses; accept tests (every block, identically); this slice's share of the residual -------------------
+    const unsigned long long dw_first = tid < L ? peek(&ws->draft_w[tid]) : 0ull;   // in flight while the masses are consumed
     consume_rows<true>(&ws->mass[0][0], R, G, s_mass, s_red, limit, &failed, vals);
     if (tid < 32) {
       bool reject = false;
       if (tid < L) {
-        const uint64_t dw = consume(&ws->draft_w[tid], limit, &failed), mass = s_mass[tid];
+        const uint64_t dw = consume(&ws->draft_w[tid], limit, &failed, dw_first), mass = s_mass[tid];
         const float pd = (my_draft >= 0 && my_draft < V && mass > 0ull) ? prob_q40(dw, mass) : 0.0f;
         reject = __fmul_rn(my_u, my_q) >= pd;
         if (b == 0 && P.out_p_draft) P.out_p_draft[tid] = pd;

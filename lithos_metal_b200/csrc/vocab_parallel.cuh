@@ -126,6 +126,11 @@ __global__ void __launch_bounds__(kVpMaxCandidates, 1) vocab_merge_kernel(VpMerg
     const float top_p = P.top_p ? P.top_p[row] : P.top_p_s;
     const float min_p = P.min_p ? P.min_p[row] : P.min_p_s;
     const double T64 = static_cast<double>(T), inv_t = 1.0 / T64;
+    uint32_t edge = 0u;
+    if (!(T > 0.0f)) {                                                     // a per-row temperature the host could not check: no token
+      if (tid == 0) { P.out_tokens[row] = -1; if (P.out_tau) P.out_tau[row] = -INFINITY; if (P.out_status) P.out_status[row] = kStatusBadParam; }
+      continue;
+    }
     // ---- gather: candidate t of the concatenated shards
     if (tid == 0) { s.hit = kVpMaxCandidates; s.token = -1; s.status = 0u; }
     __syncthreads();
@@ -215,6 +220,10 @@ __global__ void __launch_bounds__(kVpMaxCandidates, 1) vocab_merge_kernel(VpMerg
         if (!have_tau || static_cast<double>(tau_p) > tau64) tau64 = tau_p;
         have_tau = true;
       }
+      // The masses are summed here in another order than on one GPU (per shard, then over the sorted candidates): a boundary of the
+      // cumulative mass within 1e-12 of the target, on either side, may be decided differently and is reported like there.
+      const bool near = run_end && fabs(mi - target) <= 1e-12 * total;
+      if (__syncthreads_or(near)) edge = LM_STATUS_TOPP_EDGE;
     }
     if (has_m) {
       const double tau_m = static_cast<double>(vmax) + T64 * log(static_cast<double>(min_p));
@@ -223,7 +232,7 @@ __global__ void __launch_bounds__(kVpMaxCandidates, 1) vocab_merge_kernel(VpMerg
     }
     const float tau = have_tau ? __double2float_rn(tau64) : -INFINITY;
     const bool kept = valid && val >= tau;
-    uint32_t status = status0;
+    uint32_t status = status0 | edge;
     // ---- the draw
     if (P.draw == LM_DRAW_INVERSE_CDF) {
       const float c2 = exp2_scale(T);

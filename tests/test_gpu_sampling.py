@@ -443,3 +443,25 @@ def test_penalised_rows_equal_the_reference(golden):
         np.testing.assert_array_equal(r.tau.cpu().numpy(), np.array(g["tau"], dtype=np.float32))
         got = r.tokens.cpu().numpy()
         assert np.all((got == np.array(g["tokens_seed12345_step1"])) | ((status & 4) != 0))
+
+
+def test_two_streams_sample_at_once_with_their_own_workspaces():
+    """Calls that can overlap on the GPU must not share scratch: the host layer keeps one workspace per stream. Two streams run
+    different batches again and again, side by side; each gets what it gets alone."""
+    cfgs = [inputs.config3(rows=48, vocab=32768, hist_len=256, seed=s) for s in (71, 72)]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    work = []
+    for cfg in cfgs:
+        knobs = {k: torch.from_numpy(cfg[k]).cuda() for k in ("temperature", "top_k", "top_p")}
+        work.append((bf16_tensor(cfg["logits"]), lm.SamplingParams(draw="inverse_cdf", repetition_penalty=1.1, presence_penalty=0.5, **knobs),
+                     torch.from_numpy(cfg["history"]).cuda(), torch.from_numpy(cfg["uniforms"]).cuda()))
+    alone = [lm.sample(x, p, history=h, uniforms=u).tokens.clone() for x, p, h, u in work]
+    torch.cuda.synchronize()
+    got = [[], []]
+    for _ in range(20):
+        for i, (x, p, h, u) in enumerate(work):
+            with torch.cuda.stream(streams[i]):
+                got[i].append(lm.sample(x, p, history=h, uniforms=u).tokens)
+    torch.cuda.synchronize()
+    for i in range(2):
+        assert all(torch.equal(t, alone[i]) for t in got[i])

@@ -31,7 +31,7 @@ def _logits(rows, vocab, seed, dtype):
     return torch.from_numpy(z).cuda(), z
 
 
-@pytest.mark.parametrize("rows,vocab,dtype", [(8, 151936, "bf16"), (1, 151936, "f32"), (300, 4096, "bf16"), (37, 1000, "f32")])
+@pytest.mark.parametrize("rows,vocab,dtype", [(8, 151936, "bf16"), (1, 151936, "f32"), (64, 151936, "bf16"), (300, 4096, "bf16"), (37, 1000, "f32")])
 def test_static_scratch_argmax_equals_the_workspace_one(rows, vocab, dtype):
     L = _lib.lib()
     x, host = _logits(rows, vocab, rows + vocab, dtype)
@@ -55,3 +55,26 @@ def test_static_scratch_rejects_what_does_not_fit():
     assert rc == -4 and b"supported range" in L.lm_error_string(rc)
     assert L.lm_argmax_static(None, _lib.DTYPE_BF16, 4, 64, 64, out.data_ptr(), None) == -1
     assert L.lm_argmax_static(None, _lib.DTYPE_BF16, 0, 64, 64, None, None) == 0
+
+
+def test_static_scratch_allocates_nothing_and_survives_a_larger_call_before_a_smaller_one():
+    """A call that splits many rows over several blocks dirties most of the library's scratch; the smaller call behind it must
+    still be right (the entry point clears what it uses), and neither call may take device memory: the free memory the driver
+    reports and the bytes torch has handed out are the same before and after."""
+    L = _lib.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    big, big_host = _logits(_lib.ARGMAX_STATIC_MAX_ROWS, 32768, 11, "bf16")   # the largest row count the scratch holds
+    wide, wide_host = _logits(64, 151936, 12, "bf16")                        # 64 rows x 151936: split over several blocks per row
+    small, small_host = _logits(3, 151936, 13, "f32")
+    outs = [torch.full((t.shape[0],), -7, dtype=torch.int32, device="cuda") for t in (big, wide, small)]
+    L.lm_argmax_static(small.data_ptr(), _lib.DTYPE_F32, 3, 151936, 151936, outs[2].data_ptr(), stream)   # first use on this device: its set-up
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    held0 = torch.cuda.memory_allocated()
+    for x, out, code in ((big, outs[0], _lib.DTYPE_BF16), (wide, outs[1], _lib.DTYPE_BF16), (small, outs[2], _lib.DTYPE_F32)):
+        out.fill_(-7)
+        assert L.lm_argmax_static(x.data_ptr(), code, x.shape[0], x.shape[1], x.stride(0), out.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == held0
+    for out, host in zip(outs, (big_host, wide_host, small_host)):
+        assert out.cpu().tolist() == host.argmax(-1).tolist()
