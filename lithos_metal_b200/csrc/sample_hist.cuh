@@ -330,8 +330,13 @@ __device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint
     const uint32_t slot = static_cast<uint32_t>(sg) * kGrpSlots + 2u * lane;
     const uint32_t c0 = w & 0xFFFFu, c1 = w >> 16;
     const float v0 = hcode_val(code_of_slot(slot)), v1 = hcode_val(code_of_slot(slot + 1u));
-    if (c0 && v0 >= tau) mine += static_cast<uint64_t>(c0) * weight_q40(v0, vmax, c2);
-    if (c1 && v1 >= tau) mine += static_cast<uint64_t>(c1) * weight_q40(v1, vmax, c2);
+    const bool k0 = c0 && v0 >= tau, k1 = c1 && v1 >= tau;
+    if (k0 || k1) {
+      uint64_t w0, w1;
+      weight_q40_x2(v0, v1, vmax, c2, w0, w1);
+      if (k0) mine += static_cast<uint64_t>(c0) * w0;
+      if (k1) mine += static_cast<uint64_t>(c1) * w1;
+    }
   }
   if (tid == 0 && s.cz && 0.0f >= tau) mine += static_cast<uint64_t>(s.cz) * weight_q40(0.0f, vmax, c2);
   for (uint32_t j = tid; j < n_b; j += kHB) {
@@ -342,7 +347,12 @@ __device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint
   for (uint32_t i = tid; i < n_side; i += kHB) {
     const uint32_t code = s.side_raw[i];
     const float zr = hcode_val(code), zf = penalised_value(code, P.rho, P.pi);
-    const uint64_t wf = zf >= tau ? weight_q40(zf, vmax, c2) : 0ull, wr = zr >= tau ? weight_q40(zr, vmax, c2) : 0ull;
+    const bool kr = zr >= tau, kf = zf >= tau;
+    if (!kr && !kf) continue;                                              // kept neither way: nothing to correct
+    uint64_t wf, wr;
+    weight_q40_x2(zf, zr, vmax, c2, wf, wr);
+    if (!kf) wf = 0ull;
+    if (!kr) wr = 0ull;
     if (wf != wr) atomicAdd(&s.seg_fix[s.ids[i] >> 8], static_cast<unsigned long long>(wf - wr));   // modulo 2^64: the segment total is never negative
   }
   const uint64_t total = block_sum_u64(mine, s.scratch);                  // (two barriers: seg_fix is complete behind them)
@@ -355,9 +365,9 @@ __device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint
   const uint4 neg = make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);
   const int n_seg = (n_chunks + kSegChunks - 1) / kSegChunks;
   uint64_t run = 0ull, before = 0ull, found_total = 0ull;
-  int found = -1, buf = 0;
+  int found = -1, found_b0 = 0, buf = 0;
+  uint4 q[kDrawIters];                                                    // the chunks of the batch in hand (kept for the locate step)
   for (int b0 = 0; b0 < n_seg && found < 0; b0 += kBatchSegs, buf ^= 1) {
-    uint4 q[kDrawIters];
 #pragma unroll
     for (int it = 0; it < kDrawIters; it++) {
       const int k = b0 + it * kHW + warp, seg = forward ? k : n_seg - 1 - k, cc = seg * kSegChunks + lane;
@@ -396,36 +406,42 @@ __device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint
       const int idx = __shfl_sync(kFull, hit_a ? 2 * lane : 2 * lane + 1, src);
       before = __shfl_sync(kFull, hit_a ? excl : excl + a, src);
       found_total = __shfl_sync(kFull, hit_a ? a : b, src);
-      found = b0 + idx;
+      found = b0 + idx; found_b0 = b0;
     }
     run += __shfl_sync(kFull, incl, 31);
   }
   if (found < 0) return -1;                                               // cannot happen: the segments sum to `total`
-  // ---- inside the segment: the first cumulative weight, in index order, that exceeds the target ----------------------------
-  if (warp == 0) {
-    const int seg = forward ? found : n_seg - 1 - found;
-    const uint64_t prefix = forward ? before : total - before - found_total;   // the weight of everything before the segment
-    const uint64_t local_target = target - prefix;
-    const int cc = seg * kSegChunks + lane;
-    const uint4 q = cc < n_chunks ? __ldg(p4 + cc) : neg;
-    const uint32_t bits = (pen != nullptr && cc < n_chunks) ? ((pen[cc >> 2] >> ((cc & 3) * 8)) & 0xFFu) : 0u;
-    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-    uint64_t w[kChunk], sum = 0ull;
+  // ---- inside the segment: the first cumulative weight, in index order, that exceeds the target. The warp that summed the
+  // segment still holds its chunks in registers: no second load.
+  {
+    const int idx = found - found_b0;                                     // position of the segment in its batch: it * kHW + warp
+    if (warp == idx % kHW) {
+      const int seg = forward ? found : n_seg - 1 - found;
+      const uint64_t prefix = forward ? before : total - before - found_total;   // the weight of everything before the segment
+      const uint64_t local_target = target - prefix;
+      const int cc = seg * kSegChunks + lane;
+      uint4 qf = q[0];
 #pragma unroll
-    for (int e = 0; e < kChunk; e++) {
-      const uint32_t code = (e & 1) ? (words[e >> 1] >> 16) : (words[e >> 1] & 0xFFFFu);
-      const float z = ((bits >> e) & 1u) ? penalised_value(code, P.rho, P.pi) : hcode_val(code);
-      w[e] = (cc < n_chunks && z >= tau) ? weight_q40(z, vmax, c2) : 0ull;
-      sum += w[e];
-    }
-    uint64_t incl = sum;
+      for (int it = 1; it < kDrawIters; it++) if (idx / kHW == it) qf = q[it];
+      const uint32_t bits = (pen != nullptr && cc < n_chunks) ? ((pen[cc >> 2] >> ((cc & 3) * 8)) & 0xFFu) : 0u;
+      const uint32_t words[4] = {qf.x, qf.y, qf.z, qf.w};
+      uint64_t w[kChunk], sum = 0ull;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { const uint64_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
-    const uint64_t excl = incl - sum;
-    if (excl <= local_target && local_target < incl) {
-      uint64_t r = excl;
+      for (int e = 0; e < kChunk; e++) {
+        const uint32_t code = (e & 1) ? (words[e >> 1] >> 16) : (words[e >> 1] & 0xFFFFu);
+        const float z = ((bits >> e) & 1u) ? penalised_value(code, P.rho, P.pi) : hcode_val(code);
+        w[e] = (cc < n_chunks && z >= tau) ? weight_q40(z, vmax, c2) : 0ull;
+        sum += w[e];
+      }
+      uint64_t incl = sum;
 #pragma unroll
-      for (int e = 0; e < kChunk; e++) { r += w[e]; if (w[e] && r > local_target) { s.token = cc * kChunk + e; break; } }
+      for (int o = 1; o < 32; o <<= 1) { const uint64_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
+      const uint64_t excl = incl - sum;
+      if (excl <= local_target && local_target < incl) {
+        uint64_t r = excl;
+#pragma unroll
+        for (int e = 0; e < kChunk; e++) { r += w[e]; if (w[e] && r > local_target) { s.token = cc * kChunk + e; break; } }
+      }
     }
   }
   __syncthreads();
@@ -828,12 +844,15 @@ __global__ void __launch_bounds__(kHB, 2) sample_hist_kernel(SampleDev P, const 
   for (;;) {
     const int i = item[0], in = item[1];
     if (i >= n) break;
-    __syncthreads();
-    if (threadIdx.x == 0) { item[0] = in; item[1] = in < n ? atomicAdd(next_item, 1) : n; }
+    // the item after next is fetched now and only looked at when this row is done: the counter's round trip hides behind the row
+    int fetched = n;
+    if (threadIdx.x == 0 && in < n) fetched = atomicAdd(next_item, 1);
     const int row = list ? list[i] : i;
     int next = in < n ? (list ? list[in] : in) : -1;
     if (next >= P.rows) next = -1;
     if (row >= 0 && row < P.rows) sample_row_hist(P, row, next, s, pen, redo, n_redo);   // (a list entry is a row index by construction)
+    __syncthreads();
+    if (threadIdx.x == 0) { item[0] = in; item[1] = fetched; }
     __syncthreads();
   }
 }

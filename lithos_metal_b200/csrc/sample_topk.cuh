@@ -356,6 +356,18 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   const uint32_t n_hit = c.n_hit;                                           // (complete: every warp is past the pass)
   if (n_hit > 2048u) return false;
 
+  // the raw logits of the penalised positions are fetched now, after the pass (the row has just gone through L2), and used
+  // behind the expansion below: both sets of loads are in flight together
+  constexpr int kGather = kTopkHist / kTB;
+  uint32_t ids[kGather]; uint16_t raws[kGather];
+  if (pen_on) {
+#pragma unroll
+    for (int j = 0; j < kGather; j++) {
+      const uint32_t i = j * kTB + tid;
+      ids[j] = i < c.n_side ? c.side_id[i] : 0u;
+      raws[j] = __ldg(rowp + ids[j]);
+    }
+  }
   // ---- the noted chunks, expanded: their logits come back from L2; penalised positions are skipped (the hash set knows them)
   constexpr int kExpand = 1024 / kTB;                                       // chunk reloads in flight per thread
   for (uint32_t e0 = 0; e0 < n_hit; e0 += kTB * kExpand) {                  // uniform trip count
@@ -387,16 +399,7 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   }
   // ---- the penalised logits, from the list ---------------------------------------------------------------------------------
   if (pen_on) {
-    // their raw logits are fetched now, after the pass: the row has just gone through L2
     const uint32_t n_side = c.n_side;
-    constexpr int kGather = kTopkHist / kTB;
-    uint32_t ids[kGather]; uint16_t raws[kGather];
-#pragma unroll
-    for (int j = 0; j < kGather; j++) {
-      const uint32_t i = j * kTB + tid;
-      ids[j] = i < n_side ? c.side_id[i] : 0u;
-      raws[j] = __ldg(rowp + ids[j]);
-    }
 #pragma unroll
     for (int j = 0; j < kGather; j++) {
       const uint32_t i = j * kTB + tid;
@@ -638,18 +641,18 @@ __global__ void __launch_bounds__(kTB, kTopkPerSM) sample_topk_kernel(SampleDev 
   for (;;) {
     const int row = item[0], next = item[1];
     if (row >= P.rows) break;
-    __syncthreads();
-    if (threadIdx.x == 0) { item[0] = next; item[1] = next < P.rows ? atomicAdd(&counters[0], 1) : P.rows; }
+    // the row after next is fetched now and only looked at when this row is done: the counter's round trip hides behind the row
+    int fetched = P.rows;
+    if (threadIdx.x == 0 && next < P.rows) fetched = atomicAdd(&counters[0], 1);
     if (!topk_row_eligible(P, row)) {                                       // not this kernel's row: listed here, or already by sample_classify_kernel
       if (list_others && threadIdx.x == 0) list[atomicAdd(&counters[1], 1)] = row;
-      __syncthreads();                                                      // thread 0 has moved item[] on: nobody reads it again before that
-      continue;
+    } else {
+      const bool done = topk_row(P, row, next < P.rows ? next : -1, c);
+      if (threadIdx.x == 0 && !done) list[atomicAdd(&counters[1], 1)] = row;
     }
-    const bool done = topk_row(P, row, next < P.rows ? next : -1, c);
+    __syncthreads();                                                        // nobody reads item[] any more
+    if (threadIdx.x == 0) { item[0] = next; item[1] = fetched; }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      if (!done) list[atomicAdd(&counters[1], 1)] = row;
-    }
   }
   // This grid may have been started before the grid launched ahead of it had finished (programmatic stream serialization). The
   // stream takes the end of this grid for the end of both, so no block leaves before the earlier grid is complete.
