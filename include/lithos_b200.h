@@ -60,6 +60,7 @@ extern "C" {
 #define LM_STATUS_NEAR_TIE 4u     /* Gumbel draw: best and second-best key closer than 4e-6 (float32 log is library-specific) */
 #define LM_STATUS_TOPP_EDGE 8u    /* top-p: cumulative mass within 1e-12 (relative) of the target at the boundary */
 #define LM_STATUS_CANDIDATE_PATH 64u /* the row was finished by the one-pass candidate path (informational) */
+#define LM_STATUS_TILE_DECLINED 128u /* lm_tile_finish only: the row was not sampled (token -1); materialise it and call lm_sample */
 
 #define LM_MAX_VOCAB 1048576
 
@@ -406,6 +407,48 @@ typedef struct lm_confidence_args {
 } lm_confidence_args;
 
 LM_API int lm_confidence(const lm_confidence_args* args);
+
+/*
+ * Sampling from logits that arrive tile by tile: the consumer side of the boundary between the vocabulary projection and the
+ * sampler.
+ *
+ * The reference writes the projection's logits [T, V] to memory in BF16 (lm_head_forward, monolith/nn/lm_head.py:50-60) and the
+ * sampler dispatches read them back (monolith/kernels.py:720-775). A projection whose epilogue holds a tile of logits
+ * [rows, up to LM_TILE_MAX_COLS columns] hands it to lm_tile_consume instead (or calls the device function of the same name
+ * from its epilogue, csrc/sample_tiles.cuh), and [T, V] never has to exist: per row the library keeps the running maximum, the
+ * running softmass and the logits that can still be among the row's top_k, in a caller-owned state buffer.
+ *
+ *   lm_tile_begin    clears the state of `rows` rows (stream-ordered);
+ *   lm_tile_consume  takes the columns col0 .. col0 + cols of every row; tiles may come in any column order, each column once;
+ *                    FP32 tiles are rounded to BF16 first, as the projection's store would;
+ *   lm_tile_finish   writes what lm_sample would write for the same rows and knobs (tokens, tau, status with
+ *                    LM_STATUS_CANDIDATE_PATH), bit-identical; `logits`, `workspace`, `history`, `out_stats` and `out_probs`
+ *                    of the lm_sample_args are not used and history / out_stats / out_probs must be NULL.
+ *
+ * Rows this path does not take get token -1 and LM_STATUS_TILE_DECLINED: rows without a top_k in 1..1024, greedy rows
+ * (temperature 0: use lm_argmax on the tiles' maxima instead), rows with a NaN or +inf, rows whose top-k boundary lies at or
+ * below zero or whose top-p boundary cannot be decided from the FP32 softmass. The caller materialises those rows and calls
+ * lm_sample; a caller with repetition / presence penalties does so for every row.
+ */
+#define LM_TILE_MAX_COLS 2048
+typedef struct lm_tile_args {
+  uint32_t struct_size;        /* sizeof(lm_tile_args) */
+  int32_t dtype;               /* LM_DTYPE_BF16 or LM_DTYPE_F32: the tile's element type */
+  const void* tile;            /* [rows, tile_stride]: element (r, j) is the logit of row r, column col0 + j */
+  int64_t rows, vocab;
+  int64_t tile_stride;         /* elements between rows of the tile (>= cols) */
+  int64_t col0, cols;          /* 0 <= col0, col0 + cols <= vocab, 1 <= cols <= LM_TILE_MAX_COLS */
+  const float* temperature; float temperature_s;   /* as in lm_sample_args; the same values must be given to lm_tile_finish */
+  const int32_t* top_k; int32_t top_k_s;
+  void* state;                 /* lm_tile_state_bytes(rows) bytes, 256-byte aligned, device memory */
+  size_t state_bytes;
+  void* stream;
+} lm_tile_args;
+
+LM_API size_t lm_tile_state_bytes(int64_t rows);
+LM_API int lm_tile_begin(void* state, size_t state_bytes, int64_t rows, void* stream);
+LM_API int lm_tile_consume(const lm_tile_args* args);
+LM_API int lm_tile_finish(const lm_sample_args* sample, void* state, size_t state_bytes);
 
 /* Scratch sizes (host calls, no CUDA work). Stand in for sample_workspace (monolith/kernels.py:777-779). */
 LM_API size_t lm_workspace_bytes(int64_t rows, int64_t vocab);

@@ -18,6 +18,8 @@ RESIDUAL_INVERSE_CDF, RESIDUAL_GUMBEL = 0, 1
 VERIFY_SELFTEST_WITHHOLD = 1
 STATUS_GENERIC_PATH, STATUS_NAN, STATUS_NEAR_TIE, STATUS_TOPP_EDGE, STATUS_OVERFLOW = 1, 2, 4, 8, 32
 STATUS_CANDIDATE_PATH = 64
+STATUS_TILE_DECLINED = 128
+TILE_MAX_COLS = 2048
 VOCAB_MAX_CANDIDATES = 1024
 MAX_DRAFT = 15
 MAX_VOCAB = 1048576
@@ -38,6 +40,15 @@ class SampleArgs(C.Structure):
         ("out_status", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
         ("step_state", C.c_void_p), ("t_max", C.c_int32), ("gamma_max", C.c_int32),
+    ]
+
+
+class TileArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("dtype", C.c_int32), ("tile", C.c_void_p), ("rows", C.c_int64), ("vocab", C.c_int64),
+        ("tile_stride", C.c_int64), ("col0", C.c_int64), ("cols", C.c_int64),
+        ("temperature", C.c_void_p), ("temperature_s", C.c_float), ("top_k", C.c_void_p), ("top_k_s", C.c_int32),
+        ("state", C.c_void_p), ("state_bytes", C.c_size_t), ("stream", C.c_void_p),
     ]
 
 
@@ -94,7 +105,7 @@ class VocabArgs(C.Structure):
     ]
 
 
-EXPORTS = ["lm_accept_scan", "lm_verify_select", "lm_advance", "lm_step_state_bytes", "lm_sample", "lm_argmax", "lm_argmax_static", "lm_vocab_local", "lm_vocab_merge", "lm_vocab_record_bytes", "lm_vocab_candidate_cap", "lm_verify", "lm_draft_q", "lm_confidence", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
+EXPORTS = ["lm_accept_scan", "lm_verify_select", "lm_advance", "lm_step_state_bytes", "lm_sample", "lm_argmax", "lm_argmax_static", "lm_vocab_local", "lm_vocab_merge", "lm_vocab_record_bytes", "lm_vocab_candidate_cap", "lm_verify", "lm_draft_q", "lm_confidence", "lm_tile_state_bytes", "lm_tile_begin", "lm_tile_consume", "lm_tile_finish", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
            "lm_error_string", "lm_last_cuda_error", "lm_device_sm_count"]
 
 _lib = None
@@ -116,6 +127,14 @@ def lib():
         L.lm_sample.argtypes = [C.POINTER(SampleArgs)]
         L.lm_verify.restype = C.c_int
         L.lm_verify.argtypes = [C.POINTER(VerifyArgs)]
+        L.lm_tile_state_bytes.restype = C.c_size_t
+        L.lm_tile_state_bytes.argtypes = [C.c_int64]
+        L.lm_tile_begin.restype = C.c_int
+        L.lm_tile_begin.argtypes = [C.c_void_p, C.c_size_t, C.c_int64, C.c_void_p]
+        L.lm_tile_consume.restype = C.c_int
+        L.lm_tile_consume.argtypes = [C.POINTER(TileArgs)]
+        L.lm_tile_finish.restype = C.c_int
+        L.lm_tile_finish.argtypes = [C.POINTER(SampleArgs), C.c_void_p, C.c_size_t]
         L.lm_confidence.restype = C.c_int
         L.lm_confidence.argtypes = [C.POINTER(ConfidenceArgs)]
         L.lm_draft_q.restype = C.c_int

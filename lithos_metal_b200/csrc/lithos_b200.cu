@@ -11,6 +11,7 @@
 #include "sample_generic.cuh"
 #include "sample_hist.cuh"
 #include "sample_topk.cuh"
+#include "sample_tiles.cuh"
 #include "verify.cuh"
 #include "draft_q.cuh"
 #include "vocab_parallel.cuh"
@@ -100,7 +101,7 @@ static int sm_count(int* out) {
 
 // Kernels that need more than 48 KB of dynamic shared memory must be told so once per device (the attribute belongs to the
 // device's copy of the function); remembered per device and kernel, raised when a call needs more.
-enum KernelSlot { kSlotFast, kSlotTopk, kSlotGeneric, kSlotVocabLocal, kSlotVerify, kSlotDraftQ, kSlotCount };
+enum KernelSlot { kSlotFast, kSlotTopk, kSlotGeneric, kSlotVocabLocal, kSlotVerify, kSlotDraftQ, kSlotTileFinish, kSlotCount };
 
 static int ensure_dynamic_smem(KernelSlot slot, const void* func, size_t bytes) {
   if (bytes <= 48 * 1024) return LM_OK;
@@ -117,6 +118,27 @@ static int ensure_dynamic_smem(KernelSlot slot, const void* func, size_t bytes) 
   if (e != cudaSuccess) return cuda_fail(e);
   if (tracked) granted[dev][slot] = bytes;
   return LM_OK;
+}
+
+static bool sample_has_penalties(const lm_sample_args* a) {
+  return a->history != nullptr && a->hist_len > 0 && !(a->repetition_penalty == 1.0f && a->presence_penalty == 0.0f);
+}
+
+// The device-side view of a validated lm_sample_args.
+static SampleDev sample_dev(const lm_sample_args* a) {
+  SampleDev P;
+  P.logits = a->logits; P.dtype = a->dtype; P.rows = static_cast<int>(a->rows); P.vocab = static_cast<int>(a->vocab); P.row_stride = a->row_stride;
+  P.temperature = a->temperature; P.temperature_s = a->temperature_s; P.top_k = a->top_k; P.top_k_s = a->top_k_s;
+  P.top_p = a->top_p; P.top_p_s = a->top_p_s; P.min_p = a->min_p; P.min_p_s = a->min_p_s;
+  P.flags = a->flags; P.draw = a->draw;
+  const bool pen = sample_has_penalties(a);
+  P.history = pen ? a->history : nullptr; P.hist_len = static_cast<int>(a->hist_len); P.hist_stride = a->hist_stride;
+  P.rho = a->repetition_penalty; P.pi = a->presence_penalty;
+  P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
+  P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_stats = a->out_stats; P.out_probs = a->out_probs; P.probs_stride = a->probs_stride;
+  P.out_status = a->out_status;
+  P.state = static_cast<const uint32_t*>(a->step_state); P.t_max = a->t_max; P.g = a->gamma_max > 1 ? a->gamma_max : 1;
+  return P;
 }
 
 static size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
@@ -245,18 +267,8 @@ int lm_sample(const lm_sample_args* a) {
   // an all-greedy call needs no uniforms; a stochastic inverse-CDF call does
   if (a->draw == LM_DRAW_INVERSE_CDF && a->uniforms == nullptr && (a->temperature != nullptr || a->temperature_s > 0.0f)) return LM_E_INVALID;
 
-  SampleDev P;
-  P.logits = a->logits; P.dtype = a->dtype; P.rows = static_cast<int>(a->rows); P.vocab = static_cast<int>(a->vocab); P.row_stride = a->row_stride;
-  P.temperature = a->temperature; P.temperature_s = a->temperature_s; P.top_k = a->top_k; P.top_k_s = a->top_k_s;
-  P.top_p = a->top_p; P.top_p_s = a->top_p_s; P.min_p = a->min_p; P.min_p_s = a->min_p_s;
-  P.flags = a->flags; P.draw = a->draw;
-  const bool pen = a->history != nullptr && a->hist_len > 0 && !(a->repetition_penalty == 1.0f && a->presence_penalty == 0.0f);
-  P.history = pen ? a->history : nullptr; P.hist_len = static_cast<int>(a->hist_len); P.hist_stride = a->hist_stride;
-  P.rho = a->repetition_penalty; P.pi = a->presence_penalty;
-  P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
-  P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_stats = a->out_stats; P.out_probs = a->out_probs; P.probs_stride = a->probs_stride;
-  P.out_status = a->out_status;
-  P.state = static_cast<const uint32_t*>(a->step_state); P.t_max = a->t_max; P.g = a->gamma_max > 1 ? a->gamma_max : 1;
+  const bool pen = sample_has_penalties(a);
+  SampleDev P = sample_dev(a);
 
   int sms = 0;
   int rc = sm_count(&sms);
@@ -331,6 +343,64 @@ int lm_sample(const lm_sample_args* a) {
   const long long cap = fast ? sms : 8LL * sms;
   const int grid = static_cast<int>(a->rows < cap ? a->rows : cap);
   sample_generic_kernel<<<grid, kBlock, smem, st>>>(P, redo_list, redo_n);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+size_t lm_tile_state_bytes(int64_t rows) {
+  if (rows <= 0) return 0;
+  return align256(static_cast<size_t>(rows) * sizeof(TileRow)) + static_cast<size_t>(rows) * kTileListCap * sizeof(unsigned long long);
+}
+
+int lm_tile_begin(void* state, size_t state_bytes, int64_t rows, void* stream) {
+  if (rows < 0) return LM_E_INVALID;
+  if (rows == 0) return LM_OK;
+  if (rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
+  if (!state || (reinterpret_cast<uintptr_t>(state) & 255u) || state_bytes < lm_tile_state_bytes(rows)) return LM_E_WORKSPACE;
+  // only the per-row records: a list is read up to its record's count
+  const cudaError_t e = cudaMemsetAsync(state, 0, static_cast<size_t>(rows) * sizeof(TileRow), static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+int lm_tile_consume(const lm_tile_args* a) {
+  if (!a || a->struct_size != sizeof(lm_tile_args)) return LM_E_INVALID;
+  if (a->rows < 0 || a->vocab < 0 || (a->dtype != LM_DTYPE_BF16 && a->dtype != LM_DTYPE_F32)) return LM_E_INVALID;
+  if (a->rows == 0) return LM_OK;
+  if (!a->tile || a->cols < 1 || a->col0 < 0 || a->col0 + a->cols > a->vocab || a->tile_stride < a->cols) return LM_E_INVALID;
+  if (a->cols > LM_TILE_MAX_COLS || a->vocab > LM_MAX_VOCAB || a->rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
+  if (!a->state || (reinterpret_cast<uintptr_t>(a->state) & 255u) || a->state_bytes < lm_tile_state_bytes(a->rows)) return LM_E_WORKSPACE;
+  TileDev T;
+  T.tile = a->tile; T.dtype = a->dtype; T.rows = static_cast<int>(a->rows); T.vocab = static_cast<int>(a->vocab); T.tile_stride = a->tile_stride;
+  T.col0 = static_cast<int>(a->col0); T.cols = static_cast<int>(a->cols);
+  T.temperature = a->temperature; T.temperature_s = a->temperature_s; T.top_k = a->top_k; T.top_k_s = a->top_k_s;
+  T.rows_state = static_cast<TileRow*>(a->state);
+  T.lists = reinterpret_cast<unsigned long long*>(static_cast<char*>(a->state) + align256(static_cast<size_t>(a->rows) * sizeof(TileRow)));
+  tile_consume_kernel<<<T.rows, kTileBlock, 0, static_cast<cudaStream_t>(a->stream)>>>(T);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+int lm_tile_finish(const lm_sample_args* a, void* state, size_t state_bytes) {
+  if (!a || a->struct_size != sizeof(lm_sample_args)) return LM_E_INVALID;
+  if (a->rows < 0 || a->vocab < 0) return LM_E_INVALID;
+  if (a->draw != LM_DRAW_GUMBEL && a->draw != LM_DRAW_INVERSE_CDF) return LM_E_INVALID;
+  if (a->rows == 0) return LM_OK;
+  if (!a->out_tokens || a->history != nullptr || a->out_stats != nullptr || a->out_probs != nullptr) return LM_E_INVALID;
+  if (a->vocab > kTopkMaxVocab || a->rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
+  if (a->step_state != nullptr && lm_step_state_bytes(a->t_max, a->gamma_max) == 0) return LM_E_INVALID;
+  if (a->draw == LM_DRAW_INVERSE_CDF && a->uniforms == nullptr) return LM_E_INVALID;
+  if (!state || (reinterpret_cast<uintptr_t>(state) & 255u) || state_bytes < lm_tile_state_bytes(a->rows)) return LM_E_WORKSPACE;
+  SampleDev P = sample_dev(a);
+  P.logits = nullptr;
+  int sms = 0;
+  int rc = sm_count(&sms);
+  if (rc != LM_OK) return rc;
+  rc = ensure_dynamic_smem(kSlotTileFinish, reinterpret_cast<const void*>(tile_finish_kernel), sizeof(TopkSmem));
+  if (rc != LM_OK) return rc;
+  const long long cap = static_cast<long long>(kTopkPerSM) * sms;
+  const int grid = static_cast<int>(a->rows < cap ? a->rows : cap);
+  tile_finish_kernel<<<grid, kTB, sizeof(TopkSmem), static_cast<cudaStream_t>(a->stream)>>>(
+      P, static_cast<TileRow*>(state), reinterpret_cast<unsigned long long*>(static_cast<char*>(state) + align256(static_cast<size_t>(a->rows) * sizeof(TileRow))));
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }

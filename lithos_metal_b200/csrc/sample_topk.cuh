@@ -64,6 +64,12 @@ struct TopkSmem {
 
 static_assert(kTopkPerSM * (sizeof(TopkSmem) + 1024) <= 233472, "the blocks of the top-k kernel must fit one SM's shared memory");
 
+// What the candidate path knows about the softmass of the whole row when it reaches the exact phases: z_tilde approximates
+// sum_i 2^(z_i c + shift'), the exact mass relative to a maximum vmax is z_tilde * 2^(shift - vmax c); z_raw is the part of it
+// that was accumulated in FP32 (sequences of acc_terms additions), z_corr what was added and removed term by term (penalties);
+// ref is the logit the exponents were taken relative to (a logit of the row at or near its maximum).
+struct RowMass { bool need; double z_tilde, z_raw, z_corr, shift, acc_terms; float ref; };
+
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src) : "memory");
 }
@@ -154,6 +160,9 @@ __global__ void sample_classify_kernel(SampleDev P, int* list, int* n_list) {
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row < P.rows && !topk_row_eligible(P, row)) list[atomicAdd(n_list, 1)] = row;
 }
+
+struct TopkSmem;
+__device__ bool topk_finish(const SampleDev& P, int row, TopkSmem& c, uint32_t cut_code, const RowMass& zm);
 
 // One row. Every thread of the block calls with the same arguments; returns true when the row is finished, false when the
 // histogram kernel has to take it (nothing has been written then).
@@ -431,6 +440,26 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
   const double z_tilde = z_raw - z_sub + z_add;
   if (need_z && !(z_tilde > 0.0)) return false;                             // nothing left after the corrections (cancellation): the exact path
   __syncthreads();
+  RowMass zm;
+  zm.need = need_z; zm.z_tilde = z_tilde; zm.z_raw = z_raw; zm.z_corr = z_sub + z_add; zm.shift = -static_cast<double>(nb);
+  zm.ref = M; zm.acc_terms = 4.0 * n_it + 1.0;
+  return topk_finish(P, row, c, cut_code, zm);
+}
+
+// The exact phases of the candidate path, on what the pass (or a producer of logits tiles, sample_tiles.cuh) has left in shared
+// memory: c.key[0 .. c.n) = every logit of the row at or above the cutoff code as (monotone value key << 32) | ~index, c.bins[b] =
+// how many of them have BF16 code cut_code + b, c.wide set if one lies beyond the bins. `zm` is what is known about the mass of
+// the WHOLE row. Every thread of the block calls with the same arguments; returns true when the row is finished (token, tau
+// and status written), false when the exact path has to take it (nothing has been written then).
+__device__ bool topk_finish(const SampleDev& P, int row, TopkSmem& c, uint32_t cut_code, const RowMass& zm) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float T = P.temperature ? P.temperature[row] : P.temperature_s;
+  const int top_k = P.top_k ? P.top_k[row] : P.top_k_s;
+  const float top_p = P.top_p ? P.top_p[row] : P.top_p_s;
+  const float min_p = P.min_p ? P.min_p[row] : P.min_p_s;
+  const bool has_p = top_p > 0.0f && top_p < 1.0f, has_m = min_p > 0.0f;
+  const bool in_topk = (P.flags & LM_FLAG_TOPP_IN_TOPK) && has_p;
+  const double T64 = static_cast<double>(T), inv_t = 1.0 / T64;
   const int n = static_cast<int>(c.n);
   if (n > kTopkCap || n < top_k || c.wide) return false;
 
@@ -498,9 +527,9 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
     if (in_topk) total = c.cum[n_topk - 1];
     else {
       // The FP32 mass of the whole row, moved to the exact maximum. z_tilde approximates sum_i 2^(z_i c2a + nb); nb's own rounding
-      // is a common factor and is taken out exactly here (the true nb is used, not -M c2a).
+      // is a common factor and is taken out exactly here (zm.shift is the true -nb, not M c2a).
       const double c64 = 1.4426950408889634 * inv_t;
-      total = z_tilde * exp2(-static_cast<double>(nb) - static_cast<double>(vmax) * c64);
+      total = zm.z_tilde * exp2(zm.shift - static_cast<double>(vmax) * c64);
       // What separates it from sum_i 2^((z_i - vmax) c), relative, first order, worst case (u = 2^-24, the FP32 unit roundoff):
       //   - c2a = fl32(c): every term is off by a factor 2^(x_i delta), |delta| <= u, x_i = (z_i - M) c; weighted by the terms that is
       //     ln2 u E_w|x| <= u (ln V + 2 ln2 D): E_w[-x ln2] = H - ln Z <= ln V (H the entropy of the softmax, Z >= 1 relative to the
@@ -509,15 +538,15 @@ __device__ bool topk_row(const SampleDev& P, int row, int next, TopkSmem& c) {
       //     with |x| >= 32 weigh less than V 2^-32 altogether;
       //   - ex2.approx.ftz.f32: 2 ulp = 4 u;
       //   - each lane accumulates 4 n_it terms one after the other in FP32, then two accumulators and the lanes meet in FP64:
-      //     (4 n_it + 1) u;
+      //     (4 n_it + 1) u (zm.acc_terms);
       // These are relative to the mass the pass summed (z_raw), which holds the penalised positions at their raw values. The penalised
       // logits then enter as z_raw - z_sub + z_add, every term of z_sub and z_add with the per-term errors above (FMA, ex2, c2a on a
       // single term: 1.6e-6 covers them for |x| < 32); when penalised tokens carried most of the raw mass the band grows with them.
       // The band is this bound with a quarter added. A boundary of the cumulative mass inside it is decided by the exact path.
       const double u = 5.9604644775390625e-8;
-      const double D = fmax(0.0, (static_cast<double>(vmax) - static_cast<double>(M)) * c64);
-      const double rel = u * (12.5 + 1.3862943611198906 * D) + 6.6e-7 + 4.0 * u + (4.0 * n_it + 1.0) * u;
-      err = 1.25 * (rel * z_raw + 1.6e-6 * (z_sub + z_add)) * (total / z_tilde);
+      const double D = fmax(0.0, (static_cast<double>(vmax) - static_cast<double>(zm.ref)) * c64);
+      const double rel = u * (12.5 + 1.3862943611198906 * D) + 6.6e-7 + 4.0 * u + zm.acc_terms * u;
+      err = 1.25 * (rel * zm.z_raw + 1.6e-6 * zm.z_corr) * (total / zm.z_tilde);
     }
     const double target = static_cast<double>(top_p) * total;
     bool amb = false;
