@@ -60,6 +60,7 @@ extern "C" {
 #define LM_STATUS_NEAR_TIE 4u     /* Gumbel draw: best and second-best key closer than 4e-6 (float32 log is library-specific) */
 #define LM_STATUS_TOPP_EDGE 8u    /* top-p: cumulative mass within 1e-12 (relative) of the target at the boundary */
 #define LM_STATUS_CANDIDATE_PATH 64u /* the row was finished by the one-pass candidate path (informational) */
+#define LM_STATUS_SLICED_PATH 256u /* the row was cut into slices over the whole GPU (calls of a few rows; informational) */
 #define LM_STATUS_TILE_DECLINED 128u /* lm_tile_finish only: the row was not sampled (token -1); materialise it and call lm_sample */
 
 #define LM_MAX_VOCAB 1048576
@@ -303,7 +304,7 @@ LM_API int lm_draft_q(const lm_draft_q_args* args);
  *      into [shards][rows] records, shard order = vocabulary order;
  *   3. every GPU calls lm_vocab_merge on the gathered records and gets the same tokens.
  * Requirements: top_k >= 1 on every row (the kept set must lie inside the top-k candidates), cap =
- * lm_vocab_candidate_cap(largest top_k), shards * cap <= LM_VOCAB_MAX_CANDIDATES, no penalties. A row whose ties overflow
+ * lm_vocab_candidate_cap(largest top_k), shards * cap <= LM_VOCAB_MAX_CANDIDATES, at most 64 shards, no penalties. A row whose ties overflow
  * a record reports LM_STATUS_OVERFLOW and token -1; a row whose per-row temperature is not positive reports status bit 16 and
  * token -1. One exception to "bit for bit": the FP64 softmass is summed per shard and then over the sorted candidates, another
  * order than on one GPU, so a top-p boundary within 1e-12 (relative) of the target may fall on the other side; such rows carry

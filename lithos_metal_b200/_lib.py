@@ -19,6 +19,7 @@ VERIFY_SELFTEST_WITHHOLD = 1
 STATUS_GENERIC_PATH, STATUS_NAN, STATUS_NEAR_TIE, STATUS_TOPP_EDGE, STATUS_OVERFLOW = 1, 2, 4, 8, 32
 STATUS_CANDIDATE_PATH = 64
 STATUS_TILE_DECLINED = 128
+STATUS_SLICED_PATH = 256
 TILE_MAX_COLS = 2048
 VOCAB_MAX_CANDIDATES = 1024
 MAX_DRAFT = 15

@@ -12,6 +12,7 @@
 #include "sample_hist.cuh"
 #include "sample_topk.cuh"
 #include "sample_tiles.cuh"
+#include "sample_sliced.cuh"
 #include "verify.cuh"
 #include "draft_q.cuh"
 #include "vocab_parallel.cuh"
@@ -101,7 +102,7 @@ static int sm_count(int* out) {
 
 // Kernels that need more than 48 KB of dynamic shared memory must be told so once per device (the attribute belongs to the
 // device's copy of the function); remembered per device and kernel, raised when a call needs more.
-enum KernelSlot { kSlotFast, kSlotTopk, kSlotGeneric, kSlotVocabLocal, kSlotVerify, kSlotDraftQ, kSlotTileFinish, kSlotCount };
+enum KernelSlot { kSlotFast, kSlotTopk, kSlotGeneric, kSlotVocabLocal, kSlotVerify, kSlotDraftQ, kSlotTileFinish, kSlotSlice, kSlotSliceSmall, kSlotSlicedMerge, kSlotCount };
 
 static int ensure_dynamic_smem(KernelSlot slot, const void* func, size_t bytes) {
   if (bytes <= 48 * 1024) return LM_OK;
@@ -115,6 +116,10 @@ static int ensure_dynamic_smem(KernelSlot slot, const void* func, size_t bytes) 
   const bool tracked = dev >= 0 && dev < kMaxDevices;
   if (tracked && bytes <= granted[dev][slot]) return LM_OK;
   e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  if (e != cudaSuccess) return cuda_fail(e);
+  // Every large-shared-memory kernel asks for the same split of the SM's memory (all of it shared): blocks of two of them can
+  // then be resident on one SM side by side, which the sampler's side-by-side launch order relies on.
+  e = cudaFuncSetAttribute(func, cudaFuncAttributePreferredSharedMemoryCarveout, static_cast<int>(cudaSharedmemCarveoutMaxShared));
   if (e != cudaSuccess) return cuda_fail(e);
   if (tracked) granted[dev][slot] = bytes;
   return LM_OK;
@@ -177,7 +182,8 @@ size_t lm_workspace_bytes(int64_t rows, int64_t vocab) {
   (void)vocab;
   if (rows < 0) rows = 0;
   // argmax partials | rows for the generic kernel | rows that are not the top-k kernel's | rows the top-k kernel left | counters
-  return align256(static_cast<size_t>(rows) * sizeof(ArgmaxWs)) + 3 * align256(static_cast<size_t>(rows) * sizeof(uint32_t)) + 256;
+  //   | the slice records of a call of a few rows
+  return align256(static_cast<size_t>(rows) * sizeof(ArgmaxWs)) + 3 * align256(static_cast<size_t>(rows) * sizeof(uint32_t)) + 256 + kSlicedWsBytes;
 }
 
 size_t lm_verify_workspace_bytes(int32_t n_draft, int64_t vocab) {
@@ -277,6 +283,53 @@ int lm_sample(const lm_sample_args* a) {
   const int* redo_list = nullptr; const int* redo_n = nullptr;
   // BF16 rows that only need tokens (and tau) stream through the one-pass kernel; it marks the rows it cannot take
   // and the generic kernel behind it handles exactly those.
+  // A call of a few rows with one top_k for all of them: the rows are cut into slices over the whole GPU (sample_sliced.cuh).
+  const size_t ws_base = lm_workspace_bytes(a->rows, a->vocab) - kSlicedWsBytes;
+  const bool sliced = a->rows <= kSlicedMaxRows && a->vocab >= kSlicedMinVocab && a->temperature == nullptr && a->temperature_s > 0.0f &&
+                      a->top_k == nullptr && a->top_k_s >= 1 && a->top_k_s <= 64 && a->out_stats == nullptr && a->out_probs == nullptr &&
+                      a->step_state == nullptr && !(a->flags & LM_FLAG_EXACT_ONLY) && (!pen || a->hist_len <= 65536) &&
+                      a->workspace != nullptr && (reinterpret_cast<uintptr_t>(a->workspace) & 255u) == 0 && a->workspace_bytes >= ws_base + kSlicedWsBytes;
+  if (sliced) {
+    SliceDev S;
+    // a record holds twice the top_k: only a slice with more than top_k ties at its own k-th value overflows it
+    S.slices = a->top_k_s <= 8 ? 64 : (a->top_k_s <= 16 ? 32 : (a->top_k_s <= 32 ? 16 : 8));
+    S.cap = kVpMaxCandidates / S.slices;
+    S.slice_len = static_cast<int>(((a->vocab + S.slices - 1) / S.slices + 7) / 8 * 8);
+    if (S.slice_len <= kSliceMaxLen) {
+      char* ws = static_cast<char*>(a->workspace) + ws_base;
+      S.logits = a->logits; S.dtype = a->dtype; S.rows = P.rows; S.vocab = P.vocab; S.row_stride = a->row_stride;
+      S.temperature = a->temperature_s; S.top_k = a->top_k_s;
+      S.history = P.history; S.hist_len = P.hist_len; S.hist_stride = P.hist_stride; S.rho = P.rho; S.pi = P.pi;
+      S.records = reinterpret_cast<unsigned char*>(ws); S.record_bytes = static_cast<int64_t>(lm_vocab_record_bytes(S.cap));
+      const size_t slice_smem = slice_smem_bytes(S.slice_len);
+      const size_t gsmem = sizeof(GenericSmem) + (pen ? static_cast<size_t>((a->vocab + 31) / 32) * 4 : 0) + 16;
+      S.need_mass = (a->top_p != nullptr || (a->top_p_s > 0.0f && a->top_p_s < 1.0f)) && !(a->flags & LM_FLAG_TOPP_IN_TOPK);
+      const bool big = static_cast<long long>(S.slices) * P.rows <= 2LL * sms;   // few slices in all: wide blocks, for the latency
+      rc = big ? ensure_dynamic_smem(kSlotSlice, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockBig>), slice_smem)
+               : ensure_dynamic_smem(kSlotSliceSmall, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockSmall>), slice_smem);
+      if (rc == LM_OK) rc = ensure_dynamic_smem(kSlotSlicedMerge, reinterpret_cast<const void*>(sliced_merge_kernel), gsmem);
+      if (rc != LM_OK) return rc;
+      if (big) slice_local_kernel<kSliceBlockBig><<<dim3(S.slices, P.rows), kSliceBlockBig, slice_smem, st>>>(S);
+      else slice_local_kernel<kSliceBlockSmall><<<dim3(S.slices, P.rows), kSliceBlockSmall, slice_smem, st>>>(S);
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return cuda_fail(e);
+      VpMergeDev M;
+      M.records = S.records; M.shards = S.slices; M.rows = P.rows; M.cap = S.cap; M.record_bytes = S.record_bytes;
+      M.temperature = nullptr; M.temperature_s = a->temperature_s; M.top_k = nullptr; M.top_k_s = a->top_k_s;
+      M.top_p = a->top_p; M.top_p_s = a->top_p_s; M.min_p = a->min_p; M.min_p_s = a->min_p_s;
+      M.flags = a->flags; M.draw = a->draw; M.uniforms = a->uniforms; M.seed = a->seed; M.step = a->step; M.row_offset = a->row_offset;
+      M.out_tokens = a->out_tokens; M.out_tau = a->out_tau; M.out_status = a->out_status;
+      M.hand_on = 1; M.path_status = LM_STATUS_SLICED_PATH;
+      // the merge is launched with programmatic stream serialization: its blocks are resident and waiting when the slices complete
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(P.rows); cfg.blockDim = dim3(kVpMaxCandidates); cfg.dynamicSmemBytes = gsmem; cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
+      e = cudaLaunchKernelEx(&cfg, sliced_merge_kernel, M, P);
+      return e == cudaSuccess ? LM_OK : cuda_fail(e);
+    }
+  }
   const bool fast = a->dtype == LM_DTYPE_BF16 && a->out_stats == nullptr && a->out_probs == nullptr && a->vocab <= kHistMaxVocab &&
                     (a->vocab % kChunk) == 0 && (!pen || a->hist_len <= 65536);
   if (fast) {
@@ -443,7 +496,7 @@ int lm_vocab_merge(const lm_vocab_args* a) {
   if (a->temperature == nullptr && !(a->temperature_s > 0.0f)) return LM_E_INVALID;
   if (a->top_k == nullptr && a->top_k_s < 1) return LM_E_INVALID;
   if (a->draw == LM_DRAW_INVERSE_CDF && a->uniforms == nullptr) return LM_E_INVALID;
-  if (static_cast<int64_t>(a->shards) * a->cap > LM_VOCAB_MAX_CANDIDATES || a->rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
+  if (static_cast<int64_t>(a->shards) * a->cap > LM_VOCAB_MAX_CANDIDATES || a->shards > kVpMaxShards || a->rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
   VpMergeDev P;
   P.records = static_cast<const unsigned char*>(a->records); P.shards = a->shards; P.rows = static_cast<int>(a->rows); P.cap = a->cap;
   P.record_bytes = static_cast<int64_t>(lm_vocab_record_bytes(a->cap));
@@ -451,6 +504,7 @@ int lm_vocab_merge(const lm_vocab_args* a) {
   P.top_p = a->top_p; P.top_p_s = a->top_p_s; P.min_p = a->min_p; P.min_p_s = a->min_p_s;
   P.flags = a->flags; P.draw = a->draw; P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
   P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_status = a->out_status;
+  P.hand_on = 0; P.path_status = 0u;
   int sms = 0;
   const int rc = sm_count(&sms);
   if (rc != LM_OK) return rc;

@@ -513,6 +513,12 @@ __device__ void sample_row_hist(const SampleDev& P, int row, int next, HistSmem&
   const int n_chunks = V / kChunk;
   const uint4* p4 = reinterpret_cast<const uint4*>(rowp);
 
+  // The row starts its way into L2 now: the set-up below runs under its latency, and the pass finds lines instead of opening
+  // them a few at a time (a block alone on its SM has nobody else's loads to hide its own behind).
+  {
+    const char* rb = reinterpret_cast<const char*>(rowp);
+    for (int l = tid; l * 128 < V * 2; l += kHB) asm volatile("prefetch.global.L2 [%0];" ::"l"(rb + static_cast<size_t>(l) * 128));
+  }
   if (next >= 0 && tid == 0 && pen_on) {
     const char* hp = reinterpret_cast<const char*>(P.history + static_cast<int64_t>(next) * P.hist_stride);
     const uint32_t hb = (static_cast<uint32_t>(P.hist_len) * 4u) & ~15u;
@@ -839,12 +845,14 @@ __global__ void __launch_bounds__(kHB, 2) sample_hist_kernel(SampleDev P, const 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   apply_step_state(P);
   const int n = list ? min(*n_list, P.rows) : P.rows;
-  if (threadIdx.x == 0) { item[0] = atomicAdd(next_item, 1); item[1] = item[0] < n ? atomicAdd(next_item, 1) : n; }
+  // many items per block: hold the next item too and claim the one after it at the start of a row (the counter's round trip
+  // hides behind the row); few items per block: claim an item only when it is needed, so that no block sits on work
+  const bool ahead = n >= 4 * static_cast<int>(gridDim.x);
+  if (threadIdx.x == 0) { item[0] = atomicAdd(next_item, 1); item[1] = (ahead && item[0] < n) ? atomicAdd(next_item, 1) : n; }
   __syncthreads();
   for (;;) {
     const int i = item[0], in = item[1];
     if (i >= n) break;
-    // the item after next is fetched now and only looked at when this row is done: the counter's round trip hides behind the row
     int fetched = n;
     if (threadIdx.x == 0 && in < n) fetched = atomicAdd(next_item, 1);
     const int row = list ? list[i] : i;
@@ -852,7 +860,7 @@ __global__ void __launch_bounds__(kHB, 2) sample_hist_kernel(SampleDev P, const 
     if (next >= P.rows) next = -1;
     if (row >= 0 && row < P.rows) sample_row_hist(P, row, next, s, pen, redo, n_redo);   // (a list entry is a row index by construction)
     __syncthreads();
-    if (threadIdx.x == 0) { item[0] = in; item[1] = fetched; }
+    if (threadIdx.x == 0) { item[0] = ahead ? in : atomicAdd(next_item, 1); item[1] = fetched; }
     __syncthreads();
   }
 }

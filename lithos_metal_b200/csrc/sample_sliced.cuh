@@ -1,0 +1,176 @@
+// A few rows on the whole GPU: every row is cut into slices, one thread block per slice.
+//
+// One block per row (the batch kernels) leaves a call of one or a handful of rows on as many SMs, and the row's latency is that of
+// one block walking 150k logits several times. The decode step of a single stream is exactly that call (the reference's sampler
+// dispatches run on T <= 8 rows per step, monolith/kernels.py:720-775). Here the slices of a row go to different SMs:
+//
+//   slice_local_kernel  (slices x rows blocks)  reads its slice ONCE into shared memory (BF16 or FP32, widened; the penalties of
+//                       the history ids that fall into the slice applied), and leaves a record: the slice's maximum, its FP64
+//                       softmass relative to that maximum, and every logit at or above (a close lower bound of) the slice's own k-th largest;
+//   vocab_merge_kernel  (one block per row; vocab_parallel.cuh) the same merge that joins the shards of the vocab-parallel mode:
+//                       sorts the candidates of all slices, rebuilds the row's maximum and mass, thresholds, draw.
+//
+// The record format is the vocab-parallel one, a slice standing for a shard. Rows with a top_k of 1 .. 64 only: the merge sorts
+// 1024 candidates, and every slice's record has room for twice the top_k (64 / 32 / 16 / 8 slices for a top_k up to 8 / 16 / 32 /
+// 64), so that only a slice with more than top_k ties at its own k-th value overflows it; the merge's block then
+// runs the generic row algorithm on such a row itself.
+#pragma once
+#include "common.cuh"
+#include "sample_generic.cuh"
+#include "vocab_parallel.cuh"
+
+namespace lm {
+
+constexpr int kSliceBlockBig = 1024;     // threads per slice when the call has few slices (latency), else kSliceBlockSmall
+constexpr int kSliceBlockSmall = 256;
+constexpr int kSliceMaxLen = 32768;       // logits of one slice (128 KB of shared memory as binary32)
+constexpr int kSlicedMaxRows = 16;        // rows per call on this path
+constexpr int kSlicedMinVocab = 16384;
+constexpr int kSliceBins = 2048;
+constexpr size_t kSlicedWsBytes = static_cast<size_t>(kSlicedMaxRows) * (64 * kVpHeader + 8 * kVpMaxCandidates);
+
+struct SliceDev {
+  const void* logits; int dtype; int rows; int vocab; int64_t row_stride;
+  int slices; int slice_len;                          // slice_len: a multiple of 8 (the last slices of a row may be short or empty)
+  float temperature; int top_k; int cap; int need_mass;
+  const int32_t* history; int hist_len; int64_t hist_stride; float rho, pi;
+  unsigned char* records; int64_t record_bytes;       // [slices][rows] records
+};
+
+__host__ __device__ inline size_t slice_smem_bytes(int slice_len) { return static_cast<size_t>(slice_len) * 4 + static_cast<size_t>(slice_len / 32 + 1) * 4; }
+
+// A lower bound of the k-th largest of vals[0 .. n) (1 <= k <= n) that shares its upper 22 key bits: a radix descent of 11 + 11
+// bits on the monotone keys. (BF16 logits have no key bits below those; for binary32 logits the few values that share the upper
+// 22 bits with the k-th largest become candidates too, which the merge sorts out.)
+template <int B>
+__device__ uint32_t slice_kth_key(const float* vals, int n, uint32_t k, uint32_t* bins, uint64_t* scratch, uint32_t* pick) {
+  const int tid = threadIdx.x;
+  uint32_t prefix = 0u, above = 0u;
+#pragma unroll 1
+  for (int level = 0; level < 2; level++) {
+    const int shift = level == 0 ? 21 : 10;
+    const uint32_t hi_mask = level == 0 ? 0u : (0xFFFFFFFFu << (shift + 11));
+    for (int i = tid; i < kSliceBins; i += B) bins[i] = 0u;
+    __syncthreads();
+    for (int j = tid; j < n; j += B) {
+      const uint32_t key = fkey(vals[j]);
+      if ((key & hi_mask) == prefix) atomicAdd(&bins[(key >> shift) & (kSliceBins - 1)], 1u);
+    }
+    __syncthreads();
+    constexpr int kPer = kSliceBins / B;                                  // thread t owns kPer bins, walked downwards from the top
+    uint32_t cnt[kPer]; uint64_t sum = 0ull;
+#pragma unroll
+    for (int j = 0; j < kPer; j++) { cnt[j] = bins[kSliceBins - 1 - (kPer * tid + j)]; sum += cnt[j]; }
+    const uint64_t excl = block_exclusive_scan_u64(sum, scratch, nullptr);
+    uint32_t run = above + static_cast<uint32_t>(excl);
+    if (run < k && run + static_cast<uint32_t>(sum) >= k) {
+#pragma unroll
+      for (int j = 0; j < kPer; j++) {
+        if (run < k && run + cnt[j] >= k) { pick[0] = static_cast<uint32_t>(kSliceBins - 1 - (kPer * tid + j)); pick[1] = run; }
+        run += cnt[j];
+      }
+    }
+    __syncthreads();
+    prefix |= pick[0] << shift; above = pick[1];
+    __syncthreads();
+  }
+  return prefix;
+}
+
+template <int B>
+__global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* vals = reinterpret_cast<float*>(smem_raw);
+  uint32_t* marks = reinterpret_cast<uint32_t*>(smem_raw + static_cast<size_t>(P.slice_len) * 4);
+  __shared__ uint32_t bins[kSliceBins];
+  __shared__ uint64_t scratch[32];
+  __shared__ uint32_t pick[2];
+  __shared__ uint32_t s_n;
+  // the merge may be made resident while the slices are at work; it waits for this grid
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int tid = threadIdx.x, slice = blockIdx.x, row = blockIdx.y;
+  const int lo = slice * P.slice_len;
+  const int n = max(0, min(P.slice_len, P.vocab - lo));
+  unsigned char* rec = P.records + (static_cast<int64_t>(slice) * P.rows + row) * P.record_bytes;
+  float* out_val = reinterpret_cast<float*>(rec + kVpHeader);
+  int32_t* out_idx = reinterpret_cast<int32_t*>(rec + kVpHeader + 4 * static_cast<size_t>(P.cap));
+  if (n == 0) {                                                            // nothing of the row falls into this slice
+    if (tid == 0) {
+      *reinterpret_cast<float*>(rec) = -INFINITY; *reinterpret_cast<float*>(rec + 4) = 0.0f; *reinterpret_cast<double*>(rec + 8) = 0.0;
+      *reinterpret_cast<int32_t*>(rec + 16) = 0; *reinterpret_cast<uint32_t*>(rec + 20) = 0u;
+    }
+    return;
+  }
+  // ---- the slice, once, into shared memory
+  RowView rv;
+  rv.dtype = P.dtype; rv.vocab = n; rv.rho = 1.0f; rv.pi = 0.0f; rv.pen = nullptr;
+  rv.row = static_cast<const char*>(P.logits) + (static_cast<size_t>(row) * static_cast<size_t>(P.row_stride) + static_cast<size_t>(lo)) * (P.dtype == LM_DTYPE_BF16 ? 2 : 4);
+  rv.aligned = (reinterpret_cast<uintptr_t>(rv.row) & 15u) == 0;
+  const int n_chunks = (n + kChunk - 1) / kChunk;
+  const bool pen_on = P.history != nullptr;
+  if (pen_on) for (int i = tid; i < P.slice_len / 32 + 1; i += B) marks[i] = 0u;
+  for (int c = tid; c < n_chunks; c += B) {
+    float z[kChunk];
+    const int m = load_chunk(rv, c, z);
+#pragma unroll
+    for (int e = 0; e < kChunk; e++) if (e < m) vals[c * kChunk + e] = z[e];
+  }
+  __syncthreads();
+  if (pen_on) {                                                            // every distinct history id inside the slice, once
+    const int32_t* h = P.history + static_cast<int64_t>(row) * P.hist_stride;
+    for (int i = tid; i < P.hist_len; i += B) {
+      const int id = __ldg(h + i) - lo;
+      if (id >= 0 && id < n) {
+        const uint32_t bit = 1u << (id & 31);
+        if ((atomicOr(&marks[id >> 5], bit) & bit) == 0u) vals[id] = canon_zero(penalise(vals[id], P.rho, P.pi));
+      }
+    }
+    __syncthreads();
+  }
+  // ---- maximum, FP64 softmass relative to it
+  uint64_t best = 0ull;
+  for (int j = tid; j < n; j += B) { const uint64_t p = pack_best(vals[j], static_cast<uint32_t>(j)); best = p > best ? p : best; }
+  best = block_max_u64(best, scratch);
+  const float vmax = best_value(best);
+  const double inv_t = 1.0 / static_cast<double>(P.temperature);
+  double mass = 0.0;
+  if (P.need_mass) {                                                       // (only a top-p over the whole row asks for it)
+    double m = 0.0;
+    for (int j = tid; j < n; j += B) m += softmass(vals[j], vmax, inv_t);
+    mass = block_sum_f64(m, scratch);
+  }
+  // ---- the slice's k-th largest value and everything at or above it
+  if (tid == 0) s_n = 0u;
+  const uint32_t k = static_cast<uint32_t>(min(P.top_k, n));
+  const float tau_local = fkey_inv(slice_kth_key<B>(vals, n, k, bins, scratch, pick));
+  for (int j = tid; j < n; j += B) {
+    if (vals[j] >= tau_local) {
+      const uint32_t slot = atomicAdd(&s_n, 1u);
+      if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = vals[j]; out_idx[slot] = lo + j; }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    const uint32_t cnt = s_n;
+    *reinterpret_cast<float*>(rec) = vmax;
+    *reinterpret_cast<float*>(rec + 4) = 0.0f;
+    *reinterpret_cast<double*>(rec + 8) = mass;
+    *reinterpret_cast<int32_t*>(rec + 16) = static_cast<int32_t>(cnt < static_cast<uint32_t>(P.cap) ? cnt : static_cast<uint32_t>(P.cap));
+    *reinterpret_cast<uint32_t*>(rec + 20) = (cnt > static_cast<uint32_t>(P.cap) ? kStatusOverflow : 0u) | ((vmax != vmax) ? LM_STATUS_NAN : 0u);
+  }
+}
+
+// The merge of the sliced path: one block per row. Launched with programmatic stream serialization behind slice_local_kernel.
+__global__ void __launch_bounds__(kVpMaxCandidates, 1) sliced_merge_kernel(VpMergeDev M, SampleDev P) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ VpMergeSmem s;
+  asm volatile("griddepcontrol.wait;" ::: "memory");                      // the records are complete behind this
+  const int row = blockIdx.x;
+  if (row >= M.rows) return;
+  if (!vocab_merge_row(M, row, s)) {                                       // overflowed records: the generic row algorithm, here and now
+    GenericSmem& g = *reinterpret_cast<GenericSmem*>(smem_raw);
+    sample_row_generic(P, row, g, reinterpret_cast<uint32_t*>(smem_raw + sizeof(GenericSmem)));
+  }
+}
+
+}  // namespace lm

@@ -665,12 +665,15 @@ __global__ void __launch_bounds__(kTB, kTopkPerSM) sample_topk_kernel(SampleDev 
   __shared__ int item[2];                                                   // the row in hand and the one after it
   apply_step_state(P);
   if (threadIdx.x < 8) c.prev_cut[threadIdx.x] = 0u;
-  if (threadIdx.x == 0) { item[0] = atomicAdd(&counters[0], 1); item[1] = item[0] < P.rows ? atomicAdd(&counters[0], 1) : P.rows; }
+  // With many rows per block a block holds the row after its current one too (it pulls that row into L2 while it works) and
+  // claims the one after that at the start of a row, so the counter's round trip hides behind the row. With few rows per block
+  // claiming ahead would leave blocks without work while others hold two rows: a block then claims a row when it needs one.
+  const bool ahead = P.rows >= 4 * static_cast<int>(gridDim.x);
+  if (threadIdx.x == 0) { item[0] = atomicAdd(&counters[0], 1); item[1] = (ahead && item[0] < P.rows) ? atomicAdd(&counters[0], 1) : P.rows; }
   __syncthreads();
   for (;;) {
     const int row = item[0], next = item[1];
     if (row >= P.rows) break;
-    // the row after next is fetched now and only looked at when this row is done: the counter's round trip hides behind the row
     int fetched = P.rows;
     if (threadIdx.x == 0 && next < P.rows) fetched = atomicAdd(&counters[0], 1);
     if (!topk_row_eligible(P, row)) {                                       // not this kernel's row: listed here, or already by sample_classify_kernel
@@ -680,7 +683,7 @@ __global__ void __launch_bounds__(kTB, kTopkPerSM) sample_topk_kernel(SampleDev 
       if (threadIdx.x == 0 && !done) list[atomicAdd(&counters[1], 1)] = row;
     }
     __syncthreads();                                                        // nobody reads item[] any more
-    if (threadIdx.x == 0) { item[0] = next; item[1] = fetched; }
+    if (threadIdx.x == 0) { item[0] = ahead ? next : atomicAdd(&counters[0], 1); item[1] = fetched; }
     __syncthreads();
   }
   // This grid may have been started before the grid launched ahead of it had finished (programmatic stream serialization). The

@@ -1,0 +1,93 @@
+"""Calls of a few rows: lm_sample cuts every row into slices over the whole GPU (one block per slice, one merge per row).
+
+The reference's sampler dispatches run on the T <= 8 rows of one decode step (monolith/kernels.py:720-775); its own CPU-runnable
+configuration is a single FP32 row. The results must be the ones of the row-per-block kernels and of the oracle, bit for bit.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import lithos_metal_b200 as lm
+from lithos_metal_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+SLICED, GENERIC = _lib.STATUS_SLICED_PATH, 1
+
+
+def _rows(rows, vocab, seed, dtype, spikes=8):
+    rng = np.random.default_rng(seed)
+    z = (rng.standard_normal((rows, vocab)) * 2).astype(np.float32)
+    for r in range(rows):
+        z[r, rng.choice(vocab, spikes, replace=False)] = 12.0
+    if dtype == "bf16":
+        codes = oracle.f32_to_bf16(z)
+        return torch.from_numpy(codes.view(np.int16)).cuda().view(torch.bfloat16), codes
+    return torch.from_numpy(z).cuda(), z
+
+
+def _check(x, host, *, draw, temperature, top_k, top_p=0.0, min_p=0.0, history=None, rho=1.0, pi=0.0, expect_sliced=True, seed=5, step=2, row_offset=0,
+           topp_in_topk=False, exact_only=False):
+    rows = x.shape[0]
+    u = np.random.default_rng(seed + 100).random(rows).astype(np.float32)
+    p = lm.SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p, min_p=min_p, seed=seed, draw=draw, repetition_penalty=rho, presence_penalty=pi,
+                          topp_in_topk=topp_in_topk, exact_only=exact_only)
+    r = lm.sample(x, p, history=None if history is None else torch.from_numpy(history).cuda(), uniforms=torch.from_numpy(u).cuda(), step=step,
+                  row_offset=row_offset, return_tau=True, return_status=True)
+    tok, tau, _ = oracle.sample_batch(host, temperature=temperature, top_k=top_k, top_p=top_p, min_p=min_p, topp_in_topk=topp_in_topk, history=history,
+                                      repetition_penalty=rho, presence_penalty=pi, draw=draw, uniforms=u, seed=seed, step=step, row_offset=row_offset, n_threads=8)
+    st = r.status.cpu().numpy()
+    assert bool(np.all(st & SLICED)) == expect_sliced or (not expect_sliced and not np.any(st & SLICED)), st
+    assert r.tokens.cpu().tolist() == tok.tolist()
+    assert r.tau.cpu().numpy().tobytes() == tau.tobytes()
+    return r, st
+
+
+@pytest.mark.parametrize("draw", ["inverse_cdf", "gumbel"])
+@pytest.mark.parametrize("rows", [1, 3, 16])
+def test_fp32_rows_with_spikes(rows, draw):
+    x, host = _rows(rows, 151936, 1, "f32")
+    _check(x, host, draw=draw, temperature=0.7, top_k=20, top_p=0.95)
+
+
+@pytest.mark.parametrize("top_k,top_p,min_p", [(1, 0.0, 0.0), (16, 0.9, 0.0), (17, 0.0, 0.05), (32, 0.5, 0.0), (50, 0.95, 0.01), (64, 0.99, 0.0)])
+def test_bf16_rows_with_penalties(top_k, top_p, min_p):
+    rows, vocab = 5, 151936
+    x, host = _rows(rows, vocab, 2, "bf16")
+    rng = np.random.default_rng(3)
+    hist = rng.integers(0, vocab, (rows, 700)).astype(np.int32)
+    hist[:, :40] = np.argsort(-oracle.bf16_to_f32(host), axis=1)[:, :40]       # the penalties must reach the top of every row
+    hist[0, 50:60] = hist[0, 0]                                               # a repeated id is penalised once
+    for draw in ("inverse_cdf", "gumbel"):
+        _check(x, host, draw=draw, temperature=0.9, top_k=top_k, top_p=top_p, min_p=min_p, history=hist, rho=1.3, pi=0.4, row_offset=40)
+
+
+@pytest.mark.parametrize("vocab,top_k,sliced", [(16400, 10, True), (262144, 50, True), (1000000, 8, True), (1000000, 50, False), (8192, 10, False)])
+def test_vocabulary_sizes_and_the_limits_of_the_path(vocab, top_k, sliced):
+    x, host = _rows(2, vocab, 4, "bf16" if vocab % 8 == 0 else "f32")
+    _check(x, host, draw="inverse_cdf", temperature=1.1, top_k=top_k, top_p=0.9, expect_sliced=sliced)
+
+
+def test_more_ties_than_a_record_holds_go_to_the_generic_kernel():
+    x, host = _rows(2, 151936, 6, "f32", spikes=0)
+    x[0, 100:300] = 9.0; host[0, 100:300] = 9.0                               # 200 equal maxima inside one slice, top_k 20
+    r, st = _check(x, host, draw="inverse_cdf", temperature=1.0, top_k=20, expect_sliced=False)
+    assert st[0] & GENERIC and st[1] & SLICED, st
+
+
+def test_other_knobs_keep_the_row_per_block_kernels():
+    x, host = _rows(4, 151936, 7, "bf16")
+    _check(x, host, draw="gumbel", temperature=0.8, top_k=40, top_p=0.9, exact_only=True, expect_sliced=False)
+    _check(x, host, draw="gumbel", temperature=0.8, top_k=0, top_p=0.9, expect_sliced=False)
+    _check(x, host, draw="gumbel", temperature=0.8, top_k=40, top_p=0.9, topp_in_topk=True)
+    k = torch.full((4,), 40, dtype=torch.int32)
+    p = lm.SamplingParams(temperature=0.8, top_k=k, seed=1)
+    assert not np.any(lm.sample(x, p, return_status=True).status.cpu().numpy() & SLICED)
+
+
+def test_rows_that_do_not_start_on_a_16_byte_boundary():
+    base, host = _rows(3, 40001, 8, "f32")                                    # odd row length: rows 1 and 2 start unaligned
+    _check(base, host, draw="inverse_cdf", temperature=0.7, top_k=20, top_p=0.95)
+    wide = torch.zeros(3, 40009, device="cuda")
+    wide[:, 3:40004] = base                                                   # a view with a stride and an offset
+    _check(wide[:, 3:40004], host, draw="inverse_cdf", temperature=0.7, top_k=20, top_p=0.95)
