@@ -9,7 +9,8 @@
  * Conventions
  *   - plain pointers and sizes only; every data pointer is DEVICE memory unless a comment says "host";
  *   - the caller owns every buffer; scratch is sized by lm_workspace_bytes() and passed in; kernels leave the
- *     workspace reusable (a workspace must be zero-filled once before its first use and is kept clean afterwards);
+ *     workspace reusable (a workspace must be zero-filled once before its first use, belongs to the device and the entry points
+ *     it was first used with, and must not be written by the caller afterwards: the verify step keeps a launch count in it);
  *   - every call is asynchronous on the CUDA stream given (a cudaStream_t passed as void*; NULL = default stream);
  *   - every entry point returns LM_OK (0) or a negative LM_E_* code; nothing throws across this boundary;
  *   - there is no CPU fallback: without a CUDA device the entry points return LM_E_CUDA.
@@ -179,7 +180,7 @@ LM_API int lm_argmax_static(const void* logits, int32_t dtype, int64_t rows, int
  *               (over p itself on the bonus row, or when the residual is empty).
  * Outputs: out_accept[0] = accept length; out_final[0] = final token; out_tokens (optional, [n_draft + 1]) =
  * drafts[0..accept) followed by the final token, -1 beyond. A launch whose internal waits ran out (see wait_limit) reports -1
- * in all three and leaves its workspace clean for the next call.
+ * in all three and leaves its workspace usable for the next call.
  *
  * commit (optional): the fields lm_accept_scan takes (step_state, t_max, gamma_max, ring, ring_cap, eos, eos_list, n_eos, log,
  * log_cap, ctx_cap, lm; `tokens` and `stream` are ignored). The thread that writes out_tokens then runs the accept scan on them

@@ -188,8 +188,9 @@ size_t lm_workspace_bytes(int64_t rows, int64_t vocab) {
 
 size_t lm_verify_workspace_bytes(int32_t n_draft, int64_t vocab) {
   (void)n_draft; (void)vocab;
-  const size_t need = sizeof(VerifyWs) > sizeof(DraftQWs) ? sizeof(VerifyWs) : sizeof(DraftQWs);   // lm_verify and lm_draft_q may share it
-  return align256(need);
+  // lm_verify and lm_draft_q may share it: the verify kernel's words (which keep a launch count between calls) come first, the
+  // draft kernel's (all zero between calls) behind them
+  return align256(sizeof(VerifyWs)) + align256(sizeof(DraftQWs));
 }
 
 int lm_argmax(const void* logits, int32_t dtype, int64_t rows, int64_t vocab, int64_t row_stride, int32_t* out_tokens, void* workspace,
@@ -614,9 +615,9 @@ int lm_verify(const lm_verify_args* a) {
                          c->ctx_cap, c->lm};
   }
   // one block per SM, all resident at once (the blocks wait for one another's partial results): a cooperative launch guarantees it
-  int grid = sms < 256 ? sms : 256;                                        // consume_rows holds rows x grid words in kConsumeSlots per thread
-  const int max_useful = static_cast<int>((a->vocab + 7) / 8);
-  if (grid > max_useful) grid = max_useful;
+  // (the same grid for every call on a device, whatever the vocabulary: the workspace's launch count is in units of it; blocks
+  // beyond a small vocabulary hold empty slices)
+  const int grid = sms < 256 ? sms : 256;                                  // consume_rows holds rows x grid words in kConsumeSlots per thread
   // the block's slices of all rows in shared memory when they fit (they do for every vocabulary up to ~700k at 148 SMs)
   const int per = (static_cast<int>((a->vocab + grid - 1) / grid) + 7) & ~7;
   const size_t rows_cached = static_cast<size_t>(a->n_draft + 1) + (a->mode == LM_VERIFY_STOCHASTIC ? a->n_draft : 0);
@@ -648,7 +649,7 @@ int lm_draft_q(const lm_draft_q_args* a) {
   P.logits = a->logits; P.temperature = a->temperature; P.seed = a->seed; P.step = a->step;
   P.out_tokens = a->out_tokens; P.out_lse = a->out_lse; P.out_vmax = a->out_vmax; P.out_mass = reinterpret_cast<unsigned long long*>(a->out_mass);
   P.out_status = a->out_status; P.out_q_logits = a->out_q_logits; P.q_logits_stride = a->q_logits_stride;
-  P.ws = static_cast<DraftQWs*>(a->workspace);
+  P.ws = reinterpret_cast<DraftQWs*>(static_cast<char*>(a->workspace) + align256(sizeof(VerifyWs)));
   P.state = static_cast<const uint32_t*>(a->step_state); P.t_max = a->t_max; P.g = a->gamma_max > 1 ? a->gamma_max : 1;
   // one block per SM, all resident at once (one grid barrier), each holding its slice of every row in shared memory;
   // more blocks than that never, fewer when the slices would not fit

@@ -10,9 +10,13 @@
 //
 // Blocks exchange their partial results through TAGGED WORDS in a small workspace: every partial is one 64-bit word whose top
 // bit says "written". A block publishes with one plain store per word and consumes by polling the words it needs, so a
-// dependency costs one trip to L2 and back -- no counter, no fence, no second read. The workspace starts all zero; the last
-// block to leave zeroes what the launch wrote. Every poll is bounded: when it runs out the launch reports an error through its
-// outputs (and through the StepState when it commits); the GPU is never left waiting.
+// dependency costs one trip to L2 and back -- no counter, no fence, no second read. The words live in one of two BANKS. A launch
+// uses the bank its number selects, and every block clears its own words of the other bank while its loads are in flight, so
+// the next launch finds a clean bank and nobody tidies up at the end. The launch number is the count of blocks that have ever
+// left, divided by the grid size: a block adds itself on its way out (no reply awaited), and the quotient cannot change before
+// the last block of the launch has read it. The workspace starts all zero and belongs to one device (one grid size). Every poll
+// is bounded: when it runs out the launch reports an error through its outputs (and through the StepState when it commits); the
+// GPU is never left waiting.
 //
 // With a StepState given, the kernel takes the round from it on the device, as the reference's kernels do
 // (kernels/common/sample.metal:283-296): verify length, drafts (pending_tokens), seed, step, and it leaves at once when the
@@ -30,14 +34,18 @@ constexpr int kVerifyMaxGrid = 1024;                    // far above any SM coun
 constexpr unsigned kVerifyWaitLimit = 1u << 17;         // polls of one word before a wait gives up: about 0.1 s
 constexpr unsigned long long kTagged = 1ull << 63;
 
-struct VerifyWs {                                       // lives in the caller's workspace, zero-filled once, left all zero by every launch
-  unsigned exits;                                       // blocks that have left
-  unsigned error;                                       // a wait of this launch ran out
-  unsigned pad[2];
+struct VerifyBank {
+  unsigned error;                                       // a wait of the launch that used this bank ran out
+  unsigned pad[3];
   unsigned long long draft_w[kVerifyMaxRows];           // tagged: fixed-point weight of draft r in row r (0 if not kept)
   unsigned long long best[kVerifyMaxRows][kVerifyMaxGrid];   // tagged: per row and block, the slice's packed (max logit, lowest index)
   unsigned long long mass[kVerifyMaxRows][kVerifyMaxGrid];   // tagged: per row and block, the slice's fixed-point mass
   unsigned long long resid[2][kVerifyMaxGrid];          // tagged: per block, the slice's residual mass / its best draw keys
+};
+struct VerifyWs {                                       // lives in the caller's workspace, zero-filled once
+  unsigned long long exits;                             // blocks that have ever left: grid size x launches so far
+  unsigned long long pad;
+  VerifyBank bank[2];
 };
 
 struct VerifyDev {
@@ -130,17 +138,30 @@ __device__ __forceinline__ void consume_rows(const unsigned long long* words, in
                                              unsigned limit, bool* failed, uint64_t vals[kConsumeSlots]) {
   const int tid = threadIdx.x, lane = tid & 31;
   const int Gp = (G + 31) & ~31, n = R * Gp;
-  unsigned long long first[kConsumeSlots];
+  // Every word of this thread is in flight at once, on the first look and on every further one: a word that is not there yet
+  // costs one more round trip for all of the thread's words together, not one each.
+  const unsigned long long* addr[kConsumeSlots];
+  unsigned long long got[kConsumeSlots];
 #pragma unroll
-  for (int k = 0; k < kConsumeSlots; k++) {                               // every word of this thread in flight at once
+  for (int k = 0; k < kConsumeSlots; k++) {
     const int idx = k * kVerifyBlock + tid, r = idx / Gp, g = idx - r * Gp;
-    first[k] = (idx < n && g < G) ? peek(words + static_cast<size_t>(r) * kVerifyMaxGrid + g) : 0ull;
+    addr[k] = (idx < n && g < G) ? words + static_cast<size_t>(r) * kVerifyMaxGrid + g : nullptr;
+    got[k] = addr[k] ? peek(addr[k]) : kTagged;
+  }
+  for (unsigned spins = 0;; spins++) {
+    bool all = true;
+#pragma unroll
+    for (int k = 0; k < kConsumeSlots; k++) all = all && (got[k] & kTagged) != 0ull;
+    if (all) break;
+    if (spins >= limit) { *failed = true; break; }
+    if (spins > 64u) __nanosleep(100);                                    // a long wait: leave the memory system to the blocks still working
+#pragma unroll
+    for (int k = 0; k < kConsumeSlots; k++) if (!(got[k] & kTagged)) got[k] = peek(addr[k]);
   }
 #pragma unroll
   for (int k = 0; k < kConsumeSlots; k++) {
     const int idx = k * kVerifyBlock + tid, r = idx / Gp, g = idx - r * Gp;
-    uint64_t v = 0ull;
-    if (idx < n && g < G) v = consume(words + static_cast<size_t>(r) * kVerifyMaxGrid + g, limit, failed, first[k]);
+    const uint64_t v = (got[k] & kTagged) ? (got[k] & ~kTagged) : 0ull;
     vals[k] = v;
     if (k * kVerifyBlock < n) {                                           // block-uniform
       const uint64_t w = SUM ? warp_sum_u64(v) : warp_max_u64(v);
@@ -160,14 +181,18 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   extern __shared__ __align__(16) float v_smem[];
   __shared__ uint64_t scratch[32];
   __shared__ uint64_t s_red[kVerifyMaxRows][32];
-  __shared__ int s_j, s_token, s_last;
+  __shared__ int s_j, s_token;
   __shared__ int s_drafts[kVerifyMaxRows];
   __shared__ unsigned long long s_best[kVerifyMaxRows], s_mass[kVerifyMaxRows], s_own[kVerifyMaxRows];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, G = gridDim.x, b = blockIdx.x;
   const int V = P.vocab;
   const bool stochastic = P.mode == LM_VERIFY_STOCHASTIC;
   const bool gumbel_draw = stochastic && P.draw == LM_DRAW_GUMBEL;
-  VerifyWs* ws = P.ws;
+  // the bank of this launch (the load is in flight under phase 0; its value is first needed when the row maxima are published)
+  unsigned long long launches;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(launches) : "l"(&P.ws->exits) : "memory");
+  const unsigned bank_id = static_cast<unsigned>((launches / static_cast<unsigned long long>(G)) & 1ull);
+  VerifyBank* ws = &P.ws->bank[bank_id];
   const unsigned limit = P.wait_limit ? P.wait_limit : kVerifyWaitLimit;
   bool failed = false;
 
@@ -188,7 +213,16 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     seed = st.seed(); step = st.step();
   }
   const int R = L + 1;
+  // this block's words of the other bank (the previous launch's) are cleared for the next launch; block 0 also clears the shared ones
+  auto clean_other_bank = [&]() {
+    VerifyBank* other = &P.ws->bank[bank_id ^ 1u];
+    if (tid < kVerifyMaxRows) { other->best[tid][b] = 0ull; other->mass[tid][b] = 0ull; }
+    if (tid < 2) other->resid[tid][b] = 0ull;
+    if (b == 0 && tid < kVerifyMaxRows) other->draft_w[tid] = 0ull;
+    if (b == 0 && tid == 0) other->error = 0u;
+  };
   if (idle || mismatch) {
+    clean_other_bank();                                                   // (the launch still counts: the banks keep alternating)
     // nothing is verified; block 0 still closes a prefill chunk (the scan's prefill branch) or reports the caller's error
     if (b == 0 && warp == 0) {
       if (mismatch) {
@@ -349,6 +383,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
       publish(&ws->best[tid][b], best);
     }
   }
+  clean_other_bank();
   __syncthreads();                                                        // s_red is reused below
 
   uint64_t vals[kConsumeSlots];
@@ -558,21 +593,9 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     }
   }
   }
-  // ---- the last block to leave puts the workspace back to all zero -------------------------------------------------------------
+  // ---- on the way out: one more block of this launch has left (nobody waits for the reply) -----------------------------------
   __syncthreads();
-  if (tid == 0) { __threadfence(); s_last = atomicAdd(&ws->exits, 1u) == static_cast<unsigned>(G) - 1u; }
-  __syncthreads();
-  if (s_last) {
-    __threadfence();
-    for (int i = tid; i < kVerifyMaxRows * G; i += kVerifyBlock) {
-      const int r = i / G, g = i - r * G;
-      ws->best[r][g] = 0ull;
-      if (stochastic) ws->mass[r][g] = 0ull;
-    }
-    if (stochastic) for (int g = tid; g < 2 * G; g += kVerifyBlock) ws->resid[g / G][g % G] = 0ull;
-    if (tid < kVerifyMaxRows) ws->draft_w[tid] = 0ull;
-    if (tid == 0) { ws->error = 0u; ws->exits = 0u; }
-  }
+  if (tid == 0) asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(&P.ws->exits), "l"(1ull) : "memory");
 }
 
 }  // namespace lm
