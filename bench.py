@@ -519,11 +519,19 @@ def bench_verify(torch, lm, dev):
     # the drafter's side of the same round: seven BF16 logits rows, sampled one position per call as a Markov drafter does
     drafter = (target[:7].float() + torch.randn(7, VOCAB, generator=g, device=dev) * 0.5).to(torch.bfloat16)
     stats = lm.draft_q(drafter, temperature=1.0, seed=SEED, step=0)
+    # the two ends of the stochastic step: every draft accepted (no residual: two exchanges between the blocks), and the first
+    # draft rejected (the residual of row 0 is summed and drawn from: three exchanges)
+    u_zero, u_one = torch.zeros(7, device=dev), torch.full((7,), 0.999, device=dev)
+    worst = drafts.clone()
+    worst[0] = (q[0] / torch.softmax(target[0].float(), dim=-1)).argmax().to(torch.int32)       # the token the drafter overrates most
     calls = {"stochastic": lambda: lm.verify(target, drafts, q, ua, uf, "stochastic"),
+             "stochastic_all_accepted": lambda: lm.verify(target, drafts, q, u_zero, uf, "stochastic"),
+             "stochastic_first_rejected": lambda: lm.verify(target, worst, q, u_one, uf, "stochastic"),
              "stochastic_q_logits": lambda: lm.verify(target, stats.tokens, None, ua, uf, "stochastic", draft_logits=drafter, draft_stats=stats),
              "greedy": lambda: lm.verify(target, drafts, mode="greedy"),
              "draft_q_one_position": lambda: lm.draft_q(drafter[3:4], temperature=1.0, seed=SEED, step=0, first_position=3)}
-    res = {}
+    res = {"accept_len": {"stochastic": int(calls["stochastic"]()[0]), "stochastic_all_accepted": int(calls["stochastic_all_accepted"]()[0]),
+                          "stochastic_first_rejected": int(calls["stochastic_first_rejected"]()[0])}}
     for mode, call in calls.items():
         for _ in range(3):
             call()

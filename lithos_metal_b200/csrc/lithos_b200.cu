@@ -117,10 +117,6 @@ static int ensure_dynamic_smem(KernelSlot slot, const void* func, size_t bytes) 
   if (tracked && bytes <= granted[dev][slot]) return LM_OK;
   e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
   if (e != cudaSuccess) return cuda_fail(e);
-  // Every large-shared-memory kernel asks for the same split of the SM's memory (all of it shared): blocks of two of them can
-  // then be resident on one SM side by side, which the sampler's side-by-side launch order relies on.
-  e = cudaFuncSetAttribute(func, cudaFuncAttributePreferredSharedMemoryCarveout, static_cast<int>(cudaSharedmemCarveoutMaxShared));
-  if (e != cudaSuccess) return cuda_fail(e);
   if (tracked) granted[dev][slot] = bytes;
   return LM_OK;
 }
