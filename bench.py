@@ -55,7 +55,7 @@ def ncu_traffic():
 
 
 # (top-k kernel read + write) + (histogram kernel read + write) over the 4096 rows of one call
-TRAFFIC = {"dram_bytes_per_row": (1043868000 + 3853568 + 508108000 + 41251584) / 4096, "captured_at": "16f2bfc (kernels changed since: indicative only)"}
+TRAFFIC = {"dram_bytes_per_row": (1037174000 + 3975168 + 385458000 + 72841472) / 4096, "captured_at": "530573f"}
 
 
 def launches_per_call(lm, rows: int) -> int:
