@@ -60,11 +60,11 @@ TRAFFIC = {"dram_bytes_per_row": (1037174000 + 3975168 + 385458000 + 72841472) /
 
 def launches_per_call(lm, rows: int) -> int:
     """Kernels one lm_sample call launches on this workload (per rank): top-k kernel, histogram kernel, generic kernel; with at
-    most 16 rows per SM the two sampler kernels run side by side and a row-listing kernel plus a second (usually empty) launch
+    most 5 rows per SM the two sampler kernels run side by side and a row-listing kernel plus a second (usually empty) launch
     of the histogram kernel join them (the rule is lm_sample's, lithos_metal_b200/csrc/lithos_b200.cu)."""
     from lithos_metal_b200 import _lib
     sms = _lib.lib().lm_device_sm_count()
-    return 3 if rows > 16 * max(sms, 1) else 5
+    return 3 if rows > 5 * max(sms, 1) else 5
 
 
 class ClockSampler:
@@ -316,7 +316,7 @@ def main() -> None:
            "gpu_launches": launches_per_call(lm, rows) * args.steps, "clocks": clocks.summary()}
     out["roofline"]["launch"] = ("one sampling call = sample_topk_kernel (rows with a top_k) + sample_hist_kernel (the other rows) + "
                                  "sample_generic_kernel (rows handed on: none here)" + (" + the row-listing kernel and a second sample_hist_kernel launch "
-                                 "(side-by-side order below 16 rows per SM)" if launches_per_call(lm, rows) == 5 else "") + "; duration = CUDA events around the call")
+                                 "(side-by-side order up to 5 rows per SM)" if launches_per_call(lm, rows) == 5 else "") + "; duration = CUDA events around the call")
 
     if not args.skip_extras:
         # ---- e2e: host (pinned) inputs -> public API -> tokens on the host, copies inside the timed region

@@ -84,7 +84,7 @@ static int cuda_fail(cudaError_t e) {
   return LM_E_CUDA;
 }
 
-constexpr int kOverlapRowsPerSM = 16;   // up to this many rows per SM the two sampler kernels run side by side (lm_sample)
+constexpr int kOverlapRowsPerSM = 5;    // up to this many rows per SM the two sampler kernels run side by side (lm_sample)
 
 static int sm_count(int* out) {
   int dev = 0;
