@@ -48,7 +48,8 @@ extern "C" {
 
 /* draw modes */
 #define LM_DRAW_GUMBEL 0       /* argmax(z/T + Gumbel noise), noise from the splitmix64 hash of (seed, step, row, index) */
-#define LM_DRAW_INVERSE_CDF 1  /* inverse CDF over the kept set in ascending index order, from a caller-supplied uniform */
+#define LM_DRAW_INVERSE_CDF 1  /* inverse CDF over the kept set ordered by descending logit (equal logits by ascending index: the order of a
+                                  sorted top-p pipeline), on integer fixed-point weights, from a caller-supplied uniform */
 
 /* lm_sample_args.flags */
 #define LM_FLAG_TOPP_IN_TOPK 1u /* top-p over the top-k set's renormalised mass (the Hugging Face warpers' order) */
@@ -238,7 +239,7 @@ typedef struct lm_verify_args {
                                   out and the error path can be exercised (with a small wait_limit) without hanging anything */
 } lm_verify_args;
 
-#define LM_RESIDUAL_INVERSE_CDF 0 /* final token by inverse CDF over max(p - q, 0) (over p on the bonus row) from u_final */
+#define LM_RESIDUAL_INVERSE_CDF 0 /* final token by inverse CDF, in ascending index order, over max(p - q, 0) (over p on the bonus row) from u_final */
 #define LM_RESIDUAL_GUMBEL 1      /* the reference's form (kernels/common/sample.metal:322-346): argmax of ln(p - q) + gumbel(seed, step,
                                      4000, i) over the positive residual; with every draft accepted or an empty residual, the row's own
                                      Gumbel-max draw argmax(z/T + gumbel(seed, step, row, i)) over its kept set */

@@ -298,10 +298,10 @@ __device__ void sample_row_generic(const SampleDev& P, int row, GenericSmem& s, 
   // ---- the draw --------------------------------------------------------------------------------------------------
   int token;
   if (P.draw == LM_DRAW_INVERSE_CDF) {
-    token = draw_inverse_cdf<false>(rv, tau, vmax, T, P.uniforms ? P.uniforms[row] : 0.0f, s.draw);
+    token = draw_inverse_cdf(rv, tau, vmax, T, P.uniforms ? P.uniforms[row] : 0.0f, s.draw);
   } else {
     bool tie = false;
-    token = draw_gumbel<false>(rv, tau, T, P.seed, P.step, static_cast<uint32_t>(P.row_offset + row), s.draw, &tie);
+    token = draw_gumbel(rv, tau, T, P.seed, P.step, static_cast<uint32_t>(P.row_offset + row), s.draw, &tie);
     if (tie) status |= LM_STATUS_NEAR_TIE;
   }
 

@@ -309,138 +309,209 @@ __device__ __forceinline__ uint32_t kept_mask8(const uint4 q, uint32_t tau_code2
   return (m0 & 1u) | ((m0 >> 15) & 2u) | ((m1 & 1u) << 2) | ((m1 >> 13) & 8u) | ((m2 & 1u) << 4) | ((m2 >> 11) & 32u) | ((m3 & 1u) << 6) | ((m3 >> 9) & 128u);
 }
 
-// The inverse-CDF draw. The total weight S of the kept set comes from the histograms, so the target is known before the row is
-// read again. Segments of 256 logits are then summed from whichever end of the row is nearer to the target (an integer suffix
-// sum is as exact as a prefix sum), a batch of kBatchSegs at a time, until the segment that holds the target is found; one
-// warp locates the token inside it. The pass sums the raw logits; what the penalties change is in s.seg_fix (exact: the sums
-// are integers). Every thread calls; every thread gets the token (-1: the kept set has no weight).
+// 8-bit mask of the logits of a chunk whose BF16 code equals `code` (zero = true: whose value is zero, either sign).
+__device__ __forceinline__ uint32_t equal_mask8(const uint4 q, uint32_t code2, bool zero) {
+  const uint32_t strip = zero ? 0x7FFF7FFFu : 0xFFFFFFFFu;
+  const uint32_t m0 = __vcmpeq2(q.x & strip, code2), m1 = __vcmpeq2(q.y & strip, code2), m2 = __vcmpeq2(q.z & strip, code2), m3 = __vcmpeq2(q.w & strip, code2);
+  if ((m0 | m1 | m2 | m3) == 0u) return 0u;
+  return (m0 & 1u) | ((m0 >> 15) & 2u) | ((m1 & 1u) << 2) | ((m1 >> 13) & 8u) | ((m2 & 1u) << 4) | ((m2 >> 11) & 32u) | ((m3 & 1u) << 6) | ((m3 >> 9) & 128u);
+}
+
+// The inverse-CDF draw: the kept set in descending value order, equal values by ascending index. Equal values have equal
+// weights, so the histograms decide almost everything: the total weight S, hence the target; the group of 64 window positions
+// where the cumulative weight crosses it (a block scan over the groups' weights); inside the group one warp walks the merged
+// sequence of window positions and distinct penalised values down to the value v where the crossing lies. What is left is the
+// floor((target - weight above v) / w(v))-th smallest index among the logits equal to v: the row is looked at again (L2) only to
+// COUNT them -- segments of 256 logits from whichever end is nearer, a batch of kBatchSegs per barrier, packed 16-bit compares
+// against v's raw code, the penalised logits equal to v as per-segment corrections (s.seg_fix) -- and the warp that holds the
+// segment locates the token. Every thread calls; every thread gets the token (-1: the kept set has no weight).
 __device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint32_t* pen, const uint16_t* rowp, int n_chunks, float tau, float vmax, float T, float u) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float c2 = exp2_scale(T);
-  const uint32_t tc = hceil_code(tau), tau2 = tc | (tc << 16);
   const uint32_t n_side = s.n_side, n_b = s.n_b;
-  // ---- S: every kept code once, times its count ------------------------------------------------------------------------
-  uint64_t mine = 0ull;
-  const int g_last = tc == 0xFF80u ? kGroupsH : group_of_pos(ins_pos(tau));   // groups behind it hold nothing at or above tau
+  unsigned long long* g_w = reinterpret_cast<unsigned long long*>(s.g_mass);   // the groups' weights take the place of their masses
+  auto kept_weight = [&](float v, uint32_t n) -> uint64_t { return (n && v >= tau) ? static_cast<uint64_t>(n) * weight_q40(v, vmax, c2) : 0ull; };
+  // ---- the weight of every group: window positions ...
   for (int sg = warp; sg < static_cast<int>(kSlots) / kGrpSlots; sg += kHW) {
     const int g = sg < kSignGroups ? kSignGroups - 1 - sg : sg + 1;
-    if (g > g_last || s.g_cnt[g] == 0u) continue;
-    const uint32_t w = s.hist[sg * 32 + lane];
-    if (w == 0u) continue;
-    const uint32_t slot = static_cast<uint32_t>(sg) * kGrpSlots + 2u * lane;
-    const uint32_t c0 = w & 0xFFFFu, c1 = w >> 16;
-    const float v0 = hcode_val(code_of_slot(slot)), v1 = hcode_val(code_of_slot(slot + 1u));
-    const bool k0 = c0 && v0 >= tau, k1 = c1 && v1 >= tau;
-    if (k0 || k1) {
-      uint64_t w0, w1;
-      weight_q40_x2(v0, v1, vmax, c2, w0, w1);
-      if (k0) mine += static_cast<uint64_t>(c0) * w0;
-      if (k1) mine += static_cast<uint64_t>(c1) * w1;
+    uint64_t w = 0ull;
+    if (s.g_cnt[g] != 0u) {                                                // (warp-uniform)
+      const uint32_t h = s.hist[sg * 32 + lane];
+      if (h) {
+        const uint32_t slot = static_cast<uint32_t>(sg) * kGrpSlots + 2u * lane;
+        const uint32_t n0 = h & 0xFFFFu, n1 = h >> 16;
+        const float v0 = hcode_val(code_of_slot(slot)), v1 = hcode_val(code_of_slot(slot + 1u));
+        if ((n0 && v0 >= tau) || (n1 && v1 >= tau)) {
+          uint64_t w0, w1;
+          weight_q40_x2(v0, v1, vmax, c2, w0, w1);
+          if (n0 && v0 >= tau) w += static_cast<uint64_t>(n0) * w0;
+          if (n1 && v1 >= tau) w += static_cast<uint64_t>(n1) * w1;
+        }
+      }
+      w = warp_sum_u64(w);
+    }
+    if (lane == 0) g_w[g] = w;
+  }
+  if (tid == 0) { g_w[kZeroGroup] = kept_weight(0.0f, s.cz); g_w[kNinfGroup] = 0ull; s.sel_g = kGroupsH; s.token = -1; }
+  __syncthreads();
+  // ... and the distinct penalised values, each into the group of the position it is inserted before
+  for (uint32_t j = tid; j < n_b; j += kHB) {
+    const uint64_t w = kept_weight(s.b_val[j], b_count_range(s, j, j + 1u));
+    if (w) atomicAdd(&g_w[group_of_pos(s.b_ins[j])], static_cast<unsigned long long>(w));
+  }
+  __syncthreads();
+  // ---- the target and the group where the cumulative weight crosses it
+  const uint64_t gw = tid < kGroupsH ? g_w[tid] : 0ull;
+  uint64_t total = 0ull;
+  const uint64_t g_before = block_exclusive_scan_u64(gw, s.scratch, &total);
+  if (total == 0ull) { __syncthreads(); return -1; }
+  const uint64_t target = cdf_target(u, total);
+  if (gw && g_before <= target && target < g_before + gw) { s.sel_g = tid; *reinterpret_cast<unsigned long long*>(&s.base_m) = g_before; }
+  __syncthreads();
+  const int g = s.sel_g;
+  // ---- inside the group: lane l owns the positions p0 + 2l, p0 + 2l + 1 and the penalised values inserted before each; its items in
+  // descending order: B[ja, jb), A(q0), B[jb, jc), A(q1). Results in shared memory: the value, the weight above it, how many logits
+  // carry it, and whether a window position (a raw code) does.
+  if (warp == 0) {
+    const uint64_t base = *reinterpret_cast<const unsigned long long*>(&s.base_m);
+    const uint32_t p0 = first_pos_of_group(g);
+    const bool single = g == kZeroGroup || g == kNinfGroup;
+    const uint32_t q0 = p0 + 2u * lane, q1 = q0 + 1u;
+    const bool own = !single || lane == 0;
+    uint32_t ja = 0u, jb = 0u, jc = 0u;
+    if (own) {
+      ja = lower_bound_u16(s.b_ins, n_b, q0); jb = lower_bound_u16(s.b_ins, n_b, q0 + 1u);
+      jc = single ? jb : lower_bound_u16(s.b_ins, n_b, q0 + 2u);
+    }
+    const uint32_t ca0 = own ? cnt_of_pos(s, q0) : 0u, ca1 = (own && !single) ? cnt_of_pos(s, q1) : 0u;
+    const float va0 = val_of_pos(q0), va1 = val_of_pos(q1);
+    const uint32_t n_items = (jc - ja) + 2u;
+    auto item = [&](uint32_t t, float& v, uint32_t& n, bool& is_a) {
+      const uint32_t nb0 = jb - ja;
+      if (t < nb0) { const uint32_t j = ja + t; v = s.b_val[j]; n = b_count_range(s, j, j + 1u); is_a = false; }
+      else if (t == nb0) { v = va0; n = ca0; is_a = true; }
+      else if (t < n_items - 1u) { const uint32_t j = jb + (t - nb0 - 1u); v = s.b_val[j]; n = b_count_range(s, j, j + 1u); is_a = false; }
+      else { v = va1; n = ca1; is_a = true; }
+    };
+    uint64_t w_l = 0ull;
+    for (uint32_t t = 0; t < n_items; t++) { float v; uint32_t n; bool a; item(t, v, n, a); w_l += kept_weight(v, n); }
+    uint64_t ws = w_l;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const uint64_t t = __shfl_up_sync(kFull, ws, o); if (lane >= o) ws += t; }
+    const uint64_t l_before = base + ws - w_l;
+    if (w_l && l_before <= target && target < l_before + w_l) {
+      uint64_t run = l_before;
+      for (uint32_t t = 0; t < n_items; t++) {
+        float v; uint32_t n; bool a; item(t, v, n, a);
+        const uint64_t w = kept_weight(v, n);
+        if (w && target < run + w) {
+          // the items of one value are adjacent: a penalised value right before the window position it equals
+          uint64_t before = run; uint32_t n_raw = a ? n : 0u, n_pen = a ? 0u : n;
+          if (a && t > 0u) {
+            float vp; uint32_t np; bool ap; item(t - 1u, vp, np, ap);
+            if (!ap && np && vp == v) { before -= kept_weight(vp, np); n_pen = np; }
+          } else if (!a && t + 1u < n_items) {
+            float vn; uint32_t nn; bool an; item(t + 1u, vn, nn, an);
+            if (an && nn && vn == v) n_raw = nn;
+          }
+          s.res_tau = v; s.res_cum_c = n_raw; s.base_c = n_pen;
+          *reinterpret_cast<unsigned long long*>(&s.res_cum_m) = before;
+          break;
+        }
+        run += w;
+      }
     }
   }
-  if (tid == 0 && s.cz && 0.0f >= tau) mine += static_cast<uint64_t>(s.cz) * weight_q40(0.0f, vmax, c2);
-  for (uint32_t j = tid; j < n_b; j += kHB) {
-    const float v = s.b_val[j];
-    if (v >= tau) mine += static_cast<uint64_t>(b_count_range(s, j, j + 1u)) * weight_q40(v, vmax, c2);
+  __syncthreads();
+  const float v_star = s.res_tau;
+  const uint32_t n_raw = s.res_cum_c, n_pen = s.base_c, members = n_raw + n_pen;
+  const uint64_t each = weight_q40(v_star, vmax, c2);
+  const uint32_t want = static_cast<uint32_t>((target - *reinterpret_cast<const unsigned long long*>(&s.res_cum_m)) / each);   // < members
+  // ---- the penalised logits equal to the value, per segment
+  unsigned int* seg_cnt = reinterpret_cast<unsigned int*>(s.seg_fix);      // (cleared with seg_fix at the start of the row)
+  if (n_pen) {
+    for (uint32_t i = tid; i < n_side; i += kHB) if (penalised_value(s.side_raw[i], P.rho, P.pi) == v_star) atomicAdd(&seg_cnt[s.ids[i] >> 8], 1u);
   }
-  // ---- what the penalties change, per segment ---------------------------------------------------------------------------
-  for (uint32_t i = tid; i < n_side; i += kHB) {
-    const uint32_t code = s.side_raw[i];
-    const float zr = hcode_val(code), zf = penalised_value(code, P.rho, P.pi);
-    const bool kr = zr >= tau, kf = zf >= tau;
-    if (!kr && !kf) continue;                                              // kept neither way: nothing to correct
-    uint64_t wf, wr;
-    weight_q40_x2(zf, zr, vmax, c2, wf, wr);
-    if (!kf) wf = 0ull;
-    if (!kr) wr = 0ull;
-    if (wf != wr) atomicAdd(&s.seg_fix[s.ids[i] >> 8], static_cast<unsigned long long>(wf - wr));   // modulo 2^64: the segment total is never negative
-  }
-  const uint64_t total = block_sum_u64(mine, s.scratch);                  // (two barriers: seg_fix is complete behind them)
-  if (total == 0ull) return -1;
-  const uint64_t target = cdf_target(u, total);
-  const bool forward = target < total - target;
-  const uint64_t tt = forward ? target : total - target - 1ull;           // the first segment, in scan order, whose running sum exceeds tt
-  // ---- the segments, a batch at a time, from the nearer end -----------------------------------------------------------------
+  // the raw code of the value, if a window position carries it (0xFFFFFFFF: none -- every member is a penalised logit)
+  const bool zero = v_star == 0.0f;
+  const uint32_t code = n_raw ? (zero ? 0u : (__float_as_uint(v_star) >> 16)) : 0xFFFFFFFFu;
+  const uint32_t code2 = code | (code << 16);
+  const bool forward = want < members - want;
+  const uint32_t tt = forward ? want : members - 1u - want;               // the first segment, in scan order, whose running count exceeds tt
+  __syncthreads();                                                        // seg_cnt is complete
+  // ---- the segments, a batch at a time, from the nearer end
   const uint4* p4 = reinterpret_cast<const uint4*>(rowp);
-  const uint4 neg = make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);
   const int n_seg = (n_chunks + kSegChunks - 1) / kSegChunks;
-  uint64_t run = 0ull, before = 0ull, found_total = 0ull;
+  uint32_t run = 0u, before_cnt = 0u, found_total = 0u;
   int found = -1, found_b0 = 0, buf = 0;
   uint4 q[kDrawIters];                                                    // the chunks of the batch in hand (kept for the locate step)
+  unsigned int* batch_cnt = reinterpret_cast<unsigned int*>(s.batch_sum);  // [2][kBatchSegs]
   for (int b0 = 0; b0 < n_seg && found < 0; b0 += kBatchSegs, buf ^= 1) {
 #pragma unroll
     for (int it = 0; it < kDrawIters; it++) {
       const int k = b0 + it * kHW + warp, seg = forward ? k : n_seg - 1 - k, cc = seg * kSegChunks + lane;
-      q[it] = (k < n_seg && cc < n_chunks) ? __ldg(p4 + cc) : neg;
+      q[it] = (n_raw && k < n_seg && cc < n_chunks) ? __ldg(p4 + cc) : make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);
     }
 #pragma unroll
     for (int it = 0; it < kDrawIters; it++) {
-      const int k = b0 + it * kHW + warp, seg = forward ? k : n_seg - 1 - k;
-      const uint32_t mask = tc == 0xFF80u ? (k < n_seg && seg * kSegChunks + lane < n_chunks ? 0xFFu : 0u) : kept_mask8(q[it], tau2);
-      uint64_t w = 0ull;
-      if (mask) {
-        const uint32_t words[4] = {q[it].x, q[it].y, q[it].z, q[it].w};
-#pragma unroll
-        for (int e = 0; e < 4; e++) if ((mask >> (2 * e)) & 3u) {          // two logits per packed evaluation
-          uint64_t wa, wb;
-          weight_q40_x2(bf16_lo(words[e]), bf16_hi(words[e]), vmax, c2, wa, wb);
-          w += ((mask >> (2 * e)) & 1u) ? wa : 0ull;
-          w += ((mask >> (2 * e)) & 2u) ? wb : 0ull;
-        }
-      }
-      // the warp's total in two limbs (w < 2^43): two 32-bit butterflies instead of one of 64-bit values
-      const uint32_t lo = warp_sum_u32(static_cast<uint32_t>(w) & 0x3FFFFFu), hi = warp_sum_u32(static_cast<uint32_t>(w >> 22));
-      if (lane == 0) s.batch_sum[buf][it * kHW + warp] = k < n_seg ? static_cast<uint64_t>(lo) + (static_cast<uint64_t>(hi) << 22) + s.seg_fix[seg] : 0ull;
+      const int k = b0 + it * kHW + warp, seg = forward ? k : n_seg - 1 - k, cc = seg * kSegChunks + lane;
+      uint32_t mask = (n_raw && k < n_seg && cc < n_chunks) ? equal_mask8(q[it], code2, zero) : 0u;
+      if (mask && pen != nullptr) mask &= ~((pen[cc >> 2] >> ((cc & 3) * 8)) & 0xFFu);
+      const uint32_t cnt = warp_sum_u32(__popc(mask));
+      if (lane == 0) batch_cnt[buf * kBatchSegs + it * kHW + warp] = k < n_seg ? cnt + seg_cnt[seg] : 0u;
     }
     __syncthreads();
-    // every warp scans the batch's totals for itself: no second barrier (the next batch writes the other buffer)
-    const uint64_t a = s.batch_sum[buf][2 * lane], b = s.batch_sum[buf][2 * lane + 1];
-    uint64_t incl = a + b;
+    // every warp scans the batch's counts for itself: no second barrier (the next batch writes the other buffer)
+    const uint32_t a = batch_cnt[buf * kBatchSegs + 2 * lane], b = batch_cnt[buf * kBatchSegs + 2 * lane + 1];
+    uint32_t incl = a + b;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { const uint64_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
-    const uint64_t excl = run + incl - a - b;
+    for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
+    const uint32_t excl = run + incl - a - b;
     const bool hit_a = excl + a > tt, hit_b = excl + a + b > tt;
     const uint32_t hits = __ballot_sync(kFull, hit_b);
     if (hits) {
       const int src = __ffs(hits) - 1;
       const int idx = __shfl_sync(kFull, hit_a ? 2 * lane : 2 * lane + 1, src);
-      before = __shfl_sync(kFull, hit_a ? excl : excl + a, src);
+      before_cnt = __shfl_sync(kFull, hit_a ? excl : excl + a, src);
       found_total = __shfl_sync(kFull, hit_a ? a : b, src);
       found = b0 + idx; found_b0 = b0;
     }
     run += __shfl_sync(kFull, incl, 31);
   }
-  if (found < 0) return -1;                                               // cannot happen: the segments sum to `total`
-  // ---- inside the segment: the first cumulative weight, in index order, that exceeds the target. The warp that summed the
-  // segment still holds its chunks in registers: no second load.
+  if (found < 0) return -1;                                               // cannot happen: the segments hold `members` logits
+  // ---- inside the segment: the (local)-th logit equal to the value, in index order. The warp that counted the segment still holds
+  // its chunks in registers: no second load.
   {
     const int idx = found - found_b0;                                     // position of the segment in its batch: it * kHW + warp
     if (warp == idx % kHW) {
       const int seg = forward ? found : n_seg - 1 - found;
-      const uint64_t prefix = forward ? before : total - before - found_total;   // the weight of everything before the segment
-      const uint64_t local_target = target - prefix;
+      const uint32_t prefix = forward ? before_cnt : members - before_cnt - found_total;   // members before the segment
+      const uint32_t local = want - prefix;
       const int cc = seg * kSegChunks + lane;
       uint4 qf = q[0];
 #pragma unroll
       for (int it = 1; it < kDrawIters; it++) if (idx / kHW == it) qf = q[it];
+      if (!n_raw && cc < n_chunks) qf = __ldg(p4 + cc);                   // (no raw code was compared: the batches loaded nothing)
       const uint32_t bits = (pen != nullptr && cc < n_chunks) ? ((pen[cc >> 2] >> ((cc & 3) * 8)) & 0xFFu) : 0u;
       const uint32_t words[4] = {qf.x, qf.y, qf.z, qf.w};
-      uint64_t w[kChunk], sum = 0ull;
+      uint32_t hit = 0u;
 #pragma unroll
       for (int e = 0; e < kChunk; e++) {
-        const uint32_t code = (e & 1) ? (words[e >> 1] >> 16) : (words[e >> 1] & 0xFFFFu);
-        const float z = ((bits >> e) & 1u) ? penalised_value(code, P.rho, P.pi) : hcode_val(code);
-        w[e] = (cc < n_chunks && z >= tau) ? weight_q40(z, vmax, c2) : 0ull;
-        sum += w[e];
+        const uint32_t cde = (e & 1) ? (words[e >> 1] >> 16) : (words[e >> 1] & 0xFFFFu);
+        const bool is_pen = (bits >> e) & 1u;
+        const bool m = cc < n_chunks && (is_pen ? (n_pen && penalised_value(cde, P.rho, P.pi) == v_star)
+                                               : (n_raw && (zero ? (cde & 0x7FFFu) == 0u : cde == code)));
+        hit |= m ? (1u << e) : 0u;
       }
-      uint64_t incl = sum;
+      const uint32_t mine = __popc(hit);
+      uint32_t incl = mine;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) { const uint64_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
-      const uint64_t excl = incl - sum;
-      if (excl <= local_target && local_target < incl) {
-        uint64_t r = excl;
+      for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
+      const uint32_t excl = incl - mine;
+      if (excl <= local && local < incl) {
+        uint32_t r = excl;
 #pragma unroll
-        for (int e = 0; e < kChunk; e++) { r += w[e]; if (w[e] && r > local_target) { s.token = cc * kChunk + e; break; } }
+        for (int e = 0; e < kChunk; e++) if ((hit >> e) & 1u) { if (r == local) { s.token = cc * kChunk + e; break; } r++; }
       }
     }
   }

@@ -30,7 +30,6 @@ constexpr int kMaxProbes = 30;             // counters of the cutoff search per 
 constexpr int kBinSortMax = 256;           // a code bin with more candidates than this must already be in order (all equal)
 constexpr int kSampleChunks = 1024 / kTB;   // chunks per thread in the cutoff sample: 1024 chunks = 8192 logits
 constexpr int kTopkMinVocab = 32768;
-constexpr int kIdxBuckets = 1024;          // the draw buckets candidates by index >> 8: vocabularies up to 2^18
 
 constexpr int kStages = 4;                 // 16-byte asynchronous copies in flight per thread during the pass
 
@@ -576,55 +575,50 @@ __device__ bool topk_finish(const SampleDev& P, int row, TopkSmem& c, uint32_t c
   // ---- the draw ----------------------------------------------------------------------------------------------------------
   int token = -1;
   if (P.draw == LM_DRAW_INVERSE_CDF) {
-    // token = first kept index, ascending, whose cumulative fixed-point weight exceeds the target. The kept candidates are
-    // in value order: their weights are summed per bucket of 256 indices (two 20-bit limbs in 32-bit counters), the
-    // bucket that holds the target is found by a scan, and only its few candidates are ranked by index.
+    // The kept candidates are in descending value order, which is the draw's order up to the order inside a run of equal values
+    // (equal values have equal weights): an inclusive prefix sum of the weights finds the candidate where the target is crossed,
+    // hence the value; the token is the floor((target - before) / w)-th smallest index of that value's run.
     const float c2 = exp2_scale(T);
-    uint32_t* blo = reinterpret_cast<uint32_t*>(c.key);                     // the arrival-order list is no longer needed
-    uint32_t* bhi = blo + kIdxBuckets;
-    for (int i = tid; i < 2 * kIdxBuckets; i += kTB) blo[i] = 0u;
-    if (tid == 0) c.n_hit = 0u;
-    __syncthreads();
-    uint64_t mine = 0ull;
-    for (int i = tid; i < n_kept; i += kTB) {
-      const unsigned long long k = c.sel[i];
-      const uint32_t idx = 0xFFFFFFFFu - static_cast<uint32_t>(k);
-      const uint64_t w = weight_q40(fkey_inv(static_cast<uint32_t>(k >> 32)), vmax, c2);
-      c.w[i] = w; mine += w;
-      atomicAdd(&blo[idx >> 8], static_cast<uint32_t>(w & 0xFFFFFull));
-      atomicAdd(&bhi[idx >> 8], static_cast<uint32_t>(w >> 20));
+    constexpr int kPer = kTopkCap / kTB;                                    // consecutive candidates per thread
+    uint64_t wv[kPer], sum = 0ull;
+#pragma unroll
+    for (int j = 0; j < kPer; j++) {
+      const int i = tid * kPer + j;
+      wv[j] = i < n_kept ? weight_q40(fkey_inv(static_cast<uint32_t>(c.sel[i] >> 32)), vmax, c2) : 0ull;
+      sum += wv[j];
     }
-    const uint64_t total = block_sum_u64(mine, c.scratch);
+    uint64_t total = 0ull;
+    uint64_t run = block_exclusive_scan_u64(sum, c.scratch, &total);
+    if (tid == 0) { c.hit = kTopkCap; c.cross_bin = 0u; c.n_hit = static_cast<uint32_t>(n_kept); }
+    __syncthreads();
     if (total > 0ull) {
       const uint64_t target = cdf_target(P.uniforms ? P.uniforms[row] : 0.0f, total);
-      constexpr int kPer = kIdxBuckets / kTB;
-      uint64_t bt[kPer], sum = 0ull;
-#pragma unroll
-      for (int j = 0; j < kPer; j++) { const int b = tid * kPer + j; bt[j] = static_cast<uint64_t>(blo[b]) + (static_cast<uint64_t>(bhi[b]) << 20); sum += bt[j]; }
-      uint64_t run = block_exclusive_scan_u64(sum, c.scratch, nullptr);
 #pragma unroll
       for (int j = 0; j < kPer; j++) {
-        if (run <= target && target < run + bt[j]) { c.cross_bin = static_cast<uint32_t>(tid * kPer + j); c.base = run; }
-        run += bt[j];
+        const int i = tid * kPer + j;
+        run += wv[j];
+        if (i < n_kept) c.w[i] = run;                                       // inclusive
+        if (wv[j] && run > target && run - wv[j] <= target) c.hit = i;      // exactly one candidate
       }
       __syncthreads();
-      const uint32_t bucket = c.cross_bin;
-      for (int i0 = 0; i0 < n_kept; i0 += kTB) {                            // uniform trip count
-        const int i = i0 + tid;
-        const bool take = i < n_kept && ((0xFFFFFFFFu - static_cast<uint32_t>(c.sel[i])) >> 8) == bucket;
-        const uint32_t slot = warp_reserve(&c.n_hit, take ? 1u : 0u);
-        if (take) c.hitlist[slot] = static_cast<uint32_t>(i);
+      const int at = c.hit;
+      const uint32_t vkey = static_cast<uint32_t>(c.sel[at] >> 32);
+      // the run of this value: [first, last)
+      for (int i = tid; i < n_kept; i += kTB) {
+        if (static_cast<uint32_t>(c.sel[i] >> 32) != vkey) continue;
+        if (i == 0 || static_cast<uint32_t>(c.sel[i - 1] >> 32) != vkey) c.cross_bin = static_cast<uint32_t>(i);
+        if (i == n_kept - 1 || static_cast<uint32_t>(c.sel[i + 1] >> 32) != vkey) c.n_hit = static_cast<uint32_t>(i + 1);
       }
       __syncthreads();
-      const uint32_t m = c.n_hit;                                           // at most 256: one per index of the bucket
-      for (uint32_t j = tid; j < m; j += kTB) {
-        const uint32_t ij = c.hitlist[j], idx_j = 0xFFFFFFFFu - static_cast<uint32_t>(c.sel[ij]);
-        uint64_t before = c.base;
-        for (uint32_t t = 0; t < m; t++) {
-          const uint32_t it = c.hitlist[t];
-          if (0xFFFFFFFFu - static_cast<uint32_t>(c.sel[it]) < idx_j) before += c.w[it];
-        }
-        if (before <= target && target < before + c.w[ij]) c.token = static_cast<int>(idx_j);
+      const int first = static_cast<int>(c.cross_bin), last = static_cast<int>(c.n_hit);
+      const uint64_t before = first > 0 ? c.w[first - 1] : 0ull;
+      const uint64_t each = c.w[first] - before;
+      const uint32_t want = static_cast<uint32_t>((target - before) / each);   // < last - first: the crossing lies inside the run
+      for (int i = first + tid; i < last; i += kTB) {
+        const uint32_t idx_i = 0xFFFFFFFFu - static_cast<uint32_t>(c.sel[i]);
+        uint32_t smaller = 0u;
+        for (int t = first; t < last; t++) smaller += (0xFFFFFFFFu - static_cast<uint32_t>(c.sel[t])) < idx_i ? 1u : 0u;
+        if (smaller == want) c.token = static_cast<int>(idx_i);
       }
     }
     __syncthreads();

@@ -259,18 +259,13 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
   uint32_t status = status0 | edge | P.path_status;
   // ---- the draw
   if (P.draw == LM_DRAW_INVERSE_CDF) {
+    // the kept candidates are already in the draw's order (descending logit, equal logits by ascending index): one prefix sum
     const float c2 = exp2_scale(T);
     const uint64_t w = kept ? weight_q40(val, vmax, c2) : 0ull;
-    s.w[tid] = w;
-    __syncthreads();
-    const uint64_t total = block_sum_u64(w, s.scratch);
+    uint64_t total = 0ull;
+    const uint64_t before = block_exclusive_scan_u64(w, s.scratch, &total);
     if (total > 0ull && w) {
       const uint64_t target = cdf_target(P.uniforms ? P.uniforms[row] : 0.0f, total);
-      uint64_t before = 0ull;                                            // weight of the kept candidates with a smaller index
-      for (int t = 0; t < N; t++) {
-        const uint64_t wt = s.w[t];
-        if (wt && static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(s.key[t])) < idx) before += wt;
-      }
       if (before <= target && target < before + w) s.token = idx;
     }
   } else {

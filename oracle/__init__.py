@@ -48,6 +48,8 @@ def lib():
         _lib.lmo_cdf_target.argtypes = [C.c_float, C.c_uint64]
         _lib.lmo_sample_invcdf.restype = C.c_int32
         _lib.lmo_sample_invcdf.argtypes = [f32p, C.c_int64, C.c_float, C.c_float, C.c_float, u64p]
+        _lib.lmo_sample_invcdf_index.restype = C.c_int32
+        _lib.lmo_sample_invcdf_index.argtypes = [f32p, C.c_int64, C.c_float, C.c_float, C.c_float, u64p]
         _lib.lmo_accept_greedy.restype = C.c_int32
         _lib.lmo_accept_greedy.argtypes = [i32p, i32p, C.c_int32, i32p]
         _lib.lmo_confidence.restype = None
@@ -141,6 +143,12 @@ def sample_invcdf(z: np.ndarray, u: float, *, temperature: float = 1.0, top_k: i
     tau = thresholds(z, temperature=float(np.float32(temperature)), top_k=top_k, top_p=float(np.float32(top_p)), min_p=float(np.float32(min_p)),
                      topp_in_topk=topp_in_topk)
     return int(lib().lmo_sample_invcdf(_p(z, C.c_float), z.size, tau, np.float32(temperature), np.float32(u), None))
+
+
+def sample_invcdf_index_order(z: np.ndarray, u: float, *, temperature: float = 1.0, tau: float = -np.inf) -> int:
+    """The inverse-CDF draw over {z >= tau} in ascending index order: what the verify step does when it draws from a row's own softmax."""
+    z = _f32(z)
+    return int(lib().lmo_sample_invcdf_index(_p(z, C.c_float), z.size, np.float32(tau), np.float32(temperature), np.float32(u), None))
 
 
 def sample_batch(logits: np.ndarray, *, temperature, top_k=0, top_p=0.0, min_p=0.0, topp_in_topk=False, history=None,

@@ -24,7 +24,7 @@
  *                         values, tests/kernels/test_draft_ops.py:228-263, within its own bar of 2e-3)
  * What has no counterpart in the reference (PARITY UNPINNED; this file is the frozen definition):
  *   lmo_apply_penalties   repetition / presence penalties over the distinct ids of a token history
- *   lmo_spec_exp2, lmo_weight_q40, lmo_sample_invcdf   inverse-CDF draw from a caller-supplied uniform, defined
+ *   lmo_spec_exp2, lmo_weight_q40, lmo_sample_invcdf   inverse-CDF draw (descending logit order) from a caller-supplied uniform, defined
  *                         on integer fixed-point weights so that CPU and GPU agree bit for bit
  *
  * Everything that feeds an integer decision is built from IEEE-754 binary32/binary64 operations with a fixed
@@ -223,9 +223,10 @@ LMO_API uint64_t lmo_cdf_target(float u, uint64_t total) {
   return (uint64_t)(((unsigned __int128)total * (uint64_t)u24) >> 24);
 }
 
-/* token = the first kept index, ascending, whose inclusive cumulative weight exceeds the target; -1 if the kept
- * set has no weight. out_total: the kept set's integer mass. */
-LMO_API int32_t lmo_sample_invcdf(const float* z, int64_t vocab, float tau, float temperature, float u, uint64_t* out_total) {
+/* The kept set in index order: token = the first kept index, ascending, whose inclusive cumulative weight exceeds the target;
+ * -1 if the kept set has no weight. The verify step draws this way from a row's own softmax (every block of its kernel owns a
+ * contiguous piece of the vocabulary). out_total: the kept set's integer mass. */
+LMO_API int32_t lmo_sample_invcdf_index(const float* z, int64_t vocab, float tau, float temperature, float u, uint64_t* out_total) {
   float vmax = -INFINITY;
   for (int64_t i = 0; i < vocab; i++) if (z[i] > vmax) vmax = z[i];
   const float c = lmo_exp2_scale(temperature);
@@ -237,6 +238,40 @@ LMO_API int32_t lmo_sample_invcdf(const float* z, int64_t vocab, float tau, floa
   uint64_t cum = 0;
   for (int64_t i = 0; i < vocab; i++) if (z[i] >= tau) { cum += lmo_weight_q40(z[i], vmax, c); if (cum > target) return (int32_t)i; }
   return -1;
+}
+
+/* The sampler's inverse-CDF draw: the kept set ordered by descending logit, equal logits by ascending index (the order of a
+ * sorted top-p pipeline); token = the first in that order whose inclusive cumulative weight exceeds the target; -1 if the kept
+ * set has no weight. Equal logits have equal weights, so this is: the distinct value v at which the cumulative weight of the
+ * values above it plus count(v) * w(v) first exceeds the target, then the floor((target - before) / w(v))-th smallest index among
+ * the logits equal to v. out_total: the kept set's integer mass. */
+typedef struct { float v; int32_t i; uint64_t w; } lmo_kept_t;
+static int lmo_kept_cmp(const void* a, const void* b) {
+  const lmo_kept_t* x = (const lmo_kept_t*)a; const lmo_kept_t* y = (const lmo_kept_t*)b;
+  if (x->v != y->v) return x->v > y->v ? -1 : 1;
+  return x->i < y->i ? -1 : (x->i > y->i ? 1 : 0);
+}
+LMO_API int32_t lmo_sample_invcdf(const float* z, int64_t vocab, float tau, float temperature, float u, uint64_t* out_total) {
+  float vmax = -INFINITY;
+  for (int64_t i = 0; i < vocab; i++) if (z[i] > vmax) vmax = z[i];
+  const float c = lmo_exp2_scale(temperature);
+  lmo_kept_t* k = (lmo_kept_t*)malloc((size_t)(vocab > 0 ? vocab : 1) * sizeof(lmo_kept_t));
+  int64_t n = 0;
+  uint64_t total = 0;
+  for (int64_t i = 0; i < vocab; i++) if (z[i] >= tau) {
+    const uint64_t w = lmo_weight_q40(z[i], vmax, c);
+    if (w) { k[n].v = z[i] == 0.0f ? 0.0f : z[i]; k[n].i = (int32_t)i; k[n].w = w; n++; total += w; }   /* a weightless logit is never drawn */
+  }
+  if (out_total) *out_total = total;
+  int32_t token = -1;
+  if (total) {
+    qsort(k, (size_t)n, sizeof(lmo_kept_t), lmo_kept_cmp);
+    const uint64_t target = lmo_cdf_target(u, total);
+    uint64_t cum = 0;
+    for (int64_t j = 0; j < n; j++) { cum += k[j].w; if (cum > target) { token = k[j].i; break; } }
+  }
+  free(k);
+  return token;
 }
 
 /* ---- draft-side sampling (kernels/common/sample.metal:212-269) -------------------------------------------------------
@@ -367,7 +402,7 @@ LMO_API int32_t lmo_verify_stochastic(const float* z, int64_t vocab, int32_t n_d
       if (res > 0.0f) { cum += (uint64_t)(res * 1099511627776.0f); if (cum > target) { token = (int32_t)i; break; } }
     }
   } else {
-    token = lmo_sample_invcdf(zj, vocab, tau[j], temperature, u_final, NULL);
+    token = lmo_sample_invcdf_index(zj, vocab, tau[j], temperature, u_final, NULL);
   }
   if (out_final) *out_final = token;
   free(vmaxs); free(ks);

@@ -97,7 +97,7 @@ def merge_records(records: Sequence[bytes], cap: int, *, temperature: float, top
         c = L.lmo_exp2_scale(T32)
         kid = ids[kept]
         w = np.array([L.lmo_weight_q40(float(v), float(vmax), c) for v in vals[kept]], dtype=object)
-        o = np.argsort(kid)
+        o = np.lexsort((kid, -vals[kept].astype(np.float64)))          # descending logit, equal logits by ascending index
         total = int(sum(w))
         if total == 0:
             return -1, float(tau_f), status

@@ -134,7 +134,7 @@ def test_verify_models_on_a_small_step():
     assert acc == 2 and fin == int(z[2].argmax()) and toks.tolist() == z.argmax(-1).tolist()
     # all-accept (u = 0) ends on the bonus row; certain reject (q = 1 at the draft, u near 1) at row 0 resamples row 0
     acc, fin, _ = oracle.verify_stochastic(target, drafts, q, np.zeros(7, np.float32), uf)
-    assert acc == 7 and fin == oracle.sample_invcdf(z[7], uf)
+    assert acc == 7 and fin == oracle.sample_invcdf_index_order(z[7], uf)       # the verify step draws in index order
     acc, fin, _ = oracle.verify_stochastic(target, drafts, q, np.full(7, 0.999, np.float32), uf)
     assert 0 <= acc < 7 and 0 <= fin < 2000
 
