@@ -88,14 +88,6 @@ __device__ __forceinline__ int load_chunk(const RowView& rv, int c, float z[kChu
   return n;
 }
 
-// One element (slow path, used when a single index is needed).
-__device__ __forceinline__ float load_one(const RowView& rv, int i) {
-  float z = (rv.dtype == LM_DTYPE_BF16) ? __uint_as_float(static_cast<uint32_t>(__ldg(reinterpret_cast<const uint16_t*>(rv.row) + i)) << 16)
-                                        : __ldg(reinterpret_cast<const float*>(rv.row) + i);
-  if (rv.pen != nullptr && ((rv.pen[i >> 5] >> (i & 31)) & 1u)) z = penalise(z, rv.rho, rv.pi);
-  return canon_zero(z);
-}
-
 // ---- the counter-based noise of the reference's draw --------------------------------------------------------
 
 __host__ __device__ __forceinline__ float uniform01(uint64_t seed, uint32_t step, uint32_t t, uint32_t i) {

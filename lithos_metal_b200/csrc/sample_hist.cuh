@@ -14,8 +14,9 @@
 // sorting anything.
 //
 // The walks are two-level: 258 groups of 64 window positions (block scan), then one warp inside the group where the target
-// falls. The inverse-CDF draw knows the kept set's total weight from the histograms before it looks at the row again; its
-// second look (from L2) sums 256-logit segments from the nearer end of the row and stops at the segment holding the target.
+// falls. The inverse-CDF draw (descending value order, equal values by ascending index) is decided by the same walks on integer
+// weights, down to the value; its second look at the row (from L2) only counts the logits equal to that value, in 256-logit
+// segments from the nearer end of the row, and stops at the segment that holds the one it wants.
 //
 // Rows this kernel cannot take go to the generic kernel through the `redo` list: a logit outside the window other than 0
 // and -inf (NaN, +inf, |z| >= 2^25, 0 < |z| < 2^-39), more than 65535 equal logits, more than kPenCap distinct penalised ids
@@ -58,8 +59,8 @@ struct HistSmem {
   float b_val[kPenCap];                           // distinct penalised values, descending
   uint16_t b_ins[kPenCap];                        // the window position each is inserted before: the smallest p with value(p) <= b_val
   uint16_t b_cnt[kPenCap];                        // how many logits carry each value; from phase 4 on the running sum (inclusive)
-  unsigned long long seg_fix[kMaxSegs];           // draw: per segment, weight of its kept penalised logits minus what their raw codes would weigh
-  unsigned long long batch_sum[2][kBatchSegs];    // draw: segment totals of the batch in hand (double-buffered)
+  unsigned long long seg_fix[kMaxSegs];           // draw: per segment (as 32-bit counters), its penalised logits equal to the drawn value
+  unsigned long long batch_sum[2][kBatchSegs];    // draw: (as 32-bit counters) segment counts of the batch in hand, double-buffered
   double g_mass[kGroupsH + 2];
   uint32_t g_cnt[kGroupsH + 2];
   uint64_t scratch[32];

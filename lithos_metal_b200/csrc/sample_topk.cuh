@@ -77,24 +77,6 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 __device__ __forceinline__ void prefetch_l2_line(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 __device__ __forceinline__ float ex2_approx(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
-__device__ __forceinline__ int next_pow2(int n) { int p = 32; while (p < n) p <<= 1; return p; }
-// bitonic sort of a[0 .. n_pow2) in shared memory, descending; every thread of the block calls. One compare-exchange
-// per thread and step: thread t takes the t-th pair (i, i | j) with i's bit j clear.
-__device__ __forceinline__ void bitonic_desc(unsigned long long* a, int n_pow2) {
-  for (int k = 2; k <= n_pow2; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int t = threadIdx.x; t < (n_pow2 >> 1); t += blockDim.x) {
-        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
-        const int partner = i | j;
-        const unsigned long long x = a[i], y = a[partner];
-        const bool desc = (i & k) == 0;
-        if (desc ? (x < y) : (x > y)) { a[i] = y; a[partner] = x; }
-      }
-      __syncthreads();
-    }
-  }
-}
-
 // Inclusive FP64 prefix sum over v[0 .. n) in place, index order; every thread calls. warp_d: one entry per warp.
 __device__ __forceinline__ void scan_f64(double* v, int n, double* warp_d) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
@@ -113,21 +95,6 @@ __device__ __forceinline__ void scan_f64(double* v, int n, double* warp_d) {
     carry += tot;
   }
   __syncthreads();
-}
-
-// Inclusive u64 prefix sum over v[0 .. n) in place, index order; every thread calls. Returns the total.
-__device__ __forceinline__ uint64_t scan_u64(unsigned long long* v, int n, uint64_t* scratch) {
-  uint64_t carry = 0ull;
-  for (int base = 0; base < n; base += blockDim.x) {
-    const int i = base + threadIdx.x;
-    const uint64_t x = (i < n) ? v[i] : 0ull;
-    uint64_t tot = 0ull;
-    const uint64_t excl = block_exclusive_scan_u64(x, scratch, &tot);
-    if (i < n) v[i] = carry + excl + x;
-    carry += tot;
-    __syncthreads();
-  }
-  return carry;
 }
 
 // Warp-aggregated append: every lane of the warp calls with its count; returns the lane's first slot.
