@@ -82,3 +82,41 @@ def test_rows_on_the_edge_of_the_fp32_decision_band():
     far = np.abs(np.array([d for _, _, _, d in rows])) >= 1e-4
     assert on_candidate_path[far].all()                                    # the band does not reach 1e-4
     assert not on_candidate_path[np.array([d for _, _, _, d in rows]) == 0.0].any()   # dead on the boundary: never decided in FP32
+
+
+@pytest.mark.parametrize("exact_only", [False, True])
+def test_draw_over_runs_of_equal_logits_from_both_sources(exact_only):
+    """The inverse-CDF draw walks equal logits in index order. With repetition 2.0 and presence 0.5 a penalised logit lands exactly
+    on BF16 codes that unpenalised logits of the row carry too (z / 2 - 0.5), so runs of equal values mix penalised and unpenalised
+    positions; coarse logits (multiples of 1/4) make the runs long. Uniforms spread over [0, 1) land inside such runs in every
+    kernel: rows with a top_k (candidate kernel), without one (histogram kernel), and with exact_only (histogram kernel for all)."""
+    rows, vocab = 96, 65536
+    rng = np.random.default_rng(123)
+    z = np.round(rng.standard_normal((rows, vocab)) * 8.0) / 4.0                                  # values k / 4, |z| up to ~10
+    codes = oracle.f32_to_bf16(z.astype(np.float32))
+    hist = rng.integers(0, vocab, (rows, 1500)).astype(np.int32)
+    top = np.argsort(-z, axis=1)[:, :200]
+    hist[:, :200] = top                                                                            # the penalties reach the top of the row
+    cfg = dict(logits=codes, temperature=rng.uniform(0.8, 2.5, rows).astype(np.float32),
+               top_k=np.where(np.arange(rows) % 3 == 0, 0, np.where(np.arange(rows) % 3 == 1, 40, 700)).astype(np.int32),
+               top_p=rng.uniform(0.85, 0.999, rows).astype(np.float32), history=hist, uniforms=np.linspace(0.001, 0.999, rows).astype(np.float32))
+    x = bf16_tensor(cfg["logits"])
+    knobs = {k: torch.from_numpy(cfg[k]).cuda() for k in ("temperature", "top_k", "top_p")}
+    pen = dict(repetition_penalty=2.0, presence_penalty=0.5)
+    r = lm.sample(x, lm.SamplingParams(draw="inverse_cdf", exact_only=exact_only, **pen, **knobs), history=torch.from_numpy(hist).cuda(),
+                  uniforms=torch.from_numpy(cfg["uniforms"]).cuda(), return_tau=True, return_status=True)
+    tok, tau, _ = oracle.sample_batch(codes, temperature=cfg["temperature"], top_k=cfg["top_k"], top_p=cfg["top_p"], history=hist, draw="inverse_cdf",
+                                      uniforms=cfg["uniforms"], n_threads=THREADS, **pen)
+    np.testing.assert_array_equal(r.tau.cpu().numpy(), tau)
+    np.testing.assert_array_equal(r.tokens.cpu().numpy(), tok)
+    status = r.status.cpu().numpy()
+    assert np.count_nonzero(status & 1) <= rows // 8, status                                       # the streaming kernels keep (nearly) all of these rows
+    # the drawn tokens do sit in mixed runs: for some rows the token's value is carried by penalised and unpenalised positions alike
+    zf = oracle.bf16_to_f32(codes)
+    mixed = 0
+    for i in range(rows):
+        zi = oracle.apply_penalties(zf[i], hist[i], 2.0, 0.5)
+        same = np.nonzero(zi == zi[tok[i]])[0]
+        pen_ids = np.unique(hist[i])
+        mixed += int(np.isin(same, pen_ids).any() and (~np.isin(same, pen_ids)).any())
+    assert mixed >= 3, mixed
