@@ -421,17 +421,19 @@ LM_API int lm_confidence(const lm_confidence_args* args);
  * from its epilogue, csrc/sample_tiles.cuh), and [T, V] never has to exist: per row the library keeps the running maximum, the
  * running softmass and the logits that can still be among the row's top_k, in a caller-owned state buffer.
  *
- *   lm_tile_begin    clears the state of `rows` rows (stream-ordered);
+ *   lm_tile_begin    clears the state of `rows` rows and, when a history is given, notes each row's distinct history ids (the
+ *                    penalties are then applied to the logits as they arrive); stream-ordered; the tile fields are not read;
  *   lm_tile_consume  takes the columns col0 .. col0 + cols of every row; tiles may come in any column order, each column once;
- *                    FP32 tiles are rounded to BF16 first, as the projection's store would;
+ *                    FP32 tiles are rounded to BF16 first, as the projection's store would; history / penalties as given to
+ *                    lm_tile_begin;
  *   lm_tile_finish   writes what lm_sample would write for the same rows and knobs (tokens, tau, status with
- *                    LM_STATUS_CANDIDATE_PATH), bit-identical; `logits`, `workspace`, `history`, `out_stats` and `out_probs`
- *                    of the lm_sample_args are not used and history / out_stats / out_probs must be NULL.
+ *                    LM_STATUS_CANDIDATE_PATH; greedy rows: the argmax, status 0), bit-identical; `logits`, `workspace`, the
+ *                    history fields, `out_stats` and `out_probs` of the lm_sample_args are not read (out_stats / out_probs must
+ *                    be NULL): the penalties are those given to lm_tile_begin.
  *
- * Rows this path does not take get token -1 and LM_STATUS_TILE_DECLINED: rows without a top_k in 1..1024, greedy rows
- * (temperature 0: use lm_argmax on the tiles' maxima instead), rows with a NaN or +inf, rows whose top-k boundary lies at or
- * below zero or whose top-p boundary cannot be decided from the FP32 softmass. The caller materialises those rows and calls
- * lm_sample; a caller with repetition / presence penalties does so for every row.
+ * Rows this path does not take get token -1 and LM_STATUS_TILE_DECLINED: stochastic rows without a top_k in 1..1024, rows with a
+ * NaN or +inf, rows whose top-k boundary lies at or below zero or whose top-p boundary cannot be decided from the FP32 softmass.
+ * The caller materialises those rows and calls lm_sample.
  */
 #define LM_TILE_MAX_COLS 2048
 typedef struct lm_tile_args {
@@ -443,13 +445,16 @@ typedef struct lm_tile_args {
   int64_t col0, cols;          /* 0 <= col0, col0 + cols <= vocab, 1 <= cols <= LM_TILE_MAX_COLS */
   const float* temperature; float temperature_s;   /* as in lm_sample_args; the same values must be given to lm_tile_finish */
   const int32_t* top_k; int32_t top_k_s;
-  void* state;                 /* lm_tile_state_bytes(rows) bytes, 256-byte aligned, device memory */
+  void* state;                 /* lm_tile_state_bytes(rows, vocab, history != NULL) bytes, 256-byte aligned, device memory */
   size_t state_bytes;
   void* stream;
+  const int32_t* history;      /* [rows, hist_stride] token ids to penalise, or NULL; the same in every call of one step */
+  int64_t hist_len, hist_stride;
+  float repetition_penalty, presence_penalty;   /* as in lm_sample_args (1 and 0: no penalty) */
 } lm_tile_args;
 
-LM_API size_t lm_tile_state_bytes(int64_t rows);
-LM_API int lm_tile_begin(void* state, size_t state_bytes, int64_t rows, void* stream);
+LM_API size_t lm_tile_state_bytes(int64_t rows, int64_t vocab, int32_t with_history);
+LM_API int lm_tile_begin(const lm_tile_args* args);
 LM_API int lm_tile_consume(const lm_tile_args* args);
 LM_API int lm_tile_finish(const lm_sample_args* sample, void* state, size_t state_bytes);
 

@@ -50,6 +50,7 @@ class TileArgs(C.Structure):
         ("tile_stride", C.c_int64), ("col0", C.c_int64), ("cols", C.c_int64),
         ("temperature", C.c_void_p), ("temperature_s", C.c_float), ("top_k", C.c_void_p), ("top_k_s", C.c_int32),
         ("state", C.c_void_p), ("state_bytes", C.c_size_t), ("stream", C.c_void_p),
+        ("history", C.c_void_p), ("hist_len", C.c_int64), ("hist_stride", C.c_int64), ("repetition_penalty", C.c_float), ("presence_penalty", C.c_float),
     ]
 
 
@@ -129,9 +130,9 @@ def lib():
         L.lm_verify.restype = C.c_int
         L.lm_verify.argtypes = [C.POINTER(VerifyArgs)]
         L.lm_tile_state_bytes.restype = C.c_size_t
-        L.lm_tile_state_bytes.argtypes = [C.c_int64]
+        L.lm_tile_state_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int32]
         L.lm_tile_begin.restype = C.c_int
-        L.lm_tile_begin.argtypes = [C.c_void_p, C.c_size_t, C.c_int64, C.c_void_p]
+        L.lm_tile_begin.argtypes = [C.POINTER(TileArgs)]
         L.lm_tile_consume.restype = C.c_int
         L.lm_tile_consume.argtypes = [C.POINTER(TileArgs)]
         L.lm_tile_finish.restype = C.c_int

@@ -397,34 +397,56 @@ int lm_sample(const lm_sample_args* a) {
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }
 
-size_t lm_tile_state_bytes(int64_t rows) {
-  if (rows <= 0) return 0;
-  return align256(static_cast<size_t>(rows) * sizeof(TileRow)) + static_cast<size_t>(rows) * kTileListCap * sizeof(unsigned long long);
+static size_t tile_lists_offset(int64_t rows) { return align256(static_cast<size_t>(rows) * sizeof(TileRow)); }
+static size_t tile_bits_offset(int64_t rows) { return tile_lists_offset(rows) + static_cast<size_t>(rows) * kTileListCap * sizeof(unsigned long long); }
+static int tile_pen_words(int64_t vocab) { return static_cast<int>((vocab + 127) / 128 * 4); }
+
+size_t lm_tile_state_bytes(int64_t rows, int64_t vocab, int32_t with_history) {
+  if (rows <= 0 || vocab < 0) return 0;
+  return tile_bits_offset(rows) + (with_history ? static_cast<size_t>(rows) * tile_pen_words(vocab) * sizeof(uint32_t) : 0);
 }
 
-int lm_tile_begin(void* state, size_t state_bytes, int64_t rows, void* stream) {
-  if (rows < 0) return LM_E_INVALID;
-  if (rows == 0) return LM_OK;
-  if (rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
-  if (!state || (reinterpret_cast<uintptr_t>(state) & 255u) || state_bytes < lm_tile_state_bytes(rows)) return LM_E_WORKSPACE;
-  // only the per-row records: a list is read up to its record's count
-  const cudaError_t e = cudaMemsetAsync(state, 0, static_cast<size_t>(rows) * sizeof(TileRow), static_cast<cudaStream_t>(stream));
+// The checks lm_tile_begin and lm_tile_consume share, and the device-side view of the arguments.
+static int tile_dev(const lm_tile_args* a, bool consume, TileDev* out) {
+  if (!a || a->struct_size != sizeof(lm_tile_args)) return LM_E_INVALID;
+  if (a->rows < 0 || a->vocab < 0) return LM_E_INVALID;
+  if (a->rows == 0) return LM_OK;
+  if (a->vocab > LM_MAX_VOCAB || a->rows > 0x7FFFFFFF || a->hist_len > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
+  if (a->history != nullptr && (a->hist_len < 0 || a->hist_stride < a->hist_len || !(a->repetition_penalty > 0.0f))) return LM_E_INVALID;
+  if (consume) {
+    if (a->dtype != LM_DTYPE_BF16 && a->dtype != LM_DTYPE_F32) return LM_E_INVALID;
+    if (!a->tile || a->cols < 1 || a->col0 < 0 || a->col0 + a->cols > a->vocab || a->tile_stride < a->cols) return LM_E_INVALID;
+    if (a->cols > LM_TILE_MAX_COLS) return LM_E_UNSUPPORTED;
+  }
+  const bool pen = a->history != nullptr && a->hist_len > 0 && !(a->repetition_penalty == 1.0f && a->presence_penalty == 0.0f);
+  if (!a->state || (reinterpret_cast<uintptr_t>(a->state) & 255u) || a->state_bytes < lm_tile_state_bytes(a->rows, a->vocab, pen ? 1 : 0)) return LM_E_WORKSPACE;
+  TileDev& T = *out;
+  T.tile = a->tile; T.dtype = a->dtype; T.rows = static_cast<int>(a->rows); T.vocab = static_cast<int>(a->vocab); T.tile_stride = a->tile_stride;
+  T.col0 = static_cast<int>(a->col0); T.cols = static_cast<int>(a->cols);
+  T.temperature = a->temperature; T.temperature_s = a->temperature_s; T.top_k = a->top_k; T.top_k_s = a->top_k_s;
+  char* base = static_cast<char*>(a->state);
+  T.rows_state = reinterpret_cast<TileRow*>(base);
+  T.lists = reinterpret_cast<unsigned long long*>(base + tile_lists_offset(a->rows));
+  T.pen_bits = pen ? reinterpret_cast<uint32_t*>(base + tile_bits_offset(a->rows)) : nullptr;
+  T.pen_words = tile_pen_words(a->vocab);
+  T.history = pen ? a->history : nullptr; T.hist_len = static_cast<int>(a->hist_len); T.hist_stride = a->hist_stride;
+  T.rho = a->repetition_penalty; T.pi = a->presence_penalty;
+  return LM_OK;
+}
+
+int lm_tile_begin(const lm_tile_args* a) {
+  TileDev T;
+  const int rc = tile_dev(a, false, &T);
+  if (rc != LM_OK || a->rows == 0) return rc;
+  tile_begin_kernel<<<T.rows, kTileBlock, 0, static_cast<cudaStream_t>(a->stream)>>>(T);
+  const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }
 
 int lm_tile_consume(const lm_tile_args* a) {
-  if (!a || a->struct_size != sizeof(lm_tile_args)) return LM_E_INVALID;
-  if (a->rows < 0 || a->vocab < 0 || (a->dtype != LM_DTYPE_BF16 && a->dtype != LM_DTYPE_F32)) return LM_E_INVALID;
-  if (a->rows == 0) return LM_OK;
-  if (!a->tile || a->cols < 1 || a->col0 < 0 || a->col0 + a->cols > a->vocab || a->tile_stride < a->cols) return LM_E_INVALID;
-  if (a->cols > LM_TILE_MAX_COLS || a->vocab > LM_MAX_VOCAB || a->rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
-  if (!a->state || (reinterpret_cast<uintptr_t>(a->state) & 255u) || a->state_bytes < lm_tile_state_bytes(a->rows)) return LM_E_WORKSPACE;
   TileDev T;
-  T.tile = a->tile; T.dtype = a->dtype; T.rows = static_cast<int>(a->rows); T.vocab = static_cast<int>(a->vocab); T.tile_stride = a->tile_stride;
-  T.col0 = static_cast<int>(a->col0); T.cols = static_cast<int>(a->cols);
-  T.temperature = a->temperature; T.temperature_s = a->temperature_s; T.top_k = a->top_k; T.top_k_s = a->top_k_s;
-  T.rows_state = static_cast<TileRow*>(a->state);
-  T.lists = reinterpret_cast<unsigned long long*>(static_cast<char*>(a->state) + align256(static_cast<size_t>(a->rows) * sizeof(TileRow)));
+  const int rc = tile_dev(a, true, &T);
+  if (rc != LM_OK || a->rows == 0) return rc;
   tile_consume_kernel<<<T.rows, kTileBlock, 0, static_cast<cudaStream_t>(a->stream)>>>(T);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
@@ -435,13 +457,13 @@ int lm_tile_finish(const lm_sample_args* a, void* state, size_t state_bytes) {
   if (a->rows < 0 || a->vocab < 0) return LM_E_INVALID;
   if (a->draw != LM_DRAW_GUMBEL && a->draw != LM_DRAW_INVERSE_CDF) return LM_E_INVALID;
   if (a->rows == 0) return LM_OK;
-  if (!a->out_tokens || a->history != nullptr || a->out_stats != nullptr || a->out_probs != nullptr) return LM_E_INVALID;
+  if (!a->out_tokens || a->out_stats != nullptr || a->out_probs != nullptr) return LM_E_INVALID;
   if (a->vocab > kTopkMaxVocab || a->rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
   if (a->step_state != nullptr && lm_step_state_bytes(a->t_max, a->gamma_max) == 0) return LM_E_INVALID;
-  if (a->draw == LM_DRAW_INVERSE_CDF && a->uniforms == nullptr) return LM_E_INVALID;
-  if (!state || (reinterpret_cast<uintptr_t>(state) & 255u) || state_bytes < lm_tile_state_bytes(a->rows)) return LM_E_WORKSPACE;
+  if (a->draw == LM_DRAW_INVERSE_CDF && a->uniforms == nullptr && (a->temperature != nullptr || a->temperature_s > 0.0f)) return LM_E_INVALID;
+  if (!state || (reinterpret_cast<uintptr_t>(state) & 255u) || state_bytes < lm_tile_state_bytes(a->rows, a->vocab, 0)) return LM_E_WORKSPACE;
   SampleDev P = sample_dev(a);
-  P.logits = nullptr;
+  P.logits = nullptr; P.history = nullptr;
   int sms = 0;
   int rc = sm_count(&sms);
   if (rc != LM_OK) return rc;
@@ -450,7 +472,7 @@ int lm_tile_finish(const lm_sample_args* a, void* state, size_t state_bytes) {
   const long long cap = static_cast<long long>(kTopkPerSM) * sms;
   const int grid = static_cast<int>(a->rows < cap ? a->rows : cap);
   tile_finish_kernel<<<grid, kTB, sizeof(TopkSmem), static_cast<cudaStream_t>(a->stream)>>>(
-      P, static_cast<TileRow*>(state), reinterpret_cast<unsigned long long*>(static_cast<char*>(state) + align256(static_cast<size_t>(a->rows) * sizeof(TileRow))));
+      P, static_cast<TileRow*>(state), reinterpret_cast<unsigned long long*>(static_cast<char*>(state) + tile_lists_offset(a->rows)));
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }

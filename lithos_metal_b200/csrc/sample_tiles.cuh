@@ -18,8 +18,9 @@
 // the tile's own maximum and joined in FP64, so the error does not grow with the number of tiles), a cutoff value, and a list of
 // every logit seen so far at or above the cutoff. The cutoff starts at -inf and only ever rises to the value of the k'-th
 // largest logit seen so far (k' = top_k + top_k / 3 + 150, a compaction when the list fills), so the list always holds the
-// row's top_k. Rows without a top_k, with penalties, or whose candidates do not fit the exact phases are DECLINED (status bit):
-// the caller materialises those rows and calls lm_sample.
+// row's top_k. Penalties are applied as the logits arrive (a bitmap of the row's distinct history ids in the state, built by
+// tile_begin_kernel); greedy rows keep a running argmax. Rows without a top_k, or whose candidates do not fit the exact phases,
+// are DECLINED (status bit): the caller materialises those rows and calls lm_sample.
 #pragma once
 #include "common.cuh"
 #include "sample_topk.cuh"
@@ -32,10 +33,12 @@ constexpr int kTileFill = kTileListCap - kTileMaxCols;   // a list longer than t
 constexpr int kTileBlock = 256;
 constexpr uint32_t kTileDeclined = 1u;      // TileRow.flags
 
-struct TileRow {                            // 32 bytes per row; all zero = nothing seen yet
-  double m;                                 // running maximum (valid when seen != 0)
-  double s;                                 // sum_i 2^((z_i - m) c)
-  float cutoff;                             // every logit >= cutoff seen so far is in the list (valid when cut_set != 0)
+struct TileRow {                            // 48 bytes per row; all zero = nothing seen yet
+  double m;                                 // running maximum (valid when something was seen)
+  double s;                                 // sum_i 2^((z_i - m) c) over everything seen
+  double s_pen;                             // the part of s that penalised logits contributed
+  unsigned long long best;                  // packed (value, lowest index) of the running maximum: the greedy pick
+  float cutoff;                             // every logit >= cutoff seen so far is in the list (valid when the cutoff bit is set)
   uint32_t n;                               // entries in the list
   uint32_t flags;                           // bit 0: declined; bit 1: cutoff set; bit 2: something seen
   uint32_t pad;
@@ -45,6 +48,8 @@ struct TileDev {
   const void* tile; int dtype; int rows; int vocab; int64_t tile_stride; int col0; int cols;
   const float* temperature; float temperature_s; const int32_t* top_k; int32_t top_k_s;
   TileRow* rows_state; unsigned long long* lists;      // lists[row * kTileListCap + i]
+  uint32_t* pen_bits; int pen_words;                   // per row: bitmap of its distinct history ids (pen_words words), or nullptr
+  const int32_t* history; int hist_len; int64_t hist_stride; float rho, pi;
 };
 
 __device__ __forceinline__ uint32_t f32_to_bf16_code(float f) {            // round to nearest even, as a BF16 store of the logit would
@@ -101,12 +106,40 @@ __device__ int tile_filter(unsigned long long* list, int n, uint32_t min_key, ui
 
 // One row of one tile. codes: the row's `cols` BF16 codes of columns col0 .. col0 + cols (shared or global memory). Every thread
 // of the block calls with the same arguments. scratch: 256 + 2 + 32 words and 32 doubles of shared memory (TileScratch).
-struct TileScratch { uint32_t hist[256]; uint32_t pick[2]; uint32_t warp_cnt[32]; double warp_d[32]; uint64_t warp_m[32]; uint32_t n_now; };
+struct TileScratch { uint32_t hist[256]; uint32_t pick[2]; uint32_t warp_cnt[32]; double warp_d[32]; double warp_p[32]; uint64_t warp_m[32]; uint32_t n_now; };
 
 __device__ void tile_consume_row(TileRow* st, unsigned long long* list, const uint16_t* codes, int cols, int col0, float temperature, int top_k,
-                                 TileScratch& t) {
+                                 const uint32_t* pen_bits, float rho, float pi, TileScratch& t) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
   if (st->flags & kTileDeclined) return;
+  // the logit of column j of the tile, as the sampler sees it: widened, penalised if the row's history holds its id, -0 folded into +0
+  auto logit = [&](int j, bool* penalised) -> float {
+    float z = __uint_as_float(static_cast<uint32_t>(codes[j]) << 16);
+    const int id = col0 + j;
+    const bool p = pen_bits != nullptr && ((pen_bits[id >> 5] >> (id & 31)) & 1u);
+    if (p) z = penalise(z, rho, pi);
+    *penalised = p;
+    return canon_zero(z);
+  };
+  if (temperature == 0.0f) {                                               // greedy: the running argmax is all there is
+    uint64_t gb = 0ull; bool gnan = false;
+    for (int j = tid; j < cols; j += blockDim.x) {
+      bool p; const float z = logit(j, &p);
+      gnan = gnan || (z != z);
+      const uint64_t k = pack_best(z, static_cast<uint32_t>(col0 + j));
+      gb = k > gb ? k : gb;
+    }
+    gb = warp_max_u64(gb);
+    if (lane == 0) t.warp_m[warp] = gb;
+    const bool any = __syncthreads_or(gnan) != 0;
+    if (tid == 0) {
+      uint64_t bb = st->best;
+      for (int w = 0; w < nw; w++) bb = t.warp_m[w] > bb ? t.warp_m[w] : bb;
+      st->best = bb; st->flags |= 4u | (any ? kTileDeclined : 0u);
+    }
+    __syncthreads();
+    return;
+  }
   if (top_k < 1 || top_k > kTopkMaxK || !(temperature > 0.0f)) { if (tid == 0) st->flags |= kTileDeclined; return; }
   const double c64 = 1.4426950408889634 / static_cast<double>(temperature);
   const float c2a = static_cast<float>(c64);
@@ -123,7 +156,7 @@ __device__ void tile_consume_row(TileRow* st, unsigned long long* list, const ui
   // ---- the tile's maximum and its softmass relative to that maximum
   uint64_t best = 0ull; bool nan = false;
   for (int j = tid; j < cols; j += blockDim.x) {
-    const float z = canon_zero(__uint_as_float(static_cast<uint32_t>(codes[j]) << 16));
+    bool pz; const float z = logit(j, &pz);
     nan = nan || (z != z);
     const uint64_t p = pack_best(z, static_cast<uint32_t>(j));
     best = p > best ? p : best;
@@ -135,19 +168,21 @@ __device__ void tile_consume_row(TileRow* st, unsigned long long* list, const ui
   for (int w = 0; w < nw; w++) bb = t.warp_m[w] > bb ? t.warp_m[w] : bb;
   const float tmax = best_value(bb);
   if (any_nan || tmax == INFINITY) { if (tid == 0) st->flags |= kTileDeclined; return; }   // NaN / +inf: the exact path reports them
-  float acc = 0.0f;
+  float acc = 0.0f, acc_pen = 0.0f;
   for (int j = tid; j < cols; j += blockDim.x) {
-    const float z = __uint_as_float(static_cast<uint32_t>(codes[j]) << 16);
-    acc += ex2_approx(__fmul_rn(__fsub_rn(z, tmax), c2a));                // z - tmax is exact for BF16 values within 16 binades
+    bool p; const float z = logit(j, &p);
+    const float e = ex2_approx(__fmul_rn(__fsub_rn(z, tmax), c2a));       // z - tmax is exact for BF16 values within 16 binades
+    if (p) acc_pen += e; else acc += e;                                   // (a penalised logit is not on the BF16 grid: its term is counted apart)
   }
-  double sd = warp_sum_f64(static_cast<double>(acc));
-  if (lane == 0) t.warp_d[warp] = sd;
+  const double sd = warp_sum_f64(static_cast<double>(acc)), sp = warp_sum_f64(static_cast<double>(acc_pen));
+  if (lane == 0) { t.warp_d[warp] = sd; t.warp_p[warp] = sp; }
   if (tid == 0) t.n_now = static_cast<uint32_t>(n);
   __syncthreads();
   // ---- the logits at or above the cutoff join the list
   for (int j0 = 0; j0 < cols; j0 += blockDim.x) {                         // uniform trip count: warp votes inside
     const int j = j0 + tid;
-    const float z = j < cols ? canon_zero(__uint_as_float(static_cast<uint32_t>(codes[j]) << 16)) : -INFINITY;
+    bool p = false;
+    const float z = j < cols ? logit(j, &p) : -INFINITY;
     const bool take = j < cols && z >= cutoff;
     const uint32_t votes = __ballot_sync(kFull, take);
     uint32_t base = 0u;
@@ -160,14 +195,15 @@ __device__ void tile_consume_row(TileRow* st, unsigned long long* list, const ui
   }
   __syncthreads();
   if (tid == 0) {
-    double ts = 0.0;
-    for (int w = 0; w < nw; w++) ts += t.warp_d[w];
+    double ts = 0.0, tp = 0.0;
+    for (int w = 0; w < nw; w++) { ts += t.warp_d[w]; tp += t.warp_p[w]; }
     const bool seen = (st->flags & 4u) != 0u;
     const double m_old = seen ? st->m : -INFINITY, tm = static_cast<double>(tmax);
     const double m_new = tm > m_old ? tm : m_old;
-    double s = ts * exp2((tm - m_new) * c64);
-    if (seen) s += st->s * exp2((m_old - m_new) * c64);
-    st->m = m_new; st->s = s;
+    const double f_tile = exp2((tm - m_new) * c64), f_old = seen ? exp2((m_old - m_new) * c64) : 0.0;
+    st->s = (ts + tp) * f_tile + (seen ? st->s * f_old : 0.0);
+    st->s_pen = tp * f_tile + (seen ? st->s_pen * f_old : 0.0);
+    st->m = m_new;
     st->cutoff = cutoff; st->n = min(t.n_now, static_cast<uint32_t>(kTileListCap));
     st->flags |= 4u | (cutoff > -INFINITY ? 2u : 0u) | (t.n_now > static_cast<uint32_t>(kTileListCap) ? kTileDeclined : 0u);
   }
@@ -186,7 +222,24 @@ __global__ void __launch_bounds__(kTileBlock) tile_consume_kernel(TileDev P) {
   }
   __syncthreads();
   tile_consume_row(P.rows_state + row, P.lists + static_cast<size_t>(row) * kTileListCap, codes, P.cols, P.col0,
-                   P.temperature ? P.temperature[row] : P.temperature_s, P.top_k ? P.top_k[row] : P.top_k_s, t);
+                   P.temperature ? P.temperature[row] : P.temperature_s, P.top_k ? P.top_k[row] : P.top_k_s,
+                   P.pen_bits ? P.pen_bits + static_cast<size_t>(row) * P.pen_words : nullptr, P.rho, P.pi, t);
+}
+
+// Clears the rows' states and, with a history, builds each row's bitmap of distinct history ids. One block per row.
+__global__ void __launch_bounds__(kTileBlock) tile_begin_kernel(TileDev P) {
+  const int row = blockIdx.x;
+  if (row >= P.rows) return;
+  if (threadIdx.x < sizeof(TileRow) / 8) reinterpret_cast<unsigned long long*>(P.rows_state + row)[threadIdx.x] = 0ull;
+  if (P.pen_bits == nullptr) return;
+  uint32_t* bits = P.pen_bits + static_cast<size_t>(row) * P.pen_words;
+  for (int i = threadIdx.x; i < P.pen_words; i += blockDim.x) bits[i] = 0u;
+  __syncthreads();
+  const int32_t* h = P.history + static_cast<int64_t>(row) * P.hist_stride;
+  for (int i = threadIdx.x; i < P.hist_len; i += blockDim.x) {
+    const int id = __ldg(h + i);
+    if (id >= 0 && id < P.vocab) atomicOr(&bits[id >> 5], 1u << (id & 31));
+  }
 }
 
 // The rows' tokens from their states and lists: a last compaction to what the exact phases hold, the candidates into shared
@@ -202,6 +255,15 @@ __global__ void __launch_bounds__(kTB, kTopkPerSM) tile_finish_kernel(SampleDev 
     unsigned long long* list = lists + static_cast<size_t>(row) * kTileListCap;
     const int top_k = P.top_k ? P.top_k[row] : P.top_k_s;
     const float T = P.temperature ? P.temperature[row] : P.temperature_s;
+    if (T == 0.0f && !(st->flags & kTileDeclined) && (st->flags & 4u)) {     // greedy: the running argmax
+      if (tid == 0) {
+        P.out_tokens[row] = static_cast<int>(best_index(st->best));
+        if (P.out_tau) P.out_tau[row] = -INFINITY;
+        if (P.out_status) P.out_status[row] = 0u;
+      }
+      __syncthreads();
+      continue;
+    }
     bool ok = !(st->flags & kTileDeclined) && (st->flags & 4u) && top_k >= 1 && top_k <= kTopkMaxK && T > 0.0f && static_cast<int>(st->n) >= top_k;
     int n = static_cast<int>(st->n);
     uint32_t cut_key = 0u;
@@ -226,7 +288,7 @@ __global__ void __launch_bounds__(kTB, kTopkPerSM) tile_finish_kernel(SampleDev 
       }
       __syncthreads();
       RowMass zm;
-      zm.need = true; zm.z_tilde = st->s; zm.z_raw = st->s; zm.z_corr = 0.0;
+      zm.need = true; zm.z_tilde = st->s; zm.z_raw = st->s - st->s_pen; zm.z_corr = st->s_pen;
       zm.shift = st->m * (1.4426950408889634 / static_cast<double>(T));
       zm.ref = static_cast<float>(st->m); zm.acc_terms = static_cast<double>(kTileMaxCols / kTileBlock) + 1.0;
       ok = topk_finish(P, row, c, cut_code, zm);

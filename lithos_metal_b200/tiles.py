@@ -3,9 +3,9 @@
 The reference's vocabulary projection writes its logits [T, V] to memory and the sampler reads them back
 (lm_head_forward, monolith/nn/lm_head.py:50-60; the sampler dispatches, monolith/kernels.py:720-775). A projection that
 produces its output in column tiles hands each tile to :meth:`TileSampler.consume` instead and asks for the tokens at the end;
-the full tensor never has to exist. The tokens are the ones :func:`lithos_metal_b200.sample` returns for the same logits and
-knobs; rows this path does not take (no top_k, greedy, penalties, undecidable boundaries) come back as token -1 with
-``STATUS_TILE_DECLINED`` and the caller samples those from materialised logits.
+the full tensor never has to exist. The tokens are the ones :func:`lithos_metal_b200.sample` returns for the same logits,
+history and knobs; rows this path does not take (stochastic rows without a top_k, undecidable boundaries) come back as token -1
+with ``STATUS_TILE_DECLINED`` and the caller samples those from materialised logits.
 """
 import ctypes as C
 from typing import Optional
@@ -20,41 +20,60 @@ class TileSampler:
     """State for one sampling step over ``rows`` rows of a ``vocab``-wide projection whose logits arrive in column tiles.
 
     ``params`` holds the same knobs as :func:`sample`; ``temperature`` and ``top_k`` are needed while the tiles arrive, the
-    rest at :meth:`finish`. The state (about 64 KiB per row) lives on ``device`` and is reused by :meth:`begin`.
+    rest at :meth:`finish`. ``history`` [rows, n] int32 token ids (with the penalties of ``params``) is noted by :meth:`begin`
+    and applied to the logits as they arrive. The state (about 64 KiB per row, plus vocab / 8 bytes per row with a history)
+    lives on ``device`` and is reused by :meth:`begin`.
     """
 
-    def __init__(self, rows: int, vocab: int, params: SamplingParams, device: Optional[torch.device] = None) -> None:
-        if params.repetition_penalty != 1.0 or params.presence_penalty != 0.0:
-            raise ValueError("the tile path takes no penalties: sample those rows from materialised logits")
+    def __init__(self, rows: int, vocab: int, params: SamplingParams, device: Optional[torch.device] = None,
+                 history: Optional[torch.Tensor] = None) -> None:
         self.rows, self.vocab, self.params = int(rows), int(vocab), params
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if not params.repetition_penalty > 0:
+            raise ValueError("repetition_penalty must be positive")
+        self._pen = history is not None and history.shape[1] > 0 and not (params.repetition_penalty == 1.0 and params.presence_penalty == 0.0)
         L = _lib.lib()
-        self._state = torch.empty(max(L.lm_tile_state_bytes(self.rows), 256), dtype=torch.uint8, device=self.device)
-        self._keep = []
+        self._state = torch.empty(max(L.lm_tile_state_bytes(self.rows, self.vocab, 1 if self._pen else 0), 256), dtype=torch.uint8, device=self.device)
         self._t = _knob(params.temperature, self.rows, torch.float32, self.device, "temperature")
         self._k = _knob(params.top_k, self.rows, torch.int32, self.device, "top_k")
-        self.begin()
+        self._history = None
+        self.begin(history)
 
-    def begin(self) -> None:
-        """Forget every tile seen so far (stream-ordered)."""
-        L = _lib.lib()
+    def _args(self) -> "_lib.TileArgs":
+        a = _lib.TileArgs()
+        a.struct_size = C.sizeof(_lib.TileArgs)
+        a.rows, a.vocab = self.rows, self.vocab
+        a.temperature, a.temperature_s = self._t[0], float(self._t[1])
+        a.top_k, a.top_k_s = self._k[0], int(self._k[1])
+        a.state, a.state_bytes = self._state.data_ptr(), self._state.numel()
+        a.stream = torch.cuda.current_stream(self.device).cuda_stream
+        a.repetition_penalty, a.presence_penalty = float(self.params.repetition_penalty), float(self.params.presence_penalty)
+        if self._history is not None:
+            a.history, a.hist_len, a.hist_stride = self._history.data_ptr(), self._history.shape[1], _row_stride(self._history)
+        return a
+
+    def begin(self, history: Optional[torch.Tensor] = None) -> None:
+        """Forget every tile seen so far and note the step's token history (stream-ordered). A sampler built without a history
+        cannot be given one later (its state has no room for the ids)."""
+        if history is not None and self._pen:
+            if history.dim() != 2 or history.shape[0] != self.rows:
+                raise ValueError("history must be [rows, n]")
+            history = history.to(device=self.device, dtype=torch.int32)
+            self._history = history if history.stride(1) == 1 else history.contiguous()
+        elif history is not None and not (self.params.repetition_penalty == 1.0 and self.params.presence_penalty == 0.0) and history.shape[1] > 0:
+            raise ValueError("this TileSampler was built without a history")
         with torch.cuda.device(self.device):
-            _lib.check(L.lm_tile_begin(self._state.data_ptr(), self._state.numel(), self.rows, torch.cuda.current_stream(self.device).cuda_stream), "lm_tile_begin")
+            _lib.check(_lib.lib().lm_tile_begin(C.byref(self._args())), "lm_tile_begin")
 
     def consume(self, tile: torch.Tensor, col0: int) -> None:
         """Take ``tile`` [rows, cols] (bfloat16 or float32, CUDA, unit stride along columns) = the logits of columns
         ``col0 .. col0 + cols``. At most ``TILE_MAX_COLS`` columns per call; every column exactly once, in any order."""
         if tile.dim() != 2 or tile.shape[0] != self.rows or tile.stride(1) != 1 or not tile.is_cuda:
             raise ValueError("tile must be a CUDA tensor [rows, cols] with unit stride along columns")
-        a = _lib.TileArgs()
-        a.struct_size = C.sizeof(_lib.TileArgs)
+        a = self._args()
         a.dtype = _dtype_code(tile)
-        a.tile, a.rows, a.vocab, a.tile_stride = tile.data_ptr(), self.rows, self.vocab, _row_stride(tile)
+        a.tile, a.tile_stride = tile.data_ptr(), _row_stride(tile)
         a.col0, a.cols = int(col0), tile.shape[1]
-        a.temperature, a.temperature_s = self._t[0], float(self._t[1])
-        a.top_k, a.top_k_s = self._k[0], int(self._k[1])
-        a.state, a.state_bytes = self._state.data_ptr(), self._state.numel()
-        a.stream = torch.cuda.current_stream(self.device).cuda_stream
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().lm_tile_consume(C.byref(a)), "lm_tile_consume")
 
@@ -73,8 +92,9 @@ class TileSampler:
         ptr, s, t = _knob(p.min_p, rows, torch.float32, dev, "min_p"); a.min_p, a.min_p_s = ptr, float(s); keep.append(t)
         a.flags = _lib.FLAG_TOPP_IN_TOPK if p.topp_in_topk else 0
         a.draw = _lib.DRAW_GUMBEL if p.draw == "gumbel" else _lib.DRAW_INVERSE_CDF
-        a.repetition_penalty, a.presence_penalty = 1.0, 0.0
-        if p.draw == "inverse_cdf":
+        a.repetition_penalty, a.presence_penalty = float(p.repetition_penalty), float(p.presence_penalty)
+        stochastic = isinstance(p.temperature, torch.Tensor) or p.temperature > 0
+        if p.draw == "inverse_cdf" and stochastic:
             if uniforms is None:
                 raise ValueError("draw='inverse_cdf' needs uniforms [rows]")
             uniforms = uniforms.to(device=dev, dtype=torch.float32).contiguous()

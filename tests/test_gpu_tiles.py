@@ -96,25 +96,54 @@ def test_large_top_k_compacts_its_list_on_the_way():
     assert torch.equal(got.tokens, want.tokens) and torch.equal(got.tau, want.tau)
 
 
+@pytest.mark.parametrize("draw", ["inverse_cdf", "gumbel"])
+def test_penalised_and_greedy_rows_arrive_in_tiles_too(draw):
+    rows, vocab = 24, 151936
+    x, host = _logits(rows, vocab, 40)
+    g = np.random.default_rng(41)
+    hist = g.integers(0, vocab, (rows, 2048)).astype(np.int32)
+    hist[:, :64] = np.argsort(-oracle.bf16_to_f32(host), axis=1)[:, :64]            # the penalties reach the top of every row
+    t = g.uniform(0.5, 1.3, rows).astype(np.float32); t[::6] = 0.0                   # every sixth row greedy
+    k = g.choice([1, 20, 50, 1000], rows).astype(np.int32)
+    p = lm.SamplingParams(temperature=torch.from_numpy(t), top_k=torch.from_numpy(k), top_p=torch.from_numpy(g.uniform(0.8, 1.0, rows).astype(np.float32)),
+                          repetition_penalty=1.1, presence_penalty=0.5, seed=9, draw=draw)
+    u = torch.from_numpy(g.random(rows).astype(np.float32)).cuda()
+    h = torch.from_numpy(hist).cuda()
+    want = lm.sample(x, p, history=h, uniforms=u, step=2, return_tau=True)
+    ts = lm.TileSampler(rows, vocab, p, history=h)
+    for rep in range(2):                                                            # the second step reuses the state
+        _feed(ts, x, 256 if rep == 0 else 1024)
+        got = ts.finish(uniforms=u, step=2, return_tau=True)
+        st = got.status.cpu().numpy()
+        assert not np.any(st & _lib.STATUS_TILE_DECLINED), st
+        assert torch.equal(got.tokens, want.tokens) and torch.equal(got.tau, want.tau)
+        ts.begin(h)
+    tok, tau, _ = oracle.sample_batch(x.view(torch.int16).cpu().numpy().view(np.uint16), temperature=t, top_k=k, top_p=p.top_p.numpy(), history=hist,
+                                      repetition_penalty=1.1, presence_penalty=0.5, draw=draw, uniforms=u.cpu().numpy(), seed=9, step=2, n_threads=8)
+    assert want.tokens.cpu().tolist() == tok.tolist()
+
+
 def test_rows_the_tile_path_does_not_take_are_declined_not_guessed():
     rows, vocab = 5, 32768
     x, _ = _logits(rows, vocab, 30)
     x[1, 100] = float("nan")
     x[2] = -x[2].abs()                                          # no positive logit: the top-k boundary is not above zero
     k = torch.tensor([10, 10, 10, 0, 10], dtype=torch.int32)    # row 3: no top_k
-    t = torch.tensor([1.0, 1.0, 1.0, 1.0, 0.0])                 # row 4: greedy
+    t = torch.tensor([1.0, 1.0, 1.0, 1.0, 0.0])                 # row 4: greedy (taken: the running argmax)
     p = lm.SamplingParams(temperature=t, top_k=k, seed=1)
     ts = lm.TileSampler(rows, vocab, p)
     _feed(ts, x, 256)
     got = ts.finish()
     st, tok = got.status.cpu().numpy(), got.tokens.cpu().numpy()
     assert not (st[0] & _lib.STATUS_TILE_DECLINED) and tok[0] == int(lm.sample(x[:1], lm.SamplingParams(temperature=1.0, top_k=10, seed=1)).tokens[0])
-    assert all(st[r] & _lib.STATUS_TILE_DECLINED and tok[r] == -1 for r in (1, 2, 3, 4)), (st, tok)
+    assert all(st[r] & _lib.STATUS_TILE_DECLINED and tok[r] == -1 for r in (1, 2, 3)), (st, tok)
+    assert st[4] == 0 and tok[4] == int(x[4].float().argmax())
 
 
 def test_tile_arguments_are_checked():
     L = _lib.lib()
-    assert L.lm_tile_state_bytes(0) == 0 and L.lm_tile_state_bytes(4) >= 4 * 8192 * 8
+    assert L.lm_tile_state_bytes(0, 4096, 0) == 0 and L.lm_tile_state_bytes(4, 4096, 0) >= 4 * 8192 * 8
+    assert L.lm_tile_state_bytes(4, 4096, 1) == L.lm_tile_state_bytes(4, 4096, 0) + 4 * 4096 // 8
     p = lm.SamplingParams(temperature=1.0, top_k=5)
     ts = lm.TileSampler(2, 4096, p)
     x = torch.zeros(2, 4096, dtype=torch.bfloat16, device="cuda")
@@ -122,5 +151,7 @@ def test_tile_arguments_are_checked():
         ts.consume(x[:, :4096], 0)                              # wider than a tile may be
     with pytest.raises(_lib.LithosError):
         ts.consume(x[:, :256], 4000)                            # runs past the vocabulary
+    ts.begin(torch.zeros(2, 8, dtype=torch.int32))                  # no penalties in the knobs: a history changes nothing
+    bare = lm.TileSampler(2, 4096, lm.SamplingParams(temperature=1.0, top_k=5, repetition_penalty=1.2))
     with pytest.raises(ValueError):
-        lm.TileSampler(2, 4096, lm.SamplingParams(temperature=1.0, top_k=5, repetition_penalty=1.2))
+        bare.begin(torch.zeros(2, 8, dtype=torch.int32))            # built without a history: its state has no room for the ids
