@@ -445,9 +445,9 @@ __device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint
   const int n_seg = (n_chunks + kSegChunks - 1) / kSegChunks;
   uint32_t run = 0u, before_cnt = 0u, found_total = 0u;
   int found = -1, found_b0 = 0, buf = 0;
-  uint4 q[kDrawIters];                                                    // the chunks of the batch in hand (kept for the locate step)
   unsigned int* batch_cnt = reinterpret_cast<unsigned int*>(s.batch_sum);  // [2][kBatchSegs]
   for (int b0 = 0; b0 < n_seg && found < 0; b0 += kBatchSegs, buf ^= 1) {
+    uint4 q[kDrawIters];                                                  // the warp's chunks of this batch, all in flight at once
 #pragma unroll
     for (int it = 0; it < kDrawIters; it++) {
       const int k = b0 + it * kHW + warp, seg = forward ? k : n_seg - 1 - k, cc = seg * kSegChunks + lane;
@@ -480,8 +480,8 @@ __device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint
     run += __shfl_sync(kFull, incl, 31);
   }
   if (found < 0) return -1;                                               // cannot happen: the segments hold `members` logits
-  // ---- inside the segment: the (local)-th logit equal to the value, in index order. The warp that counted the segment still holds
-  // its chunks in registers: no second load.
+  // ---- inside the segment: the (local)-th logit equal to the value, in index order, by the warp that counted the segment (its
+  // chunk comes back from L2: keeping a batch of chunks alive across the loop would cost the kernel registers it does not have)
   {
     const int idx = found - found_b0;                                     // position of the segment in its batch: it * kHW + warp
     if (warp == idx % kHW) {
@@ -489,10 +489,7 @@ __device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint
       const uint32_t prefix = forward ? before_cnt : members - before_cnt - found_total;   // members before the segment
       const uint32_t local = want - prefix;
       const int cc = seg * kSegChunks + lane;
-      uint4 qf = q[0];
-#pragma unroll
-      for (int it = 1; it < kDrawIters; it++) if (idx / kHW == it) qf = q[it];
-      if (!n_raw && cc < n_chunks) qf = __ldg(p4 + cc);                   // (no raw code was compared: the batches loaded nothing)
+      const uint4 qf = cc < n_chunks ? __ldg(p4 + cc) : make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);
       const uint32_t bits = (pen != nullptr && cc < n_chunks) ? ((pen[cc >> 2] >> ((cc & 3) * 8)) & 0xFFu) : 0u;
       const uint32_t words[4] = {qf.x, qf.y, qf.z, qf.w};
       uint32_t hit = 0u;
