@@ -237,6 +237,11 @@ typedef struct lm_verify_args {
   uint32_t wait_limit;         /* polls before a wait between thread blocks gives up; 0 = the default (about 0.1 s) */
   uint32_t selftest;           /* LM_VERIFY_SELFTEST_WITHHOLD: block 0 withholds its row maxima, so every wait of the launch runs
                                   out and the error path can be exercised (with a small wait_limit) without hanging anything */
+  const float* target_vmax;    /* stochastic mode, optional: [n_draft + 1] (with a step_state: [t_max], indexed like the rows) the exact
+                                  maximum of every target row, as the sampler that produced `tau` knows it (the reference's verify
+                                  kernels take it from there too: KEPT_STATS, kernels/common/sample.metal:273-303). The launch then
+                                  spares the first of its exchanges between thread blocks. A value that is not the row's maximum
+                                  gives unspecified tokens (never a hang). NULL: the kernel finds the maxima itself. */
 } lm_verify_args;
 
 #define LM_RESIDUAL_INVERSE_CDF 0 /* final token by inverse CDF, in ascending index order, over max(p - q, 0) (over p on the bonus row) from u_final */

@@ -65,6 +65,7 @@ class VerifyArgs(C.Structure):
         ("commit", C.c_void_p),
         ("seed", C.c_uint64), ("step", C.c_uint32), ("residual_draw", C.c_int32),
         ("step_state", C.c_void_p), ("t_max", C.c_int32), ("gamma_max", C.c_int32), ("wait_limit", C.c_uint32), ("selftest", C.c_uint32),
+        ("target_vmax", C.c_void_p),
     ]
 
 

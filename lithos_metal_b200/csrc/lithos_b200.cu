@@ -616,6 +616,7 @@ int lm_verify(const lm_verify_args* a) {
   P.q_logits = static_cast<const uint16_t*>(a->draft_logits); P.q_logits_stride = a->draft_logits_stride;
   P.q_vmax = a->draft_vmax; P.q_mass = reinterpret_cast<const unsigned long long*>(a->draft_mass);
   P.tau = a->tau; P.u_accept = a->u_accept; P.u_final = a->u_final; P.seed = a->seed; P.step = a->step;
+  P.row_max = a->mode == LM_VERIFY_STOCHASTIC ? a->target_vmax : nullptr;
   P.out_accept = a->out_accept; P.out_final = a->out_final; P.out_tokens = a->out_tokens; P.out_p_draft = a->out_p_draft;
   P.ws = static_cast<VerifyWs*>(a->workspace);
   P.state = static_cast<uint32_t*>(const_cast<void*>(a->step_state)); P.t_max = a->t_max; P.g = a->gamma_max > 1 ? a->gamma_max : 1;

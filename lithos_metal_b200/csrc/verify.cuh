@@ -53,6 +53,7 @@ struct VerifyDev {
   const void* target; const int32_t* drafts; const float* q; int64_t q_stride; float temperature;
   const uint16_t* q_logits; int64_t q_logits_stride; const float* q_vmax; const unsigned long long* q_mass;   // q from the drafter's BF16 logits when q is null
   const float* tau; const float* u_accept; const float* u_final;
+  const float* row_max;                                  // stochastic mode, optional: the exact maxima of the step's rows (from the sampler): spares the first exchange
   uint64_t seed; uint32_t step;
   int32_t* out_accept; int32_t* out_final; int32_t* out_tokens; float* out_p_draft;
   VerifyWs* ws;
@@ -327,7 +328,10 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   const int n4 = (len + 3) / 4, n4p = (n4 + 31) & ~31;                      // groups of four elements per row of the slice
   const int split = max(1, kVerifyWarps / R);                              // without the shared-memory copy every row is shared by `split` warps
   const int n_red = cached ? n4p / 32 : split;                             // partial results per row in s_red
-  if (cached) {
+  const bool given_max = stochastic && P.row_max != nullptr;              // the sampler already knows the rows' maxima: nothing to find or exchange
+  if (given_max) {
+    if (tid < R) s_best[tid] = pack52(canon_zero(P.row_max[row0 + tid]), 0u);
+  } else if (cached) {
     // stochastic: the value alone (a 32-bit key); greedy: value and lowest index together (the 52-bit pack)
     for (int i0 = 0; i0 < R * n4p; i0 += kVerifyBlock) {
       const int r0 = (i0 + (tid & ~31)) / n4p;
@@ -406,7 +410,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     }
   } else {
     // ---- phase 1: every block learns the row maxima; fixed-point mass of every row's kept set; the drafts' own weights -------
-    consume_rows<false>(&ws->best[0][0], R, G, s_best, s_red, limit, &failed, vals);
+    if (!given_max) consume_rows<false>(&ws->best[0][0], R, G, s_best, s_red, limit, &failed, vals);
     if (cached) {
       // the same walk as for the maxima: four elements per load, two packed weight evaluations, one warp sum per 128 elements
       for (int i0 = 0; i0 < R * n4p; i0 += kVerifyBlock) {

@@ -149,3 +149,20 @@ def test_verify_commits_the_round_like_accept_scan(mode):
     lm.accept_scan(layout, st_a, out_a[2], ring)
     lm.verify(*args, commit=dict(layout=layout, state=st_b, ring=ring))
     assert torch.equal(st_a, st_b)
+
+
+def test_row_maxima_from_the_sampler_spare_an_exchange_and_change_nothing():
+    """The reference's verify kernels take each row's maximum from the sampler (KEPT_STATS, sample.metal:273-303). Given them, the
+    launch skips its first exchange; accept length, final token and p(draft) must be the ones it finds by itself."""
+    target, drafts, q, ua, uf = inputs.config2(vocab=151936, seed=5)
+    x = torch.from_numpy(target.view(np.int16)).cuda().view(torch.bfloat16)
+    vmax = x.float().amax(dim=1)
+    for d, u in ((drafts, ua), (drafts, np.zeros(7, np.float32)), (drafts, np.full(7, 0.999, np.float32))):
+        args = (x, torch.from_numpy(d).cuda(), torch.from_numpy(q).cuda(), torch.from_numpy(u).cuda(), torch.tensor([uf]), "stochastic")
+        a = lm.verify(*args, return_p_draft=True)
+        b = lm.verify(*args, return_p_draft=True, target_vmax=vmax)
+        assert [t.cpu().tolist() for t in a] == [t.cpu().tolist() for t in b]
+    z = oracle.bf16_to_f32(target)
+    acc, fin, _ = oracle.verify_stochastic(z, drafts, q, ua, uf)
+    out = lm.verify(x, torch.from_numpy(drafts).cuda(), torch.from_numpy(q).cuda(), torch.from_numpy(ua).cuda(), torch.tensor([uf]), "stochastic", target_vmax=vmax)
+    assert (int(out[0]), int(out[1])) == (acc, fin)
