@@ -128,6 +128,9 @@ typedef struct lm_sample_args {
    * untouched), and nothing is written once the state is done. A captured CUDA graph then draws fresh noise on every replay. */
   const void* step_state;
   int32_t t_max, gamma_max;
+  float* out_vmax;             /* [rows] each row's maximum logit (after penalties), or NULL: what the verify step takes as
+                                  lm_verify_args.target_vmax when the same rows were sampled without penalties (the reference's
+                                  KEPT_STATS carry it from its sampler to its verify kernels) */
 } lm_sample_args;
 
 LM_API int lm_sample(const lm_sample_args* args);

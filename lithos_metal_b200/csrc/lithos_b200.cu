@@ -137,7 +137,7 @@ static SampleDev sample_dev(const lm_sample_args* a) {
   P.rho = a->repetition_penalty; P.pi = a->presence_penalty;
   P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
   P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_stats = a->out_stats; P.out_probs = a->out_probs; P.probs_stride = a->probs_stride;
-  P.out_status = a->out_status;
+  P.out_status = a->out_status; P.out_vmax = a->out_vmax;
   P.state = static_cast<const uint32_t*>(a->step_state); P.t_max = a->t_max; P.g = a->gamma_max > 1 ? a->gamma_max : 1;
   return P;
 }
@@ -315,7 +315,7 @@ int lm_sample(const lm_sample_args* a) {
       M.temperature = nullptr; M.temperature_s = a->temperature_s; M.top_k = nullptr; M.top_k_s = a->top_k_s;
       M.top_p = a->top_p; M.top_p_s = a->top_p_s; M.min_p = a->min_p; M.min_p_s = a->min_p_s;
       M.flags = a->flags; M.draw = a->draw; M.uniforms = a->uniforms; M.seed = a->seed; M.step = a->step; M.row_offset = a->row_offset;
-      M.out_tokens = a->out_tokens; M.out_tau = a->out_tau; M.out_status = a->out_status;
+      M.out_tokens = a->out_tokens; M.out_tau = a->out_tau; M.out_status = a->out_status; M.out_vmax = a->out_vmax;
       M.hand_on = 1; M.path_status = LM_STATUS_SLICED_PATH;
       // the merge is launched with programmatic stream serialization: its blocks are resident and waiting when the slices complete
       cudaLaunchAttribute attr[1];
@@ -522,7 +522,7 @@ int lm_vocab_merge(const lm_vocab_args* a) {
   P.temperature = a->temperature; P.temperature_s = a->temperature_s; P.top_k = a->top_k; P.top_k_s = a->top_k_s;
   P.top_p = a->top_p; P.top_p_s = a->top_p_s; P.min_p = a->min_p; P.min_p_s = a->min_p_s;
   P.flags = a->flags; P.draw = a->draw; P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
-  P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_status = a->out_status;
+  P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_status = a->out_status; P.out_vmax = nullptr;
   P.hand_on = 0; P.path_status = 0u;
   int sms = 0;
   const int rc = sm_count(&sms);

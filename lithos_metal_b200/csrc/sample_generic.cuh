@@ -22,6 +22,7 @@ struct SampleDev {              // lm_sample_args without the host-only fields
   const int32_t* history; int hist_len; int64_t hist_stride; float rho, pi;
   const float* uniforms; uint64_t seed; uint32_t step; int64_t row_offset;
   int32_t* out_tokens; float* out_tau; float* out_stats; float* out_probs; int64_t probs_stride; uint32_t* out_status;
+  float* out_vmax;                                      // optional: the row's maximum (penalised) logit, for the verify step
   const uint32_t* state; int t_max, g;                  // optional StepState: seed, step and the active rows come from it
 };
 
@@ -156,6 +157,7 @@ __device__ void sample_row_generic(const SampleDev& P, int row, GenericSmem& s, 
       P.out_tokens[row] = -1;
       if (P.out_tau) P.out_tau[row] = -INFINITY;
       if (P.out_stats) { P.out_stats[2 * row] = 0.0f; P.out_stats[2 * row + 1] = 0.0f; }
+      if (P.out_vmax) P.out_vmax[row] = -INFINITY;
       if (P.out_status) P.out_status[row] = status | (V > 0 ? kStatusBadParam : 0u);
     }
     return;
@@ -202,6 +204,7 @@ __device__ void sample_row_generic(const SampleDev& P, int row, GenericSmem& s, 
       P.out_tokens[row] = arg;
       if (P.out_tau) P.out_tau[row] = -INFINITY;
       if (P.out_stats) { P.out_stats[2 * row] = vmax; P.out_stats[2 * row + 1] = 1.0f; }
+      if (P.out_vmax) P.out_vmax[row] = vmax;
       if (P.out_status) P.out_status[row] = status;
     }
     return;
@@ -318,6 +321,7 @@ __device__ void sample_row_generic(const SampleDev& P, int row, GenericSmem& s, 
     P.out_tokens[row] = token;
     if (P.out_tau) P.out_tau[row] = tau;
     if (P.out_stats) { P.out_stats[2 * row] = vmax; P.out_stats[2 * row + 1] = static_cast<float>(kept_mass); }
+    if (P.out_vmax) P.out_vmax[row] = vmax;
     if (P.out_status) P.out_status[row] = status;
   }
 }

@@ -676,6 +676,7 @@ __device__ void sample_row_hist(const SampleDev& P, int row, int next, HistSmem&
       P.out_tokens[row] = static_cast<int>(best_index(best));
       if (P.out_tau) P.out_tau[row] = -INFINITY;
       if (P.out_status) P.out_status[row] = (best_value(best) != best_value(best)) ? LM_STATUS_NAN : 0u;
+      if (P.out_vmax) P.out_vmax[row] = best_value(best);
     }
     return;
   }
@@ -896,6 +897,7 @@ __device__ void sample_row_hist(const SampleDev& P, int row, int next, HistSmem&
     P.out_tokens[row] = token;
     if (P.out_tau) P.out_tau[row] = tau;
     if (P.out_status) P.out_status[row] = status;
+    if (P.out_vmax) P.out_vmax[row] = vmax;
   }
 }
 

@@ -260,6 +260,7 @@ __global__ void __launch_bounds__(kTB, kTopkPerSM) tile_finish_kernel(SampleDev 
         P.out_tokens[row] = static_cast<int>(best_index(st->best));
         if (P.out_tau) P.out_tau[row] = -INFINITY;
         if (P.out_status) P.out_status[row] = 0u;
+        if (P.out_vmax) P.out_vmax[row] = best_value(st->best);
       }
       __syncthreads();
       continue;
@@ -298,6 +299,7 @@ __global__ void __launch_bounds__(kTB, kTopkPerSM) tile_finish_kernel(SampleDev 
       P.out_tokens[row] = -1;
       if (P.out_tau) P.out_tau[row] = -INFINITY;
       if (P.out_status) P.out_status[row] = LM_STATUS_TILE_DECLINED;
+      if (P.out_vmax) P.out_vmax[row] = (st->flags & 4u) ? static_cast<float>(st->m) : -INFINITY;
     }
     __syncthreads();
   }

@@ -612,6 +612,7 @@ __device__ bool topk_finish(const SampleDev& P, int row, TopkSmem& c, uint32_t c
     P.out_tokens[row] = token;
     if (P.out_tau) P.out_tau[row] = tau;
     if (P.out_status) P.out_status[row] = status;
+    if (P.out_vmax) P.out_vmax[row] = vmax;
   }
   __syncthreads();
   return true;

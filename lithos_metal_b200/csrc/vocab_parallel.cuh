@@ -106,7 +106,7 @@ struct VpMergeDev {
   const float* temperature; float temperature_s; const int32_t* top_k; int32_t top_k_s;
   const float* top_p; float top_p_s; const float* min_p; float min_p_s;
   uint32_t flags; int draw; const float* uniforms; uint64_t seed; uint32_t step; int64_t row_offset;
-  int32_t* out_tokens; float* out_tau; uint32_t* out_status;
+  int32_t* out_tokens; float* out_tau; uint32_t* out_status; float* out_vmax;
   uint32_t path_status;              // ORed into every row's status (0 in the vocab-parallel mode)
   int hand_on;                       // single-GPU use (sample_sliced.cuh): a row whose records overflowed is left to the caller
 };
@@ -286,6 +286,7 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
     P.out_tokens[row] = s.token;
     if (P.out_tau) P.out_tau[row] = tau;
     if (P.out_status) P.out_status[row] = status;
+    if (P.out_vmax) P.out_vmax[row] = vmax;
   }
   __syncthreads();
   return true;

@@ -44,6 +44,7 @@ class SampleOutput:
     stats: Optional[torch.Tensor] = None   # float32 [rows, 2]: (max logit, kept softmax mass)
     probs: Optional[torch.Tensor] = None   # float32 [rows, vocab]
     status: Optional[torch.Tensor] = None  # int32 [rows] status bits
+    vmax: Optional[torch.Tensor] = None    # float32 [rows]: the row's maximum logit (after penalties)
 
 
 _workspaces: Dict[Tuple[int, str, int], torch.Tensor] = {}
@@ -109,7 +110,8 @@ def _knob(x: Knob, rows: int, dtype: torch.dtype, device: torch.device, name: st
 
 def sample(logits: torch.Tensor, params: Optional[SamplingParams] = None, *, history: Optional[torch.Tensor] = None,
            uniforms: Optional[torch.Tensor] = None, step: int = 0, row_offset: int = 0, return_tau: bool = False, return_stats: bool = False,
-           return_probs: bool = False, return_status: bool = False, out: Optional[torch.Tensor] = None, step_state=None, **knobs: Any) -> SampleOutput:
+           return_probs: bool = False, return_status: bool = False, out: Optional[torch.Tensor] = None, step_state=None, return_vmax: bool = False,
+           **knobs: Any) -> SampleOutput:
     """One sampling step over every row of ``logits`` [rows, vocab] (bfloat16 or float32, CUDA).
 
     ``params`` (or the same fields as keyword arguments) hold scalar knobs or per-row tensors. ``history`` [rows, n]
@@ -175,6 +177,8 @@ def sample(logits: torch.Tensor, params: Optional[SamplingParams] = None, *, his
         res.probs = torch.empty(rows, vocab, dtype=torch.float32, device=dev); a.out_probs, a.probs_stride = res.probs.data_ptr(), vocab
     if return_status:
         res.status = torch.empty(rows, dtype=torch.int32, device=dev); a.out_status = res.status.data_ptr()
+    if return_vmax:
+        res.vmax = torch.empty(rows, dtype=torch.float32, device=dev); a.out_vmax = res.vmax.data_ptr()
     L = _lib.lib()
     ws = _workspace(dev, L.lm_workspace_bytes(rows, vocab))
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()

@@ -78,7 +78,7 @@ class TileSampler:
             _lib.check(_lib.lib().lm_tile_consume(C.byref(a)), "lm_tile_consume")
 
     def finish(self, *, uniforms: Optional[torch.Tensor] = None, step: int = 0, row_offset: int = 0, return_tau: bool = False,
-               return_status: bool = True, out: Optional[torch.Tensor] = None, step_state=None) -> SampleOutput:
+               return_status: bool = True, out: Optional[torch.Tensor] = None, step_state=None, return_vmax: bool = False) -> SampleOutput:
         """The tokens of the rows, as :func:`sample` would return them for the assembled logits; -1 with
         ``STATUS_TILE_DECLINED`` for rows to be sampled from materialised logits."""
         p, rows, dev = self.params, self.rows, self.device
@@ -114,6 +114,8 @@ class TileSampler:
             res.tau = torch.empty(rows, dtype=torch.float32, device=dev); a.out_tau = res.tau.data_ptr()
         if return_status:
             res.status = torch.empty(rows, dtype=torch.int32, device=dev); a.out_status = res.status.data_ptr()
+        if return_vmax:
+            res.vmax = torch.empty(rows, dtype=torch.float32, device=dev); a.out_vmax = res.vmax.data_ptr()
         a.stream = torch.cuda.current_stream(dev).cuda_stream
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().lm_tile_finish(C.byref(a), self._state.data_ptr(), self._state.numel()), "lm_tile_finish")

@@ -465,3 +465,32 @@ def test_two_streams_sample_at_once_with_their_own_workspaces():
     torch.cuda.synchronize()
     for i in range(2):
         assert all(torch.equal(t, alone[i]) for t in got[i])
+
+
+def test_row_maxima_come_out_of_every_kernel_and_feed_the_verify_step():
+    """The reference's sampler leaves each row's maximum for its verify kernels (KEPT_STATS). out_vmax is that: the maximum of the
+    (penalised) row, whichever kernel took the row."""
+    rows, vocab = 40, 151936
+    rng = np.random.default_rng(17)
+    codes = oracle.f32_to_bf16((rng.standard_normal((rows, vocab)) * 2).astype(np.float32))
+    hist = rng.integers(0, vocab, (rows, 512)).astype(np.int32)
+    hist[:, 0] = oracle.bf16_to_f32(codes).argmax(-1)                                 # the raw maximum is penalised in every row
+    want = np.stack([oracle.apply_penalties(oracle.bf16_to_f32(codes[r]), hist[r], 1.2, 0.3).max() for r in range(rows)])
+    x = bf16_tensor(codes)
+    t = torch.from_numpy(np.where(np.arange(rows) % 5 == 0, 0.0, 0.9).astype(np.float32))   # greedy rows among them
+    k = torch.from_numpy(np.where(np.arange(rows) % 2 == 0, 0, 30).astype(np.int32))        # histogram-kernel and candidate-kernel rows
+    p = lm.SamplingParams(temperature=t, top_k=k, top_p=0.9, repetition_penalty=1.2, presence_penalty=0.3, seed=3)
+    for extra in ({}, {"return_stats": True}):                                             # the streaming kernels; the generic kernel
+        r = lm.sample(x, p, history=torch.from_numpy(hist).cuda(), return_vmax=True, **extra)
+        np.testing.assert_array_equal(r.vmax.cpu().numpy(), want.astype(np.float32))
+    few = lm.sample(x[:3], lm.SamplingParams(temperature=0.9, top_k=30, top_p=0.9, seed=3), return_vmax=True, return_status=True)   # the sliced path
+    assert np.all(few.status.cpu().numpy() & 256)                                         # (the sliced path took them)
+    np.testing.assert_array_equal(few.vmax.cpu().numpy(), oracle.bf16_to_f32(codes[:3]).max(-1))
+    # and on to the verify step: thresholds and maxima of the 8 rows from one sampler call
+    target, drafts, q, ua, uf = inputs.config2(vocab=vocab, seed=23)
+    xt = bf16_tensor(target)
+    s = lm.sample(xt, lm.SamplingParams(temperature=0.8, top_k=torch.full((8,), 50, dtype=torch.int32), top_p=0.95, seed=1), return_tau=True, return_vmax=True)
+    args = (xt, torch.from_numpy(drafts).cuda(), torch.from_numpy(q).cuda(), torch.from_numpy(ua).cuda(), torch.tensor([uf]), "stochastic")
+    a = lm.verify(*args, temperature=0.8, tau=s.tau)
+    b = lm.verify(*args, temperature=0.8, tau=s.tau, target_vmax=s.vmax)
+    assert [v.cpu().tolist() for v in a] == [v.cpu().tolist() for v in b]
