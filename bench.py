@@ -55,7 +55,7 @@ def ncu_traffic():
 
 
 # (top-k kernel read + write) + (histogram kernel read + write) over the 4096 rows of one call
-TRAFFIC = {"dram_bytes_per_row": (1037142000 + 4230400 + 405580000 + 58583808) / 4096, "captured_at": "c50792a"}
+TRAFFIC = {"dram_bytes_per_row": (1038392000 + 5363456 + 398393000 + 35523328) / 4096, "captured_at": "7c195a4"}
 
 
 def launches_per_call(lm, rows: int) -> int:
