@@ -522,7 +522,8 @@ def bench_verify(torch, lm, dev):
     # the two ends of the stochastic step: every draft accepted (no residual: two exchanges between the blocks), and the first
     # draft rejected (the residual of row 0 is summed and drawn from: three exchanges)
     u_zero, u_one = torch.zeros(7, device=dev), torch.full((7,), 0.999, device=dev)
-    vmax = target.float().amax(dim=1)
+    kept = lm.sample(target, lm.SamplingParams(temperature=1.0, top_k=torch.zeros(8, dtype=torch.int32), draw="inverse_cdf"), uniforms=torch.full((8,), 0.5), return_vmax=True)
+    vmax, mass = kept.vmax, kept.mass                                  # what the sampler leaves for the verify step (no thresholds here)
     worst = drafts.clone()
     worst[0] = (q[0] / torch.softmax(target[0].float(), dim=-1)).argmax().to(torch.int32)       # the token the drafter overrates most
     calls = {"stochastic": lambda: lm.verify(target, drafts, q, ua, uf, "stochastic"),
@@ -530,6 +531,9 @@ def bench_verify(torch, lm, dev):
              "stochastic_first_rejected": lambda: lm.verify(target, worst, q, u_one, uf, "stochastic"),
              # the row maxima handed over by the sampler, as the reference's verify kernels get them (KEPT_STATS): one exchange fewer
              "stochastic_given_row_max": lambda: lm.verify(target, drafts, q, ua, uf, "stochastic", target_vmax=vmax),
+             # ... and the rows' masses too (both halves of KEPT_STATS: what lm_sample leaves in out_vmax / out_mass): one exchange in all
+             "stochastic_given_row_stats": lambda: lm.verify(target, drafts, q, ua, uf, "stochastic", target_vmax=vmax, target_mass=mass),
+             "stochastic_given_row_stats_first_rejected": lambda: lm.verify(target, worst, q, u_one, uf, "stochastic", target_vmax=vmax, target_mass=mass),
              "stochastic_q_logits": lambda: lm.verify(target, stats.tokens, None, ua, uf, "stochastic", draft_logits=drafter, draft_stats=stats),
              "greedy": lambda: lm.verify(target, drafts, mode="greedy"),
              "draft_q_one_position": lambda: lm.draft_q(drafter[3:4], temperature=1.0, seed=SEED, step=0, first_position=3)}

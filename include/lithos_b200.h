@@ -131,6 +131,8 @@ typedef struct lm_sample_args {
   float* out_vmax;             /* [rows] each row's maximum logit (after penalties), or NULL: what the verify step takes as
                                   lm_verify_args.target_vmax when the same rows were sampled without penalties (the reference's
                                   KEPT_STATS carry it from its sampler to its verify kernels) */
+  uint64_t* out_mass;          /* [rows] the kept set's mass in the library's fixed point, sum over {z >= tau} of
+                                  floor(2^40 * 2^((z - vmax) * log2(e) / T)) (0 for a greedy row), or NULL: lm_verify_args.target_mass */
 } lm_sample_args;
 
 LM_API int lm_sample(const lm_sample_args* args);
@@ -245,6 +247,10 @@ typedef struct lm_verify_args {
                                   kernels take it from there too: KEPT_STATS, kernels/common/sample.metal:273-303). The launch then
                                   spares the first of its exchanges between thread blocks. A value that is not the row's maximum
                                   gives unspecified tokens (never a hang). NULL: the kernel finds the maxima itself. */
+  const uint64_t* target_mass; /* with target_vmax, optional: per row the fixed-point mass of its kept set {z >= tau} at `temperature`, as
+                                  lm_sample_args.out_mass gives it for the same rows, thresholds and temperature (the other half of
+                                  the reference's KEPT_STATS). Every block then runs the accept test by itself and the launch has a
+                                  single exchange left (the draw). Ignored without target_vmax. */
 } lm_verify_args;
 
 #define LM_RESIDUAL_INVERSE_CDF 0 /* final token by inverse CDF, in ascending index order, over max(p - q, 0) (over p on the bonus row) from u_final */

@@ -40,7 +40,7 @@ class SampleArgs(C.Structure):
         ("out_tokens", C.c_void_p), ("out_tau", C.c_void_p), ("out_stats", C.c_void_p), ("out_probs", C.c_void_p), ("probs_stride", C.c_int64),
         ("out_status", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
-        ("step_state", C.c_void_p), ("t_max", C.c_int32), ("gamma_max", C.c_int32), ("out_vmax", C.c_void_p),
+        ("step_state", C.c_void_p), ("t_max", C.c_int32), ("gamma_max", C.c_int32), ("out_vmax", C.c_void_p), ("out_mass", C.c_void_p),
     ]
 
 
@@ -65,7 +65,7 @@ class VerifyArgs(C.Structure):
         ("commit", C.c_void_p),
         ("seed", C.c_uint64), ("step", C.c_uint32), ("residual_draw", C.c_int32),
         ("step_state", C.c_void_p), ("t_max", C.c_int32), ("gamma_max", C.c_int32), ("wait_limit", C.c_uint32), ("selftest", C.c_uint32),
-        ("target_vmax", C.c_void_p),
+        ("target_vmax", C.c_void_p), ("target_mass", C.c_void_p),
     ]
 
 

@@ -63,15 +63,14 @@ __device__ __forceinline__ uint32_t kept_chunk(const RowView& rv, int c, float t
 // floor((target - weight above v) / w(v))-th smallest index among the logits equal to v (one sweep that counts them per sweep of
 // the block, one look at the sweep that holds it). Every thread of the block calls; every thread gets the token (-1 if the kept
 // set has no weight).
-__device__ int draw_inverse_cdf(const RowView& rv, float tau, float vmax, float temperature, float u, DrawSmem& d) {
+// The kept set's total fixed-point weight. Every thread of the block calls; every thread gets the total.
+__device__ uint64_t kept_weight_total(const RowView& rv, float tau, float vmax, float temperature, DrawSmem& d) {
   const int tid = threadIdx.x;
   const int n_chunks = (rv.vocab + kChunk - 1) / kChunk;
   const int n_sweeps = (n_chunks + kBlock - 1) / kBlock;
   const float c2 = exp2_scale(temperature);
   const uint32_t tc = ceil_bf16_code(tau);
   const uint32_t tau2 = tc | (tc << 16);
-  if (tid == 0) d.token = -1;
-  // ---- the kept set's total weight
   uint64_t mine = 0ull;
   for (int it = 0; it < n_sweeps; it++) {
     float z[kChunk];
@@ -81,7 +80,19 @@ __device__ int draw_inverse_cdf(const RowView& rv, float tau, float vmax, float 
       for (int e = 0; e < kChunk; e++) if ((mask >> e) & 1u) mine += weight_q40(z[e], vmax, c2);
     }
   }
-  const uint64_t total = block_sum_u64(mine, d.scratch);
+  return block_sum_u64(mine, d.scratch);
+}
+
+__device__ int draw_inverse_cdf(const RowView& rv, float tau, float vmax, float temperature, float u, DrawSmem& d, uint64_t* out_total = nullptr) {
+  const int tid = threadIdx.x;
+  const int n_chunks = (rv.vocab + kChunk - 1) / kChunk;
+  const int n_sweeps = (n_chunks + kBlock - 1) / kBlock;
+  const float c2 = exp2_scale(temperature);
+  const uint32_t tc = ceil_bf16_code(tau);
+  const uint32_t tau2 = tc | (tc << 16);
+  if (tid == 0) d.token = -1;
+  const uint64_t total = kept_weight_total(rv, tau, vmax, temperature, d);
+  if (out_total) *out_total = total;
   if (total == 0ull) { __syncthreads(); return -1; }
   const uint64_t target = cdf_target(u, total);
   // ---- the value: digits of its key from the top

@@ -137,7 +137,7 @@ static SampleDev sample_dev(const lm_sample_args* a) {
   P.rho = a->repetition_penalty; P.pi = a->presence_penalty;
   P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
   P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_stats = a->out_stats; P.out_probs = a->out_probs; P.probs_stride = a->probs_stride;
-  P.out_status = a->out_status; P.out_vmax = a->out_vmax;
+  P.out_status = a->out_status; P.out_vmax = a->out_vmax; P.out_mass = reinterpret_cast<unsigned long long*>(a->out_mass);
   P.state = static_cast<const uint32_t*>(a->step_state); P.t_max = a->t_max; P.g = a->gamma_max > 1 ? a->gamma_max : 1;
   return P;
 }
@@ -315,7 +315,7 @@ int lm_sample(const lm_sample_args* a) {
       M.temperature = nullptr; M.temperature_s = a->temperature_s; M.top_k = nullptr; M.top_k_s = a->top_k_s;
       M.top_p = a->top_p; M.top_p_s = a->top_p_s; M.min_p = a->min_p; M.min_p_s = a->min_p_s;
       M.flags = a->flags; M.draw = a->draw; M.uniforms = a->uniforms; M.seed = a->seed; M.step = a->step; M.row_offset = a->row_offset;
-      M.out_tokens = a->out_tokens; M.out_tau = a->out_tau; M.out_status = a->out_status; M.out_vmax = a->out_vmax;
+      M.out_tokens = a->out_tokens; M.out_tau = a->out_tau; M.out_status = a->out_status; M.out_vmax = a->out_vmax; M.out_mass = reinterpret_cast<unsigned long long*>(a->out_mass);
       M.hand_on = 1; M.path_status = LM_STATUS_SLICED_PATH;
       // the merge is launched with programmatic stream serialization: its blocks are resident and waiting when the slices complete
       cudaLaunchAttribute attr[1];
@@ -522,7 +522,7 @@ int lm_vocab_merge(const lm_vocab_args* a) {
   P.temperature = a->temperature; P.temperature_s = a->temperature_s; P.top_k = a->top_k; P.top_k_s = a->top_k_s;
   P.top_p = a->top_p; P.top_p_s = a->top_p_s; P.min_p = a->min_p; P.min_p_s = a->min_p_s;
   P.flags = a->flags; P.draw = a->draw; P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
-  P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_status = a->out_status; P.out_vmax = nullptr;
+  P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_status = a->out_status; P.out_vmax = nullptr; P.out_mass = nullptr;
   P.hand_on = 0; P.path_status = 0u;
   int sms = 0;
   const int rc = sm_count(&sms);
@@ -617,6 +617,7 @@ int lm_verify(const lm_verify_args* a) {
   P.q_vmax = a->draft_vmax; P.q_mass = reinterpret_cast<const unsigned long long*>(a->draft_mass);
   P.tau = a->tau; P.u_accept = a->u_accept; P.u_final = a->u_final; P.seed = a->seed; P.step = a->step;
   P.row_max = a->mode == LM_VERIFY_STOCHASTIC ? a->target_vmax : nullptr;
+  P.row_mass = P.row_max ? reinterpret_cast<const unsigned long long*>(a->target_mass) : nullptr;
   P.out_accept = a->out_accept; P.out_final = a->out_final; P.out_tokens = a->out_tokens; P.out_p_draft = a->out_p_draft;
   P.ws = static_cast<VerifyWs*>(a->workspace);
   P.state = static_cast<uint32_t*>(const_cast<void*>(a->step_state)); P.t_max = a->t_max; P.g = a->gamma_max > 1 ? a->gamma_max : 1;

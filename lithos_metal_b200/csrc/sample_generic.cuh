@@ -23,6 +23,7 @@ struct SampleDev {              // lm_sample_args without the host-only fields
   const float* uniforms; uint64_t seed; uint32_t step; int64_t row_offset;
   int32_t* out_tokens; float* out_tau; float* out_stats; float* out_probs; int64_t probs_stride; uint32_t* out_status;
   float* out_vmax;                                      // optional: the row's maximum (penalised) logit, for the verify step
+  unsigned long long* out_mass;                         // optional: the kept set's fixed-point mass, for the verify step
   const uint32_t* state; int t_max, g;                  // optional StepState: seed, step and the active rows come from it
 };
 
@@ -158,6 +159,7 @@ __device__ void sample_row_generic(const SampleDev& P, int row, GenericSmem& s, 
       if (P.out_tau) P.out_tau[row] = -INFINITY;
       if (P.out_stats) { P.out_stats[2 * row] = 0.0f; P.out_stats[2 * row + 1] = 0.0f; }
       if (P.out_vmax) P.out_vmax[row] = -INFINITY;
+      if (P.out_mass) P.out_mass[row] = 0ull;
       if (P.out_status) P.out_status[row] = status | (V > 0 ? kStatusBadParam : 0u);
     }
     return;
@@ -205,6 +207,7 @@ __device__ void sample_row_generic(const SampleDev& P, int row, GenericSmem& s, 
       if (P.out_tau) P.out_tau[row] = -INFINITY;
       if (P.out_stats) { P.out_stats[2 * row] = vmax; P.out_stats[2 * row + 1] = 1.0f; }
       if (P.out_vmax) P.out_vmax[row] = vmax;
+      if (P.out_mass) P.out_mass[row] = 0ull;                              // (greedy: no distribution)
       if (P.out_status) P.out_status[row] = status;
     }
     return;
@@ -300,12 +303,14 @@ __device__ void sample_row_generic(const SampleDev& P, int row, GenericSmem& s, 
 
   // ---- the draw --------------------------------------------------------------------------------------------------
   int token;
+  uint64_t kept_weight = 0ull;
   if (P.draw == LM_DRAW_INVERSE_CDF) {
-    token = draw_inverse_cdf(rv, tau, vmax, T, P.uniforms ? P.uniforms[row] : 0.0f, s.draw);
+    token = draw_inverse_cdf(rv, tau, vmax, T, P.uniforms ? P.uniforms[row] : 0.0f, s.draw, &kept_weight);
   } else {
     bool tie = false;
     token = draw_gumbel(rv, tau, T, P.seed, P.step, static_cast<uint32_t>(P.row_offset + row), s.draw, &tie);
     if (tie) status |= LM_STATUS_NEAR_TIE;
+    if (P.out_mass) kept_weight = kept_weight_total(rv, tau, vmax, T, s.draw);
   }
 
   // ---- outputs ----------------------------------------------------------------------------------------------------
@@ -322,6 +327,7 @@ __device__ void sample_row_generic(const SampleDev& P, int row, GenericSmem& s, 
     if (P.out_tau) P.out_tau[row] = tau;
     if (P.out_stats) { P.out_stats[2 * row] = vmax; P.out_stats[2 * row + 1] = static_cast<float>(kept_mass); }
     if (P.out_vmax) P.out_vmax[row] = vmax;
+    if (P.out_mass) P.out_mass[row] = kept_weight;
     if (P.out_status) P.out_status[row] = status;
   }
 }

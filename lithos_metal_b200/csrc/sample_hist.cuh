@@ -326,7 +326,8 @@ __device__ __forceinline__ uint32_t equal_mask8(const uint4 q, uint32_t code2, b
 // COUNT them -- segments of 256 logits from whichever end is nearer, a batch of kBatchSegs per barrier, packed 16-bit compares
 // against v's raw code, the penalised logits equal to v as per-segment corrections (s.seg_fix) -- and the warp that holds the
 // segment locates the token. Every thread calls; every thread gets the token (-1: the kept set has no weight).
-__device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint32_t* pen, const uint16_t* rowp, int n_chunks, float tau, float vmax, float T, float u) {
+__device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint32_t* pen, const uint16_t* rowp, int n_chunks, float tau, float vmax, float T, float u,
+                                     uint64_t* out_total, bool total_only = false) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float c2 = exp2_scale(T);
   const uint32_t n_side = s.n_side, n_b = s.n_b;
@@ -365,7 +366,8 @@ __device__ int hist_draw_inverse_cdf(const SampleDev& P, HistSmem& s, const uint
   const uint64_t gw = tid < kGroupsH ? g_w[tid] : 0ull;
   uint64_t total = 0ull;
   const uint64_t g_before = block_exclusive_scan_u64(gw, s.scratch, &total);
-  if (total == 0ull) { __syncthreads(); return -1; }
+  *out_total = total;
+  if (total == 0ull || total_only) { __syncthreads(); return -1; }        // (total_only: the Gumbel draw picks the token; only the mass is wanted)
   const uint64_t target = cdf_target(u, total);
   if (gw && g_before <= target && target < g_before + gw) { s.sel_g = tid; *reinterpret_cast<unsigned long long*>(&s.base_m) = g_before; }
   __syncthreads();
@@ -677,6 +679,7 @@ __device__ void sample_row_hist(const SampleDev& P, int row, int next, HistSmem&
       if (P.out_tau) P.out_tau[row] = -INFINITY;
       if (P.out_status) P.out_status[row] = (best_value(best) != best_value(best)) ? LM_STATUS_NAN : 0u;
       if (P.out_vmax) P.out_vmax[row] = best_value(best);
+      if (P.out_mass) P.out_mass[row] = 0ull;
     }
     return;
   }
@@ -885,12 +888,14 @@ __device__ void sample_row_hist(const SampleDev& P, int row, int next, HistSmem&
 
   // ---- phase 6: the draw over the kept set (the row is in L2) ------------------------------------------------------------------
   int token;
+  uint64_t kept_weight = 0ull;
   if (P.draw == LM_DRAW_INVERSE_CDF) {
-    token = hist_draw_inverse_cdf(P, s, penmap, rowp, n_chunks, tau, vmax, T, P.uniforms ? P.uniforms[row] : 0.0f);
+    token = hist_draw_inverse_cdf(P, s, penmap, rowp, n_chunks, tau, vmax, T, P.uniforms ? P.uniforms[row] : 0.0f, &kept_weight);
   } else {
     bool tie = false;
     token = hist_draw_gumbel(P, s, penmap, rowp, n_chunks, tau, T, static_cast<uint32_t>(P.row_offset + row), &tie);
     if (tie) status |= LM_STATUS_NEAR_TIE;
+    if (P.out_mass) { __syncthreads(); hist_draw_inverse_cdf(P, s, penmap, rowp, n_chunks, tau, vmax, T, 0.0f, &kept_weight, true); }   // the histograms give the mass
   }
   // ---- phase 7: outputs ----------------------------------------------------------------------------------------------------------
   if (tid == 0) {
@@ -898,6 +903,7 @@ __device__ void sample_row_hist(const SampleDev& P, int row, int next, HistSmem&
     if (P.out_tau) P.out_tau[row] = tau;
     if (P.out_status) P.out_status[row] = status;
     if (P.out_vmax) P.out_vmax[row] = vmax;
+    if (P.out_mass) P.out_mass[row] = kept_weight;
   }
 }
 

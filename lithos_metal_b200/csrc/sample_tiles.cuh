@@ -261,6 +261,7 @@ __global__ void __launch_bounds__(kTB, kTopkPerSM) tile_finish_kernel(SampleDev 
         if (P.out_tau) P.out_tau[row] = -INFINITY;
         if (P.out_status) P.out_status[row] = 0u;
         if (P.out_vmax) P.out_vmax[row] = best_value(st->best);
+        if (P.out_mass) P.out_mass[row] = 0ull;
       }
       __syncthreads();
       continue;
@@ -300,6 +301,7 @@ __global__ void __launch_bounds__(kTB, kTopkPerSM) tile_finish_kernel(SampleDev 
       if (P.out_tau) P.out_tau[row] = -INFINITY;
       if (P.out_status) P.out_status[row] = LM_STATUS_TILE_DECLINED;
       if (P.out_vmax) P.out_vmax[row] = (st->flags & 4u) ? static_cast<float>(st->m) : -INFINITY;
+      if (P.out_mass) P.out_mass[row] = 0ull;
     }
     __syncthreads();
   }

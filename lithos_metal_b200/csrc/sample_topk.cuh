@@ -541,6 +541,7 @@ __device__ bool topk_finish(const SampleDev& P, int row, TopkSmem& c, uint32_t c
 
   // ---- the draw ----------------------------------------------------------------------------------------------------------
   int token = -1;
+  uint64_t kept_weight = 0ull;                                             // the kept set's fixed-point mass (for out_mass)
   if (P.draw == LM_DRAW_INVERSE_CDF) {
     // The kept candidates are in descending value order, which is the draw's order up to the order inside a run of equal values
     // (equal values have equal weights): an inclusive prefix sum of the weights finds the candidate where the target is crossed,
@@ -556,6 +557,7 @@ __device__ bool topk_finish(const SampleDev& P, int row, TopkSmem& c, uint32_t c
     }
     uint64_t total = 0ull;
     uint64_t run = block_exclusive_scan_u64(sum, c.scratch, &total);
+    kept_weight = total;
     if (tid == 0) { c.hit = kTopkCap; c.cross_bin = 0u; c.n_hit = static_cast<uint32_t>(n_kept); }
     __syncthreads();
     if (total > 0ull) {
@@ -607,12 +609,19 @@ __device__ bool topk_finish(const SampleDev& P, int row, TopkSmem& c, uint32_t c
       if (__syncthreads_or(rival >= best_value(win) - 4e-6f)) status |= LM_STATUS_NEAR_TIE;
       token = static_cast<int>(best_index(win));
     }
+    if (P.out_mass) {
+      const float c2 = exp2_scale(T);
+      uint64_t w = 0ull;
+      for (int i = tid; i < n_kept; i += kTB) w += weight_q40(fkey_inv(static_cast<uint32_t>(c.sel[i] >> 32)), vmax, c2);
+      kept_weight = block_sum_u64(w, c.scratch);
+    }
   }
   if (tid == 0) {
     P.out_tokens[row] = token;
     if (P.out_tau) P.out_tau[row] = tau;
     if (P.out_status) P.out_status[row] = status;
     if (P.out_vmax) P.out_vmax[row] = vmax;
+    if (P.out_mass) P.out_mass[row] = kept_weight;
   }
   __syncthreads();
   return true;

@@ -54,6 +54,7 @@ struct VerifyDev {
   const uint16_t* q_logits; int64_t q_logits_stride; const float* q_vmax; const unsigned long long* q_mass;   // q from the drafter's BF16 logits when q is null
   const float* tau; const float* u_accept; const float* u_final;
   const float* row_max;                                  // stochastic mode, optional: the exact maxima of the step's rows (from the sampler): spares the first exchange
+  const unsigned long long* row_mass;                    // ... and their kept sets' fixed-point masses (needs row_max): the accept test needs no exchange at all
   uint64_t seed; uint32_t step;
   int32_t* out_accept; int32_t* out_final; int32_t* out_tokens; float* out_p_draft;
   VerifyWs* ws;
@@ -329,6 +330,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   const int split = max(1, kVerifyWarps / R);                              // without the shared-memory copy every row is shared by `split` warps
   const int n_red = cached ? n4p / 32 : split;                             // partial results per row in s_red
   const bool given_max = stochastic && P.row_max != nullptr;              // the sampler already knows the rows' maxima: nothing to find or exchange
+  const bool given_mass = given_max && P.row_mass != nullptr;             // ... and the masses of their kept sets: only the draw is left to do together
   if (given_max) {
     if (tid < R) s_best[tid] = pack52(canon_zero(P.row_max[row0 + tid]), 0u);
   } else if (cached) {
@@ -390,7 +392,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   clean_other_bank();
   __syncthreads();                                                        // s_red is reused below
 
-  uint64_t vals[kConsumeSlots];
+  uint64_t vals[kConsumeSlots] = {0ull, 0ull, 0ull, 0ull};
   const int Gp = (G + 31) & ~31;
   if (!stochastic) {
     // ---- greedy: block 0 gathers every row's pick and votes; the others are done --------------------------------------------
@@ -411,7 +413,9 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   } else {
     // ---- phase 1: every block learns the row maxima; fixed-point mass of every row's kept set; the drafts' own weights -------
     if (!given_max) consume_rows<false>(&ws->best[0][0], R, G, s_best, s_red, limit, &failed, vals);
-    if (cached) {
+    if (given_mass) {
+      // nothing to sum: the sampler's masses, and every block evaluates the drafts' weights itself (one logit each)
+    } else if (cached) {
       // the same walk as for the maxima: four elements per load, two packed weight evaluations, one warp sum per 128 elements
       for (int i0 = 0; i0 < R * n4p; i0 += kVerifyBlock) {
         const int r0 = (i0 + (tid & ~31)) / n4p;
@@ -465,20 +469,27 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     }
     }
     __syncthreads();
-    if (tid < R) {
+    if (tid < R && !given_mass) {
       uint64_t w = 0ull;
       for (int k = 0; k < n_red; k++) w += s_red[tid][k];
       s_own[tid] = w;
       publish(&ws->mass[tid][b], w);
     }
+    if (tid < R && given_mass) s_mass[tid] = P.row_mass[row0 + tid];
     __syncthreads();
     // ---- phase 2: row masses; accept tests (every block, identically); this slice's share of the residual -------------------
-    const unsigned long long dw_first = tid < L ? peek(&ws->draft_w[tid]) : 0ull;   // in flight while the masses are consumed
-    consume_rows<true>(&ws->mass[0][0], R, G, s_mass, s_red, limit, &failed, vals);
+    const unsigned long long dw_first = (tid < L && !given_mass) ? peek(&ws->draft_w[tid]) : 0ull;   // in flight while the masses are consumed
+    if (!given_mass) consume_rows<true>(&ws->mass[0][0], R, G, s_mass, s_red, limit, &failed, vals);
     if (tid < 32) {
       bool reject = false;
       if (tid < L) {
-        const uint64_t dw = consume(&ws->draft_w[tid], limit, &failed, dw_first), mass = s_mass[tid];
+        uint64_t dw;
+        if (given_mass) {                                                  // the draft's own weight, straight from its logit
+          const float z = (my_draft >= 0 && my_draft < V) ? verify_load(P, row0 + tid, my_draft) : -INFINITY;
+          const float tau = P.tau ? P.tau[row0 + tid] : -INFINITY;
+          dw = (z >= tau) ? weight_q40(z, pack52_value(s_best[tid]), c2) : 0ull;
+        } else dw = consume(&ws->draft_w[tid], limit, &failed, dw_first);
+        const uint64_t mass = s_mass[tid];
         const float pd = (my_draft >= 0 && my_draft < V && mass > 0ull) ? prob_q40(dw, mass) : 0.0f;
         reject = __fmul_rn(my_u, my_q) >= pd;
         if (b == 0 && P.out_p_draft) P.out_p_draft[tid] = pd;
@@ -500,6 +511,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
       if (r == j && g < b) pre_w += vals[k];
     }
     pre_w = block_sum_u64(pre_w, scratch);
+    uint64_t own_w = given_mass ? 0ull : s_own[j];                         // this block's share of row j's mass (the draw over p itself)
     // residual weight of element i of this slice (0 when not kept or not positive)
     auto residual = [&](int i) -> uint64_t {
       const float z = S.z(j, i);
@@ -539,6 +551,22 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
         kr = block_max_u64(kr, scratch); ko = block_max_u64(ko, scratch);
         token = kr ? static_cast<int>(pack52_index(kr)) : (ko ? static_cast<int>(pack52_index(ko)) : -1);
       }
+    } else if (given_mass) {
+      // ---- the one exchange of a launch that was given the masses: this slice's share of row j's mass and of its residual --------
+      uint64_t w = 0ull, wo = 0ull;
+      if (mass_j > 0ull) for (int i = tid; i < len; i += kVerifyBlock) {
+        const float z = S.z(j, i);
+        if (z >= tau_j) wo += weight_q40(z, vmax_j, c2);
+        if (has_q) w += residual(i);
+      }
+      mine_r = block_sum_u64(w, scratch); own_w = block_sum_u64(wo, scratch);
+      if (tid == 0) { publish(&ws->resid[0][b], mine_r); publish(&ws->resid[1][b], own_w); }
+      uint64_t tr = 0ull, pr = 0ull, pw = 0ull;
+      for (int g = tid; g < G; g += kVerifyBlock) {
+        const uint64_t v = consume(&ws->resid[0][g], limit, &failed), o = consume(&ws->resid[1][g], limit, &failed);
+        tr += v; if (g < b) { pr += v; pw += o; }
+      }
+      total_r = block_sum_u64(tr, scratch); pre_r = block_sum_u64(pr, scratch); pre_w = block_sum_u64(pw, scratch);
     } else if (has_q) {
       // ---- the residual's total: one more exchange (skipped when every draft was accepted: the bonus row draws from p) --------
       uint64_t w = 0ull;
@@ -559,7 +587,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     } else {
       const bool use_res = total_r > 0ull;                               // an empty residual: draw from the row's own kept softmax
       const uint64_t total = use_res ? total_r : mass_j;
-      const uint64_t own = use_res ? mine_r : s_own[j];                   // this block's share of the total
+      const uint64_t own = use_res ? mine_r : own_w;                      // this block's share of the total
       const uint64_t pre = use_res ? pre_r : pre_w;
       if (tid == 0) s_token = -2;
       __syncthreads();

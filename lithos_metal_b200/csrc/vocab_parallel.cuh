@@ -106,7 +106,7 @@ struct VpMergeDev {
   const float* temperature; float temperature_s; const int32_t* top_k; int32_t top_k_s;
   const float* top_p; float top_p_s; const float* min_p; float min_p_s;
   uint32_t flags; int draw; const float* uniforms; uint64_t seed; uint32_t step; int64_t row_offset;
-  int32_t* out_tokens; float* out_tau; uint32_t* out_status; float* out_vmax;
+  int32_t* out_tokens; float* out_tau; uint32_t* out_status; float* out_vmax; unsigned long long* out_mass;
   uint32_t path_status;              // ORed into every row's status (0 in the vocab-parallel mode)
   int hand_on;                       // single-GPU use (sample_sliced.cuh): a row whose records overflowed is left to the caller
 };
@@ -258,12 +258,14 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
   const bool kept = valid && val >= tau;
   uint32_t status = status0 | edge | P.path_status;
   // ---- the draw
+  uint64_t kept_weight = 0ull;
   if (P.draw == LM_DRAW_INVERSE_CDF) {
     // the kept candidates are already in the draw's order (descending logit, equal logits by ascending index): one prefix sum
     const float c2 = exp2_scale(T);
     const uint64_t w = kept ? weight_q40(val, vmax, c2) : 0ull;
     uint64_t total = 0ull;
     const uint64_t before = block_exclusive_scan_u64(w, s.scratch, &total);
+    kept_weight = total;
     if (total > 0ull && w) {
       const uint64_t target = cdf_target(P.uniforms ? P.uniforms[row] : 0.0f, total);
       if (before <= target && target < before + w) s.token = idx;
@@ -280,6 +282,7 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
       if (__syncthreads_or(kept && mine != win && kf >= best_value(win) - 4e-6f)) status |= LM_STATUS_NEAR_TIE;
       if (tid == 0) s.token = static_cast<int>(best_index(win));
     }
+    if (P.out_mass) kept_weight = block_sum_u64(kept ? weight_q40(val, vmax, exp2_scale(T)) : 0ull, s.scratch);
   }
   __syncthreads();
   if (tid == 0) {
@@ -287,6 +290,7 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
     if (P.out_tau) P.out_tau[row] = tau;
     if (P.out_status) P.out_status[row] = status;
     if (P.out_vmax) P.out_vmax[row] = vmax;
+    if (P.out_mass) P.out_mass[row] = kept_weight;
   }
   __syncthreads();
   return true;

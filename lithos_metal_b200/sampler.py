@@ -45,6 +45,7 @@ class SampleOutput:
     probs: Optional[torch.Tensor] = None   # float32 [rows, vocab]
     status: Optional[torch.Tensor] = None  # int32 [rows] status bits
     vmax: Optional[torch.Tensor] = None    # float32 [rows]: the row's maximum logit (after penalties)
+    mass: Optional[torch.Tensor] = None    # int64 [rows]: the kept set's fixed-point mass (with vmax: what the verify step can take over)
 
 
 _workspaces: Dict[Tuple[int, str, int], torch.Tensor] = {}
@@ -179,6 +180,7 @@ def sample(logits: torch.Tensor, params: Optional[SamplingParams] = None, *, his
         res.status = torch.empty(rows, dtype=torch.int32, device=dev); a.out_status = res.status.data_ptr()
     if return_vmax:
         res.vmax = torch.empty(rows, dtype=torch.float32, device=dev); a.out_vmax = res.vmax.data_ptr()
+        res.mass = torch.empty(rows, dtype=torch.int64, device=dev); a.out_mass = res.mass.data_ptr()
     L = _lib.lib()
     ws = _workspace(dev, L.lm_workspace_bytes(rows, vocab))
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()

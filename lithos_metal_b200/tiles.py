@@ -116,6 +116,7 @@ class TileSampler:
             res.status = torch.empty(rows, dtype=torch.int32, device=dev); a.out_status = res.status.data_ptr()
         if return_vmax:
             res.vmax = torch.empty(rows, dtype=torch.float32, device=dev); a.out_vmax = res.vmax.data_ptr()
+            res.mass = torch.empty(rows, dtype=torch.int64, device=dev); a.out_mass = res.mass.data_ptr()
         a.stream = torch.cuda.current_stream(dev).cuda_stream
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().lm_tile_finish(C.byref(a), self._state.data_ptr(), self._state.numel()), "lm_tile_finish")

@@ -67,7 +67,8 @@ def verify(target_logits: torch.Tensor, draft_ids: Optional[torch.Tensor], draft
            u_resample: Optional[torch.Tensor] = None, mode: str = "greedy", *, temperature: float = 1.0, tau: Optional[torch.Tensor] = None,
            return_p_draft: bool = False, draft_logits: Optional[torch.Tensor] = None, draft_stats: Optional[DraftQ] = None,
            commit: Optional[dict] = None, seed: int = 0, step: int = 0, residual_draw: str = "inverse_cdf", step_state=None,
-           out: Optional[torch.Tensor] = None, wait_limit: int = 0, selftest: int = 0, target_vmax: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, ...]:
+           out: Optional[torch.Tensor] = None, wait_limit: int = 0, selftest: int = 0, target_vmax: Optional[torch.Tensor] = None,
+           target_mass: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, ...]:
     """``(accept_len [1], final_token [1], tokens [n + 1])`` as int32 CUDA tensors (plus ``p_draft [n]`` on request).
 
     ``target_logits`` [n + 1, V] bfloat16/float32; ``draft_ids`` [n] int32; stochastic mode also takes the drafter's
@@ -84,7 +85,8 @@ def verify(target_logits: torch.Tensor, draft_ids: Optional[torch.Tensor], draft
     verify length, drafts (``draft_ids`` may then be None: ``target_logits`` holds ``layout.t_max`` rows), seed and step are read
     there, and a finished state leaves the outputs untouched. ``out`` (int32 [rows + 2]) receives accept, final and the tokens.
     ``target_vmax`` (float32, one value per target row; stochastic mode) hands the kernel the exact row maxima the sampler already knows, as the
-    reference's verify kernels get them, and spares the launch one exchange between its thread blocks.
+    reference's verify kernels get them, and spares the launch one exchange between its thread blocks; ``target_mass`` (int64, the kept sets'
+    fixed-point masses for the same thresholds and temperature: ``sample(..., return_vmax=True).mass``) spares it the second.
     ``wait_limit`` / ``selftest`` exercise the kernel's bounded waits (tests only). Asynchronous on the current stream.
     """
     if mode not in ("greedy", "stochastic"):
@@ -118,6 +120,11 @@ def verify(target_logits: torch.Tensor, draft_ids: Optional[torch.Tensor], draft
         if target_vmax.numel() != target_logits.shape[0]:
             raise ValueError("target_vmax must hold one value per target row")
         a.target_vmax = target_vmax.data_ptr()
+        if target_mass is not None:
+            target_mass = target_mass.to(device=dev, dtype=torch.int64).contiguous()
+            if target_mass.numel() != target_logits.shape[0]:
+                raise ValueError("target_mass must hold one value per target row")
+            a.target_mass = target_mass.data_ptr()
     if step_state is not None:
         a.step_state, a.t_max, a.gamma_max, st_keep = _state_fields(step_state)
         keep.append(st_keep)

@@ -1,5 +1,7 @@
 """The CUDA sampler against the reference's golden outputs and against the CPU oracle (bit-exact token ids,
 thresholds and kept sets; probabilities within 1e-5 relative). All calls go through the C ABI."""
+import ctypes as C
+
 import numpy as np
 import pytest
 import torch
@@ -494,3 +496,20 @@ def test_row_maxima_come_out_of_every_kernel_and_feed_the_verify_step():
     a = lm.verify(*args, temperature=0.8, tau=s.tau)
     b = lm.verify(*args, temperature=0.8, tau=s.tau, target_vmax=s.vmax)
     assert [v.cpu().tolist() for v in a] == [v.cpu().tolist() for v in b]
+    # ... and the kept sets' masses, for every way a step can end (mixed, every draft accepted, first draft rejected) and both residual draws
+    for u in (ua, np.zeros(7, np.float32), np.full(7, 0.999, np.float32)):
+        for draw in ("inverse_cdf", "gumbel"):
+            args = (xt, torch.from_numpy(drafts).cuda(), torch.from_numpy(q).cuda(), torch.from_numpy(u).cuda(), torch.tensor([uf]), "stochastic")
+            kw = dict(temperature=0.8, tau=s.tau, residual_draw=draw, seed=5, step=2, return_p_draft=True)
+            a = lm.verify(*args, **kw)
+            b = lm.verify(*args, target_vmax=s.vmax, target_mass=s.mass, **kw)
+            assert [v.cpu().tolist() for v in a] == [v.cpu().tolist() for v in b], (draw, u[0])
+    # the masses themselves, from every kernel and both of the sampler's draws: the integer sum the oracle forms
+    z = oracle.bf16_to_f32(target)
+    for draw in ("inverse_cdf", "gumbel"):
+        for knobs in (dict(top_k=torch.full((8,), 50, dtype=torch.int32)), dict(top_k=torch.zeros(8, dtype=torch.int32)), dict(top_k=50)):
+            r = lm.sample(xt, lm.SamplingParams(temperature=0.8, top_p=0.95, seed=1, draw=draw, **knobs), uniforms=torch.full((8,), 0.3), return_tau=True, return_vmax=True)
+            for i in range(8):
+                total = C.c_uint64()
+                oracle.lib().lmo_sample_invcdf(z[i].ctypes.data_as(C.POINTER(C.c_float)), z.shape[1], float(r.tau[i]), np.float32(0.8), np.float32(0.3), C.byref(total))
+                assert int(r.mass[i]) == total.value, (draw, knobs, i)
