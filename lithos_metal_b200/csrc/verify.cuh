@@ -183,7 +183,8 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   extern __shared__ __align__(16) float v_smem[];
   __shared__ uint64_t scratch[32];
   __shared__ uint64_t s_red[kVerifyMaxRows][32];
-  __shared__ int s_j, s_token;
+  __shared__ int s_j, s_token, s_j2;
+  __shared__ unsigned long long s_pre2;
   __shared__ int s_drafts[kVerifyMaxRows];
   __shared__ unsigned long long s_best[kVerifyMaxRows], s_mass[kVerifyMaxRows], s_own[kVerifyMaxRows];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, G = gridDim.x, b = blockIdx.x;
@@ -242,6 +243,9 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   const float c2 = stochastic ? exp2_scale(P.temperature) : 0.0f;
   VerifySlice S{&P, zs, qs, per, lo, row0, c2};
 
+  const bool given_max = stochastic && P.row_max != nullptr;              // the sampler already knows the rows' maxima: nothing to find or exchange
+  const bool given_mass = given_max && P.row_mass != nullptr;             // ... and the masses of their kept sets: only the draw is left to do together
+
   // ---- phase 0: the only HBM pass. Slices of every target row and every draft row into shared memory.
   // The scalars the accept test needs later are fetched now, so their latency hides behind the slice loads.
   int my_draft = -1; float my_q = 0.0f, my_u = 0.0f;
@@ -252,6 +256,11 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   if (stochastic && tid < L) {
     my_u = P.u_accept ? P.u_accept[tid] : uniform01(seed, step, 3000u + static_cast<uint32_t>(tid), 0u);
     if (my_draft >= 0 && my_draft < V) my_q = verify_q(P, tid, my_draft, c2);
+  }
+  unsigned long long my_mass = 0ull; float my_zd = -INFINITY;              // given the masses: the row's mass and the draft's own logit, fetched now too
+  if (given_mass) {
+    if (tid < R) my_mass = P.row_mass[row0 + tid];
+    if (tid < L && my_draft >= 0 && my_draft < V) my_zd = verify_load(P, row0 + tid, my_draft);
   }
   if (cached) {
     // 8 elements per load item (one 16-byte load of BF16 logits, two of FP32 logits or draft probabilities), every item of
@@ -329,8 +338,6 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   const int n4 = (len + 3) / 4, n4p = (n4 + 31) & ~31;                      // groups of four elements per row of the slice
   const int split = max(1, kVerifyWarps / R);                              // without the shared-memory copy every row is shared by `split` warps
   const int n_red = cached ? n4p / 32 : split;                             // partial results per row in s_red
-  const bool given_max = stochastic && P.row_max != nullptr;              // the sampler already knows the rows' maxima: nothing to find or exchange
-  const bool given_mass = given_max && P.row_mass != nullptr;             // ... and the masses of their kept sets: only the draw is left to do together
   if (given_max) {
     if (tid < R) s_best[tid] = pack52(canon_zero(P.row_max[row0 + tid]), 0u);
   } else if (cached) {
@@ -475,7 +482,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
       s_own[tid] = w;
       publish(&ws->mass[tid][b], w);
     }
-    if (tid < R && given_mass) s_mass[tid] = P.row_mass[row0 + tid];
+    if (tid < R && given_mass) s_mass[tid] = my_mass;
     __syncthreads();
     // ---- phase 2: row masses; accept tests (every block, identically); this slice's share of the residual -------------------
     const unsigned long long dw_first = (tid < L && !given_mass) ? peek(&ws->draft_w[tid]) : 0ull;   // in flight while the masses are consumed
@@ -485,9 +492,8 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
       if (tid < L) {
         uint64_t dw;
         if (given_mass) {                                                  // the draft's own weight, straight from its logit
-          const float z = (my_draft >= 0 && my_draft < V) ? verify_load(P, row0 + tid, my_draft) : -INFINITY;
           const float tau = P.tau ? P.tau[row0 + tid] : -INFINITY;
-          dw = (z >= tau) ? weight_q40(z, pack52_value(s_best[tid]), c2) : 0ull;
+          dw = (my_zd >= tau) ? weight_q40(my_zd, pack52_value(s_best[tid]), c2) : 0ull;
         } else dw = consume(&ws->draft_w[tid], limit, &failed, dw_first);
         const uint64_t mass = s_mass[tid];
         const float pd = (my_draft >= 0 && my_draft < V && mass > 0ull) ? prob_q40(dw, mass) : 0.0f;
@@ -505,20 +511,44 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     const bool has_q = j < L;
     // this block's exclusive prefix over the blocks' masses of row j (the draw over p itself needs it)
     uint64_t pre_w = 0ull;
+    if (!given_mass) {
 #pragma unroll
-    for (int k = 0; k < kConsumeSlots; k++) {
-      const int idx = k * kVerifyBlock + tid, r = idx / Gp, g = idx - r * Gp;
-      if (r == j && g < b) pre_w += vals[k];
+      for (int k = 0; k < kConsumeSlots; k++) {
+        const int idx = k * kVerifyBlock + tid, r = idx / Gp, g = idx - r * Gp;
+        if (r == j && g < b) pre_w += vals[k];
+      }
+      pre_w = block_sum_u64(pre_w, scratch);
     }
-    pre_w = block_sum_u64(pre_w, scratch);
     uint64_t own_w = given_mass ? 0ull : s_own[j];                         // this block's share of row j's mass (the draw over p itself)
     // residual weight of element i of this slice (0 when not kept or not positive)
-    auto residual = [&](int i) -> uint64_t {
-      const float z = S.z(j, i);
+    auto residual_of = [&](const VerifySlice& V2, int i) -> uint64_t {
+      const float z = V2.z(j, i);
       if (!(z >= tau_j)) return 0ull;
       const float p = prob_q40(weight_q40(z, vmax_j, c2), mass_j);
-      const float res = has_q ? __fsub_rn(p, S.q(j, i)) : p;
+      const float res = has_q ? __fsub_rn(p, V2.q(j, i)) : p;
       return res > 0.0f ? residual_q40(res) : 0ull;
+    };
+    auto residual = [&](int i) -> uint64_t { return residual_of(S, i); };
+    // the token inside a slice (lo2, len2, read through V2): the first element, in index order, at which the running weight -- the
+    // residual's, or the row's own when the residual is empty -- passes the target; `base` = the weight of everything before the slice
+    auto locate = [&](const VerifySlice& V2, int lo2, int len2, uint64_t base, bool use_res, uint64_t target) -> int {
+      if (tid == 0) s_token = -2;
+      __syncthreads();
+      for (int i0 = 0; i0 < len2; i0 += kVerifyBlock) {                     // uniform trip count: block-wide scans inside
+        const int i = i0 + tid;
+        uint64_t w = 0ull;
+        if (i < len2) {
+          if (use_res) w = residual_of(V2, i);
+          else { const float z = V2.z(j, i); if (z >= tau_j) w = weight_q40(z, vmax_j, c2); }
+        }
+        uint64_t sweep = 0ull;
+        const uint64_t excl = block_exclusive_scan_u64(w, scratch, &sweep);
+        if (w && base + excl <= target && target < base + excl + w) s_token = lo2 + i;
+        base += sweep;
+        __syncthreads();
+        if (s_token != -2) break;
+      }
+      return s_token;
     };
     const uint32_t t_row = static_cast<uint32_t>(row0 + j);
     const float inv_t32 = __double2float_rn(1.0 / static_cast<double>(P.temperature));
@@ -561,12 +591,18 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
       }
       mine_r = block_sum_u64(w, scratch); own_w = block_sum_u64(wo, scratch);
       if (tid == 0) { publish(&ws->resid[0][b], mine_r); publish(&ws->resid[1][b], own_w); }
-      uint64_t tr = 0ull, pr = 0ull, pw = 0ull;
-      for (int g = tid; g < G; g += kVerifyBlock) {
-        const uint64_t v = consume(&ws->resid[0][g], limit, &failed), o = consume(&ws->resid[1][g], limit, &failed);
-        tr += v; if (g < b) { pr += v; pw += o; }
+      // Block 0 alone gathers the shares (148 blocks polling each other's words from the moment they have published cost more than
+      // the draw itself); it then reads the one slice that holds the crossing straight from L2. Every other block is done.
+      if (b == 0) {
+        uint64_t* a_res = &s_red[0][0];                                    // G <= 256 shares each: s_red is free from here on
+        uint64_t* a_own = &s_red[8][0];
+        uint64_t tr = 0ull;
+        for (int g = tid; g < G; g += kVerifyBlock) {
+          const uint64_t v = consume(&ws->resid[0][g], limit, &failed), o = consume(&ws->resid[1][g], limit, &failed);
+          a_res[g] = v; a_own[g] = o; tr += v;
+        }
+        total_r = block_sum_u64(tr, scratch);                              // (its barriers also publish a_res / a_own to the block)
       }
-      total_r = block_sum_u64(tr, scratch); pre_r = block_sum_u64(pr, scratch); pre_w = block_sum_u64(pw, scratch);
     } else if (has_q) {
       // ---- the residual's total: one more exchange (skipped when every draft was accepted: the bonus row draws from p) --------
       uint64_t w = 0ull;
@@ -584,34 +620,40 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     bool writer = false;
     if (gumbel_draw) {
       writer = b == 0;
+    } else if (given_mass) {
+      if (b == 0) {
+        writer = true;
+        const bool use_res = total_r > 0ull;                             // an empty residual: draw from the row's own kept softmax
+        const uint64_t total = use_res ? total_r : mass_j;
+        token = -1;                                                      // (a row with no weight at all: empty or all -inf)
+        if (total > 0ull && !bad) {
+          const float u = P.u_final ? P.u_final[0] : uniform01(seed, step, 4000u, 0u);
+          const uint64_t target = cdf_target(u, total);
+          // the block whose share holds the crossing: an exclusive prefix over the shares, one per thread
+          const uint64_t mine = tid < G ? (use_res ? (&s_red[0][0])[tid] : (&s_red[8][0])[tid]) : 0ull;
+          const uint64_t before = block_exclusive_scan_u64(mine, scratch, nullptr);
+          if (tid == 0) s_j2 = -1;
+          __syncthreads();
+          if (mine && before <= target && target < before + mine) { s_j2 = tid; s_pre2 = before; }
+          __syncthreads();
+          if (s_j2 >= 0) {
+            const int lo2 = min(V, s_j2 * per), len2 = min(V, lo2 + per) - lo2;
+            const VerifySlice V2{&P, (s_j2 == 0) ? zs : nullptr, (s_j2 == 0) ? qs : nullptr, per, lo2, row0, c2};   // block 0's own slice is in shared memory
+            token = locate(V2, lo2, len2, s_pre2, use_res, target);
+          }
+        }
+      }
     } else {
       const bool use_res = total_r > 0ull;                               // an empty residual: draw from the row's own kept softmax
       const uint64_t total = use_res ? total_r : mass_j;
       const uint64_t own = use_res ? mine_r : own_w;                      // this block's share of the total
       const uint64_t pre = use_res ? pre_r : pre_w;
-      if (tid == 0) s_token = -2;
-      __syncthreads();
       if (total > 0ull) {
         const float u = P.u_final ? P.u_final[0] : uniform01(seed, step, 4000u, 0u);
         const uint64_t target = cdf_target(u, total);
         if (own > 0ull && pre <= target && target < pre + own) {           // the crossing lies in this block's slice
           writer = true;
-          uint64_t base = pre;
-          for (int i0 = 0; i0 < len; i0 += kVerifyBlock) {                  // uniform trip count: block-wide scans inside
-            const int i = i0 + tid;
-            uint64_t w = 0ull;
-            if (i < len) {
-              if (use_res) w = residual(i);
-              else { const float z = S.z(j, i); if (z >= tau_j) w = weight_q40(z, vmax_j, c2); }
-            }
-            uint64_t sweep = 0ull;
-            const uint64_t excl = block_exclusive_scan_u64(w, scratch, &sweep);
-            if (w && base + excl <= target && target < base + excl + w) s_token = lo + i;
-            base += sweep;
-            __syncthreads();
-            if (s_token != -2) break;
-          }
-          token = s_token;
+          token = locate(S, lo, len, pre, use_res, target);
         }
       } else if (b == 0) { writer = true; token = -1; }                   // a row with no weight at all (empty or all -inf)
     }
