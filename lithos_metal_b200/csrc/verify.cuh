@@ -552,7 +552,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     };
     const uint32_t t_row = static_cast<uint32_t>(row0 + j);
     const float inv_t32 = __double2float_rn(1.0 / static_cast<double>(P.temperature));
-    uint64_t total_r = 0ull, pre_r = 0ull, mine_r = 0ull;
+    uint64_t total_r = 0ull, mine_r = 0ull;
     int token = -2;
     if (gumbel_draw) {
       // the reference's draws (kernels/common/sample.metal:322-346): argmax of ln(p - q) + noise of stream 4000 over the positive
@@ -604,14 +604,22 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
         total_r = block_sum_u64(tr, scratch);                              // (its barriers also publish a_res / a_own to the block)
       }
     } else if (has_q) {
-      // ---- the residual's total: one more exchange (skipped when every draft was accepted: the bonus row draws from p) --------
+      // ---- the residual's total: one more exchange (skipped when every draft was accepted: the bonus row draws from p). Block 0
+      // gathers, as above; the blocks' shares of row j's mass are still in the workspace from the exchange before.
       uint64_t w = 0ull;
       if (mass_j > 0ull) for (int i = tid; i < len; i += kVerifyBlock) w += residual(i);
       mine_r = block_sum_u64(w, scratch);
       if (tid == 0) publish(&ws->resid[0][b], mine_r);
-      uint64_t tr = 0ull, pr = 0ull;
-      for (int g = tid; g < G; g += kVerifyBlock) { const uint64_t v = consume(&ws->resid[0][g], limit, &failed); tr += v; if (g < b) pr += v; }
-      total_r = block_sum_u64(tr, scratch); pre_r = block_sum_u64(pr, scratch);
+      if (b == 0) {
+        uint64_t* a_res = &s_red[0][0];
+        uint64_t* a_own = &s_red[8][0];
+        uint64_t tr = 0ull;
+        for (int g = tid; g < G; g += kVerifyBlock) {
+          const uint64_t v = consume(&ws->resid[0][g], limit, &failed), o = consume(&ws->mass[j][g], limit, &failed);
+          a_res[g] = v; a_own[g] = o; tr += v;
+        }
+        total_r = block_sum_u64(tr, scratch);
+      }
     }
     const bool bad = __syncthreads_or(failed) != 0;
     if (bad && tid == 0) atomicExch(&ws->error, 1u);
@@ -620,7 +628,7 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
     bool writer = false;
     if (gumbel_draw) {
       writer = b == 0;
-    } else if (given_mass) {
+    } else if (given_mass || has_q) {                                       // the shares were gathered by block 0: it draws
       if (b == 0) {
         writer = true;
         const bool use_res = total_r > 0ull;                             // an empty residual: draw from the row's own kept softmax
@@ -644,16 +652,13 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
         }
       }
     } else {
-      const bool use_res = total_r > 0ull;                               // an empty residual: draw from the row's own kept softmax
-      const uint64_t total = use_res ? total_r : mass_j;
-      const uint64_t own = use_res ? mine_r : own_w;                      // this block's share of the total
-      const uint64_t pre = use_res ? pre_r : pre_w;
-      if (total > 0ull) {
+      // every draft accepted: the bonus row's own kept softmax; each block knows its share and its prefix from the masses' exchange
+      if (mass_j > 0ull) {
         const float u = P.u_final ? P.u_final[0] : uniform01(seed, step, 4000u, 0u);
-        const uint64_t target = cdf_target(u, total);
-        if (own > 0ull && pre <= target && target < pre + own) {           // the crossing lies in this block's slice
+        const uint64_t target = cdf_target(u, mass_j);
+        if (own_w > 0ull && pre_w <= target && target < pre_w + own_w) {   // the crossing lies in this block's slice
           writer = true;
-          token = locate(S, lo, len, pre, use_res, target);
+          token = locate(S, lo, len, pre_w, false, target);
         }
       } else if (b == 0) { writer = true; token = -1; }                   // a row with no weight at all (empty or all -inf)
     }
