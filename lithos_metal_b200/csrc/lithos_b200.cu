@@ -102,7 +102,7 @@ static int sm_count(int* out) {
 
 // Kernels that need more than 48 KB of dynamic shared memory must be told so once per device (the attribute belongs to the
 // device's copy of the function); remembered per device and kernel, raised when a call needs more.
-enum KernelSlot { kSlotFast, kSlotTopk, kSlotGeneric, kSlotVocabLocal, kSlotVerify, kSlotDraftQ, kSlotTileFinish, kSlotSlice, kSlotSliceSmall, kSlotSlicedMerge, kSlotCount };
+enum KernelSlot { kSlotFast, kSlotTopk, kSlotGeneric, kSlotVocabLocal, kSlotVerify, kSlotVerifyStats, kSlotDraftQ, kSlotTileFinish, kSlotSlice, kSlotSliceSmall, kSlotSlicedMerge, kSlotCount };
 
 static int ensure_dynamic_smem(KernelSlot slot, const void* func, size_t bytes) {
   if (bytes <= 48 * 1024) return LM_OK;
@@ -644,11 +644,12 @@ int lm_verify(const lm_verify_args* a) {
   size_t smem = rows_cached * static_cast<size_t>(per) * sizeof(float);
   int cached = smem <= 200 * 1024 ? 1 : 0;
   if (!cached) smem = 0;
-  rc = ensure_dynamic_smem(kSlotVerify, reinterpret_cast<const void*>(verify_kernel), smem);
+  const bool stats = P.row_max != nullptr && P.row_mass != nullptr;
+  const void* kernel = stats ? reinterpret_cast<const void*>(verify_kernel<true>) : reinterpret_cast<const void*>(verify_kernel<false>);
+  rc = ensure_dynamic_smem(stats ? kSlotVerifyStats : kSlotVerify, kernel, smem);
   if (rc != LM_OK) return rc;
   void* params[] = {&P, &cached};
-  const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(verify_kernel), dim3(grid), dim3(kVerifyBlock), params, smem,
-                                                    static_cast<cudaStream_t>(a->stream));
+  const cudaError_t e = cudaLaunchCooperativeKernel(const_cast<void*>(kernel), dim3(grid), dim3(kVerifyBlock), params, smem, static_cast<cudaStream_t>(a->stream));
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }
 

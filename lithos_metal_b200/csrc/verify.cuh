@@ -179,6 +179,9 @@ __device__ __forceinline__ void consume_rows(const unsigned long long* words, in
   __syncthreads();
 }
 
+// kStats: the launch was given the rows' maxima and masses (compiled apart: the launch that has to find them runs code that is
+// laid out as if the other did not exist, and the step is short enough for that to show).
+template <bool kStats>
 __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, int cached) {
   extern __shared__ __align__(16) float v_smem[];
   __shared__ uint64_t scratch[32];
@@ -243,8 +246,8 @@ __global__ void __launch_bounds__(kVerifyBlock, 1) verify_kernel(VerifyDev P, in
   const float c2 = stochastic ? exp2_scale(P.temperature) : 0.0f;
   VerifySlice S{&P, zs, qs, per, lo, row0, c2};
 
-  const bool given_max = stochastic && P.row_max != nullptr;              // the sampler already knows the rows' maxima: nothing to find or exchange
-  const bool given_mass = given_max && P.row_mass != nullptr;             // ... and the masses of their kept sets: only the draw is left to do together
+  const bool given_max = kStats || (stochastic && P.row_max != nullptr);              // the sampler already knows the rows' maxima: nothing to find or exchange
+  const bool given_mass = kStats;                                         // ... and the masses of their kept sets: only the draw is left to do together
 
   // ---- phase 0: the only HBM pass. Slices of every target row and every draft row into shared memory.
   // The scalars the accept test needs later are fetched now, so their latency hides behind the slice loads.
