@@ -82,9 +82,10 @@ def run_round(x, q, drafts, conf, st, ring, log, out, threshold, residual_draw, 
         lm.verify(x[:L + 1], d, q[:L], None, None, "stochastic", temperature=0.9, tau=tau, seed=seed, step=step, residual_draw=residual_draw,
                   out=out[:L + 3], commit=dict(layout=LAYOUT, state=st, ring=ring, log=log))
     else:                                                                 # nothing but launches: every kernel reads the state on the device
-        tau = lm.sample(x, lm.SamplingParams(temperature=0.9, top_k=50), step_state=(LAYOUT, st), return_tau=True).tau
-        lm.verify(x, None, q, None, None, "stochastic", temperature=0.9, tau=tau, residual_draw=residual_draw, step_state=(LAYOUT, st), out=out,
-                  commit=dict(layout=LAYOUT, state=st, ring=ring, log=log))
+        r = lm.sample(x, lm.SamplingParams(temperature=0.9, top_k=50), step_state=(LAYOUT, st), return_tau=True, return_vmax=True)
+        # ... and hands the verification the rows' maxima and masses along with the thresholds, as the reference's sampler does
+        lm.verify(x, None, q, None, None, "stochastic", temperature=0.9, tau=r.tau, target_vmax=r.vmax, target_mass=r.mass, residual_draw=residual_draw,
+                  step_state=(LAYOUT, st), out=out, commit=dict(layout=LAYOUT, state=st, ring=ring, log=log))
     lm.verify_select(LAYOUT, st, drafts, conf, gamma=7, threshold=threshold)
 
 
