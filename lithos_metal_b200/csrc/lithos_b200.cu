@@ -284,7 +284,7 @@ int lm_sample(const lm_sample_args* a) {
   const size_t ws_base = lm_workspace_bytes(a->rows, a->vocab) - kSlicedWsBytes;
   const bool sliced = a->rows <= kSlicedMaxRows && a->vocab >= kSlicedMinVocab && a->temperature == nullptr && a->temperature_s > 0.0f &&
                       a->top_k == nullptr && a->top_k_s >= 1 && a->top_k_s <= 64 && a->out_stats == nullptr && a->out_probs == nullptr &&
-                      a->step_state == nullptr && !(a->flags & LM_FLAG_EXACT_ONLY) && (!pen || a->hist_len <= 65536) &&
+                      !(a->flags & LM_FLAG_EXACT_ONLY) && (!pen || a->hist_len <= 65536) &&
                       a->workspace != nullptr && (reinterpret_cast<uintptr_t>(a->workspace) & 255u) == 0 && a->workspace_bytes >= ws_base + kSlicedWsBytes;
   if (sliced) {
     SliceDev S;
@@ -298,6 +298,7 @@ int lm_sample(const lm_sample_args* a) {
       S.temperature = a->temperature_s; S.top_k = a->top_k_s;
       S.history = P.history; S.hist_len = P.hist_len; S.hist_stride = P.hist_stride; S.rho = P.rho; S.pi = P.pi;
       S.records = reinterpret_cast<unsigned char*>(ws); S.record_bytes = static_cast<int64_t>(lm_vocab_record_bytes(S.cap));
+      S.state = P.state; S.t_max = P.t_max; S.g = P.g;
       const size_t slice_smem = slice_smem_bytes(S.slice_len);
       const size_t gsmem = sizeof(GenericSmem) + (pen ? static_cast<size_t>((a->vocab + 31) / 32) * 4 : 0) + 16;
       S.need_mass = (a->top_p != nullptr || (a->top_p_s > 0.0f && a->top_p_s < 1.0f)) && !(a->flags & LM_FLAG_TOPP_IN_TOPK);

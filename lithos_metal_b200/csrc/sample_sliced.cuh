@@ -35,6 +35,7 @@ struct SliceDev {
   float temperature; int top_k; int cap; int need_mass;
   const int32_t* history; int hist_len; int64_t hist_stride; float rho, pi;
   unsigned char* records; int64_t record_bytes;       // [slices][rows] records
+  const uint32_t* state; int t_max, g;                // optional StepState: rows beyond t_this_step, and a finished state, are left alone
 };
 
 __host__ __device__ inline size_t slice_smem_bytes(int slice_len) { return static_cast<size_t>(slice_len) * 4 + static_cast<size_t>(slice_len / 32 + 1) * 4; }
@@ -89,6 +90,10 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
   // the merge may be made resident while the slices are at work; it waits for this grid
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x, slice = blockIdx.x, row = blockIdx.y;
+  if (P.state) {
+    StepStateView st{const_cast<uint32_t*>(P.state), P.t_max, P.g};
+    if (st.done() || row >= static_cast<int>(st.t_this_step())) return;
+  }
   const int lo = slice * P.slice_len;
   const int n = max(0, min(P.slice_len, P.vocab - lo));
   unsigned char* rec = P.records + (static_cast<int64_t>(slice) * P.rows + row) * P.record_bytes;
@@ -165,11 +170,15 @@ __global__ void __launch_bounds__(kVpMaxCandidates, 1) sliced_merge_kernel(VpMer
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ VpMergeSmem s;
   asm volatile("griddepcontrol.wait;" ::: "memory");                      // the records are complete behind this
+  SampleDev Q = P;                                                         // with a StepState: the noise seed, the step and the active rows come from it
+  apply_step_state(Q);
+  VpMergeDev N = M;
+  N.seed = Q.seed; N.step = Q.step;
   const int row = blockIdx.x;
-  if (row >= M.rows) return;
-  if (!vocab_merge_row(M, row, s)) {                                       // overflowed records: the generic row algorithm, here and now
+  if (row >= Q.rows) return;
+  if (!vocab_merge_row(N, row, s)) {                                       // overflowed records: the generic row algorithm, here and now
     GenericSmem& g = *reinterpret_cast<GenericSmem*>(smem_raw);
-    sample_row_generic(P, row, g, reinterpret_cast<uint32_t*>(smem_raw + sizeof(GenericSmem)));
+    sample_row_generic(Q, row, g, reinterpret_cast<uint32_t*>(smem_raw + sizeof(GenericSmem)));
   }
 }
 
