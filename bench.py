@@ -526,6 +526,13 @@ def bench_verify(torch, lm, dev):
     vmax, mass = kept.vmax, kept.mass                                  # what the sampler leaves for the verify step (no thresholds here)
     worst = drafts.clone()
     worst[0] = (q[0] / torch.softmax(target[0].float(), dim=-1)).argmax().to(torch.int32)       # the token the drafter overrates most
+    round_params = lm.SamplingParams(temperature=0.8, top_k=50, top_p=0.95, draw="inverse_cdf")
+    u8 = torch.full((8,), 0.5, device=dev)
+
+    def round_tail(with_stats: bool):
+        r = lm.sample(target, round_params, uniforms=u8, return_tau=True, return_vmax=with_stats)
+        return lm.verify(target, drafts, q, ua, uf, "stochastic", temperature=0.8, tau=r.tau, target_vmax=r.vmax, target_mass=r.mass)
+
     calls = {"stochastic": lambda: lm.verify(target, drafts, q, ua, uf, "stochastic"),
              "stochastic_all_accepted": lambda: lm.verify(target, drafts, q, u_zero, uf, "stochastic"),
              "stochastic_first_rejected": lambda: lm.verify(target, worst, q, u_one, uf, "stochastic"),
@@ -534,6 +541,10 @@ def bench_verify(torch, lm, dev):
              # ... and the rows' masses too (both halves of KEPT_STATS: what lm_sample leaves in out_vmax / out_mass): one exchange in all
              "stochastic_given_row_stats": lambda: lm.verify(target, drafts, q, ua, uf, "stochastic", target_vmax=vmax, target_mass=mass),
              "stochastic_given_row_stats_first_rejected": lambda: lm.verify(target, worst, q, u_one, uf, "stochastic", target_vmax=vmax, target_mass=mass),
+             # the tail of a speculative step as the reference runs it: the sampler on the 8 rows (thresholds top_k 50 / top_p 0.95,
+             # temperature 0.8; it leaves tau and, in the second form, the rows' maxima and masses), then the verification
+             "round_sample_then_verify": lambda: round_tail(False),
+             "round_sample_then_verify_given_row_stats": lambda: round_tail(True),
              "stochastic_q_logits": lambda: lm.verify(target, stats.tokens, None, ua, uf, "stochastic", draft_logits=drafter, draft_stats=stats),
              "greedy": lambda: lm.verify(target, drafts, mode="greedy"),
              "draft_q_one_position": lambda: lm.draft_q(drafter[3:4], temperature=1.0, seed=SEED, step=0, first_position=3)}
