@@ -299,9 +299,11 @@ int lm_sample(const lm_sample_args* a) {
       S.history = P.history; S.hist_len = P.hist_len; S.hist_stride = P.hist_stride; S.rho = P.rho; S.pi = P.pi;
       S.records = reinterpret_cast<unsigned char*>(ws); S.record_bytes = static_cast<int64_t>(lm_vocab_record_bytes(S.cap));
       S.state = P.state; S.t_max = P.t_max; S.g = P.g;
-      const size_t slice_smem = slice_smem_bytes(S.slice_len);
       const size_t gsmem = sizeof(GenericSmem) + (pen ? static_cast<size_t>((a->vocab + 31) / 32) * 4 : 0) + 16;
       S.need_mass = (a->top_p != nullptr || (a->top_p_s > 0.0f && a->top_p_s < 1.0f)) && !(a->flags & LM_FLAG_TOPP_IN_TOPK);
+      // BF16 slices of at least 8 logits per thread: the softmass per distinct code (if the count table fits beside the slice)
+      S.code_table = S.need_mass && a->dtype == LM_DTYPE_BF16 && S.slice_len >= 8 * kSliceBlockBig && slice_smem_bytes(S.slice_len, true) <= 200 * 1024;
+      const size_t slice_smem = slice_smem_bytes(S.slice_len, S.code_table != 0);
       const bool big = static_cast<long long>(S.slices) * P.rows <= 2LL * sms;   // few slices in all: wide blocks, for the latency
       rc = big ? ensure_dynamic_smem(kSlotSlice, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockBig>), slice_smem)
                : ensure_dynamic_smem(kSlotSliceSmall, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockSmall>), slice_smem);

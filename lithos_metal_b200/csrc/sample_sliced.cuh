@@ -33,12 +33,16 @@ struct SliceDev {
   const void* logits; int dtype; int rows; int vocab; int64_t row_stride;
   int slices; int slice_len;                          // slice_len: a multiple of 8 (the last slices of a row may be short or empty)
   float temperature; int top_k; int cap; int need_mass;
+  int code_table;                                     // BF16 rows: the softmass per distinct code (a 128 KB table of counts behind the slice) instead of per logit
   const int32_t* history; int hist_len; int64_t hist_stride; float rho, pi;
   unsigned char* records; int64_t record_bytes;       // [slices][rows] records
   const uint32_t* state; int t_max, g;                // optional StepState: rows beyond t_this_step, and a finished state, are left alone
 };
 
-__host__ __device__ inline size_t slice_smem_bytes(int slice_len) { return static_cast<size_t>(slice_len) * 4 + static_cast<size_t>(slice_len / 32 + 1) * 4; }
+constexpr size_t kSliceTableBytes = 65536 * 2;      // one 16-bit counter per BF16 code
+__host__ __device__ inline size_t slice_marks_offset(int slice_len) { return static_cast<size_t>(slice_len) * 4; }
+__host__ __device__ inline size_t slice_table_offset(int slice_len) { return (slice_marks_offset(slice_len) + static_cast<size_t>(slice_len / 32 + 1) * 4 + 15) & ~static_cast<size_t>(15); }
+__host__ __device__ inline size_t slice_smem_bytes(int slice_len, bool table) { return slice_table_offset(slice_len) + (table ? kSliceTableBytes : 0); }
 
 // A lower bound of the k-th largest of vals[0 .. n) (1 <= k <= n) that shares its upper 22 key bits: a radix descent of 11 + 11
 // bits on the monotone keys. (BF16 logits have no key bits below those; for binary32 logits the few values that share the upper
@@ -82,7 +86,7 @@ template <int B>
 __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* vals = reinterpret_cast<float*>(smem_raw);
-  uint32_t* marks = reinterpret_cast<uint32_t*>(smem_raw + static_cast<size_t>(P.slice_len) * 4);
+  uint32_t* marks = reinterpret_cast<uint32_t*>(smem_raw + slice_marks_offset(P.slice_len));
   __shared__ uint32_t bins[kSliceBins];
   __shared__ uint64_t scratch[32];
   __shared__ uint32_t pick[2];
@@ -139,7 +143,27 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
   const float vmax = best_value(best);
   const double inv_t = 1.0 / static_cast<double>(P.temperature);
   double mass = 0.0;
-  if (P.need_mass) {                                                       // (only a top-p over the whole row asks for it)
+  if (P.need_mass && P.code_table) {
+    // A BF16 slice holds far fewer distinct values than logits: count the logits per code (16-bit counters, two per word), then one
+    // FP64 exponential per code that occurs instead of one per logit. Penalised logits are off the BF16 grid and are taken one by one.
+    uint32_t* table = reinterpret_cast<uint32_t*>(smem_raw + slice_table_offset(P.slice_len));
+    for (int i = tid; i < 32768; i += B) table[i] = 0u;
+    __syncthreads();
+    double m = 0.0;
+    for (int j = tid; j < n; j += B) {
+      if (pen_on && ((marks[j >> 5] >> (j & 31)) & 1u)) { m += softmass(vals[j], vmax, inv_t); continue; }
+      const uint32_t code = __float_as_uint(vals[j]) >> 16;
+      atomicAdd(&table[code >> 1], (code & 1u) ? 0x10000u : 1u);
+    }
+    __syncthreads();
+    for (int i = tid; i < 32768; i += B) {
+      const uint32_t w = table[i];
+      if (!w) continue;
+      if (w & 0xFFFFu) m += static_cast<double>(w & 0xFFFFu) * softmass(__uint_as_float(static_cast<uint32_t>(2 * i) << 16), vmax, inv_t);
+      if (w >> 16) m += static_cast<double>(w >> 16) * softmass(__uint_as_float(static_cast<uint32_t>(2 * i + 1) << 16), vmax, inv_t);
+    }
+    mass = block_sum_f64(m, scratch);
+  } else if (P.need_mass) {                                                // (only a top-p over the whole row asks for it)
     double m = 0.0;
     for (int j = tid; j < n; j += B) m += softmass(vals[j], vmax, inv_t);
     mass = block_sum_f64(m, scratch);
