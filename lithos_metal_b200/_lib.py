@@ -21,7 +21,7 @@ STATUS_CANDIDATE_PATH = 64
 STATUS_TILE_DECLINED = 128
 STATUS_SLICED_PATH = 256
 TILE_MAX_COLS = 2048
-VOCAB_MAX_CANDIDATES = 1024
+VOCAB_MAX_CANDIDATES = 8192
 MAX_DRAFT = 15
 MAX_VOCAB = 1048576
 ARGMAX_STATIC_MAX_ROWS = 4096

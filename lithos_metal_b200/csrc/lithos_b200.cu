@@ -288,9 +288,9 @@ int lm_sample(const lm_sample_args* a) {
                       a->workspace != nullptr && (reinterpret_cast<uintptr_t>(a->workspace) & 255u) == 0 && a->workspace_bytes >= ws_base + kSlicedWsBytes;
   if (sliced) {
     SliceDev S;
-    // a record holds twice the top_k: only a slice with more than top_k ties at its own k-th value overflows it
-    S.slices = a->top_k_s <= 8 ? 64 : (a->top_k_s <= 16 ? 32 : (a->top_k_s <= 32 ? 16 : 8));
-    S.cap = kVpMaxCandidates / S.slices;
+    // a record holds twice the top_k (16 at least): only a slice with that many logits at or above its own bound overflows it
+    S.slices = kSlices;
+    S.cap = a->top_k_s <= 8 ? 16 : 2 * a->top_k_s;
     S.slice_len = static_cast<int>(((a->vocab + S.slices - 1) / S.slices + 7) / 8 * 8);
     if (S.slice_len <= kSliceMaxLen) {
       char* ws = static_cast<char*>(a->workspace) + ws_base;
@@ -299,11 +299,9 @@ int lm_sample(const lm_sample_args* a) {
       S.history = P.history; S.hist_len = P.hist_len; S.hist_stride = P.hist_stride; S.rho = P.rho; S.pi = P.pi;
       S.records = reinterpret_cast<unsigned char*>(ws); S.record_bytes = static_cast<int64_t>(lm_vocab_record_bytes(S.cap));
       S.state = P.state; S.t_max = P.t_max; S.g = P.g;
-      const size_t gsmem = sizeof(GenericSmem) + (pen ? static_cast<size_t>((a->vocab + 31) / 32) * 4 : 0) + 16;
+      const size_t gsmem = sizeof(GenericSmem) + (pen ? static_cast<size_t>((a->vocab + 31) / 32) * 4 : 0) + 16;   // a row handed on to the generic algorithm
       S.need_mass = (a->top_p != nullptr || (a->top_p_s > 0.0f && a->top_p_s < 1.0f)) && !(a->flags & LM_FLAG_TOPP_IN_TOPK);
-      // BF16 slices of at least 8 logits per thread: the softmass per distinct code (if the count table fits beside the slice)
-      S.code_table = S.need_mass && a->dtype == LM_DTYPE_BF16 && S.slice_len >= 8 * kSliceBlockBig && slice_smem_bytes(S.slice_len, true) <= 200 * 1024;
-      const size_t slice_smem = slice_smem_bytes(S.slice_len, S.code_table != 0);
+      const size_t slice_smem = slice_smem_bytes(S.slice_len);
       const bool big = static_cast<long long>(S.slices) * P.rows <= 2LL * sms;   // few slices in all: wide blocks, for the latency
       rc = big ? ensure_dynamic_smem(kSlotSlice, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockBig>), slice_smem)
                : ensure_dynamic_smem(kSlotSliceSmall, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockSmall>), slice_smem);
@@ -518,7 +516,7 @@ int lm_vocab_merge(const lm_vocab_args* a) {
   if (a->temperature == nullptr && !(a->temperature_s > 0.0f)) return LM_E_INVALID;
   if (a->top_k == nullptr && a->top_k_s < 1) return LM_E_INVALID;
   if (a->draw == LM_DRAW_INVERSE_CDF && a->uniforms == nullptr) return LM_E_INVALID;
-  if (static_cast<int64_t>(a->shards) * a->cap > LM_VOCAB_MAX_CANDIDATES || a->shards > kVpMaxShards || a->rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
+  if (a->shards > kVpMaxShards || a->cap > kVpPerThread * (kVpMaxCandidates / a->shards) || a->rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
   VpMergeDev P;
   P.records = static_cast<const unsigned char*>(a->records); P.shards = a->shards; P.rows = static_cast<int>(a->rows); P.cap = a->cap;
   P.record_bytes = static_cast<int64_t>(lm_vocab_record_bytes(a->cap));

@@ -4,16 +4,17 @@
 // one block walking 150k logits several times. The decode step of a single stream is exactly that call (the reference's sampler
 // dispatches run on T <= 8 rows per step, monolith/kernels.py:720-775). Here the slices of a row go to different SMs:
 //
-//   slice_local_kernel  (slices x rows blocks)  reads its slice ONCE into shared memory (BF16 or FP32, widened; the penalties of
+//   slice_local_kernel  (64 slices x rows blocks)  reads its slice ONCE into shared memory (BF16 or FP32, widened; the penalties of
 //                       the history ids that fall into the slice applied), and leaves a record: the slice's maximum, its FP64
-//                       softmass relative to that maximum, and every logit at or above (a close lower bound of) the slice's own k-th largest;
-//   vocab_merge_kernel  (one block per row; vocab_parallel.cuh) the same merge that joins the shards of the vocab-parallel mode:
-//                       sorts the candidates of all slices, rebuilds the row's maximum and mass, thresholds, draw.
+//                       softmass relative to that maximum, and every logit at or above a lower bound of the slice's own k-th
+//                       largest (the k-th largest of the threads' own maxima, to 22 key bits);
+//   sliced_merge_kernel (one block per row) the merge that joins the shards of the vocab-parallel mode (vocab_parallel.cuh):
+//                       gathers the candidates of all slices, puts those at or above the row's top-k bound in order, rebuilds
+//                       the row's maximum and mass, thresholds, draw.
 //
-// The record format is the vocab-parallel one, a slice standing for a shard. Rows with a top_k of 1 .. 64 only: the merge sorts
-// 1024 candidates, and every slice's record has room for twice the top_k (64 / 32 / 16 / 8 slices for a top_k up to 8 / 16 / 32 /
-// 64), so that only a slice with more than top_k ties at its own k-th value overflows it; the merge's block then
-// runs the generic row algorithm on such a row itself.
+// The record format is the vocab-parallel one, a slice standing for a shard. Rows with a top_k of 1 .. 64 only: a slice's record
+// has room for twice the top_k (16 at least), so that only a slice with that many logits at or above its bound (ties at its own
+// k-th value) overflows it; the merge's block then runs the generic row algorithm on such a row itself.
 #pragma once
 #include "common.cuh"
 #include "sample_generic.cuh"
@@ -26,27 +27,25 @@ constexpr int kSliceBlockSmall = 256;
 constexpr int kSliceMaxLen = 32768;       // logits of one slice (128 KB of shared memory as binary32)
 constexpr int kSlicedMaxRows = 16;        // rows per call on this path
 constexpr int kSlicedMinVocab = 16384;
-constexpr int kSliceBins = 2048;
-constexpr size_t kSlicedWsBytes = static_cast<size_t>(kSlicedMaxRows) * (64 * kVpHeader + 8 * kVpMaxCandidates);
+constexpr int kSlices = 64;               // slices per row
+constexpr int kSliceMaxCap = 128;         // candidates in one slice's record: twice the largest top_k
+constexpr size_t kSlicedWsBytes = static_cast<size_t>(kSlicedMaxRows) * kSlices * (kVpHeader + 8 * kSliceMaxCap);
 
 struct SliceDev {
   const void* logits; int dtype; int rows; int vocab; int64_t row_stride;
   int slices; int slice_len;                          // slice_len: a multiple of 8 (the last slices of a row may be short or empty)
   float temperature; int top_k; int cap; int need_mass;
-  int code_table;                                     // BF16 rows: the softmass per distinct code (a 128 KB table of counts behind the slice) instead of per logit
   const int32_t* history; int hist_len; int64_t hist_stride; float rho, pi;
   unsigned char* records; int64_t record_bytes;       // [slices][rows] records
   const uint32_t* state; int t_max, g;                // optional StepState: rows beyond t_this_step, and a finished state, are left alone
 };
 
-constexpr size_t kSliceTableBytes = 65536 * 2;      // one 16-bit counter per BF16 code
 __host__ __device__ inline size_t slice_marks_offset(int slice_len) { return static_cast<size_t>(slice_len) * 4; }
-__host__ __device__ inline size_t slice_table_offset(int slice_len) { return (slice_marks_offset(slice_len) + static_cast<size_t>(slice_len / 32 + 1) * 4 + 15) & ~static_cast<size_t>(15); }
-__host__ __device__ inline size_t slice_smem_bytes(int slice_len, bool table) { return slice_table_offset(slice_len) + (table ? kSliceTableBytes : 0); }
+__host__ __device__ inline size_t slice_smem_bytes(int slice_len) { return slice_marks_offset(slice_len) + static_cast<size_t>(slice_len / 32 + 1) * 4; }
 
 // A lower bound of the k-th largest of vals[0 .. n) (1 <= k <= n) that shares its upper 22 key bits: a radix descent of 11 + 11
 // bits on the monotone keys. (BF16 logits have no key bits below those; for binary32 logits the few values that share the upper
-// 22 bits with the k-th largest become candidates too, which the merge sorts out.)
+// 22 bits with the k-th largest pass the bound too, which the merge sorts out.)
 template <int B>
 __device__ uint32_t slice_kth_key(const float* vals, int n, uint32_t k, uint32_t* bins, uint64_t* scratch, uint32_t* pick) {
   const int tid = threadIdx.x;
@@ -55,23 +54,23 @@ __device__ uint32_t slice_kth_key(const float* vals, int n, uint32_t k, uint32_t
   for (int level = 0; level < 2; level++) {
     const int shift = level == 0 ? 21 : 10;
     const uint32_t hi_mask = level == 0 ? 0u : (0xFFFFFFFFu << (shift + 11));
-    for (int i = tid; i < kSliceBins; i += B) bins[i] = 0u;
+    for (int i = tid; i < kSelectBins; i += B) bins[i] = 0u;
     __syncthreads();
     for (int j = tid; j < n; j += B) {
       const uint32_t key = fkey(vals[j]);
-      if ((key & hi_mask) == prefix) atomicAdd(&bins[(key >> shift) & (kSliceBins - 1)], 1u);
+      if ((key & hi_mask) == prefix) atomicAdd(&bins[(key >> shift) & (kSelectBins - 1)], 1u);
     }
     __syncthreads();
-    constexpr int kPer = kSliceBins / B;                                  // thread t owns kPer bins, walked downwards from the top
+    constexpr int kPer = kSelectBins / B;                                 // thread t owns kPer bins, walked downwards from the top
     uint32_t cnt[kPer]; uint64_t sum = 0ull;
 #pragma unroll
-    for (int j = 0; j < kPer; j++) { cnt[j] = bins[kSliceBins - 1 - (kPer * tid + j)]; sum += cnt[j]; }
+    for (int j = 0; j < kPer; j++) { cnt[j] = bins[kSelectBins - 1 - (kPer * tid + j)]; sum += cnt[j]; }
     const uint64_t excl = block_exclusive_scan_u64(sum, scratch, nullptr);
     uint32_t run = above + static_cast<uint32_t>(excl);
     if (run < k && run + static_cast<uint32_t>(sum) >= k) {
 #pragma unroll
       for (int j = 0; j < kPer; j++) {
-        if (run < k && run + cnt[j] >= k) { pick[0] = static_cast<uint32_t>(kSliceBins - 1 - (kPer * tid + j)); pick[1] = run; }
+        if (run < k && run + cnt[j] >= k) { pick[0] = static_cast<uint32_t>(kSelectBins - 1 - (kPer * tid + j)); pick[1] = run; }
         run += cnt[j];
       }
     }
@@ -87,13 +86,15 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* vals = reinterpret_cast<float*>(smem_raw);
   uint32_t* marks = reinterpret_cast<uint32_t*>(smem_raw + slice_marks_offset(P.slice_len));
-  __shared__ uint32_t bins[kSliceBins];
+  __shared__ uint32_t bins[kSelectBins];
+  __shared__ float tmax[B];                                                 // every thread's own largest logit
   __shared__ uint64_t scratch[32];
   __shared__ uint32_t pick[2];
   __shared__ uint32_t s_n;
   // the merge may be made resident while the slices are at work; it waits for this grid
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x, slice = blockIdx.x, row = blockIdx.y;
+  if (tid == 0) s_n = 0u;
   if (P.state) {
     StepStateView st{const_cast<uint32_t*>(P.state), P.t_max, P.g};
     if (st.done() || row >= static_cast<int>(st.t_this_step())) return;
@@ -139,39 +140,21 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
   // ---- maximum, FP64 softmass relative to it
   uint64_t best = 0ull;
   for (int j = tid; j < n; j += B) { const uint64_t p = pack_best(vals[j], static_cast<uint32_t>(j)); best = p > best ? p : best; }
+  tmax[tid] = best ? best_value(best) : -INFINITY;
   best = block_max_u64(best, scratch);
   const float vmax = best_value(best);
   const double inv_t = 1.0 / static_cast<double>(P.temperature);
   double mass = 0.0;
-  if (P.need_mass && P.code_table) {
-    // A BF16 slice holds far fewer distinct values than logits: count the logits per code (16-bit counters, two per word), then one
-    // FP64 exponential per code that occurs instead of one per logit. Penalised logits are off the BF16 grid and are taken one by one.
-    uint32_t* table = reinterpret_cast<uint32_t*>(smem_raw + slice_table_offset(P.slice_len));
-    for (int i = tid; i < 32768; i += B) table[i] = 0u;
-    __syncthreads();
-    double m = 0.0;
-    for (int j = tid; j < n; j += B) {
-      if (pen_on && ((marks[j >> 5] >> (j & 31)) & 1u)) { m += softmass(vals[j], vmax, inv_t); continue; }
-      const uint32_t code = __float_as_uint(vals[j]) >> 16;
-      atomicAdd(&table[code >> 1], (code & 1u) ? 0x10000u : 1u);
-    }
-    __syncthreads();
-    for (int i = tid; i < 32768; i += B) {
-      const uint32_t w = table[i];
-      if (!w) continue;
-      if (w & 0xFFFFu) m += static_cast<double>(w & 0xFFFFu) * softmass(__uint_as_float(static_cast<uint32_t>(2 * i) << 16), vmax, inv_t);
-      if (w >> 16) m += static_cast<double>(w >> 16) * softmass(__uint_as_float(static_cast<uint32_t>(2 * i + 1) << 16), vmax, inv_t);
-    }
-    mass = block_sum_f64(m, scratch);
-  } else if (P.need_mass) {                                                // (only a top-p over the whole row asks for it)
+  if (P.need_mass) {                                                // (only a top-p over the whole row asks for it)
     double m = 0.0;
     for (int j = tid; j < n; j += B) m += softmass(vals[j], vmax, inv_t);
     mass = block_sum_f64(m, scratch);
   }
   // ---- the slice's k-th largest value and everything at or above it
-  if (tid == 0) s_n = 0u;
+  // The k-th largest of the threads' own maxima is a logit of the slice with at least k logits at or above it: a lower bound of
+  // the slice's k-th largest that lets through only a few logits more (two of the slice's largest seldom fall to one thread).
   const uint32_t k = static_cast<uint32_t>(min(P.top_k, n));
-  const float tau_local = fkey_inv(slice_kth_key<B>(vals, n, k, bins, scratch, pick));
+  const float tau_local = fkey_inv(slice_kth_key<B>(tmax, min(n, B), k, bins, scratch, pick));
   for (int j = tid; j < n; j += B) {
     if (vals[j] >= tau_local) {
       const uint32_t slot = atomicAdd(&s_n, 1u);
@@ -200,7 +183,7 @@ __global__ void __launch_bounds__(kVpMaxCandidates, 1) sliced_merge_kernel(VpMer
   N.seed = Q.seed; N.step = Q.step;
   const int row = blockIdx.x;
   if (row >= Q.rows) return;
-  if (!vocab_merge_row(N, row, s)) {                                       // overflowed records: the generic row algorithm, here and now
+  if (!vocab_merge_row(N, row, s)) {                                      // overflowed records: the generic row algorithm, here and now
     GenericSmem& g = *reinterpret_cast<GenericSmem*>(smem_raw);
     sample_row_generic(Q, row, g, reinterpret_cast<uint32_t*>(smem_raw + sizeof(GenericSmem)));
   }

@@ -18,7 +18,10 @@
 namespace lm {
 
 constexpr int kVpHeader = 32;          // float vmax, float pad, double mass, int32 n, uint32 status, 8 bytes pad
-constexpr int kVpMaxCandidates = 1024; // all shards together, per row
+constexpr int kVpMaxCandidates = 1024; // candidates of one row that can reach the sort (those at or above the row's top-k bound); the merge's threads
+constexpr int kVpMergeCap = 8192;      // candidates of one row that the merge takes in, all shards together
+constexpr int kVpPerThread = kVpMergeCap / kVpMaxCandidates;   // ... of which every thread of the merge holds so many
+constexpr int kSelectBins = 2048;
 constexpr uint32_t kStatusOverflow = 32u;
 constexpr int kVpMaxShards = 64;       // shards (or slices) of one row
 
@@ -100,6 +103,54 @@ __global__ void __launch_bounds__(kBlock, 1) vocab_local_kernel(VpLocalDev P) {
   }
 }
 
+// A lower bound (as a monotone key) of the k-th largest of the keys the block's threads hold in registers (keys[i] == 0: none; at
+// least k of them are set), all of them within [lo_key, hi_key]: the 2048 bins divide that span, so one level usually separates the
+// keys well. Returns the bound after one level if at most `limit` keys lie at or above it, else the bound after a second level
+// inside the k-th key's bin.
+// B threads, all of them call; bins: kSelectBins words, scratch: 32 words, pick: 3 words of shared memory.
+template <int B, int PER>
+__device__ uint32_t kth_key_bound_in_span(const uint32_t (&keys)[PER], uint32_t k, uint32_t lo_key, uint32_t hi_key, uint32_t limit,
+                                          uint32_t* bins, uint64_t* scratch, uint32_t* pick) {
+  const int tid = threadIdx.x;
+  const uint32_t span = hi_key - lo_key;
+  int shift = span ? max(0, 32 - __clz(span) - 11) : 0;
+  uint32_t base = lo_key, above = 0u, width = 0u;                         // width: keys under consideration lie in [base, base + width); 0: all
+#pragma unroll 1
+  for (int level = 0; level < 2; level++) {
+    for (int i = tid; i < kSelectBins; i += B) bins[i] = 0u;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+      const uint32_t key = keys[i];
+      if (key && key >= base) {
+        const uint32_t d = key - base;
+        if (width == 0u || d < width) atomicAdd(&bins[min(d >> shift, static_cast<uint32_t>(kSelectBins - 1))], 1u);
+      }
+    }
+    __syncthreads();
+    constexpr int kPer = kSelectBins / B;                  // thread t owns kPer bins, walked downwards from the top
+    uint32_t cnt[kPer]; uint64_t sum = 0ull;
+#pragma unroll
+    for (int j = 0; j < kPer; j++) { cnt[j] = bins[kSelectBins - 1 - (kPer * tid + j)]; sum += cnt[j]; }
+    const uint64_t excl = block_exclusive_scan_u64(sum, scratch, nullptr);
+    uint32_t run = above + static_cast<uint32_t>(excl);
+    if (run < k && run + static_cast<uint32_t>(sum) >= k) {
+#pragma unroll
+      for (int j = 0; j < kPer; j++) {
+        if (run < k && run + cnt[j] >= k) { pick[0] = static_cast<uint32_t>(kSelectBins - 1 - (kPer * tid + j)); pick[1] = run; pick[2] = run + cnt[j]; }
+        run += cnt[j];
+      }
+    }
+    __syncthreads();
+    base += pick[0] << shift; above = pick[1];
+    const uint32_t at_or_above = pick[2];
+    __syncthreads();
+    if (at_or_above <= limit || shift == 0) break;
+    width = 1u << shift; shift = max(0, shift - 11);
+  }
+  return base;
+}
+
 struct VpMergeDev {
   const unsigned char* records;      // [shards][rows] records, as the all-gather leaves them
   int shards; int rows; int cap; int64_t record_bytes;
@@ -117,13 +168,16 @@ struct VpMergeSmem {
   unsigned long long w[kVpMaxCandidates];      // the candidates as they arrive (before the sort); later their fixed-point weights
   uint64_t scratch[32];
   double warp_m[32];
-  // the record headers of the row, one per shard (at most kVpMaxCandidates / cap of them: cap >= 1)
+  // the record headers of the row, one per shard
   float h_vmax[kVpMaxShards]; double h_mass[kVpMaxShards]; int h_n[kVpMaxShards]; int h_base[kVpMaxShards];
   int n_total; int hit; int token; uint32_t status;
+  uint32_t n_sel; uint32_t pick[3]; uint32_t lo_key, hi_key;
+  double h_w[kVpMaxShards]; double z_total; float vmax;
 };
 
 // One row of the merge. Every thread of the block (kVpMaxCandidates threads) calls with the same arguments; returns false when
 // the row's records overflowed and the caller asked to hand such rows on (P.hand_on): nothing has been written then.
+// The host has checked shards <= kVpMaxShards and cap <= kVpPerThread * (kVpMaxCandidates / shards).
 __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float T = P.temperature ? P.temperature[row] : P.temperature_s;
@@ -136,8 +190,25 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
     if (tid == 0) { P.out_tokens[row] = -1; if (P.out_tau) P.out_tau[row] = -INFINITY; if (P.out_status) P.out_status[row] = kStatusBadParam; }
     return true;
   }
-  // ---- the record headers, all at once (one thread per shard), then the offsets of the shards in the concatenation
-  if (tid == 0) { s.hit = kVpMaxCandidates; s.token = -1; s.status = 0u; }
+  // ---- this thread's share of the candidates (a group of threads per shard, slot j of the record to thread j mod group size),
+  // asked for before the headers say how many slots are filled: every slot of a record is readable
+  const int per = kVpMaxCandidates / P.shards;
+  const int g = tid / per, r = tid - g * per;
+  float pv[kVpPerThread]; int32_t pi[kVpPerThread];
+#pragma unroll
+  for (int i = 0; i < kVpPerThread; i++) { pv[i] = 0.0f; pi[i] = 0; }
+  if (g < P.shards) {
+    const unsigned char* rec = P.records + (static_cast<int64_t>(g) * P.rows + row) * P.record_bytes;
+    const float* rv = reinterpret_cast<const float*>(rec + kVpHeader);
+    const int32_t* ri = reinterpret_cast<const int32_t*>(rec + kVpHeader + 4 * static_cast<size_t>(P.cap));
+#pragma unroll
+    for (int i = 0; i < kVpPerThread; i++) {
+      const int j = r + i * per;
+      if (j < P.cap) { pv[i] = rv[j]; pi[i] = ri[j]; }
+    }
+  }
+  // ---- the record headers (one thread per shard)
+  if (tid == 0) { s.hit = kVpMaxCandidates; s.token = -1; s.status = 0u; s.n_sel = 0u; s.lo_key = 0xFFFFFFFFu; s.hi_key = 0u; }
   __syncthreads();
   if (tid < P.shards) {
     const unsigned char* rec = P.records + (static_cast<int64_t>(tid) * P.rows + row) * P.record_bytes;
@@ -148,47 +219,66 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
     if (st) atomicOr(&s.status, st);
   }
   __syncthreads();
-  if (warp == 0) {                                                       // exclusive prefix of the counts over the shards (at most 64)
-    const int a = lane < P.shards ? s.h_n[lane] : 0, b = lane + 32 < P.shards ? s.h_n[lane + 32] : 0;
-    int ia = a, ib = b;
+  // ---- keys of the filled slots and their span; meanwhile one warp counts the candidates and another rebuilds the row's maximum
+  // and softmass from the shards' (the masses rescaled to the common maximum and summed in shard order, by one thread)
+  uint32_t keys[kVpPerThread];
+  {
+    const int cnt = g < P.shards ? s.h_n[g] : 0;
+    uint32_t kmin = 0xFFFFFFFFu, kmax = 0u;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { const int ta = __shfl_up_sync(kFull, ia, o), tb = __shfl_up_sync(kFull, ib, o); if (lane >= o) { ia += ta; ib += tb; } }
-    const int first = __shfl_sync(kFull, ia, 31);
-    if (lane < P.shards) s.h_base[lane] = ia - a;
-    if (lane + 32 < P.shards) s.h_base[lane + 32] = first + ib - b;
-    if (lane == 31) {
-      const int total = first + ib;
-      s.n_total = total < kVpMaxCandidates ? total : kVpMaxCandidates;
-      if (total > kVpMaxCandidates) s.status |= kStatusOverflow;
+    for (int i = 0; i < kVpPerThread; i++) {
+      const bool have = r + i * per < cnt;
+      keys[i] = have ? fkey(pv[i]) : 0u;
+      if (have) { kmin = min(kmin, keys[i]); kmax = max(kmax, keys[i]); }
+    }
+    kmin = warp_min_u32(kmin); kmax = warp_max_u32(kmax);
+    if (lane == 0 && kmax) { atomicMin(&s.lo_key, kmin); atomicMax(&s.hi_key, kmax); }
+  }
+  if (warp == 0) {
+    const int total = static_cast<int>(warp_sum_u32(static_cast<uint32_t>((lane < P.shards ? s.h_n[lane] : 0) + (lane + 32 < P.shards ? s.h_n[lane + 32] : 0))));
+    if (lane == 0) s.n_total = total;
+  } else if (warp == 1) {
+    float m = fmaxf(lane < P.shards ? s.h_vmax[lane] : -INFINITY, lane + 32 < P.shards ? s.h_vmax[lane + 32] : -INFINITY);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, o));
+    for (int q = lane; q < P.shards; q += 32) s.h_w[q] = s.h_mass[q] * exp((static_cast<double>(s.h_vmax[q]) - static_cast<double>(m)) * inv_t);
+    __syncwarp();
+    if (lane == 0) {
+      double z = 0.0;
+      for (int q = 0; q < P.shards; q++) z += s.h_w[q];
+      s.z_total = z; s.vmax = m;
     }
   }
   __syncthreads();
-  // ---- gather: candidate t of the concatenated shards (one thread per candidate)
-  unsigned long long key = 0ull;
-  {
-    int g = 0;
-    for (int q = 1; q < P.shards; q++) g += (s.h_base[q] <= tid) ? 1 : 0;   // the last shard that starts at or before t (bases ascend)
-    if (tid < s.n_total && tid - s.h_base[g] < s.h_n[g]) {
-      const unsigned char* rec = P.records + (static_cast<int64_t>(g) * P.rows + row) * P.record_bytes;
-      const int j = tid - s.h_base[g];
-      const float v = reinterpret_cast<const float*>(rec + kVpHeader)[j];
-      const int32_t i = reinterpret_cast<const int32_t*>(rec + kVpHeader + 4 * static_cast<size_t>(P.cap))[j];
-      key = (static_cast<unsigned long long>(fkey(v)) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(i));
+  const int n_all = s.n_total;
+  // ---- the candidates that can matter: those at or above a lower bound of the row's top_k-th largest value (the k-th largest of
+  // the candidates is the k-th largest of the row); only they are put in order
+  uint32_t bound = 0u;
+  if (top_k >= 1 && n_all > top_k)
+    bound = kth_key_bound_in_span<kVpMaxCandidates, kVpPerThread>(keys, static_cast<uint32_t>(top_k), s.lo_key, s.hi_key, static_cast<uint32_t>(max(2 * top_k, 128)),
+                                  reinterpret_cast<uint32_t*>(s.cum), s.scratch, s.pick);
+#pragma unroll
+  for (int i = 0; i < kVpPerThread; i++) {
+    if (keys[i] && keys[i] >= bound) {
+      const uint32_t slot = atomicAdd(&s.n_sel, 1u);
+      if (slot < static_cast<uint32_t>(kVpMaxCandidates)) s.w[slot] = (static_cast<unsigned long long>(keys[i]) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(pi[i]));
     }
   }
-  s.w[tid] = key;
   __syncthreads();
+  const uint32_t n_sel = s.n_sel;
   // ---- descending order by rank: the keys are distinct (they hold the index), so the number of larger keys is the position
-  {
-    const int n_all = s.n_total;
+  unsigned long long key = 0ull;
+  if (n_sel <= static_cast<uint32_t>(kVpMaxCandidates)) {
+    const int m = static_cast<int>(n_sel);
     int rank = 0;
-    if (tid < n_all) {
-      for (int t = 0; t < n_all; t++) rank += (s.w[t] > key) ? 1 : 0;
+    if (tid < m) {
+      key = s.w[tid];
+      for (int t = 0; t < m; t++) rank += (s.w[t] > key) ? 1 : 0;
       s.key[rank] = key;
     } else s.key[tid] = 0ull;
-  }
+  } else if (tid == 0) s.status |= kStatusOverflow;                        // more ties at the bound than the sort holds
   __syncthreads();
-  const int N = s.n_total;
+  const int N = static_cast<int>(n_sel < static_cast<uint32_t>(kVpMaxCandidates) ? n_sel : static_cast<uint32_t>(kVpMaxCandidates));
   const uint32_t status0 = s.status;
   if ((status0 & kStatusOverflow) && P.hand_on) return false;             // single GPU: the caller gives the row to the generic path
   if ((status0 & kStatusOverflow) || N == 0) {
@@ -200,14 +290,8 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
   const bool valid = tid < N;
   const float val = valid ? fkey_inv(static_cast<uint32_t>(key >> 32)) : -INFINITY;
   const int idx = valid ? static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(key)) : -1;
-  // ---- global maximum and mass (shards in order)
-  float vmax = -INFINITY;
-  for (int g = 0; g < P.shards; g++) vmax = fmaxf(vmax, s.h_vmax[g]);
-  if (tid < P.shards) s.cum[tid] = s.h_mass[tid] * exp((static_cast<double>(s.h_vmax[tid]) - static_cast<double>(vmax)) * inv_t);
-  __syncthreads();
-  double z_total = 0.0;
-  for (int g = 0; g < P.shards; g++) z_total += s.cum[g];                // (in shard order, whatever the number of threads)
-  __syncthreads();
+  const float vmax = s.vmax;
+  const double z_total = s.z_total;
   // ---- thresholds
   const bool has_k = top_k > 0, has_p = top_p > 0.0f && top_p < 1.0f, has_m = min_p > 0.0f;
   double tau64 = -INFINITY; bool have_tau = false;

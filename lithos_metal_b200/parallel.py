@@ -122,9 +122,9 @@ class VocabParallelSampler:
         if k_min < 1:
             raise ValueError("vocab-parallel sampling needs top_k >= 1 on every row")
         self.cap = self.backend.candidate_cap(k_max)
-        if self.cap * self.world > _lib.VOCAB_MAX_CANDIDATES:
-            raise ValueError(f"top_k {k_max} over {self.world} shards needs {self.cap * self.world} candidates per row; the limit is "
-                             f"{_lib.VOCAB_MAX_CANDIDATES}")
+        limit = (_lib.VOCAB_MAX_CANDIDATES // 1024) * (1024 // self.world) if self.world <= 64 else 0
+        if self.cap > limit:
+            raise ValueError(f"top_k {k_max} over {self.world} shards needs {self.cap} candidates per shard and row; the merge takes {limit}")
         self.shard_start, self.shard_width = shard_vocab(self.vocab, self.rank, self.world)
 
     def sample(self, local_logits: torch.Tensor, uniforms: Optional[torch.Tensor] = None, step: int = 0, row_offset: int = 0) -> SampleOutput:

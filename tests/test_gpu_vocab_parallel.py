@@ -49,6 +49,23 @@ def test_config5_equals_the_single_gpu_result(shards, draw):
         np.testing.assert_array_equal(tok[:6].cpu().numpy(), t_o)
 
 
+def test_a_large_top_k_over_eight_shards():
+    """top_k 300 over 8 shards: 8 x 368 candidate slots per row, of which the merge puts only those at or above the row's own
+    top-k bound in order."""
+    rng = np.random.default_rng(56)
+    rows, vocab = 16, 151936
+    codes = oracle.f32_to_bf16(rng.standard_normal((rows, vocab), dtype=np.float32) * np.float32(2.0))
+    x = bf16_tensor(codes)
+    u = torch.from_numpy(rng.random(rows).astype(np.float32)).cuda()
+    for kw in (dict(top_k=300, top_p=0.9), dict(top_k=128)):
+        p = lm.SamplingParams(temperature=0.8, seed=5, draw="inverse_cdf", **kw)
+        (tok, tau, status), _, _ = run_sharded(x, 8, p, u, step=2)
+        one = lm.sample(x, p, uniforms=u, step=2, return_tau=True)
+        assert int(status.max()) & 32 == 0
+        assert torch.equal(tau, one.tau)
+        assert torch.equal(tok, one.tokens)
+
+
 def test_records_ties_and_knob_variants():
     rng = np.random.default_rng(3)
     rows, vocab, shards = 9, 8192, 4
@@ -86,7 +103,7 @@ def test_invalid_vocab_parallel_requests():
     with pytest.raises(ValueError):
         parallel.VocabParallelSampler(lm.SamplingParams(temperature=0.8, top_k=0, top_p=0.9), 1024, rank=0, world=2)
     with pytest.raises(ValueError):
-        parallel.VocabParallelSampler(lm.SamplingParams(temperature=0.8, top_k=500), 1024, rank=0, world=8)      # 8 x 568 candidates
+        parallel.VocabParallelSampler(lm.SamplingParams(temperature=0.8, top_k=1000), 1024, rank=0, world=8)     # 8 x 1064 candidates
     with pytest.raises(ValueError):
         parallel.VocabParallelSampler(lm.SamplingParams(temperature=0.8, top_k=5, repetition_penalty=1.2), 1024, rank=0, world=2)
     s = parallel.VocabParallelSampler(lm.SamplingParams(temperature=0.8, top_k=5, draw="inverse_cdf"), 1024, rank=0, world=1)
