@@ -168,8 +168,6 @@ struct VpMergeSmem {
   unsigned long long w[kVpMaxCandidates];      // the candidates as they arrive (before the sort); later their fixed-point weights
   uint64_t scratch[32];
   double warp_m[32];
-  // the record headers of the row, one per shard
-  float h_vmax[kVpMaxShards]; double h_mass[kVpMaxShards]; int h_n[kVpMaxShards]; int h_base[kVpMaxShards];
   int n_total; int hit; int token; uint32_t status;
   uint32_t n_sel; uint32_t pick[3]; uint32_t lo_key, hi_key;
   double h_w[kVpMaxShards]; double z_total; float vmax;
@@ -190,40 +188,68 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
     if (tid == 0) { P.out_tokens[row] = -1; if (P.out_tau) P.out_tau[row] = -INFINITY; if (P.out_status) P.out_status[row] = kStatusBadParam; }
     return true;
   }
-  // ---- this thread's share of the candidates (a group of threads per shard, slot j of the record to thread j mod group size),
-  // asked for before the headers say how many slots are filled: every slot of a record is readable
+  // ---- One round of loads. This thread's share of the candidates (a group of threads per shard, slot j of the record to thread
+  // j mod group size), asked for before the shard's header says how many slots are filled (every slot of a record is readable);
+  // meanwhile warp 0 adds up the shards' counts and warp 1 rebuilds the row's maximum and softmass from the shards' (the masses
+  // rescaled to the common maximum and summed in shard order, by one thread).
+  if (tid == 0) { s.hit = kVpMaxCandidates; s.token = -1; s.status = 0u; s.n_sel = 0u; s.lo_key = 0xFFFFFFFFu; s.hi_key = 0u; }
   const int per = kVpMaxCandidates / P.shards;
   const int g = tid / per, r = tid - g * per;
   float pv[kVpPerThread]; int32_t pi[kVpPerThread];
 #pragma unroll
   for (int i = 0; i < kVpPerThread; i++) { pv[i] = 0.0f; pi[i] = 0; }
+  int cnt = 0;
   if (g < P.shards) {
     const unsigned char* rec = P.records + (static_cast<int64_t>(g) * P.rows + row) * P.record_bytes;
     const float* rv = reinterpret_cast<const float*>(rec + kVpHeader);
     const int32_t* ri = reinterpret_cast<const int32_t*>(rec + kVpHeader + 4 * static_cast<size_t>(P.cap));
+    cnt = *reinterpret_cast<const int32_t*>(rec + 16);
 #pragma unroll
     for (int i = 0; i < kVpPerThread; i++) {
       const int j = r + i * per;
       if (j < P.cap) { pv[i] = rv[j]; pi[i] = ri[j]; }
     }
   }
-  // ---- the record headers (one thread per shard)
-  if (tid == 0) { s.hit = kVpMaxCandidates; s.token = -1; s.status = 0u; s.n_sel = 0u; s.lo_key = 0xFFFFFFFFu; s.hi_key = 0u; }
-  __syncthreads();
-  if (tid < P.shards) {
-    const unsigned char* rec = P.records + (static_cast<int64_t>(tid) * P.rows + row) * P.record_bytes;
-    s.h_vmax[tid] = *reinterpret_cast<const float*>(rec);
-    s.h_mass[tid] = *reinterpret_cast<const double*>(rec + 8);
-    s.h_n[tid] = *reinterpret_cast<const int32_t*>(rec + 16);
-    const uint32_t st = *reinterpret_cast<const uint32_t*>(rec + 20);
-    if (st) atomicOr(&s.status, st);
+  __syncthreads();                                                        // (the shared fields above are set)
+  if (warp == 0) {
+    int n2 = 0; uint32_t st = 0u;
+    for (int q = lane; q < P.shards; q += 32) {
+      const unsigned char* rec = P.records + (static_cast<int64_t>(q) * P.rows + row) * P.record_bytes;
+      n2 += *reinterpret_cast<const int32_t*>(rec + 16);
+      st |= *reinterpret_cast<const uint32_t*>(rec + 20);
+    }
+    const int total = static_cast<int>(warp_sum_u32(static_cast<uint32_t>(n2)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) st |= __shfl_xor_sync(kFull, st, o);
+    if (lane == 0) { s.n_total = total; if (st) atomicOr(&s.status, st); }
+  } else if (warp == 1) {
+    float hv[2]; double hm[2];
+    float m = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+      const int q = lane + 32 * e;
+      hv[e] = -INFINITY; hm[e] = 0.0;
+      if (q < P.shards) {
+        const unsigned char* rec = P.records + (static_cast<int64_t>(q) * P.rows + row) * P.record_bytes;
+        hv[e] = *reinterpret_cast<const float*>(rec); hm[e] = *reinterpret_cast<const double*>(rec + 8);
+      }
+      m = fmaxf(m, hv[e]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, o));
+#pragma unroll
+    for (int e = 0; e < 2; e++)
+      if (lane + 32 * e < P.shards) s.h_w[lane + 32 * e] = hm[e] * exp((static_cast<double>(hv[e]) - static_cast<double>(m)) * inv_t);
+    __syncwarp();
+    if (lane == 0) {
+      double z = 0.0;
+      for (int q = 0; q < P.shards; q++) z += s.h_w[q];
+      s.z_total = z; s.vmax = m;
+    }
   }
-  __syncthreads();
-  // ---- keys of the filled slots and their span; meanwhile one warp counts the candidates and another rebuilds the row's maximum
-  // and softmass from the shards' (the masses rescaled to the common maximum and summed in shard order, by one thread)
+  // ---- keys of the filled slots and their span
   uint32_t keys[kVpPerThread];
   {
-    const int cnt = g < P.shards ? s.h_n[g] : 0;
     uint32_t kmin = 0xFFFFFFFFu, kmax = 0u;
 #pragma unroll
     for (int i = 0; i < kVpPerThread; i++) {
@@ -233,21 +259,6 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
     }
     kmin = warp_min_u32(kmin); kmax = warp_max_u32(kmax);
     if (lane == 0 && kmax) { atomicMin(&s.lo_key, kmin); atomicMax(&s.hi_key, kmax); }
-  }
-  if (warp == 0) {
-    const int total = static_cast<int>(warp_sum_u32(static_cast<uint32_t>((lane < P.shards ? s.h_n[lane] : 0) + (lane + 32 < P.shards ? s.h_n[lane + 32] : 0))));
-    if (lane == 0) s.n_total = total;
-  } else if (warp == 1) {
-    float m = fmaxf(lane < P.shards ? s.h_vmax[lane] : -INFINITY, lane + 32 < P.shards ? s.h_vmax[lane + 32] : -INFINITY);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, o));
-    for (int q = lane; q < P.shards; q += 32) s.h_w[q] = s.h_mass[q] * exp((static_cast<double>(s.h_vmax[q]) - static_cast<double>(m)) * inv_t);
-    __syncwarp();
-    if (lane == 0) {
-      double z = 0.0;
-      for (int q = 0; q < P.shards; q++) z += s.h_w[q];
-      s.z_total = z; s.vmax = m;
-    }
   }
   __syncthreads();
   const int n_all = s.n_total;
