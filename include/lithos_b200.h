@@ -322,7 +322,8 @@ LM_API int lm_draft_q(const lm_draft_q_args* args);
  * Requirements: top_k >= 1 on every row (the kept set must lie inside the top-k candidates), cap =
  * lm_vocab_candidate_cap(largest top_k), at most 64 shards, cap <= (LM_VOCAB_MAX_CANDIDATES / 1024) * (1024 / shards) (integer division: shards * cap <=
  * LM_VOCAB_MAX_CANDIDATES when shards is a power of two), no penalties. A row whose ties overflow
- * a record reports LM_STATUS_OVERFLOW and token -1; a row whose per-row temperature is not positive reports status bit 16 and
+ * a record (or, beyond 1024 logits tied at the top-k boundary, the merge) reports LM_STATUS_OVERFLOW and token -1; a row with a NaN or a
+ * maximum that is not finite reports LM_STATUS_NAN and token -1; a row whose per-row temperature is not positive reports status bit 16 and
  * token -1. One exception to "bit for bit": the FP64 softmass is summed per shard and then over the sorted candidates, another
  * order than on one GPU, so a top-p boundary within 1e-12 (relative) of the target may fall on the other side; such rows carry
  * LM_STATUS_TOPP_EDGE here as they do there.

@@ -90,11 +90,11 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
   __shared__ float tmax[B];                                                 // every thread's own largest logit
   __shared__ uint64_t scratch[32];
   __shared__ uint32_t pick[2];
-  __shared__ uint32_t s_n;
+  __shared__ uint32_t s_n, s_flags, s_ninf;
   // the merge may be made resident while the slices are at work; it waits for this grid
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x, slice = blockIdx.x, row = blockIdx.y;
-  if (tid == 0) s_n = 0u;
+  if (tid == 0) { s_n = 0u; s_flags = 0u; s_ninf = 0xFFFFFFFFu; }
   if (P.state) {
     StepStateView st{const_cast<uint32_t*>(P.state), P.t_max, P.g};
     if (st.done() || row >= static_cast<int>(st.t_this_step())) return;
@@ -139,13 +139,19 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
   }
   // ---- maximum, FP64 softmass relative to it
   uint64_t best = 0ull;
-  for (int j = tid; j < n; j += B) { const uint64_t p = pack_best(vals[j], static_cast<uint32_t>(j)); best = p > best ? p : best; }
+  bool nan = false;
+  for (int j = tid; j < n; j += B) {
+    const float v = vals[j];
+    nan |= v != v;
+    const uint64_t p = pack_best(v, static_cast<uint32_t>(j)); best = p > best ? p : best;
+  }
+  if (nan) s_flags = LM_STATUS_NAN;                                         // (the row goes to the generic algorithm, which defines what a NaN does)
   tmax[tid] = best ? best_value(best) : -INFINITY;
   best = block_max_u64(best, scratch);
   const float vmax = best_value(best);
   const double inv_t = 1.0 / static_cast<double>(P.temperature);
   double mass = 0.0;
-  if (P.need_mass) {                                                // (only a top-p over the whole row asks for it)
+  if (P.need_mass && vmax > -INFINITY) {                                   // (only a top-p over the whole row asks for it)
     double m = 0.0;
     for (int j = tid; j < n; j += B) m += softmass(vals[j], vmax, inv_t);
     mass = block_sum_f64(m, scratch);
@@ -154,12 +160,32 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
   // The k-th largest of the threads' own maxima is a logit of the slice with at least k logits at or above it: a lower bound of
   // the slice's k-th largest that lets through only a few logits more (two of the slice's largest seldom fall to one thread).
   const uint32_t k = static_cast<uint32_t>(min(P.top_k, n));
-  const float tau_local = fkey_inv(slice_kth_key<B>(tmax, min(n, B), k, bins, scratch, pick));
-  for (int j = tid; j < n; j += B) {
-    if (vals[j] >= tau_local) {
-      const uint32_t slot = atomicAdd(&s_n, 1u);
-      if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = vals[j]; out_idx[slot] = lo + j; }
+  const uint32_t bound = slice_kth_key<B>(tmax, min(n, B), k, bins, scratch, pick);
+  // Fewer than k threads with a logit above -inf (a masked vocabulary): every logit above -inf is a candidate, and one -inf logit
+  // (the first) stands for the rest, so that a row with fewer than top_k logits above -inf still finds its k-th largest at -inf.
+  constexpr uint32_t kNinfKey = 0x007FFFFFu;                               // fkey(-inf)
+  const bool open = bound <= kNinfKey;
+  if (!open) {
+    const float tau_local = fkey_inv(bound);
+    for (int j = tid; j < n; j += B) {
+      if (vals[j] >= tau_local) {
+        const uint32_t slot = atomicAdd(&s_n, 1u);
+        if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = vals[j]; out_idx[slot] = lo + j; }
+      }
     }
+  } else {
+    for (int j = tid; j < n; j += B) {
+      const float v = vals[j];
+      if (v > -INFINITY) {
+        const uint32_t slot = atomicAdd(&s_n, 1u);
+        if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = v; out_idx[slot] = lo + j; }
+      } else if (v == -INFINITY) atomicMin(&s_ninf, static_cast<uint32_t>(j));
+    }
+  }
+  __syncthreads();
+  if (open && tid == 0 && s_ninf != 0xFFFFFFFFu) {
+    const uint32_t slot = s_n++;
+    if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = -INFINITY; out_idx[slot] = lo + static_cast<int>(s_ninf); }
   }
   __syncthreads();
   if (tid == 0) {
@@ -168,7 +194,7 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
     *reinterpret_cast<float*>(rec + 4) = 0.0f;
     *reinterpret_cast<double*>(rec + 8) = mass;
     *reinterpret_cast<int32_t*>(rec + 16) = static_cast<int32_t>(cnt < static_cast<uint32_t>(P.cap) ? cnt : static_cast<uint32_t>(P.cap));
-    *reinterpret_cast<uint32_t*>(rec + 20) = (cnt > static_cast<uint32_t>(P.cap) ? kStatusOverflow : 0u) | ((vmax != vmax) ? LM_STATUS_NAN : 0u);
+    *reinterpret_cast<uint32_t*>(rec + 20) = (cnt > static_cast<uint32_t>(P.cap) ? kStatusOverflow : 0u) | s_flags;
   }
 }
 

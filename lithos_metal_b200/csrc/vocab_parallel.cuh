@@ -34,7 +34,7 @@ struct VpLocalDev {
 __global__ void __launch_bounds__(kBlock, 1) vocab_local_kernel(VpLocalDev P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   GenericSmem& s = *reinterpret_cast<GenericSmem*>(smem_raw);
-  __shared__ uint32_t s_n;
+  __shared__ uint32_t s_n, s_ninf;
   const int tid = threadIdx.x;
   for (int row = blockIdx.x; row < P.rows; row += gridDim.x) {
     const int V = P.vocab_local;
@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(kBlock, 1) vocab_local_kernel(VpLocalDev P) {
     rv.row = static_cast<const char*>(P.logits) + static_cast<size_t>(row) * static_cast<size_t>(P.row_stride) * (P.dtype == LM_DTYPE_BF16 ? 2 : 4);
     rv.aligned = (reinterpret_cast<uintptr_t>(rv.row) & 15u) == 0;
     const int n_chunks = (V + kChunk - 1) / kChunk;
-    if (tid == 0) s_n = 0u;
+    if (tid == 0) { s_n = 0u; s_ninf = 0xFFFFFFFFu; }
     // the shard's maximum
     uint64_t best = 0ull;
     for (int c = tid; c < n_chunks; c += kBlock) {
@@ -62,11 +62,13 @@ __global__ void __launch_bounds__(kBlock, 1) vocab_local_kernel(VpLocalDev P) {
     // its FP64 softmass relative to that maximum
     const double inv_t = 1.0 / static_cast<double>(T);
     double m = 0.0;
-    for (int c = tid; c < n_chunks; c += kBlock) {
-      float z[kChunk];
-      const int n = load_chunk(rv, c, z);
+    if (vmax > -INFINITY) {                                                // (a shard of nothing but -inf has no mass)
+      for (int c = tid; c < n_chunks; c += kBlock) {
+        float z[kChunk];
+        const int n = load_chunk(rv, c, z);
 #pragma unroll
-      for (int e = 0; e < kChunk; e++) if (e < n) m += softmass(z[e], vmax, inv_t);
+        for (int e = 0; e < kChunk; e++) if (e < n) m += softmass(z[e], vmax, inv_t);
+      }
     }
     const double mass = block_sum_f64(m, s.scratch);
     // its k-th largest value: 4 x 8-bit radix select on the monotone key, ties kept
@@ -80,15 +82,25 @@ __global__ void __launch_bounds__(kBlock, 1) vocab_local_kernel(VpLocalDev P) {
       prefix |= static_cast<uint32_t>(select_bin<false>(s.cnt, nullptr, static_cast<uint32_t>(top_k), 0.0, s)) << (24 - 8 * level);
     }
     const float tau_local = fkey_inv(prefix);
-    // every logit at or above it, with its global index
+    // every logit at or above it, with its global index. A shard with fewer than top_k logits above -inf (a masked vocabulary)
+    // hands over those and ONE -inf logit (its first), which stands for the rest: they weigh nothing, and a row with fewer than
+    // top_k logits above -inf still finds its k-th largest at -inf.
+    const bool open = !(tau_local > -INFINITY);
     for (int c = tid; c < n_chunks; c += kBlock) {
       float z[kChunk];
       const int n = load_chunk(rv, c, z);
 #pragma unroll
-      for (int e = 0; e < kChunk; e++) if (e < n && z[e] >= tau_local) {
-        const uint32_t slot = atomicAdd(&s_n, 1u);
-        if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = z[e]; out_idx[slot] = P.shard_start + c * kChunk + e; }
+      for (int e = 0; e < kChunk; e++) if (e < n) {
+        if (open ? z[e] > -INFINITY : z[e] >= tau_local) {
+          const uint32_t slot = atomicAdd(&s_n, 1u);
+          if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = z[e]; out_idx[slot] = P.shard_start + c * kChunk + e; }
+        } else if (open && z[e] == -INFINITY) atomicMin(&s_ninf, static_cast<uint32_t>(c * kChunk + e));
       }
+    }
+    __syncthreads();
+    if (open && tid == 0 && s_ninf != 0xFFFFFFFFu) {
+      const uint32_t slot = s_n++;
+      if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = -INFINITY; out_idx[slot] = P.shard_start + static_cast<int>(s_ninf); }
     }
     __syncthreads();
     if (tid == 0) {
@@ -262,6 +274,14 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
   }
   __syncthreads();
   const int n_all = s.n_total;
+  // A NaN in the row or a maximum that is not finite: the generic row algorithm defines what happens (single GPU); not supported
+  // across GPUs, where such a row reports LM_STATUS_NAN and token -1.
+  if ((s.status & LM_STATUS_NAN) || !(fabsf(s.vmax) < INFINITY)) {
+    if (P.hand_on) return false;
+    if (tid == 0) { P.out_tokens[row] = -1; if (P.out_tau) P.out_tau[row] = -INFINITY; if (P.out_status) P.out_status[row] = s.status | LM_STATUS_NAN; }
+    __syncthreads();
+    return true;
+  }
   // ---- the candidates that can matter: those at or above a lower bound of the row's top_k-th largest value (the k-th largest of
   // the candidates is the k-th largest of the row); only they are put in order
   uint32_t bound = 0u;

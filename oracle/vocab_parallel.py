@@ -33,10 +33,13 @@ def local_record(z_shard: np.ndarray, shard_start: int, *, temperature: float, t
     """One row of one shard -> its record."""
     z = np.asarray(z_shard, dtype=np.float32)
     vmax = np.float32(z.max())
-    mass = float(np.exp((z.astype(np.float64) - float(vmax)) / float(np.float32(temperature))).sum())
+    mass = float(np.exp((z.astype(np.float64) - float(vmax)) / float(np.float32(temperature))).sum()) if vmax > -np.inf else 0.0
     k = min(top_k, z.size)
     tau_local = np.partition(z, z.size - k)[z.size - k]
-    idx = np.nonzero(z >= tau_local)[0]
+    if tau_local > -np.inf:
+        idx = np.nonzero(z >= tau_local)[0]
+    else:                                                                  # fewer than top_k logits above -inf: those, and the first -inf logit for the rest
+        idx = np.concatenate([np.nonzero(z > -np.inf)[0], np.nonzero(z == -np.inf)[0][:1]])
     status = 0
     if idx.size > cap:
         status, idx = STATUS_OVERFLOW, idx[:cap]

@@ -68,6 +68,50 @@ def test_vocabulary_sizes_and_the_limits_of_the_path(vocab, top_k, sliced):
     _check(x, host, draw="inverse_cdf", temperature=1.1, top_k=top_k, top_p=0.9, expect_sliced=sliced)
 
 
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_a_masked_vocabulary_stays_on_the_sliced_path(dtype):
+    """-inf logits (constrained decoding): slices with fewer than top_k logits above -inf hand over what they have and one -inf logit."""
+    rng = np.random.default_rng(31)
+    rows, vocab = 4, 151936
+    z = (rng.standard_normal((rows, vocab)) * 2).astype(np.float32)
+    z[0, rng.random(vocab) < 0.9] = -np.inf                                   # nine in ten masked, everywhere
+    keep = np.zeros(vocab, bool); keep[1000:1040] = True
+    z[1, ~keep] = -np.inf                                                     # 40 logits left: fewer than a top_k of 50
+    z[2, :50000] = -np.inf; z[2, 60000:] = -np.inf                            # whole slices masked
+    z[3, 5] = -np.inf                                                         # one masked logit
+    if dtype == "bf16":
+        host = oracle.f32_to_bf16(z)
+        x = torch.from_numpy(host.view(np.int16)).cuda().view(torch.bfloat16)
+    else:
+        host, x = z, torch.from_numpy(z).cuda()
+    for draw in ("inverse_cdf", "gumbel"):
+        for top_k, top_p in ((20, 0.9), (50, 0.9), (50, 0.0), (1, 0.0)):
+            _check(x, host, draw=draw, temperature=0.8, top_k=top_k, top_p=top_p)
+
+
+def test_rows_with_a_nan_or_an_infinite_maximum_go_to_the_generic_kernel():
+    x, host = _rows(3, 151936, 8, "f32")
+    x[0, 77] = float("nan"); x[1, 123456] = float("inf")
+    u = torch.rand(3, device="cuda")
+    for kw in (dict(top_k=20, top_p=0.9), dict(top_k=8)):
+        p = lm.SamplingParams(temperature=0.9, draw="inverse_cdf", **kw)
+        pe = lm.SamplingParams(temperature=0.9, draw="inverse_cdf", exact_only=True, **kw)
+        r = lm.sample(x, p, uniforms=u, return_tau=True, return_status=True)
+        e = lm.sample(x, pe, uniforms=u, return_tau=True, return_status=True)
+        st = r.status.cpu().numpy()
+        assert st[0] & GENERIC and st[1] & GENERIC and st[2] & SLICED, st
+        assert r.tokens.cpu().tolist() == e.tokens.cpu().tolist()
+        assert r.tau.cpu().numpy().tobytes() == e.tau.cpu().numpy().tobytes()
+        assert (st[:2] & ~(GENERIC | SLICED)).tolist() == (e.status.cpu().numpy()[:2] & ~(GENERIC | SLICED)).tolist()
+
+
+def test_more_equal_logits_at_the_top_k_boundary_than_the_merge_sorts():
+    x, host = _rows(2, 151936, 9, "f32", spikes=0)
+    x[0, ::50] = 9.0; host[0, ::50] = 9.0                                     # 3039 equal maxima, about 47 per slice: no record overflows (cap 128), the merge does
+    r, st = _check(x, host, draw="inverse_cdf", temperature=1.0, top_k=64, expect_sliced=False)
+    assert st[0] & GENERIC and st[1] & SLICED, st
+
+
 def test_more_ties_than_a_record_holds_go_to_the_generic_kernel():
     x, host = _rows(2, 151936, 6, "f32", spikes=0)
     x[0, 100:300] = 9.0; host[0, 100:300] = 9.0                               # 200 equal maxima inside one slice, top_k 20

@@ -66,6 +66,32 @@ def test_a_large_top_k_over_eight_shards():
         assert torch.equal(tok, one.tokens)
 
 
+def test_a_masked_vocabulary_over_four_shards():
+    """-inf logits: a shard with fewer than top_k logits above -inf hands over those and one -inf logit; the result is the oracle's."""
+    rng = np.random.default_rng(57)
+    rows, vocab = 3, 65536
+    z = (rng.standard_normal((rows, vocab)) * 2).astype(np.float32)
+    keep = np.zeros(vocab, bool); keep[20000:20030] = True
+    z[0, ~keep] = -np.inf                                                  # 30 logits left, all in one shard
+    z[1, rng.random(vocab) < 0.95] = -np.inf
+    z[2, :40000] = -np.inf                                                 # two shards masked out, a third partly
+    x = torch.from_numpy(z).cuda()
+    u = rng.random(rows).astype(np.float32)
+    for kw in (dict(top_k=50, top_p=0.9), dict(top_k=20)):
+        p = lm.SamplingParams(temperature=0.8, seed=5, draw="inverse_cdf", **kw)
+        (tok, tau, status), gathered, cap = run_sharded(x, 4, p, torch.from_numpy(u).cuda())
+        t_o, tau_o, _ = oracle.sample_batch(z, temperature=0.8, top_k=kw["top_k"], top_p=kw.get("top_p", 0.0), draw="inverse_cdf", uniforms=u, seed=5, n_threads=3)
+        assert int(status.max()) & 32 == 0
+        np.testing.assert_array_equal(tau.cpu().numpy(), tau_o)
+        np.testing.assert_array_equal(tok.cpu().numpy(), t_o)
+        g = gathered.cpu().numpy()                                         # and the records are the CPU model's
+        for s in range(4):
+            lo, width = parallel.shard_vocab(vocab, s, 4)
+            a = vp.unpack_record(g[s, 0].tobytes(), cap)
+            b = vp.unpack_record(vp.local_record(z[0, lo:lo + width], lo, temperature=0.8, top_k=kw["top_k"], cap=cap), cap)
+            assert a[2] == b[2] and sorted(a[5].tolist()) == sorted(b[5].tolist())
+
+
 def test_records_ties_and_knob_variants():
     rng = np.random.default_rng(3)
     rows, vocab, shards = 9, 8192, 4
