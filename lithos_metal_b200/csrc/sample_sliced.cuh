@@ -187,7 +187,6 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
     const uint32_t slot = s_n++;
     if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = -INFINITY; out_idx[slot] = lo + static_cast<int>(s_ninf); }
   }
-  __syncthreads();
   if (tid == 0) {
     const uint32_t cnt = s_n;
     *reinterpret_cast<float*>(rec) = vmax;
