@@ -318,6 +318,7 @@ int lm_sample(const lm_sample_args* a) {
       M.flags = a->flags; M.draw = a->draw; M.uniforms = a->uniforms; M.seed = a->seed; M.step = a->step; M.row_offset = a->row_offset;
       M.out_tokens = a->out_tokens; M.out_tau = a->out_tau; M.out_status = a->out_status; M.out_vmax = a->out_vmax; M.out_mass = reinterpret_cast<unsigned long long*>(a->out_mass);
       M.hand_on = 1; M.path_status = LM_STATUS_SLICED_PATH;
+      M.mass_band = S.need_mass ? slice_mass_band(S.slice_len, big ? kSliceBlockBig : kSliceBlockSmall) : 0.0;
       // the merge is launched with programmatic stream serialization: its blocks are resident and waiting when the slices complete
       cudaLaunchAttribute attr[1];
       attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -524,7 +525,7 @@ int lm_vocab_merge(const lm_vocab_args* a) {
   P.top_p = a->top_p; P.top_p_s = a->top_p_s; P.min_p = a->min_p; P.min_p_s = a->min_p_s;
   P.flags = a->flags; P.draw = a->draw; P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
   P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_status = a->out_status; P.out_vmax = nullptr; P.out_mass = nullptr;
-  P.hand_on = 0; P.path_status = 0u;
+  P.hand_on = 0; P.path_status = 0u; P.mass_band = 0.0;
   int sms = 0;
   const int rc = sm_count(&sms);
   if (rc != LM_OK) return rc;

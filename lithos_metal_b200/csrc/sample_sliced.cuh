@@ -18,6 +18,7 @@
 #pragma once
 #include "common.cuh"
 #include "sample_generic.cuh"
+#include "sample_topk.cuh"
 #include "vocab_parallel.cuh"
 
 namespace lm {
@@ -39,6 +40,19 @@ struct SliceDev {
   unsigned char* records; int64_t record_bytes;       // [slices][rows] records
   const uint32_t* state; int t_max, g;                // optional StepState: rows beyond t_this_step, and a finished state, are left alone
 };
+
+// How far (relative) a slice's FP32 softmass can be from the exact one, first order, worst case, with a quarter added (u = 2^-24):
+//   - c2a = fl32(c): term j is off by a factor 2^(x_j delta), |delta| <= u, x_j = (z_j - vmax) c <= 0; weighted by the terms that is
+//     ln2 u E_w|x| <= u ln(slice_len) (E_w[-x ln2] = H - ln Z <= ln n: H the entropy of the slice's softmax, Z >= 1 relative to its maximum);
+//   - the FMA rounds its result: half an ulp of |x| < 32 is at most 2^-20, a factor 1 + 6.6e-7 on the term (the terms with |x| >= 32
+//     weigh less than n 2^-32 altogether);
+//   - ex2.approx.ftz.f32: 2 ulp = 4 u;
+//   - a thread adds ceil(slice_len / threads) terms one after the other in FP32, then the threads meet in FP64.
+// The slices' masses are scaled to the row's maximum and added in FP64; the bound holds for the sum as for each of them.
+inline double slice_mass_band(int slice_len, int threads) {
+  const double u = 5.9604644775390625e-8;
+  return 1.25 * (u * (log(static_cast<double>(slice_len)) + 4.0 + static_cast<double>((slice_len + threads - 1) / threads + 1)) + 6.6e-7);
+}
 
 __host__ __device__ inline size_t slice_marks_offset(int slice_len) { return static_cast<size_t>(slice_len) * 4; }
 __host__ __device__ inline size_t slice_smem_bytes(int slice_len) { return slice_marks_offset(slice_len) + static_cast<size_t>(slice_len / 32 + 1) * 4; }
@@ -152,9 +166,14 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
   const double inv_t = 1.0 / static_cast<double>(P.temperature);
   double mass = 0.0;
   if (P.need_mass && vmax > -INFINITY) {                                   // (only a top-p over the whole row asks for it)
-    double m = 0.0;
-    for (int j = tid; j < n; j += B) m += softmass(vals[j], vmax, inv_t);
-    mass = block_sum_f64(m, scratch);
+    // In FP32, one ex2 per logit: sum_j 2^(z_j c2a + nb) with c2a = fl32(log2(e) / T) and nb = fl32(-vmax c2a); the common factor
+    // that nb's rounding leaves is taken out exactly afterwards, so the result approximates sum_j 2^((z_j - vmax) c2a). The merge
+    // knows how far that can be from the exact mass (slice_mass_band) and hands a row on when its top-p boundary is closer than that.
+    const float c2a = static_cast<float>(1.4426950408889634 * inv_t);
+    const float nb = __fmul_rn(-vmax, c2a);
+    float acc = 0.0f;
+    for (int j = tid; j < n; j += B) acc += ex2_approx(__fmaf_rn(vals[j], c2a, nb));
+    mass = block_sum_f64(static_cast<double>(acc), scratch) * exp2(-(static_cast<double>(vmax) * static_cast<double>(c2a) + static_cast<double>(nb)));
   }
   // ---- the slice's k-th largest value and everything at or above it
   // The k-th largest of the threads' own maxima is a logit of the slice with at least k logits at or above it: a lower bound of

@@ -172,6 +172,7 @@ struct VpMergeDev {
   int32_t* out_tokens; float* out_tau; uint32_t* out_status; float* out_vmax; unsigned long long* out_mass;
   uint32_t path_status;              // ORed into every row's status (0 in the vocab-parallel mode)
   int hand_on;                       // single-GPU use (sample_sliced.cuh): a row whose records overflowed is left to the caller
+  double mass_band;                  // how far (relative) the records' masses may be from the exact ones (0: they are FP64 sums); with hand_on only
 };
 
 struct VpMergeSmem {
@@ -353,7 +354,10 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
     const double target = static_cast<double>(top_p) * total;
     const bool run_end = valid && (tid == N - 1 || (s.key[tid + 1] >> 32) != (key >> 32));
     if (run_end && mi >= target) atomicMin(&s.hit, tid);
-    __syncthreads();
+    // approximate masses: a boundary above the top-k threshold that lies within the band of the target is not decided here
+    const bool amb = P.hand_on && P.mass_band > 0.0 && !((P.flags & LM_FLAG_TOPP_IN_TOPK) && has_k) && run_end && val > tau_k &&
+                     fabs(mi - target) <= P.mass_band * total;
+    if (__syncthreads_or(amb)) return false;
     if (s.hit < kVpMaxCandidates) {
       const float tau_p = fkey_inv(static_cast<uint32_t>(s.key[s.hit] >> 32));
       if (!have_tau || static_cast<double>(tau_p) > tau64) tau64 = tau_p;

@@ -105,6 +105,18 @@ def test_rows_with_a_nan_or_an_infinite_maximum_go_to_the_generic_kernel():
         assert (st[:2] & ~(GENERIC | SLICED)).tolist() == (e.status.cpu().numpy()[:2] & ~(GENERIC | SLICED)).tolist()
 
 
+def test_a_top_p_boundary_too_close_for_the_fp32_softmass_goes_to_the_generic_kernel():
+    """The slices sum the softmass in FP32; a cumulative mass that meets top_p * total to within that sum's error band is decided by the
+    exact kernel instead. Row 0: weights 1 and 1/3 (and nothing else that counts), top_p = 3/4."""
+    vocab = 151936
+    z = np.full((2, vocab), -40.0, np.float32)
+    z[0, 1234] = 10.0; z[0, 99999] = np.float32(10.0 - np.log(3.0))
+    z[1] = (np.random.default_rng(12).standard_normal(vocab) * 2).astype(np.float32)
+    x = torch.from_numpy(z).cuda()
+    r, st = _check(x, z, draw="inverse_cdf", temperature=1.0, top_k=20, top_p=0.75, expect_sliced=False)
+    assert st[0] & GENERIC and st[1] & SLICED, st
+
+
 def test_more_equal_logits_at_the_top_k_boundary_than_the_merge_sorts():
     x, host = _rows(2, 151936, 9, "f32", spikes=0)
     x[0, ::50] = 9.0; host[0, ::50] = 9.0                                     # 3039 equal maxima, about 47 per slice: no record overflows (cap 128), the merge does
