@@ -255,6 +255,14 @@ int lm_argmax_static(const void* logits, int32_t dtype, int64_t rows, int64_t vo
   return lm_argmax(logits, dtype, rows, vocab, row_stride, out_tokens, ws, lm_workspace_bytes(rows, vocab), st);
 }
 
+// The merge's thread geometry and the FP64 reciprocal of a scalar temperature, once per call on the host.
+static void merge_geometry(VpMergeDev& M) {
+  M.per = kVpMaxCandidates / M.shards;
+  M.per_log2 = -1;
+  for (int b = 0; b <= 10; b++) if ((1 << b) == M.per) M.per_log2 = b;
+  M.inv_t_s = M.temperature == nullptr ? 1.0 / static_cast<double>(M.temperature_s) : 0.0;
+}
+
 int lm_sample(const lm_sample_args* a) {
   if (!a || a->struct_size != sizeof(lm_sample_args)) return LM_E_INVALID;
   if (a->rows < 0 || a->vocab < 0 || (a->dtype != LM_DTYPE_BF16 && a->dtype != LM_DTYPE_F32)) return LM_E_INVALID;
@@ -318,6 +326,7 @@ int lm_sample(const lm_sample_args* a) {
       M.flags = a->flags; M.draw = a->draw; M.uniforms = a->uniforms; M.seed = a->seed; M.step = a->step; M.row_offset = a->row_offset;
       M.out_tokens = a->out_tokens; M.out_tau = a->out_tau; M.out_status = a->out_status; M.out_vmax = a->out_vmax; M.out_mass = reinterpret_cast<unsigned long long*>(a->out_mass);
       M.hand_on = 1; M.path_status = LM_STATUS_SLICED_PATH;
+      merge_geometry(M);
       M.mass_band = S.need_mass ? slice_mass_band(S.slice_len, big ? kSliceBlockBig : kSliceBlockSmall) : 0.0;
       // the merge is launched with programmatic stream serialization: its blocks are resident and waiting when the slices complete
       cudaLaunchAttribute attr[1];
@@ -526,6 +535,7 @@ int lm_vocab_merge(const lm_vocab_args* a) {
   P.flags = a->flags; P.draw = a->draw; P.uniforms = a->uniforms; P.seed = a->seed; P.step = a->step; P.row_offset = a->row_offset;
   P.out_tokens = a->out_tokens; P.out_tau = a->out_tau; P.out_status = a->out_status; P.out_vmax = nullptr; P.out_mass = nullptr;
   P.hand_on = 0; P.path_status = 0u; P.mass_band = 0.0;
+  merge_geometry(P);
   int sms = 0;
   const int rc = sm_count(&sms);
   if (rc != LM_OK) return rc;

@@ -172,6 +172,8 @@ struct VpMergeDev {
   int32_t* out_tokens; float* out_tau; uint32_t* out_status; float* out_vmax; unsigned long long* out_mass;
   uint32_t path_status;              // ORed into every row's status (0 in the vocab-parallel mode)
   int hand_on;                       // single-GPU use (sample_sliced.cuh): a row whose records overflowed is left to the caller
+  double inv_t_s;                    // 1 / temperature_s in FP64 (the host's division: one per call instead of one per thread)
+  int per, per_log2;                 // kVpMaxCandidates / shards, and its base-2 logarithm if it is a power of two (else -1)
   double mass_band;                  // how far (relative) the records' masses may be from the exact ones (0: they are FP64 sums); with hand_on only
 };
 
@@ -195,7 +197,7 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
   int top_k = P.top_k ? P.top_k[row] : P.top_k_s;
   const float top_p = P.top_p ? P.top_p[row] : P.top_p_s;
   const float min_p = P.min_p ? P.min_p[row] : P.min_p_s;
-  const double T64 = static_cast<double>(T), inv_t = 1.0 / T64;
+  const double T64 = static_cast<double>(T), inv_t = P.temperature ? 1.0 / T64 : P.inv_t_s;
   uint32_t edge = 0u;
   if (!(T > 0.0f)) {                                                     // a per-row temperature the host could not check: no token
     if (tid == 0) { P.out_tokens[row] = -1; if (P.out_tau) P.out_tau[row] = -INFINITY; if (P.out_status) P.out_status[row] = kStatusBadParam; }
@@ -206,8 +208,8 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
   // meanwhile warp 0 adds up the shards' counts and warp 1 rebuilds the row's maximum and softmass from the shards' (the masses
   // rescaled to the common maximum and summed in shard order, by one thread).
   if (tid == 0) { s.hit = kVpMaxCandidates; s.token = -1; s.status = 0u; s.n_sel = 0u; s.lo_key = 0xFFFFFFFFu; s.hi_key = 0u; }
-  const int per = kVpMaxCandidates / P.shards;
-  const int g = tid / per, r = tid - g * per;
+  const int per = P.per;
+  const int g = P.per_log2 >= 0 ? tid >> P.per_log2 : tid / per, r = tid - g * per;
   float pv[kVpPerThread]; int32_t pi[kVpPerThread];
 #pragma unroll
   for (int i = 0; i < kVpPerThread; i++) { pv[i] = 0.0f; pi[i] = 0; }
