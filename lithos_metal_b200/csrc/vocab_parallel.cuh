@@ -184,9 +184,96 @@ struct VpMergeSmem {
   uint64_t scratch[32];
   double warp_m[32];
   int n_total; int hit; int token; uint32_t status;
-  uint32_t n_sel; uint32_t pick[3]; uint32_t lo_key, hi_key;
+  uint32_t n_sel; uint32_t pick[3]; uint32_t lo_key, hi_key; int amb;
   double h_w[kVpMaxShards]; double z_total; float vmax;
 };
+
+// The thresholds and the draw of a row whose ordered candidates fit one warp (N <= 32, the usual case for a top_k up to ~30): warp
+// 0 alone, lane i holding candidate i, with shuffles and votes where the block-wide code below needs barriers. The same arithmetic in
+// the same order (the block-wide prefix sums reduce to warp 0's). Sets s.amb instead of writing when the row has to be handed on.
+__device__ void merge_tail_one_warp(const VpMergeDev& P, int row, VpMergeSmem& s, int N, float T, int top_k, float top_p, float min_p, double inv_t,
+                                    uint32_t status0) {
+  const int lane = threadIdx.x & 31;
+  const unsigned long long key = s.key[lane];
+  const bool valid = lane < N;
+  const float val = valid ? fkey_inv(static_cast<uint32_t>(key >> 32)) : -INFINITY;
+  const int idx = valid ? static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(key)) : -1;
+  const float vmax = s.vmax;
+  const double T64 = static_cast<double>(T);
+  const bool has_k = top_k > 0, has_p = top_p > 0.0f && top_p < 1.0f, has_m = min_p > 0.0f;
+  double tau64 = -INFINITY; bool have_tau = false;
+  float tau_k = -INFINITY;
+  uint32_t edge = 0u;
+  if (has_k) {
+    tau_k = __shfl_sync(kFull, val, (top_k < N ? top_k : N) - 1);
+    tau64 = tau_k; have_tau = true;
+  }
+  if (has_p) {
+    double mi = valid ? softmass(val, vmax, inv_t) : 0.0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const double t = __shfl_up_sync(kFull, mi, o); if (lane >= o) mi += t; }
+    const bool in_topk = (P.flags & LM_FLAG_TOPP_IN_TOPK) && has_k;
+    double total = s.z_total;
+    if (in_topk) total = __shfl_sync(kFull, mi, 31 - __clz(static_cast<int>(__ballot_sync(kFull, valid && val >= tau_k))));   // the top-k set is a prefix
+    const double target = static_cast<double>(top_p) * total;
+    const uint32_t next_hi = __shfl_down_sync(kFull, static_cast<uint32_t>(key >> 32), 1);
+    const bool run_end = valid && (lane == N - 1 || next_hi != static_cast<uint32_t>(key >> 32));
+    const uint32_t hits = __ballot_sync(kFull, run_end && mi >= target);
+    const bool amb = P.hand_on && P.mass_band > 0.0 && !in_topk && run_end && val > tau_k && fabs(mi - target) <= P.mass_band * total;
+    if (__any_sync(kFull, amb)) { if (lane == 0) s.amb = 1; return; }
+    if (hits) {
+      const float tau_p = __shfl_sync(kFull, val, __ffs(static_cast<int>(hits)) - 1);
+      if (!have_tau || static_cast<double>(tau_p) > tau64) tau64 = tau_p;
+      have_tau = true;
+    }
+    if (__any_sync(kFull, run_end && fabs(mi - target) <= 1e-12 * total)) edge = LM_STATUS_TOPP_EDGE;
+  }
+  if (has_m) {
+    const double tau_m = static_cast<double>(vmax) + T64 * log(static_cast<double>(min_p));
+    if (!have_tau || tau_m > tau64) tau64 = tau_m;
+    have_tau = true;
+  }
+  const float tau = have_tau ? __double2float_rn(tau64) : -INFINITY;
+  const bool kept = valid && val >= tau;
+  uint32_t status = status0 | edge | P.path_status;
+  uint64_t kept_weight = 0ull;
+  int token = -1;
+  if (P.draw == LM_DRAW_INVERSE_CDF) {
+    const uint64_t w = kept ? weight_q40(val, vmax, exp2_scale(T)) : 0ull;
+    uint64_t incl = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const uint64_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
+    const uint64_t total = __shfl_sync(kFull, incl, 31), before = incl - w;
+    kept_weight = total;
+    bool mine = false;
+    if (total > 0ull && w) {
+      const uint64_t target = cdf_target(P.uniforms ? P.uniforms[row] : 0.0f, total);
+      mine = before <= target && target < before + w;
+    }
+    const uint32_t who = __ballot_sync(kFull, mine);
+    if (who) token = __shfl_sync(kFull, idx, __ffs(static_cast<int>(who)) - 1);
+  } else {
+    const float inv_t32 = __double2float_rn(1.0 / T64);
+    uint64_t mine = 0ull; float kf = -INFINITY;
+    if (kept) {
+      kf = __fadd_rn(__fmul_rn(val, inv_t32), gumbel(P.seed, P.step, static_cast<uint32_t>(P.row_offset + row), static_cast<uint32_t>(idx)));
+      mine = pack_best(kf, static_cast<uint32_t>(idx));
+    }
+    const uint64_t win = warp_max_u64(mine);
+    if (win) {
+      if (__any_sync(kFull, kept && mine != win && kf >= best_value(win) - 4e-6f)) status |= LM_STATUS_NEAR_TIE;
+      token = static_cast<int>(best_index(win));
+    }
+    if (P.out_mass) kept_weight = warp_sum_u64(kept ? weight_q40(val, vmax, exp2_scale(T)) : 0ull);
+  }
+  if (lane == 0) {
+    P.out_tokens[row] = token;
+    if (P.out_tau) P.out_tau[row] = tau;
+    if (P.out_status) P.out_status[row] = status;
+    if (P.out_vmax) P.out_vmax[row] = vmax;
+    if (P.out_mass) P.out_mass[row] = kept_weight;
+  }
+}
 
 // One row of the merge. Every thread of the block (kVpMaxCandidates threads) calls with the same arguments; returns false when
 // the row's records overflowed and the caller asked to hand such rows on (P.hand_on): nothing has been written then.
@@ -207,7 +294,7 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
   // j mod group size), asked for before the shard's header says how many slots are filled (every slot of a record is readable);
   // meanwhile warp 0 adds up the shards' counts and warp 1 rebuilds the row's maximum and softmass from the shards' (the masses
   // rescaled to the common maximum and summed in shard order, by one thread).
-  if (tid == 0) { s.hit = kVpMaxCandidates; s.token = -1; s.status = 0u; s.n_sel = 0u; s.lo_key = 0xFFFFFFFFu; s.hi_key = 0u; }
+  if (tid == 0) { s.hit = kVpMaxCandidates; s.token = -1; s.status = 0u; s.n_sel = 0u; s.lo_key = 0xFFFFFFFFu; s.hi_key = 0u; s.amb = 0; }
   const int per = P.per;
   const int g = P.per_log2 >= 0 ? tid >> P.per_log2 : tid / per, r = tid - g * per;
   float pv[kVpPerThread]; int32_t pi[kVpPerThread];
@@ -319,6 +406,11 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
     if (tid == 0) { P.out_tokens[row] = -1; if (P.out_tau) P.out_tau[row] = -INFINITY; if (P.out_status) P.out_status[row] = status0; }
     __syncthreads();
     return true;
+  }
+  if (N <= 32) {                                                          // the candidates in order fit one warp: no more barriers but the last
+    if (warp == 0) merge_tail_one_warp(P, row, s, N, T, top_k, top_p, min_p, inv_t, status0);
+    __syncthreads();
+    return s.amb == 0;
   }
   key = s.key[tid];
   const bool valid = tid < N;
