@@ -188,16 +188,29 @@ struct VpMergeSmem {
   double h_w[kVpMaxShards]; double z_total; float vmax;
 };
 
-// The thresholds and the draw of a row whose ordered candidates fit one warp (N <= 32, the usual case for a top_k up to ~30): warp
-// 0 alone, lane i holding candidate i, with shuffles and votes where the block-wide code below needs barriers. The same arithmetic in
-// the same order (the block-wide prefix sums reduce to warp 0's). Sets s.amb instead of writing when the row has to be handed on.
+// The thresholds and the draw of a row with at most 64 ordered candidates (the usual case for a top_k up to ~60): warp 0 alone, lane
+// i holding candidate i (E = 1: up to 32) or candidates i and 32 + i (E = 2), with shuffles and votes where the block-wide code below needs barriers. The same arithmetic in
+// the same order (the block-wide prefix sums reduce to those of warps 0 and 1). Sets s.amb instead of writing when the row has to be
+// handed on.
+template <int E>
 __device__ void merge_tail_one_warp(const VpMergeDev& P, int row, VpMergeSmem& s, int N, float T, int top_k, float top_p, float min_p, double inv_t,
                                     uint32_t status0) {
   const int lane = threadIdx.x & 31;
-  const unsigned long long key = s.key[lane];
-  const bool valid = lane < N;
-  const float val = valid ? fkey_inv(static_cast<uint32_t>(key >> 32)) : -INFINITY;
-  const int idx = valid ? static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(key)) : -1;
+  unsigned long long key[E]; bool valid[E]; float val[E]; int idx[E]; uint32_t hi[E];
+#pragma unroll
+  for (int e = 0; e < E; e++) {
+    key[e] = s.key[lane + 32 * e];
+    valid[e] = lane + 32 * e < N;
+    hi[e] = static_cast<uint32_t>(key[e] >> 32);
+    val[e] = valid[e] ? fkey_inv(hi[e]) : -INFINITY;
+    idx[e] = valid[e] ? static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(key[e])) : -1;
+  }
+  // the value at position i of the order (every lane asks for the same i)
+  auto at_f = [&](const float (&v)[E], int i) { const float a = __shfl_sync(kFull, v[0], i & 31), b = __shfl_sync(kFull, v[E - 1], i & 31); return i < 32 ? a : b; };
+  auto at_d = [&](const double (&v)[E], int i) { const double a = __shfl_sync(kFull, v[0], i & 31), b = __shfl_sync(kFull, v[E - 1], i & 31); return i < 32 ? a : b; };
+  auto at_i = [&](const int (&v)[E], int i) { const int a = __shfl_sync(kFull, v[0], i & 31), b = __shfl_sync(kFull, v[E - 1], i & 31); return i < 32 ? a : b; };
+  // position of the first candidate for which `f` holds (-1: none)
+  auto first_of = [&](const bool (&f)[E]) { const uint32_t m0 = __ballot_sync(kFull, f[0]), m1 = E > 1 ? __ballot_sync(kFull, f[E - 1]) : 0u; return m0 ? __ffs(static_cast<int>(m0)) - 1 : (m1 ? 31 + __ffs(static_cast<int>(m1)) : -1); };
   const float vmax = s.vmax;
   const double T64 = static_cast<double>(T);
   const bool has_k = top_k > 0, has_p = top_p > 0.0f && top_p < 1.0f, has_m = min_p > 0.0f;
@@ -205,28 +218,50 @@ __device__ void merge_tail_one_warp(const VpMergeDev& P, int row, VpMergeSmem& s
   float tau_k = -INFINITY;
   uint32_t edge = 0u;
   if (has_k) {
-    tau_k = __shfl_sync(kFull, val, (top_k < N ? top_k : N) - 1);
+    tau_k = at_f(val, (top_k < N ? top_k : N) - 1);
     tau64 = tau_k; have_tau = true;
   }
   if (has_p) {
-    double mi = valid ? softmass(val, vmax, inv_t) : 0.0;
+    double mi[E];
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { const double t = __shfl_up_sync(kFull, mi, o); if (lane >= o) mi += t; }
+    for (int e = 0; e < E; e++) {
+      mi[e] = valid[e] ? softmass(val[e], vmax, inv_t) : 0.0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const double t = __shfl_up_sync(kFull, mi[e], o); if (lane >= o) mi[e] += t; }
+    }
+    if (E > 1) mi[E - 1] += __shfl_sync(kFull, mi[0], 31);
     const bool in_topk = (P.flags & LM_FLAG_TOPP_IN_TOPK) && has_k;
     double total = s.z_total;
-    if (in_topk) total = __shfl_sync(kFull, mi, 31 - __clz(static_cast<int>(__ballot_sync(kFull, valid && val >= tau_k))));   // the top-k set is a prefix
+    if (in_topk) {                                                        // the top-k set is a prefix of the order
+      int n_topk = 0;
+#pragma unroll
+      for (int e = 0; e < E; e++) n_topk += __popc(__ballot_sync(kFull, valid[e] && val[e] >= tau_k));
+      total = at_d(mi, n_topk - 1);
+    }
     const double target = static_cast<double>(top_p) * total;
-    const uint32_t next_hi = __shfl_down_sync(kFull, static_cast<uint32_t>(key >> 32), 1);
-    const bool run_end = valid && (lane == N - 1 || next_hi != static_cast<uint32_t>(key >> 32));
-    const uint32_t hits = __ballot_sync(kFull, run_end && mi >= target);
-    const bool amb = P.hand_on && P.mass_band > 0.0 && !in_topk && run_end && val > tau_k && fabs(mi - target) <= P.mass_band * total;
+    bool run_end[E], reached[E];
+#pragma unroll
+    for (int e = 0; e < E; e++) {                                         // the candidate after this one: the next lane's, or the first of the second set
+      const uint32_t down = __shfl_down_sync(kFull, hi[e], 1), wrap = __shfl_sync(kFull, hi[E - 1], 0);
+      const bool last = lane + 32 * e == N - 1 || (lane == 31 && e == E - 1);
+      run_end[e] = valid[e] && (last || (lane == 31 ? wrap : down) != hi[e]);
+      reached[e] = run_end[e] && mi[e] >= target;
+    }
+    const int hit = first_of(reached);
+    bool amb = false;
+#pragma unroll
+    for (int e = 0; e < E; e++)
+      amb |= P.hand_on && P.mass_band > 0.0 && !in_topk && run_end[e] && val[e] > tau_k && fabs(mi[e] - target) <= P.mass_band * total;
     if (__any_sync(kFull, amb)) { if (lane == 0) s.amb = 1; return; }
-    if (hits) {
-      const float tau_p = __shfl_sync(kFull, val, __ffs(static_cast<int>(hits)) - 1);
+    if (hit >= 0) {
+      const float tau_p = at_f(val, hit);
       if (!have_tau || static_cast<double>(tau_p) > tau64) tau64 = tau_p;
       have_tau = true;
     }
-    if (__any_sync(kFull, run_end && fabs(mi - target) <= 1e-12 * total)) edge = LM_STATUS_TOPP_EDGE;
+    bool near = false;
+#pragma unroll
+    for (int e = 0; e < E; e++) near |= run_end[e] && fabs(mi[e] - target) <= 1e-12 * total;
+    if (__any_sync(kFull, near)) edge = LM_STATUS_TOPP_EDGE;
   }
   if (has_m) {
     const double tau_m = static_cast<double>(vmax) + T64 * log(static_cast<double>(min_p));
@@ -234,37 +269,58 @@ __device__ void merge_tail_one_warp(const VpMergeDev& P, int row, VpMergeSmem& s
     have_tau = true;
   }
   const float tau = have_tau ? __double2float_rn(tau64) : -INFINITY;
-  const bool kept = valid && val >= tau;
+  bool kept[E];
+#pragma unroll
+  for (int e = 0; e < E; e++) kept[e] = valid[e] && val[e] >= tau;
   uint32_t status = status0 | edge | P.path_status;
   uint64_t kept_weight = 0ull;
   int token = -1;
   if (P.draw == LM_DRAW_INVERSE_CDF) {
-    const uint64_t w = kept ? weight_q40(val, vmax, exp2_scale(T)) : 0ull;
-    uint64_t incl = w;
+    const float c2 = exp2_scale(T);
+    uint64_t w[E], incl[E];
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { const uint64_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
-    const uint64_t total = __shfl_sync(kFull, incl, 31), before = incl - w;
-    kept_weight = total;
-    bool mine = false;
-    if (total > 0ull && w) {
-      const uint64_t target = cdf_target(P.uniforms ? P.uniforms[row] : 0.0f, total);
-      mine = before <= target && target < before + w;
+    for (int e = 0; e < E; e++) {
+      w[e] = kept[e] ? weight_q40(val[e], vmax, c2) : 0ull;
+      incl[e] = w[e];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const uint64_t t = __shfl_up_sync(kFull, incl[e], o); if (lane >= o) incl[e] += t; }
     }
-    const uint32_t who = __ballot_sync(kFull, mine);
-    if (who) token = __shfl_sync(kFull, idx, __ffs(static_cast<int>(who)) - 1);
+    if (E > 1) incl[E - 1] += __shfl_sync(kFull, incl[0], 31);
+    const uint64_t total = __shfl_sync(kFull, incl[E - 1], 31);
+    kept_weight = total;
+    const uint64_t target = cdf_target(P.uniforms ? P.uniforms[row] : 0.0f, total);
+    bool mine[E];
+#pragma unroll
+    for (int e = 0; e < E; e++) { const uint64_t before = incl[e] - w[e]; mine[e] = total > 0ull && w[e] && before <= target && target < before + w[e]; }
+    const int who = first_of(mine);
+    if (who >= 0) token = at_i(idx, who);
   } else {
     const float inv_t32 = __double2float_rn(1.0 / T64);
-    uint64_t mine = 0ull; float kf = -INFINITY;
-    if (kept) {
-      kf = __fadd_rn(__fmul_rn(val, inv_t32), gumbel(P.seed, P.step, static_cast<uint32_t>(P.row_offset + row), static_cast<uint32_t>(idx)));
-      mine = pack_best(kf, static_cast<uint32_t>(idx));
+    uint64_t mine[E], top = 0ull; float kf[E];
+#pragma unroll
+    for (int e = 0; e < E; e++) { mine[e] = 0ull; kf[e] = -INFINITY; }
+#pragma unroll
+    for (int e = 0; e < E; e++) if (kept[e]) {
+      kf[e] = __fadd_rn(__fmul_rn(val[e], inv_t32), gumbel(P.seed, P.step, static_cast<uint32_t>(P.row_offset + row), static_cast<uint32_t>(idx[e])));
+      mine[e] = pack_best(kf[e], static_cast<uint32_t>(idx[e]));
+      top = mine[e] > top ? mine[e] : top;
     }
-    const uint64_t win = warp_max_u64(mine);
+    const uint64_t win = warp_max_u64(top);
     if (win) {
-      if (__any_sync(kFull, kept && mine != win && kf >= best_value(win) - 4e-6f)) status |= LM_STATUS_NEAR_TIE;
+      const float edge_kf = best_value(win) - 4e-6f;
+      bool tie = false;
+#pragma unroll
+      for (int e = 0; e < E; e++) tie |= kept[e] && mine[e] != win && kf[e] >= edge_kf;
+      if (__any_sync(kFull, tie)) status |= LM_STATUS_NEAR_TIE;
       token = static_cast<int>(best_index(win));
     }
-    if (P.out_mass) kept_weight = warp_sum_u64(kept ? weight_q40(val, vmax, exp2_scale(T)) : 0ull);
+    if (P.out_mass) {
+      const float c2 = exp2_scale(T);
+      uint64_t ws = 0ull;
+#pragma unroll
+      for (int e = 0; e < E; e++) ws += kept[e] ? weight_q40(val[e], vmax, c2) : 0ull;
+      kept_weight = warp_sum_u64(ws);
+    }
   }
   if (lane == 0) {
     P.out_tokens[row] = token;
@@ -407,8 +463,8 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
     __syncthreads();
     return true;
   }
-  if (N <= 32) {                                                          // the candidates in order fit one warp: no more barriers but the last
-    if (warp == 0) merge_tail_one_warp(P, row, s, N, T, top_k, top_p, min_p, inv_t, status0);
+  if (N <= 64) {                                                          // few candidates in order: one warp does the rest, no more barriers but the last
+    if (warp == 0) { if (N <= 32) merge_tail_one_warp<1>(P, row, s, N, T, top_k, top_p, min_p, inv_t, status0); else merge_tail_one_warp<2>(P, row, s, N, T, top_k, top_p, min_p, inv_t, status0); }
     __syncthreads();
     return s.amb == 0;
   }
