@@ -136,6 +136,8 @@ def test_other_knobs_keep_the_row_per_block_kernels():
     _check(x, host, draw="gumbel", temperature=0.8, top_k=40, top_p=0.9, exact_only=True, expect_sliced=False)
     _check(x, host, draw="gumbel", temperature=0.8, top_k=0, top_p=0.9, expect_sliced=False)
     _check(x, host, draw="gumbel", temperature=0.8, top_k=40, top_p=0.9, topp_in_topk=True)
+    _check(x, host, draw="inverse_cdf", temperature=0.8, top_k=12, top_p=0.9, topp_in_topk=True)
+    _check(x, host, draw="inverse_cdf", temperature=0.8, top_k=64, top_p=0.9, min_p=0.02, topp_in_topk=True)
     k = torch.full((4,), 40, dtype=torch.int32)
     p = lm.SamplingParams(temperature=0.8, top_k=k, seed=1)
     assert not np.any(lm.sample(x, p, return_status=True).status.cpu().numpy() & SLICED)
