@@ -102,7 +102,7 @@ static int sm_count(int* out) {
 
 // Kernels that need more than 48 KB of dynamic shared memory must be told so once per device (the attribute belongs to the
 // device's copy of the function); remembered per device and kernel, raised when a call needs more.
-enum KernelSlot { kSlotFast, kSlotTopk, kSlotGeneric, kSlotVocabLocal, kSlotVerify, kSlotVerifyStats, kSlotDraftQ, kSlotTileFinish, kSlotSlice, kSlotSliceSmall, kSlotSlicedMerge, kSlotCount };
+enum KernelSlot { kSlotFast, kSlotTopk, kSlotGeneric, kSlotVocabLocal, kSlotVerify, kSlotVerifyStats, kSlotDraftQ, kSlotTileFinish, kSlotSlice, kSlotSliceSmall, kSlotSliceTiny, kSlotSlicedMerge, kSlotCount };
 
 static int ensure_dynamic_smem(KernelSlot slot, const void* func, size_t bytes) {
   if (bytes <= 48 * 1024) return LM_OK;
@@ -310,13 +310,19 @@ int lm_sample(const lm_sample_args* a) {
       const size_t gsmem = sizeof(GenericSmem) + (pen ? static_cast<size_t>((a->vocab + 31) / 32) * 4 : 0) + 16;   // a row handed on to the generic algorithm
       S.need_mass = (a->top_p != nullptr || (a->top_p_s > 0.0f && a->top_p_s < 1.0f)) && !(a->flags & LM_FLAG_TOPP_IN_TOPK);
       const size_t slice_smem = slice_smem_bytes(S.slice_len);
-      const bool big = static_cast<long long>(S.slices) * P.rows <= 2LL * sms;   // few slices in all: wide blocks, for the latency
-      rc = big ? ensure_dynamic_smem(kSlotSlice, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockBig>), slice_smem)
-               : ensure_dynamic_smem(kSlotSliceSmall, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockSmall>), slice_smem);
+      // threads per slice: 1024 when every slice has an SM to itself (the latency of one or two rows), else 128 (or 256 for a large
+      // top_k, whose bound needs more threads' maxima to stay close): with several slices per SM the launch is bound by instruction
+      // issue, and the per-warp work of the selection is most of a slice's instructions
+      const int threads = static_cast<long long>(S.slices) * P.rows <= sms ? kSliceBlockBig : (a->top_k_s <= kSliceTinyMaxK ? kSliceBlockTiny : kSliceBlockSmall);
+      const void* slice_fn = threads == kSliceBlockBig ? reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockBig>)
+                           : threads == kSliceBlockSmall ? reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockSmall>)
+                                                         : reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockTiny>);
+      rc = ensure_dynamic_smem(threads == kSliceBlockBig ? kSlotSlice : (threads == kSliceBlockSmall ? kSlotSliceSmall : kSlotSliceTiny), slice_fn, slice_smem);
       if (rc == LM_OK) rc = ensure_dynamic_smem(kSlotSlicedMerge, reinterpret_cast<const void*>(sliced_merge_kernel), gsmem);
       if (rc != LM_OK) return rc;
-      if (big) slice_local_kernel<kSliceBlockBig><<<dim3(S.slices, P.rows), kSliceBlockBig, slice_smem, st>>>(S);
-      else slice_local_kernel<kSliceBlockSmall><<<dim3(S.slices, P.rows), kSliceBlockSmall, slice_smem, st>>>(S);
+      if (threads == kSliceBlockBig) slice_local_kernel<kSliceBlockBig><<<dim3(S.slices, P.rows), kSliceBlockBig, slice_smem, st>>>(S);
+      else if (threads == kSliceBlockSmall) slice_local_kernel<kSliceBlockSmall><<<dim3(S.slices, P.rows), kSliceBlockSmall, slice_smem, st>>>(S);
+      else slice_local_kernel<kSliceBlockTiny><<<dim3(S.slices, P.rows), kSliceBlockTiny, slice_smem, st>>>(S);
       cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return cuda_fail(e);
       VpMergeDev M;
@@ -327,7 +333,7 @@ int lm_sample(const lm_sample_args* a) {
       M.out_tokens = a->out_tokens; M.out_tau = a->out_tau; M.out_status = a->out_status; M.out_vmax = a->out_vmax; M.out_mass = reinterpret_cast<unsigned long long*>(a->out_mass);
       M.hand_on = 1; M.path_status = LM_STATUS_SLICED_PATH;
       merge_geometry(M);
-      M.mass_band = S.need_mass ? slice_mass_band(S.slice_len, big ? kSliceBlockBig : kSliceBlockSmall) : 0.0;
+      M.mass_band = S.need_mass ? slice_mass_band(S.slice_len, threads) : 0.0;
       // the merge is launched with programmatic stream serialization: its blocks are resident and waiting when the slices complete
       cudaLaunchAttribute attr[1];
       attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

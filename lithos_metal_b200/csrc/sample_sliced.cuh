@@ -23,8 +23,10 @@
 
 namespace lm {
 
-constexpr int kSliceBlockBig = 1024;     // threads per slice when the call has few slices (latency), else kSliceBlockSmall
-constexpr int kSliceBlockSmall = 256;
+constexpr int kSliceBlockBig = 1024;     // threads per slice when every slice has an SM to itself (latency), else kSliceBlockSmall
+constexpr int kSliceBlockSmall = 256;   // ... and kSliceBlockTiny when the top_k leaves its record room (fewer warps: fewer instructions per slice)
+constexpr int kSliceBlockTiny = 128;
+constexpr int kSliceTinyMaxK = 50;        // largest top_k for kSliceBlockTiny: about 62 of a record's 100 slots filled then
 constexpr int kSliceMaxLen = 32768;       // logits of one slice (128 KB of shared memory as binary32)
 constexpr int kSlicedMaxRows = 16;        // rows per call on this path
 constexpr int kSlicedMinVocab = 16384;
