@@ -28,7 +28,7 @@ constexpr int kSliceBlockSmall = 256;   // ... and kSliceBlockTiny when the top_
 constexpr int kSliceBlockTiny = 128;
 constexpr int kSliceTinyMaxK = 50;        // largest top_k for kSliceBlockTiny: about 62 of a record's 100 slots filled then
 constexpr int kSliceMaxLen = 32768;       // logits of one slice (128 KB of shared memory as binary32)
-constexpr int kSlicedMaxRows = 16;        // rows per call on this path
+constexpr int kSlicedMaxRows = 32;        // rows per call on this path
 constexpr int kSlicedMinVocab = 16384;
 constexpr int kSlices = 64;               // slices per row
 constexpr int kSliceMaxCap = 128;         // candidates in one slice's record: twice the largest top_k

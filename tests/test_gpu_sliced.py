@@ -44,7 +44,7 @@ def _check(x, host, *, draw, temperature, top_k, top_p=0.0, min_p=0.0, history=N
 
 
 @pytest.mark.parametrize("draw", ["inverse_cdf", "gumbel"])
-@pytest.mark.parametrize("rows", [1, 3, 16])
+@pytest.mark.parametrize("rows", [1, 3, 16, 32])
 def test_fp32_rows_with_spikes(rows, draw):
     x, host = _rows(rows, 151936, 1, "f32")
     _check(x, host, draw=draw, temperature=0.7, top_k=20, top_p=0.95)
@@ -132,6 +132,8 @@ def test_more_ties_than_a_record_holds_go_to_the_generic_kernel():
 
 
 def test_other_knobs_keep_the_row_per_block_kernels():
+    x33, host33 = _rows(33, 32768, 7, "bf16")
+    _check(x33, host33, draw="inverse_cdf", temperature=0.8, top_k=20, top_p=0.9, expect_sliced=False)      # more rows than the path takes
     x, host = _rows(4, 151936, 7, "bf16")
     _check(x, host, draw="gumbel", temperature=0.8, top_k=40, top_p=0.9, exact_only=True, expect_sliced=False)
     _check(x, host, draw="gumbel", temperature=0.8, top_k=0, top_p=0.9, expect_sliced=False)
