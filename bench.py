@@ -484,12 +484,12 @@ def bench_vocab_parallel(torch, dist, lm, dev, rank, world, warmup):
     parts = torch.zeros(3, dtype=torch.float64, device=dev)
     for _ in range(n):
         ev[0].record()
-        rec = sampler.backend.local(shard, sampler.shard_start, p, sampler.cap)
+        rec = sampler.backend.local(shard, sampler.shard_start, p, sampler.cap, world)
         ev[1].record()
         flat = torch.empty(world * rec.shape[0], rec.shape[1], dtype=rec.dtype, device=dev)
         dist.all_gather_into_tensor(flat, rec)
         ev[2].record()
-        sampler.backend.merge(flat.view(world, rec.shape[0], rec.shape[1]), p, sampler.cap, u, 0, 0)
+        sampler.backend.merge(flat.view(-1, rows, rec.shape[1]), p, sampler.cap, u, 0, 0)
         ev[3].record()
         torch.cuda.synchronize(dev)
         parts += torch.tensor([ev[i].elapsed_time(ev[i + 1]) for i in range(3)], dtype=torch.float64, device=dev)
@@ -502,7 +502,7 @@ def bench_vocab_parallel(torch, dist, lm, dev, rank, world, warmup):
     return {"workload": "64 rows x 262144 bf16, vocab split over the ranks, top_k 50, top_p 0.9, T 0.8", "us_per_step": 1e3 * ms,
             "rows_per_s": rows / (ms * 1e-3), "local_kernel_us": 1e3 * float(parts[0]), "allgather_us": 1e3 * float(parts[1]),
             "merge_kernel_us": 1e3 * float(parts[2]), "parts_timing": "each part between its own CUDA events with a synchronize per step (launch gaps included), max over ranks",
-            "allgather_bytes_per_rank": int(rows * sampler.backend.record_bytes(sampler.cap)),
+            "allgather_bytes_per_rank": int(rec.numel()), "records_per_row_and_rank": int(rec.shape[0] // rows),
             "tokens_equal_single_gpu_on_every_rank": bool(same.item())}
 
 

@@ -349,17 +349,22 @@ typedef struct lm_vocab_args {
   int32_t draw;                /* LM_DRAW_*, merge step */
   const float* uniforms;       /* [rows], merge step */
   uint64_t seed; uint32_t step; int64_t row_offset;
-  void* records;               /* local step: out [rows] records; merge step: in [shards][rows] records */
+  void* records;               /* local step: out [pieces][rows] records; merge step: in [shards][rows] records (every piece of every GPU's shard counts as a shard) */
   int32_t* out_tokens;         /* merge step: [rows] */
   float* out_tau;              /* merge step, optional */
   uint32_t* out_status;        /* merge step, optional */
   void* stream;
+  int32_t pieces;              /* local step: records per row that this GPU's shard is cut into, 1 (or 0) or lm_vocab_pieces(...) */
+  int32_t pad_;
 } lm_vocab_args;
 
 LM_API int lm_vocab_local(const lm_vocab_args* args);
 LM_API int lm_vocab_merge(const lm_vocab_args* args);
 LM_API size_t lm_vocab_record_bytes(int32_t cap);
 LM_API int32_t lm_vocab_candidate_cap(int32_t top_k);
+/* How many pieces (records per row) the local step may cut a shard of vocab_local logits into when `shards` GPUs take part: with
+ * one block per piece the local step spreads over the GPU. The merge then sees shards * pieces shards. */
+LM_API int32_t lm_vocab_pieces(int32_t shards, int32_t cap, int64_t vocab_local);
 
 /*
  * The scalar step-closing kernels, on the reference's StepState buffer (monolith/core/step_state.py:38-62: 4-byte fields in the

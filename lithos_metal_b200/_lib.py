@@ -105,10 +105,11 @@ class VocabArgs(C.Structure):
         ("top_p", C.c_void_p), ("top_p_s", C.c_float), ("min_p", C.c_void_p), ("min_p_s", C.c_float),
         ("flags", C.c_uint32), ("draw", C.c_int32), ("uniforms", C.c_void_p), ("seed", C.c_uint64), ("step", C.c_uint32), ("row_offset", C.c_int64),
         ("records", C.c_void_p), ("out_tokens", C.c_void_p), ("out_tau", C.c_void_p), ("out_status", C.c_void_p), ("stream", C.c_void_p),
+        ("pieces", C.c_int32), ("pad_", C.c_int32),
     ]
 
 
-EXPORTS = ["lm_accept_scan", "lm_verify_select", "lm_advance", "lm_step_state_bytes", "lm_sample", "lm_argmax", "lm_argmax_static", "lm_vocab_local", "lm_vocab_merge", "lm_vocab_record_bytes", "lm_vocab_candidate_cap", "lm_verify", "lm_draft_q", "lm_confidence", "lm_tile_state_bytes", "lm_tile_begin", "lm_tile_consume", "lm_tile_finish", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
+EXPORTS = ["lm_accept_scan", "lm_verify_select", "lm_advance", "lm_step_state_bytes", "lm_sample", "lm_argmax", "lm_argmax_static", "lm_vocab_local", "lm_vocab_merge", "lm_vocab_record_bytes", "lm_vocab_candidate_cap", "lm_vocab_pieces", "lm_verify", "lm_draft_q", "lm_confidence", "lm_tile_state_bytes", "lm_tile_begin", "lm_tile_consume", "lm_tile_finish", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
            "lm_error_string", "lm_last_cuda_error", "lm_device_sm_count"]
 
 _lib = None
@@ -152,6 +153,8 @@ def lib():
         L.lm_vocab_record_bytes.argtypes = [C.c_int32]
         L.lm_vocab_candidate_cap.restype = C.c_int32
         L.lm_vocab_candidate_cap.argtypes = [C.c_int32]
+        L.lm_vocab_pieces.restype = C.c_int32
+        L.lm_vocab_pieces.argtypes = [C.c_int32, C.c_int32, C.c_int64]
         for fn in (L.lm_accept_scan, L.lm_verify_select, L.lm_advance):
             fn.restype, fn.argtypes = C.c_int, [C.POINTER(StepArgs)]
         L.lm_step_state_bytes.restype = C.c_size_t

@@ -304,6 +304,7 @@ int lm_sample(const lm_sample_args* a) {
       char* ws = static_cast<char*>(a->workspace) + ws_base;
       S.logits = a->logits; S.dtype = a->dtype; S.rows = P.rows; S.vocab = P.vocab; S.row_stride = a->row_stride;
       S.temperature = a->temperature_s; S.top_k = a->top_k_s;
+      S.temperature_rows = nullptr; S.top_k_rows = nullptr; S.exact_mass = 0; S.index_base = 0;
       S.history = P.history; S.hist_len = P.hist_len; S.hist_stride = P.hist_stride; S.rho = P.rho; S.pi = P.pi;
       S.records = reinterpret_cast<unsigned char*>(ws); S.record_bytes = static_cast<int64_t>(lm_vocab_record_bytes(S.cap));
       S.state = P.state; S.t_max = P.t_max; S.g = P.g;
@@ -498,6 +499,17 @@ size_t lm_vocab_record_bytes(int32_t cap) { return cap > 0 ? static_cast<size_t>
 
 int32_t lm_vocab_candidate_cap(int32_t top_k) { return top_k > 0 ? (top_k + 64 + 7) / 8 * 8 : 0; }
 
+// Pieces a shard is cut into by the local step (each with a record of its own): the most that the merge still takes with the
+// other shards' (shards * pieces <= 64 records per row, cap <= 8 * (1024 / (shards * pieces))), pieces of at least 2048 logits,
+// and only for records of at most 128 candidates (a top_k up to 64): beyond that the piece's bound, taken from its threads'
+// maxima, is no longer close to its k-th largest logit.
+int32_t lm_vocab_pieces(int32_t shards, int32_t cap, int64_t vocab_local) {
+  if (shards < 1 || cap < 1 || cap > 128 || vocab_local < 1) return 1;
+  int32_t p = 1;
+  while (2 * p * shards <= kVpMaxShards && cap <= kVpPerThread * (kVpMaxCandidates / (2 * p * shards)) && vocab_local / (2 * p) >= 2048) p *= 2;
+  return p;
+}
+
 int lm_vocab_local(const lm_vocab_args* a) {
   if (!a || a->struct_size != sizeof(lm_vocab_args)) return LM_E_INVALID;
   if (a->rows < 0 || a->vocab_local < 1 || (a->dtype != LM_DTYPE_BF16 && a->dtype != LM_DTYPE_F32)) return LM_E_INVALID;
@@ -514,6 +526,38 @@ int lm_vocab_local(const lm_vocab_args* a) {
   int sms = 0;
   const int rc = sm_count(&sms);
   if (rc != LM_OK) return rc;
+  if (a->pieces > 1) {
+    // the shard in pieces, one block each (the few-row path's slice kernel, with FP64 masses: no exact path stands behind this merge)
+    if (a->pieces > kVpMaxShards || a->cap > 128) return LM_E_UNSUPPORTED;
+    SliceDev S;
+    S.logits = a->logits; S.dtype = a->dtype; S.rows = P.rows; S.vocab = P.vocab_local; S.row_stride = a->row_stride;
+    S.slices = a->pieces;
+    S.slice_len = static_cast<int>(((a->vocab_local + S.slices - 1) / S.slices + 7) / 8 * 8);
+    if (S.slice_len > kSliceMaxLen) return LM_E_UNSUPPORTED;
+    S.temperature = a->temperature_s; S.top_k = a->top_k_s; S.cap = a->cap; S.need_mass = 1;
+    S.temperature_rows = a->temperature; S.top_k_rows = a->top_k; S.exact_mass = 1; S.index_base = P.shard_start;
+    S.history = nullptr; S.hist_len = 0; S.hist_stride = 0; S.rho = 1.0f; S.pi = 0.0f;
+    S.records = P.records; S.record_bytes = P.record_bytes;
+    S.state = nullptr; S.t_max = 0; S.g = 0;
+    const size_t slice_smem = slice_smem_bytes(S.slice_len);
+    cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+    // threads per piece as on the few-row path; a record of cap candidates serves a top_k up to cap - 64
+    const int threads = static_cast<long long>(S.slices) * P.rows <= sms ? kSliceBlockBig : (a->cap - 64 <= kSliceTinyMaxK ? kSliceBlockTiny : kSliceBlockSmall);
+    int rs;
+    if (threads == kSliceBlockBig) {
+      rs = ensure_dynamic_smem(kSlotSlice, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockBig>), slice_smem);
+      if (rs == LM_OK) slice_local_kernel<kSliceBlockBig><<<dim3(S.slices, P.rows), kSliceBlockBig, slice_smem, st>>>(S);
+    } else if (threads == kSliceBlockSmall) {
+      rs = ensure_dynamic_smem(kSlotSliceSmall, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockSmall>), slice_smem);
+      if (rs == LM_OK) slice_local_kernel<kSliceBlockSmall><<<dim3(S.slices, P.rows), kSliceBlockSmall, slice_smem, st>>>(S);
+    } else {
+      rs = ensure_dynamic_smem(kSlotSliceTiny, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockTiny>), slice_smem);
+      if (rs == LM_OK) slice_local_kernel<kSliceBlockTiny><<<dim3(S.slices, P.rows), kSliceBlockTiny, slice_smem, st>>>(S);
+    }
+    if (rs != LM_OK) return rs;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? LM_OK : cuda_fail(e);
+  }
   const size_t smem = sizeof(GenericSmem) + 16;
   const int rs = ensure_dynamic_smem(kSlotVocabLocal, reinterpret_cast<const void*>(vocab_local_kernel), smem);
   if (rs != LM_OK) return rs;

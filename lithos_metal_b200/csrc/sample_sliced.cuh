@@ -38,6 +38,9 @@ struct SliceDev {
   const void* logits; int dtype; int rows; int vocab; int64_t row_stride;
   int slices; int slice_len;                          // slice_len: a multiple of 8 (the last slices of a row may be short or empty)
   float temperature; int top_k; int cap; int need_mass;
+  const float* temperature_rows; const int32_t* top_k_rows;   // per-row values instead of the two scalars (vocab-parallel callers)
+  int exact_mass;                                     // the softmass as an FP64 sum (where no exact path stands behind the merge)
+  int index_base;                                     // added to every candidate's index (the shard's first logit)
   const int32_t* history; int hist_len; int64_t hist_stride; float rho, pi;
   unsigned char* records; int64_t record_bytes;       // [slices][rows] records
   const uint32_t* state; int t_max, g;                // optional StepState: rows beyond t_this_step, and a finished state, are left alone
@@ -165,9 +168,13 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
   tmax[tid] = best ? best_value(best) : -INFINITY;
   best = block_max_u64(best, scratch);
   const float vmax = best_value(best);
-  const double inv_t = 1.0 / static_cast<double>(P.temperature);
+  const double inv_t = 1.0 / static_cast<double>(P.temperature_rows ? P.temperature_rows[row] : P.temperature);
   double mass = 0.0;
-  if (P.need_mass && vmax > -INFINITY) {                                   // (only a top-p over the whole row asks for it)
+  if (P.need_mass && P.exact_mass && vmax > -INFINITY) {
+    double m = 0.0;
+    for (int j = tid; j < n; j += B) m += softmass(vals[j], vmax, inv_t);
+    mass = block_sum_f64(m, scratch);
+  } else if (P.need_mass && vmax > -INFINITY) {                            // (only a top-p over the whole row asks for it)
     // In FP32, one ex2 per logit: sum_j 2^(z_j c2a + nb) with c2a = fl32(log2(e) / T) and nb = fl32(-vmax c2a); the common factor
     // that nb's rounding leaves is taken out exactly afterwards, so the result approximates sum_j 2^((z_j - vmax) c2a). The merge
     // knows how far that can be from the exact mass (slice_mass_band) and hands a row on when its top-p boundary is closer than that.
@@ -180,7 +187,7 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
   // ---- the slice's k-th largest value and everything at or above it
   // The k-th largest of the threads' own maxima is a logit of the slice with at least k logits at or above it: a lower bound of
   // the slice's k-th largest that lets through only a few logits more (two of the slice's largest seldom fall to one thread).
-  const uint32_t k = static_cast<uint32_t>(min(P.top_k, n));
+  const uint32_t k = static_cast<uint32_t>(min(max(P.top_k_rows ? P.top_k_rows[row] : P.top_k, 1), min(n, B)));
   const uint32_t bound = slice_kth_key<B>(tmax, min(n, B), k, bins, scratch, pick);
   // Fewer than k threads with a logit above -inf (a masked vocabulary): every logit above -inf is a candidate, and one -inf logit
   // (the first) stands for the rest, so that a row with fewer than top_k logits above -inf still finds its k-th largest at -inf.
@@ -191,7 +198,7 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
     for (int j = tid; j < n; j += B) {
       if (vals[j] >= tau_local) {
         const uint32_t slot = atomicAdd(&s_n, 1u);
-        if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = vals[j]; out_idx[slot] = lo + j; }
+        if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = vals[j]; out_idx[slot] = P.index_base + lo + j; }
       }
     }
   } else {
@@ -199,14 +206,14 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
       const float v = vals[j];
       if (v > -INFINITY) {
         const uint32_t slot = atomicAdd(&s_n, 1u);
-        if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = v; out_idx[slot] = lo + j; }
+        if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = v; out_idx[slot] = P.index_base + lo + j; }
       } else if (v == -INFINITY) atomicMin(&s_ninf, static_cast<uint32_t>(j));
     }
   }
   __syncthreads();
   if (open && tid == 0 && s_ninf != 0xFFFFFFFFu) {
     const uint32_t slot = s_n++;
-    if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = -INFINITY; out_idx[slot] = lo + static_cast<int>(s_ninf); }
+    if (slot < static_cast<uint32_t>(P.cap)) { out_val[slot] = -INFINITY; out_idx[slot] = P.index_base + lo + static_cast<int>(s_ninf); }
   }
   if (tid == 0) {
     const uint32_t cnt = s_n;

@@ -60,14 +60,17 @@ class CudaVocabBackend:
         ptr, s, t = _knob(p.top_p, rows, torch.float32, dev, "top_p"); a.top_p, a.top_p_s = ptr, float(s); keep.append(t)
         ptr, s, t = _knob(p.min_p, rows, torch.float32, dev, "min_p"); a.min_p, a.min_p_s = ptr, float(s); keep.append(t)
 
-    def local(self, logits: torch.Tensor, shard_start: int, p: SamplingParams, cap: int) -> torch.Tensor:
+    def local(self, logits: torch.Tensor, shard_start: int, p: SamplingParams, cap: int, shards: int = 1) -> torch.Tensor:
+        """This GPU's records, [pieces * rows, record bytes]: the shard is cut into as many pieces (each with a record per row) as
+        the merge still takes together with the other ``shards - 1`` GPUs' pieces, so that the local step spreads over the GPU."""
         logits = _check_logits(logits)
         rows, width = logits.shape
-        rec = torch.empty(rows, self.record_bytes(cap), dtype=torch.uint8, device=logits.device)
+        pieces = int(_lib.lib().lm_vocab_pieces(int(shards), int(cap), int(width)))
+        rec = torch.empty(pieces * rows, self.record_bytes(cap), dtype=torch.uint8, device=logits.device)
         a = _lib.VocabArgs()
         a.struct_size = C.sizeof(_lib.VocabArgs)
         a.dtype, a.logits, a.rows, a.vocab_local, a.row_stride, a.shard_start = _dtype_code(logits), logits.data_ptr(), rows, width, _row_stride(logits), shard_start
-        a.cap, a.records = cap, rec.data_ptr()
+        a.cap, a.records, a.pieces = cap, rec.data_ptr(), pieces
         keep = []
         self._fill(a, p, rows, logits.device, keep)
         a.stream = torch.cuda.current_stream(logits.device).cuda_stream
@@ -132,12 +135,13 @@ class VocabParallelSampler:
             raise ValueError(f"this rank's shard is {self.shard_width} wide, got {local_logits.shape[1]}")
         if self.params.draw == "inverse_cdf" and uniforms is None:
             raise ValueError("draw='inverse_cdf' needs uniforms [rows]")
-        rec = self.backend.local(local_logits, self.shard_start, self.params, self.cap)
-        flat = torch.empty(self.world * rec.shape[0], rec.shape[1], dtype=rec.dtype, device=rec.device)   # shard-major: [shard][row]
+        rows = local_logits.shape[0]
+        rec = self.backend.local(local_logits, self.shard_start, self.params, self.cap, self.world)   # [pieces * rows, record bytes]
+        flat = torch.empty(self.world * rec.shape[0], rec.shape[1], dtype=rec.dtype, device=rec.device)   # shard-major: [shard][piece][row]
         if self.world > 1:
             dist.all_gather_into_tensor(flat, rec, group=self.group)           # the one exchange of the step
         else:
             flat.copy_(rec)
-        gathered = flat.view(self.world, rec.shape[0], rec.shape[1])
+        gathered = flat.view(-1, rows, rec.shape[1])                           # every piece of every shard is a shard of the merge
         tokens, tau, status = self.backend.merge(gathered, self.params, self.cap, uniforms, step, row_offset)
         return SampleOutput(tokens, tau=tau, status=status)

@@ -27,10 +27,11 @@ class NumpyVocabBackend:
     def record_bytes(self, cap):
         return vp.record_bytes(cap)
 
-    def local(self, logits, shard_start, p, cap):
+    def local(self, logits, shard_start, p, cap, shards=1):
         z = logits.numpy()
-        recs = [np.frombuffer(vp.local_record(z[r], shard_start, temperature=float(p.temperature), top_k=int(p.top_k), cap=cap), np.uint8)
-                for r in range(z.shape[0])]
+        half = z.shape[1] // 2                                              # two pieces per shard, piece-major like the CUDA backend's records
+        recs = [np.frombuffer(vp.local_record(z[r, lo:hi], shard_start + lo, temperature=float(p.temperature), top_k=int(p.top_k), cap=cap), np.uint8)
+                for lo, hi in ((0, half), (half, z.shape[1])) for r in range(z.shape[0])]
         return torch.from_numpy(np.stack(recs).copy())
 
     def merge(self, gathered, p, cap, uniforms, step, row_offset):

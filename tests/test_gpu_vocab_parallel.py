@@ -22,8 +22,8 @@ def run_sharded(x, shards, p, uniforms, step=0, row_offset=0):
     recs = []
     for s in range(shards):
         lo, width = parallel.shard_vocab(vocab, s, shards)
-        recs.append(backend.local(x[:, lo:lo + width], lo, p, cap))
-    gathered = torch.stack(recs)
+        recs.append(backend.local(x[:, lo:lo + width], lo, p, cap, shards))     # [pieces * rows, record bytes]
+    gathered = torch.stack(recs).view(-1, x.shape[0], recs[0].shape[1])        # [shards * pieces, rows, record bytes]
     return backend.merge(gathered, p, cap, uniforms, step, row_offset), gathered, cap
 
 
@@ -84,12 +84,17 @@ def test_a_masked_vocabulary_over_four_shards():
         assert int(status.max()) & 32 == 0
         np.testing.assert_array_equal(tau.cpu().numpy(), tau_o)
         np.testing.assert_array_equal(tok.cpu().numpy(), t_o)
-        g = gathered.cpu().numpy()                                         # and the records are the CPU model's
-        for s in range(4):
-            lo, width = parallel.shard_vocab(vocab, s, 4)
-            a = vp.unpack_record(g[s, 0].tobytes(), cap)
-            b = vp.unpack_record(vp.local_record(z[0, lo:lo + width], lo, temperature=0.8, top_k=kw["top_k"], cap=cap), cap)
-            assert a[2] == b[2] and sorted(a[5].tolist()) == sorted(b[5].tolist())
+    # the records of unsplit shards (a small vocabulary) are the CPU model's
+    small = z[:, 18000:22096].copy()
+    p = lm.SamplingParams(temperature=0.8, seed=5, draw="inverse_cdf", top_k=50)
+    _, gathered, cap = run_sharded(torch.from_numpy(small).cuda(), 4, p, torch.from_numpy(u).cuda())
+    g = gathered.cpu().numpy()
+    assert g.shape[0] == 4
+    for s in range(4):
+        lo, width = parallel.shard_vocab(small.shape[1], s, 4)
+        a = vp.unpack_record(g[s, 0].tobytes(), cap)
+        b = vp.unpack_record(vp.local_record(small[0, lo:lo + width], lo, temperature=0.8, top_k=50, cap=cap), cap)
+        assert a[2] == b[2] and sorted(a[5].tolist()) == sorted(b[5].tolist())
 
 
 def test_records_ties_and_knob_variants():
