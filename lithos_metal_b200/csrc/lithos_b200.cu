@@ -85,6 +85,8 @@ static int cuda_fail(cudaError_t e) {
 }
 
 constexpr int kOverlapRowsPerSM = 5;    // up to this many rows per SM the two sampler kernels run side by side (lm_sample)
+constexpr int kAloneRowsPerSM = 2;      // ... and up to this many the histogram kernel's blocks have their SM to themselves
+constexpr size_t kAloneSmemBytes = 140 * 1024;   // more than an SM's shared memory less a block of the top-k kernel
 
 static int sm_count(int* out) {
   int dev = 0;
@@ -388,7 +390,16 @@ int lm_sample(const lm_sample_args* a) {
       // as the histogram kernel's blocks leave them (at once, for the SMs it has no rows for); a second launch of the histogram
       // kernel takes what the top-k kernel handed on (usually nothing: it leaves at once).
       sample_classify_kernel<<<static_cast<int>((a->rows + 255) / 256), 256, 0, st>>>(P, list_other, counters + 4);
-      sample_hist_kernel<<<grid, kHB, hist_smem, st>>>(P, list_other, counters + 4, counters + 2, redo, counters + 3);
+      // With at most kAloneRowsPerSM rows per SM the histogram kernel's blocks ask for so much shared memory that nothing else fits
+      // beside them: a long row then has its SM to itself, and the blocks that find no row leave their SM to the top-k kernel at
+      // once (256 rows of the benchmark mix: 112 -> 106 us per call; from 3 rows per SM on it costs time).
+      size_t hist_smem_first = hist_smem; int grid_first = grid;
+      if (a->rows <= static_cast<int64_t>(kAloneRowsPerSM) * sms && hist_smem < kAloneSmemBytes) {
+        hist_smem_first = kAloneSmemBytes; grid_first = static_cast<int>(a->rows < sms ? a->rows : sms);
+        rc = ensure_dynamic_smem(kSlotFast, reinterpret_cast<const void*>(sample_hist_kernel), hist_smem_first);
+        if (rc != LM_OK) return rc;
+      }
+      sample_hist_kernel<<<grid_first, kHB, hist_smem_first, st>>>(P, list_other, counters + 4, counters + 2, redo, counters + 3);
       cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return cuda_fail(e);
       cudaLaunchConfig_t cfg = {};
