@@ -546,6 +546,9 @@ def bench_verify(torch, lm, dev):
              "round_sample_then_verify": lambda: round_tail(False),
              "round_sample_then_verify_given_row_stats": lambda: round_tail(True),
              "stochastic_q_logits": lambda: lm.verify(target, stats.tokens, None, ua, uf, "stochastic", draft_logits=drafter, draft_stats=stats),
+             # both hand-overs of a round at once: q from the drafter's logits and statistics, the target rows' maxima and masses from the sampler
+             "stochastic_q_logits_given_row_stats": lambda: lm.verify(target, stats.tokens, None, ua, uf, "stochastic", draft_logits=drafter, draft_stats=stats,
+                                                                      target_vmax=vmax, target_mass=mass),
              "greedy": lambda: lm.verify(target, drafts, mode="greedy"),
              "draft_q_one_position": lambda: lm.draft_q(drafter[3:4], temperature=1.0, seed=SEED, step=0, first_position=3)}
     res = {"accept_len": {"stochastic": int(calls["stochastic"]()[0]), "stochastic_all_accepted": int(calls["stochastic_all_accepted"]()[0]),

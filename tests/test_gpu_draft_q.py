@@ -76,6 +76,12 @@ def test_verify_from_drafter_logits(temperature):
         np.testing.assert_array_equal(got[3].cpu().numpy(), pd)
         same = lm.verify(tx, ids, torch.from_numpy(q).cuda(), torch.from_numpy(ua), torch.tensor([uf]), "stochastic", temperature=temperature)
         assert (int(same[0]), int(same[1])) == (acc, fin)
+        # the whole hand-over of a round: q from the drafter's logits and statistics, the target rows' maxima and masses from the sampler
+        kept = lm.sample(tx, lm.SamplingParams(temperature=temperature, top_k=torch.zeros(n + 1, dtype=torch.int32), draw="inverse_cdf"),
+                         uniforms=torch.full((n + 1,), 0.5), return_vmax=True)
+        both = lm.verify(tx, ids, None, torch.from_numpy(ua), torch.tensor([uf]), "stochastic", temperature=temperature, draft_logits=dx,
+                         draft_stats=st, target_vmax=kept.vmax, target_mass=kept.mass)
+        assert (int(both[0]), int(both[1])) == (acc, fin), trial
     np.testing.assert_allclose(q.sum(axis=1), 1.0, rtol=1e-5)
 
 
