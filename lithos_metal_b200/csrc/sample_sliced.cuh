@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(B) slice_local_kernel(SliceDev P) {
     }
     __syncthreads();
   }
-  // ---- maximum, FP64 softmass relative to it
+  // ---- maximum, softmass relative to it
   uint64_t best = 0ull;
   bool nan = false;
   for (int j = tid; j < n; j += B) {

@@ -2,12 +2,15 @@
 // in the reference (which is single-device); the result is defined as the single-GPU sampler's result on the whole
 // row, bit for bit.
 //
-//   vocab_local_kernel  (each GPU, its shard): per row the shard's maximum, its FP64 softmass relative to that
-//                       maximum, and every logit at or above the shard's own k-th largest value (ties kept), with
-//                       global indices -> one fixed-size record per row;
+//   local step          (each GPU, its shard): per row the shard's maximum, its FP64 softmass relative to that maximum, and every
+//                       logit at or above (a lower bound of) the shard's own k-th largest value, with global indices -> a
+//                       fixed-size record per row. vocab_local_kernel: one block and one record per row, any top_k; for a top_k
+//                       up to 64 the shard is cut into pieces, one block and one record per piece (slice_local_kernel,
+//                       sample_sliced.cuh), so that the step spreads over the GPU;
 //   [one all-gather of the records, done by the host layer over NCCL]
-//   vocab_merge_kernel  (every GPU, identically): sorts the gathered candidates, rebuilds the global maximum and
-//                       mass, finds tau_k / tau_p / tau_m exactly as the single-GPU walk does, and draws.
+//   vocab_merge_kernel  (every GPU, identically): takes the candidates of all records (every piece of every GPU a shard), puts
+//                       those at or above the row's top-k bound in order, rebuilds the global maximum and mass, finds
+//                       tau_k / tau_p / tau_m exactly as the single-GPU walk does, and draws.
 //
 // Every logit at or above the global k-th largest value is a candidate of its shard (a shard holds fewer than k logits
 // above that value, so its own k-th largest lies at or below it), which is why the merge sees the complete top-k set.

@@ -6,9 +6,9 @@ The reference is single-device, so both modes are new; each is defined by "same 
   of rows with ``row_offset`` = its first global row, so Gumbel streams and tokens do not depend on the split. No
   collective on the data path.
 * vocab-parallel sampling (``VocabParallelSampler``): every rank holds a contiguous shard of each row's vocabulary; per
-  step it computes one small record per row (shard maximum, FP64 softmass, top-k candidates), all-gathers the records
-  (the only exchange: a few hundred bytes per row and rank, NCCL over NVLink), and merges them identically on every
-  rank. The kept set must lie inside the top-k candidates, so ``top_k >= 1`` is required.
+  step it computes small records per row (maximum, FP64 softmass, top-k candidates of the shard, or of each piece the shard
+  is cut into), all-gathers the records (the only exchange: a few KB per row and rank, NCCL over NVLink), and merges them
+  identically on every rank. The kept set must lie inside the top-k candidates, so ``top_k >= 1`` is required.
 
 The compute steps go through a backend object so that the exchange logic can be exercised on CPU ranks (gloo) with a
 stand-in backend; the default backend is the CUDA library and nothing else ships.
