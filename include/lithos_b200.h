@@ -488,6 +488,35 @@ LM_API size_t lm_verify_workspace_bytes(int32_t n_draft, int64_t vocab);
 LM_API float lm_uniform01(uint64_t seed, uint32_t step, uint32_t t, uint32_t index);
 
 /* Library identification and diagnostics (host calls). */
+/*
+ * The vocabulary projection of a decode step with the final RMSNorm fused on its input: the reference's `lm_head` op
+ * (monolith/nn/lm_head.py:50-60; semantics monolith/nn/oracle.py:20-32): logits[r, v] = bf16(sum_k x[r, k] * weight[v, k]) in
+ * FP32, x = the rows of `hidden` as they are (norm_weight NULL: already normalised) or bf16(hidden * rsqrt(mean(hidden^2) + eps) *
+ * (one_plus ? 1 + norm_weight : norm_weight)). At most 8 rows (one token, or the rows of a speculative round): a matrix-vector
+ * product bound by the weight stream. hidden_dim a multiple of 64; hidden, weight and their strides 16-byte aligned. The logits
+ * are what lm_sample / lm_argmax / lm_verify take next on the same stream (they are still in L2 then). Floating point: the FP32
+ * sums are formed in another order than a reference's, so a logit may differ from it by one BF16 unit in the last place.
+ */
+#define LM_HEAD_MAX_ROWS 8
+typedef struct lm_head_args {
+  uint32_t struct_size;
+  int32_t rows;                /* 1 .. LM_HEAD_MAX_ROWS */
+  const void* hidden;          /* [rows, hidden_stride] BF16 */
+  int64_t hidden_stride;
+  const void* weight;          /* [vocab, weight_stride] BF16: one row of hidden_dim weights per vocabulary entry */
+  int64_t weight_stride;
+  int64_t hidden_dim;
+  int64_t vocab;
+  const void* norm_weight;     /* [hidden_dim] BF16 or NULL */
+  float eps;
+  int32_t one_plus;            /* the norm's scale is 1 + norm_weight (zero-centred weights) */
+  void* logits;                /* out [rows, logits_stride] BF16 */
+  int64_t logits_stride;
+  void* stream;
+} lm_head_args;
+
+LM_API int lm_head(const lm_head_args* args);
+
 LM_API int lm_abi_version(void);
 LM_API const char* lm_error_string(int code);
 LM_API const char* lm_last_cuda_error(void);   /* text of the last CUDA error seen by this thread's calls, "" if none */

@@ -9,8 +9,9 @@ from .verify import DraftQ, draft_q, verify
 from .step_state import StepStateLayout, accept_scan, advance, confidence, verify_select
 from .records import accept_args_from_record, sample_args_from_record, select_args_from_record
 from .tiles import TileSampler
+from .head import lm_head
 from . import parallel
 
-__all__ = ["TileSampler", "GreedySampler", "StochasticSampler", "SamplingParams", "SampleOutput", "sample", "argmax", "sample_row", "thresholds",
+__all__ = ["TileSampler", "lm_head", "GreedySampler", "StochasticSampler", "SamplingParams", "SampleOutput", "sample", "argmax", "sample_row", "thresholds",
            "warped_probabilities", "verify", "draft_q", "DraftQ", "StepStateLayout", "accept_scan", "verify_select", "advance", "confidence", "parallel",
            "sample_args_from_record", "select_args_from_record", "accept_args_from_record"]

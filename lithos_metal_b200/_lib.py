@@ -109,7 +109,15 @@ class VocabArgs(C.Structure):
     ]
 
 
-EXPORTS = ["lm_accept_scan", "lm_verify_select", "lm_advance", "lm_step_state_bytes", "lm_sample", "lm_argmax", "lm_argmax_static", "lm_vocab_local", "lm_vocab_merge", "lm_vocab_record_bytes", "lm_vocab_candidate_cap", "lm_vocab_pieces", "lm_verify", "lm_draft_q", "lm_confidence", "lm_tile_state_bytes", "lm_tile_begin", "lm_tile_consume", "lm_tile_finish", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
+class HeadArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("rows", C.c_int32), ("hidden", C.c_void_p), ("hidden_stride", C.c_int64), ("weight", C.c_void_p),
+        ("weight_stride", C.c_int64), ("hidden_dim", C.c_int64), ("vocab", C.c_int64), ("norm_weight", C.c_void_p), ("eps", C.c_float),
+        ("one_plus", C.c_int32), ("logits", C.c_void_p), ("logits_stride", C.c_int64), ("stream", C.c_void_p),
+    ]
+
+
+EXPORTS = ["lm_head", "lm_accept_scan", "lm_verify_select", "lm_advance", "lm_step_state_bytes", "lm_sample", "lm_argmax", "lm_argmax_static", "lm_vocab_local", "lm_vocab_merge", "lm_vocab_record_bytes", "lm_vocab_candidate_cap", "lm_vocab_pieces", "lm_verify", "lm_draft_q", "lm_confidence", "lm_tile_state_bytes", "lm_tile_begin", "lm_tile_consume", "lm_tile_finish", "lm_workspace_bytes", "lm_verify_workspace_bytes", "lm_uniform01", "lm_abi_version",
            "lm_error_string", "lm_last_cuda_error", "lm_device_sm_count"]
 
 _lib = None
@@ -153,6 +161,8 @@ def lib():
         L.lm_vocab_record_bytes.argtypes = [C.c_int32]
         L.lm_vocab_candidate_cap.restype = C.c_int32
         L.lm_vocab_candidate_cap.argtypes = [C.c_int32]
+        L.lm_head.restype = C.c_int
+        L.lm_head.argtypes = [C.POINTER(HeadArgs)]
         L.lm_vocab_pieces.restype = C.c_int32
         L.lm_vocab_pieces.argtypes = [C.c_int32, C.c_int32, C.c_int64]
         for fn in (L.lm_accept_scan, L.lm_verify_select, L.lm_advance):

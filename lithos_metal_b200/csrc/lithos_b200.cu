@@ -17,6 +17,7 @@
 #include "draft_q.cuh"
 #include "vocab_parallel.cuh"
 #include "spec_ops.cuh"
+#include "lm_head.cuh"
 
 namespace lm {
 
@@ -104,7 +105,7 @@ static int sm_count(int* out) {
 
 // Kernels that need more than 48 KB of dynamic shared memory must be told so once per device (the attribute belongs to the
 // device's copy of the function); remembered per device and kernel, raised when a call needs more.
-enum KernelSlot { kSlotFast, kSlotTopk, kSlotGeneric, kSlotVocabLocal, kSlotVerify, kSlotVerifyStats, kSlotDraftQ, kSlotTileFinish, kSlotSlice, kSlotSliceSmall, kSlotSliceTiny, kSlotSlicedMerge, kSlotCount };
+enum KernelSlot { kSlotFast, kSlotTopk, kSlotGeneric, kSlotVocabLocal, kSlotVerify, kSlotVerifyStats, kSlotDraftQ, kSlotTileFinish, kSlotSlice, kSlotSliceSmall, kSlotSliceTiny, kSlotSlicedMerge, kSlotHead, kSlotCount };
 
 static int ensure_dynamic_smem(KernelSlot slot, const void* func, size_t bytes) {
   if (bytes <= 48 * 1024) return LM_OK;
@@ -602,6 +603,32 @@ int lm_vocab_merge(const lm_vocab_args* a) {
   if (rc != LM_OK) return rc;
   const int grid = static_cast<int>(a->rows < 4LL * sms ? a->rows : 4LL * sms);
   vocab_merge_kernel<<<grid, kVpMaxCandidates, 0, static_cast<cudaStream_t>(a->stream)>>>(P);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LM_OK : cuda_fail(e);
+}
+
+int lm_head(const lm_head_args* a) {
+  if (!a || a->struct_size != sizeof(lm_head_args)) return LM_E_INVALID;
+  if (a->rows < 0 || a->vocab < 0 || a->hidden_dim < 1) return LM_E_INVALID;
+  if (a->rows == 0 || a->vocab == 0) return LM_OK;
+  if (!a->hidden || !a->weight || !a->logits || a->hidden_stride < a->hidden_dim || a->weight_stride < a->hidden_dim || a->logits_stride < a->vocab) return LM_E_INVALID;
+  if (a->rows > LM_HEAD_MAX_ROWS || a->vocab > LM_MAX_VOCAB || (a->hidden_dim % kHeadStep) != 0 || a->hidden_dim > 16384) return LM_E_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(a->weight) & 15u) || (a->weight_stride % 8) != 0) return LM_E_UNSUPPORTED;      // 16-byte loads of the weights
+  HeadDev P;
+  P.x = static_cast<const uint16_t*>(a->hidden); P.x_stride = a->hidden_stride; P.rows = a->rows;
+  P.w = static_cast<const uint16_t*>(a->weight); P.w_stride = a->weight_stride; P.hidden = static_cast<int>(a->hidden_dim); P.vocab = static_cast<int>(a->vocab);
+  P.gamma = static_cast<const uint16_t*>(a->norm_weight); P.eps = a->eps; P.one_plus = a->one_plus;
+  P.logits = static_cast<uint16_t*>(a->logits); P.logits_stride = a->logits_stride;
+  int sms = 0;
+  int rc = sm_count(&sms);
+  if (rc != LM_OK) return rc;
+  const size_t smem = head_smem_bytes(P.hidden);
+  rc = ensure_dynamic_smem(kSlotHead, reinterpret_cast<const void*>(lm_head_kernel), smem);
+  if (rc != LM_OK) return rc;
+  const long long per_sm = smem + 1024 <= 75 * 1024 ? 3 : (smem + 1024 <= 113 * 1024 ? 2 : 1);     // blocks that fit one SM's shared memory
+  const long long tiles = (a->vocab + kHeadTile - 1) / kHeadTile, want = (tiles + kHeadWarps - 1) / kHeadWarps;
+  const int grid = static_cast<int>(want < per_sm * sms ? want : per_sm * sms);
+  lm_head_kernel<<<grid, kHeadThreads, smem, static_cast<cudaStream_t>(a->stream)>>>(P);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LM_OK : cuda_fail(e);
 }

@@ -3,7 +3,7 @@
 Run once, in a container where the reference checkout is available, with its path as the only argument:
 
     python tests/golden/make_golden.py /path/to/lithos-metal
-    python tests/golden/make_golden.py /path/to/lithos-metal --only draft_q      (adds that section, or `confidence` / `penalised`, to the existing file)
+    python tests/golden/make_golden.py /path/to/lithos-metal --only draft_q      (adds that section, or `confidence` / `penalised` / `lm_head`, to the existing file)
 
 It imports ``monolith.nn.sampling_ref`` / ``monolith.nn.sampler`` / ``monolith.kernels`` / ``monolith.core`` read-only
 (numpy and torch are their only dependencies), extracts the ``model_accept`` function from
@@ -97,10 +97,39 @@ def penalised_section(ref, f32_to_bf16, bf16_to_f32) -> dict:
             "history_crc": int(history.astype(np.uint64).sum())}
 
 
+def lm_head_inputs(seed: int = 77, rows: int = 5, hidden: int = 256, vocab: int = 600):
+    """The seeded inputs of the lm_head section, as BF16 codes (uint16): hidden states, weight [vocab, hidden], norm weight."""
+    rng = np.random.default_rng(seed)
+
+    def codes(a):
+        u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+        return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return (codes(rng.standard_normal((rows, hidden)) * 1.5), codes(rng.standard_normal((vocab, hidden)) * 0.06), codes(rng.standard_normal(hidden) * 0.2))
+
+
+def lm_head_section() -> dict:
+    """The reference's own definitions of the lm_head op (monolith/nn/oracle.py: linear, rms_norm) on seeded BF16 inputs: the logits
+    as BF16 codes, hex, row-major [rows, vocab]; without the norm, with it (1 + weight), and with a plain weight."""
+    import torch
+    from monolith.nn import oracle as nn_oracle
+    x, w, g = lm_head_inputs()
+
+    def t(c):
+        return torch.from_numpy((c.astype(np.uint32) << 16).view(np.float32).copy()).to(torch.bfloat16)
+
+    def hexed(y):
+        return y.view(torch.int16).numpy().view(np.uint16).tobytes().hex()
+    xt, wt, gt = t(x), t(w), t(g)
+    return {"seed": 77, "rows": 5, "hidden": 256, "vocab": 600, "eps": 1e-6,
+            "plain": hexed(nn_oracle.linear(xt, wt)),
+            "norm_one_plus": hexed(nn_oracle.linear(nn_oracle.rms_norm(xt, gt, 1e-6, one_plus=True), wt)),
+            "norm_plain_weight": hexed(nn_oracle.linear(nn_oracle.rms_norm(xt, gt, 1e-6, one_plus=False), wt))}
+
+
 def main(ref_root: str, only: str = "") -> None:
     sys.dont_write_bytecode = True
     sys.path.insert(0, ref_root)
-    if only in ("draft_q", "confidence", "penalised"):                                  # add this section to the existing file without redoing the rest
+    if only in ("draft_q", "confidence", "penalised", "lm_head"):                                  # add this section to the existing file without redoing the rest
         from monolith.formats.fp import bf16_to_f32, f32_to_bf16
         from monolith.nn import sampling_ref as ref
         path = os.path.join(HERE, "reference_outputs.json")
@@ -108,6 +137,8 @@ def main(ref_root: str, only: str = "") -> None:
             out = json.load(f)
         if only == "draft_q":
             out["draft_q"] = draft_q_section(ref, f32_to_bf16, bf16_to_f32)
+        elif only == "lm_head":
+            out["lm_head"] = lm_head_section()
         elif only == "penalised":
             out["penalised"] = penalised_section(ref, f32_to_bf16, bf16_to_f32)
         else:
@@ -250,6 +281,7 @@ def main(ref_root: str, only: str = "") -> None:
     out["draft_q"] = draft_q_section(ref, f32_to_bf16, bf16_to_f32)
     out["confidence"] = confidence_section(f32_to_bf16, bf16_to_f32)
     out["penalised"] = penalised_section(ref, f32_to_bf16, bf16_to_f32)
+    out["lm_head"] = lm_head_section()
 
     with open(os.path.join(HERE, "reference_outputs.json"), "w") as f:
         json.dump(out, f, indent=1, sort_keys=True)
