@@ -233,6 +233,7 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=TOTAL_ROWS, help="total rows over all ranks (default: the workload's 4096)")
     ap.add_argument("--skip-extras", action="store_true", help="skip the e2e, CPU-baseline, small-batch and verify legs")
     ap.add_argument("--verify-only", action="store_true", help="run only the DSpark verify / draft legs (plain launches first, then the timed graphs)")
+    ap.add_argument("--head-only", action="store_true", help="run only the lm_head legs (the projection alone, and the decode tail behind it)")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -253,6 +254,10 @@ def main() -> None:
     if args.verify_only:
         if rank == 0:
             print(json.dumps({"verify": bench_verify(torch, lm, dev)}))
+        return
+    if args.head_only:
+        if rank == 0:
+            print(json.dumps({"lm_head": bench_lm_head(torch, lm, dev)}))
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
@@ -383,6 +388,7 @@ def main() -> None:
             out["cpu_baseline"]["rows_compared"] = int(rows)
             out["config1"] = bench_config1(torch, lm, dev)
             out["config5_single_gpu"] = bench_config5_single(torch, lm, dev)
+            out["lm_head"] = bench_lm_head(torch, lm, dev)
     if world > 1 and not args.skip_extras:
         out["vocab_parallel"] = bench_vocab_parallel(torch, dist, lm, dev, rank, world, args.warmup)
     if rank == 0:
@@ -438,6 +444,34 @@ def bench_config1(torch, lm, dev):
     stochastic = _graph_us(torch, dev, [(lambda i=i: lm.sample(z[i:i + 1], p, uniforms=u[i:i + 1], out=out)) for i in range(n)])
     return {"workload": "1 row x 151936 fp32, 8 spikes at +12", "greedy_us": greedy, "stochastic_us": stochastic,
             "timing": f"CUDA graph of {n} calls on {n} different rows ({n * VOCAB * 4 >> 20} MiB), min of 8 replays"}
+
+
+def bench_lm_head(torch, lm, dev):
+    """The vocabulary projection in front of the sampler (the reference's lm_head op: 8 rows of a speculative round, hidden 4096,
+    151936 x 4096 BF16 weights = 1.24 GB, larger than L2, read once per call; final norm fused), alone and as the head of the
+    decode tail: projection, sampler on its 8 rows of logits (thresholds and row statistics), stochastic verification."""
+    g = torch.Generator(device=dev); g.manual_seed(SEED)
+    rows, hidden = 8, 4096
+    x = torch.randn(rows, hidden, generator=g, device=dev).to(torch.bfloat16)
+    w = (torch.randn(VOCAB, hidden, generator=g, device=dev) * 0.03).to(torch.bfloat16)
+    gamma = (torch.randn(hidden, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    logits = torch.empty(rows, VOCAB, dtype=torch.bfloat16, device=dev)
+    head_us = _graph_us(torch, dev, [lambda: lm.lm_head(x, w, gamma, out=logits)] * 8)
+    drafts = torch.randint(0, VOCAB, (7,), generator=g, device=dev, dtype=torch.int32)
+    q = torch.softmax(torch.randn(7, VOCAB, generator=g, device=dev) * 2.0, dim=-1)
+    ua, uf, u8 = torch.rand(7, generator=g, device=dev), torch.rand(1, generator=g, device=dev), torch.full((8,), 0.5, device=dev)
+    p = lm.SamplingParams(temperature=0.8, top_k=50, top_p=0.95, draw="inverse_cdf")
+
+    def tail():
+        lm.lm_head(x, w, gamma, out=logits)
+        r = lm.sample(logits, p, uniforms=u8, return_tau=True, return_vmax=True)
+        lm.verify(logits, drafts, q, ua, uf, "stochastic", temperature=0.8, tau=r.tau, target_vmax=r.vmax, target_mass=r.mass)
+    tail_us = _graph_us(torch, dev, [tail] * 8)
+    weight_bytes = VOCAB * hidden * 2
+    return {"workload": f"{rows} rows x hidden {hidden} -> {VOCAB} logits, BF16 weights ({weight_bytes >> 20} MiB, read once per call), RMSNorm fused",
+            "us_per_call": head_us, "weight_gbs": weight_bytes / (head_us * 1e-6) / 1e9, "frac_of_peak": weight_bytes / (head_us * 1e-6) / 1e9 / peaks()[0],
+            "decode_tail_us": tail_us, "decode_tail": "lm_head -> lm_sample (8 rows, top_k 50, top_p 0.95, row statistics out) -> lm_verify (stochastic, statistics in)",
+            "timing": "CUDA graph of 8 calls, min of 8 replays"}
 
 
 def bench_config5_single(torch, lm, dev):

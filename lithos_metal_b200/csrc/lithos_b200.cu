@@ -625,9 +625,10 @@ int lm_head(const lm_head_args* a) {
   const size_t smem = head_smem_bytes(P.hidden);
   rc = ensure_dynamic_smem(kSlotHead, reinterpret_cast<const void*>(lm_head_kernel), smem);
   if (rc != LM_OK) return rc;
-  const long long per_sm = smem + 1024 <= 75 * 1024 ? 3 : (smem + 1024 <= 113 * 1024 ? 2 : 1);     // blocks that fit one SM's shared memory
+  int per_sm = 1;                                                          // blocks of the kernel that one SM holds (registers and shared memory)
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lm_head_kernel, kHeadThreads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
   const long long tiles = (a->vocab + kHeadTile - 1) / kHeadTile, want = (tiles + kHeadWarps - 1) / kHeadWarps;
-  const int grid = static_cast<int>(want < per_sm * sms ? want : per_sm * sms);
+  const int grid = static_cast<int>(want < static_cast<long long>(per_sm) * sms ? want : static_cast<long long>(per_sm) * sms);
   lm_head_kernel<<<grid, kHeadThreads, smem, static_cast<cudaStream_t>(a->stream)>>>(P);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LM_OK : cuda_fail(e);

@@ -25,7 +25,7 @@ constexpr int kHeadTile = 16;                // vocabulary rows per warp tile (t
 constexpr int kHeadStep = 64;                // hidden elements per step: 32 bytes per thread and row, a whole 128-byte line per row and quad
 constexpr int kHeadPad = 8;                  // elements between the rows of x in shared memory beyond H: a 16-byte skew, so that the
                                              // 16-byte loads of a quarter warp (two rows, four offsets 32 bytes apart) fall on different banks
-constexpr int kHeadUnroll = 2;               // steps whose loads are in flight together (8 x 16 bytes per thread)
+constexpr int kHeadUnroll = 8;               // steps whose loads are in flight together (16 x 16 bytes per thread)
 
 struct HeadDev {
   const uint16_t* x; int64_t x_stride; int rows;
