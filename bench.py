@@ -391,6 +391,7 @@ def main() -> None:
             out["lm_head"] = bench_lm_head(torch, lm, dev)
     if world > 1 and not args.skip_extras:
         out["vocab_parallel"] = bench_vocab_parallel(torch, dist, lm, dev, rank, world, args.warmup)
+        out["tensor_parallel_decode_tail"] = bench_tp_tail(torch, dist, lm, dev, rank, world, args.warmup)
     if rank == 0:
         print(json.dumps(out))
     if world > 1:
@@ -537,6 +538,50 @@ def bench_vocab_parallel(torch, dist, lm, dev, rank, world, warmup):
             "rows_per_s": rows / (ms * 1e-3), "local_kernel_us": 1e3 * float(parts[0]), "allgather_us": 1e3 * float(parts[1]),
             "merge_kernel_us": 1e3 * float(parts[2]), "parts_timing": "each part between its own CUDA events with a synchronize per step (launch gaps included), max over ranks",
             "allgather_bytes_per_rank": int(rec.numel()), "records_per_row_and_rank": int(rec.shape[0] // rows),
+            "tokens_equal_single_gpu_on_every_rank": bool(same.item())}
+
+
+def bench_tp_tail(torch, dist, lm, dev, rank, world, warmup):
+    """The decode tail with the vocabulary projection split over the ranks (a tensor-parallel head): every rank projects the 8 rows onto
+    its own vocab/world rows of the 151936 x 4096 BF16 weight (lm_head on a shard gives the bits of the whole), then the vocab-parallel
+    sampler on the local logits (records, one all-gather, merge). Microseconds per step (CUDA events, max over ranks), and whether every
+    rank's tokens equal the single-GPU tail's (projection onto the whole weight, then lm_sample) computed on rank 0's GPU."""
+    from lithos_metal_b200 import parallel
+    rows, hidden = 8, 4096
+    g = torch.Generator(device=dev); g.manual_seed(SEED)                   # the same tensors on every rank; a rank keeps its shard of the weight
+    x = torch.randn(rows, hidden, generator=g, device=dev).to(torch.bfloat16)
+    gamma = (torch.randn(hidden, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    u = torch.rand(rows, generator=g, device=dev)
+    w = (torch.randn(VOCAB, hidden, generator=g, device=dev) * 0.03).to(torch.bfloat16)
+    p = lm.SamplingParams(temperature=0.8, top_k=50, top_p=0.95, draw="inverse_cdf")
+    one = lm.sample(lm.lm_head(x, w, gamma), p, uniforms=u).tokens
+    lo, width = parallel.shard_vocab(VOCAB, rank, world)
+    w_local = w[lo:lo + width].clone()
+    del w
+    sampler = parallel.VocabParallelSampler(p, VOCAB)
+    local = torch.empty(rows, width, dtype=torch.bfloat16, device=dev)
+
+    def step():
+        lm.lm_head(x, w_local, gamma, out=local)
+        return sampler.sample(local, uniforms=u)
+    for _ in range(max(3, warmup)):
+        r = step()
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    n = 20
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(n):
+        r = step()
+    b.record()
+    torch.cuda.synchronize(dev)
+    t = torch.tensor([a.elapsed_time(b) / n], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    same = torch.tensor([int(torch.equal(one, r.tokens))], device=dev)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    return {"workload": f"8 rows x hidden 4096 -> {VOCAB} logits over {world} ranks ({width} vocabulary rows each), then top_k 50 / top_p 0.95 sampling over the ranks",
+            "us_per_step": 1e3 * float(t.item()), "weight_bytes_per_rank": int(width * hidden * 2),
+            "timing": "20 steps between CUDA events (host launches included), max over ranks",
             "tokens_equal_single_gpu_on_every_rank": bool(same.item())}
 
 

@@ -10,7 +10,8 @@
 // shared memory, four mma.sync m16n8k16 (BF16 in, FP32 accumulate) whose k slots are fed in the order the loads deliver --
 // the same permutation of k on both operands, so the sums are over the same products. (The tensor-core instruction is here for
 // the 8 FMAs per weight, which the FP32 pipes could not do at the rate HBM delivers weights; its throughput is nowhere near a
-// limit.) The logits go to memory (2.4 MB for 8 x 151,936: they stay in L2 for the sampler that is launched behind).
+// limit.) Every vocabulary row's sum is formed in the same order wherever the row sits, so a shard of the weight gives the
+// bits of the whole. The logits go to memory (2.4 MB for 8 x 151,936: they stay in L2 for the sampler that is launched behind).
 #pragma once
 #include <cuda_bf16.h>
 
@@ -98,23 +99,20 @@ __global__ void __launch_bounds__(kHeadThreads) lm_head_kernel(HeadDev P) {
     const uint4* wb = reinterpret_cast<const uint4*>(P.w + static_cast<int64_t>(rb) * P.w_stride) + 2 * t;
     float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const int steps = H / kHeadStep;
-    // every tile starts its walk at another step (and wraps around): the rows of W lie a power of two apart, and tiles in step
-    // with one another would all ask the same memory channels at once
-    const int start = (tile * 5) % steps;
     for (int s0 = 0; s0 < steps; s0 += kHeadUnroll) {
       uint4 a[kHeadUnroll][2], b[kHeadUnroll][2];
 #pragma unroll
       for (int u = 0; u < kHeadUnroll; u++) {
-        const int s = (start + s0 + u) % steps;
-        if (s0 + u < steps) {                                             // streamed: every weight is used once
+        const int s = s0 + u;
+        if (s < steps) {                                             // streamed: every weight is used once
           a[u][0] = __ldcs(wa + 8 * s); a[u][1] = __ldcs(wa + 8 * s + 1);
           b[u][0] = __ldcs(wb + 8 * s); b[u][1] = __ldcs(wb + 8 * s + 1);
         } else { a[u][0] = a[u][1] = b[u][0] = b[u][1] = make_uint4(0u, 0u, 0u, 0u); }
       }
 #pragma unroll
       for (int u = 0; u < kHeadUnroll; u++) {
-        const int s = (start + s0 + u) % steps;
-        if (s0 + u >= steps) break;
+        const int s = s0 + u;
+        if (s >= steps) break;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
           const uint4 x = xrow[8 * s + h];

@@ -73,6 +73,20 @@ def test_the_decode_tail_projection_then_sampler():
     assert int(lm.argmax(logits[:1])[0]) == int(oracle.bf16_to_f32(host[0]).argmax())
 
 
+def test_a_vocabulary_shard_of_the_weight_gives_the_bits_of_the_whole():
+    """Tensor-parallel heads: every GPU projects onto its own rows of the weight; the logits must not depend on the split."""
+    rng = np.random.default_rng(9)
+    x = bf16(oracle.f32_to_bf16(rng.standard_normal((8, 512)).astype(np.float32)))
+    w = bf16(oracle.f32_to_bf16((rng.standard_normal((40000, 512)) * 0.07).astype(np.float32)))
+    whole = lm.lm_head(x, w)
+    for shards in (2, 3, 8):
+        parts = []
+        for s in range(shards):
+            lo, width = lm.parallel.shard_vocab(40000, s, shards)
+            parts.append(lm.lm_head(x, w[lo:lo + width]))
+        assert torch.equal(torch.cat(parts, dim=1).view(torch.int16), whole.view(torch.int16))
+
+
 def test_argument_checks():
     x = torch.zeros(2, 64, dtype=torch.bfloat16, device="cuda")
     w = torch.zeros(100, 64, dtype=torch.bfloat16, device="cuda")
