@@ -493,7 +493,7 @@ LM_API float lm_uniform01(uint64_t seed, uint32_t step, uint32_t t, uint32_t ind
  * (monolith/nn/lm_head.py:50-60; semantics monolith/nn/oracle.py:20-32): logits[r, v] = bf16(sum_k x[r, k] * weight[v, k]) in
  * FP32, x = the rows of `hidden` as they are (norm_weight NULL: already normalised) or bf16(hidden * rsqrt(mean(hidden^2) + eps) *
  * (one_plus ? 1 + norm_weight : norm_weight)). At most 8 rows (one token, or the rows of a speculative round): a matrix-vector
- * product bound by the weight stream. hidden_dim a multiple of 64; hidden, weight and their strides 16-byte aligned. The logits
+ * product bound by the weight stream. hidden_dim a multiple of 64, at most 12,736 (the rows sit in shared memory); hidden, weight and their strides 16-byte aligned. The logits
  * are what lm_sample / lm_argmax / lm_verify take next on the same stream (they are still in L2 then). Floating point: the FP32
  * sums are formed in another order than a reference's, so a logit may differ from it by one BF16 unit in the last place.
  */

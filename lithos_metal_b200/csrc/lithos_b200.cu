@@ -612,7 +612,7 @@ int lm_head(const lm_head_args* a) {
   if (a->rows < 0 || a->vocab < 0 || a->hidden_dim < 1) return LM_E_INVALID;
   if (a->rows == 0 || a->vocab == 0) return LM_OK;
   if (!a->hidden || !a->weight || !a->logits || a->hidden_stride < a->hidden_dim || a->weight_stride < a->hidden_dim || a->logits_stride < a->vocab) return LM_E_INVALID;
-  if (a->rows > LM_HEAD_MAX_ROWS || a->vocab > LM_MAX_VOCAB || (a->hidden_dim % kHeadStep) != 0 || a->hidden_dim > 16384) return LM_E_UNSUPPORTED;
+  if (a->rows > LM_HEAD_MAX_ROWS || a->vocab > LM_MAX_VOCAB || (a->hidden_dim % kHeadStep) != 0 || head_smem_bytes(static_cast<int>(a->hidden_dim < 65536 ? a->hidden_dim : 65536)) > 200 * 1024) return LM_E_UNSUPPORTED;   // the rows of x must fit shared memory (hidden up to 12,736)
   if ((reinterpret_cast<uintptr_t>(a->weight) & 15u) || (a->weight_stride % 8) != 0) return LM_E_UNSUPPORTED;      // 16-byte loads of the weights
   HeadDev P;
   P.x = static_cast<const uint16_t*>(a->hidden); P.x_stride = a->hidden_stride; P.rows = a->rows;
