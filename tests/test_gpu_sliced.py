@@ -151,3 +151,53 @@ def test_rows_that_do_not_start_on_a_16_byte_boundary():
     wide = torch.zeros(3, 40009, device="cuda")
     wide[:, 3:40004] = base                                                   # a view with a stride and an offset
     _check(wide[:, 3:40004], host, draw="inverse_cdf", temperature=0.7, top_k=20, top_p=0.95)
+
+
+def test_random_configurations_equal_the_exact_kernels():
+    """A sweep of seeded random calls (rows, vocabulary, dtype, knobs, draw, penalties, -inf masks, planted ties): the few-row path
+    against the same library with LM_FLAG_EXACT_ONLY (the generic kernel, which the other tests hold to the oracle), bit for bit;
+    a sample of the calls against the oracle itself."""
+    rng = np.random.default_rng(2024)
+    checked_with_oracle = 0
+    for trial in range(60):
+        rows = int(rng.integers(1, 33))
+        vocab = int(rng.choice([16384, 20000, 50257, 151936, 131073]))
+        dtype = "bf16" if (vocab % 8 == 0 and rng.random() < 0.6) else "f32"
+        z = (rng.standard_normal((rows, vocab)) * float(rng.uniform(0.5, 4.0))).astype(np.float32)
+        if rng.random() < 0.3:
+            z[rng.random((rows, vocab)) < float(rng.uniform(0.3, 0.97))] = -np.inf                # masked vocabulary
+            z[np.arange(rows), rng.integers(0, vocab, rows)] = 1.0                                # (never a row of nothing but -inf)
+        if rng.random() < 0.3:
+            r, n = int(rng.integers(0, rows)), int(rng.integers(2, 40))
+            z[r, rng.choice(vocab, n, replace=False)] = np.float32(z[r][np.isfinite(z[r])].max())  # ties at the top
+        if dtype == "bf16":
+            host = oracle.f32_to_bf16(z)
+            x = torch.from_numpy(host.view(np.int16)).cuda().view(torch.bfloat16)
+        else:
+            host, x = z, torch.from_numpy(z).cuda()
+        kw = dict(temperature=float(rng.uniform(0.2, 1.6)), top_k=int(rng.integers(1, 65)), top_p=float(rng.choice([0.0, 0.5, 0.9, 0.99])),
+                  min_p=float(rng.choice([0.0, 0.0, 0.02])), draw=str(rng.choice(["inverse_cdf", "gumbel"])), seed=int(rng.integers(0, 1 << 30)),
+                  topp_in_topk=bool(rng.random() < 0.2))
+        hist = None
+        if rng.random() < 0.4:
+            hist = rng.integers(0, vocab, (rows, int(rng.integers(1, 600)))).astype(np.int32)
+            kw.update(repetition_penalty=float(rng.uniform(1.0, 1.5)), presence_penalty=float(rng.uniform(0.0, 1.0)))
+        u = rng.random(rows).astype(np.float32)
+        step, off = int(rng.integers(0, 100)), int(rng.integers(0, 1000))
+        args = dict(history=None if hist is None else torch.from_numpy(hist).cuda(), uniforms=torch.from_numpy(u).cuda(), step=step, row_offset=off,
+                    return_tau=True, return_status=True)
+        fast = lm.sample(x, lm.SamplingParams(**kw), **args)
+        exact = lm.sample(x, lm.SamplingParams(exact_only=True, **kw), **args)
+        st = fast.status.cpu().numpy()
+        assert np.all(st & (SLICED | GENERIC)), (trial, st)                                        # every row took the path (or was handed on by it)
+        tie = ((st | exact.status.cpu().numpy()) & 4) != 0                                         # Gumbel keys within 4e-6 of one another: flagged, not compared
+        assert fast.tau.cpu().numpy().tobytes() == exact.tau.cpu().numpy().tobytes(), (trial, kw, rows, vocab, dtype)
+        assert np.all((fast.tokens.cpu().numpy() == exact.tokens.cpu().numpy()) | tie), (trial, kw, rows, vocab, dtype)
+        if trial % 10 == 0 and vocab <= 60000:
+            tok, tau, _ = oracle.sample_batch(host, temperature=kw["temperature"], top_k=kw["top_k"], top_p=kw["top_p"], min_p=kw["min_p"],
+                                              topp_in_topk=kw["topp_in_topk"], history=hist, repetition_penalty=kw.get("repetition_penalty", 1.0),
+                                              presence_penalty=kw.get("presence_penalty", 0.0), draw=kw["draw"], uniforms=u, seed=kw["seed"], step=step,
+                                              row_offset=off, n_threads=8)
+            assert fast.tau.cpu().numpy().tobytes() == tau.tobytes() and np.all((fast.tokens.cpu().numpy() == tok) | tie), trial
+            checked_with_oracle += 1
+    assert checked_with_oracle >= 2
