@@ -54,6 +54,10 @@ class CudaVocabBackend:
     def record_bytes(self, cap: int) -> int:
         return int(_lib.lib().lm_vocab_record_bytes(cap))
 
+    def pieces(self, shards: int, cap: int, width: int) -> int:
+        """Records per row that the local step leaves for a shard of ``width`` logits when ``shards`` GPUs take part."""
+        return int(_lib.lib().lm_vocab_pieces(int(shards), int(cap), int(width)))
+
     def _fill(self, a, p: SamplingParams, rows: int, dev, keep):
         ptr, s, t = _knob(p.temperature, rows, torch.float32, dev, "temperature"); a.temperature, a.temperature_s = ptr, float(s); keep.append(t)
         ptr, s, t = _knob(p.top_k, rows, torch.int32, dev, "top_k"); a.top_k, a.top_k_s = ptr, int(s); keep.append(t)
@@ -65,7 +69,7 @@ class CudaVocabBackend:
         the merge still takes together with the other ``shards - 1`` GPUs' pieces, so that the local step spreads over the GPU."""
         logits = _check_logits(logits)
         rows, width = logits.shape
-        pieces = int(_lib.lib().lm_vocab_pieces(int(shards), int(cap), int(width)))
+        pieces = self.pieces(shards, cap, width)
         rec = torch.empty(pieces * rows, self.record_bytes(cap), dtype=torch.uint8, device=logits.device)
         a = _lib.VocabArgs()
         a.struct_size = C.sizeof(_lib.VocabArgs)
@@ -129,6 +133,11 @@ class VocabParallelSampler:
         if self.cap > limit:
             raise ValueError(f"top_k {k_max} over {self.world} shards needs {self.cap} candidates per shard and row; the merge takes {limit}")
         self.shard_start, self.shard_width = shard_vocab(self.vocab, self.rank, self.world)
+        # When the local step cuts the shard into pieces, a piece's record needs room for twice the top_k only (its bound lets a few
+        # logits more than top_k through), not for top_k + 64: smaller records, a smaller all-gather.
+        pieces_of = getattr(self.backend, "pieces", None)
+        if pieces_of is not None and pieces_of(self.world, self.cap, self.shard_width) > 1:
+            self.cap = min(self.cap, max(16, (2 * k_max + 7) // 8 * 8))
 
     def sample(self, local_logits: torch.Tensor, uniforms: Optional[torch.Tensor] = None, step: int = 0, row_offset: int = 0) -> SampleOutput:
         if local_logits.shape[1] != self.shard_width:

@@ -143,6 +143,21 @@ def test_invalid_vocab_parallel_requests():
     assert torch.equal(s.sample(x, uniforms=u).tokens, lm.sample(x, s.params, uniforms=u).tokens)      # one shard: the plain sampler
 
 
+def test_the_sampler_object_with_pieces_and_small_records():
+    """VocabParallelSampler on one rank (its records all-gathered with nobody): the shard is cut into pieces, whose records hold twice
+    the top_k instead of top_k + 64; the result is the plain sampler's."""
+    rng = np.random.default_rng(58)
+    x = bf16_tensor(oracle.f32_to_bf16((rng.standard_normal((12, 151936)) * 2).astype(np.float32)))
+    u = torch.from_numpy(rng.random(12).astype(np.float32)).cuda()
+    for k in (8, 20, 50, 64):
+        p = lm.SamplingParams(temperature=0.8, top_k=k, top_p=0.9, draw="inverse_cdf")
+        s = parallel.VocabParallelSampler(p, 151936, rank=0, world=1)
+        assert s.cap == max(16, (2 * k + 7) // 8 * 8) and s.backend.pieces(1, s.cap, 151936) == 64
+        r = s.sample(x, uniforms=u)
+        one = lm.sample(x, lm.SamplingParams(exact_only=True, temperature=0.8, top_k=k, top_p=0.9, draw="inverse_cdf"), uniforms=u, return_tau=True)
+        assert torch.equal(r.tokens, one.tokens) and torch.equal(r.tau, one.tau) and int(r.status.max()) & 32 == 0
+
+
 def test_random_configurations_equal_the_exact_kernel():
     """Seeded random calls (shards, vocabulary, dtype, knobs, draw, -inf masks): local step (in pieces or not) + merge against the
     single-GPU generic kernel on the whole rows, bit for bit."""
