@@ -558,7 +558,7 @@ def bench_tp_tail(torch, dist, lm, dev, rank, world, warmup):
     lo, width = parallel.shard_vocab(VOCAB, rank, world)
     w_local = w[lo:lo + width].clone()
     del w
-    sampler = parallel.VocabParallelSampler(p, VOCAB)
+    sampler = parallel.VocabParallelSampler(p, VOCAB, reuse_buffers=True)
     local = torch.empty(rows, width, dtype=torch.bfloat16, device=dev)
 
     def step():

@@ -64,13 +64,15 @@ class CudaVocabBackend:
         ptr, s, t = _knob(p.top_p, rows, torch.float32, dev, "top_p"); a.top_p, a.top_p_s = ptr, float(s); keep.append(t)
         ptr, s, t = _knob(p.min_p, rows, torch.float32, dev, "min_p"); a.min_p, a.min_p_s = ptr, float(s); keep.append(t)
 
-    def local(self, logits: torch.Tensor, shard_start: int, p: SamplingParams, cap: int, shards: int = 1) -> torch.Tensor:
+    def local(self, logits: torch.Tensor, shard_start: int, p: SamplingParams, cap: int, shards: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """This GPU's records, [pieces * rows, record bytes]: the shard is cut into as many pieces (each with a record per row) as
         the merge still takes together with the other ``shards - 1`` GPUs' pieces, so that the local step spreads over the GPU."""
         logits = _check_logits(logits)
         rows, width = logits.shape
         pieces = self.pieces(shards, cap, width)
-        rec = torch.empty(pieces * rows, self.record_bytes(cap), dtype=torch.uint8, device=logits.device)
+        rec = out if out is not None else torch.empty(pieces * rows, self.record_bytes(cap), dtype=torch.uint8, device=logits.device)
+        if rec.shape != (pieces * rows, self.record_bytes(cap)) or rec.dtype != torch.uint8 or not rec.is_contiguous():
+            raise ValueError("local: out must be a contiguous uint8 tensor [pieces * rows, record bytes]")
         a = _lib.VocabArgs()
         a.struct_size = C.sizeof(_lib.VocabArgs)
         a.dtype, a.logits, a.rows, a.vocab_local, a.row_stride, a.shard_start = _dtype_code(logits), logits.data_ptr(), rows, width, _row_stride(logits), shard_start
@@ -82,7 +84,7 @@ class CudaVocabBackend:
             _lib.check(_lib.lib().lm_vocab_local(C.byref(a)), "lm_vocab_local")
         return rec
 
-    def merge(self, gathered: torch.Tensor, p: SamplingParams, cap: int, uniforms: Optional[torch.Tensor], step: int, row_offset: int):
+    def merge(self, gathered: torch.Tensor, p: SamplingParams, cap: int, uniforms: Optional[torch.Tensor], step: int, row_offset: int, out=None):
         shards, rows, _ = gathered.shape
         dev = gathered.device
         a = _lib.VocabArgs()
@@ -96,9 +98,12 @@ class CudaVocabBackend:
             uniforms = uniforms.to(device=dev, dtype=torch.float32).contiguous()
             a.uniforms = uniforms.data_ptr()
         a.seed, a.step, a.row_offset = int(p.seed) & (2**64 - 1), int(step) & 0xFFFFFFFF, int(row_offset)
-        tokens = torch.empty(rows, dtype=torch.int32, device=dev)
-        tau = torch.empty(rows, dtype=torch.float32, device=dev)
-        status = torch.empty(rows, dtype=torch.int32, device=dev)
+        if out is not None:
+            tokens, tau, status = out                                      # [rows] int32 / float32 / int32 on the records' device
+        else:
+            tokens = torch.empty(rows, dtype=torch.int32, device=dev)
+            tau = torch.empty(rows, dtype=torch.float32, device=dev)
+            status = torch.empty(rows, dtype=torch.int32, device=dev)
         a.out_tokens, a.out_tau, a.out_status = tokens.data_ptr(), tau.data_ptr(), status.data_ptr()
         a.stream = torch.cuda.current_stream(dev).cuda_stream
         with torch.cuda.device(dev):
@@ -114,8 +119,12 @@ class VocabParallelSampler:
     in this mode.
     """
 
-    def __init__(self, params: SamplingParams, vocab: int, group=None, backend=None, rank: Optional[int] = None, world: Optional[int] = None):
+    def __init__(self, params: SamplingParams, vocab: int, group=None, backend=None, rank: Optional[int] = None, world: Optional[int] = None,
+                 reuse_buffers: bool = False):
+        """``reuse_buffers``: keep the record, gather and result tensors between calls of the same shape (a decode loop: no allocation per
+        step; a call's results are then overwritten by the next call's)."""
         self.params, self.vocab, self.group = params, int(vocab), group
+        self._reuse, self._buffers = bool(reuse_buffers), {}
         self.rank = dist.get_rank(group) if rank is None else rank
         self.world = dist.get_world_size(group) if world is None else world
         self.backend = backend if backend is not None else CudaVocabBackend()
@@ -145,12 +154,25 @@ class VocabParallelSampler:
         if self.params.draw == "inverse_cdf" and uniforms is None:
             raise ValueError("draw='inverse_cdf' needs uniforms [rows]")
         rows = local_logits.shape[0]
-        rec = self.backend.local(local_logits, self.shard_start, self.params, self.cap, self.world)   # [pieces * rows, record bytes]
-        flat = torch.empty(self.world * rec.shape[0], rec.shape[1], dtype=rec.dtype, device=rec.device)   # shard-major: [shard][piece][row]
+        kept = self._buffers.get((rows, local_logits.device)) if self._reuse else None
+        if kept is None:
+            rec = self.backend.local(local_logits, self.shard_start, self.params, self.cap, self.world)   # [pieces * rows, record bytes]
+            flat = torch.empty(self.world * rec.shape[0], rec.shape[1], dtype=rec.dtype, device=rec.device)   # shard-major: [shard][piece][row]
+            out = None
+            if self._reuse and rec.is_cuda:
+                out = (torch.empty(rows, dtype=torch.int32, device=rec.device), torch.empty(rows, dtype=torch.float32, device=rec.device),
+                       torch.empty(rows, dtype=torch.int32, device=rec.device))
+                self._buffers[(rows, local_logits.device)] = (rec, flat, out)
+        else:
+            rec, flat, out = kept
+            self.backend.local(local_logits, self.shard_start, self.params, self.cap, self.world, out=rec)
         if self.world > 1:
             dist.all_gather_into_tensor(flat, rec, group=self.group)           # the one exchange of the step
         else:
             flat.copy_(rec)
         gathered = flat.view(-1, rows, rec.shape[1])                           # every piece of every shard is a shard of the merge
-        tokens, tau, status = self.backend.merge(gathered, self.params, self.cap, uniforms, step, row_offset)
+        if out is not None:
+            tokens, tau, status = self.backend.merge(gathered, self.params, self.cap, uniforms, step, row_offset, out=out)
+        else:
+            tokens, tau, status = self.backend.merge(gathered, self.params, self.cap, uniforms, step, row_offset)
         return SampleOutput(tokens, tau=tau, status=status)

@@ -156,6 +156,10 @@ def test_the_sampler_object_with_pieces_and_small_records():
         r = s.sample(x, uniforms=u)
         one = lm.sample(x, lm.SamplingParams(exact_only=True, temperature=0.8, top_k=k, top_p=0.9, draw="inverse_cdf"), uniforms=u, return_tau=True)
         assert torch.equal(r.tokens, one.tokens) and torch.equal(r.tau, one.tau) and int(r.status.max()) & 32 == 0
+        kept = parallel.VocabParallelSampler(p, 151936, rank=0, world=1, reuse_buffers=True)       # the same with its buffers kept between calls
+        for _ in range(2):
+            r2 = kept.sample(x, uniforms=u)
+            assert torch.equal(r2.tokens, one.tokens) and torch.equal(r2.tau, one.tau)
 
 
 def test_random_configurations_equal_the_exact_kernel():
