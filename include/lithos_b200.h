@@ -362,9 +362,10 @@ LM_API int lm_vocab_local(const lm_vocab_args* args);
 LM_API int lm_vocab_merge(const lm_vocab_args* args);
 LM_API size_t lm_vocab_record_bytes(int32_t cap);
 LM_API int32_t lm_vocab_candidate_cap(int32_t top_k);
-/* How many pieces (records per row) the local step may cut a shard of vocab_local logits into when `shards` GPUs take part: with
- * one block per piece the local step spreads over the GPU. The merge then sees shards * pieces shards. */
-LM_API int32_t lm_vocab_pieces(int32_t shards, int32_t cap, int64_t vocab_local);
+/* How many pieces (records per row) the local step should cut a shard of vocab_local logits into when `shards` GPUs take part and
+ * the call has `rows` rows: with one block per piece the local step spreads over the GPU, at the price of more bytes to gather. The
+ * merge then sees shards * pieces shards. */
+LM_API int32_t lm_vocab_pieces(int32_t shards, int32_t cap, int64_t vocab_local, int64_t rows);
 
 /*
  * The scalar step-closing kernels, on the reference's StepState buffer (monolith/core/step_state.py:38-62: 4-byte fields in the

@@ -164,7 +164,7 @@ def lib():
         L.lm_head.restype = C.c_int
         L.lm_head.argtypes = [C.POINTER(HeadArgs)]
         L.lm_vocab_pieces.restype = C.c_int32
-        L.lm_vocab_pieces.argtypes = [C.c_int32, C.c_int32, C.c_int64]
+        L.lm_vocab_pieces.argtypes = [C.c_int32, C.c_int32, C.c_int64, C.c_int64]
         for fn in (L.lm_accept_scan, L.lm_verify_select, L.lm_advance):
             fn.restype, fn.argtypes = C.c_int, [C.POINTER(StepArgs)]
         L.lm_step_state_bytes.restype = C.c_size_t

@@ -511,15 +511,22 @@ size_t lm_vocab_record_bytes(int32_t cap) { return cap > 0 ? static_cast<size_t>
 
 int32_t lm_vocab_candidate_cap(int32_t top_k) { return top_k > 0 ? (top_k + 64 + 7) / 8 * 8 : 0; }
 
-// Pieces a shard is cut into by the local step (each with a record of its own): the most that the merge still takes with the
-// other shards' (shards * pieces <= 64 records per row, cap <= 8 * (1024 / (shards * pieces))), pieces of at least 2048 logits,
-// and only for records of at most 128 candidates (a top_k up to 64): beyond that the piece's bound, taken from its threads'
-// maxima, is no longer close to its k-th largest logit.
-int32_t lm_vocab_pieces(int32_t shards, int32_t cap, int64_t vocab_local) {
+// Pieces a shard is cut into by the local step (each with a record of its own). As many as the merge still takes with the other
+// shards' (shards * pieces <= 64 records per row, cap <= 8 * (1024 / (shards * pieces))), pieces of at least 2048 logits, and only
+// for records of at most 128 candidates (a top_k up to 64): beyond that a piece's bound, taken from its threads' maxima, is no
+// longer close to its k-th largest logit. More pieces also mean more bytes in the all-gather behind the step, which soon costs more
+// than the local step gains: beyond the pieces a shard needs for its length (at most 32768 logits each), no more than keep the
+// gathered records of all GPUs and rows under 1 MB.
+int32_t lm_vocab_pieces(int32_t shards, int32_t cap, int64_t vocab_local, int64_t rows) {
   if (shards < 1 || cap < 1 || cap > 128 || vocab_local < 1) return 1;
+  if (rows < 1) rows = 1;
+  int32_t need = 1;                                                        // the fewest pieces that fit the slice kernel
+  while (vocab_local / need > kSliceMaxLen) need *= 2;
+  const int64_t record = static_cast<int64_t>(lm_vocab_record_bytes(cap));
   int32_t p = 1;
-  while (2 * p * shards <= kVpMaxShards && cap <= kVpPerThread * (kVpMaxCandidates / (2 * p * shards)) && vocab_local / (2 * p) >= 2048) p *= 2;
-  return p;
+  while (2 * p * shards <= kVpMaxShards && cap <= kVpPerThread * (kVpMaxCandidates / (2 * p * shards)) && vocab_local / (2 * p) >= 2048 &&
+         (2 * p <= need || static_cast<int64_t>(2 * p) * shards * rows * record <= (1 << 20))) p *= 2;
+  return p >= need ? p : 1;
 }
 
 int lm_vocab_local(const lm_vocab_args* a) {
@@ -554,7 +561,8 @@ int lm_vocab_local(const lm_vocab_args* a) {
     const size_t slice_smem = slice_smem_bytes(S.slice_len);
     cudaStream_t st = static_cast<cudaStream_t>(a->stream);
     // threads per piece as on the few-row path; a record of cap candidates serves a top_k up to cap - 64
-    const int threads = static_cast<long long>(S.slices) * P.rows <= sms ? kSliceBlockBig : (a->cap - 64 <= kSliceTinyMaxK ? kSliceBlockTiny : kSliceBlockSmall);
+    const int threads = (static_cast<long long>(S.slices) * P.rows <= sms || S.slice_len >= 8192) ? kSliceBlockBig
+                        : (a->cap - 64 <= kSliceTinyMaxK ? kSliceBlockTiny : kSliceBlockSmall);      // (long pieces: many logits per thread otherwise)
     int rs;
     if (threads == kSliceBlockBig) {
       rs = ensure_dynamic_smem(kSlotSlice, reinterpret_cast<const void*>(slice_local_kernel<kSliceBlockBig>), slice_smem);

@@ -54,9 +54,9 @@ class CudaVocabBackend:
     def record_bytes(self, cap: int) -> int:
         return int(_lib.lib().lm_vocab_record_bytes(cap))
 
-    def pieces(self, shards: int, cap: int, width: int) -> int:
-        """Records per row that the local step leaves for a shard of ``width`` logits when ``shards`` GPUs take part."""
-        return int(_lib.lib().lm_vocab_pieces(int(shards), int(cap), int(width)))
+    def pieces(self, shards: int, cap: int, width: int, rows: int = 1) -> int:
+        """Records per row that the local step leaves for a shard of ``width`` logits when ``shards`` GPUs take part in a call of ``rows`` rows."""
+        return int(_lib.lib().lm_vocab_pieces(int(shards), int(cap), int(width), int(rows)))
 
     def _fill(self, a, p: SamplingParams, rows: int, dev, keep):
         ptr, s, t = _knob(p.temperature, rows, torch.float32, dev, "temperature"); a.temperature, a.temperature_s = ptr, float(s); keep.append(t)
@@ -69,7 +69,7 @@ class CudaVocabBackend:
         the merge still takes together with the other ``shards - 1`` GPUs' pieces, so that the local step spreads over the GPU."""
         logits = _check_logits(logits)
         rows, width = logits.shape
-        pieces = self.pieces(shards, cap, width)
+        pieces = self.pieces(shards, cap, width, rows)
         rec = out if out is not None else torch.empty(pieces * rows, self.record_bytes(cap), dtype=torch.uint8, device=logits.device)
         if rec.shape != (pieces * rows, self.record_bytes(cap)) or rec.dtype != torch.uint8 or not rec.is_contiguous():
             raise ValueError("local: out must be a contiguous uint8 tensor [pieces * rows, record bytes]")

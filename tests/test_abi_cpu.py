@@ -69,9 +69,11 @@ def test_argument_validation_needs_no_device():
     assert L.lm_argmax(None, 0, 0, 10, 10, None, None, 0, None) == 0
     assert L.lm_argmax(None, 0, 2, 10, 10, None, None, 0, None) == -1
     assert L.lm_workspace_bytes(256, 151936) >= 256 * 16 and L.lm_verify_workspace_bytes(7, 151936) > 0
-    # pieces of a vocabulary shard: as many as the merge takes with the other GPUs' (64 records of up to 128 candidates per row), none for large records or short shards
-    assert [L.lm_vocab_pieces(s, 120, 262144 // s) for s in (2, 4, 8)] == [32, 16, 8]
-    assert L.lm_vocab_pieces(8, 568, 32768) == 1 and L.lm_vocab_pieces(4, 120, 2048) == 1 and L.lm_vocab_pieces(3, 72, 100000) == 16
+    # pieces of a vocabulary shard: as many as the merge takes with the other GPUs' (64 records of up to 128 candidates per row), none for
+    # large records or short shards; for many rows only as many as keep the records to gather small (or as the shard's length needs)
+    assert [L.lm_vocab_pieces(s, 120, 262144 // s, 1) for s in (2, 4, 8)] == [32, 16, 8]
+    assert [L.lm_vocab_pieces(s, 104, 262144 // s, 64) for s in (2, 4, 8)] == [8, 4, 2]
+    assert L.lm_vocab_pieces(8, 568, 32768, 1) == 1 and L.lm_vocab_pieces(4, 120, 2048, 1) == 1 and L.lm_vocab_pieces(3, 72, 100000, 1) == 16
 
 
 def test_host_hash_equals_the_oracle():

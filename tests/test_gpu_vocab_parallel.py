@@ -152,7 +152,7 @@ def test_the_sampler_object_with_pieces_and_small_records():
     for k in (8, 20, 50, 64):
         p = lm.SamplingParams(temperature=0.8, top_k=k, top_p=0.9, draw="inverse_cdf")
         s = parallel.VocabParallelSampler(p, 151936, rank=0, world=1)
-        assert s.cap == max(16, (2 * k + 7) // 8 * 8) and s.backend.pieces(1, s.cap, 151936) == 64
+        assert s.cap == max(16, (2 * k + 7) // 8 * 8) and s.backend.pieces(1, s.cap, 151936, 12) == 64
         r = s.sample(x, uniforms=u)
         one = lm.sample(x, lm.SamplingParams(exact_only=True, temperature=0.8, top_k=k, top_p=0.9, draw="inverse_cdf"), uniforms=u, return_tau=True)
         assert torch.equal(r.tokens, one.tokens) and torch.equal(r.tau, one.tau) and int(r.status.max()) & 32 == 0
