@@ -487,6 +487,35 @@ def bench_config5_single(torch, lm, dev):
             "frac_of_peak": 64 * 262144 * 2 / (us * 1e-6) / 1e9 / peaks()[0], "timing": "L2 flushed, min of 20"}
 
 
+def _peer_exchange_us(torch, dist, dev, make_sampler, step_of, expect, warmup, n=20):
+    """The same step with the records read in place from the peers' memory (symmetric memory over NVLink, a barrier over the ranks on
+    the stream, no collective): microseconds per step (max over ranks) and whether every rank's tokens are the expected ones; or why
+    not. Never raises: the all-gather figures stand on their own."""
+    try:
+        sampler = make_sampler()
+        r = None
+        for _ in range(max(3, warmup)):
+            r = step_of(sampler)
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            r = step_of(sampler)
+        b.record()
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([a.elapsed_time(b) / n], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        used = torch.tensor([int(any(v is not None for v in sampler._peer.values()))], device=dev)
+        same = torch.tensor([int(torch.equal(expect, r.tokens))], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        dist.all_reduce(used, op=dist.ReduceOp.MIN)
+        return {"us_per_step": 1e3 * float(t.item()), "tokens_equal_single_gpu_on_every_rank": bool(same.item()),
+                "records_read_in_place_from_peers": bool(used.item())}
+    except Exception as e:                                                  # (the ranks fail together or not at all: the setup is collective)
+        return {"unavailable": repr(e)[:200]}
+
+
 def bench_vocab_parallel(torch, dist, lm, dev, rank, world, warmup):
     """The vocab-parallel configuration (64 rows x 262144 BF16 logits N(0, 2^2), top_k 50, top_p 0.9, temperature 0.8), the
     vocabulary split over the ranks: per-step time of local kernel + NCCL all-gather + merge kernel (CUDA events, max over
@@ -538,7 +567,9 @@ def bench_vocab_parallel(torch, dist, lm, dev, rank, world, warmup):
             "rows_per_s": rows / (ms * 1e-3), "local_kernel_us": 1e3 * float(parts[0]), "allgather_us": 1e3 * float(parts[1]),
             "merge_kernel_us": 1e3 * float(parts[2]), "parts_timing": "each part between its own CUDA events with a synchronize per step (launch gaps included), max over ranks",
             "allgather_bytes_per_rank": int(rec.numel()), "records_per_row_and_rank": int(rec.shape[0] // rows),
-            "tokens_equal_single_gpu_on_every_rank": bool(same.item())}
+            "tokens_equal_single_gpu_on_every_rank": bool(same.item()),
+            "peer_records": _peer_exchange_us(torch, dist, dev, lambda: parallel.VocabParallelSampler(p, vocab, exchange="peer"),
+                                              lambda sm: sm.sample(shard, uniforms=u), one, warmup)}
 
 
 def bench_tp_tail(torch, dist, lm, dev, rank, world, warmup):
@@ -582,7 +613,9 @@ def bench_tp_tail(torch, dist, lm, dev, rank, world, warmup):
     return {"workload": f"8 rows x hidden 4096 -> {VOCAB} logits over {world} ranks ({width} vocabulary rows each), then top_k 50 / top_p 0.95 sampling over the ranks",
             "us_per_step": 1e3 * float(t.item()), "weight_bytes_per_rank": int(width * hidden * 2),
             "timing": "20 steps between CUDA events (host launches included), max over ranks",
-            "tokens_equal_single_gpu_on_every_rank": bool(same.item())}
+            "tokens_equal_single_gpu_on_every_rank": bool(same.item()),
+            "peer_records": _peer_exchange_us(torch, dist, dev, lambda: parallel.VocabParallelSampler(p, VOCAB, exchange="peer"),
+                                              lambda sm: (lm.lm_head(x, w_local, gamma, out=local), sm.sample(local, uniforms=u))[1], one, warmup)}
 
 
 def bench_verify(torch, lm, dev):

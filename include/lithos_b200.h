@@ -354,8 +354,11 @@ typedef struct lm_vocab_args {
   float* out_tau;              /* merge step, optional */
   uint32_t* out_status;        /* merge step, optional */
   void* stream;
-  int32_t pieces;              /* local step: records per row that this GPU's shard is cut into, 1 (or 0) or lm_vocab_pieces(...) */
+  int32_t pieces;              /* local step: records per row that this GPU's shard is cut into, 1 (or 0) or lm_vocab_pieces(...); merge step with record_ptrs: the same */
   int32_t pad_;
+  const void* record_ptrs;     /* merge step, optional: device array of shards / pieces addresses (as 64-bit integers), one per GPU in shard order: where that
+                                  GPU's [pieces][rows] records lie -- its own memory or a peer's mapping, read in place (plain loads) instead of a gathered
+                                  `records` array. The caller orders the GPUs' local steps before this call (a barrier over the GPUs on the stream). */
 } lm_vocab_args;
 
 LM_API int lm_vocab_local(const lm_vocab_args* args);

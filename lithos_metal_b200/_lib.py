@@ -105,7 +105,7 @@ class VocabArgs(C.Structure):
         ("top_p", C.c_void_p), ("top_p_s", C.c_float), ("min_p", C.c_void_p), ("min_p_s", C.c_float),
         ("flags", C.c_uint32), ("draw", C.c_int32), ("uniforms", C.c_void_p), ("seed", C.c_uint64), ("step", C.c_uint32), ("row_offset", C.c_int64),
         ("records", C.c_void_p), ("out_tokens", C.c_void_p), ("out_tau", C.c_void_p), ("out_status", C.c_void_p), ("stream", C.c_void_p),
-        ("pieces", C.c_int32), ("pad_", C.c_int32),
+        ("pieces", C.c_int32), ("pad_", C.c_int32), ("record_ptrs", C.c_void_p),
     ]
 
 

@@ -330,6 +330,7 @@ int lm_sample(const lm_sample_args* a) {
       cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return cuda_fail(e);
       VpMergeDev M;
+      M.bases = nullptr; M.pieces = 1;
       M.records = S.records; M.shards = S.slices; M.rows = P.rows; M.cap = S.cap; M.record_bytes = S.record_bytes;
       M.temperature = nullptr; M.temperature_s = a->temperature_s; M.top_k = nullptr; M.top_k_s = a->top_k_s;
       M.top_p = a->top_p; M.top_p_s = a->top_p_s; M.min_p = a->min_p; M.min_p_s = a->min_p_s;
@@ -592,13 +593,15 @@ int lm_vocab_merge(const lm_vocab_args* a) {
   if (a->rows < 0 || a->shards < 1 || a->cap < 1) return LM_E_INVALID;
   if (a->draw != LM_DRAW_GUMBEL && a->draw != LM_DRAW_INVERSE_CDF) return LM_E_INVALID;
   if (a->rows == 0) return LM_OK;
-  if (!a->records || !a->out_tokens) return LM_E_INVALID;
+  if ((!a->records && !a->record_ptrs) || !a->out_tokens) return LM_E_INVALID;
   if (a->temperature == nullptr && !(a->temperature_s > 0.0f)) return LM_E_INVALID;
   if (a->top_k == nullptr && a->top_k_s < 1) return LM_E_INVALID;
   if (a->draw == LM_DRAW_INVERSE_CDF && a->uniforms == nullptr) return LM_E_INVALID;
   if (a->shards > kVpMaxShards || a->cap > kVpPerThread * (kVpMaxCandidates / a->shards) || a->rows > 0x7FFFFFFF) return LM_E_UNSUPPORTED;
   VpMergeDev P;
   P.records = static_cast<const unsigned char*>(a->records); P.shards = a->shards; P.rows = static_cast<int>(a->rows); P.cap = a->cap;
+  P.bases = static_cast<const unsigned long long*>(a->record_ptrs); P.pieces = a->pieces > 0 ? a->pieces : 1;
+  if (P.bases && (a->shards % P.pieces) != 0) return LM_E_INVALID;
   P.record_bytes = static_cast<int64_t>(lm_vocab_record_bytes(a->cap));
   P.temperature = a->temperature; P.temperature_s = a->temperature_s; P.top_k = a->top_k; P.top_k_s = a->top_k_s;
   P.top_p = a->top_p; P.top_p_s = a->top_p_s; P.min_p = a->min_p; P.min_p_s = a->min_p_s;

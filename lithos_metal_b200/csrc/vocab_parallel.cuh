@@ -167,7 +167,9 @@ __device__ uint32_t kth_key_bound_in_span(const uint32_t (&keys)[PER], uint32_t 
 }
 
 struct VpMergeDev {
-  const unsigned char* records;      // [shards][rows] records, as the all-gather leaves them
+  const unsigned char* records;      // [shards][rows] records, as the all-gather leaves them; or, with `bases`, unused
+  const unsigned long long* bases;   // per GPU, the address of its [pieces][rows] records (its own memory or a peer's, read in place); or null
+  int pieces;                        // with `bases`: records per row and GPU (shard s of the merge = piece s % pieces of GPU s / pieces)
   int shards; int rows; int cap; int64_t record_bytes;
   const float* temperature; float temperature_s; const int32_t* top_k; int32_t top_k_s;
   const float* top_p; float top_p_s; const float* min_p; float min_p_s;
@@ -195,6 +197,15 @@ struct VpMergeSmem {
 // i holding candidate i (E = 1: up to 32) or candidates i and 32 + i (E = 2), with shuffles and votes where the block-wide code below needs barriers. The same arithmetic in
 // the same order (the block-wide prefix sums reduce to those of warps 0 and 1). Sets s.amb instead of writing when the row has to be
 // handed on.
+// Where the record of (shard, row) lies: in the gathered array, or in place in the memory of the GPU that wrote it.
+__device__ __forceinline__ const unsigned char* merge_record(const VpMergeDev& P, int shard, int row) {
+  if (P.bases) {
+    const int gpu = shard / P.pieces, piece = shard - gpu * P.pieces;
+    return reinterpret_cast<const unsigned char*>(P.bases[gpu]) + (static_cast<int64_t>(piece) * P.rows + row) * P.record_bytes;
+  }
+  return P.records + (static_cast<int64_t>(shard) * P.rows + row) * P.record_bytes;
+}
+
 template <int E>
 __device__ void merge_tail_one_warp(const VpMergeDev& P, int row, VpMergeSmem& s, int N, float T, int top_k, float top_p, float min_p, double inv_t,
                                     uint32_t status0) {
@@ -361,7 +372,7 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
   for (int i = 0; i < kVpPerThread; i++) { pv[i] = 0.0f; pi[i] = 0; }
   int cnt = 0;
   if (g < P.shards) {
-    const unsigned char* rec = P.records + (static_cast<int64_t>(g) * P.rows + row) * P.record_bytes;
+    const unsigned char* rec = merge_record(P, g, row);
     const float* rv = reinterpret_cast<const float*>(rec + kVpHeader);
     const int32_t* ri = reinterpret_cast<const int32_t*>(rec + kVpHeader + 4 * static_cast<size_t>(P.cap));
     cnt = *reinterpret_cast<const int32_t*>(rec + 16);
@@ -375,7 +386,7 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
   if (warp == 0) {
     int n2 = 0; uint32_t st = 0u;
     for (int q = lane; q < P.shards; q += 32) {
-      const unsigned char* rec = P.records + (static_cast<int64_t>(q) * P.rows + row) * P.record_bytes;
+      const unsigned char* rec = merge_record(P, q, row);
       n2 += *reinterpret_cast<const int32_t*>(rec + 16);
       st |= *reinterpret_cast<const uint32_t*>(rec + 20);
     }
@@ -391,7 +402,7 @@ __device__ bool vocab_merge_row(const VpMergeDev& P, int row, VpMergeSmem& s) {
       const int q = lane + 32 * e;
       hv[e] = -INFINITY; hm[e] = 0.0;
       if (q < P.shards) {
-        const unsigned char* rec = P.records + (static_cast<int64_t>(q) * P.rows + row) * P.record_bytes;
+        const unsigned char* rec = merge_record(P, q, row);
         hv[e] = *reinterpret_cast<const float*>(rec); hm[e] = *reinterpret_cast<const double*>(rec + 8);
       }
       m = fmaxf(m, hv[e]);

@@ -84,12 +84,19 @@ class CudaVocabBackend:
             _lib.check(_lib.lib().lm_vocab_local(C.byref(a)), "lm_vocab_local")
         return rec
 
-    def merge(self, gathered: torch.Tensor, p: SamplingParams, cap: int, uniforms: Optional[torch.Tensor], step: int, row_offset: int, out=None):
-        shards, rows, _ = gathered.shape
-        dev = gathered.device
+    def merge(self, gathered: Optional[torch.Tensor], p: SamplingParams, cap: int, uniforms: Optional[torch.Tensor], step: int, row_offset: int, out=None,
+              in_place=None):
+        """``gathered`` [shards, rows, record bytes], or ``in_place`` = (device pointer to one 64-bit address per GPU, GPUs, pieces, rows,
+        device): the records read where their GPUs left them (own memory and peer mappings) instead of a gathered copy."""
         a = _lib.VocabArgs()
         a.struct_size = C.sizeof(_lib.VocabArgs)
-        a.rows, a.shards, a.cap, a.records = rows, shards, cap, gathered.data_ptr()
+        if in_place is not None:
+            ptrs, gpus, pieces, rows, dev = in_place
+            a.rows, a.shards, a.cap, a.record_ptrs, a.pieces = rows, gpus * pieces, cap, int(ptrs), pieces
+        else:
+            shards, rows, _ = gathered.shape
+            dev = gathered.device
+            a.rows, a.shards, a.cap, a.records = rows, shards, cap, gathered.data_ptr()
         keep = []
         self._fill(a, p, rows, dev, keep)
         a.flags = _lib.FLAG_TOPP_IN_TOPK if p.topp_in_topk else 0
@@ -120,11 +127,18 @@ class VocabParallelSampler:
     """
 
     def __init__(self, params: SamplingParams, vocab: int, group=None, backend=None, rank: Optional[int] = None, world: Optional[int] = None,
-                 reuse_buffers: bool = False):
+                 reuse_buffers: bool = False, exchange: str = "all_gather"):
         """``reuse_buffers``: keep the record, gather and result tensors between calls of the same shape (a decode loop: no allocation per
         step; a call's results are then overwritten by the next call's)."""
         self.params, self.vocab, self.group = params, int(vocab), group
         self._reuse, self._buffers = bool(reuse_buffers), {}
+        # exchange = "peer": no collective at all. Every rank leaves its records in a buffer that its peers have mapped (symmetric
+        # memory over NVLink), a barrier over the ranks on the stream orders the local steps before the merges, and every rank's merge
+        # reads the peers' records in place. Two buffers in turn: a rank two steps ahead would need to pass a barrier that the rank
+        # still reading has not reached. Falls back to the all-gather where symmetric memory cannot be set up.
+        if exchange not in ("all_gather", "peer"):
+            raise ValueError("exchange is 'all_gather' or 'peer'")
+        self._exchange, self._peer, self._turn = exchange, {}, 0
         self.rank = dist.get_rank(group) if rank is None else rank
         self.world = dist.get_world_size(group) if world is None else world
         self.backend = backend if backend is not None else CudaVocabBackend()
@@ -148,12 +162,46 @@ class VocabParallelSampler:
         if pieces_of is not None and pieces_of(self.world, self.cap, self.shard_width) > 1:
             self.cap = min(self.cap, max(16, (2 * k_max + 7) // 8 * 8))
 
+    def _peer_buffers(self, rows: int, dev):
+        """Two record buffers of this rank that the peers have mapped, their handles, result tensors, pieces; None if that cannot be had."""
+        key = (rows, dev)
+        if key not in self._peer:
+            made = None
+            try:
+                import torch.distributed._symmetric_memory as symm
+                group = self.group if self.group is not None else dist.group.WORLD
+                pieces = self.backend.pieces(self.world, self.cap, self.shard_width, rows)
+                nbytes = pieces * rows * self.backend.record_bytes(self.cap)
+                recs, handles = [], []
+                for _ in range(2):
+                    flat = symm.empty(nbytes, dtype=torch.uint8, device=dev)
+                    handles.append(symm.rendezvous(flat, group))
+                    recs.append(flat.view(pieces * rows, -1))
+                out = (torch.empty(rows, dtype=torch.int32, device=dev), torch.empty(rows, dtype=torch.float32, device=dev),
+                       torch.empty(rows, dtype=torch.int32, device=dev))
+                made = (recs, handles, out, pieces)
+            except Exception:                                                 # no symmetric memory here: the all-gather it is
+                made = None
+            self._peer[key] = made
+        return self._peer[key]
+
     def sample(self, local_logits: torch.Tensor, uniforms: Optional[torch.Tensor] = None, step: int = 0, row_offset: int = 0) -> SampleOutput:
         if local_logits.shape[1] != self.shard_width:
             raise ValueError(f"this rank's shard is {self.shard_width} wide, got {local_logits.shape[1]}")
         if self.params.draw == "inverse_cdf" and uniforms is None:
             raise ValueError("draw='inverse_cdf' needs uniforms [rows]")
         rows = local_logits.shape[0]
+        if self._exchange == "peer" and self.world > 1 and local_logits.is_cuda:
+            peer = self._peer_buffers(rows, local_logits.device)
+            if peer is not None:
+                recs, handles, out, pieces = peer
+                i = self._turn
+                self._turn ^= 1
+                self.backend.local(local_logits, self.shard_start, self.params, self.cap, self.world, out=recs[i])
+                handles[i].barrier(channel=0)                                  # every rank's records of this step are written
+                tokens, tau, status = self.backend.merge(None, self.params, self.cap, uniforms, step, row_offset, out=out,
+                                                         in_place=(handles[i].buffer_ptrs_dev, self.world, pieces, rows, local_logits.device))
+                return SampleOutput(tokens, tau=tau, status=status)
         kept = self._buffers.get((rows, local_logits.device)) if self._reuse else None
         if kept is None:
             rec = self.backend.local(local_logits, self.shard_start, self.params, self.cap, self.world)   # [pieces * rows, record bytes]
