@@ -8,7 +8,10 @@ The reference is single-device, so both modes are new; each is defined by "same 
 * vocab-parallel sampling (``VocabParallelSampler``): every rank holds a contiguous shard of each row's vocabulary; per
   step it computes small records per row (maximum, FP64 softmass, top-k candidates of the shard, or of each piece the shard
   is cut into), all-gathers the records (the only exchange: a few KB per row and rank, NCCL over NVLink), and merges them
-  identically on every rank. The kept set must lie inside the top-k candidates, so ``top_k >= 1`` is required.
+  identically on every rank. The kept set must lie inside the top-k candidates, so ``top_k >= 1`` is required. With
+  ``exchange="peer"`` there is no collective: the records stay in memory that the peers have mapped (symmetric memory), a barrier
+  over the ranks orders the local steps before the merges, and every merge reads the peers' records in place (the results of a call
+  are then overwritten by the next call's).
 
 The compute steps go through a backend object so that the exchange logic can be exercised on CPU ranks (gloo) with a
 stand-in backend; the default backend is the CUDA library and nothing else ships.
