@@ -510,10 +510,37 @@ def _peer_exchange_us(torch, dist, dev, make_sampler, step_of, expect, warmup, n
         same = torch.tensor([int(torch.equal(expect, r.tokens))], device=dev)
         dist.all_reduce(same, op=dist.ReduceOp.MIN)
         dist.all_reduce(used, op=dist.ReduceOp.MIN)
-        return {"us_per_step": 1e3 * float(t.item()), "tokens_equal_single_gpu_on_every_rank": bool(same.item()),
-                "records_read_in_place_from_peers": bool(used.item())}
+        res = {"us_per_step": 1e3 * float(t.item()), "tokens_equal_single_gpu_on_every_rank": bool(same.item()),
+               "records_read_in_place_from_peers": bool(used.item())}
     except Exception as e:                                                  # (the ranks fail together or not at all: the setup is collective)
         return {"unavailable": repr(e)[:200]}
+    try:
+        # the same steps as one CUDA graph per rank (two steps: both record buffers), replayed: without the host's launch path
+        side = torch.cuda.Stream(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(2):
+                    r = step_of(sampler)
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        graph.replay()
+        torch.cuda.synchronize(dev)
+        same = torch.tensor([int(torch.equal(expect, r.tokens))], device=dev)
+        dist.barrier()
+        a.record()
+        for _ in range(n // 2):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([a.elapsed_time(b) / (2 * (n // 2))], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        res["us_per_step_graph"] = 1e3 * float(t.item())
+        res["graph_tokens_equal"] = bool(same.item())
+    except Exception as e:
+        res["graph"] = "unavailable: " + repr(e)[:160]
+    return res
 
 
 def bench_vocab_parallel(torch, dist, lm, dev, rank, world, warmup):
