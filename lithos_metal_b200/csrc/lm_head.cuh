@@ -26,7 +26,8 @@ constexpr int kHeadTile = 16;                // vocabulary rows per warp tile (t
 constexpr int kHeadStep = 64;                // hidden elements per step: 32 bytes per thread and row, a whole 128-byte line per row and quad
 constexpr int kHeadPad = 8;                  // elements between the rows of x in shared memory beyond H: a 16-byte skew, so that the
                                              // 16-byte loads of a quarter warp (two rows, four offsets 32 bytes apart) fall on different banks
-constexpr int kHeadUnroll = 8;               // steps whose loads are in flight together (16 x 16 bytes per thread)
+constexpr int kHeadUnroll = 8;               // steps whose loads are in flight together (32 x 16 bytes per thread): a batch
+constexpr int kHeadMaxBatches = 25;          // batches of the longest row that fits (hidden 12,736)
 
 struct HeadDev {
   const uint16_t* x; int64_t x_stride; int rows;
@@ -89,39 +90,39 @@ __global__ void __launch_bounds__(kHeadThreads) lm_head_kernel(HeadDev P) {
   }
   __syncthreads();
   // ---- the tiles: 16 vocabulary rows per warp and turn
+  // A tile's sums are formed batch by batch (kHeadUnroll steps into a fresh accumulator, then added to the total), the batches in
+  // order: the same additions whether one warp walks the whole row or, for the few tiles left over after the last full round, the
+  // warps of a block take a batch each and one of them adds the partial sums up in that order.
   const int g = lane >> 2, t = lane & 3;
   const int n_tiles = (P.vocab + kHeadTile - 1) / kHeadTile;
+  const int steps = H / kHeadStep, batches = (steps + kHeadUnroll - 1) / kHeadUnroll;
   const uint4* xrow = reinterpret_cast<const uint4*>(xs + g * ld) + 2 * t;  // this thread's 32 bytes of x per step: row g, elements 16 t ..
-  for (int tile = blockIdx.x * kHeadWarps + warp; tile < n_tiles; tile += gridDim.x * kHeadWarps) {
-    const int v0 = tile * kHeadTile;
-    const int ra = min(v0 + g, P.vocab - 1), rb = min(v0 + g + 8, P.vocab - 1);    // (rows beyond the vocabulary: loaded again, never stored)
-    const uint4* wa = reinterpret_cast<const uint4*>(P.w + static_cast<int64_t>(ra) * P.w_stride) + 2 * t;
-    const uint4* wb = reinterpret_cast<const uint4*>(P.w + static_cast<int64_t>(rb) * P.w_stride) + 2 * t;
-    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    const int steps = H / kHeadStep;
-    for (int s0 = 0; s0 < steps; s0 += kHeadUnroll) {
-      uint4 a[kHeadUnroll][2], b[kHeadUnroll][2];
+  auto batch_sum = [&](const uint4* wa, const uint4* wb, int batch, float (&c)[4]) {
+    const int s0 = batch * kHeadUnroll;
+    uint4 a[kHeadUnroll][2], b[kHeadUnroll][2];
 #pragma unroll
-      for (int u = 0; u < kHeadUnroll; u++) {
-        const int s = s0 + u;
-        if (s < steps) {                                             // streamed: every weight is used once
-          a[u][0] = __ldcs(wa + 8 * s); a[u][1] = __ldcs(wa + 8 * s + 1);
-          b[u][0] = __ldcs(wb + 8 * s); b[u][1] = __ldcs(wb + 8 * s + 1);
-        } else { a[u][0] = a[u][1] = b[u][0] = b[u][1] = make_uint4(0u, 0u, 0u, 0u); }
-      }
+    for (int u = 0; u < kHeadUnroll; u++) {
+      const int s = s0 + u;
+      if (s < steps) {                                                    // streamed: every weight is used once
+        a[u][0] = __ldcs(wa + 8 * s); a[u][1] = __ldcs(wa + 8 * s + 1);
+        b[u][0] = __ldcs(wb + 8 * s); b[u][1] = __ldcs(wb + 8 * s + 1);
+      } else { a[u][0] = a[u][1] = b[u][0] = b[u][1] = make_uint4(0u, 0u, 0u, 0u); }
+    }
+    c[0] = c[1] = c[2] = c[3] = 0.0f;
 #pragma unroll
-      for (int u = 0; u < kHeadUnroll; u++) {
-        const int s = s0 + u;
-        if (s >= steps) break;
+    for (int u = 0; u < kHeadUnroll; u++) {
+      const int s = s0 + u;
+      if (s >= steps) break;
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-          const uint4 x = xrow[8 * s + h];
-          mma_bf16_16816(c, a[u][h].x, b[u][h].x, a[u][h].y, b[u][h].y, x.x, x.y);
-          mma_bf16_16816(c, a[u][h].z, b[u][h].z, a[u][h].w, b[u][h].w, x.z, x.w);
-        }
+      for (int h = 0; h < 2; h++) {
+        const uint4 x = xrow[8 * s + h];
+        mma_bf16_16816(c, a[u][h].x, b[u][h].x, a[u][h].y, b[u][h].y, x.x, x.y);
+        mma_bf16_16816(c, a[u][h].z, b[u][h].z, a[u][h].w, b[u][h].w, x.z, x.w);
       }
     }
-    // c[0], c[1]: vocabulary row v0 + g, rows 2 t and 2 t + 1 of x; c[2], c[3]: vocabulary row v0 + g + 8
+  };
+  // c[0], c[1]: vocabulary row v0 + g, rows 2 t and 2 t + 1 of x; c[2], c[3]: vocabulary row v0 + g + 8
+  auto store = [&](int v0, const float (&c)[4]) {
     const int r0 = 2 * t, r1 = 2 * t + 1;
     if (v0 + g < P.vocab) {
       if (r0 < P.rows) P.logits[r0 * P.logits_stride + v0 + g] = f32_to_bf16_rn(c[0]);
@@ -131,6 +132,47 @@ __global__ void __launch_bounds__(kHeadThreads) lm_head_kernel(HeadDev P) {
       if (r0 < P.rows) P.logits[r0 * P.logits_stride + v0 + g + 8] = f32_to_bf16_rn(c[2]);
       if (r1 < P.rows) P.logits[r1 * P.logits_stride + v0 + g + 8] = f32_to_bf16_rn(c[3]);
     }
+  };
+  auto rows_of = [&](int tile, const uint4*& wa, const uint4*& wb) {
+    const int v0 = tile * kHeadTile;
+    const int ra = min(v0 + g, P.vocab - 1), rb = min(v0 + g + 8, P.vocab - 1);    // (rows beyond the vocabulary: loaded again, never stored)
+    wa = reinterpret_cast<const uint4*>(P.w + static_cast<int64_t>(ra) * P.w_stride) + 2 * t;
+    wb = reinterpret_cast<const uint4*>(P.w + static_cast<int64_t>(rb) * P.w_stride) + 2 * t;
+  };
+  const int all_warps = gridDim.x * kHeadWarps;
+  const int full = n_tiles / all_warps * all_warps;                        // tiles of the full rounds: one warp each
+  for (int tile = blockIdx.x * kHeadWarps + warp; tile < full; tile += all_warps) {
+    const uint4 *wa, *wb;
+    rows_of(tile, wa, wb);
+    float total[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c[4];
+    for (int batch = 0; batch < batches; batch++) {
+      batch_sum(wa, wb, batch, c);
+#pragma unroll
+      for (int e = 0; e < 4; e++) total[e] = __fadd_rn(total[e], c[e]);
+    }
+    store(tile * kHeadTile, total);
+  }
+  // the tiles left over: one block each, a batch per warp and turn, the partial sums added up in batch order by warp 0
+  __shared__ float part[kHeadMaxBatches][32][4];
+  for (int tile = full + blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const uint4 *wa, *wb;
+    rows_of(tile, wa, wb);
+    for (int batch = warp; batch < batches; batch += kHeadWarps) {
+      float c[4];
+      batch_sum(wa, wb, batch, c);
+#pragma unroll
+      for (int e = 0; e < 4; e++) part[batch][lane][e] = c[e];
+    }
+    __syncthreads();
+    if (warp == 0) {
+      float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      for (int batch = 0; batch < batches; batch++) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) total[e] = __fadd_rn(total[e], part[batch][lane][e]);
+      }
+      store(tile * kHeadTile, total);
+    }
+    __syncthreads();
   }
 }
 
